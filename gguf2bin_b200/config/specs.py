@@ -1,0 +1,94 @@
+"""Typed descriptions of a model: which parts each layer is made of, and in which
+order layers run.
+
+A ``ModelSpec`` is pure data.  It is what an architecture's configuration reader
+produces from ``config.json`` and what the engine builds a model from.  Every size
+and constant of a part lives in that part's spec; nothing about the parts is
+implied by the architecture's name.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Mapping, Optional
+
+
+class ConfigError(ValueError):
+    """A configuration that cannot be built, with the reason."""
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """A part chosen by ``kind`` (a name in that part family's registry) with its
+    parameters.  ``params`` holds only plain values so that specs compare and hash."""
+    kind: str
+    params: tuple = ()
+
+    @staticmethod
+    def make(kind: str, **params: Any) -> "PartSpec":
+        return PartSpec(kind, tuple(sorted(params.items())))
+
+    def get(self, key: str, default: Any = None) -> Any:
+        for k, v in self.params:
+            if k == key:
+                return v
+        return default
+
+    def __getitem__(self, key: str) -> Any:
+        for k, v in self.params:
+            if k == key:
+                return v
+        raise KeyError(f"{self.kind} spec has no parameter {key!r}")
+
+    def as_dict(self) -> dict:
+        return dict(self.params)
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """One layer: a block arrangement around a mixer and a feed-forward, the norm
+    used in the block, and the tensor-name prefix of the layer in the checkpoint."""
+    block: PartSpec
+    mixer: PartSpec
+    feed_forward: PartSpec
+    norm: PartSpec
+    prefix: str
+
+
+@dataclass(frozen=True)
+class ScheduleEntry:
+    """One execution of a layer.  ``cache_of`` names the layer whose cache storage
+    this execution reads and writes (itself by default); a layer that lists another
+    layer there owns no storage."""
+    layer: int
+    cache_of: Optional[int] = None
+
+    @property
+    def cache_layer(self) -> int:
+        return self.layer if self.cache_of is None else self.cache_of
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    architecture: str
+    hidden_size: int
+    vocab_size: int
+    max_positions: int
+    layers: tuple                     # tuple[LayerSpec, ...]
+    schedule: tuple                   # tuple[ScheduleEntry, ...]
+    embedding: PartSpec               # kind "token_embedding"
+    final_norm: PartSpec
+    head: PartSpec                    # kind "lm_head" (tied or own matrix)
+    stop_token_ids: tuple = ()
+    source: Mapping[str, Any] = field(default_factory=dict, compare=False, hash=False)
+
+    def validate(self) -> None:
+        if self.hidden_size <= 0 or self.vocab_size <= 0 or self.max_positions <= 0:
+            raise ConfigError("hidden_size, vocab_size and max_positions must be positive")
+        if self.vocab_size >= 2 ** 31:
+            raise ConfigError("vocab_size does not fit a 32-bit token id")
+        if not self.layers or not self.schedule:
+            raise ConfigError("a model needs at least one layer and one schedule entry")
+        n = len(self.layers)
+        for e in self.schedule:
+            if not (0 <= e.layer < n) or not (0 <= e.cache_layer < n):
+                raise ConfigError(f"schedule entry {e} names a layer outside 0..{n - 1}")

@@ -1,0 +1,81 @@
+// Shared helpers of the sm_100a kernels: element conversion, warp and block
+// reductions, and the error channel of the C launchers.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+typedef __nv_bfloat16 bf16;
+
+// ---- error channel ---------------------------------------------------------
+// Every launcher returns 0 on success.  On a refusal (sizes a kernel does not take)
+// or a CUDA launch error it returns non-zero and leaves a message that
+// g2b_last_error() of the same shared object returns.
+static thread_local char g2b_error_text[512] = "";
+
+#define G2B_REFUSE(...)                                                   \
+  do {                                                                    \
+    snprintf(g2b_error_text, sizeof(g2b_error_text), __VA_ARGS__);        \
+    return 1;                                                             \
+  } while (0)
+
+static inline int g2b_check_launch(const char *what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    snprintf(g2b_error_text, sizeof(g2b_error_text), "%s: %s", what, cudaGetErrorString(e));
+    return 2;
+  }
+  return 0;
+}
+
+#define G2B_DEFINE_LAST_ERROR \
+  extern "C" const char *g2b_last_error() { return g2b_error_text; }
+
+// element type codes used by the launchers
+enum { G2B_F32 = 0, G2B_BF16 = 1 };
+
+// ---- conversion ------------------------------------------------------------
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// ---- reductions ------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The order of
+// the additions depends only on the block size.  `scratch` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float *scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < n_warps) ? scratch[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float *scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_warps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < n_warps) ? scratch[lane] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}

@@ -1,0 +1,273 @@
+// Memory-bound kernels of the step: embedding rows, RMSNorm (optionally on gathered
+// rows), fused per-head RMSNorm + half-split rotation + cache write, the cache write
+// alone, and the SiLU gate.  All statistics, angles and products are 32-bit.
+//
+// Formulas (paths relative to AnonymoDGH/gguf2bin):
+//   embedding      src/l5_model.c:488-491
+//   rmsnorm        src/l3_math.c:34-36,49      o_j = (w_j * x_j) * 1/sqrt(sum x^2 / n + eps)
+//   per-head norm  src/l3_math.c:107-114
+//   rotation       src/l3_math.c:84-102        pairs (j, j+half), ang = pos * freq_j
+//   cache write    src/l5_model.c:232-247      K after norm and rotation, V raw
+//   SiLU gate      src/l3_math.c:57-62, src/l5_model.c:594-595
+#include "common.cuh"
+
+G2B_DEFINE_LAST_ERROR
+
+// ---------------------------------------------------------------------------
+// embedding: out[t, :] = table[ids[t], :]   (out is the 32-bit residual stream)
+// ---------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_rows_kernel(const TW *__restrict__ table, const int *__restrict__ ids,
+                                  float *__restrict__ out, int H, int V) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  const bool ok = (id >= 0 && id < V);
+  if (!ok) id = 0;                                   // host validates ids; never read outside
+  const TW *row = table + (size_t)id * H;
+  float *o = out + (size_t)t * H;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = ok ? to_f32(row[j]) : 0.f;
+}
+
+extern "C" int g2b_embed_rows(const void *table, int table_dtype, const int *ids, float *out,
+                              int T, int H, int V, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || V <= 0) G2B_REFUSE("embed_rows: bad sizes H=%d V=%d", H, V);
+  const int threads = H >= 256 ? 256 : 64;
+  if (table_dtype == G2B_F32)
+    embed_rows_kernel<float><<<T, threads, 0, stream>>>((const float *)table, ids, out, H, V);
+  else if (table_dtype == G2B_BF16)
+    embed_rows_kernel<bf16><<<T, threads, 0, stream>>>((const bf16 *)table, ids, out, H, V);
+  else
+    G2B_REFUSE("embed_rows: unknown table dtype %d", table_dtype);
+  return g2b_check_launch("embed_rows");
+}
+
+// ---------------------------------------------------------------------------
+// rmsnorm over rows of the 32-bit stream; rows == nullptr means rows 0..n_rows-1
+// ---------------------------------------------------------------------------
+template <typename TO>
+__global__ void rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ w,
+                               const int *__restrict__ rows, TO *__restrict__ out, int H,
+                               float eps) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const float *xr = x + (size_t)(rows ? rows[r] : r) * H;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    const float v = xr[j];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)H + eps);
+  TO *o = out + (size_t)r * H;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = from_f32<TO>((w[j] * xr[j]) * inv);
+}
+
+extern "C" int g2b_rmsnorm(const float *x, const float *w, const int *rows, int n_rows, int H,
+                           float eps, void *out, int out_dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (H <= 0) G2B_REFUSE("rmsnorm: bad width %d", H);
+  const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 32);
+  if (out_dtype == G2B_F32)
+    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, w, rows, (float *)out, H, eps);
+  else if (out_dtype == G2B_BF16)
+    rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, w, rows, (bf16 *)out, H, eps);
+  else
+    G2B_REFUSE("rmsnorm: unknown output dtype %d", out_dtype);
+  return g2b_check_launch("rmsnorm");
+}
+
+// ---------------------------------------------------------------------------
+// per-head norm + rotation + cache write.  One warp per (token, head) of the fused
+// projection output qkv[t] = [q heads | k heads | v heads].
+//   q heads: norm (if q_w), rotate (if inv_freq)  -> q_out[t, h*hd + j]
+//   k heads: norm (if k_w), rotate (if inv_freq)  -> cache K, or k_out when given
+//   v heads: copied                                -> cache V, or v_out when given
+// Cache of one layer: [n_pages][2][nkv][page_size][hd]; the page of position p of
+// sequence b is page_table[b*P + p/page_size].
+// ---------------------------------------------------------------------------
+#define QKN_MAX_HD 512
+#define QKN_WARPS 4
+
+template <typename T>
+__global__ void qknorm_rope_cache_kernel(
+    const T *__restrict__ qkv, int T_tokens, int nh, int nkv, int hd,
+    const float *__restrict__ q_w, const float *__restrict__ k_w, float eps,
+    const float *__restrict__ inv_freq, int rot_dim,
+    const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
+    const int *__restrict__ page_table, int P, T *__restrict__ cache, int page_size,
+    T *__restrict__ q_out, T *__restrict__ k_out, T *__restrict__ v_out) {
+  __shared__ float buf[QKN_WARPS][QKN_MAX_HD];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = nh + 2 * nkv;
+  const long long item = (long long)blockIdx.x * QKN_WARPS + warp;
+  if (item >= (long long)T_tokens * heads) return;
+  const int t = (int)(item / heads), h = (int)(item % heads);
+  const T *src = qkv + (size_t)t * heads * hd + (size_t)h * hd;
+  float *x = buf[warp];
+
+  const int kind = h < nh ? 0 : (h < nh + nkv ? 1 : 2);       // 0 q, 1 k, 2 v
+  const float *w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
+
+  float ss = 0.f;
+  for (int j = lane; j < hd; j += 32) {
+    const float v = to_f32(src[j]);
+    x[j] = v;
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  __syncwarp();
+  if (w) {
+    const float inv = 1.f / sqrtf(ss / (float)hd + eps);
+    for (int j = lane; j < hd; j += 32) x[j] = (w[j] * x[j]) * inv;
+    __syncwarp();
+  }
+  const int pos = tok_pos[t];
+  if (kind != 2 && inv_freq) {
+    const int half = rot_dim >> 1;
+    for (int j = lane; j < half; j += 32) {
+      const float ang = (float)pos * inv_freq[j];
+      float s, c;
+      sincosf(ang, &s, &c);
+      const float a = x[j], b = x[j + half];
+      x[j] = a * c - b * s;
+      x[j + half] = a * s + b * c;
+    }
+    __syncwarp();
+  }
+
+  T *dst;
+  if (kind == 0) {
+    dst = q_out + (size_t)t * nh * hd + (size_t)h * hd;
+  } else {
+    const int kvh = kind == 1 ? h - nh : h - nh - nkv;
+    T *flat = kind == 1 ? k_out : v_out;
+    if (flat) {
+      dst = flat + (size_t)t * nkv * hd + (size_t)kvh * hd;
+    } else {
+      const int page = page_table[(size_t)tok_seq[t] * P + pos / page_size];
+      dst = cache + ((((size_t)page * 2 + (kind - 1)) * nkv + kvh) * page_size + pos % page_size) * hd;
+    }
+  }
+  for (int j = lane; j < hd; j += 32) dst[j] = from_f32<T>(x[j]);
+}
+
+extern "C" int g2b_qknorm_rope_cache(const void *qkv, int dtype, int T_tokens, int nh, int nkv,
+                                     int hd, const float *q_w, const float *k_w, float eps,
+                                     const float *inv_freq, int rot_dim, const int *tok_pos,
+                                     const int *tok_seq, const int *page_table, int P,
+                                     void *cache, int page_size, void *q_out, void *k_out,
+                                     void *v_out, cudaStream_t stream) {
+  if (T_tokens <= 0) return 0;
+  if (hd <= 0 || hd > QKN_MAX_HD)
+    G2B_REFUSE("qknorm_rope_cache: head_dim %d outside 1..%d", hd, QKN_MAX_HD);
+  if (inv_freq && (rot_dim <= 0 || rot_dim > hd || (rot_dim & 1)))
+    G2B_REFUSE("qknorm_rope_cache: rotary_dim %d must be even and at most head_dim %d", rot_dim, hd);
+  if ((k_out == nullptr) != (v_out == nullptr))
+    G2B_REFUSE("qknorm_rope_cache: k_out and v_out must be given together");
+  if (!k_out && (!cache || !page_table || page_size <= 0))
+    G2B_REFUSE("qknorm_rope_cache: no cache to write to");
+  const long long items = (long long)T_tokens * (nh + 2 * nkv);
+  const unsigned blocks = (unsigned)((items + QKN_WARPS - 1) / QKN_WARPS);
+  if (dtype == G2B_F32)
+    qknorm_rope_cache_kernel<float><<<blocks, QKN_WARPS * 32, 0, stream>>>(
+        (const float *)qkv, T_tokens, nh, nkv, hd, q_w, k_w, eps, inv_freq, rot_dim, tok_pos,
+        tok_seq, page_table, P, (float *)cache, page_size, (float *)q_out, (float *)k_out,
+        (float *)v_out);
+  else if (dtype == G2B_BF16)
+    qknorm_rope_cache_kernel<bf16><<<blocks, QKN_WARPS * 32, 0, stream>>>(
+        (const bf16 *)qkv, T_tokens, nh, nkv, hd, q_w, k_w, eps, inv_freq, rot_dim, tok_pos,
+        tok_seq, page_table, P, (bf16 *)cache, page_size, (bf16 *)q_out, (bf16 *)k_out,
+        (bf16 *)v_out);
+  else
+    G2B_REFUSE("qknorm_rope_cache: unknown dtype %d", dtype);
+  return g2b_check_launch("qknorm_rope_cache");
+}
+
+// ---------------------------------------------------------------------------
+// cache write alone: k, v [T, nkv*hd] -> the layer's pages
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void cache_write_kernel(const T *__restrict__ k, const T *__restrict__ v, int nkv,
+                                   int hd, const int *__restrict__ tok_pos,
+                                   const int *__restrict__ tok_seq,
+                                   const int *__restrict__ page_table, int P,
+                                   T *__restrict__ cache, int page_size) {
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  const int page = page_table[(size_t)tok_seq[t] * P + pos / page_size];
+  const int n = nkv * hd;
+  for (int i = threadIdx.x; i < 2 * n; i += blockDim.x) {
+    const int which = i / n, r = i % n, kvh = r / hd, j = r % hd;
+    const T val = (which == 0 ? k : v)[(size_t)t * n + r];
+    cache[((((size_t)page * 2 + which) * nkv + kvh) * page_size + pos % page_size) * hd + j] = val;
+  }
+}
+
+extern "C" int g2b_cache_write(const void *k, const void *v, int dtype, int T_tokens, int nkv,
+                               int hd, const int *tok_pos, const int *tok_seq,
+                               const int *page_table, int P, void *cache, int page_size,
+                               cudaStream_t stream) {
+  if (T_tokens <= 0) return 0;
+  if (dtype == G2B_F32)
+    cache_write_kernel<float><<<T_tokens, 128, 0, stream>>>(
+        (const float *)k, (const float *)v, nkv, hd, tok_pos, tok_seq, page_table, P,
+        (float *)cache, page_size);
+  else if (dtype == G2B_BF16)
+    cache_write_kernel<bf16><<<T_tokens, 128, 0, stream>>>(
+        (const bf16 *)k, (const bf16 *)v, nkv, hd, tok_pos, tok_seq, page_table, P, (bf16 *)cache,
+        page_size);
+  else
+    G2B_REFUSE("cache_write: unknown dtype %d", dtype);
+  return g2b_check_launch("cache_write");
+}
+
+// ---------------------------------------------------------------------------
+// SiLU gate on a fused gate/up projection.  Rows of the fused matrix alternate in
+// blocks of `blk`: columns [2*blk*b, 2*blk*b+blk) are gate_{blk*b ..}, the next blk are
+// up_{blk*b ..}; blk == I means "all gates, then all ups".
+//   out[t, i] = (g / (1 + exp(-g))) * u
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T *__restrict__ gu, T *__restrict__ out, long long total,
+                              int I, int blk) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long long t = idx / I;
+  const int i = (int)(idx % I);
+  const int b = i / blk, r = i % blk;
+  const T *row = gu + (size_t)t * 2 * I;
+  const float g = to_f32(row[(size_t)2 * blk * b + r]);
+  const float u = to_f32(row[(size_t)2 * blk * b + blk + r]);
+  out[idx] = from_f32<T>((g / (1.f + expf(-g))) * u);
+}
+
+extern "C" int g2b_swiglu(const void *gu, int dtype, int T_tokens, int I, int blk, void *out,
+                          cudaStream_t stream) {
+  if (T_tokens <= 0) return 0;
+  if (I <= 0 || blk <= 0 || I % blk) G2B_REFUSE("swiglu: block %d does not divide width %d", blk, I);
+  const long long total = (long long)T_tokens * I;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == G2B_F32)
+    swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float *)gu, (float *)out, total, I, blk);
+  else if (dtype == G2B_BF16)
+    swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16 *)gu, (bf16 *)out, total, I, blk);
+  else
+    G2B_REFUSE("swiglu: unknown dtype %d", dtype);
+  return g2b_check_launch("swiglu");
+}
+
+// ---------------------------------------------------------------------------
+// decode bookkeeping on the device, for steps replayed from a CUDA graph:
+// positions advance by one.
+// ---------------------------------------------------------------------------
+__global__ void advance_positions_kernel(int *tok_pos, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) tok_pos[i] += 1;
+}
+
+extern "C" int g2b_advance_positions(int *tok_pos, int n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  advance_positions_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tok_pos, n);
+  return g2b_check_launch("advance_positions");
+}

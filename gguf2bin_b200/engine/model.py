@@ -1,0 +1,137 @@
+"""A model: parts built from a ``ModelSpec``, weights bound by name, and the forward
+pass of one step over the residual stream.
+
+The forward pass is the reference's (src/l5_model.c:488-605 of AnonymoDGH/gguf2bin):
+embedding rows, the scheduled layers, final norm and lm_head — the last two only on the
+rows whose logits are wanted.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+from .. import kernels
+from ..cache.storage import Cache
+from ..config import ModelSpec, model_spec_from_folder
+from ..config.specs import ConfigError
+from ..parts import block_class, norm_class
+from ..parts.base import StepContext
+from ..weights.loader import Expected, load_weights
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise ConfigError(f"dtype must be bfloat16 or float32, got {dtype!r}") from None
+
+
+def expected_tensors(spec: ModelSpec) -> dict:
+    """Every tensor the model needs, by checkpoint name."""
+    out = {spec.embedding["name"]: Expected((spec.vocab_size, spec.hidden_size))}
+    out.update(norm_class(spec.final_norm).expected(spec.final_norm, spec.hidden_size,
+                                                    spec.final_norm["name"]))
+    out[spec.head["name"]] = Expected((spec.vocab_size, spec.hidden_size),
+                                      optional=bool(spec.head["tied"]))
+    for layer in spec.layers:
+        for name, e in block_class(layer.block).expected(layer, spec.hidden_size).items():
+            out[layer.prefix + name] = e
+    return out
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, dtype="bfloat16", device="cuda:0"):
+        spec.validate()
+        self.spec = spec
+        self.dtype = parse_dtype(dtype)
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise kernels.KernelError("the engine runs on a CUDA device only (no CPU path)")
+        self.hidden, self.vocab = spec.hidden_size, spec.vocab_size
+        self.blocks = [block_class(l.block)(l, spec.hidden_size, self.dtype, self.device)
+                       for l in spec.layers]
+        self.final_norm = norm_class(spec.final_norm)(spec.final_norm, spec.hidden_size,
+                                                      self.dtype, self.device)
+        self.embedding = None
+        self.head = None
+        self.n_params = 0
+
+    # ---- construction ---------------------------------------------------------
+    @classmethod
+    def from_folder(cls, folder, dtype="bfloat16", device="cuda:0") -> "Model":
+        """The model class comes from config.json's architecture through the registry."""
+        spec = model_spec_from_folder(folder)
+        model = cls(spec, dtype, device)
+        tensors = load_weights(Path(folder), expected_tensors(spec), model.dtype, model.device)
+        model.bind(tensors)
+        return model
+
+    def bind(self, tensors: dict) -> None:
+        spec = self.spec
+        self.n_params = sum(t.numel() for t in tensors.values())
+        self.embedding = tensors[spec.embedding["name"]].contiguous()
+        if spec.head["tied"]:
+            self.head = self.embedding           # src/l5_model.c:602-603: no output matrix
+        else:
+            self.head = tensors[spec.head["name"]].contiguous()
+        self.final_norm.bind(tensors[spec.final_norm["name"]])
+        for layer, block in zip(spec.layers, self.blocks):
+            n = len(layer.prefix)
+            block.bind({k[n:]: v for k, v in tensors.items() if k.startswith(layer.prefix)})
+
+    # ---- cache ----------------------------------------------------------------
+    def cache_needs(self) -> list:
+        """The need of each layer that owns cache storage (None for the others)."""
+        owners = {e.cache_layer for e in self.spec.schedule}
+        return [b.cache_need() if i in owners else None for i, b in enumerate(self.blocks)]
+
+    def new_cache(self, max_tokens: int, max_seqs: Optional[int] = None) -> Cache:
+        return Cache(self.cache_needs(), max_tokens, self.dtype, self.device, max_seqs)
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        for t in self._all_weights():
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+        return total
+
+    def _all_weights(self):
+        yield self.embedding
+        yield self.head
+        for b in self.blocks:
+            for part in (b.mixer, b.feed_forward):
+                for v in vars(part).values():
+                    if isinstance(v, torch.Tensor) and v.dim() == 2:
+                        yield v
+
+    def describe(self) -> str:
+        s = self.spec
+        return (f"{s.architecture}: {len(s.layers)} layers, width {s.hidden_size}, vocab "
+                f"{s.vocab_size}, {self.n_params / 1e6:.1f} M parameters, "
+                f"{self.weight_bytes() / 2**20:.1f} MiB, compute {self.dtype}")
+
+    # ---- one step ---------------------------------------------------------------
+    def forward(self, ctx: StepContext, cache: Cache, want_rows: Optional[torch.Tensor],
+                n_want: int, logits_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """Runs the step's tokens through the scheduled layers.  ``want_rows`` (int32
+        [n_want]) are the token indices whose logits are returned as float32 [n_want, V];
+        with ``n_want == 0`` only the cache is updated."""
+        ws = ctx.workspace
+        x = ws.buffer("stream", (ctx.n_tokens, self.hidden), torch.float32)
+        kernels.embed_rows(self.embedding, ctx.tok_ids[:ctx.n_tokens], x)
+        for entry in self.spec.schedule:
+            self.blocks[entry.layer].forward(x, ctx, cache.view(entry.cache_layer))
+        if n_want == 0:
+            return None
+        xn = ws.buffer("head.normed", (n_want, self.hidden), self.dtype)
+        self.final_norm.forward(x, xn, rows=want_rows)
+        logits = logits_out if logits_out is not None else \
+            ws.buffer("head.logits", (n_want, self.vocab), torch.float32)
+        kernels.linear(xn, self.head, logits)
+        return logits

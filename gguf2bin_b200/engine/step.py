@@ -1,0 +1,146 @@
+"""The step function: a batch of sequences, their next tokens, the cache, the logits at
+the wanted places.
+
+A step runs only the tokens it is given, as one ragged batch: the tokens of all
+sequences one after another, each token with its own absolute position, no padding
+anywhere (so padding cannot change a result).  Sequences of a step may be at any
+position: all prompts at once, then one token each, or a prompt cut into pieces.
+
+Before anything is launched the whole step is checked on the host (token ids, room in
+the cache, positions); a refused step changes nothing.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional, Sequence as Seq
+
+import numpy as np
+import torch
+
+from ..cache.pool import CacheError, Sequence
+from ..cache.storage import Cache
+from ..parts.base import StepContext
+from .model import Model
+from .workspace import Workspace
+
+
+class StepError(ValueError):
+    """A step that cannot run; nothing was changed."""
+
+
+@dataclass
+class StepEntry:
+    """One sequence's share of a step: its next tokens and the indices among them whose
+    logits are wanted."""
+    seq: Sequence
+    tokens: Seq[int]
+    want: Seq[int] = field(default_factory=tuple)
+
+
+class Engine:
+    """A model with its cache and scratch memory; ``step`` is the one way tokens run."""
+
+    def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None):
+        self.model = model
+        self.cache: Cache = model.new_cache(max_tokens, max_seqs)
+        self.workspace = Workspace(model.device)
+        self.device = model.device
+        self._meta_cap = 0
+        self._meta_dev: Optional[torch.Tensor] = None
+        self._meta_host: Optional[torch.Tensor] = None
+
+    # ---- sequences -----------------------------------------------------------
+    def open_sequence(self) -> Sequence:
+        return self.cache.open_sequence()
+
+    def close_sequence(self, seq: Sequence) -> None:
+        self.cache.close_sequence(seq)
+
+    # ---- step ------------------------------------------------------------------
+    def _check(self, entries: Seq[StepEntry]) -> None:
+        if not entries:
+            raise StepError("a step needs at least one sequence")
+        V, maxpos = self.model.vocab, self.model.spec.max_positions
+        seen = set()
+        for e in entries:
+            if e.seq.slot < 0 or self.cache.table.live.get(e.seq.slot) is not e.seq:
+                raise StepError("a sequence of the step is not live in this engine's cache")
+            if e.seq.slot in seen:
+                raise StepError(f"slot {e.seq.slot} appears twice in one step")
+            seen.add(e.seq.slot)
+            n = len(e.tokens)
+            if n < 1:
+                raise StepError("every sequence of a step needs at least one token")
+            for t in e.tokens:
+                if not (0 <= int(t) < V):
+                    raise StepError(f"token id {t} outside the vocabulary 0..{V - 1}")
+            if e.seq.length + n > maxpos:
+                raise StepError(f"sequence would reach {e.seq.length + n} positions; the model "
+                                f"allows {maxpos}")
+            for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise StepError(f"wanted place {w} outside the step's {n} tokens")
+        need = sum(self.cache.table.pages_needed(e.seq, e.seq.length + len(e.tokens))
+                   for e in entries)
+        if need > self.cache.table.pages.n_free:
+            raise StepError(f"the cache is full: the step needs {need} more pages of "
+                            f"{self.cache.page_size} tokens, {self.cache.table.pages.n_free} free")
+
+    def build_context(self, entries: Seq[StepEntry]) -> tuple[StepContext, torch.Tensor, int]:
+        """Host metadata of the step packed into one pinned buffer and copied once."""
+        B = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        past = [e.seq.length for e in entries]
+        T = sum(q_lens)
+        P = max(len(e.seq.pages) for e in entries)
+        n_want = sum(len(e.want) for e in entries)
+        # layout: tok_ids[T] tok_pos[T] tok_seq[T] want[n_want] seq_meta[B*4] page_table[B*P]
+        total = 3 * T + n_want + 4 * B + B * P
+        if total > self._meta_cap:
+            self._meta_cap = max(2 * total, 1024)
+            self._meta_dev = torch.empty(self._meta_cap, dtype=torch.int32, device=self.device)
+            self._meta_host = torch.empty(self._meta_cap, dtype=torch.int32, pin_memory=True)
+        host = self._meta_host.numpy()
+        o_ids, o_pos, o_seq, o_want = 0, T, 2 * T, 3 * T
+        o_meta = o_want + n_want
+        o_pt = o_meta + 4 * B
+        t0 = w0 = 0
+        for b, e in enumerate(entries):
+            n = q_lens[b]
+            host[o_ids + t0:o_ids + t0 + n] = np.asarray(e.tokens, dtype=np.int32)
+            host[o_pos + t0:o_pos + t0 + n] = np.arange(past[b], past[b] + n, dtype=np.int32)
+            host[o_seq + t0:o_seq + t0 + n] = b
+            for w in e.want:
+                host[o_want + w0] = t0 + int(w)
+                w0 += 1
+            host[o_meta + 4 * b:o_meta + 4 * b + 4] = (t0, n, past[b], e.seq.slot)
+            row = host[o_pt + b * P:o_pt + (b + 1) * P]
+            row[:len(e.seq.pages)] = e.seq.pages
+            row[len(e.seq.pages):] = 0
+            t0 += n
+        dev = self._meta_dev
+        dev[:total].copy_(self._meta_host[:total], non_blocking=True)
+        ctx = StepContext(
+            n_tokens=T, n_seqs=B, tok_ids=dev[o_ids:o_ids + T], tok_pos=dev[o_pos:o_pos + T],
+            tok_seq=dev[o_seq:o_seq + T], page_table=dev[o_pt:o_pt + B * P].view(B, P),
+            page_size=self.cache.page_size, workspace=self.workspace, dtype=self.model.dtype,
+            q_lens=q_lens, past_lens=past, slots=[e.seq.slot for e in entries],
+            max_kv_len=max(p + n for p, n in zip(past, q_lens)),
+            seq_meta=dev[o_meta:o_meta + 4 * B].view(B, 4))
+        return ctx, dev[o_want:o_want + n_want], n_want
+
+    def step(self, entries: Seq[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs the entries' tokens as one batch.  Returns float32 logits
+        [number of wanted places, vocab] in the order of the entries and of their
+        ``want`` (None when nothing is wanted).  The tensor is scratch memory: it is
+        valid until the next step."""
+        self._check(entries)
+        for e in entries:
+            self.cache.reserve(e.seq, e.seq.length + len(e.tokens))
+        # the pinned staging buffer is reused: the previous step's copy must be over
+        torch.cuda.current_stream().synchronize()
+        ctx, want_rows, n_want = self.build_context(entries)
+        logits = self.model.forward(ctx, self.cache, want_rows, n_want)
+        for e in entries:
+            e.seq.length += len(e.tokens)
+        return logits

@@ -1,0 +1,28 @@
+"""Scratch memory of a step: named device buffers that grow to the largest request and
+are then reused, so that steady-state steps allocate nothing (which is also what lets a
+step be captured in a CUDA graph)."""
+from __future__ import annotations
+
+import torch
+
+
+class Workspace:
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self._buffers: dict[str, torch.Tensor] = {}
+
+    def buffer(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        raw = self._buffers.get(name)
+        if raw is None or raw.numel() < nbytes:
+            # room to spare, so a slowly growing batch does not reallocate every step
+            cap = max(nbytes, 256) if raw is None else max(nbytes, 2 * raw.numel())
+            raw = torch.empty(cap, dtype=torch.uint8, device=self.device)
+            self._buffers[name] = raw
+        return raw[:nbytes].view(dtype).view(*shape)
+
+    def bytes(self) -> int:
+        return sum(b.numel() for b in self._buffers.values())

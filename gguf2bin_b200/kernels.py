@@ -1,0 +1,260 @@
+"""Python bindings of the CUDA kernels (ctypes over the C launchers of ``csrc/``).
+
+Every function takes CUDA tensors, launches on the current torch stream and returns
+nothing or its output tensor.  There is no CPU path: a tensor that is not on a CUDA
+device raises ``KernelError``, and a missing or unbuildable extension raises
+``KernelBuildError`` at the first call.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+from .csrc.build import KernelBuildError, KernelError, load_unit
+
+__all__ = ["KernelError", "KernelBuildError", "embed_rows", "rmsnorm", "qknorm_rope_cache",
+           "cache_write", "swiglu", "advance_positions", "gemm_simt", "linear", "attn_generic",
+           "attention", "sample_rows", "sample_filtered", "seed_slots"]
+
+F32, BF16 = 0, 1
+EPI_STORE_F32, EPI_STORE_BF16, EPI_ACCUM_F32 = 0, 1, 2
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, not {dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("kernel called with a tensor that is not on a CUDA device "
+                          "(there is no CPU path)")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t: torch.Tensor, dtype: torch.dtype, what: str) -> None:
+    if t.dtype != dtype:
+        raise KernelError(f"{what} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{what} must be contiguous")
+
+
+_fn_cache: dict = {}
+
+
+def _fn(unit: str, name: str, argtypes, defines=()):
+    key = (unit, name, tuple(defines))
+    f = _fn_cache.get(key)
+    if f is None:
+        lib = load_unit(unit, defines)
+        f = getattr(lib, name)
+        f.argtypes = argtypes
+        f.restype = c_int
+        f._lib = lib
+        _fn_cache[key] = f
+    return f
+
+
+def _call(f, *args) -> None:
+    rc = f(*args)
+    if rc != 0:
+        raise KernelError(f._lib.g2b_last_error().decode("utf-8", "replace"))
+
+
+# ---------------------------------------------------------------------------
+# elementwise.cu
+# ---------------------------------------------------------------------------
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = table[ids[t]] widened to float32.  ids int32 [T], out float32 [T, H]."""
+    _need(ids, torch.int32, "ids")
+    _need(out, torch.float32, "out")
+    V, H = table.shape
+    f = _fn("elementwise.cu", "g2b_embed_rows",
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _call(f, _ptr(table), _code(table.dtype), _ptr(ids), _ptr(out), out.shape[0], H, V, _stream())
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = (w * x[row_r]) / sqrt(mean(x[row_r]^2) + eps); x, w float32; statistics in
+    float32.  ``rows`` (int32) gathers rows of x; out has one row per gathered row."""
+    _need(x, torch.float32, "x")
+    _need(w, torch.float32, "norm weight")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    n_rows, H = out.shape
+    f = _fn("elementwise.cu", "g2b_rmsnorm",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p])
+    _call(f, _ptr(x), _ptr(w), _ptr(rows), n_rows, H, eps, _ptr(out), _code(out.dtype), _stream())
+
+
+def qknorm_rope_cache(qkv, n_heads, n_kv_heads, head_dim, q_w, k_w, eps, inv_freq, rotary_dim,
+                      tok_pos, tok_seq, page_table, cache_pages, page_size, q_out,
+                      k_out=None, v_out=None) -> None:
+    """Per-head RMSNorm of the q and k heads (when q_w / k_w are given), half-split
+    rotation by ``pos * inv_freq`` (when inv_freq is given), q to ``q_out``; k and v to
+    the layer's cache pages, or to ``k_out`` / ``v_out`` when those are given."""
+    T = qkv.shape[0]
+    f = _fn("elementwise.cu", "g2b_qknorm_rope_cache",
+            [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
+             c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+             c_void_p, c_void_p])
+    P = page_table.shape[1] if page_table is not None else 0
+    for t in (q_out, k_out, v_out, cache_pages):
+        if t is not None and t.dtype != qkv.dtype:
+            raise KernelError("qknorm_rope_cache: outputs and cache must have the input's dtype")
+    _call(f, _ptr(qkv), _code(qkv.dtype), T, n_heads, n_kv_heads, head_dim, _ptr(q_w), _ptr(k_w),
+          eps, _ptr(inv_freq), rotary_dim, _ptr(tok_pos), _ptr(tok_seq), _ptr(page_table), P,
+          _ptr(cache_pages), page_size, _ptr(q_out), _ptr(k_out), _ptr(v_out), _stream())
+
+
+def cache_write(k, v, n_kv_heads, head_dim, tok_pos, tok_seq, page_table, cache_pages,
+                page_size) -> None:
+    """k, v [T, n_kv_heads*head_dim] into the layer's cache pages at each token's position."""
+    f = _fn("elementwise.cu", "g2b_cache_write",
+            [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+             c_void_p, c_int, c_void_p])
+    if k.dtype != cache_pages.dtype or v.dtype != cache_pages.dtype:
+        raise KernelError("cache_write: k, v and the cache must have one dtype")
+    _call(f, _ptr(k.contiguous()), _ptr(v.contiguous()), _code(k.dtype), k.shape[0], n_kv_heads,
+          head_dim, _ptr(tok_pos), _ptr(tok_seq), _ptr(page_table), page_table.shape[1],
+          _ptr(cache_pages), page_size, _stream())
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, block: int) -> None:
+    """out[t, i] = silu(g_i) * u_i from a fused projection whose columns alternate
+    ``block`` gates and ``block`` ups."""
+    T, I = out.shape
+    f = _fn("elementwise.cu", "g2b_swiglu",
+            [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _call(f, _ptr(gate_up), _code(gate_up.dtype), T, I, block, _ptr(out), _stream())
+
+
+def advance_positions(tok_pos: torch.Tensor, n: int) -> None:
+    f = _fn("elementwise.cu", "g2b_advance_positions", [c_void_p, c_int, c_void_p])
+    _call(f, _ptr(tok_pos), n, _stream())
+
+
+# ---------------------------------------------------------------------------
+# matrix products
+# ---------------------------------------------------------------------------
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out (=|+=) a @ w.T in true float32 arithmetic.  a [M,K], w [N,K], out [M,N];
+    accumulate needs a float32 out."""
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm: shapes a{list(a.shape)} w{list(w.shape)} out{list(out.shape)}")
+    if accumulate:
+        _need(out, torch.float32, "accumulated output")
+        epi = EPI_ACCUM_F32
+    else:
+        epi = EPI_STORE_F32 if out.dtype == torch.float32 else EPI_STORE_BF16
+        _code(out.dtype)
+    f = _fn("gemm_simt.cu", "g2b_gemm_simt",
+            [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_void_p])
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm: innermost strides must be 1")
+    _call(f, _ptr(a), _code(a.dtype), _ptr(w), _code(w.dtype), _ptr(out), M, N, K, a.stride(0),
+          w.stride(0), out.stride(0), epi, _stream())
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """The product a layer asks for; picks the kernel from the dtypes and sizes.  Anything
+    that is not all-bfloat16 runs on the float32 kernel (true 32-bit arithmetic)."""
+    if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        from . import kernels_bf16
+        if kernels_bf16.linear_bf16(a, w, out, accumulate):
+            return
+    gemm_simt(a, w, out, accumulate)
+
+
+# ---------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------
+def attn_generic(q, out, cache_pages, tok_pos, tok_seq, page_table, n_heads, n_kv_heads,
+                 head_dim, page_size, window, scale) -> None:
+    """Causal attention of every token of the step over its sequence's cache pages,
+    32-bit arithmetic; q, out [T, n_heads*head_dim]."""
+    f = _fn("attn_generic.cu", "g2b_attn_generic",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    if q.dtype != cache_pages.dtype or out.dtype != q.dtype:
+        raise KernelError("attention: q, out and the cache must have one dtype")
+    _call(f, _ptr(q), _ptr(out), _code(q.dtype), _ptr(cache_pages), _ptr(tok_pos), _ptr(tok_seq),
+          _ptr(page_table), page_table.shape[1], q.shape[0], n_heads, n_kv_heads, head_dim,
+          page_size, window, scale, _stream())
+
+
+def attention(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
+              scale) -> None:
+    """Attention of a step: the tensor-core kernels when they take the case, else the
+    32-bit kernel."""
+    if q.dtype == torch.bfloat16:
+        from . import kernels_bf16
+        if kernels_bf16.attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim,
+                                       page_size, window, scale):
+            return
+    attn_generic(q, out, cache_pages, ctx.tok_pos, ctx.tok_seq, ctx.page_table, n_heads,
+                 n_kv_heads, head_dim, page_size, window, scale)
+
+
+def gate_up_fused(h, w_gate_up, mid, block) -> bool:
+    """silu(gate) * up computed inside the product's epilogue; False when no kernel takes
+    the case (the caller then runs the product and ``swiglu`` separately)."""
+    if h.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16:
+        from . import kernels_bf16
+        return kernels_bf16.gate_up_bf16(h, w_gate_up, mid, block)
+    return False
+
+
+# ---------------------------------------------------------------------------
+# sampling.cu
+# ---------------------------------------------------------------------------
+def sample_rows(logits, temperature, seq_state, slots, out_ids) -> None:
+    """Greedy (temperature <= 0) or temperature sampling of one id per row of float32
+    logits; random numbers come from the per-slot records."""
+    _need(logits, torch.float32, "logits")
+    _need(out_ids, torch.int32, "out_ids")
+    R, V = logits.shape
+    f = _fn("sampling.cu", "g2b_sample_rows",
+            [c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
+    _call(f, _ptr(logits), R, V, logits.stride(0), temperature, _ptr(seq_state),
+          seq_state.shape[1] if seq_state is not None else 0, _ptr(slots), _ptr(out_ids), _stream())
+
+
+def sample_filtered(logits, temperature, top_k, top_p, penalty, recent, recent_n, seq_state, slots,
+                    out_ids) -> None:
+    """Repeat penalty, top-k, top-p, then temperature sampling; logits are changed in
+    place by the penalty.  recent int32 [R, n], recent_n int32 [R]."""
+    _need(logits, torch.float32, "logits")
+    _need(out_ids, torch.int32, "out_ids")
+    R, V = logits.shape
+    f = _fn("sampling.cu", "g2b_sample_filtered",
+            [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_void_p, c_int,
+             c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
+    _call(f, _ptr(logits), R, V, logits.stride(0), temperature, top_k, top_p, penalty,
+          _ptr(recent), recent.shape[1] if recent is not None else 0, _ptr(recent_n),
+          _ptr(seq_state), seq_state.shape[1] if seq_state is not None else 0, _ptr(slots),
+          _ptr(out_ids), _stream())
+
+
+def seed_slots(seq_state, slots, streams, seed: int) -> None:
+    """Starts the random stream of each given slot: key = seed, stream id, zero draws."""
+    f = _fn("sampling.cu", "g2b_seed_slots",
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_ulonglong, c_void_p])
+    _call(f, _ptr(seq_state), seq_state.shape[1], _ptr(slots), _ptr(streams), slots.shape[0],
+          seed & 0xFFFFFFFFFFFFFFFF, _stream())

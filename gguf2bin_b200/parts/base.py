@@ -1,0 +1,55 @@
+"""What every part gets and must offer.
+
+Common rules
+* A part is built from its ``PartSpec`` plus the sizes of its surroundings (the model
+  width, the compute dtype, the device).  It never sees the model or the architecture.
+* ``expected(spec, ...)`` (a classmethod) lists the tensors the part needs as
+  ``{checkpoint name relative to the layer prefix: Expected}``; ``bind(tensors)`` receives
+  them under the same names once loaded and may fuse or re-lay them.
+* ``forward`` launches kernels on the current stream, allocates only through
+  ``ctx.workspace`` and returns nothing that lives longer than the step.
+
+Norm          forward(x32 [T,H] float32, out [T,H] compute dtype, rows=None)
+Position      fused_rotation() -> (inv_freq float32 [r/2], rotary_dim) or None;
+              apply(q [T,nh*hd], k [T,nkv*hd], ctx) in place when it cannot be fused
+Mixer         cache_need() -> KVNeed | StateNeed | None;
+              forward(h [T,H], ctx, cache_view, residual32 [T,H]): ADDS its output
+Feed-forward  forward(h [T,H], ctx, residual32 [T,H]): ADDS its output
+Block         forward(x32 [T,H], ctx, cache_view): one whole layer on the residual stream
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+
+@dataclass
+class StepContext:
+    """One step's batch as the kernels see it.  All index tensors are int32 on the device.
+
+    tok_ids [T]      token ids, sequences one after another
+    tok_pos [T]      absolute position of each token in its sequence
+    tok_seq [T]      index (0..B-1) of each token's sequence in this step
+    page_table [B,P] pages of each sequence, in position order
+    Host-side copies (lists) describe the same batch for parts that plan launches.
+    """
+    n_tokens: int
+    n_seqs: int
+    tok_ids: torch.Tensor
+    tok_pos: torch.Tensor
+    tok_seq: torch.Tensor
+    page_table: torch.Tensor
+    page_size: int
+    workspace: "object"
+    dtype: torch.dtype
+    q_lens: list = field(default_factory=list)       # tokens of each sequence in this step
+    past_lens: list = field(default_factory=list)    # tokens each sequence held before it
+    slots: list = field(default_factory=list)        # slot of each sequence
+    max_kv_len: int = 0                              # longest sequence after this step
+    seq_meta: Optional[torch.Tensor] = None          # [B,4] int32: q_start, q_len, past, slot
+
+    @property
+    def all_single(self) -> bool:
+        return self.n_tokens == self.n_seqs

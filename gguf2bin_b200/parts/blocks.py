@@ -1,0 +1,51 @@
+"""Block arrangements.  ``prenorm``: x += mixer(norm(x)); x += feed_forward(norm(x)), the
+residual stream kept in float32 (src/l5_model.c:494-597 of AnonymoDGH/gguf2bin)."""
+from __future__ import annotations
+
+import torch
+
+from ..config.specs import LayerSpec
+from .registry import (feed_forward_class, mixer_class, norm_class, register_block)
+
+
+class PreNormBlock:
+    def __init__(self, layer: LayerSpec, hidden_size: int, dtype: torch.dtype, device):
+        self.names = dict(layer.block["names"])
+        self.hidden, self.dtype = int(hidden_size), dtype
+        ncls = norm_class(layer.norm)
+        self.mixer_norm = ncls(layer.norm, hidden_size, dtype, device)
+        self.ffn_norm = ncls(layer.norm, hidden_size, dtype, device)
+        self.mixer = mixer_class(layer.mixer)(layer.mixer, hidden_size, dtype, device)
+        self.feed_forward = feed_forward_class(layer.feed_forward)(layer.feed_forward, hidden_size,
+                                                                   dtype, device)
+
+    @classmethod
+    def expected(cls, layer: LayerSpec, hidden_size: int) -> dict:
+        names = dict(layer.block["names"])
+        ncls = norm_class(layer.norm)
+        out = {}
+        out.update(ncls.expected(layer.norm, hidden_size, names["mixer_norm"]))
+        out.update(ncls.expected(layer.norm, hidden_size, names["ffn_norm"]))
+        out.update(mixer_class(layer.mixer).expected(layer.mixer, hidden_size))
+        out.update(feed_forward_class(layer.feed_forward).expected(layer.feed_forward, hidden_size))
+        return out
+
+    def bind(self, tensors: dict) -> None:
+        self.mixer_norm.bind(tensors[self.names["mixer_norm"]])
+        self.ffn_norm.bind(tensors[self.names["ffn_norm"]])
+        self.mixer.bind(tensors)
+        self.feed_forward.bind(tensors)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, x32: torch.Tensor, ctx, cache_view) -> None:
+        T = x32.shape[0]
+        h = ctx.workspace.buffer("block.normed", (T, self.hidden), self.dtype)
+        self.mixer_norm.forward(x32, h)
+        self.mixer.forward(h, ctx, cache_view, x32)
+        self.ffn_norm.forward(x32, h)
+        self.feed_forward.forward(h, ctx, x32)
+
+
+register_block("prenorm", PreNormBlock)

@@ -1,0 +1,105 @@
+"""Sequence mixers.  ``gqa_attention``: causal grouped-query attention over the cache.
+
+Order of operations (src/l5_model.c:497-583 of AnonymoDGH/gguf2bin): q, k, v projections
+without bias; per-head RMSNorm of q and k (if the spec has ``qk_norm``); position
+encoding of q and k; k (normed, rotated) and v (raw) written to the cache; scores
+(q . k) * scale over the keys up to the token's own position (optionally only the last
+``window`` of them); softmax; weighted values; output projection added to the residual.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import kernels
+from ..cache.storage import KVNeed, KVView
+from ..config.specs import ConfigError, PartSpec
+from ..weights.loader import Expected
+from .registry import norm_class, position_class, register_mixer
+
+
+class GQAAttention:
+    def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device):
+        self.nh = int(spec["n_heads"])
+        self.nkv = int(spec["n_kv_heads"])
+        self.hd = int(spec["head_dim"])
+        self.hidden = int(hidden_size)
+        self.window = int(spec.get("window") or 0)
+        scale = spec.get("scale")
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.hd)
+        if self.nh <= 0 or self.nkv <= 0 or self.nh % self.nkv:
+            raise ConfigError(f"gqa_attention: {self.nh} heads are not a multiple of "
+                              f"{self.nkv} kv heads")
+        if self.hd <= 0 or self.hd > 512:
+            raise ConfigError(f"gqa_attention: head_dim {self.hd} outside 1..512")
+        self.dtype, self.device = dtype, device
+        self.names = dict(spec["names"])
+        qk = spec.get("qk_norm")
+        self.qk_eps = 0.0
+        self.has_qk_norm = qk is not None
+        if qk is not None:
+            if qk.kind != "rmsnorm":
+                raise ConfigError(f"gqa_attention: qk_norm of kind {qk.kind!r} is not supported")
+            norm_class(qk)                            # must be registered
+            self.qk_eps = float(qk["eps"])
+        pos = spec.get("position") or PartSpec.make("none")
+        self.position = position_class(pos)(pos, self.hd, device)
+        self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+
+    # ---- weights -------------------------------------------------------------
+    @classmethod
+    def expected(cls, spec: PartSpec, hidden_size: int) -> dict:
+        n = dict(spec["names"])
+        nq, nk = spec["n_heads"] * spec["head_dim"], spec["n_kv_heads"] * spec["head_dim"]
+        out = {n["q"]: Expected((nq, hidden_size)), n["k"]: Expected((nk, hidden_size)),
+               n["v"]: Expected((nk, hidden_size)), n["o"]: Expected((hidden_size, nq))}
+        if spec.get("qk_norm") is not None:
+            out[n["q_norm"]] = Expected((spec["head_dim"],), init="scale")
+            out[n["k_norm"]] = Expected((spec["head_dim"],), init="scale")
+        return out
+
+    def bind(self, tensors: dict) -> None:
+        n = self.names
+        parts = [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]]
+        common = torch.float32 if any(p.dtype == torch.float32 for p in parts) else parts[0].dtype
+        self.w_qkv = torch.cat([p.to(common) for p in parts], dim=0).contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
+        if self.has_qk_norm:
+            self.q_norm_w = tensors[n["q_norm"]].to(torch.float32).contiguous()
+            self.k_norm_w = tensors[n["k_norm"]].to(torch.float32).contiguous()
+
+    # ---- cache ---------------------------------------------------------------
+    def cache_need(self):
+        return KVNeed(self.nkv, self.hd, self.window)
+
+    # ---- step ----------------------------------------------------------------
+    def forward(self, h: torch.Tensor, ctx, view: KVView, residual32: torch.Tensor) -> None:
+        T = h.shape[0]
+        nq, nk = self.nh * self.hd, self.nkv * self.hd
+        ws = ctx.workspace
+        qkv = ws.buffer("attn.qkv", (T, nq + 2 * nk), self.dtype)
+        kernels.linear(h, self.w_qkv, qkv)
+        q = ws.buffer("attn.q", (T, nq), self.dtype)
+        fused = self.position.fused_rotation()
+        if fused is not None:
+            inv_freq, rot = fused
+            kernels.qknorm_rope_cache(qkv, self.nh, self.nkv, self.hd, self.q_norm_w,
+                                      self.k_norm_w, self.qk_eps, inv_freq, rot, ctx.tok_pos,
+                                      ctx.tok_seq, ctx.page_table, view.pages, view.page_size, q)
+        else:
+            k = ws.buffer("attn.k", (T, nk), self.dtype)
+            v = ws.buffer("attn.v", (T, nk), self.dtype)
+            kernels.qknorm_rope_cache(qkv, self.nh, self.nkv, self.hd, self.q_norm_w,
+                                      self.k_norm_w, self.qk_eps, None, 0, ctx.tok_pos,
+                                      ctx.tok_seq, None, None, view.page_size, q, k, v)
+            self.position.apply(q, k, ctx)
+            kernels.cache_write(k, v, self.nkv, self.hd, ctx.tok_pos, ctx.tok_seq, ctx.page_table,
+                                view.pages, view.page_size)
+        o = ws.buffer("attn.o", (T, nq), self.dtype)
+        kernels.attention(q, o, view.pages, ctx, self.nh, self.nkv, self.hd, view.page_size,
+                          self.window, self.scale)
+        kernels.linear(o, self.w_o, residual32, accumulate=True)
+
+
+register_mixer("gqa_attention", GQAAttention)

@@ -1,0 +1,30 @@
+"""Norms.  ``rmsnorm``: o_j = (w_j * x_j) / sqrt(mean(x^2) + eps), statistics in float32,
+the weight a plain multiplier (src/l3_math.c:21-51 of AnonymoDGH/gguf2bin)."""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..config.specs import PartSpec
+from ..weights.loader import Expected
+from .registry import register_norm
+
+
+class RMSNorm:
+    def __init__(self, spec: PartSpec, width: int, dtype: torch.dtype, device):
+        self.eps = float(spec["eps"])
+        self.width = int(width)
+        self.weight = None
+
+    @classmethod
+    def expected(cls, spec: PartSpec, width: int, name: str) -> dict:
+        return {name: Expected((int(width),), init="scale")}
+
+    def bind(self, weight: torch.Tensor) -> None:
+        self.weight = weight.to(torch.float32).contiguous()      # exact widening
+
+    def forward(self, x32: torch.Tensor, out: torch.Tensor, rows=None) -> None:
+        kernels.rmsnorm(x32, self.weight, self.eps, out, rows)
+
+
+register_norm("rmsnorm", RMSNorm)

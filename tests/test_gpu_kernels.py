@@ -1,0 +1,232 @@
+"""Each kernel alone against a plain float32 computation in torch/numpy, at sizes other
+than the engine's: widths that are no power of two, odd row counts, shuffled pages."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import philox_plain, qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_rows(dtype):
+    from gguf2bin_b200 import kernels
+    table = rnd(311, 100, dtype=dtype)
+    ids = torch.tensor([0, 310, 5, 5, 17], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 100, device=DEV)
+    kernels.embed_rows(table, ids, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("H", [100, 64, 1030])
+@pytest.mark.parametrize("odtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm(H, odtype):
+    from gguf2bin_b200 import kernels
+    x, w = rnd(7, H, seed=1), 1 + 0.1 * rnd(H, seed=2)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    for r in (None, rows):
+        n = 7 if r is None else 3
+        out = torch.empty(n, H, dtype=odtype, device=DEV)
+        kernels.rmsnorm(x, w, 1e-5, out, r)
+        xs = x if r is None else x[r.long()]
+        ref = P.rmsnorm(xs.cpu().numpy(), w.cpu().numpy(), 1e-5, np.float32)
+        tol = 2e-6 if odtype == torch.float32 else 2.0 ** -8
+        np.testing.assert_allclose(out.float().cpu().numpy(), ref, rtol=tol, atol=tol * 1e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 53, 29), (37, 64, 128), (130, 70, 33), (5, 311, 96)])
+@pytest.mark.parametrize("adt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.bfloat16, torch.float32), (torch.float32, torch.bfloat16)])
+def test_gemm_simt(M, N, K, adt, wdt):
+    from gguf2bin_b200 import kernels
+    a, w = rnd(M, K, dtype=adt, seed=3), rnd(N, K, dtype=wdt, seed=4)
+    ref = a.double() @ w.double().T
+    out = torch.empty(M, N, device=DEV)
+    kernels.gemm_simt(a, w, out)
+    assert (out.double() - ref).abs().max().item() < 1e-5 * math.sqrt(K) * 4
+    base = rnd(M, N, seed=5)
+    acc = base.clone()
+    kernels.gemm_simt(a, w, acc, accumulate=True)
+    assert (acc.double() - (base.double() + ref)).abs().max().item() < 1e-5 * math.sqrt(K) * 4
+    out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_simt(a, w, out16)
+    assert (out16.double() - ref).abs().max().item() <= (ref.abs().max().item() * 2.0 ** -8 + 1e-6)
+
+
+def make_paged(n_seqs, lens, nkv, hd, page_size, dtype, seed):
+    """Random K/V for sequences of the given lengths, scattered over shuffled pages.
+    Returns (cache pages [n_pages,2,nkv,ps,hd], page_table [B,P], K list, V list)."""
+    pages_per = [-(-l // page_size) for l in lens]
+    n_pages = sum(pages_per) + 3
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    cache = rnd(n_pages, 2, nkv, page_size, hd, dtype=dtype, seed=seed + 1)   # junk everywhere
+    table = torch.zeros(n_seqs, max(pages_per), dtype=torch.int32)
+    Ks, Vs, nxt = [], [], 0
+    for b, l in enumerate(lens):
+        K, V = rnd(l, nkv, hd, dtype=dtype, seed=seed + 10 + b), rnd(l, nkv, hd, dtype=dtype, seed=seed + 50 + b)
+        for p in range(pages_per[b]):
+            pg = perm[nxt]; nxt += 1
+            table[b, p] = pg
+            n = min(page_size, l - p * page_size)
+            cache[pg, 0, :, :n] = K[p * page_size:p * page_size + n].transpose(0, 1)
+            cache[pg, 1, :, :n] = V[p * page_size:p * page_size + n].transpose(0, 1)
+        Ks.append(K); Vs.append(V)
+    return cache, table.to(DEV), Ks, Vs
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(6, 2, 48, 0), (4, 4, 16, 0), (5, 1, 80, 37), (8, 2, 128, 0)])
+def test_attn_generic(dtype, nh, nkv, hd, window):
+    """Ragged: sequence 0 a whole prompt, sequence 1 a prompt continued after a past,
+    sequence 2 a single token far into its sequence."""
+    from gguf2bin_b200 import kernels
+    ps = 64
+    lens = [70, 200, 333]
+    q_lens = [70, 9, 1]
+    cache, table, Ks, Vs = make_paged(3, lens, nkv, hd, ps, dtype, seed=7)
+    tok_pos, tok_seq = [], []
+    for b, (l, ql) in enumerate(zip(lens, q_lens)):
+        tok_pos += list(range(l - ql, l)); tok_seq += [b] * ql
+    T = len(tok_pos)
+    q = rnd(T, nh * hd, dtype=dtype, seed=8)
+    out = torch.empty_like(q)
+    scale = 1 / math.sqrt(hd)
+    kernels.attn_generic(q, out, cache, torch.tensor(tok_pos, dtype=torch.int32, device=DEV),
+                         torch.tensor(tok_seq, dtype=torch.int32, device=DEV), table, nh, nkv, hd,
+                         ps, window, scale)
+    got = out.float().cpu().numpy().reshape(T, nh, hd)
+    t = 0
+    for b, (l, ql) in enumerate(zip(lens, q_lens)):
+        K, V = Ks[b].float().cpu().numpy(), Vs[b].float().cpu().numpy()
+        qfull = np.zeros((l, nh, hd), np.float32)
+        qfull[l - ql:] = q[t:t + ql].float().cpu().numpy().reshape(ql, nh, hd)
+        ref = P.causal_attention(qfull, K, V, np.float32, window=window)[l - ql:]
+        tol = 2e-5 if dtype == torch.float32 else 2.0 ** -7
+        np.testing.assert_allclose(got[t:t + ql], ref, atol=tol * max(1, np.abs(ref).max()), rtol=0)
+        t += ql
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,rot,norm", [(4, 2, 16, 16, True), (3, 1, 48, 32, True), (2, 2, 128, 128, False)])
+def test_qknorm_rope_cache(dtype, nh, nkv, hd, rot, norm):
+    from gguf2bin_b200 import kernels
+    ps, lens, q_lens = 64, [70, 130], [70, 2]
+    cache, table, _, _ = make_paged(2, lens, nkv, hd, ps, dtype, seed=11)
+    tok_pos, tok_seq = [], []
+    for b, (l, ql) in enumerate(zip(lens, q_lens)):
+        tok_pos += list(range(l - ql, l)); tok_seq += [b] * ql
+    T = len(tok_pos)
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=12)
+    qw, kw = (1 + 0.1 * rnd(hd, seed=13), 1 + 0.1 * rnd(hd, seed=14)) if norm else (None, None)
+    theta, eps = 1e4, 1e-5
+    inv_freq = (theta ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).float().to(DEV)
+    q_out = torch.empty(T, nh * hd, dtype=dtype, device=DEV)
+    before = cache.clone()
+    kernels.qknorm_rope_cache(qkv, nh, nkv, hd, qw, kw, eps, inv_freq, rot,
+                              torch.tensor(tok_pos, dtype=torch.int32, device=DEV),
+                              torch.tensor(tok_seq, dtype=torch.int32, device=DEV), table, cache, ps, q_out)
+    x = qkv.float().cpu().numpy().reshape(T, nh + 2 * nkv, hd)
+    qq, kk, vv = x[:, :nh], x[:, nh:nh + nkv], x[:, nh + nkv:]
+    if norm:
+        qq = P.qk_rmsnorm(qq, qw.cpu().numpy(), eps, np.float32)
+        kk = P.qk_rmsnorm(kk, kw.cpu().numpy(), eps, np.float32)
+
+    def rope(a):
+        r = P.rope_neox(a[..., :rot], tok_pos, theta, np.float32)
+        return np.concatenate([r, a[..., rot:]], -1)
+    qq, kk = rope(qq), rope(kk)
+    tol = 3e-6 if dtype == torch.float32 else 2.0 ** -8
+    np.testing.assert_allclose(q_out.float().cpu().numpy().reshape(T, nh, hd), qq, rtol=tol, atol=tol)
+    touched = torch.zeros_like(cache, dtype=torch.bool)
+    for t, (pos, b) in enumerate(zip(tok_pos, tok_seq)):
+        pg = int(table[b, pos // ps])
+        np.testing.assert_allclose(cache[pg, 0, :, pos % ps].float().cpu().numpy(), kk[t], rtol=tol, atol=tol)
+        np.testing.assert_allclose(cache[pg, 1, :, pos % ps].float().cpu().numpy(), vv[t], rtol=tol, atol=tol)
+        touched[pg, :, :, pos % ps] = True
+    assert torch.equal(cache[~touched], before[~touched]), "cache written outside the tokens' places"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("I,blk", [(24, 8), (100, 100), (224, 8)])
+def test_swiglu(dtype, I, blk):
+    from gguf2bin_b200 import kernels
+    T = 5
+    g, u = rnd(T, I, dtype=dtype, seed=20), rnd(T, I, dtype=dtype, seed=21)
+    fused = torch.stack([g.view(T, I // blk, blk), u.view(T, I // blk, blk)], dim=2).reshape(T, 2 * I).contiguous()
+    out = torch.empty(T, I, dtype=dtype, device=DEV)
+    kernels.swiglu(fused, out, blk)
+    gf, uf = g.float(), u.float()
+    ref = (gf / (1 + torch.exp(-gf))) * uf
+    tol = 1e-6 if dtype == torch.float32 else 2.0 ** -8
+    assert ((out.float() - ref).abs() <= tol * (1 + ref.abs())).all()
+
+
+def test_sampling_greedy_and_temperature():
+    from gguf2bin_b200 import kernels
+    from gguf2bin_b200.cache import SEQ_STATE_WORDS
+    R, V = 6, 1537
+    logits = rnd(R, V, scale=3.0, seed=30)
+    logits[0, 100] = logits[0, 900] = 50.0            # a tie: the lower id wins
+    state = torch.zeros(8, SEQ_STATE_WORDS, dtype=torch.int32, device=DEV)
+    slots = torch.tensor([3, 1, 4, 0, 5, 7], dtype=torch.int32, device=DEV)
+    streams = torch.tensor([10, 11, 12, 13, 14, 15], dtype=torch.int32, device=DEV)
+    seed = 0x1234567890ABCDEF
+    kernels.seed_slots(state, slots, streams, seed)
+    ids = torch.empty(R, dtype=torch.int32, device=DEV)
+    kernels.sample_rows(logits, 0.0, state, slots, ids)
+    assert ids.tolist() == [P.greedy(l) for l in logits.cpu().numpy()]
+    assert ids[0].item() == 100
+    for draw in range(3):
+        kernels.sample_rows(logits, 0.8, state, slots, ids)
+        for r in range(R):
+            u = philox_plain.uniform(seed, 10 + r, draw)
+            want, cdf = P.sample_temperature(logits[r].cpu().numpy(), 0.8, u)
+            got = ids[r].item()
+            lo = cdf[got - 1] if got > 0 else 0.0
+            assert lo - 1e-5 <= u <= cdf[got] + 1e-5, (r, draw, got, want, u)
+    assert state[slots.long(), 3].tolist() == [3] * R
+
+
+@pytest.mark.parametrize("top_k,top_p,penalty", [(40, 0.9, 1.1), (0, 0.9, 1.0), (5, 1.0, 1.3), (0, 1.0, 1.0), (1, 0.5, 1.0)])
+def test_sampling_filtered(top_k, top_p, penalty):
+    from gguf2bin_b200 import kernels
+    from gguf2bin_b200.cache import SEQ_STATE_WORDS
+    R, V, temp = 5, 2011, 0.7
+    logits = rnd(R, V, scale=2.5, seed=31)
+    recent = torch.randint(0, V, (R, 64), generator=torch.Generator().manual_seed(5), dtype=torch.int32)
+    recent[:, 10] = recent[:, 3]                       # a repeated id is penalised once
+    recent_n = torch.tensor([64, 0, 17, 64, 1], dtype=torch.int32)
+    state = torch.zeros(R, SEQ_STATE_WORDS, dtype=torch.int32, device=DEV)
+    slots = torch.arange(R, dtype=torch.int32, device=DEV)
+    seed = 77
+    kernels.seed_slots(state, slots, slots.clone(), seed)
+    ids = torch.empty(R, dtype=torch.int32, device=DEV)
+    for draw in range(4):
+        work = logits.clone()
+        kernels.sample_filtered(work, temp, top_k, top_p, penalty, recent.to(DEV), recent_n.to(DEV),
+                                state, slots, ids)
+        for r in range(R):
+            u = philox_plain.uniform(seed, r, draw)
+            rec = recent[r, :recent_n[r]].tolist()
+            want, kept, cdf = P.sample_advanced(logits[r].cpu().numpy(), temp, top_k, top_p, penalty, rec, u)
+            got = ids[r].item()
+            where = np.nonzero(kept == got)[0]
+            assert len(where) == 1, (r, draw, got, "not in the kept set", len(kept))
+            i = int(where[0])
+            lo = cdf[i - 1] if i > 0 else 0.0
+            assert lo - 1e-4 <= u <= cdf[i] + 1e-4, (r, draw, got, want, u, lo, cdf[i])
+    # greedy through the same kernel applies the penalty first
+    work = logits.clone()
+    kernels.sample_filtered(work, 0.0, top_k, top_p, penalty, recent.to(DEV), recent_n.to(DEV), state, slots, ids)
+    for r in range(R):
+        rec = recent[r, :recent_n[r]].tolist()
+        assert ids[r].item() == P.sample_advanced(logits[r].cpu().numpy(), 0.0, top_k, top_p, penalty, rec, 0.5)[0]
