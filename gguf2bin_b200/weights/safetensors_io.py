@@ -81,7 +81,7 @@ class SafetensorsFile:
                     f"{self.path}: tensor {name!r} ({dtype}{list(shape)}) has data range "
                     f"[{a},{b}) but needs {want} bytes within a file of {size} bytes (truncated?)")
             self.entries[name] = TensorEntry(name, dtype, shape, base + a, base + b, self.path)
-        self._map = mmap.mmap(self._fh.fileno(), 0, access=mmap.ACCESS_READ)
+        self._map = mmap.mmap(self._fh.fileno(), 0, access=mmap.ACCESS_COPY)
 
     def tensor(self, name: str) -> torch.Tensor:
         e = self.entries[name]
