@@ -1,7 +1,8 @@
 """Device storage of the cache.
 
-Layers say what they need through a ``CacheNeed``; layers with equal needs share one
-group, and every group has storage of its own:
+Every execution of a layer (a position of the model's schedule) says what it needs
+through a ``KVNeed`` or ``StateNeed``; positions with equal needs share one group, and
+every group has storage of its own:
 
 * ``KVNeed``: keys and values of every position (``window == 0``) or of a window of
   them.  Storage ``[layers, pages, 2 (K,V), kv_heads, page_size, head_dim]``: one
@@ -68,8 +69,8 @@ class Cache:
 
     def __init__(self, needs: Seq[Optional[object]], max_tokens: int, dtype: torch.dtype, device,
                  max_seqs: Optional[int] = None, page_size: int = PAGE_SIZE):
-        """``needs[i]`` is the need of layer ``i`` (None: the layer stores nothing, or
-        uses another layer's storage).  ``max_tokens`` is the most tokens live sequences
+        """``needs[i]`` is the need of schedule position ``i`` (None: it stores nothing, or
+        uses another position's storage).  ``max_tokens`` is the most tokens live sequences
         hold together, each sequence rounded up to whole pages."""
         if max_tokens <= 0:
             raise CacheError("max_tokens must be positive")

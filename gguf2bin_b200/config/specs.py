@@ -56,15 +56,12 @@ class LayerSpec:
 
 @dataclass(frozen=True)
 class ScheduleEntry:
-    """One execution of a layer.  ``cache_of`` names the layer whose cache storage
-    this execution reads and writes (itself by default); a layer that lists another
-    layer there owns no storage."""
+    """One execution of a layer.  Every execution has cache storage of its own (a layer
+    that is named twice runs with the same weights but keeps two caches), unless
+    ``cache_of`` names an EARLIER position of the schedule: then this execution uses the
+    storage of that one (a layer that reads another layer's keys and values)."""
     layer: int
     cache_of: Optional[int] = None
-
-    @property
-    def cache_layer(self) -> int:
-        return self.layer if self.cache_of is None else self.cache_of
 
 
 @dataclass(frozen=True)
@@ -89,6 +86,18 @@ class ModelSpec:
         if not self.layers or not self.schedule:
             raise ConfigError("a model needs at least one layer and one schedule entry")
         n = len(self.layers)
-        for e in self.schedule:
-            if not (0 <= e.layer < n) or not (0 <= e.cache_layer < n):
-                raise ConfigError(f"schedule entry {e} names a layer outside 0..{n - 1}")
+        for i, e in enumerate(self.schedule):
+            if not (0 <= e.layer < n):
+                raise ConfigError(f"schedule entry {i} names layer {e.layer}, outside 0..{n - 1}")
+            if e.cache_of is not None:
+                if not (0 <= e.cache_of < i):
+                    raise ConfigError(f"schedule entry {i}: cache_of={e.cache_of} must name an "
+                                      "earlier entry of the schedule")
+                if self.schedule[e.cache_of].cache_of is not None:
+                    raise ConfigError(f"schedule entry {i}: cache_of={e.cache_of} names an entry "
+                                      "that itself borrows its storage")
+
+    def cache_owner(self, position: int) -> int:
+        """The schedule position whose storage the execution at ``position`` uses."""
+        e = self.schedule[position]
+        return position if e.cache_of is None else e.cache_of

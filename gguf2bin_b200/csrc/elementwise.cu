@@ -165,7 +165,7 @@ extern "C" int g2b_qknorm_rope_cache(const void *qkv, int dtype, int T_tokens, i
     G2B_REFUSE("qknorm_rope_cache: rotary_dim %d must be even and at most head_dim %d", rot_dim, hd);
   if ((k_out == nullptr) != (v_out == nullptr))
     G2B_REFUSE("qknorm_rope_cache: k_out and v_out must be given together");
-  if (!k_out && (!cache || !page_table || page_size <= 0))
+  if (nkv > 0 && !k_out && (!cache || !page_table || page_size <= 0))
     G2B_REFUSE("qknorm_rope_cache: no cache to write to");
   const long long items = (long long)T_tokens * (nh + 2 * nkv);
   const unsigned blocks = (unsigned)((items + QKN_WARPS - 1) / QKN_WARPS);

@@ -1,0 +1,20 @@
+"""The list of kernel objects: (source file, -D defines).  Units without defines take
+every size at run time; units specialised on a head size exist once per size in
+``HEAD_SIZES`` and any other size is compiled when a model first asks for it."""
+from __future__ import annotations
+
+GENERIC_UNITS = [("elementwise.cu", ()), ("gemm_simt.cu", ()), ("attn_generic.cu", ()),
+                 ("sampling.cu", ())]
+
+# head sizes built ahead of time (what the tests and the benchmark use)
+HEAD_SIZES = (64, 128)
+
+SPECIALISED_SOURCES: list = []          # filled by the bfloat16 kernels' bindings
+
+
+def all_units() -> list:
+    units = list(GENERIC_UNITS)
+    for src, extra in SPECIALISED_SOURCES:
+        for hd in HEAD_SIZES:
+            units.append((src, (f"HD={hd}",) + tuple(extra)))
+    return units

@@ -86,9 +86,10 @@ class Model:
 
     # ---- cache ----------------------------------------------------------------
     def cache_needs(self) -> list:
-        """The need of each layer that owns cache storage (None for the others)."""
-        owners = {e.cache_layer for e in self.spec.schedule}
-        return [b.cache_need() if i in owners else None for i, b in enumerate(self.blocks)]
+        """The need of each schedule position: what its layer asks for, or None when the
+        position borrows another position's storage or its layer stores nothing."""
+        return [self.blocks[e.layer].cache_need() if e.cache_of is None else None
+                for e in self.spec.schedule]
 
     def new_cache(self, max_tokens: int, max_seqs: Optional[int] = None) -> Cache:
         return Cache(self.cache_needs(), max_tokens, self.dtype, self.device, max_seqs)
@@ -125,8 +126,8 @@ class Model:
         ws = ctx.workspace
         x = ws.buffer("stream", (ctx.n_tokens, self.hidden), torch.float32)
         kernels.embed_rows(self.embedding, ctx.tok_ids[:ctx.n_tokens], x)
-        for entry in self.spec.schedule:
-            self.blocks[entry.layer].forward(x, ctx, cache.view(entry.cache_layer))
+        for position, entry in enumerate(self.spec.schedule):
+            self.blocks[entry.layer].forward(x, ctx, cache.view(self.spec.cache_owner(position)))
         if n_want == 0:
             return None
         xn = ws.buffer("head.normed", (n_want, self.hidden), self.dtype)

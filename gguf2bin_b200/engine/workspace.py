@@ -10,6 +10,7 @@ class Workspace:
     def __init__(self, device):
         self.device = torch.device(device)
         self._buffers: dict[str, torch.Tensor] = {}
+        self.generation = 0            # bumps whenever a buffer moves (captured graphs go stale)
 
     def buffer(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         n = 1
@@ -22,6 +23,7 @@ class Workspace:
             cap = max(nbytes, 256) if raw is None else max(nbytes, 2 * raw.numel())
             raw = torch.empty(cap, dtype=torch.uint8, device=self.device)
             self._buffers[name] = raw
+            self.generation += 1
         return raw[:nbytes].view(dtype).view(*shape)
 
     def bytes(self) -> int:

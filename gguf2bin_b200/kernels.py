@@ -67,7 +67,17 @@ def _fn(unit: str, name: str, argtypes, defines=()):
     return f
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel launchers were called so far in this process."""
+    return _launches
+
+
 def _call(f, *args) -> None:
+    global _launches
+    _launches += 1
     rc = f(*args)
     if rc != 0:
         raise KernelError(f._lib.g2b_last_error().decode("utf-8", "replace"))

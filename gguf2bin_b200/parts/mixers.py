@@ -5,6 +5,10 @@ without bias; per-head RMSNorm of q and k (if the spec has ``qk_norm``); positio
 encoding of q and k; k (normed, rotated) and v (raw) written to the cache; scores
 (q . k) * scale over the keys up to the token's own position (optionally only the last
 ``window`` of them); softmax; weighted values; output projection added to the residual.
+
+With ``shared_kv`` the mixer has no k and v projections and writes nothing: it attends
+over the keys and values that another layer stored (the schedule entry's ``cache_of``
+names that layer, whose kv heads and head size it must share).
 """
 from __future__ import annotations
 
@@ -26,6 +30,7 @@ class GQAAttention:
         self.hd = int(spec["head_dim"])
         self.hidden = int(hidden_size)
         self.window = int(spec.get("window") or 0)
+        self.shared_kv = bool(spec.get("shared_kv") or False)
         scale = spec.get("scale")
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.hd)
         if self.nh <= 0 or self.nkv <= 0 or self.nh % self.nkv:
@@ -52,31 +57,39 @@ class GQAAttention:
     def expected(cls, spec: PartSpec, hidden_size: int) -> dict:
         n = dict(spec["names"])
         nq, nk = spec["n_heads"] * spec["head_dim"], spec["n_kv_heads"] * spec["head_dim"]
-        out = {n["q"]: Expected((nq, hidden_size)), n["k"]: Expected((nk, hidden_size)),
-               n["v"]: Expected((nk, hidden_size)), n["o"]: Expected((hidden_size, nq))}
+        shared = bool(spec.get("shared_kv") or False)
+        out = {n["q"]: Expected((nq, hidden_size)), n["o"]: Expected((hidden_size, nq))}
+        if not shared:
+            out[n["k"]] = Expected((nk, hidden_size))
+            out[n["v"]] = Expected((nk, hidden_size))
         if spec.get("qk_norm") is not None:
             out[n["q_norm"]] = Expected((spec["head_dim"],), init="scale")
-            out[n["k_norm"]] = Expected((spec["head_dim"],), init="scale")
+            if not shared:
+                out[n["k_norm"]] = Expected((spec["head_dim"],), init="scale")
         return out
 
     def bind(self, tensors: dict) -> None:
         n = self.names
-        parts = [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]]
+        parts = [tensors[n["q"]]] if self.shared_kv else \
+            [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]]
         common = torch.float32 if any(p.dtype == torch.float32 for p in parts) else parts[0].dtype
         self.w_qkv = torch.cat([p.to(common) for p in parts], dim=0).contiguous()
         self.w_o = tensors[n["o"]].contiguous()
         if self.has_qk_norm:
             self.q_norm_w = tensors[n["q_norm"]].to(torch.float32).contiguous()
-            self.k_norm_w = tensors[n["k_norm"]].to(torch.float32).contiguous()
+            if not self.shared_kv:
+                self.k_norm_w = tensors[n["k_norm"]].to(torch.float32).contiguous()
 
     # ---- cache ---------------------------------------------------------------
     def cache_need(self):
-        return KVNeed(self.nkv, self.hd, self.window)
+        return None if self.shared_kv else KVNeed(self.nkv, self.hd, self.window)
 
     # ---- step ----------------------------------------------------------------
     def forward(self, h: torch.Tensor, ctx, view: KVView, residual32: torch.Tensor) -> None:
         T = h.shape[0]
-        nq, nk = self.nh * self.hd, self.nkv * self.hd
+        nq = self.nh * self.hd
+        nkv_own = 0 if self.shared_kv else self.nkv        # kv heads this layer projects
+        nk = nkv_own * self.hd
         ws = ctx.workspace
         qkv = ws.buffer("attn.qkv", (T, nq + 2 * nk), self.dtype)
         kernels.linear(h, self.w_qkv, qkv)
@@ -84,18 +97,19 @@ class GQAAttention:
         fused = self.position.fused_rotation()
         if fused is not None:
             inv_freq, rot = fused
-            kernels.qknorm_rope_cache(qkv, self.nh, self.nkv, self.hd, self.q_norm_w,
+            kernels.qknorm_rope_cache(qkv, self.nh, nkv_own, self.hd, self.q_norm_w,
                                       self.k_norm_w, self.qk_eps, inv_freq, rot, ctx.tok_pos,
                                       ctx.tok_seq, ctx.page_table, view.pages, view.page_size, q)
         else:
             k = ws.buffer("attn.k", (T, nk), self.dtype)
             v = ws.buffer("attn.v", (T, nk), self.dtype)
-            kernels.qknorm_rope_cache(qkv, self.nh, self.nkv, self.hd, self.q_norm_w,
+            kernels.qknorm_rope_cache(qkv, self.nh, nkv_own, self.hd, self.q_norm_w,
                                       self.k_norm_w, self.qk_eps, None, 0, ctx.tok_pos,
                                       ctx.tok_seq, None, None, view.page_size, q, k, v)
             self.position.apply(q, k, ctx)
-            kernels.cache_write(k, v, self.nkv, self.hd, ctx.tok_pos, ctx.tok_seq, ctx.page_table,
-                                view.pages, view.page_size)
+            if nkv_own:
+                kernels.cache_write(k, v, self.nkv, self.hd, ctx.tok_pos, ctx.tok_seq,
+                                    ctx.page_table, view.pages, view.page_size)
         o = ws.buffer("attn.o", (T, nq), self.dtype)
         kernels.attention(q, o, view.pages, ctx, self.nh, self.nkv, self.hd, view.page_size,
                           self.window, self.scale)

@@ -1,0 +1,139 @@
+"""Generation through the Python entry point against the plain implementation."""
+import numpy as np
+import pytest
+
+from helpers import TINY, model_folder, plain_model, random_tokens
+from plain import philox_plain, qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+
+
+def plain_generate(name, storage, prompt, n, temperature=0.0, seed=0, stream=0, stop=()):
+    """Greedy or temperature generation by the plain implementation: the whole sequence
+    is run again for every new token (no cache)."""
+    cfg, W = plain_model(name, storage)
+    toks, out = list(prompt), []
+    for draw in range(n):
+        logits = P.forward(cfg, W, toks, np.float32)[-1]
+        if temperature <= 0:
+            t = P.greedy(logits)
+        else:
+            t, _ = P.sample_temperature(logits, temperature, philox_plain.uniform(seed, stream, draw))
+        if t in stop:
+            return out, "stop"
+        out.append(t)
+        toks.append(t)
+    return out, "length"
+
+
+@pytest.fixture(scope="module")
+def llms():
+    from gguf2bin_b200.api import LLM
+    made = {}
+
+    def get(name, dtype, max_tokens=1024):
+        key = (name, dtype, max_tokens)
+        if key not in made:
+            storage = "float32" if dtype == "float32" else "bfloat16"
+            made[key] = LLM(model_folder(name, storage), dtype=dtype, max_tokens=max_tokens)
+        return made[key]
+    return get
+
+
+def test_greedy_tiny_a_float32(llms):
+    """Tiny A: one prompt of 7 tokens, 9 greedy steps."""
+    prompt = random_tokens("a", 7, 0)
+    out = llms("a", "float32").generate([prompt], n=9, temperature=0.0, top_k=0, top_p=1.0,
+                                        repeat_penalty=1.0)[0]
+    want, _ = plain_generate("a", "float32", prompt, 9)
+    assert out.tokens == want and out.finish_reason == "length"
+
+
+def test_temperature_tiny_b_unequal_batch(llms):
+    """Tiny B: three unequal prompts (5, 11, 2), 6 steps at temperature 0.8, seeded.  The
+    same requests alone, and in another order, draw the same tokens: a request's random
+    stream is its own."""
+    llm = llms("b", "float32")
+    prompts = [random_tokens("b", n, 10 + i) for i, n in enumerate([5, 11, 2])]
+    kw = dict(n=6, temperature=0.8, top_k=0, top_p=1.0, repeat_penalty=1.0, seed=1234)
+    outs = llm.generate(prompts, **kw)
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        want, _ = plain_generate("b", "float32", p, 6, 0.8, seed=1234, stream=i)
+        assert o.tokens == want, f"request {i}"
+    assert llm.generate(prompts[:1], **kw)[0].tokens == outs[0].tokens
+    assert llm.generate(prompts, max_batch=1, **kw)[2].tokens == outs[2].tokens
+
+
+@pytest.mark.parametrize("name,dtype", [("a", "bfloat16"), ("c", "bfloat16"), ("d", "bfloat16"), ("c", "float32")])
+def test_greedy_batches_with_stop_and_reuse(llms, name, dtype):
+    """Seven requests through a cache that holds three at a time; one stop token ends
+    some of them early.  Greedy ids equal the plain implementation's wherever its top
+    two logits are further apart than the engine's tolerance."""
+    storage = "float32" if dtype == "float32" else "bfloat16"
+    lens = [3, 40, 17, 1, 64 if name != "a" else 50, 9, 30]
+    prompts = [random_tokens(name, n, 40 + i) for i, n in enumerate(lens)]
+    n_new = 12
+    ref0, _ = plain_generate(name, storage, prompts[1], n_new)
+    first_seen = [j for j in range(n_new) if ref0[j] not in ref0[:j]]
+    cut = first_seen[-1]                      # greedy output repeats itself: stop at a token's first occurrence
+    assert cut >= 1
+    stop = {ref0[cut]}
+    llm = llms(name, dtype, max_tokens=3 * 128)
+    outs = llm.generate(prompts, n=n_new, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0,
+                        stop_ids=stop)
+    cfg, W = plain_model(name, storage)
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        toks = list(p)
+        for j, t in enumerate(o.tokens + ([o.stop_token] if o.stop_token is not None else [])):
+            logits = P.forward(cfg, W, toks, np.float32)[-1]
+            top = np.sort(logits)[-2:]
+            margin = 1e-4 if dtype == "float32" else 8 * 2.0 ** -8 * 2 * max(1.0, np.abs(logits).max())
+            if top[1] - top[0] > margin:
+                assert t == int(np.argmax(logits)), f"request {i} token {j}"
+            else:
+                assert logits[t] >= top[1] - margin, f"request {i} token {j}"
+            toks.append(t)
+        if o.finish_reason == "stop":
+            assert o.stop_token in stop and all(t not in stop for t in o.tokens)
+        else:
+            assert o.finish_reason == "length" and len(o.tokens) == n_new
+    assert outs[1].finish_reason == "stop" and len(outs[1].tokens) == cut
+    assert llm.engine.cache.table.pages.n_held == 0 and llm.engine.cache.table.slots.n_held == 0
+
+
+def test_filtered_sampling_is_reproducible_and_batch_independent(llms):
+    llm = llms("b", "float32")
+    prompts = [random_tokens("b", n, 70 + i) for i, n in enumerate([9, 4, 20, 6])]
+    kw = dict(n=10, seed=99)                                  # the reference's defaults otherwise
+    a = llm.generate(prompts, **kw)
+    b = llm.generate(prompts, **kw)
+    c = llm.generate(prompts, max_batch=3, **kw)
+    assert [o.tokens for o in a] == [o.tokens for o in b] == [o.tokens for o in c]
+    d = llm.generate(prompts, n=10, seed=100)
+    assert [o.tokens for o in a] != [o.tokens for o in d]
+    # top_k = 1 is greedy with the penalty applied, whatever the seed
+    e = llm.generate(prompts[:1], n=6, top_k=1, repeat_penalty=1.0, seed=5)[0]
+    assert e.tokens == plain_generate("b", "float32", prompts[0], 6)[0]
+
+
+def test_context_limit_and_errors(llms):
+    from gguf2bin_b200.engine import GenerationError, StepEntry, StepError
+    llm = llms("a", "float32")
+    p = random_tokens("a", 60, 5)
+    out = llm.generate([p], n=20, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0)[0]
+    assert out.finish_reason == "context" and len(out.tokens) == 4       # 64 positions in all
+    assert out.tokens == plain_generate("a", "float32", p, 4)[0]
+    out = llm.generate([p], n=20, ctx=62, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0)[0]
+    assert out.finish_reason == "context" and len(out.tokens) == 2
+    with pytest.raises(GenerationError, match="context"):
+        llm.generate([random_tokens("a", 65, 6)], n=1)
+    held = llm.engine.cache.table.pages.n_held
+    seq = llm.open_sequence()
+    for bad in ([StepEntry(seq, [300], [0])], [StepEntry(seq, [], [])], [StepEntry(seq, [1, 2], [2])],
+                [StepEntry(seq, [1] * 65, [])], [StepEntry(seq, [1], []), StepEntry(seq, [2], [])]):
+        with pytest.raises(StepError):
+            llm.step(bad)
+        assert seq.length == 0 and llm.engine.cache.table.pages.n_held == held
+    llm.close_sequence(seq)
+    with pytest.raises(StepError, match="not live"):
+        llm.step([StepEntry(seq, [1], [0])])

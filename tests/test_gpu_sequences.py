@@ -1,0 +1,191 @@
+"""Places where a cache or a batch goes wrong first: long decoding, the first tokens of a
+sequence, a far key among hundreds, page boundaries, a slot used again; and the trace
+replay program run as a user runs it."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import TINY, assert_close, model_folder, plain_logits, plain_model, random_tokens
+from plain import qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def make_engine(name, dtype, max_tokens=1024):
+    from gguf2bin_b200.engine import Engine, Model
+    storage = "float32" if dtype == "float32" else "bfloat16"
+    return Engine(Model.from_folder(model_folder(name, storage), dtype=dtype), max_tokens=max_tokens)
+
+
+@pytest.mark.parametrize("name,dtype", [("c", "float32"), ("c", "bfloat16"), ("d", "bfloat16")])
+def test_long_decoding(name, dtype):
+    """A short prompt, then some three hundred tokens one by one across several pages."""
+    from gguf2bin_b200.engine import StepEntry
+    n = 330 if name == "c" else 300
+    toks = random_tokens(name, n, 21)
+    eng = make_engine(name, dtype)
+    seq = eng.open_sequence()
+    got = [eng.step([StepEntry(seq, toks[:5], range(5))]).cpu().numpy()]
+    for t in toks[5:]:
+        got.append(eng.step([StepEntry(seq, [t], [0])]).cpu().numpy())
+    storage = "float32" if dtype == "float32" else "bfloat16"
+    assert_close(np.concatenate(got), plain_logits(name, storage, toks), dtype, f"{name}/{dtype} long decode")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_every_cut(dtype):
+    """The first six tokens of a sequence, cut into steps in every possible way."""
+    from gguf2bin_b200.engine import StepEntry
+    storage = "float32" if dtype == "float32" else "bfloat16"
+    toks = random_tokens("b", 6, 3)
+    ref = plain_logits("b", storage, toks)
+    eng = make_engine("b", dtype)
+    for mask in range(32):                               # a cut after token i where bit i is set
+        cuts = [i + 1 for i in range(5) if mask >> i & 1] + [6]
+        seq, got, a = eng.open_sequence(), [], 0
+        for b in cuts:
+            got.append(eng.step([StepEntry(seq, toks[a:b], range(b - a))]).cpu().numpy())
+            a = b
+        eng.close_sequence(seq)
+        assert_close(np.concatenate(got), ref, dtype, f"cuts {cuts}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_far_key_stands_out(dtype):
+    """Weights made so that one key, hundreds of positions back, takes nearly all the
+    attention of the last query: with queries and keys that ignore their input except
+    for a marker token, a cache that drops, shifts or mixes up one position shows at
+    once.  Checked against the plain implementation on the same weights."""
+    from gguf2bin_b200.engine import Engine, Model, StepEntry
+    from gguf2bin_b200.weights import write_random_model, write_safetensors
+    from helpers import tmp_root
+    name, storage = "c", ("float32" if dtype == "float32" else "bfloat16")
+    cfg, W = plain_model(name, storage)
+    W = {k: v.copy() for k, v in W.items()}
+    A, B, hd = 7, 8, TINY[name]["head_dim"]
+    # token A's embedding is direction 0, which only layer 0's queries read; token B's is
+    # direction 1, which only its keys and values read; both land in the two slowest
+    # rotary dimensions of every head, so the match survives hundreds of positions
+    E = W["model.embed_tokens.weight"]
+    E[A] = 0
+    E[A, 0] = 4.0
+    E[B] = 0
+    E[B, 1] = 4.0
+    for p, n_heads, col in (("q_proj", TINY[name]["num_attention_heads"], 0),
+                            ("k_proj", TINY[name]["num_key_value_heads"], 1)):
+        w = W[f"model.layers.0.self_attn.{p}.weight"]
+        w[:, 0] = 0
+        w[:, 1] = 0
+        for h in range(n_heads):
+            w[h * hd + hd // 2 - 1, col] = 1.5
+            w[h * hd + hd - 1, col] = 1.5
+    W["model.layers.0.self_attn.v_proj.weight"][:, 1] = 0.5
+    folder = tmp_root() / f"far_key_{storage}"
+    folder.mkdir(exist_ok=True)
+    (folder / "config.json").write_text(json.dumps(TINY[name]))
+    tdt = torch.float32 if storage == "float32" else torch.bfloat16
+    write_safetensors(folder / "model.safetensors",
+                      [(k, v.shape, tdt, (lambda v=v: torch.from_numpy(v).to(tdt))) for k, v in W.items()])
+    cfg2, W2 = P.read_model_folder(folder)
+    toks = [t if t not in (A, B) else 9 for t in random_tokens(name, 400, 9)]
+    toks[37] = B                                         # the far key
+    toks[-1] = A                                         # the query that looks for it
+    ref = P.forward(cfg2, W2, toks, np.float32)
+    base = P.forward(cfg2, W2, toks[:37] + [10] + toks[38:], np.float32)
+    tol = (1e-5 if dtype == "float32" else 8 * 2.0 ** -8) * max(1.0, np.abs(ref).max())
+    assert np.abs(ref[-1] - base[-1]).max() > 3 * tol, \
+        "the construction does not make the far key matter"
+    eng = Engine(Model.from_folder(folder, dtype=dtype), max_tokens=1024)
+    seq = eng.open_sequence()
+    got = [eng.step([StepEntry(seq, toks[:300], range(300))]).cpu().numpy()]
+    for t in toks[300:]:
+        got.append(eng.step([StepEntry(seq, [t], [0])]).cpu().numpy())
+    assert_close(np.concatenate(got), ref, dtype, "far key")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_page_edges_and_slot_reuse(dtype):
+    """Prompts that end just before, at and just after a page boundary, decoded across
+    it, on a cache whose only free pages are the ones the previous sequence left full
+    of other data."""
+    from gguf2bin_b200.engine import StepEntry
+    storage = "float32" if dtype == "float32" else "bfloat16"
+    eng = make_engine("c", dtype, max_tokens=192)        # three pages: one sequence at a time
+    for i, plen in enumerate([63, 64, 65, 127, 128, 129]):
+        toks = random_tokens("c", plen + 4, 50 + i)
+        seq = eng.open_sequence()
+        got = [eng.step([StepEntry(seq, toks[:plen], [plen - 1])]).cpu().numpy()]
+        for t in toks[plen:]:
+            got.append(eng.step([StepEntry(seq, [t], [0])]).cpu().numpy())
+        eng.close_sequence(seq)
+        ref = plain_logits("c", storage, toks)[plen - 1:]
+        assert_close(np.concatenate(got), ref, dtype, f"prompt of {plen}")
+
+
+def test_padding_rows_change_nothing():
+    """A batch with a one-token neighbour gives bit-equal logits to the same request
+    alone: there is no padding, and no reduction spans sequences."""
+    from gguf2bin_b200.engine import StepEntry
+    for dtype in ("float32", "bfloat16"):
+        eng = make_engine("b", dtype)
+        toks, other = random_tokens("b", 50, 1), random_tokens("b", 1, 2)
+        s = eng.open_sequence()
+        alone = eng.step([StepEntry(s, toks, range(50))]).clone()
+        eng.close_sequence(s)
+        s1, s2 = eng.open_sequence(), eng.open_sequence()
+        both = eng.step([StepEntry(s2, other, [0]), StepEntry(s1, toks, range(50))])
+        assert torch.equal(both[1:], alone)
+        eng.close_sequence(s1); eng.close_sequence(s2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, tmp_path):
+    """bin/trace_run as a user runs it: a batch of unequal requests, shorter ones ending
+    earlier, then a second batch in the freed slots, with some steps wanting nothing."""
+    storage = "float32" if dtype == "float32" else "bfloat16"
+    reqs = {"r0": random_tokens("b", 40, 80), "r1": random_tokens("b", 9, 81),
+            "r2": random_tokens("b", 70, 82), "r3": random_tokens("b", 33, 83)}
+    steps, expect = [], {}
+    n = 0
+    for batch in (["r0", "r1"], ["r2", "r3"]):
+        heads = {r: max(1, len(reqs[r]) - 6) for r in batch}
+        done = dict(heads)
+        entries = [{"id": r, "tokens": reqs[r][:heads[r]], "want": [0, heads[r] - 1]} for r in batch]
+        expect[n] = [(r, i) for r in batch for i in (0, heads[r] - 1)]
+        steps.append({"step": n, "entries": entries, "end": [r for r in batch if done[r] == len(reqs[r])]})
+        n += 1
+        live = [r for r in batch if done[r] < len(reqs[r])]
+        while live:
+            want_now = n % 2 == 0
+            entries = [{"id": r, "tokens": [reqs[r][done[r]]], "want": [0] if want_now else []} for r in live]
+            if want_now:
+                expect[n] = [(r, done[r]) for r in live]
+            for r in live:
+                done[r] += 1
+            ended = [r for r in live if done[r] == len(reqs[r])]
+            steps.append({"step": n, "entries": entries, "end": ended})
+            live = [r for r in live if r not in ended]
+            n += 1
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model",
+                           str(model_folder("b", storage)), "--dtype", dtype, "--out", str(out),
+                           "--max-tokens", "192"],
+                          input="".join(json.dumps(s) + "\n" for s in steps), text=True,
+                          capture_output=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == [w for s in steps for w in ("done", str(s["step"]))]
+    V = TINY["b"]["vocab_size"]
+    for s in steps:
+        f = out / f"{s['step']}.f32"
+        if s["step"] not in expect:
+            assert not f.exists()
+            continue
+        got = np.fromfile(f, "<f4").reshape(-1, V)
+        ref = np.stack([plain_logits("b", storage, reqs[r])[i] for r, i in expect[s["step"]]])
+        assert_close(got, ref, dtype, f"trace step {s['step']}")
