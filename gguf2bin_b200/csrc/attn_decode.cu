@@ -1,0 +1,310 @@
+// Decode attention over the paged bfloat16 cache, split along the keys.
+//
+// One token per query row: every token t of the step attends, for each of its query
+// heads, to the keys 0..pos_t of its own sequence (optionally only the last `window`).
+// Grid (key chunk, kv head x head tile, token): a CTA takes one chunk of CHUNK_KEYS keys
+// (chunks start at absolute positions that are multiples of CHUNK_KEYS, so the split of
+// a token's keys depends on nothing but its position) and ALL query heads that share the
+// kv head: they are the rows of a 16-row tensor-core tile, so K and V are read once per
+// group.  Each warp streams whole pages: K and V panels of a (page, kv head) are
+// contiguous, copied with 16-byte cp.async into XOR-swizzled shared memory and read back
+// with ldmatrix; while a warp computes on K the V of the same page is in flight, while it
+// computes P.V the next K is.  Scores, softmax statistics and the output are 32-bit;
+// probabilities are rounded to bfloat16 for the P.V product.
+//
+// Each CTA writes an unnormalised partial output with its maximum and sum (log2 domain)
+// to scratch; `attn_combine_kernel` merges a token's chunks in increasing order.
+//
+// Formula: src/l5_model.c:518, 559-577 of AnonymoDGH/gguf2bin.  Compiled per head size
+// (-DHD=64 or 128); the page size is 64 keys.
+#include "common.cuh"
+#include "mma.cuh"
+
+G2B_DEFINE_LAST_ERROR
+
+#ifndef HD
+#define HD 128
+#endif
+static_assert(HD == 64 || HD == 128, "attn_decode: head sizes 64 and 128");
+
+constexpr int PAGE = 64;                       // keys per page
+constexpr int ROW_BYTES = HD * 2;
+constexpr int ROW_CHUNKS = HD / 8;             // 16-byte pieces per row
+constexpr int PANEL_BYTES = PAGE * ROW_BYTES;  // one (page, kv head) panel of K or of V
+constexpr int WARPS = 2;
+constexpr int PAGES_PER_CTA = 4;
+constexpr int CHUNK_KEYS = PAGE * PAGES_PER_CTA;
+constexpr int KSTEPS = HD / 16;                // k-steps of q.k over the head size
+constexpr int DTILES = HD / 8;                 // n-tiles of the output over the head size
+constexpr float LOG2E = 1.4426950408889634f;
+
+// byte offset of (row, 16-byte piece) in a swizzled panel
+__device__ __forceinline__ uint32_t swz(int row, int piece) {
+  return (uint32_t)(row * ROW_BYTES + ((piece ^ (row & 7)) << 4));
+}
+
+__device__ __forceinline__ void load_panel(uint32_t smem_panel, const bf16 *gpanel, int lane) {
+  // PAGE * ROW_CHUNKS pieces, 32 lanes
+#pragma unroll
+  for (int i = 0; i < PAGE * ROW_CHUNKS / 32; ++i) {
+    const int idx = i * 32 + lane;
+    const int row = idx / ROW_CHUNKS, piece = idx % ROW_CHUNKS;
+    cp_async_16(smem_panel + swz(row, piece), gpanel + (size_t)row * HD + piece * 8);
+  }
+}
+
+__global__ void __launch_bounds__(WARPS * 32)
+attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
+                   const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
+                   const int *__restrict__ page_table, int P, int nh, int nkv, int window,
+                   float scale_log2, float *__restrict__ part_o, float2 *__restrict__ part_ml,
+                   int n_chunks) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int group = nh / nkv;
+  const int head_tiles = (group + 15) / 16;
+  const int chunk = blockIdx.x;
+  const int kvh = blockIdx.y / head_tiles, ht = blockIdx.y % head_tiles;
+  const int t = blockIdx.z;
+  const int pos = tok_pos[t], b = tok_seq[t];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int key_begin = chunk * CHUNK_KEYS;
+  if (key_begin > pos || key_begin + CHUNK_KEYS <= lo) return;     // no key of this chunk is seen
+
+  unsigned char *my = smem + warp * 2 * PANEL_BYTES;
+  const uint32_t k_smem = smem_u32(my), v_smem = smem_u32(my + PANEL_BYTES);
+
+  // the pages of this warp: key_begin/PAGE + warp, + WARPS, ... that hold a visible key
+  const int first_page = key_begin / PAGE;
+  int pages[PAGES_PER_CTA / WARPS];
+  int n_pages = 0;
+#pragma unroll
+  for (int i = 0; i < PAGES_PER_CTA / WARPS; ++i) {
+    const int pg = first_page + warp + i * WARPS;
+    if (pg * PAGE <= pos && (pg + 1) * PAGE > lo) pages[n_pages++] = pg;
+  }
+  const size_t panel_elems = (size_t)PAGE * HD;
+  auto k_panel = [&](int pg) {
+    const int phys = page_table[(size_t)b * P + pg];
+    return cache + (((size_t)phys * 2 + 0) * nkv + kvh) * panel_elems;
+  };
+  auto v_panel = [&](int pg) {
+    const int phys = page_table[(size_t)b * P + pg];
+    return cache + (((size_t)phys * 2 + 1) * nkv + kvh) * panel_elems;
+  };
+
+  if (n_pages > 0) load_panel(k_smem, k_panel(pages[0]), lane);
+  cp_async_commit();
+  if (n_pages > 0) load_panel(v_smem, v_panel(pages[0]), lane);
+  cp_async_commit();
+
+  // query rows of this tile: head = kvh*group + ht*16 + row, as A fragments
+  const int row0 = ht * 16 + g, row1 = row0 + 8;
+  const bf16 *q0 = q + ((size_t)t * nh + (size_t)kvh * group + row0) * HD;
+  const bf16 *q1 = q0 + 8 * HD;
+  uint32_t qa[KSTEPS][4];
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    const int d = ks * 16 + 2 * c;
+    qa[ks][0] = row0 < group ? *reinterpret_cast<const uint32_t *>(q0 + d) : 0u;
+    qa[ks][1] = row1 < group ? *reinterpret_cast<const uint32_t *>(q1 + d) : 0u;
+    qa[ks][2] = row0 < group ? *reinterpret_cast<const uint32_t *>(q0 + d + 8) : 0u;
+    qa[ks][3] = row1 < group ? *reinterpret_cast<const uint32_t *>(q1 + d + 8) : 0u;
+  }
+
+  float o[DTILES][4];
+#pragma unroll
+  for (int n = 0; n < DTILES; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  for (int i = 0; i < n_pages; ++i) {
+    const int key0 = pages[i] * PAGE;
+    cp_async_wait<1>();                    // this page's K has landed (its V may be in flight)
+    __syncwarp();
+    float s[PAGE / 8][4];
+#pragma unroll
+    for (int j = 0; j < PAGE / 8; ++j) {
+      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+      for (int kp = 0; kp < KSTEPS / 2; ++kp) {
+        uint32_t kb[4];
+        ldmatrix_x4(kb, k_smem + swz(8 * j + (lane & 7), 4 * kp + (lane >> 3)));
+        mma_bf16_16816(s[j], qa[2 * kp], kb[0], kb[1]);
+        mma_bf16_16816(s[j], qa[2 * kp + 1], kb[2], kb[3]);
+      }
+    }
+    __syncwarp();                          // every lane is done reading K
+    if (i + 1 < n_pages) load_panel(k_smem, k_panel(pages[i + 1]), lane);
+    cp_async_commit();
+
+    // scale (log2 domain), mask, running maximum and sum
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < PAGE / 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key0 + 8 * j + 2 * c + (e & 1);
+        const float v = (key <= pos && key >= lo) ? s[j][e] * scale_log2 : -INFINITY;
+        s[j][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float m_new = fmaxf(m[r], mx[r]);          // finite: the page holds a visible key
+      corr[r] = exp2f(m[r] - m_new);
+      m[r] = m_new;
+      l[r] *= corr[r];
+    }
+    uint32_t pa[PAGE / 16][4];
+#pragma unroll
+    for (int j = 0; j < PAGE / 8; ++j) {
+      const float p0 = exp2f(s[j][0] - m[0]), p1 = exp2f(s[j][1] - m[0]);
+      const float p2 = exp2f(s[j][2] - m[1]), p3 = exp2f(s[j][3] - m[1]);
+      l[0] += p0 + p1;
+      l[1] += p2 + p3;
+      pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
+      pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int n = 0; n < DTILES; ++n) {
+      o[n][0] *= corr[0]; o[n][1] *= corr[0];
+      o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+
+    cp_async_wait<1>();                    // this page's V has landed (the next K may be in flight)
+    __syncwarp();
+#pragma unroll
+    for (int kk = 0; kk < PAGE / 16; ++kk) {
+#pragma unroll
+      for (int dp = 0; dp < DTILES / 2; ++dp) {
+        uint32_t vb[4];
+        // matrices: (keys +0..7, d tile 2dp), (keys +8..15, d tile 2dp), (keys +0..7, 2dp+1), (+8..15, 2dp+1)
+        const int mi = lane >> 3;
+        ldmatrix_x4_trans(vb, v_smem + swz(16 * kk + (mi & 1) * 8 + (lane & 7), 2 * dp + (mi >> 1)));
+        mma_bf16_16816(o[2 * dp], pa[kk], vb[0], vb[1]);
+        mma_bf16_16816(o[2 * dp + 1], pa[kk], vb[2], vb[3]);
+      }
+    }
+    __syncwarp();
+    if (i + 1 < n_pages) load_panel(v_smem, v_panel(pages[i + 1]), lane);
+    cp_async_commit();
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+
+  // merge the warps in order through shared memory (the panels are no longer needed)
+  __syncthreads();
+  float *xo = reinterpret_cast<float *>(smem);                 // [WARPS][32 lanes][DTILES*4 + 4]
+  constexpr int PER_LANE = DTILES * 4 + 4;
+  if (warp > 0) {
+    float *dst = xo + ((size_t)warp * 32 + lane) * PER_LANE;
+#pragma unroll
+    for (int n = 0; n < DTILES; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) dst[n * 4 + e] = o[n][e];
+    dst[DTILES * 4 + 0] = m[0]; dst[DTILES * 4 + 1] = m[1];
+    dst[DTILES * 4 + 2] = l[0]; dst[DTILES * 4 + 3] = l[1];
+  }
+  __syncthreads();
+  if (warp == 0) {
+#pragma unroll
+    for (int w = 1; w < WARPS; ++w) {
+      const float *src = xo + ((size_t)w * 32 + lane) * PER_LANE;
+      float a[2], bb[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const float mo = src[DTILES * 4 + r];
+        const float m_new = fmaxf(m[r], mo);
+        a[r] = m[r] == -INFINITY ? 0.f : exp2f(m[r] - m_new);
+        bb[r] = mo == -INFINITY ? 0.f : exp2f(mo - m_new);
+        l[r] = l[r] * a[r] + src[DTILES * 4 + 2 + r] * bb[r];
+        m[r] = m_new;
+      }
+#pragma unroll
+      for (int n = 0; n < DTILES; ++n) {
+        o[n][0] = o[n][0] * a[0] + src[n * 4 + 0] * bb[0];
+        o[n][1] = o[n][1] * a[0] + src[n * 4 + 1] * bb[0];
+        o[n][2] = o[n][2] * a[1] + src[n * 4 + 2] * bb[1];
+        o[n][3] = o[n][3] * a[1] + src[n * 4 + 3] * bb[1];
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = ht * 16 + g + 8 * r;
+      if (row >= group) continue;
+      const size_t slot = ((size_t)t * nh + (size_t)kvh * group + row) * n_chunks + chunk;
+      float *po = part_o + slot * HD;
+#pragma unroll
+      for (int n = 0; n < DTILES; ++n)
+        *reinterpret_cast<float2 *>(po + 8 * n + 2 * c) = make_float2(o[n][2 * r], o[n][2 * r + 1]);
+      if (c == 0) part_ml[slot] = make_float2(m[r], l[r]);
+    }
+  }
+}
+
+// out[t, h, :] = sum_i 2^(m_i - M) o_i / sum_i 2^(m_i - M) l_i over the token's chunks in order
+__global__ void __launch_bounds__(HD)
+attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__ part_ml,
+                    const int *__restrict__ tok_pos, int nh, int window, int n_chunks,
+                    bf16 *__restrict__ out) {
+  const size_t th = blockIdx.x;                                // t * nh + h
+  const int t = (int)(th / nh), d = threadIdx.x;
+  const int pos = tok_pos[t];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int c0 = lo / CHUNK_KEYS, c1 = pos / CHUNK_KEYS;
+  const float2 *ml = part_ml + th * n_chunks;
+  float M = -INFINITY;
+  for (int i = c0; i <= c1; ++i) M = fmaxf(M, ml[i].x);
+  float num = 0.f, den = 0.f;
+  for (int i = c0; i <= c1; ++i) {
+    const float w = exp2f(ml[i].x - M);
+    num = fmaf(w, part_o[(th * n_chunks + i) * HD + d], num);
+    den = fmaf(w, ml[i].y, den);
+  }
+  out[th * HD + d] = __float2bfloat16_rn(num / den);
+}
+
+// Scratch: part_o float [T*nh*n_chunks*HD], part_ml float2 [T*nh*n_chunks], with
+// n_chunks = ceil(max_kv_len / 256).  q, out [T, nh*HD] bfloat16.
+extern "C" int g2b_attn_decode(const void *q, void *out, const void *cache, const int *tok_pos,
+                               const int *tok_seq, const int *page_table, int P, int T, int nh,
+                               int nkv, int hd, int page_size, int window, float scale,
+                               int max_kv_len, float *part_o, float *part_ml,
+                               cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (hd != HD) G2B_REFUSE("attn_decode: built for head_dim %d, got %d", HD, hd);
+  if (page_size != PAGE) G2B_REFUSE("attn_decode: page size must be %d, got %d", PAGE, page_size);
+  if (nkv <= 0 || nh % nkv) G2B_REFUSE("attn_decode: %d heads are not a multiple of %d kv heads", nh, nkv);
+  if (T > 65535) G2B_REFUSE("attn_decode: %d tokens in one step (at most 65535)", T);
+  const int group = nh / nkv, head_tiles = (group + 15) / 16;
+  if ((long long)nkv * head_tiles > 65535) G2B_REFUSE("attn_decode: too many kv heads (%d)", nkv);
+  const int n_chunks = (max_kv_len + CHUNK_KEYS - 1) / CHUNK_KEYS;
+  if (n_chunks <= 0) G2B_REFUSE("attn_decode: max_kv_len %d", max_kv_len);
+  const int smem = WARPS * 2 * PANEL_BYTES;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) G2B_REFUSE("attn_decode: shared memory of %d bytes refused: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid(n_chunks, nkv * head_tiles, T);
+  attn_decode_kernel<<<grid, WARPS * 32, smem, stream>>>(
+      (const bf16 *)q, (const bf16 *)cache, tok_pos, tok_seq, page_table, P, nh, nkv, window,
+      scale * LOG2E, part_o, (float2 *)part_ml, n_chunks);
+  int rc = g2b_check_launch("attn_decode");
+  if (rc) return rc;
+  attn_combine_kernel<<<(unsigned)((size_t)T * nh), HD, 0, stream>>>(
+      part_o, (const float2 *)part_ml, tok_pos, nh, window, n_chunks, (bf16 *)out);
+  return g2b_check_launch("attn_combine");
+}
+
+extern "C" int g2b_attn_decode_chunk_keys() { return CHUNK_KEYS; }

@@ -2,7 +2,17 @@
 False when it does not take the case (the caller then uses the 32-bit kernel)."""
 from __future__ import annotations
 
+from ctypes import c_float, c_int, c_void_p
+
 import torch
+
+from .csrc import units
+from .kernels import _call, _fn, _ptr, _stream
+
+FAST_HEAD_SIZES = (64, 128)          # head sizes the tensor-core attention kernels are written for
+DECODE_CHUNK_KEYS = 256              # keys per CTA of the decode kernel (attn_decode.cu)
+
+units.SPECIALISED_SOURCES[:] = [("attn_decode.cu", ())]
 
 
 def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
@@ -15,4 +25,27 @@ def gate_up_bf16(h: torch.Tensor, w_gate_up: torch.Tensor, mid: torch.Tensor, bl
 
 def attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
                    scale) -> bool:
+    if head_dim not in FAST_HEAD_SIZES or page_size != 64 or cache_pages.dtype != torch.bfloat16:
+        return False
+    if ctx.all_single:
+        attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window, scale)
+        return True
     return False
+
+
+def attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
+                scale) -> None:
+    """One token per sequence: split-key attention with partial results in scratch memory
+    and a combine pass."""
+    T = q.shape[0]
+    n_chunks = -(-max(int(ctx.max_kv_len), 1) // DECODE_CHUNK_KEYS)
+    ws = ctx.workspace
+    part_o = ws.buffer("attn.part_o", (T * n_heads * n_chunks * head_dim,), torch.float32)
+    part_ml = ws.buffer("attn.part_ml", (T * n_heads * n_chunks * 2,), torch.float32)
+    f = _fn("attn_decode.cu", "g2b_attn_decode",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p],
+            defines=(f"HD={head_dim}",))
+    _call(f, _ptr(q), _ptr(out), _ptr(cache_pages), _ptr(ctx.tok_pos), _ptr(ctx.tok_seq),
+          _ptr(ctx.page_table), ctx.page_table.shape[1], T, n_heads, n_kv_heads, head_dim,
+          page_size, window, scale, int(ctx.max_kv_len), _ptr(part_o), _ptr(part_ml), _stream())

@@ -230,3 +230,37 @@ def test_sampling_filtered(top_k, top_p, penalty):
     for r in range(R):
         rec = recent[r, :recent_n[r]].tolist()
         assert ids[r].item() == P.sample_advanced(logits[r].cpu().numpy(), 0.0, top_k, top_p, penalty, rec, 0.5)[0]
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(16, 8, 128, 0), (5, 1, 128, 0), (20, 1, 64, 0), (6, 2, 64, 300),
+                                              (4, 4, 128, 70)])
+def test_attn_decode(nh, nkv, hd, window):
+    """Split-key decode attention: one token per sequence at positions before, at and
+    after chunk (256) and page (64) edges; groups of 1, 2, 5 and 20 query heads per kv
+    head; a window that starts inside a chunk."""
+    from types import SimpleNamespace
+    from gguf2bin_b200 import kernels_bf16
+    from gguf2bin_b200.engine.workspace import Workspace
+    ps = 64
+    lens = [1, 63, 64, 65, 255, 256, 257, 700, 1025]
+    cache, table, Ks, Vs = make_paged(len(lens), lens, nkv, hd, ps, torch.bfloat16, seed=40)
+    T = len(lens)
+    q = rnd(T, nh * hd, dtype=torch.bfloat16, seed=41)
+    # make one far key stand out for the longest sequence
+    Ks[-1][17] = (q[-1].view(nh, hd)[0] * 0.5)[None, :].expand(nkv, hd)
+    pg = int(table[T - 1, 0])
+    cache[pg, 0, :, 17] = Ks[-1][17]
+    out = torch.empty_like(q)
+    ctx = SimpleNamespace(tok_pos=torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV),
+                          tok_seq=torch.arange(T, dtype=torch.int32, device=DEV), page_table=table,
+                          max_kv_len=table.shape[1] * ps, workspace=Workspace(DEV), all_single=True)
+    scale = 1 / math.sqrt(hd)
+    assert kernels_bf16.attention_bf16(q, out, cache, ctx, nh, nkv, hd, ps, window, scale)
+    got = out.float().cpu().numpy().reshape(T, nh, hd)
+    for b, l in enumerate(lens):
+        K, V = Ks[b].float().cpu().numpy(), Vs[b].float().cpu().numpy()
+        qfull = np.zeros((l, nh, hd), np.float32)
+        qfull[-1] = q[b].float().cpu().numpy().reshape(nh, hd)
+        ref = P.causal_attention(qfull, K, V, np.float32, window=window)[-1]
+        np.testing.assert_allclose(got[b], ref, atol=2.0 ** -7 * max(1, np.abs(ref).max()), rtol=0,
+                                   err_msg=f"sequence of {l} keys")
