@@ -1,0 +1,201 @@
+// Matrix product for few rows (decode): C[M,N] = A[M,K] * W[N,K]^T, bfloat16 in, 32-bit
+// accumulation, M <= 64.  The time goes to reading W once, so the kernel is built around
+// the weight stream:
+//
+//  * Operands are swapped: 16 rows of W are the 16-row operand of mma.m16n8k16 and the
+//    batch is the 8-wide one, so no tensor-core work is wasted on padding M to 64 or 128.
+//  * A CTA owns 16 rows of W over the whole K; its 8 warps split every 256-wide block of
+//    K into 32-wide pieces.  A thread loads 16 contiguous bytes (8 values of k) of rows g
+//    and g+8 straight from global memory into registers.  The eight values feed two MMAs
+//    under a permutation of k that is applied to both operands alike, so no shuffle and
+//    no shared-memory staging of W is needed; several blocks of K are in flight at once.
+//  * The activations of a K block (M x 256) are staged in shared memory (double buffer).
+//  * The 8 partial sums of an output are added in warp order through shared memory: the
+//    order of the sum depends on K only, not on M or on the batch's contents.
+//
+// Epilogues: store (bfloat16 or float), add into a float matrix (the residual stream), or
+// the SiLU gate on a fused gate/up matrix whose rows alternate 8 gates / 8 ups:
+// out[m, 8b + r] = silu(row r of block b) * (row 8 + r)   (src/l3_math.c:57-62,
+// src/l5_model.c:594-595 of AnonymoDGH/gguf2bin).
+#include "common.cuh"
+#include "mma.cuh"
+
+G2B_DEFINE_LAST_ERROR
+
+constexpr int WARPS = 8;
+constexpr int KB = 256;                 // K block: 8 warps x 32
+constexpr int XPAD = 32;                // elements of padding per staged row (64 bytes)
+constexpr int XROW = KB + XPAD;
+constexpr int DEPTH = 4;                // K blocks of W in flight per thread
+
+enum { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ACCUM_F32 = 2, EPI_SWIGLU_BF16 = 3 };
+
+__device__ __forceinline__ uint4 ld_stream(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+template <int MT, int EPI>
+__global__ void __launch_bounds__(WARPS * 32)
+gemm_small_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W, void *__restrict__ Cv,
+                  int M, int N, int K, int lda, int ldw, int ldc) {
+  constexpr int MROWS = MT * 8;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  bf16 *xs = reinterpret_cast<bf16 *>(smem_raw);          // [2][MROWS][XROW]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int n0 = blockIdx.x * 16;
+  const int nkb = (K + KB - 1) / KB;
+
+  const bf16 *w0 = W + (size_t)min(n0 + g, N - 1) * ldw;
+  const bf16 *w1 = W + (size_t)min(n0 + g + 8, N - 1) * ldw;
+  const int kw = 32 * warp + 8 * c;                       // this thread's k offset in a block
+
+  auto load_w = [&](uint4 (&dst)[2], int kb) {
+    const int k = kb * KB + kw;
+    if (k < K) {
+      dst[0] = ld_stream(w0 + k);
+      dst[1] = ld_stream(w1 + k);
+    } else {
+      dst[0] = dst[1] = make_uint4(0, 0, 0, 0);
+    }
+  };
+  auto stage_x = [&](int kb, int buf) {
+    bf16 *dst = xs + (size_t)buf * MROWS * XROW;
+    for (int i = threadIdx.x; i < MROWS * (KB / 8); i += WARPS * 32) {
+      const int r = i / (KB / 8), piece = i % (KB / 8);
+      const int k = kb * KB + piece * 8;
+      bf16 *d = dst + r * XROW + piece * 8;
+      if (r < M && k < K) cp_async_16(smem_u32(d), A + (size_t)r * lda + k);
+      else *reinterpret_cast<uint4 *>(d) = make_uint4(0, 0, 0, 0);
+    }
+  };
+
+  uint4 wb[DEPTH][2];
+#pragma unroll
+  for (int d = 0; d < DEPTH; ++d)
+    if (d < nkb) load_w(wb[d], d);
+  stage_x(0, 0);
+  cp_async_commit();
+
+  float acc[MT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+
+  for (int kb0 = 0; kb0 < nkb; kb0 += DEPTH) {
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      const int kb = kb0 + d;
+      if (kb < nkb) {
+        if (kb + 1 < nkb) stage_x(kb + 1, (kb + 1) & 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const bf16 *xb = xs + (size_t)(kb & 1) * MROWS * XROW + 32 * warp + 8 * c;
+        const uint4 a_lo = wb[d][0], a_hi = wb[d][1];
+        const uint32_t a1[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};
+        const uint32_t a2[4] = {a_lo.z, a_hi.z, a_lo.w, a_hi.w};
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint4 xv = *reinterpret_cast<const uint4 *>(xb + (size_t)(8 * mt + g) * XROW);
+          mma_bf16_16816(acc[mt], a1, xv.x, xv.y);
+          mma_bf16_16816(acc[mt], a2, xv.z, xv.w);
+        }
+        if (kb + DEPTH < nkb) load_w(wb[d], kb + DEPTH);
+        __syncthreads();                 // the staged block may be overwritten two blocks on
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  // partial sums of the 8 warps -> shared memory [warp][16 rows][MROWS], summed in warp order
+  float *red = reinterpret_cast<float *>(smem_raw);
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    float *r0 = red + ((size_t)warp * 16 + g) * MROWS + 8 * mt + 2 * c;
+    float *r1 = r0 + 8 * MROWS;
+    r0[0] = acc[mt][0]; r0[1] = acc[mt][1];
+    r1[0] = acc[mt][2]; r1[1] = acc[mt][3];
+  }
+  __syncthreads();
+  if (EPI == EPI_SWIGLU_BF16) {
+    // rows 0..7 of the tile are gates, rows 8..15 the ups of the same outputs
+    for (int i = threadIdx.x; i < 8 * MROWS; i += WARPS * 32) {
+      const int m = i / 8, r = i % 8;
+      float gate = 0.f, up = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        gate += red[((size_t)w * 16 + r) * MROWS + m];
+        up += red[((size_t)w * 16 + 8 + r) * MROWS + m];
+      }
+      const int col = (n0 >> 1) + r;
+      if (m < M && n0 + 8 + r < N)
+        ((bf16 *)Cv)[(size_t)m * ldc + col] = __float2bfloat16_rn((gate / (1.f + expf(-gate))) * up);
+    }
+  } else {
+    for (int i = threadIdx.x; i < 16 * MROWS; i += WARPS * 32) {
+      const int m = i / 16, r = i % 16;
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) v += red[((size_t)w * 16 + r) * MROWS + m];
+      const int n = n0 + r;
+      if (m < M && n < N) {
+        const size_t o = (size_t)m * ldc + n;
+        if (EPI == EPI_STORE_BF16) ((bf16 *)Cv)[o] = __float2bfloat16_rn(v);
+        else if (EPI == EPI_STORE_F32) ((float *)Cv)[o] = v;
+        else ((float *)Cv)[o] += v;
+      }
+    }
+  }
+}
+
+template <int MT>
+static int launch_mt(const void *A, const void *W, void *C, int M, int N, int K, int lda, int ldw,
+                     int ldc, int epi, cudaStream_t stream) {
+  constexpr int MROWS = MT * 8;
+  const size_t stage = (size_t)2 * MROWS * XROW * sizeof(bf16);
+  const size_t red = (size_t)WARPS * 16 * MROWS * sizeof(float);
+  const int smem = (int)(stage > red ? stage : red);
+  const unsigned grid = (unsigned)((N + 15) / 16);
+#define G2B_LAUNCH(E)                                                                            \
+  do {                                                                                           \
+    static bool configured = false;                                                              \
+    if (!configured) {                                                                           \
+      cudaError_t e = cudaFuncSetAttribute(gemm_small_kernel<MT, E>,                             \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem);   \
+      if (e != cudaSuccess) G2B_REFUSE("gemm_small: shared memory: %s", cudaGetErrorString(e));  \
+      configured = true;                                                                         \
+    }                                                                                            \
+    gemm_small_kernel<MT, E><<<grid, WARPS * 32, smem, stream>>>(                                \
+        (const bf16 *)A, (const bf16 *)W, C, M, N, K, lda, ldw, ldc);                            \
+  } while (0)
+  switch (epi) {
+    case EPI_STORE_BF16: G2B_LAUNCH(EPI_STORE_BF16); break;
+    case EPI_STORE_F32: G2B_LAUNCH(EPI_STORE_F32); break;
+    case EPI_ACCUM_F32: G2B_LAUNCH(EPI_ACCUM_F32); break;
+    case EPI_SWIGLU_BF16: G2B_LAUNCH(EPI_SWIGLU_BF16); break;
+    default: G2B_REFUSE("gemm_small: unknown epilogue %d", epi);
+  }
+#undef G2B_LAUNCH
+  return g2b_check_launch("gemm_small");
+}
+
+// A [M,K] and W [N,K] bfloat16 with unit inner stride; rows 16-byte aligned.
+// epi: 0 store bfloat16, 1 store float, 2 add into float, 3 SiLU gate (C is [M, N/2] bfloat16;
+// N must be a multiple of 16).
+extern "C" int g2b_gemm_small(const void *A, const void *W, void *C, int M, int N, int K, int lda,
+                              int ldw, int ldc, int epi, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 64) G2B_REFUSE("gemm_small: M=%d (at most 64 rows)", M);
+  if (K <= 0 || K % 8 || lda % 8 || ldw % 8)
+    G2B_REFUSE("gemm_small: K=%d and the row strides (%d, %d) must be multiples of 8", K, lda, ldw);
+  if (((uintptr_t)A | (uintptr_t)W) & 15) G2B_REFUSE("gemm_small: operands must be 16-byte aligned");
+  if (epi == EPI_SWIGLU_BF16 && N % 16) G2B_REFUSE("gemm_small: gated output needs N %% 16 == 0, N=%d", N);
+  if (M <= 8) return launch_mt<1>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+  if (M <= 16) return launch_mt<2>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+  if (M <= 32) return launch_mt<4>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+  return launch_mt<8>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+}

@@ -10,10 +10,12 @@ GENERIC_UNITS = [("elementwise.cu", ()), ("gemm_simt.cu", ()), ("attn_generic.cu
 HEAD_SIZES = (64, 128)
 
 SPECIALISED_SOURCES: list = []          # filled by the bfloat16 kernels' bindings
+BF16_UNITS: list = []                   # bfloat16 kernels that take every size at run time
 
 
 def all_units() -> list:
-    units = list(GENERIC_UNITS)
+    from .. import kernels_bf16  # noqa: F401  (registers the bfloat16 kernels' sources)
+    units = list(GENERIC_UNITS) + [(s, ()) for s, _ in BF16_UNITS]
     for src, extra in SPECIALISED_SOURCES:
         for hd in HEAD_SIZES:
             units.append((src, (f"HD={hd}",) + tuple(extra)))

@@ -13,13 +13,51 @@ FAST_HEAD_SIZES = (64, 128)          # head sizes the tensor-core attention kern
 DECODE_CHUNK_KEYS = 256              # keys per CTA of the decode kernel (attn_decode.cu)
 
 units.SPECIALISED_SOURCES[:] = [("attn_decode.cu", ())]
+units.BF16_UNITS[:] = [("gemm_small.cu", ())]
+
+
+SMALL_M = 64                         # rows the weight-streaming product takes
+EPI_STORE_BF16, EPI_STORE_F32, EPI_ACCUM_F32, EPI_SWIGLU_BF16 = 0, 1, 2, 3
+
+
+def _small_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    K = a.shape[1]
+    return (a.shape[0] <= SMALL_M and K % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1
+            and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def _gemm_small(a, w, out, epi) -> None:
+    f = _fn("gemm_small.cu", "g2b_gemm_small",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _call(f, _ptr(a), _ptr(w), _ptr(out), a.shape[0], w.shape[0], a.shape[1], a.stride(0),
+          w.stride(0), out.stride(0), epi, _stream())
 
 
 def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
+    """out (=|+=) a @ w.T for bfloat16 a and w on the tensor cores."""
+    if out.stride(1) != 1:
+        return False
+    if accumulate:
+        if out.dtype != torch.float32:
+            return False
+        epi = EPI_ACCUM_F32
+    else:
+        epi = EPI_STORE_BF16 if out.dtype == torch.bfloat16 else EPI_STORE_F32
+    if _small_ok(a, w):
+        _gemm_small(a, w, out, epi)
+        return True
     return False
 
 
 def gate_up_bf16(h: torch.Tensor, w_gate_up: torch.Tensor, mid: torch.Tensor, block: int) -> bool:
+    """mid = silu(gate) * up with the gate computed in the product's epilogue; takes fused
+    matrices whose rows alternate 8 gates / 8 ups."""
+    if block != 8 or mid.dtype != torch.bfloat16 or mid.stride(1) != 1 or w_gate_up.shape[0] % 16:
+        return False
+    if _small_ok(h, w_gate_up):
+        _gemm_small(h, w_gate_up, mid, EPI_SWIGLU_BF16)
+        return True
     return False
 
 

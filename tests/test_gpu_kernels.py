@@ -264,3 +264,37 @@ def test_attn_decode(nh, nkv, hd, window):
         ref = P.causal_attention(qfull, K, V, np.float32, window=window)[-1]
         np.testing.assert_allclose(got[b], ref, atol=2.0 ** -7 * max(1, np.abs(ref).max()), rtol=0,
                                    err_msg=f"sequence of {l} keys")
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 48, 64), (8, 1024, 2048), (3, 200, 264), (16, 96, 1032),
+                                   (33, 1000, 520), (64, 311, 96)])
+def test_gemm_small(M, N, K):
+    """Weight-streaming product for few rows: every epilogue, widths that are no multiple
+    of the 16-row tile or of the 256-wide K block."""
+    from gguf2bin_b200 import kernels_bf16
+    a, w = rnd(M, K, dtype=torch.bfloat16, seed=60), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=61)
+    ref = a.double() @ w.double().T
+    tol = 1e-5 * math.sqrt(K) * max(1.0, ref.abs().max().item())
+    out = torch.full((M, N), 7.0, device=DEV)
+    assert kernels_bf16.linear_bf16(a, w, out, False)
+    assert (out.double() - ref).abs().max().item() < tol
+    base = rnd(M, N, seed=62)
+    acc = base.clone()
+    assert kernels_bf16.linear_bf16(a, w, acc, True)
+    assert (acc.double() - base.double() - ref).abs().max().item() < tol
+    out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    assert kernels_bf16.linear_bf16(a, w, out16, False)
+    assert (out16.double() - ref).abs().max().item() <= ref.abs().max().item() * 2.0 ** -8 + tol
+    # a row changes nothing in the other rows: bit-equal when run alone
+    if M > 1:
+        alone = torch.empty(1, N, device=DEV)
+        kernels_bf16.linear_bf16(a[M - 1:M], w, alone, False)
+        assert torch.equal(alone[0], out[M - 1])
+    if N % 16 == 0:
+        I = N // 2
+        g = ref.view(M, I // 8, 2, 8)[:, :, 0].reshape(M, I)
+        u = ref.view(M, I // 8, 2, 8)[:, :, 1].reshape(M, I)
+        want = (g / (1 + torch.exp(-g))) * u
+        mid = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+        assert kernels_bf16.gate_up_bf16(a, w, mid, 8)
+        assert (mid.double() - want).abs().max().item() <= want.abs().max().item() * 2.0 ** -8 + tol
