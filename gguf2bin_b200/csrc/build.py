@@ -15,6 +15,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -79,12 +80,26 @@ def _build_dir_locked() -> Path:
     raise KernelBuildError("no writable folder for built kernels; set GGUF2BIN_B200_BUILD_DIR")
 
 
+_INCLUDE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)
+
+
+def _with_includes(source: Path, seen: dict) -> None:
+    """``source`` and every file of this folder that it includes with quotes, recursively."""
+    if source.name in seen or not source.is_file():
+        return
+    text = source.read_text()
+    seen[source.name] = text
+    for name in _INCLUDE.findall(text):
+        _with_includes(CSRC / name, seen)
+
+
 def _digest(source: Path, defines: Sequence[str]) -> str:
     h = hashlib.sha256()
-    h.update(source.read_bytes())
-    for hdr in sorted(CSRC.glob("*.cuh")):
-        h.update(hdr.name.encode())
-        h.update(hdr.read_bytes())
+    files: dict = {}
+    _with_includes(source, files)
+    for name in sorted(files):
+        h.update(name.encode())
+        h.update(files[name].encode())
     h.update(" ".join(list(defines) + ARCH_FLAGS + BASE_FLAGS).encode())
     return h.hexdigest()[:16]
 

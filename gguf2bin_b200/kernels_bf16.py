@@ -12,7 +12,7 @@ from .kernels import _call, _fn, _ptr, _stream
 FAST_HEAD_SIZES = (64, 128)          # head sizes the tensor-core attention kernels are written for
 DECODE_CHUNK_KEYS = 256              # keys per CTA of the decode kernel (attn_decode.cu)
 
-units.SPECIALISED_SOURCES[:] = [("attn_decode.cu", ())]
+units.SPECIALISED_SOURCES[:] = [("attn_decode.cu", ()), ("attn_decode_noalloc.cu", ())]
 units.BF16_UNITS[:] = [("gemm_small.cu", ())]
 
 
