@@ -19,7 +19,7 @@ import torch
 
 from ..cache.pool import CacheError, Sequence
 from ..cache.storage import Cache
-from ..parts.base import StepContext
+from ..parts.base import ATTN_TILE_ROWS, StepContext
 from .model import Model
 from .workspace import Workspace
 
@@ -94,15 +94,27 @@ class Engine:
         T = sum(q_lens)
         P = max(len(e.seq.pages) for e in entries)
         n_want = sum(len(e.want) for e in entries)
-        # layout: tok_ids[T] tok_pos[T] tok_seq[T] want[n_want] seq_meta[B*4] page_table[B*P]
-        total = 3 * T + n_want + 4 * B + B * P
+        # prompt-attention work list: tiles of 64 query rows, the longest key ranges first
+        tiles = []
+        t0 = 0
+        for b, e in enumerate(entries):
+            for r in range(0, q_lens[b], ATTN_TILE_ROWS):
+                tiles.append((b, t0 + r, min(ATTN_TILE_ROWS, q_lens[b] - r), past[b] + r))
+            t0 += q_lens[b]
+        tiles.sort(key=lambda t: -(t[3] + t[2]))
+        n_tiles = len(tiles)
+        # layout: tiles[n_tiles*4] tok_ids[T] tok_pos[T] tok_seq[T] want[n_want] seq_meta[B*4]
+        #         page_table[B*P]   (the tiles come first: the kernel reads them 16 bytes at a time)
+        total = 4 * n_tiles + 3 * T + n_want + 4 * B + B * P
         if total > self._meta_cap:
             self._meta_cap = max(2 * total, 1024)
             self._meta_dev = torch.empty(self._meta_cap, dtype=torch.int32, device=self.device)
             self._meta_host = torch.empty(self._meta_cap, dtype=torch.int32, pin_memory=True)
         host = self._meta_host.numpy()
-        o_ids, o_pos, o_seq, o_want = 0, T, 2 * T, 3 * T
+        o_ids = 4 * n_tiles
+        o_pos, o_seq, o_want = o_ids + T, o_ids + 2 * T, o_ids + 3 * T
         o_meta = o_want + n_want
+        host[:4 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
         o_pt = o_meta + 4 * B
         t0 = w0 = 0
         for b, e in enumerate(entries):
@@ -126,7 +138,8 @@ class Engine:
             page_size=self.cache.page_size, workspace=self.workspace, dtype=self.model.dtype,
             q_lens=q_lens, past_lens=past, slots=[e.seq.slot for e in entries],
             max_kv_len=max(p + n for p, n in zip(past, q_lens)),
-            seq_meta=dev[o_meta:o_meta + 4 * B].view(B, 4))
+            seq_meta=dev[o_meta:o_meta + 4 * B].view(B, 4),
+            attn_tiles=dev[:4 * n_tiles].view(n_tiles, 4), n_attn_tiles=n_tiles)
         return ctx, dev[o_want:o_want + n_want], n_want
 
     def step(self, entries: Seq[StepEntry]) -> Optional[torch.Tensor]:

@@ -12,7 +12,8 @@ from .kernels import _call, _fn, _ptr, _stream
 FAST_HEAD_SIZES = (64, 128)          # head sizes the tensor-core attention kernels are written for
 DECODE_CHUNK_KEYS = 256              # keys per CTA of the decode kernel (attn_decode.cu)
 
-units.SPECIALISED_SOURCES[:] = [("attn_decode.cu", ()), ("attn_decode_noalloc.cu", ())]
+units.SPECIALISED_SOURCES[:] = [("attn_decode.cu", ()), ("attn_decode_noalloc.cu", ()),
+                                ("attn_prefill.cu", ())]
 units.BF16_UNITS[:] = [("gemm_small.cu", ())]
 
 
@@ -68,7 +69,21 @@ def attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page
     if ctx.all_single:
         attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window, scale)
         return True
+    if getattr(ctx, "attn_tiles", None) is not None and ctx.n_attn_tiles > 0:
+        attn_prefill(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window, scale)
+        return True
     return False
+
+
+def attn_prefill(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
+                 scale) -> None:
+    """Prompt attention over the step's work list of 64-row query tiles."""
+    f = _fn("attn_prefill.cu", "g2b_attn_prefill",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+             c_int, c_int, c_float, c_void_p], defines=(f"HD={head_dim}",))
+    _call(f, _ptr(q), _ptr(out), _ptr(cache_pages), _ptr(ctx.attn_tiles), ctx.n_attn_tiles,
+          _ptr(ctx.page_table), ctx.page_table.shape[1], n_heads, n_kv_heads, head_dim, page_size,
+          window, scale, _stream())
 
 
 def attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,

@@ -25,6 +25,9 @@ from typing import Optional
 import torch
 
 
+ATTN_TILE_ROWS = 64          # query rows per work item of the prompt attention kernel
+
+
 @dataclass
 class StepContext:
     """One step's batch as the kernels see it.  All index tensors are int32 on the device.
@@ -49,6 +52,8 @@ class StepContext:
     slots: list = field(default_factory=list)        # slot of each sequence
     max_kv_len: int = 0                              # longest sequence after this step
     seq_meta: Optional[torch.Tensor] = None          # [B,4] int32: q_start, q_len, past, slot
+    attn_tiles: Optional[torch.Tensor] = None        # [n,4] int32: sequence, first token, rows, position
+    n_attn_tiles: int = 0                            # of row 0; tiles of ATTN_TILE_ROWS query rows
 
     @property
     def all_single(self) -> bool:

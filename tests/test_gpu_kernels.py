@@ -298,3 +298,38 @@ def test_gemm_small(M, N, K):
         mid = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
         assert kernels_bf16.gate_up_bf16(a, w, mid, 8)
         assert (mid.double() - want).abs().max().item() <= want.abs().max().item() * 2.0 ** -8 + tol
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(16, 8, 128, 0), (5, 1, 128, 0), (6, 2, 64, 0), (4, 2, 64, 100),
+                                              (2, 2, 128, 33)])
+def test_attn_prefill(nh, nkv, hd, window):
+    """Prompt attention: a whole prompt that is no multiple of the 64-row tile, a prompt
+    continued after a past that ends inside a page, a single token far into a sequence,
+    and a short prompt; windows that start inside a page."""
+    from types import SimpleNamespace
+    from gguf2bin_b200 import kernels_bf16
+    ps = 64
+    lens = [333, 200, 700, 5]
+    q_lens = [333, 70, 1, 5]
+    cache, table, Ks, Vs = make_paged(len(lens), lens, nkv, hd, ps, torch.bfloat16, seed=70)
+    tiles, t0 = [], 0
+    for b, (l, ql) in enumerate(zip(lens, q_lens)):
+        for r in range(0, ql, 64):
+            tiles.append((b, t0 + r, min(64, ql - r), l - ql + r))
+        t0 += ql
+    T = t0
+    q = rnd(T, nh * hd, dtype=torch.bfloat16, seed=71)
+    out = torch.zeros_like(q)
+    ctx = SimpleNamespace(page_table=table, all_single=False, n_attn_tiles=len(tiles),
+                          attn_tiles=torch.tensor(tiles, dtype=torch.int32, device=DEV))
+    assert kernels_bf16.attention_bf16(q, out, cache, ctx, nh, nkv, hd, ps, window, 1 / math.sqrt(hd))
+    got = out.float().cpu().numpy().reshape(T, nh, hd)
+    t = 0
+    for b, (l, ql) in enumerate(zip(lens, q_lens)):
+        K, V = Ks[b].float().cpu().numpy(), Vs[b].float().cpu().numpy()
+        qfull = np.zeros((l, nh, hd), np.float32)
+        qfull[l - ql:] = q[t:t + ql].float().cpu().numpy().reshape(ql, nh, hd)
+        ref = P.causal_attention(qfull, K, V, np.float32, window=window)[l - ql:]
+        np.testing.assert_allclose(got[t:t + ql], ref, atol=2.0 ** -7 * max(1, np.abs(ref).max()), rtol=0,
+                                   err_msg=f"sequence {b}")
+        t += ql
