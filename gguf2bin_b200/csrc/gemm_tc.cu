@@ -1,0 +1,345 @@
+// Matrix product for many rows (prompts) on the 5th-generation tensor cores:
+//   C[M,N] = A[M,K] * W[N,K]^T, bfloat16 operands, float accumulation in tensor memory.
+//
+// One CTA computes a 128 x BN tile of C.  Roles by warp:
+//   warp 4, one thread   TMA producer: for every 64-wide block of K, two tiled bulk copies
+//                        (cp.async.bulk.tensor.2d, 128-byte swizzle) bring A[128 x 64] and
+//                        W[BN x 64] into a ring of shared-memory stages and signal the
+//                        stage's "full" mbarrier with their byte count.  No multicast.
+//   warp 5, one thread   MMA issuer: waits for "full", issues four tcgen05.mma
+//                        (cta_group::1, kind::f16, M=128, N=BN, K=16) whose operands are
+//                        shared-memory descriptors (K-major, SWIZZLE_128B, 1024 bytes between
+//                        8-row groups) and whose accumulator is BN columns of tensor memory;
+//                        tcgen05.commit frees the stage ("empty") and, after the last block,
+//                        signals "accumulator ready".  Warp 5 also allocates and frees the
+//                        tensor memory.
+//   warps 0..3           epilogue: each warp reads its 32 lanes of the accumulator with
+//                        tcgen05.ld (32 columns at a time) and writes C: store (bfloat16 or
+//                        float), add into a float matrix (the residual stream), or the SiLU
+//                        gate on a fused gate/up matrix whose rows alternate 8 gates / 8 ups
+//                        (src/l3_math.c:57-62, src/l5_model.c:594-595 of AnonymoDGH/gguf2bin).
+// Rows and columns past M, N and K are zero-filled by the TMA unit on load and masked on store.
+//
+// Every wait (mbarrier) gives up after a bounded number of polls: the thread records a
+// code in `*status`, all roles fall through to the common exit, the tensor memory is freed
+// and the kernel returns; the host reads `*status` (0 = fine).
+#include "common.cuh"
+
+#include <cuda.h>
+
+G2B_DEFINE_LAST_ERROR
+
+constexpr int BM = 128;
+constexpr int BK = 64;                      // 64 bf16 = 128 bytes = one swizzle row
+constexpr int STAGES = 3;
+constexpr int THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;   // polls of a barrier before giving up
+
+enum { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ACCUM_F32 = 2, EPI_SWIGLU_BF16 = 3 };
+enum { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3 };
+
+// ---- PTX wrappers -----------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+// true when the phase with the given parity has completed; false after SPIN_LIMIT polls
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+__device__ __forceinline__ uint32_t pack2(uint32_t lo, uint32_t hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(lo), __uint_as_float(hi));
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// Shared-memory operand descriptor: K-major tile of rows x 64 bf16, rows of 128 bytes,
+// 128-byte swizzle, 8-row groups 1024 bytes apart (the layout the TMA unit writes).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);          // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                          // leading byte offset (unused with swizzle): 1
+  d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                          // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D float, A and B bfloat16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <int BN> struct Smem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BARRIER_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BARRIER_OFFSET + 128 + 1024;   // barriers + tmem slot + alignment slack
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               void *__restrict__ Cv, int M, int N, int K, int ldc, int *__restrict__ status) {
+  extern __shared__ unsigned char smem_raw[];
+  using S = Smem<BN>;
+  // 1024-byte alignment: the swizzle pattern is a function of address bits 4..9
+  unsigned char *smem = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::BARRIER_OFFSET);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 1);
+  const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES);
+  const uint32_t acc_bar = smem_addr(bars + 2 * STAGES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int nkb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                     smem_addr(tmem_slot)), "r"((uint32_t)BN));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % STAGES;
+        if (kb >= STAGES && !mbar_wait(empty0 + 8 * s, ((kb / STAGES) - 1) & 1)) {
+          atomicExch(status, ST_PRODUCER_TIMEOUT);
+          break;
+        }
+        const uint32_t a_dst = smem_addr(smem + s * S::STAGE_BYTES);
+        mbar_expect_tx(full0 + 8 * s, S::STAGE_BYTES);
+        tma_load_2d(a_dst, &map_a, kb * BK, m0, full0 + 8 * s);
+        tma_load_2d(a_dst + S::A_BYTES, &map_w, kb * BK, n0, full0 + 8 * s);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BN);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int s = kb % STAGES;
+        if (!mbar_wait(full0 + 8 * s, (kb / STAGES) & 1)) {
+          atomicExch(status, ST_MMA_TIMEOUT);
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        const uint32_t a_addr = smem_addr(smem + s * S::STAGE_BYTES);
+        const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(a_addr + S::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)            // 16 bf16 = 32 bytes = 2 descriptor units
+          umma_bf16(tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+        umma_commit(empty0 + 8 * s);                 // the stage is free once these MMAs have read it
+      }
+      umma_commit(acc_bar);                          // all MMAs issued so far have completed
+    }
+  } else {
+    // epilogue: warp w owns accumulator lanes (rows) 32w .. 32w+31
+    if (!mbar_wait(acc_bar, 0)) {
+      if (lane == 0) atomicExch(status, ST_EPILOGUE_TIMEOUT);
+    } else {
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const int row = m0 + warp * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        const int n = n0 + c0;
+        if (row >= M || n >= N) continue;
+        if (EPI == EPI_SWIGLU_BF16) {
+          // columns 16b .. 16b+7 are gates, 16b+8 .. 16b+15 the ups of the same outputs
+          bf16 *dst = (bf16 *)Cv + (size_t)row * ldc + (n >> 1);
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float gate = __uint_as_float(r[16 * blk + j]);
+              const float up = __uint_as_float(r[16 * blk + 8 + j]);
+              if (n + 16 * blk + 8 + j < N)
+                dst[8 * blk + j] = __float2bfloat16_rn((gate / (1.f + expf(-gate))) * up);
+            }
+        } else if (EPI == EPI_STORE_BF16) {
+          bf16 *dst = (bf16 *)Cv + (size_t)row * ldc + n;
+          if (n + 32 <= N && ((((uintptr_t)dst) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 v;
+              v.x = pack2(r[j], r[j + 1]); v.y = pack2(r[j + 2], r[j + 3]);
+              v.z = pack2(r[j + 4], r[j + 5]); v.w = pack2(r[j + 6], r[j + 7]);
+              *reinterpret_cast<uint4 *>(dst + j) = v;
+            }
+          } else {
+            for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+          }
+        } else {
+          float *dst = (float *)Cv + (size_t)row * ldc + n;
+          if (n + 32 <= N && ((((uintptr_t)dst) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                     __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              if (EPI == EPI_ACCUM_F32) {
+                const float4 old = *reinterpret_cast<float4 *>(dst + j);
+                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+              }
+              *reinterpret_cast<float4 *>(dst + j) = v;
+            }
+          } else {
+            for (int j = 0; j < 32 && n + j < N; ++j) {
+              const float v = __uint_as_float(r[j]);
+              dst[j] = EPI == EPI_ACCUM_F32 ? dst[j] + v : v;
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"((uint32_t)BN));
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A tiled map of a row-major [rows, K] bfloat16 matrix with boxes of box_rows x 64, 128-byte swizzle.
+static int make_map(CUtensorMap *map, const void *base, int rows, int K, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) G2B_REFUSE("gemm_tc: cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) G2B_REFUSE("gemm_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+template <int BN, int EPI>
+static int launch(const CUtensorMap &ma, const CUtensorMap &mw, void *C, int M, int N, int K, int ldc,
+                  int *status, cudaStream_t stream) {
+  static bool configured = false;
+  const int smem = Smem<BN>::TOTAL;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) G2B_REFUSE("gemm_tc: shared memory of %d bytes refused: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  if (grid.y > 65535) G2B_REFUSE("gemm_tc: M=%d is too large for one launch", M);
+  gemm_tc_kernel<BN, EPI><<<grid, THREADS, smem, stream>>>(ma, mw, C, M, N, K, ldc, status);
+  return g2b_check_launch("gemm_tc");
+}
+
+// A [M,K], W [N,K] bfloat16, inner stride 1, row strides multiples of 8 elements, base
+// addresses 16-byte aligned.  epi: 0 store bfloat16, 1 store float, 2 add into float,
+// 3 SiLU gate (C is [M, N/2] bfloat16; N a multiple of 16).  `status` is a device int the
+// kernel sets non-zero if one of its bounded waits gave up.  bn: 128 or 256.
+extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, int K, int lda,
+                           int ldw, int ldc, int epi, int bn, int *status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || lda % 8 || ldw % 8)
+    G2B_REFUSE("gemm_tc: K=%d and the row strides (%d, %d) must be multiples of 8", K, lda, ldw);
+  if (((uintptr_t)A | (uintptr_t)W) & 15) G2B_REFUSE("gemm_tc: operands must be 16-byte aligned");
+  if (epi == EPI_SWIGLU_BF16 && N % 16) G2B_REFUSE("gemm_tc: gated output needs N %% 16 == 0, N=%d", N);
+  if (!status) G2B_REFUSE("gemm_tc: no status word");
+  if (bn != 128 && bn != 256) G2B_REFUSE("gemm_tc: tile width %d (128 or 256)", bn);
+  CUtensorMap ma, mw;
+  int rc = make_map(&ma, A, M, K, lda, BM);
+  if (rc) return rc;
+  rc = make_map(&mw, W, N, K, ldw, bn == 256 ? 256 : 128);
+  if (rc) return rc;
+#define G2B_CASE(BN_, E)                                                           \
+  if (bn == BN_ && epi == E) return launch<BN_, E>(ma, mw, C, M, N, K, ldc, status, stream);
+  G2B_CASE(128, EPI_STORE_BF16) G2B_CASE(128, EPI_STORE_F32) G2B_CASE(128, EPI_ACCUM_F32)
+  G2B_CASE(128, EPI_SWIGLU_BF16) G2B_CASE(256, EPI_STORE_BF16) G2B_CASE(256, EPI_STORE_F32)
+  G2B_CASE(256, EPI_ACCUM_F32) G2B_CASE(256, EPI_SWIGLU_BF16)
+#undef G2B_CASE
+  G2B_REFUSE("gemm_tc: unknown epilogue %d", epi);
+}

@@ -7,14 +7,14 @@ from ctypes import c_float, c_int, c_void_p
 import torch
 
 from .csrc import units
-from .kernels import _call, _fn, _ptr, _stream
+from .kernels import KernelError, _call, _fn, _ptr, _stream
 
 FAST_HEAD_SIZES = (64, 128)          # head sizes the tensor-core attention kernels are written for
 DECODE_CHUNK_KEYS = 256              # keys per CTA of the decode kernel (attn_decode.cu)
 
 units.SPECIALISED_SOURCES[:] = [("attn_decode.cu", ()), ("attn_decode_noalloc.cu", ()),
                                 ("attn_prefill.cu", ())]
-units.BF16_UNITS[:] = [("gemm_small.cu", ())]
+units.BF16_UNITS[:] = [("gemm_small.cu", ()), ("gemm_tc.cu", ())]
 
 
 SMALL_M = 64                         # rows the weight-streaming product takes
@@ -35,6 +35,43 @@ def _gemm_small(a, w, out, epi) -> None:
           w.stride(0), out.stride(0), epi, _stream())
 
 
+_status: dict = {}
+
+
+def _status_word(device) -> torch.Tensor:
+    """The device word in which the tcgen05 kernels report a wait that gave up."""
+    key = torch.device(device)
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=key)
+    return _status[key]
+
+
+def check_status() -> None:
+    """Raises if a kernel's bounded wait gave up since the last check (reads the device
+    word, so it synchronises)."""
+    for dev, word in _status.items():
+        code = int(word.item())
+        if code:
+            word.zero_()
+            what = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code, "a role")
+            raise KernelError(f"gemm_tc on {dev}: {what} gave up waiting on a barrier (code {code}); "
+                              "the result of that product is invalid")
+
+
+def _tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    K = a.shape[1]
+    return (K % 8 == 0 and a.stride(1) == 1 and w.stride(1) == 1 and a.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def _gemm_tc(a, w, out, epi, bn: int = 128) -> None:
+    f = _fn("gemm_tc.cu", "g2b_gemm_tc",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_void_p, c_void_p])
+    _call(f, _ptr(a), _ptr(w), _ptr(out), a.shape[0], w.shape[0], a.shape[1], a.stride(0),
+          w.stride(0), out.stride(0), epi, bn, _ptr(_status_word(a.device)), _stream())
+
+
 def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
     """out (=|+=) a @ w.T for bfloat16 a and w on the tensor cores."""
     if out.stride(1) != 1:
@@ -48,6 +85,9 @@ def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate:
     if _small_ok(a, w):
         _gemm_small(a, w, out, epi)
         return True
+    if _tc_ok(a, w):
+        _gemm_tc(a, w, out, epi)
+        return True
     return False
 
 
@@ -58,6 +98,9 @@ def gate_up_bf16(h: torch.Tensor, w_gate_up: torch.Tensor, mid: torch.Tensor, bl
         return False
     if _small_ok(h, w_gate_up):
         _gemm_small(h, w_gate_up, mid, EPI_SWIGLU_BF16)
+        return True
+    if _tc_ok(h, w_gate_up):
+        _gemm_tc(h, w_gate_up, mid, EPI_SWIGLU_BF16)
         return True
     return False
 
