@@ -59,6 +59,8 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
                    const int *__restrict__ page_table, int P, int nh, int nkv, int window,
                    float scale_log2, float *__restrict__ part_o, float2 *__restrict__ part_ml,
                    int n_chunks) {
+  pdl_launch();
+  pdl_wait();
   extern __shared__ __align__(128) unsigned char smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -255,6 +257,8 @@ __global__ void __launch_bounds__(HD)
 attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__ part_ml,
                     const int *__restrict__ tok_pos, int nh, int window, int n_chunks,
                     bf16 *__restrict__ out) {
+  pdl_launch();
+  pdl_wait();
   const size_t th = blockIdx.x;                                // t * nh + h
   const int t = (int)(th / nh), d = threadIdx.x;
   const int pos = tok_pos[t];
@@ -297,12 +301,12 @@ extern "C" int g2b_attn_decode(const void *q, void *out, const void *cache, cons
     configured = true;
   }
   dim3 grid(n_chunks, nkv * head_tiles, T);
-  attn_decode_kernel<<<grid, WARPS * 32, smem, stream>>>(
+  g2b_launch(attn_decode_kernel, dim3(grid), dim3(WARPS * 32), smem, stream, 
       (const bf16 *)q, (const bf16 *)cache, tok_pos, tok_seq, page_table, P, nh, nkv, window,
       scale * LOG2E, part_o, (float2 *)part_ml, n_chunks);
   int rc = g2b_check_launch("attn_decode");
   if (rc) return rc;
-  attn_combine_kernel<<<(unsigned)((size_t)T * nh), HD, 0, stream>>>(
+  g2b_launch(attn_combine_kernel, dim3((unsigned)((size_t)T * nh)), dim3(HD), 0, stream, 
       part_o, (const float2 *)part_ml, tok_pos, nh, window, n_chunks, (bf16 *)out);
   return g2b_check_launch("attn_combine");
 }

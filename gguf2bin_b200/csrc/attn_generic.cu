@@ -24,6 +24,8 @@ attn_generic_kernel(const T *__restrict__ q, T *__restrict__ out, const T *__res
                     const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
                     const int *__restrict__ page_table, int P, int n_tokens, int nh, int nkv,
                     int hd, int page_size, int window, float scale) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float qs[AG_WARPS][AG_MAX_HD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * AG_WARPS + warp;
@@ -97,11 +99,11 @@ extern "C" int g2b_attn_generic(const void *q, void *out, int dtype, const void 
   const long long items = (long long)n_tokens * nh;
   const unsigned blocks = (unsigned)((items + AG_WARPS - 1) / AG_WARPS);
   if (dtype == G2B_F32)
-    attn_generic_kernel<float><<<blocks, AG_WARPS * 32, 0, stream>>>(
+    g2b_launch(attn_generic_kernel<float>, dim3(blocks), dim3(AG_WARPS * 32), 0, stream, 
         (const float *)q, (float *)out, (const float *)cache, tok_pos, tok_seq, page_table, P,
         n_tokens, nh, nkv, hd, page_size, window, scale);
   else if (dtype == G2B_BF16)
-    attn_generic_kernel<bf16><<<blocks, AG_WARPS * 32, 0, stream>>>(
+    g2b_launch(attn_generic_kernel<bf16>, dim3(blocks), dim3(AG_WARPS * 32), 0, stream, 
         (const bf16 *)q, (bf16 *)out, (const bf16 *)cache, tok_pos, tok_seq, page_table, P,
         n_tokens, nh, nkv, hd, page_size, window, scale);
   else

@@ -56,6 +56,8 @@ attn_prefill_kernel(const bf16 *__restrict__ q, bf16 *__restrict__ out,
                     const bf16 *__restrict__ cache, const int4 *__restrict__ tiles,
                     const int *__restrict__ page_table, int P, int nh, int nkv, int window,
                     float scale_log2) {
+  pdl_launch();
+  pdl_wait();
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -216,7 +218,7 @@ extern "C" int g2b_attn_prefill(const void *q, void *out, const void *cache, con
     configured = true;
   }
   dim3 grid(n_tiles, nh);
-  attn_prefill_kernel<<<grid, WARPS * 32, smem, stream>>>(
+  g2b_launch(attn_prefill_kernel, dim3(grid), dim3(WARPS * 32), smem, stream, 
       (const bf16 *)q, (bf16 *)out, (const bf16 *)cache, (const int4 *)tiles, page_table, P, nh,
       nkv, window, scale * LOG2E);
   return g2b_check_launch("attn_prefill");

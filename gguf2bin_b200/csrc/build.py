@@ -165,6 +165,13 @@ def compile_unit(source_name: str, defines: Sequence[str] = (), verbose: bool = 
     if verbose and output:
         print(output, file=sys.stderr)
     os.replace(tmp, out)
+    prefix = out.name.rsplit("-", 1)[0] + "-"
+    for old in out.parent.glob(prefix + "*.so"):        # objects of older versions of this source
+        if old != out and old.name.rsplit("-", 1)[0] + "-" == prefix:
+            try:
+                old.unlink()
+            except OSError:
+                pass
     _log(f"  built {out.name} in {time.time() - t0:.1f} s")
     return out
 
@@ -207,5 +214,20 @@ def load_unit(source_name: str, defines: Sequence[str] = ()) -> ctypes.CDLL:
             raise KernelBuildError(f"cannot load {path}: {e}") from None
         lib.g2b_last_error.restype = ctypes.c_char_p
         lib.g2b_last_error.argtypes = []
+        lib.g2b_set_pdl.argtypes = [ctypes.c_int]
+        lib.g2b_set_pdl.restype = None
+        lib.g2b_set_pdl(1 if _pdl else 0)
         _loaded[key] = lib
     return lib
+
+
+# Programmatic dependent launch (kernels start while their predecessor drains, and wait
+# on the device before touching its results).  On unless GGUF2BIN_B200_PDL=0.
+_pdl = os.environ.get("GGUF2BIN_B200_PDL", "1") != "0"
+
+
+def set_pdl(on: bool) -> None:
+    global _pdl
+    _pdl = bool(on)
+    for lib in _loaded.values():
+        lib.g2b_set_pdl(1 if _pdl else 0)

@@ -30,8 +30,37 @@ static inline int g2b_check_launch(const char *what) {
   return 0;
 }
 
-#define G2B_DEFINE_LAST_ERROR \
-  extern "C" const char *g2b_last_error() { return g2b_error_text; }
+// Programmatic dependent launch: with the switch on, a kernel is launched with the
+// programmatic-stream-serialization attribute, so its blocks may start while the kernel
+// before it in the stream is still running.  Every kernel of this library therefore calls
+// pdl_wait() before it reads anything an earlier kernel wrote and before its first write,
+// and may do independent work (index arithmetic, streaming WEIGHTS into registers) above
+// that line; pdl_launch() lets the next kernel start its own independent part.  Both are
+// no-ops for a kernel launched the ordinary way.
+static int g2b_pdl_enabled = 0;
+
+#define G2B_DEFINE_LAST_ERROR                                            \
+  extern "C" const char *g2b_last_error() { return g2b_error_text; }    \
+  extern "C" void g2b_set_pdl(int on) { g2b_pdl_enabled = on; }
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+
+template <typename... KArgs, typename... Args>
+static inline void g2b_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g2b_pdl_enabled ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);       // errors surface in g2b_check_launch
+}
 
 // element type codes used by the launchers
 enum { G2B_F32 = 0, G2B_BF16 = 1 };

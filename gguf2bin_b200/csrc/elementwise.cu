@@ -19,6 +19,8 @@ G2B_DEFINE_LAST_ERROR
 template <typename TW>
 __global__ void embed_rows_kernel(const TW *__restrict__ table, const int *__restrict__ ids,
                                   float *__restrict__ out, int H, int V) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   const bool ok = (id >= 0 && id < V);
@@ -34,9 +36,9 @@ extern "C" int g2b_embed_rows(const void *table, int table_dtype, const int *ids
   if (H <= 0 || V <= 0) G2B_REFUSE("embed_rows: bad sizes H=%d V=%d", H, V);
   const int threads = H >= 256 ? 256 : 64;
   if (table_dtype == G2B_F32)
-    embed_rows_kernel<float><<<T, threads, 0, stream>>>((const float *)table, ids, out, H, V);
+    g2b_launch(embed_rows_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float *)table, ids, out, H, V);
   else if (table_dtype == G2B_BF16)
-    embed_rows_kernel<bf16><<<T, threads, 0, stream>>>((const bf16 *)table, ids, out, H, V);
+    g2b_launch(embed_rows_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16 *)table, ids, out, H, V);
   else
     G2B_REFUSE("embed_rows: unknown table dtype %d", table_dtype);
   return g2b_check_launch("embed_rows");
@@ -49,6 +51,8 @@ template <typename TO>
 __global__ void rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ w,
                                const int *__restrict__ rows, TO *__restrict__ out, int H,
                                float eps) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const float *xr = x + (size_t)(rows ? rows[r] : r) * H;
@@ -63,15 +67,76 @@ __global__ void rmsnorm_kernel(const float *__restrict__ x, const float *__restr
   for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = from_f32<TO>((w[j] * xr[j]) * inv);
 }
 
+// one warp per row, 16-byte loads, eight of them in flight per lane; H a multiple of 4
+template <typename TO>
+__global__ void __launch_bounds__(128)
+rmsnorm_rows_kernel(const float *__restrict__ x, const float *__restrict__ w,
+                    const int *__restrict__ rows, TO *__restrict__ out, int n_rows, int H,
+                    float eps) {
+  pdl_launch();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const float *xr = x + (size_t)(rows ? rows[r] : r) * H;
+  float ss = 0.f;
+  for (int k0 = lane * 4; k0 < H; k0 += 128 * 8) {
+    float4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int k = k0 + 128 * i;
+      v[i] = k < H ? *reinterpret_cast<const float4 *>(xr + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+      ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+    }
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / (float)H + eps);
+  TO *o = out + (size_t)r * H;
+  for (int k0 = lane * 4; k0 < H; k0 += 128 * 4) {
+    float4 v[4], g[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + 128 * i;
+      if (k < H) {
+        v[i] = *reinterpret_cast<const float4 *>(xr + k);
+        g[i] = *reinterpret_cast<const float4 *>(w + k);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + 128 * i;
+      if (k < H) {
+        o[k + 0] = from_f32<TO>((g[i].x * v[i].x) * inv);
+        o[k + 1] = from_f32<TO>((g[i].y * v[i].y) * inv);
+        o[k + 2] = from_f32<TO>((g[i].z * v[i].z) * inv);
+        o[k + 3] = from_f32<TO>((g[i].w * v[i].w) * inv);
+      }
+    }
+  }
+}
+
 extern "C" int g2b_rmsnorm(const float *x, const float *w, const int *rows, int n_rows, int H,
                            float eps, void *out, int out_dtype, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (H <= 0) G2B_REFUSE("rmsnorm: bad width %d", H);
+  if (H % 4 == 0 && H >= 128 && ((((uintptr_t)x) | ((uintptr_t)w)) & 15) == 0 &&
+      (out_dtype == G2B_F32 || out_dtype == G2B_BF16)) {
+    const unsigned blocks = (unsigned)((n_rows + 3) / 4);
+    if (out_dtype == G2B_F32)
+      g2b_launch(rmsnorm_rows_kernel<float>, dim3(blocks), dim3(128), 0, stream, x, w, rows, (float *)out, n_rows, H, eps);
+    else
+      g2b_launch(rmsnorm_rows_kernel<bf16>, dim3(blocks), dim3(128), 0, stream, x, w, rows, (bf16 *)out, n_rows, H, eps);
+    return g2b_check_launch("rmsnorm");
+  }
   const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 32);
   if (out_dtype == G2B_F32)
-    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, w, rows, (float *)out, H, eps);
+    g2b_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, w, rows, (float *)out, H, eps);
   else if (out_dtype == G2B_BF16)
-    rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, w, rows, (bf16 *)out, H, eps);
+    g2b_launch(rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, w, rows, (bf16 *)out, H, eps);
   else
     G2B_REFUSE("rmsnorm: unknown output dtype %d", out_dtype);
   return g2b_check_launch("rmsnorm");
@@ -89,6 +154,9 @@ extern "C" int g2b_rmsnorm(const float *x, const float *w, const int *rows, int 
 #define QKN_MAX_HD 512
 #define QKN_WARPS 4
 
+// Grid (token, split): the block's warps share the heads [split * heads_per_block, ...) of
+// one token, one head at a time per warp.  The sines and cosines of the token's position
+// are computed once per block into shared memory instead of once per head.
 template <typename T>
 __global__ void qknorm_rope_cache_kernel(
     const T *__restrict__ qkv, int T_tokens, int nh, int nkv, int hd,
@@ -96,60 +164,70 @@ __global__ void qknorm_rope_cache_kernel(
     const float *__restrict__ inv_freq, int rot_dim,
     const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
     const int *__restrict__ page_table, int P, T *__restrict__ cache, int page_size,
-    T *__restrict__ q_out, T *__restrict__ k_out, T *__restrict__ v_out) {
+    T *__restrict__ q_out, T *__restrict__ k_out, T *__restrict__ v_out, int heads_per_block) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float buf[QKN_WARPS][QKN_MAX_HD];
+  __shared__ float cs[QKN_MAX_HD];                  // cos at [j], sin at [half + j]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = nh + 2 * nkv;
-  const long long item = (long long)blockIdx.x * QKN_WARPS + warp;
-  if (item >= (long long)T_tokens * heads) return;
-  const int t = (int)(item / heads), h = (int)(item % heads);
-  const T *src = qkv + (size_t)t * heads * hd + (size_t)h * hd;
-  float *x = buf[warp];
-
-  const int kind = h < nh ? 0 : (h < nh + nkv ? 1 : 2);       // 0 q, 1 k, 2 v
-  const float *w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
-
-  float ss = 0.f;
-  for (int j = lane; j < hd; j += 32) {
-    const float v = to_f32(src[j]);
-    x[j] = v;
-    ss = fmaf(v, v, ss);
-  }
-  ss = warp_sum(ss);
-  __syncwarp();
-  if (w) {
-    const float inv = 1.f / sqrtf(ss / (float)hd + eps);
-    for (int j = lane; j < hd; j += 32) x[j] = (w[j] * x[j]) * inv;
-    __syncwarp();
-  }
+  const int t = blockIdx.x;
   const int pos = tok_pos[t];
-  if (kind != 2 && inv_freq) {
-    const int half = rot_dim >> 1;
-    for (int j = lane; j < half; j += 32) {
-      const float ang = (float)pos * inv_freq[j];
-      float s, c;
-      sincosf(ang, &s, &c);
-      const float a = x[j], b = x[j + half];
-      x[j] = a * c - b * s;
-      x[j + half] = a * s + b * c;
+  const int half = rot_dim >> 1;
+  if (inv_freq) {
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+      float sn, c;
+      sincosf((float)pos * inv_freq[j], &sn, &c);
+      cs[j] = c;
+      cs[half + j] = sn;
     }
+  }
+  __syncthreads();
+  const int h_begin = blockIdx.y * heads_per_block;
+  const int h_end = min(heads, h_begin + heads_per_block);
+  float *x = buf[warp];
+  for (int h = h_begin + warp; h < h_end; h += QKN_WARPS) {
+    const T *src = qkv + (size_t)t * heads * hd + (size_t)h * hd;
+    const int kind = h < nh ? 0 : (h < nh + nkv ? 1 : 2);       // 0 q, 1 k, 2 v
+    const float *w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
+    float ss = 0.f;
+    for (int j = lane; j < hd; j += 32) {
+      const float v = to_f32(src[j]);
+      x[j] = v;
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
     __syncwarp();
-  }
-
-  T *dst;
-  if (kind == 0) {
-    dst = q_out + (size_t)t * nh * hd + (size_t)h * hd;
-  } else {
-    const int kvh = kind == 1 ? h - nh : h - nh - nkv;
-    T *flat = kind == 1 ? k_out : v_out;
-    if (flat) {
-      dst = flat + (size_t)t * nkv * hd + (size_t)kvh * hd;
-    } else {
-      const int page = page_table[(size_t)tok_seq[t] * P + pos / page_size];
-      dst = cache + ((((size_t)page * 2 + (kind - 1)) * nkv + kvh) * page_size + pos % page_size) * hd;
+    if (w) {
+      const float inv = 1.f / sqrtf(ss / (float)hd + eps);
+      for (int j = lane; j < hd; j += 32) x[j] = (w[j] * x[j]) * inv;
+      __syncwarp();
     }
+    if (kind != 2 && inv_freq) {
+      for (int j = lane; j < half; j += 32) {
+        const float c = cs[j], sn = cs[half + j];
+        const float a = x[j], b = x[j + half];
+        x[j] = a * c - b * sn;
+        x[j + half] = a * sn + b * c;
+      }
+      __syncwarp();
+    }
+    T *dst;
+    if (kind == 0) {
+      dst = q_out + (size_t)t * nh * hd + (size_t)h * hd;
+    } else {
+      const int kvh = kind == 1 ? h - nh : h - nh - nkv;
+      T *flat = kind == 1 ? k_out : v_out;
+      if (flat) {
+        dst = flat + (size_t)t * nkv * hd + (size_t)kvh * hd;
+      } else {
+        const int page = page_table[(size_t)tok_seq[t] * P + pos / page_size];
+        dst = cache + ((((size_t)page * 2 + (kind - 1)) * nkv + kvh) * page_size + pos % page_size) * hd;
+      }
+    }
+    for (int j = lane; j < hd; j += 32) dst[j] = from_f32<T>(x[j]);
+    __syncwarp();                                  // x is reused for the warp's next head
   }
-  for (int j = lane; j < hd; j += 32) dst[j] = from_f32<T>(x[j]);
 }
 
 extern "C" int g2b_qknorm_rope_cache(const void *qkv, int dtype, int T_tokens, int nh, int nkv,
@@ -167,18 +245,21 @@ extern "C" int g2b_qknorm_rope_cache(const void *qkv, int dtype, int T_tokens, i
     G2B_REFUSE("qknorm_rope_cache: k_out and v_out must be given together");
   if (nkv > 0 && !k_out && (!cache || !page_table || page_size <= 0))
     G2B_REFUSE("qknorm_rope_cache: no cache to write to");
-  const long long items = (long long)T_tokens * (nh + 2 * nkv);
-  const unsigned blocks = (unsigned)((items + QKN_WARPS - 1) / QKN_WARPS);
+  // few tokens: one head per warp (more blocks); many tokens: a block takes all heads
+  const int heads = nh + 2 * nkv;
+  const int heads_per_block = T_tokens >= 256 ? heads : QKN_WARPS;
+  const dim3 blocks((unsigned)T_tokens, (unsigned)((heads + heads_per_block - 1) / heads_per_block));
+  if (blocks.y > 65535) G2B_REFUSE("qknorm_rope_cache: %d heads", heads);
   if (dtype == G2B_F32)
-    qknorm_rope_cache_kernel<float><<<blocks, QKN_WARPS * 32, 0, stream>>>(
+    g2b_launch(qknorm_rope_cache_kernel<float>, dim3(blocks), dim3(QKN_WARPS * 32), 0, stream, 
         (const float *)qkv, T_tokens, nh, nkv, hd, q_w, k_w, eps, inv_freq, rot_dim, tok_pos,
         tok_seq, page_table, P, (float *)cache, page_size, (float *)q_out, (float *)k_out,
-        (float *)v_out);
+        (float *)v_out, heads_per_block);
   else if (dtype == G2B_BF16)
-    qknorm_rope_cache_kernel<bf16><<<blocks, QKN_WARPS * 32, 0, stream>>>(
+    g2b_launch(qknorm_rope_cache_kernel<bf16>, dim3(blocks), dim3(QKN_WARPS * 32), 0, stream, 
         (const bf16 *)qkv, T_tokens, nh, nkv, hd, q_w, k_w, eps, inv_freq, rot_dim, tok_pos,
         tok_seq, page_table, P, (bf16 *)cache, page_size, (bf16 *)q_out, (bf16 *)k_out,
-        (bf16 *)v_out);
+        (bf16 *)v_out, heads_per_block);
   else
     G2B_REFUSE("qknorm_rope_cache: unknown dtype %d", dtype);
   return g2b_check_launch("qknorm_rope_cache");
@@ -193,6 +274,8 @@ __global__ void cache_write_kernel(const T *__restrict__ k, const T *__restrict_
                                    const int *__restrict__ tok_seq,
                                    const int *__restrict__ page_table, int P,
                                    T *__restrict__ cache, int page_size) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
   const int page = page_table[(size_t)tok_seq[t] * P + pos / page_size];
@@ -210,11 +293,11 @@ extern "C" int g2b_cache_write(const void *k, const void *v, int dtype, int T_to
                                cudaStream_t stream) {
   if (T_tokens <= 0) return 0;
   if (dtype == G2B_F32)
-    cache_write_kernel<float><<<T_tokens, 128, 0, stream>>>(
+    g2b_launch(cache_write_kernel<float>, dim3(T_tokens), dim3(128), 0, stream, 
         (const float *)k, (const float *)v, nkv, hd, tok_pos, tok_seq, page_table, P,
         (float *)cache, page_size);
   else if (dtype == G2B_BF16)
-    cache_write_kernel<bf16><<<T_tokens, 128, 0, stream>>>(
+    g2b_launch(cache_write_kernel<bf16>, dim3(T_tokens), dim3(128), 0, stream, 
         (const bf16 *)k, (const bf16 *)v, nkv, hd, tok_pos, tok_seq, page_table, P, (bf16 *)cache,
         page_size);
   else
@@ -231,6 +314,8 @@ extern "C" int g2b_cache_write(const void *k, const void *v, int dtype, int T_to
 template <typename T>
 __global__ void swiglu_kernel(const T *__restrict__ gu, T *__restrict__ out, long long total,
                               int I, int blk) {
+  pdl_launch();
+  pdl_wait();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const long long t = idx / I;
@@ -249,9 +334,9 @@ extern "C" int g2b_swiglu(const void *gu, int dtype, int T_tokens, int I, int bl
   const long long total = (long long)T_tokens * I;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == G2B_F32)
-    swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float *)gu, (float *)out, total, I, blk);
+    g2b_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float *)gu, (float *)out, total, I, blk);
   else if (dtype == G2B_BF16)
-    swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16 *)gu, (bf16 *)out, total, I, blk);
+    g2b_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16 *)gu, (bf16 *)out, total, I, blk);
   else
     G2B_REFUSE("swiglu: unknown dtype %d", dtype);
   return g2b_check_launch("swiglu");
@@ -262,12 +347,14 @@ extern "C" int g2b_swiglu(const void *gu, int dtype, int T_tokens, int I, int bl
 // positions advance by one.
 // ---------------------------------------------------------------------------
 __global__ void advance_positions_kernel(int *tok_pos, int n) {
+  pdl_launch();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) tok_pos[i] += 1;
 }
 
 extern "C" int g2b_advance_positions(int *tok_pos, int n, cudaStream_t stream) {
   if (n <= 0) return 0;
-  advance_positions_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tok_pos, n);
+  g2b_launch(advance_positions_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tok_pos, n);
   return g2b_check_launch("advance_positions");
 }

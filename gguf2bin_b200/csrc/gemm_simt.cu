@@ -21,6 +21,8 @@ template <typename TA, typename TW, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA *__restrict__ A, const TW *__restrict__ W, void *__restrict__ Cv, int M,
                  int N, int K, int lda, int ldw, int ldc) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -80,15 +82,15 @@ static int launch(const void *A, const void *W, void *C, int M, int N, int K, in
   if (grid.y > 65535) G2B_REFUSE("gemm_simt: M=%d is too large for one launch", M);
   switch (epi) {
     case EPI_STORE_F32:
-      gemm_simt_kernel<TA, TW, EPI_STORE_F32><<<grid, 256, 0, stream>>>(
+      g2b_launch(gemm_simt_kernel<TA, TW, EPI_STORE_F32>, dim3(grid), dim3(256), 0, stream, 
           (const TA *)A, (const TW *)W, C, M, N, K, lda, ldw, ldc);
       break;
     case EPI_STORE_BF16:
-      gemm_simt_kernel<TA, TW, EPI_STORE_BF16><<<grid, 256, 0, stream>>>(
+      g2b_launch(gemm_simt_kernel<TA, TW, EPI_STORE_BF16>, dim3(grid), dim3(256), 0, stream, 
           (const TA *)A, (const TW *)W, C, M, N, K, lda, ldw, ldc);
       break;
     case EPI_ACCUM_F32:
-      gemm_simt_kernel<TA, TW, EPI_ACCUM_F32><<<grid, 256, 0, stream>>>(
+      g2b_launch(gemm_simt_kernel<TA, TW, EPI_ACCUM_F32>, dim3(grid), dim3(256), 0, stream, 
           (const TA *)A, (const TW *)W, C, M, N, K, lda, ldw, ldc);
       break;
     default:

@@ -13,6 +13,14 @@
 //  * The 8 partial sums of an output are added in warp order through shared memory: the
 //    order of the sum depends on K only, not on M or on the batch's contents.
 //
+// Two ways of staging the activations.  `gemm_small_kernel` stages one 256-wide block of K
+// at a time (any K, M up to 64).  `gemm_small_whole_kernel` stages all of A once, when
+// M x K fits shared memory: its K loop then has no barrier at all, up to 8 blocks of W are
+// in flight per thread, and it can take the float32 residual stream directly and apply
+// RMSNorm while staging (o_j = (w_j * x_j) / sqrt(mean(x^2) + eps), statistics in float32,
+// src/l3_math.c:34-36,49), optionally on gathered rows, which removes the separate norm
+// kernel and a round trip of the normed activations through memory.
+//
 // Epilogues: store (bfloat16 or float), add into a float matrix (the residual stream), or
 // the SiLU gate on a fused gate/up matrix whose rows alternate 8 gates / 8 ups:
 // out[m, 8b + r] = silu(row r of block b) * (row 8 + r)   (src/l3_math.c:57-62,
@@ -42,6 +50,7 @@ template <int MT, int EPI>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_small_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W, void *__restrict__ Cv,
                   int M, int N, int K, int lda, int ldw, int ldc) {
+  pdl_launch();
   constexpr int MROWS = MT * 8;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   bf16 *xs = reinterpret_cast<bf16 *>(smem_raw);          // [2][MROWS][XROW]
@@ -78,6 +87,7 @@ gemm_small_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W, void *
 #pragma unroll
   for (int d = 0; d < DEPTH; ++d)
     if (d < nkb) load_w(wb[d], d);
+  pdl_wait();                            // the activations come from the kernel before
   stage_x(0, 0);
   cp_async_commit();
 
@@ -152,6 +162,217 @@ gemm_small_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W, void *
   }
 }
 
+
+constexpr int DEPTH_WHOLE = 8;          // K blocks of W in flight per thread (whole-A kernel)
+
+// NORM: A is the float32 stream x[rows_or_identity[m], :] and is normalised while staged.
+// A CTA takes `tiles_per_cta` consecutive 16-row tiles of W: the activations are staged
+// once, and the weight stream runs on across the tiles while a tile's sums are reduced.
+template <int MT, int EPI, bool NORM>
+__global__ void __launch_bounds__(WARPS * 32)
+gemm_small_whole_kernel(const void *__restrict__ Av, const float *__restrict__ norm_w, float eps,
+                        const int *__restrict__ rows, const bf16 *__restrict__ W,
+                        void *__restrict__ Cv, int M, int N, int K, int lda, int ldw, int ldc,
+                        int tiles_per_cta) {
+  pdl_launch();
+  constexpr int MROWS = MT * 8;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int nkb = (K + KB - 1) / KB;
+  const int xrow = nkb * KB + XPAD;                       // staged row length (zero padded)
+  bf16 *xs = reinterpret_cast<bf16 *>(smem_raw);          // [MROWS][xrow]
+  float *red = reinterpret_cast<float *>(smem_raw + (((size_t)MROWS * xrow * sizeof(bf16)) + 127) / 128 * 128);
+
+  const int n_tiles = (N + 15) / 16;
+  const int tile0 = blockIdx.x * tiles_per_cta;
+  const int my_tiles = min(tiles_per_cta, n_tiles - tile0);
+  const int total = my_tiles * nkb;                       // (tile, K block) pairs of this CTA
+  const int kw = 32 * warp + 8 * c;
+  auto load_w = [&](uint4 (&dst)[2], int it) {
+    const int n0 = (tile0 + it / nkb) * 16, k = (it % nkb) * KB + kw;
+    if (k < K) {
+      dst[0] = ld_stream(W + (size_t)min(n0 + g, N - 1) * ldw + k);
+      dst[1] = ld_stream(W + (size_t)min(n0 + g + 8, N - 1) * ldw + k);
+    } else {
+      dst[0] = dst[1] = make_uint4(0, 0, 0, 0);
+    }
+  };
+  // the weights do not depend on anything computed before: start their stream first
+  uint4 wb[DEPTH_WHOLE][2];
+#pragma unroll
+  for (int d = 0; d < DEPTH_WHOLE; ++d)
+    if (d < total) load_w(wb[d], d);
+  pdl_wait();                            // the activations come from the kernel before
+
+  // stage A (normalised if NORM): one warp per row, many loads in flight per lane
+  for (int r = warp; r < MROWS; r += WARPS) {
+    bf16 *dst = xs + (size_t)r * xrow;
+    if (r >= M) {
+      for (int k = lane * 8; k < xrow; k += 256) *reinterpret_cast<uint4 *>(dst + k) = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    if (NORM) {
+      const float *x = (const float *)Av + (size_t)(rows ? rows[r] : r) * lda;
+      float ss = 0.f;
+      for (int k0 = lane * 4; k0 < K; k0 += 128 * 8) {
+        float4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int k = k0 + 128 * i;
+          v[i] = k < K ? *reinterpret_cast<const float4 *>(x + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+          ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+        }
+      }
+      ss = warp_sum(ss);
+      const float inv = 1.f / sqrtf(ss / (float)K + eps);
+      for (int k0 = lane * 4; k0 < K; k0 += 128 * 4) {
+        float4 v[4], w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int k = k0 + 128 * i;
+          if (k < K) {
+            v[i] = *reinterpret_cast<const float4 *>(x + k);
+            w[i] = *reinterpret_cast<const float4 *>(norm_w + k);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int k = k0 + 128 * i;
+          if (k < K) {
+            uint2 o;
+            o.x = pack_bf16((w[i].x * v[i].x) * inv, (w[i].y * v[i].y) * inv);
+            o.y = pack_bf16((w[i].z * v[i].z) * inv, (w[i].w * v[i].w) * inv);
+            *reinterpret_cast<uint2 *>(dst + k) = o;
+          }
+        }
+      }
+    } else {
+      const bf16 *x = (const bf16 *)Av + (size_t)r * lda;
+      for (int k = lane * 8; k < K; k += 256) cp_async_16(smem_u32(dst + k), x + k);
+    }
+    for (int k = K + lane * 4; k < xrow; k += 128) *reinterpret_cast<uint2 *>(dst + k) = make_uint2(0, 0);
+  }
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+
+  float acc[MT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+  int kb = 0, tile = 0;                  // position of iteration `it` inside the CTA's work
+  for (int it0 = 0; it0 < total; it0 += DEPTH_WHOLE) {
+#pragma unroll
+    for (int d = 0; d < DEPTH_WHOLE; ++d) {
+      const int it = it0 + d;
+      if (it < total) {
+        const bf16 *xb = xs + kb * KB + 32 * warp + 8 * c;
+        const uint4 a_lo = wb[d][0], a_hi = wb[d][1];
+        const uint32_t a1[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};
+        const uint32_t a2[4] = {a_lo.z, a_hi.z, a_lo.w, a_hi.w};
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint4 xv = *reinterpret_cast<const uint4 *>(xb + (size_t)(8 * mt + g) * xrow);
+          mma_bf16_16816(acc[mt], a1, xv.x, xv.y);
+          mma_bf16_16816(acc[mt], a2, xv.z, xv.w);
+        }
+        if (it + DEPTH_WHOLE < total) load_w(wb[d], it + DEPTH_WHOLE);
+        if (++kb == nkb) {
+          // this tile is complete: add the 8 warps' partial sums in warp order, write it out
+          kb = 0;
+          const int n0 = (tile0 + tile) * 16;
+          ++tile;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            float *r0 = red + ((size_t)warp * 16 + g) * MROWS + 8 * mt + 2 * c;
+            float *r1 = r0 + 8 * MROWS;
+            r0[0] = acc[mt][0]; r0[1] = acc[mt][1];
+            r1[0] = acc[mt][2]; r1[1] = acc[mt][3];
+            acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+          }
+          __syncthreads();
+          if (EPI == EPI_SWIGLU_BF16) {
+            for (int i = threadIdx.x; i < 8 * MROWS; i += WARPS * 32) {
+              const int m = i / 8, r = i % 8;
+              float gate = 0.f, up = 0.f;
+#pragma unroll
+              for (int w = 0; w < WARPS; ++w) {
+                gate += red[((size_t)w * 16 + r) * MROWS + m];
+                up += red[((size_t)w * 16 + 8 + r) * MROWS + m];
+              }
+              const int col = (n0 >> 1) + r;
+              if (m < M && n0 + 8 + r < N)
+                ((bf16 *)Cv)[(size_t)m * ldc + col] =
+                    __float2bfloat16_rn((gate / (1.f + expf(-gate))) * up);
+            }
+          } else {
+            for (int i = threadIdx.x; i < 16 * MROWS; i += WARPS * 32) {
+              const int m = i / 16, r = i % 16;
+              float v = 0.f;
+#pragma unroll
+              for (int w = 0; w < WARPS; ++w) v += red[((size_t)w * 16 + r) * MROWS + m];
+              const int n = n0 + r;
+              if (m < M && n < N) {
+                const size_t o = (size_t)m * ldc + n;
+                if (EPI == EPI_STORE_BF16) ((bf16 *)Cv)[o] = __float2bfloat16_rn(v);
+                else if (EPI == EPI_STORE_F32) ((float *)Cv)[o] = v;
+                else ((float *)Cv)[o] += v;
+              }
+            }
+          }
+          __syncthreads();               // the sums' buffer is free for the next tile
+        }
+      }
+    }
+  }
+}
+
+// shared memory the whole-A kernel needs, or 0 if the case does not fit
+static size_t whole_smem(int mrows, int K) {
+  const int nkb = (K + KB - 1) / KB;
+  const size_t stage = ((size_t)mrows * (nkb * KB + XPAD) * sizeof(bf16) + 127) / 128 * 128;
+  const size_t red = (size_t)WARPS * 16 * mrows * sizeof(float);
+  const size_t need = stage + red;
+  return need <= 200 * 1024 ? need : 0;
+}
+
+template <int MT, bool NORM>
+static int launch_whole(const void *A, const float *norm_w, float eps, const int *rows,
+                        const void *W, void *C, int M, int N, int K, int lda, int ldw, int ldc,
+                        int epi, cudaStream_t stream) {
+  const int smem = (int)whole_smem(MT * 8, K);
+  // one tile per CTA measured fastest at every width tried (with more, the reduction of a
+  // tile stalls the weight stream of the next); the loop over tiles stays for experiments
+  const int n_tiles = (N + 15) / 16;
+  const int tiles_per_cta = 1;
+  const unsigned grid = (unsigned)((n_tiles + tiles_per_cta - 1) / tiles_per_cta);
+#define G2B_LAUNCH(E)                                                                            \
+  do {                                                                                           \
+    static int configured = 0;                                                                   \
+    if (configured < smem) {                                                                     \
+      cudaError_t e = cudaFuncSetAttribute(gemm_small_whole_kernel<MT, E, NORM>,                 \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem);   \
+      if (e != cudaSuccess) G2B_REFUSE("gemm_small: shared memory: %s", cudaGetErrorString(e));  \
+      configured = smem;                                                                         \
+    }                                                                                            \
+    g2b_launch(gemm_small_whole_kernel<MT, E, NORM>, dim3(grid), dim3(WARPS * 32), smem, stream,                     \
+        A, norm_w, eps, rows, (const bf16 *)W, C, M, N, K, lda, ldw, ldc, tiles_per_cta);        \
+  } while (0)
+  switch (epi) {
+    case EPI_STORE_BF16: G2B_LAUNCH(EPI_STORE_BF16); break;
+    case EPI_STORE_F32: G2B_LAUNCH(EPI_STORE_F32); break;
+    case EPI_ACCUM_F32: G2B_LAUNCH(EPI_ACCUM_F32); break;
+    case EPI_SWIGLU_BF16: G2B_LAUNCH(EPI_SWIGLU_BF16); break;
+    default: G2B_REFUSE("gemm_small: unknown epilogue %d", epi);
+  }
+#undef G2B_LAUNCH
+  return g2b_check_launch("gemm_small_whole");
+}
+
 template <int MT>
 static int launch_mt(const void *A, const void *W, void *C, int M, int N, int K, int lda, int ldw,
                      int ldc, int epi, cudaStream_t stream) {
@@ -169,7 +390,7 @@ static int launch_mt(const void *A, const void *W, void *C, int M, int N, int K,
       if (e != cudaSuccess) G2B_REFUSE("gemm_small: shared memory: %s", cudaGetErrorString(e));  \
       configured = true;                                                                         \
     }                                                                                            \
-    gemm_small_kernel<MT, E><<<grid, WARPS * 32, smem, stream>>>(                                \
+    g2b_launch(gemm_small_kernel<MT, E>, dim3(grid), dim3(WARPS * 32), smem, stream,                                 \
         (const bf16 *)A, (const bf16 *)W, C, M, N, K, lda, ldw, ldc);                            \
   } while (0)
   switch (epi) {
@@ -194,8 +415,40 @@ extern "C" int g2b_gemm_small(const void *A, const void *W, void *C, int M, int 
     G2B_REFUSE("gemm_small: K=%d and the row strides (%d, %d) must be multiples of 8", K, lda, ldw);
   if (((uintptr_t)A | (uintptr_t)W) & 15) G2B_REFUSE("gemm_small: operands must be 16-byte aligned");
   if (epi == EPI_SWIGLU_BF16 && N % 16) G2B_REFUSE("gemm_small: gated output needs N %% 16 == 0, N=%d", N);
+  const int mrows = M <= 8 ? 8 : (M <= 16 ? 16 : (M <= 32 ? 32 : 64));
+  if (whole_smem(mrows, K)) {
+    if (M <= 8) return launch_whole<1, false>(A, nullptr, 0.f, nullptr, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+    if (M <= 16) return launch_whole<2, false>(A, nullptr, 0.f, nullptr, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+    if (M <= 32) return launch_whole<4, false>(A, nullptr, 0.f, nullptr, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+    return launch_whole<8, false>(A, nullptr, 0.f, nullptr, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+  }
   if (M <= 8) return launch_mt<1>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
   if (M <= 16) return launch_mt<2>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
   if (M <= 32) return launch_mt<4>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
   return launch_mt<8>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+}
+
+// The same product on the normalised float32 stream: A = rmsnorm(x[rows[m], :]) with weight
+// norm_w and eps, computed while staging (rows == nullptr: rows 0..M-1).  x float32 with
+// row stride ldx (a multiple of 4), K a multiple of 8.  Returns 3 when the case does not
+// fit the whole-A kernel (the caller then normalises separately).
+extern "C" int g2b_gemm_small_normed(const float *x, const float *norm_w, float eps,
+                                     const int *rows, const void *W, void *C, int M, int N, int K,
+                                     int ldx, int ldw, int ldc, int epi, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 64) G2B_REFUSE("gemm_small_normed: M=%d (at most 64 rows)", M);
+  if (K <= 0 || K % 8 || ldx % 4 || ldw % 8)
+    G2B_REFUSE("gemm_small_normed: K=%d, ldx=%d, ldw=%d: K and ldw multiples of 8, ldx of 4", K, ldx, ldw);
+  if (((uintptr_t)x | (uintptr_t)W | (uintptr_t)norm_w) & 15)
+    G2B_REFUSE("gemm_small_normed: operands must be 16-byte aligned");
+  if (epi == EPI_SWIGLU_BF16 && N % 16) G2B_REFUSE("gemm_small_normed: gated output needs N %% 16 == 0, N=%d", N);
+  const int mrows = M <= 8 ? 8 : (M <= 16 ? 16 : (M <= 32 ? 32 : 64));
+  if (!whole_smem(mrows, K)) {
+    snprintf(g2b_error_text, sizeof(g2b_error_text), "gemm_small_normed: %d x %d activations do not fit shared memory", mrows, K);
+    return 3;
+  }
+  if (M <= 8) return launch_whole<1, true>(x, norm_w, eps, rows, W, C, M, N, K, ldx, ldw, ldc, epi, stream);
+  if (M <= 16) return launch_whole<2, true>(x, norm_w, eps, rows, W, C, M, N, K, ldx, ldw, ldc, epi, stream);
+  if (M <= 32) return launch_whole<4, true>(x, norm_w, eps, rows, W, C, M, N, K, ldx, ldw, ldc, epi, stream);
+  return launch_whole<8, true>(x, norm_w, eps, rows, W, C, M, N, K, ldx, ldw, ldc, epi, stream);
 }

@@ -102,6 +102,11 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo, uint32_t hi) {
   return *reinterpret_cast<uint32_t *>(&v);
 }
 
+__device__ __forceinline__ uint32_t pack2f(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+
 // Shared-memory operand descriptor: K-major tile of rows x 64 bf16, rows of 128 bytes,
 // 128-byte swizzle, 8-row groups 1024 bytes apart (the layout the TMA unit writes).
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
@@ -130,6 +135,7 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                void *__restrict__ Cv, int M, int N, int K, int ldc, int *__restrict__ status) {
+  pdl_launch();
   extern __shared__ unsigned char smem_raw[];
   using S = Smem<BN>;
   // 1024-byte alignment: the swizzle pattern is a function of address bits 4..9
@@ -161,6 +167,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const uint32_t tmem = *tmem_slot;
+  pdl_wait();                  // barriers and tensor memory are set up; now the inputs are needed
 
   if (warp == 4) {
     if (lane == 0) {
@@ -210,19 +217,55 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
         asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
         const int n = n0 + c0;
+        if (EPI == EPI_STORE_F32 || EPI == EPI_ACCUM_F32) {
+          // through shared memory, so that a warp touches 128 contiguous bytes of one row of
+          // C at a time (the operand stages are free: every MMA has completed)
+          if (n >= N) continue;                              // uniform over the warp
+          float *scr = reinterpret_cast<float *>(smem) + warp * (32 * 33);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) scr[lane * 33 + j] = __uint_as_float(r[j]);
+          __syncwarp();
+          const bool col_ok = n + lane < N;
+          float *cbase = (float *)Cv + (size_t)(m0 + warp * 32) * ldc + n + lane;
+#pragma unroll 8
+          for (int rr = 0; rr < 32; ++rr) {
+            if (col_ok && m0 + warp * 32 + rr < M) {
+              float *p = cbase + (size_t)rr * ldc;
+              const float v = scr[rr * 33 + lane];
+              *p = EPI == EPI_ACCUM_F32 ? *p + v : v;
+            }
+          }
+          __syncwarp();
+          continue;
+        }
         if (row >= M || n >= N) continue;
         if (EPI == EPI_SWIGLU_BF16) {
           // columns 16b .. 16b+7 are gates, 16b+8 .. 16b+15 the ups of the same outputs
           bf16 *dst = (bf16 *)Cv + (size_t)row * ldc + (n >> 1);
+          float h[16];
 #pragma unroll
           for (int blk = 0; blk < 2; ++blk)
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const float gate = __uint_as_float(r[16 * blk + j]);
               const float up = __uint_as_float(r[16 * blk + 8 + j]);
-              if (n + 16 * blk + 8 + j < N)
-                dst[8 * blk + j] = __float2bfloat16_rn((gate / (1.f + expf(-gate))) * up);
+              h[8 * blk + j] = (gate / (1.f + __expf(-gate))) * up;
             }
+          if (n + 32 <= N && ((((uintptr_t)dst) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 8) {
+              uint4 v;
+              v.x = pack2f(h[j], h[j + 1]); v.y = pack2f(h[j + 2], h[j + 3]);
+              v.z = pack2f(h[j + 4], h[j + 5]); v.w = pack2f(h[j + 6], h[j + 7]);
+              *reinterpret_cast<uint4 *>(dst + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (n + 16 * blk + 8 + j < N) dst[8 * blk + j] = __float2bfloat16_rn(h[8 * blk + j]);
+          }
         } else if (EPI == EPI_STORE_BF16) {
           bf16 *dst = (bf16 *)Cv + (size_t)row * ldc + n;
           if (n + 32 <= N && ((((uintptr_t)dst) & 15) == 0)) {
@@ -235,25 +278,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
           } else {
             for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-          }
-        } else {
-          float *dst = (float *)Cv + (size_t)row * ldc + n;
-          if (n + 32 <= N && ((((uintptr_t)dst) & 15) == 0)) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                     __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-              if (EPI == EPI_ACCUM_F32) {
-                const float4 old = *reinterpret_cast<float4 *>(dst + j);
-                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
-              }
-              *reinterpret_cast<float4 *>(dst + j) = v;
-            }
-          } else {
-            for (int j = 0; j < 32 && n + j < N; ++j) {
-              const float v = __uint_as_float(r[j]);
-              dst[j] = EPI == EPI_ACCUM_F32 ? dst[j] + v : v;
-            }
           }
         }
       }
@@ -313,7 +337,7 @@ static int launch(const CUtensorMap &ma, const CUtensorMap &mw, void *C, int M, 
   }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) G2B_REFUSE("gemm_tc: M=%d is too large for one launch", M);
-  gemm_tc_kernel<BN, EPI><<<grid, THREADS, smem, stream>>>(ma, mw, C, M, N, K, ldc, status);
+  g2b_launch(gemm_tc_kernel<BN, EPI>, dim3(grid), dim3(THREADS), smem, stream, ma, mw, C, M, N, K, ldc, status);
   return g2b_check_launch("gemm_tc");
 }
 

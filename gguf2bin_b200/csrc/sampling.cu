@@ -79,6 +79,8 @@ __device__ int block_argmax(const float *row, int V, float inv_temp, float *best
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float *__restrict__ logits, int V, int ld, float temp, int *seq_state,
                    int state_words, const int *__restrict__ slots, int *__restrict__ out_ids) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float scratch[32];
   __shared__ float s_part[SAMPLE_THREADS];
   __shared__ int s_choice;
@@ -130,9 +132,85 @@ extern "C" int g2b_sample_rows(const float *logits, int R, int V, int ld, float 
   if (V <= 0 || ld < V) G2B_REFUSE("sample_rows: bad sizes V=%d ld=%d", V, ld);
   if (temp > 0.f && (!seq_state || !slots || state_words < 4))
     G2B_REFUSE("sample_rows: temperature sampling needs the per-slot state");
-  sample_rows_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, V, ld, temp, seq_state,
+  g2b_launch(sample_rows_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, logits, V, ld, temp, seq_state,
                                                        state_words, slots, out_ids);
   return g2b_check_launch("sample_rows");
+}
+
+// ---- greedy over many blocks per row ---------------------------------------------
+// A vocabulary of 150k entries and a handful of rows leave most of the GPU idle when a
+// row is one block's work.  Stage 1: grid (row, split), each block reduces a contiguous
+// slice of the row to (value, index); stage 2: one block per row picks among the slices.
+// The first maximum wins at both stages, as a scan from index 0 would find it.
+#define ARGMAX_SPLITS 64
+
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float *__restrict__ logits, int V, int ld, float *__restrict__ part_val,
+                      int *__restrict__ part_idx) {
+  pdl_launch();
+  pdl_wait();
+  const float *row = logits + (size_t)blockIdx.x * ld;
+  const int per = (V + ARGMAX_SPLITS - 1) / ARGMAX_SPLITS;
+  const int begin = min(V, (int)blockIdx.y * per), end = min(V, begin + per);
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+    const float v = row[i];
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+  }
+  __shared__ float s_val[8];
+  __shared__ int s_idx[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { s_val[warp] = bv; s_idx[warp] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (s_val[w] > bv || (s_val[w] == bv && s_idx[w] < bi)) { bv = s_val[w]; bi = s_idx[w]; }
+    part_val[blockIdx.x * ARGMAX_SPLITS + blockIdx.y] = bv;
+    part_idx[blockIdx.x * ARGMAX_SPLITS + blockIdx.y] = bi;
+  }
+}
+
+__global__ void __launch_bounds__(ARGMAX_SPLITS)
+argmax_final_kernel(const float *__restrict__ part_val, const int *__restrict__ part_idx,
+                    int *__restrict__ out_ids) {
+  pdl_launch();
+  pdl_wait();
+  float bv = part_val[blockIdx.x * ARGMAX_SPLITS + threadIdx.x];
+  int bi = part_idx[blockIdx.x * ARGMAX_SPLITS + threadIdx.x];
+  __shared__ float s_val[ARGMAX_SPLITS / 32];
+  __shared__ int s_idx[ARGMAX_SPLITS / 32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { s_val[threadIdx.x >> 5] = bv; s_idx[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < ARGMAX_SPLITS / 32; ++w)
+      if (s_val[w] > bv || (s_val[w] == bv && s_idx[w] < bi)) { bv = s_val[w]; bi = s_idx[w]; }
+    out_ids[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
+// scratch: part_val float [R * 64], part_idx int [R * 64]
+extern "C" int g2b_argmax_rows(const float *logits, int R, int V, int ld, float *part_val,
+                               int *part_idx, int *out_ids, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (V <= 0 || ld < V) G2B_REFUSE("argmax_rows: bad sizes V=%d ld=%d", V, ld);
+  if (R > 65535) G2B_REFUSE("argmax_rows: %d rows", R);
+  g2b_launch(argmax_partial_kernel, dim3(R, ARGMAX_SPLITS), dim3(256), 0, stream, logits, V, ld,
+             part_val, part_idx);
+  g2b_launch(argmax_final_kernel, dim3(R), dim3(ARGMAX_SPLITS), 0, stream, part_val, part_idx, out_ids);
+  return g2b_check_launch("argmax_rows");
 }
 
 // ---- filtered sampling: repeat penalty, top-k, top-p ---------------------------
@@ -246,6 +324,8 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
                        float top_p, float penalty, const int *__restrict__ recent, int recent_ld,
                        const int *__restrict__ recent_n, int *seq_state, int state_words,
                        const int *__restrict__ slots, int *__restrict__ out_ids) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float scratch[32];
   __shared__ float hist[256];
   __shared__ float s_r;
@@ -318,7 +398,7 @@ extern "C" int g2b_sample_filtered(float *logits, int R, int V, int ld, float te
   if (!(penalty > 0.f)) G2B_REFUSE("sample_filtered: repeat penalty must be positive, got %g", penalty);
   if (temp > 0.f && (!seq_state || !slots || state_words < 4))
     G2B_REFUSE("sample_filtered: temperature sampling needs the per-slot state");
-  sample_filtered_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(
+  g2b_launch(sample_filtered_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, 
       logits, V, ld, temp, top_k, top_p, penalty, recent, recent_ld, recent_n, seq_state,
       state_words, slots, out_ids);
   return g2b_check_launch("sample_filtered");
@@ -327,6 +407,8 @@ extern "C" int g2b_sample_filtered(float *logits, int R, int V, int ld, float te
 // Seeds the per-slot records of the given slots: {seed_lo, seed_hi, stream, draws = 0}.
 __global__ void seed_slots_kernel(int *seq_state, int words, const int *slots, const int *streams,
                                   int n, uint32_t seed_lo, uint32_t seed_hi) {
+  pdl_launch();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   int *rec = seq_state + (size_t)slots[i] * words;
@@ -336,7 +418,7 @@ __global__ void seed_slots_kernel(int *seq_state, int words, const int *slots, c
 extern "C" int g2b_seed_slots(int *seq_state, int words, const int *slots, const int *streams,
                               int n, unsigned long long seed, cudaStream_t stream) {
   if (n <= 0) return 0;
-  seed_slots_kernel<<<(n + 127) / 128, 128, 0, stream>>>(
+  g2b_launch(seed_slots_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, 
       seq_state, words, slots, streams, n, (uint32_t)(seed & 0xffffffffull), (uint32_t)(seed >> 32));
   return g2b_check_launch("seed_slots");
 }

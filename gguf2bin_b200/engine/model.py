@@ -18,6 +18,7 @@ from ..config import ModelSpec, model_spec_from_folder
 from ..config.specs import ConfigError
 from ..parts import block_class, norm_class
 from ..parts.base import StepContext
+from ..parts.fused import normed_linear
 from ..weights.loader import Expected, load_weights
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
@@ -130,9 +131,7 @@ class Model:
             self.blocks[entry.layer].forward(x, ctx, cache.view(self.spec.cache_owner(position)))
         if n_want == 0:
             return None
-        xn = ws.buffer("head.normed", (n_want, self.hidden), self.dtype)
-        self.final_norm.forward(x, xn, rows=want_rows)
         logits = logits_out if logits_out is not None else \
             ws.buffer("head.logits", (n_want, self.vocab), torch.float32)
-        kernels.linear(xn, self.head, logits)
+        normed_linear(x, self.final_norm, self.head, logits, ctx, rows=want_rows)
         return logits

@@ -68,6 +68,7 @@ def _fn(unit: str, name: str, argtypes, defines=()):
 
 
 _launches = 0
+_scratch: dict = {}       # small persistent device buffers of the bindings, by (device, use)
 
 
 def launch_count() -> int:
@@ -240,6 +241,20 @@ def sample_rows(logits, temperature, seq_state, slots, out_ids) -> None:
     _need(logits, torch.float32, "logits")
     _need(out_ids, torch.int32, "out_ids")
     R, V = logits.shape
+    if temperature <= 0.0 and V >= 4096:
+        # greedy over a large vocabulary: many blocks per row, then one
+        key = (logits.device, "argmax")
+        scratch = _scratch.get(key)
+        if scratch is None or scratch[0].shape[0] < R * 64:
+            n = max(R, 64) * 64
+            scratch = (torch.empty(n, dtype=torch.float32, device=logits.device),
+                       torch.empty(n, dtype=torch.int32, device=logits.device))
+            _scratch[key] = scratch
+        f = _fn("sampling.cu", "g2b_argmax_rows",
+                [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+        _call(f, _ptr(logits), R, V, logits.stride(0), _ptr(scratch[0]), _ptr(scratch[1]),
+              _ptr(out_ids), _stream())
+        return
     f = _fn("sampling.cu", "g2b_sample_rows",
             [c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
     _call(f, _ptr(logits), R, V, logits.stride(0), temperature, _ptr(seq_state),

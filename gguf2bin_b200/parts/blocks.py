@@ -40,12 +40,21 @@ class PreNormBlock:
         return self.mixer.cache_need()
 
     def forward(self, x32: torch.Tensor, ctx, cache_view) -> None:
+        # a part that offers ``forward_from_stream`` takes the stream and the norm and may
+        # fold the norm into its first product; any other part gets normed activations
         T = x32.shape[0]
-        h = ctx.workspace.buffer("block.normed", (T, self.hidden), self.dtype)
-        self.mixer_norm.forward(x32, h)
-        self.mixer.forward(h, ctx, cache_view, x32)
-        self.ffn_norm.forward(x32, h)
-        self.feed_forward.forward(h, ctx, x32)
+        if hasattr(self.mixer, "forward_from_stream"):
+            self.mixer.forward_from_stream(x32, self.mixer_norm, ctx, cache_view, x32)
+        else:
+            h = ctx.workspace.buffer("block.normed", (T, self.hidden), self.dtype)
+            self.mixer_norm.forward(x32, h)
+            self.mixer.forward(h, ctx, cache_view, x32)
+        if hasattr(self.feed_forward, "forward_from_stream"):
+            self.feed_forward.forward_from_stream(x32, self.ffn_norm, ctx, x32)
+        else:
+            h = ctx.workspace.buffer("block.normed", (T, self.hidden), self.dtype)
+            self.ffn_norm.forward(x32, h)
+            self.feed_forward.forward(h, ctx, x32)
 
 
 register_block("prenorm", PreNormBlock)

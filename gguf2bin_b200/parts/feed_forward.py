@@ -13,6 +13,7 @@ import torch
 from .. import kernels
 from ..config.specs import PartSpec
 from ..weights.loader import Expected
+from .fused import normed_linear
 from .registry import register_feed_forward
 
 
@@ -49,6 +50,12 @@ class SwiGLU:
             gu = ws.buffer("ffn.gate_up", (T, 2 * self.inter), self.dtype)
             kernels.linear(h, self.w_gate_up, gu)
             kernels.swiglu(gu, mid, self.block)
+        kernels.linear(mid, self.w_down, residual32, accumulate=True)
+
+    def forward_from_stream(self, x32: torch.Tensor, norm, ctx, residual32: torch.Tensor) -> None:
+        """The same with the block's norm folded into the gate/up product."""
+        mid = ctx.workspace.buffer("ffn.mid", (x32.shape[0], self.inter), self.dtype)
+        normed_linear(x32, norm, self.w_gate_up, mid, ctx, gate_block=self.block)
         kernels.linear(mid, self.w_down, residual32, accumulate=True)
 
 

@@ -20,6 +20,7 @@ from .. import kernels
 from ..cache.storage import KVNeed, KVView
 from ..config.specs import ConfigError, PartSpec
 from ..weights.loader import Expected
+from .fused import normed_linear
 from .registry import norm_class, position_class, register_mixer
 
 
@@ -87,12 +88,26 @@ class GQAAttention:
     # ---- step ----------------------------------------------------------------
     def forward(self, h: torch.Tensor, ctx, view: KVView, residual32: torch.Tensor) -> None:
         T = h.shape[0]
+        nk = (0 if self.shared_kv else self.nkv) * self.hd
+        qkv = ctx.workspace.buffer("attn.qkv", (T, self.nh * self.hd + 2 * nk), self.dtype)
+        kernels.linear(h, self.w_qkv, qkv)
+        self._attend(qkv, ctx, view, residual32)
+
+    def forward_from_stream(self, x32: torch.Tensor, norm, ctx, view: KVView,
+                            residual32: torch.Tensor) -> None:
+        """The same with the block's norm folded into the q/k/v product."""
+        T = x32.shape[0]
+        nk = (0 if self.shared_kv else self.nkv) * self.hd
+        qkv = ctx.workspace.buffer("attn.qkv", (T, self.nh * self.hd + 2 * nk), self.dtype)
+        normed_linear(x32, norm, self.w_qkv, qkv, ctx)
+        self._attend(qkv, ctx, view, residual32)
+
+    def _attend(self, qkv: torch.Tensor, ctx, view: KVView, residual32: torch.Tensor) -> None:
+        T = qkv.shape[0]
         nq = self.nh * self.hd
         nkv_own = 0 if self.shared_kv else self.nkv        # kv heads this layer projects
         nk = nkv_own * self.hd
         ws = ctx.workspace
-        qkv = ws.buffer("attn.qkv", (T, nq + 2 * nk), self.dtype)
-        kernels.linear(h, self.w_qkv, qkv)
         q = ws.buffer("attn.q", (T, nq), self.dtype)
         fused = self.position.fused_rotation()
         if fused is not None:
