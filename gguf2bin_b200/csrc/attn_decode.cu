@@ -157,15 +157,15 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
       const float m_new = fmaxf(m[r], mx[r]);          // finite: the page holds a visible key
-      corr[r] = exp2f(m[r] - m_new);
+      corr[r] = fast_exp2(m[r] - m_new);
       m[r] = m_new;
       l[r] *= corr[r];
     }
     uint32_t pa[PAGE / 16][4];
 #pragma unroll
     for (int j = 0; j < PAGE / 8; ++j) {
-      const float p0 = exp2f(s[j][0] - m[0]), p1 = exp2f(s[j][1] - m[0]);
-      const float p2 = exp2f(s[j][2] - m[1]), p3 = exp2f(s[j][3] - m[1]);
+      const float p0 = fast_exp2(s[j][0] - m[0]), p1 = fast_exp2(s[j][1] - m[0]);
+      const float p2 = fast_exp2(s[j][2] - m[1]), p3 = fast_exp2(s[j][3] - m[1]);
       l[0] += p0 + p1;
       l[1] += p2 + p3;
       pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
@@ -225,8 +225,8 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
       for (int r = 0; r < 2; ++r) {
         const float mo = src[DTILES * 4 + r];
         const float m_new = fmaxf(m[r], mo);
-        a[r] = m[r] == -INFINITY ? 0.f : exp2f(m[r] - m_new);
-        bb[r] = mo == -INFINITY ? 0.f : exp2f(mo - m_new);
+        a[r] = m[r] == -INFINITY ? 0.f : fast_exp2(m[r] - m_new);
+        bb[r] = mo == -INFINITY ? 0.f : fast_exp2(mo - m_new);
         l[r] = l[r] * a[r] + src[DTILES * 4 + 2 + r] * bb[r];
         m[r] = m_new;
       }
@@ -269,7 +269,7 @@ attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__
   for (int i = c0; i <= c1; ++i) M = fmaxf(M, ml[i].x);
   float num = 0.f, den = 0.f;
   for (int i = c0; i <= c1; ++i) {
-    const float w = exp2f(ml[i].x - M);
+    const float w = fast_exp2(ml[i].x - M);
     num = fmaf(w, part_o[(th * n_chunks + i) * HD + d], num);
     den = fmaf(w, ml[i].y, den);
   }

@@ -51,7 +51,7 @@ __device__ __forceinline__ void load_panel(uint32_t smem_panel, const bf16 *gpan
 }
 
 // tiles: [n_tiles][4] = {sequence index, first token index, rows, position of row 0}
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, 3)
 attn_prefill_kernel(const bf16 *__restrict__ q, bf16 *__restrict__ out,
                     const bf16 *__restrict__ cache, const int4 *__restrict__ tiles,
                     const int *__restrict__ page_table, int P, int nh, int nkv, int window,
@@ -152,15 +152,15 @@ attn_prefill_kernel(const bf16 *__restrict__ q, bf16 *__restrict__ out,
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
         const float m_new = fmaxf(m[r], mx[r]);
         msafe[r] = m_new == -INFINITY ? 0.f : m_new;      // a row that has seen no key yet
-        corr[r] = exp2f(m[r] - msafe[r]);
+        corr[r] = fast_exp2(m[r] - msafe[r]);
         m[r] = m_new;
         l[r] *= corr[r];
       }
       uint32_t pa[PAGE / 16][4];
 #pragma unroll
       for (int j = 0; j < PAGE / 8; ++j) {
-        const float p0 = exp2f(s[j][0] - msafe[0]), p1 = exp2f(s[j][1] - msafe[0]);
-        const float p2 = exp2f(s[j][2] - msafe[1]), p3 = exp2f(s[j][3] - msafe[1]);
+        const float p0 = fast_exp2(s[j][0] - msafe[0]), p1 = fast_exp2(s[j][1] - msafe[0]);
+        const float p2 = fast_exp2(s[j][2] - msafe[1]), p3 = fast_exp2(s[j][3] - msafe[1]);
         l[0] += p0 + p1;
         l[1] += p2 + p3;
         pa[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);

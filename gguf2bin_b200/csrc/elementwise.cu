@@ -185,11 +185,63 @@ __global__ void qknorm_rope_cache_kernel(
   __syncthreads();
   const int h_begin = blockIdx.y * heads_per_block;
   const int h_end = min(heads, h_begin + heads_per_block);
+  const int page = (cache && page_table) ? page_table[(size_t)tok_seq[t] * P + pos / page_size] : 0;
+  // register path: head sizes that are multiples of 4 up to 256, rotation (if any) over the
+  // whole head.  A lane holds the elements (2l, 2l+1) of each half and their partners.
+  const bool in_registers = (hd % 4 == 0) && hd <= 256 && (!inv_freq || rot_dim == hd);
   float *x = buf[warp];
   for (int h = h_begin + warp; h < h_end; h += QKN_WARPS) {
     const T *src = qkv + (size_t)t * heads * hd + (size_t)h * hd;
     const int kind = h < nh ? 0 : (h < nh + nkv ? 1 : 2);       // 0 q, 1 k, 2 v
     const float *w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
+    T *dst;
+    if (kind == 0) {
+      dst = q_out + (size_t)t * nh * hd + (size_t)h * hd;
+    } else {
+      const int kvh = kind == 1 ? h - nh : h - nh - nkv;
+      T *flat = kind == 1 ? k_out : v_out;
+      if (flat) dst = flat + (size_t)t * nkv * hd + (size_t)kvh * hd;
+      else dst = cache + ((((size_t)page * 2 + (kind - 1)) * nkv + kvh) * page_size + pos % page_size) * hd;
+    }
+    if (in_registers) {
+      const int hh = hd >> 1;                      // first element of the second half
+      float a[2][2], b[2][2];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int j = 2 * lane + 64 * i;
+        if (j < hh) {
+          a[i][0] = to_f32(src[j]); a[i][1] = to_f32(src[j + 1]);
+          b[i][0] = to_f32(src[hh + j]); b[i][1] = to_f32(src[hh + j + 1]);
+          ss = fmaf(a[i][0], a[i][0], ss); ss = fmaf(a[i][1], a[i][1], ss);
+          ss = fmaf(b[i][0], b[i][0], ss); ss = fmaf(b[i][1], b[i][1], ss);
+        }
+      }
+      ss = warp_sum(ss);
+      const float inv = w ? 1.f / sqrtf(ss / (float)hd + eps) : 1.f;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int j = 2 * lane + 64 * i;
+        if (j < hh) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            float av = a[i][e], bv = b[i][e];
+            if (w) {
+              av = (w[j + e] * av) * inv;
+              bv = (w[hh + j + e] * bv) * inv;
+            }
+            if (kind != 2 && inv_freq) {
+              const float c = cs[j + e], sn = cs[half + j + e];
+              const float ra = av * c - bv * sn, rb = av * sn + bv * c;
+              av = ra; bv = rb;
+            }
+            dst[j + e] = from_f32<T>(av);
+            dst[hh + j + e] = from_f32<T>(bv);
+          }
+        }
+      }
+      continue;
+    }
     float ss = 0.f;
     for (int j = lane; j < hd; j += 32) {
       const float v = to_f32(src[j]);
@@ -206,24 +258,11 @@ __global__ void qknorm_rope_cache_kernel(
     if (kind != 2 && inv_freq) {
       for (int j = lane; j < half; j += 32) {
         const float c = cs[j], sn = cs[half + j];
-        const float a = x[j], b = x[j + half];
-        x[j] = a * c - b * sn;
-        x[j + half] = a * sn + b * c;
+        const float av = x[j], bv = x[j + half];
+        x[j] = av * c - bv * sn;
+        x[j + half] = av * sn + bv * c;
       }
       __syncwarp();
-    }
-    T *dst;
-    if (kind == 0) {
-      dst = q_out + (size_t)t * nh * hd + (size_t)h * hd;
-    } else {
-      const int kvh = kind == 1 ? h - nh : h - nh - nkv;
-      T *flat = kind == 1 ? k_out : v_out;
-      if (flat) {
-        dst = flat + (size_t)t * nkv * hd + (size_t)kvh * hd;
-      } else {
-        const int page = page_table[(size_t)tok_seq[t] * P + pos / page_size];
-        dst = cache + ((((size_t)page * 2 + (kind - 1)) * nkv + kvh) * page_size + pos % page_size) * hd;
-      }
     }
     for (int j = lane; j < hd; j += 32) dst[j] = from_f32<T>(x[j]);
     __syncwarp();                                  // x is reused for the warp's next head
@@ -245,9 +284,10 @@ extern "C" int g2b_qknorm_rope_cache(const void *qkv, int dtype, int T_tokens, i
     G2B_REFUSE("qknorm_rope_cache: k_out and v_out must be given together");
   if (nkv > 0 && !k_out && (!cache || !page_table || page_size <= 0))
     G2B_REFUSE("qknorm_rope_cache: no cache to write to");
-  // few tokens: one head per warp (more blocks); many tokens: a block takes all heads
+  // few tokens: one head per warp (more blocks); many tokens: two heads per warp, so that the
+  // position's sines and cosines are shared by eight heads and a warp's chain stays short
   const int heads = nh + 2 * nkv;
-  const int heads_per_block = T_tokens >= 256 ? heads : QKN_WARPS;
+  const int heads_per_block = T_tokens >= 256 ? 2 * QKN_WARPS : QKN_WARPS;
   const dim3 blocks((unsigned)T_tokens, (unsigned)((heads + heads_per_block - 1) / heads_per_block));
   if (blocks.y > 65535) G2B_REFUSE("qknorm_rope_cache: %d heads", heads);
   if (dtype == G2B_F32)

@@ -156,7 +156,7 @@ gemm_small_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W, void *
         const size_t o = (size_t)m * ldc + n;
         if (EPI == EPI_STORE_BF16) ((bf16 *)Cv)[o] = __float2bfloat16_rn(v);
         else if (EPI == EPI_STORE_F32) ((float *)Cv)[o] = v;
-        else ((float *)Cv)[o] += v;
+        else atomicAdd((float *)Cv + o, v);   // a reduction: one add per element and launch, no load on the path
       }
     }
   }
@@ -320,7 +320,7 @@ gemm_small_whole_kernel(const void *__restrict__ Av, const float *__restrict__ n
                 const size_t o = (size_t)m * ldc + n;
                 if (EPI == EPI_STORE_BF16) ((bf16 *)Cv)[o] = __float2bfloat16_rn(v);
                 else if (EPI == EPI_STORE_F32) ((float *)Cv)[o] = v;
-                else ((float *)Cv)[o] += v;
+                else atomicAdd((float *)Cv + o, v);   // a reduction: one add per element and launch, no load on the path
               }
             }
           }

@@ -27,11 +27,14 @@
 
 #include <cuda.h>
 
+#include <functional>
+#include <mutex>
+#include <unordered_map>
+
 G2B_DEFINE_LAST_ERROR
 
 constexpr int BM = 128;
 constexpr int BK = 64;                      // 64 bf16 = 128 bytes = one swizzle row
-constexpr int STAGES = 3;
 constexpr int THREADS = 192;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;   // polls of a barrier before giving up
 
@@ -123,7 +126,7 @@ __host__ __device__ constexpr uint32_t instr_desc(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
-template <int BN> struct Smem {
+template <int BN, int STAGES> struct Smem {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -131,13 +134,13 @@ template <int BN> struct Smem {
   static constexpr int TOTAL = BARRIER_OFFSET + 128 + 1024;   // barriers + tmem slot + alignment slack
 };
 
-template <int BN, int EPI>
+template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                void *__restrict__ Cv, int M, int N, int K, int ldc, int *__restrict__ status) {
   pdl_launch();
   extern __shared__ unsigned char smem_raw[];
-  using S = Smem<BN>;
+  using S = Smem<BN, STAGES>;
   // 1024-byte alignment: the swizzle pattern is a function of address bits 4..9
   unsigned char *smem = reinterpret_cast<unsigned char *>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -232,7 +235,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (col_ok && m0 + warp * 32 + rr < M) {
               float *p = cbase + (size_t)rr * ldc;
               const float v = scr[rr * 33 + lane];
-              *p = EPI == EPI_ACCUM_F32 ? *p + v : v;
+              // one thread adds to an element once per launch, so the reduction (no value
+              // comes back, nothing waits for the old one) gives the same sum as load-add-store
+              if (EPI == EPI_ACCUM_F32) atomicAdd(p, v);
+              else *p = v;
             }
           }
           __syncwarp();
@@ -309,8 +315,44 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// Encoded maps are kept by (address, rows, K, stride, box): weights and the step's scratch
+// buffers come back with the same values every step, and an encode costs microseconds.
+struct MapKey {
+  const void *base; int rows, K, ld, box;
+  bool operator==(const MapKey &o) const {
+    return base == o.base && rows == o.rows && K == o.K && ld == o.ld && box == o.box;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey &k) const {
+    size_t h = std::hash<const void *>()(k.base);
+    h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.K;
+    h = h * 1000003u ^ (size_t)k.ld;   h = h * 1000003u ^ (size_t)k.box;
+    return h;
+  }
+};
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+static std::mutex g_maps_mutex;
+
+static int encode_map(CUtensorMap *map, const void *base, int rows, int K, int ld, int box_rows);
+
 // A tiled map of a row-major [rows, K] bfloat16 matrix with boxes of box_rows x 64, 128-byte swizzle.
 static int make_map(CUtensorMap *map, const void *base, int rows, int K, int ld, int box_rows) {
+  const MapKey key{base, rows, K, ld, box_rows};
+  std::lock_guard<std::mutex> lock(g_maps_mutex);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *map = it->second;
+    return 0;
+  }
+  const int rc = encode_map(map, base, rows, K, ld, box_rows);
+  if (rc) return rc;
+  if (g_maps.size() > 65536) g_maps.clear();         // a bound, not a policy: maps are cheap to rebuild
+  g_maps.emplace(key, *map);
+  return 0;
+}
+
+static int encode_map(CUtensorMap *map, const void *base, int rows, int K, int ld, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) G2B_REFUSE("gemm_tc: cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -324,46 +366,56 @@ static int make_map(CUtensorMap *map, const void *base, int rows, int K, int ld,
   return 0;
 }
 
-template <int BN, int EPI>
+template <int BN, int STAGES, int EPI>
 static int launch(const CUtensorMap &ma, const CUtensorMap &mw, void *C, int M, int N, int K, int ldc,
                   int *status, cudaStream_t stream) {
   static bool configured = false;
-  const int smem = Smem<BN>::TOTAL;
+  const int smem = Smem<BN, STAGES>::TOTAL;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) G2B_REFUSE("gemm_tc: shared memory of %d bytes refused: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) G2B_REFUSE("gemm_tc: M=%d is too large for one launch", M);
-  g2b_launch(gemm_tc_kernel<BN, EPI>, dim3(grid), dim3(THREADS), smem, stream, ma, mw, C, M, N, K, ldc, status);
+  g2b_launch(gemm_tc_kernel<BN, STAGES, EPI>, dim3(grid), dim3(THREADS), smem, stream, ma, mw, C, M, N, K, ldc, status);
   return g2b_check_launch("gemm_tc");
 }
 
 // A [M,K], W [N,K] bfloat16, inner stride 1, row strides multiples of 8 elements, base
 // addresses 16-byte aligned.  epi: 0 store bfloat16, 1 store float, 2 add into float,
 // 3 SiLU gate (C is [M, N/2] bfloat16; N a multiple of 16).  `status` is a device int the
-// kernel sets non-zero if one of its bounded waits gave up.  bn: 128 or 256.
+// kernel sets non-zero if one of its bounded waits gave up.  Tile shapes (bn, stages):
+// (64,4) (64,8) (128,3) (128,6) (256,4); bn = 0 picks one from the sizes: wide tiles when
+// there are plenty of them, narrow tiles with a deeper ring when the grid would not fill
+// the GPU (the ring has to cover the latency of the copies by itself then).
 extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, int K, int lda,
-                           int ldw, int ldc, int epi, int bn, int *status, cudaStream_t stream) {
+                           int ldw, int ldc, int epi, int bn, int stages, int *status,
+                           cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || lda % 8 || ldw % 8)
     G2B_REFUSE("gemm_tc: K=%d and the row strides (%d, %d) must be multiples of 8", K, lda, ldw);
   if (((uintptr_t)A | (uintptr_t)W) & 15) G2B_REFUSE("gemm_tc: operands must be 16-byte aligned");
   if (epi == EPI_SWIGLU_BF16 && N % 16) G2B_REFUSE("gemm_tc: gated output needs N %% 16 == 0, N=%d", N);
   if (!status) G2B_REFUSE("gemm_tc: no status word");
-  if (bn != 128 && bn != 256) G2B_REFUSE("gemm_tc: tile width %d (128 or 256)", bn);
+  if (bn == 0) {
+    const long long tiles128 = (long long)((M + BM - 1) / BM) * ((N + 127) / 128);
+    if (tiles128 >= 2 * 148) { bn = 128; stages = 3; }
+    else { bn = 64; stages = 4; }
+  }
   CUtensorMap ma, mw;
   int rc = make_map(&ma, A, M, K, lda, BM);
   if (rc) return rc;
-  rc = make_map(&mw, W, N, K, ldw, bn == 256 ? 256 : 128);
+  rc = make_map(&mw, W, N, K, ldw, bn);
   if (rc) return rc;
-#define G2B_CASE(BN_, E)                                                           \
-  if (bn == BN_ && epi == E) return launch<BN_, E>(ma, mw, C, M, N, K, ldc, status, stream);
-  G2B_CASE(128, EPI_STORE_BF16) G2B_CASE(128, EPI_STORE_F32) G2B_CASE(128, EPI_ACCUM_F32)
-  G2B_CASE(128, EPI_SWIGLU_BF16) G2B_CASE(256, EPI_STORE_BF16) G2B_CASE(256, EPI_STORE_F32)
-  G2B_CASE(256, EPI_ACCUM_F32) G2B_CASE(256, EPI_SWIGLU_BF16)
+#define G2B_CASE(BN_, ST_, E) \
+  if (bn == BN_ && stages == ST_ && epi == E) return launch<BN_, ST_, E>(ma, mw, C, M, N, K, ldc, status, stream);
+#define G2B_SHAPE(BN_, ST_) \
+  G2B_CASE(BN_, ST_, EPI_STORE_BF16) G2B_CASE(BN_, ST_, EPI_STORE_F32) \
+  G2B_CASE(BN_, ST_, EPI_ACCUM_F32) G2B_CASE(BN_, ST_, EPI_SWIGLU_BF16)
+  G2B_SHAPE(64, 4) G2B_SHAPE(64, 8) G2B_SHAPE(128, 3) G2B_SHAPE(128, 6) G2B_SHAPE(256, 4)
+#undef G2B_SHAPE
 #undef G2B_CASE
-  G2B_REFUSE("gemm_tc: unknown epilogue %d", epi);
+  G2B_REFUSE("gemm_tc: no kernel for tile width %d with %d stages and epilogue %d", bn, stages, epi);
 }

@@ -64,12 +64,13 @@ def _tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
             and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def _gemm_tc(a, w, out, epi, bn: int = 128) -> None:
+def _gemm_tc(a, w, out, epi, bn: int = 0, stages: int = 0) -> None:
+    """bn = 0 lets the launcher pick the tile shape from the sizes."""
     f = _fn("gemm_tc.cu", "g2b_gemm_tc",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_void_p, c_void_p])
+             c_int, c_void_p, c_void_p])
     _call(f, _ptr(a), _ptr(w), _ptr(out), a.shape[0], w.shape[0], a.shape[1], a.stride(0),
-          w.stride(0), out.stride(0), epi, bn, _ptr(_status_word(a.device)), _stream())
+          w.stride(0), out.stride(0), epi, bn, stages, _ptr(_status_word(a.device)), _stream())
 
 
 def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
