@@ -31,8 +31,14 @@ constexpr int PAGE = 64;                       // keys per page
 constexpr int ROW_BYTES = HD * 2;
 constexpr int ROW_CHUNKS = HD / 8;             // 16-byte pieces per row
 constexpr int PANEL_BYTES = PAGE * ROW_BYTES;  // one (page, kv head) panel of K or of V
-constexpr int WARPS = 2;
-constexpr int PAGES_PER_CTA = 4;
+#ifndef ATTN_DECODE_WARPS
+#define ATTN_DECODE_WARPS 2
+#endif
+#ifndef ATTN_DECODE_PAGES
+#define ATTN_DECODE_PAGES 4
+#endif
+constexpr int WARPS = ATTN_DECODE_WARPS;
+constexpr int PAGES_PER_CTA = ATTN_DECODE_PAGES;
 constexpr int CHUNK_KEYS = PAGE * PAGES_PER_CTA;
 constexpr int KSTEPS = HD / 16;                // k-steps of q.k over the head size
 constexpr int DTILES = HD / 8;                 // n-tiles of the output over the head size

@@ -163,13 +163,14 @@ gemm_small_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W, void *
 }
 
 
-constexpr int DEPTH_WHOLE = 8;          // K blocks of W in flight per thread (whole-A kernel)
+// K blocks of W in flight per thread (whole-A kernel): 4 when K has at most four blocks, else
+// 8; the shallower ring frees registers, so that three blocks instead of two fit an SM
 
 // NORM: A is the float32 stream x[rows_or_identity[m], :] and is normalised while staged.
 // A CTA takes `tiles_per_cta` consecutive 16-row tiles of W: the activations are staged
 // once, and the weight stream runs on across the tiles while a tile's sums are reduced.
-template <int MT, int EPI, bool NORM>
-__global__ void __launch_bounds__(WARPS * 32)
+template <int MT, int EPI, bool NORM, int DEPTH_WHOLE>
+__global__ void __launch_bounds__(WARPS * 32, DEPTH_WHOLE == 4 ? 3 : 2)
 gemm_small_whole_kernel(const void *__restrict__ Av, const float *__restrict__ norm_w, float eps,
                         const int *__restrict__ rows, const bf16 *__restrict__ W,
                         void *__restrict__ Cv, int M, int N, int K, int lda, int ldw, int ldc,
@@ -340,8 +341,8 @@ static size_t whole_smem(int mrows, int K) {
   return need <= 200 * 1024 ? need : 0;
 }
 
-template <int MT, bool NORM>
-static int launch_whole(const void *A, const float *norm_w, float eps, const int *rows,
+template <int MT, bool NORM, int DEPTH_WHOLE>
+static int launch_whole_depth(const void *A, const float *norm_w, float eps, const int *rows,
                         const void *W, void *C, int M, int N, int K, int lda, int ldw, int ldc,
                         int epi, cudaStream_t stream) {
   const int smem = (int)whole_smem(MT * 8, K);
@@ -354,12 +355,12 @@ static int launch_whole(const void *A, const float *norm_w, float eps, const int
   do {                                                                                           \
     static int configured = 0;                                                                   \
     if (configured < smem) {                                                                     \
-      cudaError_t e = cudaFuncSetAttribute(gemm_small_whole_kernel<MT, E, NORM>,                 \
+      cudaError_t e = cudaFuncSetAttribute(gemm_small_whole_kernel<MT, E, NORM, DEPTH_WHOLE>,                 \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem);   \
       if (e != cudaSuccess) G2B_REFUSE("gemm_small: shared memory: %s", cudaGetErrorString(e));  \
       configured = smem;                                                                         \
     }                                                                                            \
-    g2b_launch(gemm_small_whole_kernel<MT, E, NORM>, dim3(grid), dim3(WARPS * 32), smem, stream,                     \
+    g2b_launch(gemm_small_whole_kernel<MT, E, NORM, DEPTH_WHOLE>, dim3(grid), dim3(WARPS * 32), smem, stream,                     \
         A, norm_w, eps, rows, (const bf16 *)W, C, M, N, K, lda, ldw, ldc, tiles_per_cta);        \
   } while (0)
   switch (epi) {
@@ -402,6 +403,15 @@ static int launch_mt(const void *A, const void *W, void *C, int M, int N, int K,
   }
 #undef G2B_LAUNCH
   return g2b_check_launch("gemm_small");
+}
+
+template <int MT, bool NORM>
+static int launch_whole(const void *A, const float *norm_w, float eps, const int *rows,
+                        const void *W, void *C, int M, int N, int K, int lda, int ldw, int ldc,
+                        int epi, cudaStream_t stream) {
+  if ((K + KB - 1) / KB <= 4)
+    return launch_whole_depth<MT, NORM, 4>(A, norm_w, eps, rows, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+  return launch_whole_depth<MT, NORM, 8>(A, norm_w, eps, rows, W, C, M, N, K, lda, ldw, ldc, epi, stream);
 }
 
 // A [M,K] and W [N,K] bfloat16 with unit inner stride; rows 16-byte aligned.

@@ -16,7 +16,7 @@ from .. import kernels
 
 
 FUSE_MAX_ROWS = 16
-FUSE_MAX_OUTPUTS = 8192
+FUSE_MAX_OUTPUTS = 4096
 
 
 def _rms_params(norm):
