@@ -19,7 +19,7 @@ import torch
 
 from ..cache.pool import CacheError, Sequence
 from ..cache.storage import Cache
-from ..parts.base import ATTN_TILE_ROWS, StepContext
+from ..parts.base import ATTN_TILE_ROWS, ATTN_WIDE_TILE_ROWS, StepContext
 from .model import Model
 from .workspace import Workspace
 
@@ -95,13 +95,18 @@ class Engine:
         P = max(len(e.seq.pages) for e in entries)
         n_want = sum(len(e.want) for e in entries)
         # prompt-attention work list: tiles of 64 query rows, the longest key ranges first
-        tiles = []
+        tiles, wide = [], []
         t0 = 0
         for b, e in enumerate(entries):
             for r in range(0, q_lens[b], ATTN_TILE_ROWS):
                 tiles.append((b, t0 + r, min(ATTN_TILE_ROWS, q_lens[b] - r), past[b] + r))
+            for r in range(0, q_lens[b], ATTN_WIDE_TILE_ROWS):
+                wide.append((b, t0 + r, min(ATTN_WIDE_TILE_ROWS, q_lens[b] - r), past[b] + r))
             t0 += q_lens[b]
         tiles.sort(key=lambda t: -(t[3] + t[2]))
+        wide.sort(key=lambda t: -(t[3] + t[2]))
+        n_narrow = len(tiles)
+        tiles = tiles + wide
         n_tiles = len(tiles)
         # layout: tiles[n_tiles*4] tok_ids[T] tok_pos[T] tok_seq[T] want[n_want] seq_meta[B*4]
         #         page_table[B*P]   (the tiles come first: the kernel reads them 16 bytes at a time)
@@ -139,7 +144,9 @@ class Engine:
             q_lens=q_lens, past_lens=past, slots=[e.seq.slot for e in entries],
             max_kv_len=max(p + n for p, n in zip(past, q_lens)),
             seq_meta=dev[o_meta:o_meta + 4 * B].view(B, 4),
-            attn_tiles=dev[:4 * n_tiles].view(n_tiles, 4), n_attn_tiles=n_tiles)
+            attn_tiles=dev[:4 * n_narrow].view(n_narrow, 4), n_attn_tiles=n_narrow,
+            attn_tiles_wide=dev[4 * n_narrow:4 * n_tiles].view(n_tiles - n_narrow, 4),
+            n_attn_tiles_wide=n_tiles - n_narrow)
         return ctx, dev[o_want:o_want + n_want], n_want
 
     def step(self, entries: Seq[StepEntry]) -> Optional[torch.Tensor]:

@@ -161,7 +161,7 @@ def prefill(a) -> None:
           nbytes=T * H * 6)
     ps = 64
     pages = -(-T // ps)
-    if b.want("attn_prefill") or b.want("qknorm_rope_cache"):
+    if b.want("attn_prefill") or b.want("attn_prefill_tc") or b.want("qknorm_rope_cache"):
         caches = [torch.randn(pages, 2, nkv, ps, hd, device=DEV).to(torch.bfloat16) for _ in range(L)]
         table = torch.arange(pages, dtype=torch.int32, device=DEV).view(1, pages)
         tok_pos = torch.arange(T, dtype=torch.int32, device=DEV)
@@ -178,6 +178,12 @@ def prefill(a) -> None:
                               attn_tiles=torch.tensor(tiles, dtype=torch.int32, device=DEV))
         b.run("attn_prefill", lambda: [kernels_bf16.attn_prefill(q, out, c, ctx, nh, nkv, hd, ps, 0, 1 / math.sqrt(hd))
                                        for c in caches], L, flops=4 * NQ * T * (T + 1) / 2)
+        wide = sorted([(0, r, min(128, T - r), r) for r in range(0, T, 128)], key=lambda t: -t[3])
+        ctx2 = SimpleNamespace(page_table=table, all_single=False, n_attn_tiles_wide=len(wide),
+                               attn_tiles_wide=torch.tensor(wide, dtype=torch.int32, device=DEV))
+        b.run("attn_prefill_tc", lambda: [kernels_bf16.attn_prefill_tc(
+            q, out, c, ctx2, nh, nkv, hd, ps, 0, 1 / math.sqrt(hd)) for c in caches], L,
+            flops=4 * NQ * T * (T + 1) / 2)
     kernels_bf16.check_status()
 
 

@@ -13,7 +13,7 @@ FAST_HEAD_SIZES = (64, 128)          # head sizes the tensor-core attention kern
 DECODE_CHUNK_KEYS = 256              # keys per CTA of the decode kernel (attn_decode.cu)
 
 units.SPECIALISED_SOURCES[:] = [("attn_decode.cu", ()), ("attn_decode_noalloc.cu", ()),
-                                ("attn_prefill.cu", ())]
+                                ("attn_prefill.cu", ()), ("attn_prefill_tc.cu", ())]
 units.BF16_UNITS[:] = [("gemm_small.cu", ()), ("gemm_tc.cu", ())]
 
 
@@ -139,10 +139,28 @@ def attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page
     if ctx.all_single:
         attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window, scale)
         return True
+    if USE_TC_ATTENTION and getattr(ctx, "attn_tiles_wide", None) is not None and ctx.n_attn_tiles_wide > 0:
+        attn_prefill_tc(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window, scale)
+        return True
     if getattr(ctx, "attn_tiles", None) is not None and ctx.n_attn_tiles > 0:
         attn_prefill(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window, scale)
         return True
     return False
+
+
+USE_TC_ATTENTION = True      # prompt attention on tcgen05 (else the mma.sync kernel)
+
+
+def attn_prefill_tc(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
+                    scale) -> None:
+    """Prompt attention on the tcgen05 tensor cores over the step's 128-row query tiles."""
+    from ctypes import c_longlong
+    f = _fn("attn_prefill_tc.cu", "g2b_attn_prefill_tc",
+            [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p], defines=(f"HD={head_dim}",))
+    _call(f, _ptr(q), _ptr(out), _ptr(cache_pages), cache_pages.shape[0], _ptr(ctx.attn_tiles_wide),
+          ctx.n_attn_tiles_wide, _ptr(ctx.page_table), ctx.page_table.shape[1], q.shape[0], n_heads,
+          n_kv_heads, head_dim, page_size, window, scale, _ptr(_status_word(q.device)), _stream())
 
 
 def attn_prefill(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,

@@ -25,7 +25,8 @@ from typing import Optional
 import torch
 
 
-ATTN_TILE_ROWS = 64          # query rows per work item of the prompt attention kernel
+ATTN_TILE_ROWS = 64          # query rows per work item of the prompt attention kernel (mma.sync)
+ATTN_WIDE_TILE_ROWS = 128    # ... of the tcgen05 prompt attention kernel
 
 
 @dataclass
@@ -54,6 +55,8 @@ class StepContext:
     seq_meta: Optional[torch.Tensor] = None          # [B,4] int32: q_start, q_len, past, slot
     attn_tiles: Optional[torch.Tensor] = None        # [n,4] int32: sequence, first token, rows, position
     n_attn_tiles: int = 0                            # of row 0; tiles of ATTN_TILE_ROWS query rows
+    attn_tiles_wide: Optional[torch.Tensor] = None   # the same with ATTN_WIDE_TILE_ROWS rows (tcgen05 kernel)
+    n_attn_tiles_wide: int = 0
 
     @property
     def all_single(self) -> bool:

@@ -300,9 +300,10 @@ def test_gemm_small(M, N, K):
         assert (mid.double() - want).abs().max().item() <= want.abs().max().item() * 2.0 ** -8 + tol
 
 
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
 @pytest.mark.parametrize("nh,nkv,hd,window", [(16, 8, 128, 0), (5, 1, 128, 0), (6, 2, 64, 0), (4, 2, 64, 100),
                                               (2, 2, 128, 33)])
-def test_attn_prefill(nh, nkv, hd, window):
+def test_attn_prefill(nh, nkv, hd, window, kernel):
     """Prompt attention: a whole prompt that is no multiple of the 64-row tile, a prompt
     continued after a past that ends inside a page, a single token far into a sequence,
     and a short prompt; windows that start inside a page."""
@@ -312,17 +313,23 @@ def test_attn_prefill(nh, nkv, hd, window):
     lens = [333, 200, 700, 5]
     q_lens = [333, 70, 1, 5]
     cache, table, Ks, Vs = make_paged(len(lens), lens, nkv, hd, ps, torch.bfloat16, seed=70)
+    rows = 64 if kernel == "mma" else 128
     tiles, t0 = [], 0
     for b, (l, ql) in enumerate(zip(lens, q_lens)):
-        for r in range(0, ql, 64):
-            tiles.append((b, t0 + r, min(64, ql - r), l - ql + r))
+        for r in range(0, ql, rows):
+            tiles.append((b, t0 + r, min(rows, ql - r), l - ql + r))
         t0 += ql
     T = t0
     q = rnd(T, nh * hd, dtype=torch.bfloat16, seed=71)
     out = torch.zeros_like(q)
-    ctx = SimpleNamespace(page_table=table, all_single=False, n_attn_tiles=len(tiles),
-                          attn_tiles=torch.tensor(tiles, dtype=torch.int32, device=DEV))
-    assert kernels_bf16.attention_bf16(q, out, cache, ctx, nh, nkv, hd, ps, window, 1 / math.sqrt(hd))
+    tt = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    if kernel == "mma":
+        ctx = SimpleNamespace(page_table=table, all_single=False, n_attn_tiles=len(tiles), attn_tiles=tt)
+        kernels_bf16.attn_prefill(q, out, cache, ctx, nh, nkv, hd, ps, window, 1 / math.sqrt(hd))
+    else:
+        ctx = SimpleNamespace(page_table=table, all_single=False, n_attn_tiles_wide=len(tiles), attn_tiles_wide=tt)
+        kernels_bf16.attn_prefill_tc(q, out, cache, ctx, nh, nkv, hd, ps, window, 1 / math.sqrt(hd))
+        kernels_bf16.check_status()
     got = out.float().cpu().numpy().reshape(T, nh, hd)
     t = 0
     for b, (l, ql) in enumerate(zip(lens, q_lens)):
