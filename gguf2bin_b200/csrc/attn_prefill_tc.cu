@@ -5,19 +5,22 @@
 // first row), longest first; grid (tile, query head).  Roles by warp:
 //   warp 4, one thread  TMA producer: the 128 x HD query tile once, then per key page the K
 //                       and V panels of (page, kv head), each as 64-column boxes with 128-byte
-//                       swizzle, into a two-stage ring.
+//                       swizzle, into a four-stage ring.
 //   warp 5, one thread  MMA issuer (tcgen05.mma, cta_group::1, kind::f16):
-//                         S[128 x 64]  = Q K^T      (both operands K-major)  -> tensor memory
-//                         O[128 x HD] += P V        (P K-major from shared memory, V read as
+//                         S[128 x 64]  = Q K^T      (both operands K-major)  -> tensor memory,
+//                                                    two S buffers, always one page ahead
+//                         O[128 x HD] += P V        (P read from tensor memory, V read as
 //                                                    an MN-major operand: keys are its K index)
 //   warps 0..3          softmax, one thread per query row: reads its row of S with tcgen05.ld,
 //                       scales (log2 domain), masks (causal, window), keeps a reference maximum
-//                       and a sum in float, writes P = 2^(s - m) as bfloat16 into swizzled
-//                       shared memory for the second product.  O is rescaled in tensor memory
-//                       only when a row's maximum has grown by more than 2^8 since its
-//                       reference (the result is the same function of the scores; the factor
-//                       just stays bounded), and is normalised and stored at the end.
-// Per page: S MMA -> softmax -> P.V MMA; two CTAs per SM overlap each other's phases.
+//                       and a sum in float, and writes P = 2^(s - m) as packed bfloat16 back
+//                       into the first columns of the same S buffer (tcgen05.st), where the
+//                       second product reads it.  O is rescaled in tensor memory only when a
+//                       row's maximum has grown by more than 2^8 since its reference (the
+//                       result is the same function of the scores; the factor just stays
+//                       bounded), and is normalised and stored at the end.
+// Issue order of the MMAs: S0, S1, [P0 ready] PV0, S2, [P1 ready] PV1, S3, ...: while the
+// softmax warps work on page i, S of page i+1 is already there and P.V of page i-1 runs.
 //
 // Every mbarrier wait is bounded; a wait that gives up records a code in `*status`, all roles
 // fall through to the common exit and the tensor memory is freed.
@@ -38,22 +41,22 @@ using namespace tc;
 constexpr int PAGE = 64;
 constexpr int BM = 128;
 constexpr int THREADS = 192;
-constexpr int STAGES = 2;
+constexpr int STAGES = 4;
 constexpr int SUBS = HD / 64;                       // 64-column boxes along the head dimension
 constexpr int Q_SUB_BYTES = BM * 128;               // one 128 x 64 box
 constexpr int Q_BYTES = SUBS * Q_SUB_BYTES;
 constexpr int KV_SUB_BYTES = PAGE * 128;            // one 64 x 64 box
 constexpr int KV_BYTES = SUBS * KV_SUB_BYTES;       // K (or V) of one page and kv head
 constexpr int STAGE_BYTES = 2 * KV_BYTES;
-constexpr int P_BYTES = BM * 128;
-constexpr int BAR_OFFSET = Q_BYTES + STAGES * STAGE_BYTES + P_BYTES;
+constexpr int BAR_OFFSET = Q_BYTES + STAGES * STAGE_BYTES;
 constexpr int SMEM_TOTAL = BAR_OFFSET + 128 + 1024;
-constexpr int O_COL0 = 64;                          // S at columns 0..63, O from 64
-constexpr int TMEM_COLS = (64 + HD) <= 128 ? 128 : 256;
+constexpr int O_COL0 = 128;                         // S buffers at columns 0..63 and 64..127, O from 128
+constexpr int TMEM_COLS = 256;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.f;                 // log2 of the growth that triggers a rescale
 
 enum { ST_PRODUCER = 11, ST_MMA = 12, ST_SOFTMAX = 13 };
+static_assert(HD <= 128, "O uses columns 128..255");
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -76,12 +79,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char *q_smem = smem;
   unsigned char *kv_smem = smem + Q_BYTES;
-  unsigned char *p_smem = smem + Q_BYTES + STAGES * STAGE_BYTES;
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + BAR_OFFSET);
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 8);
-  const uint32_t q_full = smem_addr(bars + 0), kv_full0 = smem_addr(bars + 1);
-  const uint32_t kv_empty0 = smem_addr(bars + 3), s_ready = smem_addr(bars + 5);
-  const uint32_t p_ready = smem_addr(bars + 6), o_ready = smem_addr(bars + 7);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 15);
+  const uint32_t q_full = smem_addr(bars + 0), kv_full0 = smem_addr(bars + 1);      // [STAGES]
+  const uint32_t kv_empty0 = smem_addr(bars + 1 + STAGES);                            // [STAGES]
+  const uint32_t s_ready0 = smem_addr(bars + 9), p_ready0 = smem_addr(bars + 11);    // [2] each
+  const uint32_t pv_done = smem_addr(bars + 13), o_ready = smem_addr(bars + 14);
+  static_assert(1 + 2 * STAGES <= 9, "barrier slots");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -90,8 +94,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       mbar_init(kv_full0 + 8 * s, 1);
       mbar_init(kv_empty0 + 8 * s, 1);
     }
-    mbar_init(s_ready, 1);
-    mbar_init(p_ready, BM);
+    for (int j = 0; j < 2; ++j) {
+      mbar_init(s_ready0 + 8 * j, 1);
+      mbar_init(p_ready0 + 8 * j, BM);
+    }
+    mbar_init(pv_done, 1);
     mbar_init(o_ready, 1);
     mbar_init_fence();
   }
@@ -140,27 +147,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       constexpr uint32_t idesc_pv = instr_desc(BM, HD, true);
       bool ok = mbar_wait(q_full, 0);
       if (!ok) atomicExch(status, ST_MMA);
-      for (int i = 0; i < n_pages && ok; ++i) {
+      // S of page i into S buffer i % 2 (needs K of stage i % STAGES)
+      auto issue_s = [&](int i) -> bool {
         const int s = i % STAGES;
-        if (!mbar_wait(kv_full0 + 8 * s, (i / STAGES) & 1)) { atomicExch(status, ST_MMA); break; }
+        if (!mbar_wait(kv_full0 + 8 * s, (i / STAGES) & 1)) { atomicExch(status, ST_MMA); return false; }
         tc_fence_after();
-        const uint32_t k_addr = smem_addr(kv_smem + s * STAGE_BYTES), v_addr = k_addr + KV_BYTES;
-        // S = Q K^T: the head dimension is the K index, 16 per MMA, 64 per box
+        const uint32_t k_addr = smem_addr(kv_smem + s * STAGE_BYTES);
 #pragma unroll
         for (int sub = 0; sub < SUBS; ++sub)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem, desc_k_major(smem_addr(q_smem + sub * Q_SUB_BYTES)) + 2 * k,
+            umma_bf16(tmem + 64 * (i & 1), desc_k_major(smem_addr(q_smem + sub * Q_SUB_BYTES)) + 2 * k,
                       desc_k_major(k_addr + sub * KV_SUB_BYTES) + 2 * k, idesc_s, (sub | k) != 0);
-        umma_commit(s_ready);
-        if (!mbar_wait(p_ready, i & 1)) { atomicExch(status, ST_MMA); break; }
+        umma_commit(s_ready0 + 8 * (i & 1));
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      if (ok && n_pages > 1) ok = issue_s(1);
+      for (int i = 0; i < n_pages && ok; ++i) {
+        const int s = i % STAGES;
+        if (!mbar_wait(p_ready0 + 8 * (i & 1), (i >> 1) & 1)) { atomicExch(status, ST_MMA); break; }
         tc_fence_after();
-        // O += P V: the keys are the K index, 16 per MMA = 16 rows of 128 bytes of the V boxes
+        // O += P V: the keys are the K index, 16 per MMA: 8 packed columns of P, 16 rows of V
+        const uint32_t v_addr = smem_addr(kv_smem + s * STAGE_BYTES) + KV_BYTES;
 #pragma unroll
         for (int k = 0; k < PAGE / 16; ++k)
-          umma_bf16(tmem + O_COL0, desc_k_major(smem_addr(p_smem)) + 2 * k,
-                    desc_mn_major(v_addr + k * 16 * 128, KV_SUB_BYTES), idesc_pv, (i | k) != 0);
+          umma_bf16_ts(tmem + O_COL0, tmem + 64 * (i & 1) + 8 * k,
+                       desc_mn_major(v_addr + k * 16 * 128, KV_SUB_BYTES), idesc_pv, (i | k) != 0);
         umma_commit(kv_empty0 + 8 * s);            // K and V of this stage have been read
+        umma_commit(pv_done);                      // O holds pages 0..i; P of page i has been read
+        if (i + 2 < n_pages) ok = issue_s(i + 2);  // overwrites the S/P buffer of page i (in order)
       }
       umma_commit(o_ready);
     }
@@ -173,29 +189,45 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int i = 0; i < n_pages && ok; ++i) {
-      if (!mbar_wait(s_ready, i & 1)) {
+      const uint32_t sbuf = lane_base + 64 * (i & 1);
+      if (!mbar_wait(s_ready0 + 8 * (i & 1), (i >> 1) & 1)) {
         if (lane == 0) atomicExch(status, ST_SOFTMAX);
         ok = false;
         break;
       }
       tc_fence_after();
       uint32_t sr[2][32];
-      tmem_ld32(lane_base, sr[0]);
-      tmem_ld32(lane_base + 32, sr[1]);
+      tmem_ld32(sbuf, sr[0]);
+      tmem_ld32(sbuf + 32, sr[1]);
       tmem_ld_wait();
       const int key0 = (first_page + i) * PAGE;
+      // raw scores stay in sr; the scale (> 0) is applied to the maximum and inside the exponent.
+      // Only pages that cross this row's limits are masked (warp-uniform test on the warp's rows).
+      const int warp_pos_min = pos0 + warp * 32, warp_pos_max = warp_pos_min + 31;
+      const bool partial = key0 + PAGE - 1 > warp_pos_min ||
+                           (window > 0 && key0 < max(0, warp_pos_max - window + 1));
       float mx = -INFINITY;
+      if (partial) {
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const int key = key0 + c;
-        float v = __uint_as_float(sr[c >> 5][c & 31]) * scale_log2;
-        if (key > pos_r || key < lo_r) v = -INFINITY;
-        sr[c >> 5][c & 31] = __float_as_uint(v);
-        mx = fmaxf(mx, v);
+        for (int c = 0; c < 64; ++c) {
+          const int key = key0 + c;
+          if (key > pos_r || key < lo_r) sr[c >> 5][c & 31] = 0xff800000u;      // -inf
+          mx = fmaxf(mx, __uint_as_float(sr[c >> 5][c & 31]));
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c >> 5][c & 31]));
       }
-      // s_ready(i) also means that P.V of page i-1 has completed: P may be overwritten, O is stable
+      mx *= scale_log2;                            // -inf stays -inf
       const bool grow = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
       if (i > 0 && __any_sync(0xffffffffu, grow)) {
+        // O must hold pages 0..i-1 completely before it is rescaled
+        if (!mbar_wait(pv_done, (i - 1) & 1)) {
+          if (lane == 0) atomicExch(status, ST_SOFTMAX);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
         const float f = grow ? ex2(m_ref - mx) : 1.f;      // 0 for a row that had seen no key
 #pragma unroll 1
         for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -210,25 +242,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         l *= f;
       }
       if (grow) m_ref = mx;
-      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      unsigned char *prow = p_smem + r * 128;
+      const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
+      uint32_t pk[32];
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        float p[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int c = 8 * ch + j;
-          p[j] = ex2(__uint_as_float(sr[c >> 5][c & 31]) - m_use);
-          l += p[j];
-        }
-        uint4 v;
-        v.x = pack2(p[0], p[1]); v.y = pack2(p[2], p[3]);
-        v.z = pack2(p[4], p[5]); v.w = pack2(p[6], p[7]);
-        *reinterpret_cast<uint4 *>(prow + ((ch ^ (r & 7)) << 4)) = v;
+      for (int c = 0; c < 64; c += 2) {
+        const float p0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), scale_log2, neg_m));
+        const float p1 = ex2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), scale_log2, neg_m));
+        l += p0 + p1;
+        pk[c >> 1] = pack2(p0, p1);
       }
-      fence_async_shared();
+      tmem_st32(sbuf, pk);                         // P over the first 32 columns of this S buffer
+      tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(p_ready);
+      mbar_arrive(p_ready0 + 8 * (i & 1));
     }
     if (ok) {
       if (!mbar_wait(o_ready, 0)) {
