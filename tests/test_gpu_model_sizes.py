@@ -1,0 +1,52 @@
+"""The engine at the layer sizes of the benchmark configurations (Qwen3-0.6B, 8B, 14B) with
+few layers, against the plain implementation: an unequal batch of prompts in one step, then
+a few single-token steps.  The 0.6B case keeps the real vocabulary (151,936, tied); the two
+larger ones use a small vocabulary so that the files stay small (the vocabulary is not a
+layer size)."""
+import numpy as np
+import pytest
+
+from helpers import assert_close, tmp_root
+from plain import qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+
+SIZES = {
+    "0.6b": dict(hidden_size=1024, intermediate_size=3072, num_hidden_layers=2, num_attention_heads=16,
+                 num_key_value_heads=8, head_dim=128, vocab_size=151936, tie_word_embeddings=True),
+    "8b": dict(hidden_size=4096, intermediate_size=12288, num_hidden_layers=1, num_attention_heads=32,
+               num_key_value_heads=8, head_dim=128, vocab_size=1000, tie_word_embeddings=False),
+    "14b": dict(hidden_size=5120, intermediate_size=17408, num_hidden_layers=1, num_attention_heads=40,
+                num_key_value_heads=8, head_dim=128, vocab_size=1000, tie_word_embeddings=False),
+}
+
+
+@pytest.mark.parametrize("name,dtype", [("0.6b", "bfloat16"), ("0.6b", "float32"), ("8b", "bfloat16"),
+                                        ("14b", "bfloat16")])
+def test_layer_sizes(name, dtype):
+    from gguf2bin_b200.engine import Engine, Model, StepEntry
+    from gguf2bin_b200.weights import write_random_model
+    cfg = dict(architectures=["Qwen3ForCausalLM"], rope_theta=1e6, rms_norm_eps=1e-6,
+               max_position_embeddings=40960, **SIZES[name])
+    folder = write_random_model(tmp_root() / f"sizes_{name}", cfg, seed=11, dtype="bfloat16")
+    pcfg, W = P.read_model_folder(folder)
+    rng = np.random.default_rng(5)
+    reqs = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (70, 9, 133)]
+    n_dec = 3
+    eng = Engine(Model.from_folder(folder, dtype=dtype), max_tokens=1024)
+    seqs = [eng.open_sequence() for _ in reqs]
+    heads = [len(t) - n_dec for t in reqs]
+    got = [[] for _ in reqs]
+    out = eng.step([StepEntry(s, t[:h], [h - 2, h - 1]) for s, t, h in zip(seqs, reqs, heads)]).cpu().numpy()
+    for j in range(len(reqs)):
+        got[j].append(out[2 * j:2 * j + 2])
+    for d in range(n_dec):
+        out = eng.step([StepEntry(s, [t[h + d]], [0]) for s, t, h in zip(seqs, reqs, heads)]).cpu().numpy()
+        for j in range(len(reqs)):
+            got[j].append(out[j:j + 1])
+    for j, toks in enumerate(reqs):
+        ref = P.forward(pcfg, W, toks, np.float32)[heads[j] - 2:]
+        assert_close(np.concatenate(got[j]), ref, dtype, f"{name}/{dtype} request {j}")
+    if dtype == "bfloat16":
+        from gguf2bin_b200 import kernels_bf16
+        kernels_bf16.check_status()
