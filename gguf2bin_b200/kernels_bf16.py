@@ -83,13 +83,34 @@ def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate:
         epi = EPI_ACCUM_F32
     else:
         epi = EPI_STORE_BF16 if out.dtype == torch.bfloat16 else EPI_STORE_F32
-    if _small_ok(a, w):
+    choice = _pick_product(a, w)
+    if choice == "small":
         _gemm_small(a, w, out, epi)
         return True
-    if _tc_ok(a, w):
-        _gemm_tc(a, w, out, epi)
+    if choice == "tc":
+        _gemm_tc(a, w, out, epi, *_tc_shape(a.shape[0], w.shape[0]))
         return True
     return False
+
+
+def _pick_product(a: torch.Tensor, w: torch.Tensor):
+    """Which kernel multiplies: the weight-streaming one up to 16 rows (every 16-row tile of
+    W re-stages all rows of a, which stops paying beyond that) and for narrow outputs up to
+    64 rows; the tcgen05 one otherwise."""
+    M, N = a.shape[0], w.shape[0]
+    small, tc_ = _small_ok(a, w), _tc_ok(a, w)
+    if small and (M <= 16 or (N < 2048 and M <= SMALL_M) or not tc_):
+        return "small"
+    if tc_:
+        return "tc"
+    return None
+
+
+def _tc_shape(M: int, N: int):
+    """(tile width, stages) of the tcgen05 product; (0, 0) lets the launcher choose."""
+    if M <= 128:                       # one row of tiles: the weights stream, as in decode
+        return (128, 3) if N >= 32768 else (64, 8)
+    return (0, 0)
 
 
 def linear_normed_bf16(x32, norm_w, eps, rows, w, out, epi=None) -> bool:
@@ -123,11 +144,12 @@ def gate_up_bf16(h: torch.Tensor, w_gate_up: torch.Tensor, mid: torch.Tensor, bl
     matrices whose rows alternate 8 gates / 8 ups."""
     if block != 8 or mid.dtype != torch.bfloat16 or mid.stride(1) != 1 or w_gate_up.shape[0] % 16:
         return False
-    if _small_ok(h, w_gate_up):
+    choice = _pick_product(h, w_gate_up)
+    if choice == "small":
         _gemm_small(h, w_gate_up, mid, EPI_SWIGLU_BF16)
         return True
-    if _tc_ok(h, w_gate_up):
-        _gemm_tc(h, w_gate_up, mid, EPI_SWIGLU_BF16)
+    if choice == "tc":
+        _gemm_tc(h, w_gate_up, mid, EPI_SWIGLU_BF16, *_tc_shape(h.shape[0], w_gate_up.shape[0]))
         return True
     return False
 
