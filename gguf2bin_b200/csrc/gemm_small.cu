@@ -28,6 +28,8 @@
 #include "common.cuh"
 #include "mma.cuh"
 
+#include <cooperative_groups.h>
+
 G2B_DEFINE_LAST_ERROR
 
 constexpr int WARPS = 8;
@@ -163,38 +165,45 @@ gemm_small_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W, void *
 }
 
 
-// K blocks of W in flight per thread (whole-A kernel): 4 when K has at most four blocks, else
-// 8; the shallower ring frees registers, so that three blocks instead of two fit an SM
-
+// K blocks of W in flight per thread (whole-A kernel): 4 when a CTA has at most four blocks of
+// K, else 8; the shallower ring frees registers, so that three blocks instead of two fit an SM.
+//
 // NORM: A is the float32 stream x[rows_or_identity[m], :] and is normalised while staged.
-// A CTA takes `tiles_per_cta` consecutive 16-row tiles of W: the activations are staged
-// once, and the weight stream runs on across the tiles while a tile's sums are reduced.
-template <int MT, int EPI, bool NORM, int DEPTH_WHOLE>
+// SPLIT > 1: a thread-block cluster of SPLIT CTAs shares one 16-row tile of W, each taking a
+// contiguous slice of K (its part of the activations and of the weights); the CTAs leave
+// their partial tiles in their own shared memory and the first CTA of the cluster adds them
+// in rank order through distributed shared memory.  Narrow outputs (N = 1024 means only 64
+// tiles) fill the GPU this way, and the order of the sum still depends on K and N only.
+template <int MT, int EPI, bool NORM, int DEPTH_WHOLE, int SPLIT>
 __global__ void __launch_bounds__(WARPS * 32, DEPTH_WHOLE == 4 ? 3 : 2)
 gemm_small_whole_kernel(const void *__restrict__ Av, const float *__restrict__ norm_w, float eps,
                         const int *__restrict__ rows, const bf16 *__restrict__ W,
-                        void *__restrict__ Cv, int M, int N, int K, int lda, int ldw, int ldc,
-                        int tiles_per_cta) {
+                        void *__restrict__ Cv, int M, int N, int K, int lda, int ldw, int ldc) {
   pdl_launch();
   constexpr int MROWS = MT * 8;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
-  const int nkb = (K + KB - 1) / KB;
-  const int xrow = nkb * KB + XPAD;                       // staged row length (zero padded)
+  const int nkb_all = (K + KB - 1) / KB;
+  const int rank = SPLIT > 1 ? (int)(blockIdx.x % SPLIT) : 0;
+  const int per = (nkb_all + SPLIT - 1) / SPLIT;
+  const int kb_lo = rank * per, kb_hi = min(nkb_all, kb_lo + per);
+  const int nkb = max(0, kb_hi - kb_lo);                  // K blocks of this CTA
+  const int k_lo = kb_lo * KB;                            // first k of this CTA
+  const int xrow = per * KB + XPAD;                       // staged row length (zero padded)
   bf16 *xs = reinterpret_cast<bf16 *>(smem_raw);          // [MROWS][xrow]
   float *red = reinterpret_cast<float *>(smem_raw + (((size_t)MROWS * xrow * sizeof(bf16)) + 127) / 128 * 128);
+  float *part = red + WARPS * 16 * MROWS;                 // [16][MROWS]: this CTA's partial tile
 
-  const int n_tiles = (N + 15) / 16;
-  const int tile0 = blockIdx.x * tiles_per_cta;
-  const int my_tiles = min(tiles_per_cta, n_tiles - tile0);
-  const int total = my_tiles * nkb;                       // (tile, K block) pairs of this CTA
+  const int n0 = (int)(blockIdx.x / SPLIT) * 16;
+  const bf16 *w0 = W + (size_t)min(n0 + g, N - 1) * ldw;
+  const bf16 *w1 = W + (size_t)min(n0 + g + 8, N - 1) * ldw;
   const int kw = 32 * warp + 8 * c;
-  auto load_w = [&](uint4 (&dst)[2], int it) {
-    const int n0 = (tile0 + it / nkb) * 16, k = (it % nkb) * KB + kw;
+  auto load_w = [&](uint4 (&dst)[2], int kb) {            // kb counts from this CTA's first block
+    const int k = k_lo + kb * KB + kw;
     if (k < K) {
-      dst[0] = ld_stream(W + (size_t)min(n0 + g, N - 1) * ldw + k);
-      dst[1] = ld_stream(W + (size_t)min(n0 + g + 8, N - 1) * ldw + k);
+      dst[0] = ld_stream(w0 + k);
+      dst[1] = ld_stream(w1 + k);
     } else {
       dst[0] = dst[1] = make_uint4(0, 0, 0, 0);
     }
@@ -203,17 +212,18 @@ gemm_small_whole_kernel(const void *__restrict__ Av, const float *__restrict__ n
   uint4 wb[DEPTH_WHOLE][2];
 #pragma unroll
   for (int d = 0; d < DEPTH_WHOLE; ++d)
-    if (d < total) load_w(wb[d], d);
+    if (d < nkb) load_w(wb[d], d);
   pdl_wait();                            // the activations come from the kernel before
 
-  // stage A (normalised if NORM): one warp per row, many loads in flight per lane
+  // stage this CTA's columns of A (normalised if NORM): one warp per row, many loads in flight
+  const int k_hi = min(K, k_lo + nkb * KB);               // one past this CTA's last k
   for (int r = warp; r < MROWS; r += WARPS) {
     bf16 *dst = xs + (size_t)r * xrow;
     if (r >= M) {
       for (int k = lane * 8; k < xrow; k += 256) *reinterpret_cast<uint4 *>(dst + k) = make_uint4(0, 0, 0, 0);
       continue;
     }
-    if (NORM) {
+    if (NORM) {                                           // SPLIT == 1: the whole row is here
       const float *x = (const float *)Av + (size_t)(rows ? rows[r] : r) * lda;
       float ss = 0.f;
       for (int k0 = lane * 4; k0 < K; k0 += 128 * 8) {
@@ -253,10 +263,10 @@ gemm_small_whole_kernel(const void *__restrict__ Av, const float *__restrict__ n
         }
       }
     } else {
-      const bf16 *x = (const bf16 *)Av + (size_t)r * lda;
-      for (int k = lane * 8; k < K; k += 256) cp_async_16(smem_u32(dst + k), x + k);
+      const bf16 *x = (const bf16 *)Av + (size_t)r * lda + k_lo;
+      for (int k = lane * 8; k < k_hi - k_lo; k += 256) cp_async_16(smem_u32(dst + k), x + k);
     }
-    for (int k = K + lane * 4; k < xrow; k += 128) *reinterpret_cast<uint2 *>(dst + k) = make_uint2(0, 0);
+    for (int k = max(0, k_hi - k_lo) + lane * 4; k < xrow; k += 128) *reinterpret_cast<uint2 *>(dst + k) = make_uint2(0, 0);
   }
   cp_async_commit();
   cp_async_wait<0>();
@@ -265,12 +275,11 @@ gemm_small_whole_kernel(const void *__restrict__ Av, const float *__restrict__ n
   float acc[MT][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
-  int kb = 0, tile = 0;                  // position of iteration `it` inside the CTA's work
-  for (int it0 = 0; it0 < total; it0 += DEPTH_WHOLE) {
+  for (int kb0 = 0; kb0 < nkb; kb0 += DEPTH_WHOLE) {
 #pragma unroll
     for (int d = 0; d < DEPTH_WHOLE; ++d) {
-      const int it = it0 + d;
-      if (it < total) {
+      const int kb = kb0 + d;
+      if (kb < nkb) {
         const bf16 *xb = xs + kb * KB + 32 * warp + 8 * c;
         const uint4 a_lo = wb[d][0], a_hi = wb[d][1];
         const uint32_t a1[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};
@@ -281,87 +290,117 @@ gemm_small_whole_kernel(const void *__restrict__ Av, const float *__restrict__ n
           mma_bf16_16816(acc[mt], a1, xv.x, xv.y);
           mma_bf16_16816(acc[mt], a2, xv.z, xv.w);
         }
-        if (it + DEPTH_WHOLE < total) load_w(wb[d], it + DEPTH_WHOLE);
-        if (++kb == nkb) {
-          // this tile is complete: add the 8 warps' partial sums in warp order, write it out
-          kb = 0;
-          const int n0 = (tile0 + tile) * 16;
-          ++tile;
+        if (kb + DEPTH_WHOLE < nkb) load_w(wb[d], kb + DEPTH_WHOLE);
+      }
+    }
+  }
+  // the 8 warps' partial sums -> shared memory, added in warp order
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            float *r0 = red + ((size_t)warp * 16 + g) * MROWS + 8 * mt + 2 * c;
-            float *r1 = r0 + 8 * MROWS;
-            r0[0] = acc[mt][0]; r0[1] = acc[mt][1];
-            r1[0] = acc[mt][2]; r1[1] = acc[mt][3];
-            acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
-          }
-          __syncthreads();
-          if (EPI == EPI_SWIGLU_BF16) {
-            for (int i = threadIdx.x; i < 8 * MROWS; i += WARPS * 32) {
-              const int m = i / 8, r = i % 8;
-              float gate = 0.f, up = 0.f;
+  for (int mt = 0; mt < MT; ++mt) {
+    float *r0 = red + ((size_t)warp * 16 + g) * MROWS + 8 * mt + 2 * c;
+    float *r1 = r0 + 8 * MROWS;
+    r0[0] = acc[mt][0]; r0[1] = acc[mt][1];
+    r1[0] = acc[mt][2]; r1[1] = acc[mt][3];
+  }
+  __syncthreads();
+  if (SPLIT > 1) {
+    // every CTA reduces its own warps; the first CTA of the cluster then adds the CTAs in order
+    for (int i = threadIdx.x; i < 16 * MROWS; i += WARPS * 32) {
+      float v = 0.f;
 #pragma unroll
-              for (int w = 0; w < WARPS; ++w) {
-                gate += red[((size_t)w * 16 + r) * MROWS + m];
-                up += red[((size_t)w * 16 + 8 + r) * MROWS + m];
-              }
-              const int col = (n0 >> 1) + r;
-              if (m < M && n0 + 8 + r < N)
-                ((bf16 *)Cv)[(size_t)m * ldc + col] =
-                    __float2bfloat16_rn((gate / (1.f + expf(-gate))) * up);
-            }
-          } else {
-            for (int i = threadIdx.x; i < 16 * MROWS; i += WARPS * 32) {
-              const int m = i / 16, r = i % 16;
-              float v = 0.f;
+      for (int w = 0; w < WARPS; ++w) v += red[(size_t)w * 16 * MROWS + i];
+      part[i] = v;
+    }
+    cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
+    cluster.sync();
+    if (rank == 0) {
+      for (int i = threadIdx.x; i < 16 * MROWS; i += WARPS * 32) {
+        float v = part[i];
 #pragma unroll
-              for (int w = 0; w < WARPS; ++w) v += red[((size_t)w * 16 + r) * MROWS + m];
-              const int n = n0 + r;
-              if (m < M && n < N) {
-                const size_t o = (size_t)m * ldc + n;
-                if (EPI == EPI_STORE_BF16) ((bf16 *)Cv)[o] = __float2bfloat16_rn(v);
-                else if (EPI == EPI_STORE_F32) ((float *)Cv)[o] = v;
-                else atomicAdd((float *)Cv + o, v);   // a reduction: one add per element and launch, no load on the path
-              }
-            }
-          }
-          __syncthreads();               // the sums' buffer is free for the next tile
-        }
+        for (int r = 1; r < SPLIT; ++r) v += cluster.map_shared_rank(part, r)[i];
+        red[i] = v;                                   // the tile, as warp 0's partial; the others zero
+#pragma unroll
+        for (int w = 1; w < WARPS; ++w) red[(size_t)w * 16 * MROWS + i] = 0.f;
+      }
+    }
+    cluster.sync();                                   // peers' memory stays alive until it was read
+    if (rank != 0) return;
+    __syncthreads();
+  }
+  if (EPI == EPI_SWIGLU_BF16) {
+    for (int i = threadIdx.x; i < 8 * MROWS; i += WARPS * 32) {
+      const int m = i / 8, r = i % 8;
+      float gate = 0.f, up = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        gate += red[((size_t)w * 16 + r) * MROWS + m];
+        up += red[((size_t)w * 16 + 8 + r) * MROWS + m];
+      }
+      const int col = (n0 >> 1) + r;
+      if (m < M && n0 + 8 + r < N)
+        ((bf16 *)Cv)[(size_t)m * ldc + col] = __float2bfloat16_rn((gate / (1.f + expf(-gate))) * up);
+    }
+  } else {
+    for (int i = threadIdx.x; i < 16 * MROWS; i += WARPS * 32) {
+      const int m = i / 16, r = i % 16;
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) v += red[((size_t)w * 16 + r) * MROWS + m];
+      const int n = n0 + r;
+      if (m < M && n < N) {
+        const size_t o = (size_t)m * ldc + n;
+        if (EPI == EPI_STORE_BF16) ((bf16 *)Cv)[o] = __float2bfloat16_rn(v);
+        else if (EPI == EPI_STORE_F32) ((float *)Cv)[o] = v;
+        else atomicAdd((float *)Cv + o, v);   // a reduction: one add per element and launch, no load on the path
       }
     }
   }
 }
 
 // shared memory the whole-A kernel needs, or 0 if the case does not fit
-static size_t whole_smem(int mrows, int K) {
-  const int nkb = (K + KB - 1) / KB;
-  const size_t stage = ((size_t)mrows * (nkb * KB + XPAD) * sizeof(bf16) + 127) / 128 * 128;
-  const size_t red = (size_t)WARPS * 16 * mrows * sizeof(float);
+static size_t whole_smem(int mrows, int K, int split = 1) {
+  const int nkb = (K + KB - 1) / KB, per = (nkb + split - 1) / split;
+  const size_t stage = ((size_t)mrows * (per * KB + XPAD) * sizeof(bf16) + 127) / 128 * 128;
+  const size_t red = (size_t)(WARPS + 1) * 16 * mrows * sizeof(float);
   const size_t need = stage + red;
   return need <= 200 * 1024 ? need : 0;
 }
 
-template <int MT, bool NORM, int DEPTH_WHOLE>
+// CTAs per 16-row tile: narrow outputs with a long K are split over a cluster
+static int pick_split(int N, int K) {
+  const int n_tiles = (N + 15) / 16, nkb = (K + KB - 1) / KB;
+  if (n_tiles <= 96 && nkb >= 12) return 4;      // measured: K = 2048 is faster unsplit, K = 3072 split
+  if (n_tiles <= 160 && nkb >= 10) return 2;
+  return 1;
+}
+
+// the split that is built for the case: a CTA of a split product keeps at most 4 blocks of K
+static int final_split(int N, int K) {
+  const int nkb = (K + KB - 1) / KB, s = pick_split(N, K);
+  if (s == 4 && (nkb + 3) / 4 <= 4) return 4;
+  if (s >= 2 && (nkb + 1) / 2 <= 4) return 2;
+  return 1;
+}
+
+template <int MT, bool NORM, int DEPTH_WHOLE, int SPLIT>
 static int launch_whole_depth(const void *A, const float *norm_w, float eps, const int *rows,
-                        const void *W, void *C, int M, int N, int K, int lda, int ldw, int ldc,
-                        int epi, cudaStream_t stream) {
-  const int smem = (int)whole_smem(MT * 8, K);
-  // one tile per CTA measured fastest at every width tried (with more, the reduction of a
-  // tile stalls the weight stream of the next); the loop over tiles stays for experiments
+                              const void *W, void *C, int M, int N, int K, int lda, int ldw,
+                              int ldc, int epi, cudaStream_t stream) {
+  const int smem = (int)whole_smem(MT * 8, K, SPLIT);
   const int n_tiles = (N + 15) / 16;
-  const int tiles_per_cta = 1;
-  const unsigned grid = (unsigned)((n_tiles + tiles_per_cta - 1) / tiles_per_cta);
+  const unsigned grid = (unsigned)(n_tiles * SPLIT);
 #define G2B_LAUNCH(E)                                                                            \
   do {                                                                                           \
     static int configured = 0;                                                                   \
     if (configured < smem) {                                                                     \
-      cudaError_t e = cudaFuncSetAttribute(gemm_small_whole_kernel<MT, E, NORM, DEPTH_WHOLE>,                 \
+      cudaError_t e = cudaFuncSetAttribute(gemm_small_whole_kernel<MT, E, NORM, DEPTH_WHOLE, SPLIT>, \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem);   \
       if (e != cudaSuccess) G2B_REFUSE("gemm_small: shared memory: %s", cudaGetErrorString(e));  \
       configured = smem;                                                                         \
     }                                                                                            \
-    g2b_launch(gemm_small_whole_kernel<MT, E, NORM, DEPTH_WHOLE>, dim3(grid), dim3(WARPS * 32), smem, stream,                     \
-        A, norm_w, eps, rows, (const bf16 *)W, C, M, N, K, lda, ldw, ldc, tiles_per_cta);        \
+    g2b_launch_cluster(gemm_small_whole_kernel<MT, E, NORM, DEPTH_WHOLE, SPLIT>, dim3(grid),     \
+                       dim3(WARPS * 32), smem, stream, (unsigned)SPLIT, A, norm_w, eps, rows,    \
+                       (const bf16 *)W, C, M, N, K, lda, ldw, ldc);                              \
   } while (0)
   switch (epi) {
     case EPI_STORE_BF16: G2B_LAUNCH(EPI_STORE_BF16); break;
@@ -372,6 +411,21 @@ static int launch_whole_depth(const void *A, const float *norm_w, float eps, con
   }
 #undef G2B_LAUNCH
   return g2b_check_launch("gemm_small_whole");
+}
+
+template <int MT, bool NORM>
+static int launch_whole(const void *A, const float *norm_w, float eps, const int *rows,
+                        const void *W, void *C, int M, int N, int K, int lda, int ldw, int ldc,
+                        int epi, cudaStream_t stream) {
+  const int nkb = (K + KB - 1) / KB;
+  const int split = NORM ? 1 : final_split(N, K);
+  if (split == 4)
+    return launch_whole_depth<MT, false, 4, 4>(A, norm_w, eps, rows, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+  if (split == 2)
+    return launch_whole_depth<MT, false, 4, 2>(A, norm_w, eps, rows, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+  if (nkb <= 4)
+    return launch_whole_depth<MT, NORM, 4, 1>(A, norm_w, eps, rows, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+  return launch_whole_depth<MT, NORM, 8, 1>(A, norm_w, eps, rows, W, C, M, N, K, lda, ldw, ldc, epi, stream);
 }
 
 template <int MT>
@@ -405,15 +459,6 @@ static int launch_mt(const void *A, const void *W, void *C, int M, int N, int K,
   return g2b_check_launch("gemm_small");
 }
 
-template <int MT, bool NORM>
-static int launch_whole(const void *A, const float *norm_w, float eps, const int *rows,
-                        const void *W, void *C, int M, int N, int K, int lda, int ldw, int ldc,
-                        int epi, cudaStream_t stream) {
-  if ((K + KB - 1) / KB <= 4)
-    return launch_whole_depth<MT, NORM, 4>(A, norm_w, eps, rows, W, C, M, N, K, lda, ldw, ldc, epi, stream);
-  return launch_whole_depth<MT, NORM, 8>(A, norm_w, eps, rows, W, C, M, N, K, lda, ldw, ldc, epi, stream);
-}
-
 // A [M,K] and W [N,K] bfloat16 with unit inner stride; rows 16-byte aligned.
 // epi: 0 store bfloat16, 1 store float, 2 add into float, 3 SiLU gate (C is [M, N/2] bfloat16;
 // N must be a multiple of 16).
@@ -426,7 +471,7 @@ extern "C" int g2b_gemm_small(const void *A, const void *W, void *C, int M, int 
   if (((uintptr_t)A | (uintptr_t)W) & 15) G2B_REFUSE("gemm_small: operands must be 16-byte aligned");
   if (epi == EPI_SWIGLU_BF16 && N % 16) G2B_REFUSE("gemm_small: gated output needs N %% 16 == 0, N=%d", N);
   const int mrows = M <= 8 ? 8 : (M <= 16 ? 16 : (M <= 32 ? 32 : 64));
-  if (whole_smem(mrows, K)) {
+  if (whole_smem(mrows, K, final_split(N, K))) {
     if (M <= 8) return launch_whole<1, false>(A, nullptr, 0.f, nullptr, W, C, M, N, K, lda, ldw, ldc, epi, stream);
     if (M <= 16) return launch_whole<2, false>(A, nullptr, 0.f, nullptr, W, C, M, N, K, lda, ldw, ldc, epi, stream);
     if (M <= 32) return launch_whole<4, false>(A, nullptr, 0.f, nullptr, W, C, M, N, K, lda, ldw, ldc, epi, stream);
