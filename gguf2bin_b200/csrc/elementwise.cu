@@ -145,8 +145,8 @@ extern "C" int g2b_rmsnorm(const float *x, const float *w, const int *rows, int 
 // ---------------------------------------------------------------------------
 // per-head norm + rotation + cache write.  One warp per (token, head) of the fused
 // projection output qkv[t] = [q heads | k heads | v heads].
-//   q heads: norm (if q_w), rotate (if inv_freq)  -> q_out[t, h*hd + j]
-//   k heads: norm (if k_w), rotate (if inv_freq)  -> cache K, or k_out when given
+//   q heads: norm (if q_w), rotate (if a table is given)  -> q_out[t, h*hd + j]
+//   k heads: norm (if k_w), rotate (if a table is given)  -> cache K, or k_out when given
 //   v heads: copied                                -> cache V, or v_out when given
 // Cache of one layer: [n_pages][2][nkv][page_size][hd]; the page of position p of
 // sequence b is page_table[b*P + p/page_size].
@@ -154,94 +154,144 @@ extern "C" int g2b_rmsnorm(const float *x, const float *w, const int *rows, int 
 #define QKN_MAX_HD 512
 #define QKN_WARPS 4
 
-// Grid (token, split): the block's warps share the heads [split * heads_per_block, ...) of
-// one token, one head at a time per warp.  The sines and cosines of the token's position
-// are computed once per block into shared memory instead of once per head.
+// cos and sin of pos * inv_freq[j] for every token of the step, once per step: all layers
+// with the same frequencies read the same table.  table[t * half + j] = (cos, sin).
+__global__ void rope_table_kernel(const int *__restrict__ tok_pos, const float *__restrict__ inv_freq,
+                                  float2 *__restrict__ table, int T_tokens, int half) {
+  pdl_launch();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)T_tokens * half) return;
+  const int t = (int)(i / half), j = (int)(i % half);
+  float sn, c;
+  sincosf((float)tok_pos[t] * inv_freq[j], &sn, &c);
+  table[i] = make_float2(c, sn);
+}
+
+extern "C" int g2b_rope_table(const int *tok_pos, const float *inv_freq, float *table, int T_tokens,
+                              int half, cudaStream_t stream) {
+  if (T_tokens <= 0 || half <= 0) return 0;
+  const long long n = (long long)T_tokens * half;
+  g2b_launch(rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, tok_pos, inv_freq,
+             (float2 *)table, T_tokens, half);
+  return g2b_check_launch("rope_table");
+}
+
+__device__ __forceinline__ float2 ld2(const bf16 *p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p));
+}
+__device__ __forceinline__ float2 ld2(const float *p) { return *reinterpret_cast<const float2 *>(p); }
+__device__ __forceinline__ void st2(bf16 *p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162 *>(p) = __floats2bfloat162_rn(a, b);
+}
+__device__ __forceinline__ void st2(float *p, float a, float b) { *reinterpret_cast<float2 *>(p) = make_float2(a, b); }
+
+// One warp per QKN_HEADS consecutive heads of a token.  `rope` is the step's table for these
+// frequencies (or null).  Register path (head sizes that are multiples of 4 up to 256,
+// rotation over the whole head): a lane holds the elements (2l, 2l+1) of each half of the
+// head and their partners, loaded and stored two at a time; the loads of both heads are
+// issued before either is used.
+#define QKN_HEADS 2
+
 template <typename T>
-__global__ void qknorm_rope_cache_kernel(
+__global__ void __launch_bounds__(QKN_WARPS * 32)
+qknorm_rope_cache_kernel(
     const T *__restrict__ qkv, int T_tokens, int nh, int nkv, int hd,
     const float *__restrict__ q_w, const float *__restrict__ k_w, float eps,
-    const float *__restrict__ inv_freq, int rot_dim,
+    const float2 *__restrict__ rope, int rot_dim,
     const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
     const int *__restrict__ page_table, int P, T *__restrict__ cache, int page_size,
-    T *__restrict__ q_out, T *__restrict__ k_out, T *__restrict__ v_out, int heads_per_block) {
+    T *__restrict__ q_out, T *__restrict__ k_out, T *__restrict__ v_out) {
   pdl_launch();
   pdl_wait();
   __shared__ float buf[QKN_WARPS][QKN_MAX_HD];
-  __shared__ float cs[QKN_MAX_HD];                  // cos at [j], sin at [half + j]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = nh + 2 * nkv;
-  const int t = blockIdx.x;
-  const int pos = tok_pos[t];
+  const int groups = (heads + QKN_HEADS - 1) / QKN_HEADS;          // head groups per token
+  const long long item = (long long)blockIdx.x * QKN_WARPS + warp;
+  if (item >= (long long)T_tokens * groups) return;
+  const int t = (int)(item / groups), h0 = (int)(item % groups) * QKN_HEADS;
   const int half = rot_dim >> 1;
-  if (inv_freq) {
-    for (int j = threadIdx.x; j < half; j += blockDim.x) {
-      float sn, c;
-      sincosf((float)pos * inv_freq[j], &sn, &c);
-      cs[j] = c;
-      cs[half + j] = sn;
-    }
-  }
-  __syncthreads();
-  const int h_begin = blockIdx.y * heads_per_block;
-  const int h_end = min(heads, h_begin + heads_per_block);
+  const int pos = tok_pos[t];
   const int page = (cache && page_table) ? page_table[(size_t)tok_seq[t] * P + pos / page_size] : 0;
-  // register path: head sizes that are multiples of 4 up to 256, rotation (if any) over the
-  // whole head.  A lane holds the elements (2l, 2l+1) of each half and their partners.
-  const bool in_registers = (hd % 4 == 0) && hd <= 256 && (!inv_freq || rot_dim == hd);
-  float *x = buf[warp];
-  for (int h = h_begin + warp; h < h_end; h += QKN_WARPS) {
-    const T *src = qkv + (size_t)t * heads * hd + (size_t)h * hd;
-    const int kind = h < nh ? 0 : (h < nh + nkv ? 1 : 2);       // 0 q, 1 k, 2 v
-    const float *w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
-    T *dst;
-    if (kind == 0) {
-      dst = q_out + (size_t)t * nh * hd + (size_t)h * hd;
-    } else {
-      const int kvh = kind == 1 ? h - nh : h - nh - nkv;
-      T *flat = kind == 1 ? k_out : v_out;
-      if (flat) dst = flat + (size_t)t * nkv * hd + (size_t)kvh * hd;
-      else dst = cache + ((((size_t)page * 2 + (kind - 1)) * nkv + kvh) * page_size + pos % page_size) * hd;
+
+  auto kind_of = [&](int h) { return h < nh ? 0 : (h < nh + nkv ? 1 : 2); };   // 0 q, 1 k, 2 v
+  auto dst_of = [&](int h) -> T * {
+    const int kind = kind_of(h);
+    if (kind == 0) return q_out + (size_t)t * nh * hd + (size_t)h * hd;
+    const int kvh = kind == 1 ? h - nh : h - nh - nkv;
+    T *flat = kind == 1 ? k_out : v_out;
+    if (flat) return flat + (size_t)t * nkv * hd + (size_t)kvh * hd;
+    return cache + ((((size_t)page * 2 + (kind - 1)) * nkv + kvh) * page_size + pos % page_size) * hd;
+  };
+
+  if ((hd % 4 == 0) && hd <= 256 && (!rope || rot_dim == hd)) {
+    const int hh = hd >> 1;                        // first element of the second half
+    float2 a[QKN_HEADS][2], b[QKN_HEADS][2];
+#pragma unroll
+    for (int u = 0; u < QKN_HEADS; ++u) {
+      const T *src = qkv + (size_t)t * heads * hd + (size_t)min(h0 + u, heads - 1) * hd;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int j = 2 * lane + 64 * i;
+        if (j < hh) {
+          a[u][i] = ld2(src + j);
+          b[u][i] = ld2(src + hh + j);
+        } else {
+          a[u][i] = b[u][i] = make_float2(0.f, 0.f);
+        }
+      }
     }
-    if (in_registers) {
-      const int hh = hd >> 1;                      // first element of the second half
-      float a[2][2], b[2][2];
+#pragma unroll
+    for (int u = 0; u < QKN_HEADS; ++u) {
+      const int h = h0 + u;
+      if (h >= heads) break;
+      const int kind = kind_of(h);
+      const float *w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
+      const float2 *cs = (rope && kind != 2) ? rope + (size_t)t * half : nullptr;
       float ss = 0.f;
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
-        const int j = 2 * lane + 64 * i;
-        if (j < hh) {
-          a[i][0] = to_f32(src[j]); a[i][1] = to_f32(src[j + 1]);
-          b[i][0] = to_f32(src[hh + j]); b[i][1] = to_f32(src[hh + j + 1]);
-          ss = fmaf(a[i][0], a[i][0], ss); ss = fmaf(a[i][1], a[i][1], ss);
-          ss = fmaf(b[i][0], b[i][0], ss); ss = fmaf(b[i][1], b[i][1], ss);
-        }
+        ss = fmaf(a[u][i].x, a[u][i].x, ss); ss = fmaf(a[u][i].y, a[u][i].y, ss);
+        ss = fmaf(b[u][i].x, b[u][i].x, ss); ss = fmaf(b[u][i].y, b[u][i].y, ss);
       }
       ss = warp_sum(ss);
       const float inv = w ? 1.f / sqrtf(ss / (float)hd + eps) : 1.f;
+      T *dst = dst_of(h);
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         const int j = 2 * lane + 64 * i;
         if (j < hh) {
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            float av = a[i][e], bv = b[i][e];
-            if (w) {
-              av = (w[j + e] * av) * inv;
-              bv = (w[hh + j + e] * bv) * inv;
-            }
-            if (kind != 2 && inv_freq) {
-              const float c = cs[j + e], sn = cs[half + j + e];
-              const float ra = av * c - bv * sn, rb = av * sn + bv * c;
-              av = ra; bv = rb;
-            }
-            dst[j + e] = from_f32<T>(av);
-            dst[hh + j + e] = from_f32<T>(bv);
+          float2 av = a[u][i], bv = b[u][i];
+          if (w) {
+            const float2 wa = *reinterpret_cast<const float2 *>(w + j);
+            const float2 wb = *reinterpret_cast<const float2 *>(w + hh + j);
+            av.x = (wa.x * av.x) * inv; av.y = (wa.y * av.y) * inv;
+            bv.x = (wb.x * bv.x) * inv; bv.y = (wb.y * bv.y) * inv;
           }
+          if (cs) {
+            const float4 r = *reinterpret_cast<const float4 *>(cs + j);      // (cos, sin) of j and j+1
+            const float ax = av.x * r.x - bv.x * r.y, bx = av.x * r.y + bv.x * r.x;
+            const float ay = av.y * r.z - bv.y * r.w, by = av.y * r.w + bv.y * r.z;
+            av = make_float2(ax, ay);
+            bv = make_float2(bx, by);
+          }
+          st2(dst + j, av.x, av.y);
+          st2(dst + hh + j, bv.x, bv.y);
         }
       }
-      continue;
     }
+    return;
+  }
+  float *x = buf[warp];
+  for (int u = 0; u < QKN_HEADS; ++u) {
+    const int h = h0 + u;
+    if (h >= heads) break;
+    const T *src = qkv + (size_t)t * heads * hd + (size_t)h * hd;
+    const int kind = kind_of(h);
+    const float *w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
+    const float2 *cs = (rope && kind != 2) ? rope + (size_t)t * half : nullptr;
+    T *dst = dst_of(h);
     float ss = 0.f;
     for (int j = lane; j < hd; j += 32) {
       const float v = to_f32(src[j]);
@@ -255,51 +305,50 @@ __global__ void qknorm_rope_cache_kernel(
       for (int j = lane; j < hd; j += 32) x[j] = (w[j] * x[j]) * inv;
       __syncwarp();
     }
-    if (kind != 2 && inv_freq) {
+    if (cs) {
       for (int j = lane; j < half; j += 32) {
-        const float c = cs[j], sn = cs[half + j];
+        const float2 r = cs[j];
         const float av = x[j], bv = x[j + half];
-        x[j] = av * c - bv * sn;
-        x[j + half] = av * sn + bv * c;
+        x[j] = av * r.x - bv * r.y;
+        x[j + half] = av * r.y + bv * r.x;
       }
       __syncwarp();
     }
     for (int j = lane; j < hd; j += 32) dst[j] = from_f32<T>(x[j]);
-    __syncwarp();                                  // x is reused for the warp's next head
+    __syncwarp();                                  // x is reused for the next head
   }
 }
 
 extern "C" int g2b_qknorm_rope_cache(const void *qkv, int dtype, int T_tokens, int nh, int nkv,
                                      int hd, const float *q_w, const float *k_w, float eps,
-                                     const float *inv_freq, int rot_dim, const int *tok_pos,
+                                     const float *rope_table, int rot_dim, const int *tok_pos,
                                      const int *tok_seq, const int *page_table, int P,
                                      void *cache, int page_size, void *q_out, void *k_out,
                                      void *v_out, cudaStream_t stream) {
   if (T_tokens <= 0) return 0;
   if (hd <= 0 || hd > QKN_MAX_HD)
     G2B_REFUSE("qknorm_rope_cache: head_dim %d outside 1..%d", hd, QKN_MAX_HD);
-  if (inv_freq && (rot_dim <= 0 || rot_dim > hd || (rot_dim & 1)))
+  if (rope_table && (rot_dim <= 0 || rot_dim > hd || (rot_dim & 1)))
     G2B_REFUSE("qknorm_rope_cache: rotary_dim %d must be even and at most head_dim %d", rot_dim, hd);
   if ((k_out == nullptr) != (v_out == nullptr))
     G2B_REFUSE("qknorm_rope_cache: k_out and v_out must be given together");
   if (nkv > 0 && !k_out && (!cache || !page_table || page_size <= 0))
     G2B_REFUSE("qknorm_rope_cache: no cache to write to");
-  // few tokens: one head per warp (more blocks); many tokens: two heads per warp, so that the
-  // position's sines and cosines are shared by eight heads and a warp's chain stays short
-  const int heads = nh + 2 * nkv;
-  const int heads_per_block = T_tokens >= 256 ? 2 * QKN_WARPS : QKN_WARPS;
-  const dim3 blocks((unsigned)T_tokens, (unsigned)((heads + heads_per_block - 1) / heads_per_block));
-  if (blocks.y > 65535) G2B_REFUSE("qknorm_rope_cache: %d heads", heads);
+  const long long items = (long long)T_tokens * ((nh + 2 * nkv + QKN_HEADS - 1) / QKN_HEADS);
+  const unsigned blocks = (unsigned)((items + QKN_WARPS - 1) / QKN_WARPS);
+  if ((((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)k_out | (uintptr_t)v_out |
+        (uintptr_t)rope_table | (uintptr_t)q_w | (uintptr_t)k_w) & 15) != 0)
+    G2B_REFUSE("qknorm_rope_cache: tensors must be 16-byte aligned");
   if (dtype == G2B_F32)
-    g2b_launch(qknorm_rope_cache_kernel<float>, dim3(blocks), dim3(QKN_WARPS * 32), 0, stream, 
-        (const float *)qkv, T_tokens, nh, nkv, hd, q_w, k_w, eps, inv_freq, rot_dim, tok_pos,
-        tok_seq, page_table, P, (float *)cache, page_size, (float *)q_out, (float *)k_out,
-        (float *)v_out, heads_per_block);
+    g2b_launch(qknorm_rope_cache_kernel<float>, dim3(blocks), dim3(QKN_WARPS * 32), 0, stream,
+        (const float *)qkv, T_tokens, nh, nkv, hd, q_w, k_w, eps, (const float2 *)rope_table, rot_dim,
+        tok_pos, tok_seq, page_table, P, (float *)cache, page_size, (float *)q_out, (float *)k_out,
+        (float *)v_out);
   else if (dtype == G2B_BF16)
-    g2b_launch(qknorm_rope_cache_kernel<bf16>, dim3(blocks), dim3(QKN_WARPS * 32), 0, stream, 
-        (const bf16 *)qkv, T_tokens, nh, nkv, hd, q_w, k_w, eps, inv_freq, rot_dim, tok_pos,
-        tok_seq, page_table, P, (bf16 *)cache, page_size, (bf16 *)q_out, (bf16 *)k_out,
-        (bf16 *)v_out, heads_per_block);
+    g2b_launch(qknorm_rope_cache_kernel<bf16>, dim3(blocks), dim3(QKN_WARPS * 32), 0, stream,
+        (const bf16 *)qkv, T_tokens, nh, nkv, hd, q_w, k_w, eps, (const float2 *)rope_table, rot_dim,
+        tok_pos, tok_seq, page_table, P, (bf16 *)cache, page_size, (bf16 *)q_out, (bf16 *)k_out,
+        (bf16 *)v_out);
   else
     G2B_REFUSE("qknorm_rope_cache: unknown dtype %d", dtype);
   return g2b_check_launch("qknorm_rope_cache");

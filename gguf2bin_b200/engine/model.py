@@ -125,6 +125,7 @@ class Model:
         [n_want]) are the token indices whose logits are returned as float32 [n_want, V];
         with ``n_want == 0`` only the cache is updated."""
         ws = ctx.workspace
+        ctx.step_cache.clear()                     # per-step tables are rebuilt from this step's tokens
         x = ws.buffer("stream", (ctx.n_tokens, self.hidden), torch.float32)
         kernels.embed_rows(self.embedding, ctx.tok_ids[:ctx.n_tokens], x)
         for position, entry in enumerate(self.spec.schedule):

@@ -125,9 +125,11 @@ def decode(a) -> None:
                                       for c in caches], L, B * (ctx_len + 1) * 2 * nkv * hd * 2)
         qw = torch.ones(hd, device=DEV)
         inv = torch.ones(hd // 2, device=DEV)
+        rope = torch.empty(B, hd // 2, 2, device=DEV)
+        kernels.rope_table(ctx.tok_pos, inv, rope)
         qkvb = bf(B, NQ + 2 * NK)
         b.run("qknorm_rope_cache", lambda: [kernels.qknorm_rope_cache(
-            qkvb, nh, nkv, hd, qw, qw, 1e-6, inv, hd, ctx.tok_pos, ctx.tok_seq, table, c, ps, q) for c in caches], L)
+            qkvb, nh, nkv, hd, qw, qw, 1e-6, rope, hd, ctx.tok_pos, ctx.tok_seq, table, c, ps, q) for c in caches], L)
 
 
 def prefill(a) -> None:
@@ -170,8 +172,10 @@ def prefill(a) -> None:
         inv = (1e6 ** (-2 * torch.arange(hd // 2, dtype=torch.float64) / hd)).float().to(DEV)
         q = bf(T, NQ)
         out = torch.empty_like(q)
+        rope = torch.empty(T, hd // 2, 2, device=DEV)
+        kernels.rope_table(tok_pos, inv, rope)
         b.run("qknorm_rope_cache", lambda: [kernels.qknorm_rope_cache(
-            qkv, nh, nkv, hd, qw, qw, 1e-6, inv, hd, tok_pos, tok_seq, table, c, ps, q) for c in caches], L,
+            qkv, nh, nkv, hd, qw, qw, 1e-6, rope, hd, tok_pos, tok_seq, table, c, ps, q) for c in caches], L,
             nbytes=T * (NQ + 2 * NK) * 4)
         tiles = sorted([(0, r, min(64, T - r), r) for r in range(0, T, 64)], key=lambda t: -t[3])
         ctx = SimpleNamespace(page_table=table, all_single=False, n_attn_tiles=len(tiles),

@@ -16,7 +16,7 @@ import torch
 from .csrc.build import KernelBuildError, KernelError, load_unit
 
 __all__ = ["KernelError", "KernelBuildError", "embed_rows", "rmsnorm", "qknorm_rope_cache",
-           "cache_write", "swiglu", "advance_positions", "gemm_simt", "linear", "attn_generic",
+           "rope_table", "cache_write", "swiglu", "advance_positions", "gemm_simt", "linear", "attn_generic",
            "attention", "sample_rows", "sample_filtered", "seed_slots"]
 
 F32, BF16 = 0, 1
@@ -111,12 +111,22 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
     _call(f, _ptr(x), _ptr(w), _ptr(rows), n_rows, H, eps, _ptr(out), _code(out.dtype), _stream())
 
 
-def qknorm_rope_cache(qkv, n_heads, n_kv_heads, head_dim, q_w, k_w, eps, inv_freq, rotary_dim,
+def rope_table(tok_pos: torch.Tensor, inv_freq: torch.Tensor, table: torch.Tensor) -> None:
+    """table[t, j] = (cos, sin)(tok_pos[t] * inv_freq[j]) in float32; table [T, half, 2]."""
+    _need(tok_pos, torch.int32, "tok_pos")
+    _need(inv_freq, torch.float32, "inv_freq")
+    _need(table, torch.float32, "table")
+    f = _fn("elementwise.cu", "g2b_rope_table", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _call(f, _ptr(tok_pos), _ptr(inv_freq), _ptr(table), table.shape[0], inv_freq.shape[0], _stream())
+
+
+def qknorm_rope_cache(qkv, n_heads, n_kv_heads, head_dim, q_w, k_w, eps, rope, rotary_dim,
                       tok_pos, tok_seq, page_table, cache_pages, page_size, q_out,
                       k_out=None, v_out=None) -> None:
     """Per-head RMSNorm of the q and k heads (when q_w / k_w are given), half-split
-    rotation by ``pos * inv_freq`` (when inv_freq is given), q to ``q_out``; k and v to
-    the layer's cache pages, or to ``k_out`` / ``v_out`` when those are given."""
+    rotation by the angles of ``rope`` (a table from ``rope_table`` for this step's
+    tokens; None: no rotation), q to ``q_out``; k and v to the layer's cache pages, or to
+    ``k_out`` / ``v_out`` when those are given."""
     T = qkv.shape[0]
     f = _fn("elementwise.cu", "g2b_qknorm_rope_cache",
             [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
@@ -127,7 +137,7 @@ def qknorm_rope_cache(qkv, n_heads, n_kv_heads, head_dim, q_w, k_w, eps, inv_fre
         if t is not None and t.dtype != qkv.dtype:
             raise KernelError("qknorm_rope_cache: outputs and cache must have the input's dtype")
     _call(f, _ptr(qkv), _code(qkv.dtype), T, n_heads, n_kv_heads, head_dim, _ptr(q_w), _ptr(k_w),
-          eps, _ptr(inv_freq), rotary_dim, _ptr(tok_pos), _ptr(tok_seq), _ptr(page_table), P,
+          eps, _ptr(rope), rotary_dim, _ptr(tok_pos), _ptr(tok_seq), _ptr(page_table), P,
           _ptr(cache_pages), page_size, _ptr(q_out), _ptr(k_out), _ptr(v_out), _stream())
 
 

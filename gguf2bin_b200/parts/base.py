@@ -57,6 +57,20 @@ class StepContext:
     n_attn_tiles: int = 0                            # of row 0; tiles of ATTN_TILE_ROWS query rows
     attn_tiles_wide: Optional[torch.Tensor] = None   # the same with ATTN_WIDE_TILE_ROWS rows (tcgen05 kernel)
     n_attn_tiles_wide: int = 0
+    step_cache: dict = field(default_factory=dict)   # tensors derived once per step (cleared by the model)
+
+    def rope_table(self, inv_freq: torch.Tensor) -> torch.Tensor:
+        """(cos, sin) of every token's position times ``inv_freq``, computed once per step and
+        shared by all layers that rotate with these frequencies; float32 [T, half, 2]."""
+        key = ("rope", inv_freq.data_ptr())
+        table = self.step_cache.get(key)
+        if table is None:
+            from .. import kernels
+            table = self.workspace.buffer(f"rope.table.{len(self.step_cache)}",
+                                          (self.n_tokens, inv_freq.shape[0], 2), torch.float32)
+            kernels.rope_table(self.tok_pos[:self.n_tokens], inv_freq, table)
+            self.step_cache[key] = table
+        return table
 
     @property
     def all_single(self) -> bool:

@@ -112,8 +112,9 @@ class GQAAttention:
         fused = self.position.fused_rotation()
         if fused is not None:
             inv_freq, rot = fused
+            rope = ctx.rope_table(inv_freq) if inv_freq is not None else None
             kernels.qknorm_rope_cache(qkv, self.nh, nkv_own, self.hd, self.q_norm_w,
-                                      self.k_norm_w, self.qk_eps, inv_freq, rot, ctx.tok_pos,
+                                      self.k_norm_w, self.qk_eps, rope, rot, ctx.tok_pos,
                                       ctx.tok_seq, ctx.page_table, view.pages, view.page_size, q)
         else:
             k = ws.buffer("attn.k", (T, nk), self.dtype)

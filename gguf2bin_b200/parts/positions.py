@@ -15,6 +15,9 @@ from ..config.specs import ConfigError, PartSpec
 from .registry import register_position
 
 
+_INV_FREQ: dict = {}
+
+
 class RopeNeox:
     def __init__(self, spec: PartSpec, head_dim: int, device):
         self.theta = float(spec["theta"])
@@ -22,8 +25,13 @@ class RopeNeox:
         if self.rotary_dim % 2 or not (0 < self.rotary_dim <= head_dim):
             raise ConfigError(f"rope_neox: rotary_dim {self.rotary_dim} must be even and at most "
                               f"head_dim {head_dim}")
-        j = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
-        self.inv_freq = (self.theta ** (-2.0 * j / self.rotary_dim)).to(torch.float32).to(device)
+        # one table per (theta, rotary_dim, device): layers with equal frequencies share the tensor,
+        # and with it the step's (cos, sin) table
+        key = (self.theta, self.rotary_dim, str(device))
+        if key not in _INV_FREQ:
+            j = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
+            _INV_FREQ[key] = (self.theta ** (-2.0 * j / self.rotary_dim)).to(torch.float32).to(device)
+        self.inv_freq = _INV_FREQ[key]
 
     def fused_rotation(self):
         return self.inv_freq, self.rotary_dim

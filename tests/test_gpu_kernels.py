@@ -131,8 +131,10 @@ def test_qknorm_rope_cache(dtype, nh, nkv, hd, rot, norm):
     inv_freq = (theta ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).float().to(DEV)
     q_out = torch.empty(T, nh * hd, dtype=dtype, device=DEV)
     before = cache.clone()
-    kernels.qknorm_rope_cache(qkv, nh, nkv, hd, qw, kw, eps, inv_freq, rot,
-                              torch.tensor(tok_pos, dtype=torch.int32, device=DEV),
+    pos_t = torch.tensor(tok_pos, dtype=torch.int32, device=DEV)
+    rope = torch.empty(T, rot // 2, 2, device=DEV)
+    kernels.rope_table(pos_t, inv_freq, rope)
+    kernels.qknorm_rope_cache(qkv, nh, nkv, hd, qw, kw, eps, rope, rot, pos_t,
                               torch.tensor(tok_seq, dtype=torch.int32, device=DEV), table, cache, ps, q_out)
     x = qkv.float().cpu().numpy().reshape(T, nh + 2 * nkv, hd)
     qq, kk, vv = x[:, :nh], x[:, nh:nh + nkv], x[:, nh + nkv:]

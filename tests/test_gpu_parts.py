@@ -231,8 +231,10 @@ def test_position_part(dtype):
     positions = [0, 1, 5, 300]
     q = gpu(rng.standard_normal((4, nh * hd)).astype(np.float32), tdt)
     out = torch.empty_like(q)
-    kernels.qknorm_rope_cache(q, nh, 0, hd, None, None, 0.0, inv_freq, r,
-                              torch.tensor(positions, dtype=torch.int32, device=DEV),
+    pos_t = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    rope = torch.empty(4, r // 2, 2, device=DEV)
+    kernels.rope_table(pos_t, inv_freq, rope)
+    kernels.qknorm_rope_cache(q, nh, 0, hd, None, None, 0.0, rope, r, pos_t,
                               torch.zeros(4, dtype=torch.int32, device=DEV), None, None, 64, out)
     x = q.float().cpu().numpy().reshape(4, nh, hd)
     ref = np.concatenate([P.rope_neox(x[..., :rot], positions, 777.0, np.float32), x[..., rot:]], -1)
