@@ -177,22 +177,113 @@ extern "C" int g2b_rope_table(const int *tok_pos, const float *inv_freq, float *
   return g2b_check_launch("rope_table");
 }
 
-__device__ __forceinline__ float2 ld2(const bf16 *p) {
-  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p));
+__device__ __forceinline__ void ld4(const bf16 *p, float (&v)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+  const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+  const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+  v[0] = lo.x; v[1] = lo.y; v[2] = hi.x; v[3] = hi.y;
 }
-__device__ __forceinline__ float2 ld2(const float *p) { return *reinterpret_cast<const float2 *>(p); }
-__device__ __forceinline__ void st2(bf16 *p, float a, float b) {
-  *reinterpret_cast<__nv_bfloat162 *>(p) = __floats2bfloat162_rn(a, b);
+__device__ __forceinline__ void ld4(const float *p, float (&v)[4]) {
+  const float4 raw = *reinterpret_cast<const float4 *>(p);
+  v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
 }
-__device__ __forceinline__ void st2(float *p, float a, float b) { *reinterpret_cast<float2 *>(p) = make_float2(a, b); }
+__device__ __forceinline__ void st4(bf16 *p, const float (&v)[4]) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162 *>(&raw.x) = __floats2bfloat162_rn(v[0], v[1]);
+  *reinterpret_cast<__nv_bfloat162 *>(&raw.y) = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<uint2 *>(p) = raw;
+}
+__device__ __forceinline__ void st4(float *p, const float (&v)[4]) {
+  *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
 
-// One warp per QKN_HEADS consecutive heads of a token.  `rope` is the step's table for these
-// frequencies (or null).  Register path (head sizes that are multiples of 4 up to 256,
-// rotation over the whole head): a lane holds the elements (2l, 2l+1) of each half of the
-// head and their partners, loaded and stored two at a time; the loads of both heads are
-// issued before either is used.
-#define QKN_HEADS 2
+// Head sizes 8 * LPH (LPH a power of two up to 32) with the rotation over the whole head:
+// LPH lanes share a head, so a warp works on 32 / LPH heads of one token at once.  A lane
+// holds four consecutive elements of the first half and their rotation partners in the
+// second half, loaded and stored as one vector each; everything stays in registers.
+#define QKN_FAST_WARPS 8
 
+template <typename T, int LPH>
+__global__ void __launch_bounds__(QKN_FAST_WARPS * 32)
+qknorm_rope_fast_kernel(
+    const T *__restrict__ qkv, int T_tokens, int nh, int nkv,
+    const float *__restrict__ q_w, const float *__restrict__ k_w, float eps,
+    const float2 *__restrict__ rope,
+    const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
+    const int *__restrict__ page_table, int P, T *__restrict__ cache, int page_size,
+    T *__restrict__ q_out, T *__restrict__ k_out, T *__restrict__ v_out) {
+  pdl_launch();
+  pdl_wait();
+  constexpr int HPW = 32 / LPH, HD = 8 * LPH, HH = 4 * LPH;
+  const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned heads = nh + 2 * nkv;
+  const unsigned groups = (heads + HPW - 1) / HPW;
+  const unsigned item = blockIdx.x * QKN_FAST_WARPS + warp;
+  if (item >= (unsigned)T_tokens * groups) return;
+  const unsigned t = item / groups;
+  const unsigned h = (item - t * groups) * HPW + lane / LPH;
+  const bool valid = h < heads;
+  const unsigned hc = valid ? h : heads - 1;
+  const int j = 4 * (lane % LPH);
+  const T *src = qkv + ((size_t)t * heads + hc) * HD;
+  float a[4], b[4];
+  ld4(src + j, a);
+  ld4(src + HH + j, b);
+  const int kind = hc < (unsigned)nh ? 0 : (hc < (unsigned)(nh + nkv) ? 1 : 2);     // q, k, v
+  const float *w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
+  T *dst;
+  if (kind == 0) {
+    dst = q_out + ((size_t)t * nh + hc) * HD;
+  } else {
+    const unsigned kvh = kind == 1 ? hc - nh : hc - nh - nkv;
+    T *flat = kind == 1 ? k_out : v_out;
+    if (flat) {
+      dst = flat + ((size_t)t * nkv + kvh) * HD;
+    } else {
+      const int pos = tok_pos[t];
+      const int page = page_table[(size_t)tok_seq[t] * P + pos / page_size];
+      dst = cache + ((((size_t)page * 2 + (kind - 1)) * nkv + kvh) * page_size + pos % page_size) * HD;
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    ss = fmaf(a[i], a[i], ss);
+    ss = fmaf(b[i], b[i], ss);
+  }
+#pragma unroll
+  for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (w) {
+    const float inv = 1.f / sqrtf(ss / (float)HD + eps);
+    float wa[4], wb[4];
+    ld4(w + j, wa);
+    ld4(w + HH + j, wb);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      a[i] = (wa[i] * a[i]) * inv;
+      b[i] = (wb[i] * b[i]) * inv;
+    }
+  }
+  if (rope && kind != 2) {
+    const float2 *cs = rope + (size_t)t * HH + j;
+    const float4 r01 = *reinterpret_cast<const float4 *>(cs);          // (cos, sin) of j, j+1
+    const float4 r23 = *reinterpret_cast<const float4 *>(cs + 2);      // and of j+2, j+3
+    const float c[4] = {r01.x, r01.z, r23.x, r23.z}, sn[4] = {r01.y, r01.w, r23.y, r23.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float av = a[i], bv = b[i];
+      a[i] = av * c[i] - bv * sn[i];
+      b[i] = av * sn[i] + bv * c[i];
+    }
+  }
+  if (valid) {
+    st4(dst + j, a);
+    st4(dst + HH + j, b);
+  }
+}
+
+// Every other head size and a rotation over part of the head: one warp per (token, head),
+// the head staged in shared memory.
 template <typename T>
 __global__ void __launch_bounds__(QKN_WARPS * 32)
 qknorm_rope_cache_kernel(
@@ -207,116 +298,64 @@ qknorm_rope_cache_kernel(
   __shared__ float buf[QKN_WARPS][QKN_MAX_HD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = nh + 2 * nkv;
-  const int groups = (heads + QKN_HEADS - 1) / QKN_HEADS;          // head groups per token
   const long long item = (long long)blockIdx.x * QKN_WARPS + warp;
-  if (item >= (long long)T_tokens * groups) return;
-  const int t = (int)(item / groups), h0 = (int)(item % groups) * QKN_HEADS;
+  if (item >= (long long)T_tokens * heads) return;
+  const int t = (int)(item / heads), h = (int)(item % heads);
   const int half = rot_dim >> 1;
-  const int pos = tok_pos[t];
-  const int page = (cache && page_table) ? page_table[(size_t)tok_seq[t] * P + pos / page_size] : 0;
-
-  auto kind_of = [&](int h) { return h < nh ? 0 : (h < nh + nkv ? 1 : 2); };   // 0 q, 1 k, 2 v
-  auto dst_of = [&](int h) -> T * {
-    const int kind = kind_of(h);
-    if (kind == 0) return q_out + (size_t)t * nh * hd + (size_t)h * hd;
+  const T *src = qkv + (size_t)t * heads * hd + (size_t)h * hd;
+  const int kind = h < nh ? 0 : (h < nh + nkv ? 1 : 2);
+  const float *w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
+  const float2 *cs = (rope && kind != 2) ? rope + (size_t)t * half : nullptr;
+  T *dst;
+  if (kind == 0) {
+    dst = q_out + (size_t)t * nh * hd + (size_t)h * hd;
+  } else {
     const int kvh = kind == 1 ? h - nh : h - nh - nkv;
     T *flat = kind == 1 ? k_out : v_out;
-    if (flat) return flat + (size_t)t * nkv * hd + (size_t)kvh * hd;
-    return cache + ((((size_t)page * 2 + (kind - 1)) * nkv + kvh) * page_size + pos % page_size) * hd;
-  };
-
-  if ((hd % 4 == 0) && hd <= 256 && (!rope || rot_dim == hd)) {
-    const int hh = hd >> 1;                        // first element of the second half
-    float2 a[QKN_HEADS][2], b[QKN_HEADS][2];
-#pragma unroll
-    for (int u = 0; u < QKN_HEADS; ++u) {
-      const T *src = qkv + (size_t)t * heads * hd + (size_t)min(h0 + u, heads - 1) * hd;
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int j = 2 * lane + 64 * i;
-        if (j < hh) {
-          a[u][i] = ld2(src + j);
-          b[u][i] = ld2(src + hh + j);
-        } else {
-          a[u][i] = b[u][i] = make_float2(0.f, 0.f);
-        }
-      }
+    if (flat) {
+      dst = flat + (size_t)t * nkv * hd + (size_t)kvh * hd;
+    } else {
+      const int pos = tok_pos[t];
+      const int page = page_table[(size_t)tok_seq[t] * P + pos / page_size];
+      dst = cache + ((((size_t)page * 2 + (kind - 1)) * nkv + kvh) * page_size + pos % page_size) * hd;
     }
-#pragma unroll
-    for (int u = 0; u < QKN_HEADS; ++u) {
-      const int h = h0 + u;
-      if (h >= heads) break;
-      const int kind = kind_of(h);
-      const float *w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
-      const float2 *cs = (rope && kind != 2) ? rope + (size_t)t * half : nullptr;
-      float ss = 0.f;
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        ss = fmaf(a[u][i].x, a[u][i].x, ss); ss = fmaf(a[u][i].y, a[u][i].y, ss);
-        ss = fmaf(b[u][i].x, b[u][i].x, ss); ss = fmaf(b[u][i].y, b[u][i].y, ss);
-      }
-      ss = warp_sum(ss);
-      const float inv = w ? 1.f / sqrtf(ss / (float)hd + eps) : 1.f;
-      T *dst = dst_of(h);
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int j = 2 * lane + 64 * i;
-        if (j < hh) {
-          float2 av = a[u][i], bv = b[u][i];
-          if (w) {
-            const float2 wa = *reinterpret_cast<const float2 *>(w + j);
-            const float2 wb = *reinterpret_cast<const float2 *>(w + hh + j);
-            av.x = (wa.x * av.x) * inv; av.y = (wa.y * av.y) * inv;
-            bv.x = (wb.x * bv.x) * inv; bv.y = (wb.y * bv.y) * inv;
-          }
-          if (cs) {
-            const float4 r = *reinterpret_cast<const float4 *>(cs + j);      // (cos, sin) of j and j+1
-            const float ax = av.x * r.x - bv.x * r.y, bx = av.x * r.y + bv.x * r.x;
-            const float ay = av.y * r.z - bv.y * r.w, by = av.y * r.w + bv.y * r.z;
-            av = make_float2(ax, ay);
-            bv = make_float2(bx, by);
-          }
-          st2(dst + j, av.x, av.y);
-          st2(dst + hh + j, bv.x, bv.y);
-        }
-      }
-    }
-    return;
   }
   float *x = buf[warp];
-  for (int u = 0; u < QKN_HEADS; ++u) {
-    const int h = h0 + u;
-    if (h >= heads) break;
-    const T *src = qkv + (size_t)t * heads * hd + (size_t)h * hd;
-    const int kind = kind_of(h);
-    const float *w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
-    const float2 *cs = (rope && kind != 2) ? rope + (size_t)t * half : nullptr;
-    T *dst = dst_of(h);
-    float ss = 0.f;
-    for (int j = lane; j < hd; j += 32) {
-      const float v = to_f32(src[j]);
-      x[j] = v;
-      ss = fmaf(v, v, ss);
-    }
-    ss = warp_sum(ss);
-    __syncwarp();
-    if (w) {
-      const float inv = 1.f / sqrtf(ss / (float)hd + eps);
-      for (int j = lane; j < hd; j += 32) x[j] = (w[j] * x[j]) * inv;
-      __syncwarp();
-    }
-    if (cs) {
-      for (int j = lane; j < half; j += 32) {
-        const float2 r = cs[j];
-        const float av = x[j], bv = x[j + half];
-        x[j] = av * r.x - bv * r.y;
-        x[j + half] = av * r.y + bv * r.x;
-      }
-      __syncwarp();
-    }
-    for (int j = lane; j < hd; j += 32) dst[j] = from_f32<T>(x[j]);
-    __syncwarp();                                  // x is reused for the next head
+  float ss = 0.f;
+  for (int j = lane; j < hd; j += 32) {
+    const float v = to_f32(src[j]);
+    x[j] = v;
+    ss = fmaf(v, v, ss);
   }
+  ss = warp_sum(ss);
+  __syncwarp();
+  if (w) {
+    const float inv = 1.f / sqrtf(ss / (float)hd + eps);
+    for (int j = lane; j < hd; j += 32) x[j] = (w[j] * x[j]) * inv;
+    __syncwarp();
+  }
+  if (cs) {
+    for (int j = lane; j < half; j += 32) {
+      const float2 r = cs[j];
+      const float av = x[j], bv = x[j + half];
+      x[j] = av * r.x - bv * r.y;
+      x[j + half] = av * r.y + bv * r.x;
+    }
+    __syncwarp();
+  }
+  for (int j = lane; j < hd; j += 32) dst[j] = from_f32<T>(x[j]);
+}
+
+template <typename T, int LPH>
+static void launch_qkn_fast(const void *qkv, int T_tokens, int nh, int nkv, const float *q_w, const float *k_w,
+                            float eps, const float *rope_table, const int *tok_pos, const int *tok_seq,
+                            const int *page_table, int P, void *cache, int page_size, void *q_out, void *k_out,
+                            void *v_out, cudaStream_t stream) {
+  const long long items = (long long)T_tokens * ((nh + 2 * nkv + 32 / LPH - 1) / (32 / LPH));
+  const unsigned blocks = (unsigned)((items + QKN_FAST_WARPS - 1) / QKN_FAST_WARPS);
+  g2b_launch(qknorm_rope_fast_kernel<T, LPH>, dim3(blocks), dim3(QKN_FAST_WARPS * 32), 0, stream,
+             (const T *)qkv, T_tokens, nh, nkv, q_w, k_w, eps, (const float2 *)rope_table, tok_pos, tok_seq,
+             page_table, P, (T *)cache, page_size, (T *)q_out, (T *)k_out, (T *)v_out);
 }
 
 extern "C" int g2b_qknorm_rope_cache(const void *qkv, int dtype, int T_tokens, int nh, int nkv,
@@ -326,6 +365,7 @@ extern "C" int g2b_qknorm_rope_cache(const void *qkv, int dtype, int T_tokens, i
                                      void *cache, int page_size, void *q_out, void *k_out,
                                      void *v_out, cudaStream_t stream) {
   if (T_tokens <= 0) return 0;
+  if (dtype != G2B_F32 && dtype != G2B_BF16) G2B_REFUSE("qknorm_rope_cache: unknown dtype %d", dtype);
   if (hd <= 0 || hd > QKN_MAX_HD)
     G2B_REFUSE("qknorm_rope_cache: head_dim %d outside 1..%d", hd, QKN_MAX_HD);
   if (rope_table && (rot_dim <= 0 || rot_dim > hd || (rot_dim & 1)))
@@ -334,23 +374,40 @@ extern "C" int g2b_qknorm_rope_cache(const void *qkv, int dtype, int T_tokens, i
     G2B_REFUSE("qknorm_rope_cache: k_out and v_out must be given together");
   if (nkv > 0 && !k_out && (!cache || !page_table || page_size <= 0))
     G2B_REFUSE("qknorm_rope_cache: no cache to write to");
-  const long long items = (long long)T_tokens * ((nh + 2 * nkv + QKN_HEADS - 1) / QKN_HEADS);
+  const int heads = nh + 2 * nkv;
+  const int lph = hd / 8;
+  const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)k_out |
+                         (uintptr_t)v_out | (uintptr_t)rope_table | (uintptr_t)q_w | (uintptr_t)k_w) & 15) == 0;
+  const bool fast = aligned && hd % 8 == 0 && lph >= 2 && lph <= 32 && (lph & (lph - 1)) == 0 &&
+                    (!rope_table || rot_dim == hd) && (long long)T_tokens * heads < (1ll << 31);
+  if (fast) {
+#define G2B_QKN_FAST(L)                                                                                     \
+  case L:                                                                                                   \
+    if (dtype == G2B_F32)                                                                                   \
+      launch_qkn_fast<float, L>(qkv, T_tokens, nh, nkv, q_w, k_w, eps, rope_table, tok_pos, tok_seq,        \
+                                page_table, P, cache, page_size, q_out, k_out, v_out, stream);              \
+    else                                                                                                    \
+      launch_qkn_fast<bf16, L>(qkv, T_tokens, nh, nkv, q_w, k_w, eps, rope_table, tok_pos, tok_seq,         \
+                               page_table, P, cache, page_size, q_out, k_out, v_out, stream);               \
+    break;
+    switch (lph) {
+      G2B_QKN_FAST(2) G2B_QKN_FAST(4) G2B_QKN_FAST(8) G2B_QKN_FAST(16) G2B_QKN_FAST(32)
+    }
+#undef G2B_QKN_FAST
+    return g2b_check_launch("qknorm_rope_cache");
+  }
+  const long long items = (long long)T_tokens * heads;
   const unsigned blocks = (unsigned)((items + QKN_WARPS - 1) / QKN_WARPS);
-  if ((((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)k_out | (uintptr_t)v_out |
-        (uintptr_t)rope_table | (uintptr_t)q_w | (uintptr_t)k_w) & 15) != 0)
-    G2B_REFUSE("qknorm_rope_cache: tensors must be 16-byte aligned");
   if (dtype == G2B_F32)
     g2b_launch(qknorm_rope_cache_kernel<float>, dim3(blocks), dim3(QKN_WARPS * 32), 0, stream,
         (const float *)qkv, T_tokens, nh, nkv, hd, q_w, k_w, eps, (const float2 *)rope_table, rot_dim,
         tok_pos, tok_seq, page_table, P, (float *)cache, page_size, (float *)q_out, (float *)k_out,
         (float *)v_out);
-  else if (dtype == G2B_BF16)
+  else
     g2b_launch(qknorm_rope_cache_kernel<bf16>, dim3(blocks), dim3(QKN_WARPS * 32), 0, stream,
         (const bf16 *)qkv, T_tokens, nh, nkv, hd, q_w, k_w, eps, (const float2 *)rope_table, rot_dim,
         tok_pos, tok_seq, page_table, P, (bf16 *)cache, page_size, (bf16 *)q_out, (bf16 *)k_out,
         (bf16 *)v_out);
-  else
-    G2B_REFUSE("qknorm_rope_cache: unknown dtype %d", dtype);
   return g2b_check_launch("qknorm_rope_cache");
 }
 

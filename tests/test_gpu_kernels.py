@@ -116,7 +116,9 @@ def test_attn_generic(dtype, nh, nkv, hd, window):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nh,nkv,hd,rot,norm", [(4, 2, 16, 16, True), (3, 1, 48, 32, True), (2, 2, 128, 128, False)])
+@pytest.mark.parametrize("nh,nkv,hd,rot,norm", [(4, 2, 16, 16, True), (3, 1, 48, 32, True), (2, 2, 128, 128, False),
+                                                (5, 1, 64, 64, True), (4, 2, 256, 256, True), (2, 1, 96, 96, True),
+                                                (3, 3, 32, 32, True), (7, 1, 128, 128, True)])
 def test_qknorm_rope_cache(dtype, nh, nkv, hd, rot, norm):
     from gguf2bin_b200 import kernels
     ps, lens, q_lens = 64, [70, 130], [70, 2]
