@@ -2,10 +2,14 @@
 // a past, over the paged bfloat16 cache (the step's own keys are already in it).
 //
 // Work list: tiles of 128 query rows (sequence, first token index, rows, position of the
-// first row), longest first; grid (tile, query head).  Roles by warp:
+// first row), longest first; one CTA per (tile, query head), numbered tile-major so that the
+// long tiles of every head start first and the short ones fill in behind them.  Two CTAs fit
+// on an SM (shared memory and tensor memory are sized for that): while one waits on its
+// softmax the other's products run.  Roles by warp:
 //   warp 4, one thread  TMA producer: the 128 x HD query tile once, then per key page the K
 //                       and V panels of (page, kv head), each as 64-column boxes with 128-byte
-//                       swizzle, into a four-stage ring.
+//                       swizzle, into a ring of three K panels and a ring of two V panels (K is
+//                       free again as soon as its S product is done, V only after P.V).
 //   warp 5, one thread  MMA issuer (tcgen05.mma, cta_group::1, kind::f16):
 //                         S[128 x 64]  = Q K^T      (both operands K-major)  -> tensor memory,
 //                                                    two S buffers, always one page ahead
@@ -41,21 +45,23 @@ using namespace tc;
 constexpr int PAGE = 64;
 constexpr int BM = 128;
 constexpr int THREADS = 192;
-constexpr int STAGES = 4;
+constexpr int K_STAGES = 3, V_STAGES = 2;
 constexpr int SUBS = HD / 64;                       // 64-column boxes along the head dimension
 constexpr int Q_SUB_BYTES = BM * 128;               // one 128 x 64 box
 constexpr int Q_BYTES = SUBS * Q_SUB_BYTES;
 constexpr int KV_SUB_BYTES = PAGE * 128;            // one 64 x 64 box
 constexpr int KV_BYTES = SUBS * KV_SUB_BYTES;       // K (or V) of one page and kv head
-constexpr int STAGE_BYTES = 2 * KV_BYTES;
-constexpr int BAR_OFFSET = Q_BYTES + STAGES * STAGE_BYTES;
-constexpr int SMEM_TOTAL = BAR_OFFSET + 128 + 1024;
+constexpr int K_OFFSET = Q_BYTES, V_OFFSET = K_OFFSET + K_STAGES * KV_BYTES;
+constexpr int BAR_OFFSET = V_OFFSET + V_STAGES * KV_BYTES;
+constexpr int SMEM_TOTAL = BAR_OFFSET + 256;
+// two CTAs per SM: 2 x (dynamic + 1 KB reserved) must stay within the 227 KB of an SM
+static_assert(2 * (SMEM_TOTAL + 1024) <= 227 * 1024, "two CTAs per SM");
 constexpr int O_COL0 = 128;                         // S buffers at columns 0..63 and 64..127, O from 128
 constexpr int TMEM_COLS = 256;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.f;                 // log2 of the growth that triggers a rescale
 
-enum { ST_PRODUCER = 11, ST_MMA = 12, ST_SOFTMAX = 13 };
+enum { ST_PRODUCER = 11, ST_MMA = 12, ST_SOFTMAX = 13, ST_ALIGN = 14 };
 static_assert(HD <= 128, "O uses columns 128..255");
 
 __device__ __forceinline__ float ex2(float x) {
@@ -68,31 +74,40 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t *>(&v);
 }
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_kv, bf16 *__restrict__ out,
                        const int4 *__restrict__ tiles, const int *__restrict__ page_table, int P,
                        int nh, int nkv, int window, float scale_log2, int *__restrict__ status) {
   pdl_launch();
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char *smem = reinterpret_cast<unsigned char *>(
-      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  // The swizzled panels need 1024-byte alignment.  The kernel has no static shared memory, so
+  // the dynamic part starts at the aligned base of the window; checked rather than assumed.
+  extern __shared__ __align__(1024) unsigned char smem[];
+  if (smem_addr(smem) & 1023u) {
+    if (threadIdx.x == 0) atomicExch(status, ST_ALIGN);
+    return;
+  }
   unsigned char *q_smem = smem;
-  unsigned char *kv_smem = smem + Q_BYTES;
+  unsigned char *k_smem = smem + K_OFFSET, *v_smem = smem + V_OFFSET;
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + BAR_OFFSET);
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 15);
-  const uint32_t q_full = smem_addr(bars + 0), kv_full0 = smem_addr(bars + 1);      // [STAGES]
-  const uint32_t kv_empty0 = smem_addr(bars + 1 + STAGES);                            // [STAGES]
-  const uint32_t s_ready0 = smem_addr(bars + 9), p_ready0 = smem_addr(bars + 11);    // [2] each
-  const uint32_t pv_done = smem_addr(bars + 13), o_ready = smem_addr(bars + 14);
-  static_assert(1 + 2 * STAGES <= 9, "barrier slots");
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 20);
+  const uint32_t q_full = smem_addr(bars + 0);
+  const uint32_t k_full0 = smem_addr(bars + 1), k_empty0 = smem_addr(bars + 4);       // [K_STAGES] each
+  const uint32_t v_full0 = smem_addr(bars + 7), v_empty0 = smem_addr(bars + 9);       // [V_STAGES] each
+  const uint32_t s_ready0 = smem_addr(bars + 11), p_ready0 = smem_addr(bars + 13);    // [2] each
+  const uint32_t pv_done = smem_addr(bars + 15), o_ready = smem_addr(bars + 16);
+  static_assert(K_STAGES == 3 && V_STAGES == 2, "barrier slots");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(kv_full0 + 8 * s, 1);
-      mbar_init(kv_empty0 + 8 * s, 1);
+    for (int s = 0; s < K_STAGES; ++s) {
+      mbar_init(k_full0 + 8 * s, 1);
+      mbar_init(k_empty0 + 8 * s, 1);
+    }
+    for (int s = 0; s < V_STAGES; ++s) {
+      mbar_init(v_full0 + 8 * s, 1);
+      mbar_init(v_empty0 + 8 * s, 1);
     }
     for (int j = 0; j < 2; ++j) {
       mbar_init(s_ready0 + 8 * j, 1);
@@ -109,9 +124,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const uint32_t tmem = *tmem_slot;
   pdl_wait();                                   // the queries and the cache come from earlier kernels
 
-  const int4 tile = tiles[blockIdx.x];
+  const int4 tile = tiles[blockIdx.x / nh];
   const int b = tile.x, t0 = tile.y, n_rows = tile.z, pos0 = tile.w;
-  const int h = blockIdx.y, kvh = h / (nh / nkv);
+  const int h = blockIdx.x % nh, kvh = h / (nh / nkv);
   const int first_page = window > 0 ? max(0, pos0 - window + 1) / PAGE : 0;
   const int last_page = (pos0 + n_rows - 1) / PAGE;
   const int n_pages = last_page - first_page + 1;
@@ -123,23 +138,35 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       for (int sub = 0; sub < SUBS; ++sub)
         tma_load_2d(smem_addr(q_smem + sub * Q_SUB_BYTES), &map_q, h * HD + 64 * sub, t0, q_full);
       const int *pt = page_table + (size_t)b * P + first_page;
-      for (int i = 0; i < n_pages; ++i) {
-        const int s = i % STAGES;
-        if (i >= STAGES && !mbar_wait(kv_empty0 + 8 * s, ((i / STAGES) - 1) & 1)) {
-          atomicExch(status, ST_PRODUCER);
-          break;
-        }
-        const int phys = pt[i];
-        const int row_k = ((phys * 2 + 0) * nkv + kvh) * PAGE;
-        const int row_v = ((phys * 2 + 1) * nkv + kvh) * PAGE;
-        const uint32_t dst = smem_addr(kv_smem + s * STAGE_BYTES);
-        mbar_expect_tx(kv_full0 + 8 * s, STAGE_BYTES);
+      auto load_k = [&](int i) -> bool {
+        const int s = i % K_STAGES;
+        if (i >= K_STAGES && !mbar_wait(k_empty0 + 8 * s, ((i / K_STAGES) - 1) & 1)) return false;
+        const int row = ((pt[i] * 2 + 0) * nkv + kvh) * PAGE;
+        const uint32_t dst = smem_addr(k_smem + s * KV_BYTES);
+        mbar_expect_tx(k_full0 + 8 * s, KV_BYTES);
 #pragma unroll
-        for (int sub = 0; sub < SUBS; ++sub) {
-          tma_load_2d(dst + sub * KV_SUB_BYTES, &map_kv, 64 * sub, row_k, kv_full0 + 8 * s);
-          tma_load_2d(dst + KV_BYTES + sub * KV_SUB_BYTES, &map_kv, 64 * sub, row_v, kv_full0 + 8 * s);
-        }
+        for (int sub = 0; sub < SUBS; ++sub)
+          tma_load_2d(dst + sub * KV_SUB_BYTES, &map_kv, 64 * sub, row, k_full0 + 8 * s);
+        return true;
+      };
+      auto load_v = [&](int i) -> bool {
+        const int s = i % V_STAGES;
+        if (i >= V_STAGES && !mbar_wait(v_empty0 + 8 * s, ((i / V_STAGES) - 1) & 1)) return false;
+        const int row = ((pt[i] * 2 + 1) * nkv + kvh) * PAGE;
+        const uint32_t dst = smem_addr(v_smem + s * KV_BYTES);
+        mbar_expect_tx(v_full0 + 8 * s, KV_BYTES);
+#pragma unroll
+        for (int sub = 0; sub < SUBS; ++sub)
+          tma_load_2d(dst + sub * KV_SUB_BYTES, &map_kv, 64 * sub, row, v_full0 + 8 * s);
+        return true;
+      };
+      // in the order of use: K0, K1, V0, K2, V1, K3, ...
+      bool ok = load_k(0);
+      for (int i = 0; i < n_pages && ok; ++i) {
+        if (i + 1 < n_pages) ok = load_k(i + 1);
+        if (ok) ok = load_v(i);
       }
+      if (!ok) atomicExch(status, ST_PRODUCER);
     }
   } else if (warp == 5) {
     if (lane == 0) {
@@ -147,34 +174,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       constexpr uint32_t idesc_pv = instr_desc(BM, HD, true);
       bool ok = mbar_wait(q_full, 0);
       if (!ok) atomicExch(status, ST_MMA);
-      // S of page i into S buffer i % 2 (needs K of stage i % STAGES)
+      // S of page i into S buffer i % 2 (needs K of stage i % K_STAGES)
       auto issue_s = [&](int i) -> bool {
-        const int s = i % STAGES;
-        if (!mbar_wait(kv_full0 + 8 * s, (i / STAGES) & 1)) { atomicExch(status, ST_MMA); return false; }
+        const int s = i % K_STAGES;
+        if (!mbar_wait(k_full0 + 8 * s, (i / K_STAGES) & 1)) { atomicExch(status, ST_MMA); return false; }
         tc_fence_after();
-        const uint32_t k_addr = smem_addr(kv_smem + s * STAGE_BYTES);
+        const uint32_t k_addr = smem_addr(k_smem + s * KV_BYTES);
 #pragma unroll
         for (int sub = 0; sub < SUBS; ++sub)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma_bf16(tmem + 64 * (i & 1), desc_k_major(smem_addr(q_smem + sub * Q_SUB_BYTES)) + 2 * k,
                       desc_k_major(k_addr + sub * KV_SUB_BYTES) + 2 * k, idesc_s, (sub | k) != 0);
+        umma_commit(k_empty0 + 8 * s);             // K of this stage has been read
         umma_commit(s_ready0 + 8 * (i & 1));
         return true;
       };
       if (ok) ok = issue_s(0);
       if (ok && n_pages > 1) ok = issue_s(1);
       for (int i = 0; i < n_pages && ok; ++i) {
-        const int s = i % STAGES;
-        if (!mbar_wait(p_ready0 + 8 * (i & 1), (i >> 1) & 1)) { atomicExch(status, ST_MMA); break; }
+        const int s = i % V_STAGES;
+        if (!mbar_wait(v_full0 + 8 * s, (i / V_STAGES) & 1) ||
+            !mbar_wait(p_ready0 + 8 * (i & 1), (i >> 1) & 1)) { atomicExch(status, ST_MMA); break; }
         tc_fence_after();
         // O += P V: the keys are the K index, 16 per MMA: 8 packed columns of P, 16 rows of V
-        const uint32_t v_addr = smem_addr(kv_smem + s * STAGE_BYTES) + KV_BYTES;
+        const uint32_t v_addr = smem_addr(v_smem + s * KV_BYTES);
 #pragma unroll
         for (int k = 0; k < PAGE / 16; ++k)
           umma_bf16_ts(tmem + O_COL0, tmem + 64 * (i & 1) + 8 * k,
                        desc_mn_major(v_addr + k * 16 * 128, KV_SUB_BYTES), idesc_pv, (i | k) != 0);
-        umma_commit(kv_empty0 + 8 * s);            // K and V of this stage have been read
+        umma_commit(v_empty0 + 8 * s);             // V of this stage has been read
         umma_commit(pv_done);                      // O holds pages 0..i; P of page i has been read
         if (i + 2 < n_pages) ok = issue_s(i + 2);  // overwrites the S/P buffer of page i (in order)
       }
@@ -206,18 +235,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       const int warp_pos_min = pos0 + warp * 32, warp_pos_max = warp_pos_min + 31;
       const bool partial = key0 + PAGE - 1 > warp_pos_min ||
                            (window > 0 && key0 < max(0, warp_pos_max - window + 1));
-      float mx = -INFINITY;
       if (partial) {
 #pragma unroll
         for (int c = 0; c < 64; ++c) {
           const int key = key0 + c;
           if (key > pos_r || key < lo_r) sr[c >> 5][c & 31] = 0xff800000u;      // -inf
-          mx = fmaxf(mx, __uint_as_float(sr[c >> 5][c & 31]));
         }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c >> 5][c & 31]));
       }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};          // four short chains
+#pragma unroll
+      for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c >> 5][c & 31]));
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       mx *= scale_log2;                            // -inf stays -inf
       const bool grow = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
       if (i > 0 && __any_sync(0xffffffffu, grow)) {
@@ -244,13 +272,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       if (grow) m_ref = mx;
       const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
       uint32_t pk[32];
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
         const float p0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), scale_log2, neg_m));
         const float p1 = ex2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), scale_log2, neg_m));
-        l += p0 + p1;
+        l4[(c >> 1) & 3] += p0 + p1;
         pk[c >> 1] = pack2(p0, p1);
       }
+      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       tmem_st32(sbuf, pk);                         // P over the first 32 columns of this S buffer
       tmem_st_wait();
       tc_fence_before();
@@ -301,7 +331,7 @@ extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, 
   if (hd != HD) G2B_REFUSE("attn_prefill_tc: built for head_dim %d, got %d", HD, hd);
   if (page_size != PAGE) G2B_REFUSE("attn_prefill_tc: page size must be %d, got %d", PAGE, page_size);
   if (nkv <= 0 || nh % nkv) G2B_REFUSE("attn_prefill_tc: %d heads are not a multiple of %d kv heads", nh, nkv);
-  if (nh > 65535) G2B_REFUSE("attn_prefill_tc: %d heads", nh);
+  if ((long long)n_tiles * nh > 0x7fffffffLL) G2B_REFUSE("attn_prefill_tc: %d tiles x %d heads", n_tiles, nh);
   if (!status) G2B_REFUSE("attn_prefill_tc: no status word");
   if (((uintptr_t)q | (uintptr_t)cache | (uintptr_t)out) & 15)
     G2B_REFUSE("attn_prefill_tc: q, out and the cache must be 16-byte aligned");
@@ -317,9 +347,10 @@ extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, 
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
     if (e != cudaSuccess) G2B_REFUSE("attn_prefill_tc: shared memory: %s", cudaGetErrorString(e));
+    cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     configured = true;
   }
-  g2b_launch(attn_prefill_tc_kernel, dim3(n_tiles, nh), dim3(THREADS), SMEM_TOTAL, stream, mq, mkv,
+  g2b_launch(attn_prefill_tc_kernel, dim3((unsigned)n_tiles * nh), dim3(THREADS), SMEM_TOTAL, stream, mq, mkv,
              (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, status);
   return g2b_check_launch("attn_prefill_tc");
 }

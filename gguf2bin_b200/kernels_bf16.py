@@ -53,9 +53,14 @@ def check_status() -> None:
         code = int(word.item())
         if code:
             word.zero_()
-            what = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code, "a role")
-            raise KernelError(f"gemm_tc on {dev}: {what} gave up waiting on a barrier (code {code}); "
-                              "the result of that product is invalid")
+            if code == 14:
+                raise KernelError(f"attn_prefill_tc on {dev}: dynamic shared memory does not start on a "
+                                  "1024-byte boundary; nothing was computed")
+            kernel = "attn_prefill_tc" if code > 10 else "gemm_tc"
+            what = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue",
+                    11: "the TMA producer", 12: "the MMA issuer", 13: "a softmax warp"}.get(code, "a role")
+            raise KernelError(f"{kernel} on {dev}: {what} gave up waiting on a barrier (code {code}); "
+                              "the result of that launch is invalid")
 
 
 def _tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
