@@ -6,19 +6,23 @@
 // long tiles of every head start first and the short ones fill in behind them.  Two CTAs fit
 // on an SM (shared memory and tensor memory are sized for that): while one waits on its
 // softmax the other's products run.  Roles by warp:
-//   warp 4, one thread  TMA producer: the 128 x HD query tile once, then per key page the K
+//   warp 8, one thread  TMA producer: the 128 x HD query tile once, then per key page the K
 //                       and V panels of (page, kv head), each as 64-column boxes with 128-byte
 //                       swizzle, into a ring of three K panels and a ring of two V panels (K is
 //                       free again as soon as its S product is done, V only after P.V).
-//   warp 5, one thread  MMA issuer (tcgen05.mma, cta_group::1, kind::f16):
+//   warp 9, one thread  MMA issuer (tcgen05.mma, cta_group::1, kind::f16):
 //                         S[128 x 64]  = Q K^T      (both operands K-major)  -> tensor memory,
 //                                                    two S buffers, always one page ahead
 //                         O[128 x HD] += P V        (P read from tensor memory, V read as
 //                                                    an MN-major operand: keys are its K index)
-//   warps 0..3          softmax, one thread per query row: reads its row of S with tcgen05.ld,
+//   warps 0..7          softmax, 16 query rows per warp (warps w and w + 4 share a quarter of
+//                       the tensor-memory lanes; each takes 16 of its 32 lanes).  S is read
+//                       with the 16-lane shape whose layout is that of a warp-level product's
+//                       accumulator: a thread holds two rows and, with the three other threads
+//                       of its quad, all 64 keys of them, so row maxima are two shuffles.  It
 //                       scales (log2 domain), masks (causal, window), keeps a reference maximum
-//                       and a sum in float, and writes P = 2^(s - m) as packed bfloat16 back
-//                       into the first columns of the same S buffer (tcgen05.st), where the
+//                       and a partial sum per row in float, and writes P = 2^(s - m) as packed
+//                       bfloat16 back into the first columns of the same S buffer, where the
 //                       second product reads it.  O is rescaled in tensor memory only when a
 //                       row's maximum has grown by more than 2^8 since its reference (the
 //                       result is the same function of the scores; the factor just stays
@@ -44,7 +48,8 @@ using namespace tc;
 
 constexpr int PAGE = 64;
 constexpr int BM = 128;
-constexpr int THREADS = 192;
+constexpr int SOFTMAX_WARPS = 8;
+constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
 constexpr int K_STAGES = 3, V_STAGES = 2;
 constexpr int SUBS = HD / 64;                       // 64-column boxes along the head dimension
 constexpr int Q_SUB_BYTES = BM * 128;               // one 128 x 64 box
@@ -74,11 +79,23 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t *>(&v);
 }
 
+#ifdef G2B_ATTN_TIMING
+// Development aid (off unless built with -DG2B_ATTN_TIMING): cycles that the roles of CTA 0
+// spend waiting and working, read back with g2b_attn_prefill_tc_timing.
+__device__ unsigned long long g2b_timing[16];
+#define TICK(v) const long long v = clock64()
+#define TOCK(slot, v) if (blockIdx.x == 0) g2b_timing[slot] += (unsigned long long)(clock64() - v)
+#else
+#define TICK(v)
+#define TOCK(slot, v)
+#endif
+
 __global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_kv, bf16 *__restrict__ out,
                        const int4 *__restrict__ tiles, const int *__restrict__ page_table, int P,
-                       int nh, int nkv, int window, float scale_log2, int *__restrict__ status) {
+                       int nh, int nkv, int window, float scale_log2, int first_wave,
+                       int *__restrict__ status) {
   pdl_launch();
   // The swizzled panels need 1024-byte alignment.  The kernel has no static shared memory, so
   // the dynamic part starts at the aligned base of the window; checked rather than assumed.
@@ -95,7 +112,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const uint32_t k_full0 = smem_addr(bars + 1), k_empty0 = smem_addr(bars + 4);       // [K_STAGES] each
   const uint32_t v_full0 = smem_addr(bars + 7), v_empty0 = smem_addr(bars + 9);       // [V_STAGES] each
   const uint32_t s_ready0 = smem_addr(bars + 11), p_ready0 = smem_addr(bars + 13);    // [2] each
-  const uint32_t pv_done = smem_addr(bars + 15), o_ready = smem_addr(bars + 16);
+  const uint32_t o_ready = smem_addr(bars + 15);
   static_assert(K_STAGES == 3 && V_STAGES == 2, "barrier slots");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -111,27 +128,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     }
     for (int j = 0; j < 2; ++j) {
       mbar_init(s_ready0 + 8 * j, 1);
-      mbar_init(p_ready0 + 8 * j, BM);
+      mbar_init(p_ready0 + 8 * j, SOFTMAX_WARPS * 32);
     }
-    mbar_init(pv_done, 1);
     mbar_init(o_ready, 1);
     mbar_init_fence();
   }
-  if (warp == 5) tmem_alloc(smem_addr(tmem_slot), TMEM_COLS);
+  if (warp == SOFTMAX_WARPS + 1) tmem_alloc(smem_addr(tmem_slot), TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   pdl_wait();                                   // the queries and the cache come from earlier kernels
 
-  const int4 tile = tiles[blockIdx.x / nh];
+  // CTA -> (tile, head).  Items are numbered tile-major, longest tile first.  The first wave
+  // (one CTA on every SM) takes them from the long end.  When everything fits in two waves the
+  // second CTAs of the SMs take the rest from the short end, so that the longest tiles share
+  // their SM with the shortest; with more waves the rest follows longest first.
+  const int n_items = gridDim.x;
+  int item = blockIdx.x;
+  if (item >= first_wave && n_items <= 2 * first_wave) item = n_items - 1 - (item - first_wave);
+  const int4 tile = tiles[item / nh];
   const int b = tile.x, t0 = tile.y, n_rows = tile.z, pos0 = tile.w;
-  const int h = blockIdx.x % nh, kvh = h / (nh / nkv);
+  const int h = item % nh, kvh = h / (nh / nkv);
   const int first_page = window > 0 ? max(0, pos0 - window + 1) / PAGE : 0;
   const int last_page = (pos0 + n_rows - 1) / PAGE;
   const int n_pages = last_page - first_page + 1;
 
-  if (warp == 4) {
+  if (warp == SOFTMAX_WARPS) {
     if (lane == 0) {
       mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
@@ -168,146 +191,219 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       if (!ok) atomicExch(status, ST_PRODUCER);
     }
-  } else if (warp == 5) {
+  } else if (warp == SOFTMAX_WARPS + 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = instr_desc(BM, PAGE, false);
       constexpr uint32_t idesc_pv = instr_desc(BM, HD, true);
+      // descriptors once: only the start-address field (low word) changes between products
+      const uint64_t dq = desc_k_major(smem_addr(q_smem)), dk = desc_k_major(smem_addr(k_smem));
+      const uint64_t dv = desc_mn_major(smem_addr(v_smem), KV_SUB_BYTES);
+      const uint32_t q_lo = (uint32_t)dq, q_hi = (uint32_t)(dq >> 32);
+      const uint32_t k_lo = (uint32_t)dk, k_hi = (uint32_t)(dk >> 32);
+      const uint32_t v_lo = (uint32_t)dv, v_hi = (uint32_t)(dv >> 32);
+      TICK(t_all);
       bool ok = mbar_wait(q_full, 0);
       if (!ok) atomicExch(status, ST_MMA);
-      // S of page i into S buffer i % 2 (needs K of stage i % K_STAGES)
+      // S of page i into S buffer i % 2 (needs K of stage i % K_STAGES).  The softmax warps see
+      // its completion and pass it on to the producer (the K panel is free then).
       auto issue_s = [&](int i) -> bool {
         const int s = i % K_STAGES;
+        TICK(t_k);
         if (!mbar_wait(k_full0 + 8 * s, (i / K_STAGES) & 1)) { atomicExch(status, ST_MMA); return false; }
+        TOCK(1, t_k);
         tc_fence_after();
-        const uint32_t k_addr = smem_addr(k_smem + s * KV_BYTES);
+        const uint32_t ks_lo = k_lo + s * (KV_BYTES >> 4), d_s = tmem + 64 * (i & 1);
+        TICK(t_is);
+        umma_bf16_lh<false>(d_s, q_lo, q_hi, ks_lo, k_hi, idesc_s);
 #pragma unroll
-        for (int sub = 0; sub < SUBS; ++sub)
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem + 64 * (i & 1), desc_k_major(smem_addr(q_smem + sub * Q_SUB_BYTES)) + 2 * k,
-                      desc_k_major(k_addr + sub * KV_SUB_BYTES) + 2 * k, idesc_s, (sub | k) != 0);
-        umma_commit(k_empty0 + 8 * s);             // K of this stage has been read
+        for (int n = 1; n < SUBS * 4; ++n)
+          umma_bf16_lh<true>(d_s, q_lo + (n / 4) * (Q_SUB_BYTES >> 4) + 2 * (n % 4), q_hi,
+                             ks_lo + (n / 4) * (KV_SUB_BYTES >> 4) + 2 * (n % 4), k_hi, idesc_s);
+        TOCK(9, t_is);
+        TICK(t_cs);
         umma_commit(s_ready0 + 8 * (i & 1));
+        TOCK(10, t_cs);
         return true;
       };
       if (ok) ok = issue_s(0);
       if (ok && n_pages > 1) ok = issue_s(1);
       for (int i = 0; i < n_pages && ok; ++i) {
         const int s = i % V_STAGES;
-        if (!mbar_wait(v_full0 + 8 * s, (i / V_STAGES) & 1) ||
-            !mbar_wait(p_ready0 + 8 * (i & 1), (i >> 1) & 1)) { atomicExch(status, ST_MMA); break; }
+        TICK(t_v);
+        if (!mbar_wait(v_full0 + 8 * s, (i / V_STAGES) & 1)) { atomicExch(status, ST_MMA); break; }
+        TOCK(2, t_v);
+        TICK(t_p);
+        if (!mbar_wait(p_ready0 + 8 * (i & 1), (i >> 1) & 1)) { atomicExch(status, ST_MMA); break; }
+        TOCK(3, t_p);
         tc_fence_after();
         // O += P V: the keys are the K index, 16 per MMA: 8 packed columns of P, 16 rows of V
-        const uint32_t v_addr = smem_addr(v_smem + s * KV_BYTES);
+        const uint32_t vs_lo = v_lo + s * (KV_BYTES >> 4), p_addr = tmem + 64 * (i & 1);
+        TICK(t_ipv);
 #pragma unroll
         for (int k = 0; k < PAGE / 16; ++k)
-          umma_bf16_ts(tmem + O_COL0, tmem + 64 * (i & 1) + 8 * k,
-                       desc_mn_major(v_addr + k * 16 * 128, KV_SUB_BYTES), idesc_pv, (i | k) != 0);
-        umma_commit(v_empty0 + 8 * s);             // V of this stage has been read
-        umma_commit(pv_done);                      // O holds pages 0..i; P of page i has been read
+          umma_bf16_ts_lh(tmem + O_COL0, p_addr + 8 * k, vs_lo + k * (16 * 128 >> 4), v_hi, idesc_pv,
+                          k == 0 ? (uint32_t)(i != 0) : 1u);
+        TOCK(11, t_ipv);
+        // V of this stage has been read, O holds pages 0..i, P of page i has been read
+        umma_commit(v_empty0 + 8 * s);
         if (i + 2 < n_pages) ok = issue_s(i + 2);  // overwrites the S/P buffer of page i (in order)
       }
       umma_commit(o_ready);
+      TOCK(0, t_all);
     }
   } else {
-    // softmax: thread (warp, lane) owns query row r and tensor-memory lane r
-    const int r = warp * 32 + lane;
-    const int pos_r = pos0 + r;
-    const int lo_r = window > 0 ? max(0, pos_r - window + 1) : 0;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-    float m_ref = -INFINITY, l = 0.f;
+    // softmax: this warp owns rows row0 .. row0 + 15 (tensor-memory lanes of the same numbers);
+    // the thread holds rows rA = row0 + g and rB = rA + 8, keys 8j + 2c, 8j + 2c + 1 of a page
+    const int g = lane >> 2, c = lane & 3;
+    const int row0 = (warp & 3) * 32 + (warp >> 2) * 16;
+    const int rA = row0 + g, rB = rA + 8;
+    const int pos_a = pos0 + rA, pos_b = pos0 + rB;
+    const int lo_a = window > 0 ? max(0, pos_a - window + 1) : 0;
+    const int lo_b = window > 0 ? max(0, pos_b - window + 1) : 0;
+    const uint32_t lane_base = tmem + ((uint32_t)row0 << 16);
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;      // l: this thread's keys only
     bool ok = true;
+#ifdef G2B_ATTN_TIMING
+    const bool timed = threadIdx.x == 0;
+#endif
+    TICK(t_sm);
     for (int i = 0; i < n_pages && ok; ++i) {
       const uint32_t sbuf = lane_base + 64 * (i & 1);
+      TICK(t_s);
       if (!mbar_wait(s_ready0 + 8 * (i & 1), (i >> 1) & 1)) {
         if (lane == 0) atomicExch(status, ST_SOFTMAX);
         ok = false;
         break;
       }
+#ifdef G2B_ATTN_TIMING
+      if (timed) { TOCK(5, t_s); }
+#endif
+      if (threadIdx.x == 0) mbar_arrive(k_empty0 + 8 * (i % K_STAGES));       // S of page i is done: K is free
       tc_fence_after();
-      uint32_t sr[2][32];
-      tmem_ld32(sbuf, sr[0]);
-      tmem_ld32(sbuf + 32, sr[1]);
+      uint32_t sr[32];                             // [4j + 2s + e]: row (s ? rB : rA), key 8j + 2c + e
+      TICK(t_ld);
+      tmem_ld_16x256b_x8(sbuf, sr);
       tmem_ld_wait();
+#ifdef G2B_ATTN_TIMING
+      if (timed) { TOCK(6, t_ld); }
+#endif
       const int key0 = (first_page + i) * PAGE;
       // raw scores stay in sr; the scale (> 0) is applied to the maximum and inside the exponent.
-      // Only pages that cross this row's limits are masked (warp-uniform test on the warp's rows).
-      const int warp_pos_min = pos0 + warp * 32, warp_pos_max = warp_pos_min + 31;
+      // Only pages that cross the limits of the warp's rows are masked (warp-uniform test).
+      const int warp_pos_min = pos0 + row0, warp_pos_max = warp_pos_min + 15;
       const bool partial = key0 + PAGE - 1 > warp_pos_min ||
                            (window > 0 && key0 < max(0, warp_pos_max - window + 1));
       if (partial) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const int key = key0 + c;
-          if (key > pos_r || key < lo_r) sr[c >> 5][c & 31] = 0xff800000u;      // -inf
-        }
-      }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};          // four short chains
+        for (int j = 0; j < 8; ++j)
 #pragma unroll
-      for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c >> 5][c & 31]));
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      mx *= scale_log2;                            // -inf stays -inf
-      const bool grow = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
-      if (i > 0 && __any_sync(0xffffffffu, grow)) {
-        // O must hold pages 0..i-1 completely before it is rescaled
-        if (!mbar_wait(pv_done, (i - 1) & 1)) {
+          for (int e = 0; e < 2; ++e) {
+            const int key = key0 + 8 * j + 2 * c + e;
+            if (key > pos_a || key < lo_a) sr[4 * j + e] = 0xff800000u;           // -inf
+            if (key > pos_b || key < lo_b) sr[4 * j + 2 + e] = 0xff800000u;
+          }
+      }
+      float mxa[2] = {-INFINITY, -INFINITY}, mxb[2] = {-INFINITY, -INFINITY};       // short chains
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        mxa[j & 1] = fmaxf(mxa[j & 1], fmaxf(__uint_as_float(sr[4 * j]), __uint_as_float(sr[4 * j + 1])));
+        mxb[j & 1] = fmaxf(mxb[j & 1], fmaxf(__uint_as_float(sr[4 * j + 2]), __uint_as_float(sr[4 * j + 3])));
+      }
+      float mx_a = fmaxf(mxa[0], mxa[1]), mx_b = fmaxf(mxb[0], mxb[1]);
+      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+      mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+      mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+      mx_a *= scale_log2;                          // -inf stays -inf
+      mx_b *= scale_log2;
+      const bool grow_a = mx_a > m_a + RESCALE_STEP || (m_a == -INFINITY && mx_a > -INFINITY);
+      const bool grow_b = mx_b > m_b + RESCALE_STEP || (m_b == -INFINITY && mx_b > -INFINITY);
+      if (i > 0 && __any_sync(0xffffffffu, grow_a || grow_b)) {
+        // O must hold pages 0..i-1 completely before it is rescaled: P.V of page i-1 is done when
+        // its V panel is released (the next release of that panel needs P of page i+1, so the
+        // phase cannot run ahead of this wait)
+        if (!mbar_wait(v_empty0 + 8 * ((i - 1) % V_STAGES), ((i - 1) / V_STAGES) & 1)) {
           if (lane == 0) atomicExch(status, ST_SOFTMAX);
           ok = false;
           break;
         }
         tc_fence_after();
-        const float f = grow ? ex2(m_ref - mx) : 1.f;      // 0 for a row that had seen no key
+        const float f_a = grow_a ? ex2(m_a - mx_a) : 1.f;      // 0 for a row that had seen no key
+        const float f_b = grow_b ? ex2(m_b - mx_b) : 1.f;
 #pragma unroll 1
-        for (int c0 = 0; c0 < HD; c0 += 32) {
+        for (int c0 = 0; c0 < HD; c0 += 64) {
           uint32_t o[32];
-          tmem_ld32(lane_base + O_COL0 + c0, o);
+          tmem_ld_16x256b_x8(lane_base + O_COL0 + c0, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * f);
-          tmem_st32(lane_base + O_COL0 + c0, o);
+          for (int j = 0; j < 8; ++j) {
+            o[4 * j] = __float_as_uint(__uint_as_float(o[4 * j]) * f_a);
+            o[4 * j + 1] = __float_as_uint(__uint_as_float(o[4 * j + 1]) * f_a);
+            o[4 * j + 2] = __float_as_uint(__uint_as_float(o[4 * j + 2]) * f_b);
+            o[4 * j + 3] = __float_as_uint(__uint_as_float(o[4 * j + 3]) * f_b);
+          }
+          tmem_st_16x256b_x8(lane_base + O_COL0 + c0, o);
         }
         tmem_st_wait();
-        l *= f;
+        l_a *= f_a;
+        l_b *= f_b;
       }
-      if (grow) m_ref = mx;
-      const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
-      uint32_t pk[32];
-      float l4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (grow_a) m_a = mx_a;
+      if (grow_b) m_b = mx_b;
+      const float neg_a = m_a == -INFINITY ? 0.f : -m_a;
+      const float neg_b = m_b == -INFINITY ? 0.f : -m_b;
+      uint32_t pk[16];                             // [2j + s]: row (s ? rB : rA), packed column 4j + c
+      float la2[2] = {0.f, 0.f}, lb2[2] = {0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
-        const float p0 = ex2(fmaf(__uint_as_float(sr[c >> 5][c & 31]), scale_log2, neg_m));
-        const float p1 = ex2(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), scale_log2, neg_m));
-        l4[(c >> 1) & 3] += p0 + p1;
-        pk[c >> 1] = pack2(p0, p1);
+      for (int j = 0; j < 8; ++j) {
+        const float a0 = ex2(fmaf(__uint_as_float(sr[4 * j]), scale_log2, neg_a));
+        const float a1 = ex2(fmaf(__uint_as_float(sr[4 * j + 1]), scale_log2, neg_a));
+        const float b0 = ex2(fmaf(__uint_as_float(sr[4 * j + 2]), scale_log2, neg_b));
+        const float b1 = ex2(fmaf(__uint_as_float(sr[4 * j + 3]), scale_log2, neg_b));
+        la2[j & 1] += a0 + a1;
+        lb2[j & 1] += b0 + b1;
+        pk[2 * j] = pack2(a0, a1);
+        pk[2 * j + 1] = pack2(b0, b1);
       }
-      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-      tmem_st32(sbuf, pk);                         // P over the first 32 columns of this S buffer
+      l_a += la2[0] + la2[1];
+      l_b += lb2[0] + lb2[1];
+      TICK(t_st);
+      tmem_st_16x128b_x8(sbuf, pk);                // P over the first 32 columns of this S buffer
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(p_ready0 + 8 * (i & 1));
+#ifdef G2B_ATTN_TIMING
+      if (timed) { TOCK(7, t_st); }
+#endif
     }
+#ifdef G2B_ATTN_TIMING
+    if (timed) { TOCK(4, t_sm); g2b_timing[8] = (unsigned long long)n_pages; }
+#endif
     if (ok) {
       if (!mbar_wait(o_ready, 0)) {
         if (lane == 0) atomicExch(status, ST_SOFTMAX);
       } else {
         tc_fence_after();
-        const float inv = 1.f / l;
-        bf16 *op = out + ((size_t)(t0 + r) * nh + h) * HD;
+        l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+        l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+        const float inv_a = 1.f / l_a, inv_b = 1.f / l_b;
+        bf16 *op_a = out + ((size_t)(t0 + rA) * nh + h) * HD + 2 * c;
+        bf16 *op_b = out + ((size_t)(t0 + rB) * nh + h) * HD + 2 * c;
 #pragma unroll 1
-        for (int c0 = 0; c0 < HD; c0 += 32) {
+        for (int c0 = 0; c0 < HD; c0 += 64) {
           uint32_t o[32];
-          tmem_ld32(lane_base + O_COL0 + c0, o);
+          tmem_ld_16x256b_x8(lane_base + O_COL0 + c0, o);
           tmem_ld_wait();
-          if (r < n_rows) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 v;
-              v.x = pack2(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
-              v.y = pack2(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
-              v.z = pack2(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
-              v.w = pack2(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
-              *reinterpret_cast<uint4 *>(op + c0 + j) = v;
-            }
+          for (int j = 0; j < 8; ++j) {
+            if (rA < n_rows)
+              *reinterpret_cast<uint32_t *>(op_a + c0 + 8 * j) =
+                  pack2(__uint_as_float(o[4 * j]) * inv_a, __uint_as_float(o[4 * j + 1]) * inv_a);
+            if (rB < n_rows)
+              *reinterpret_cast<uint32_t *>(op_b + c0 + 8 * j) =
+                  pack2(__uint_as_float(o[4 * j + 2]) * inv_b, __uint_as_float(o[4 * j + 3]) * inv_b);
           }
         }
       }
@@ -315,7 +411,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == SOFTMAX_WARPS + 1) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
@@ -343,7 +439,11 @@ extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, 
   rc = get_map(&mkv, cache, n_cache_pages * 2 * nkv * PAGE, HD, HD, PAGE);
   if (rc) G2B_REFUSE("attn_prefill_tc: tensor map of the cache failed (%d)", rc);
   static bool configured = false;
+  static int n_sms = 0;
   if (!configured) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
     if (e != cudaSuccess) G2B_REFUSE("attn_prefill_tc: shared memory: %s", cudaGetErrorString(e));
@@ -351,8 +451,19 @@ extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, 
     configured = true;
   }
   g2b_launch(attn_prefill_tc_kernel, dim3((unsigned)n_tiles * nh), dim3(THREADS), SMEM_TOTAL, stream, mq, mkv,
-             (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, status);
+             (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, n_sms, status);
   return g2b_check_launch("attn_prefill_tc");
 }
 
 extern "C" int g2b_attn_prefill_tc_tile_rows() { return BM; }
+
+#ifdef G2B_ATTN_TIMING
+// Copies the 16 counters to `out` and clears them.
+extern "C" int g2b_attn_prefill_tc_timing(unsigned long long *out) {
+  static unsigned long long zero[16] = {0};
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, g2b_timing, sizeof(zero));
+  cudaMemcpyToSymbol(g2b_timing, zero, sizeof(zero));
+  return 0;
+}
+#endif
