@@ -83,11 +83,15 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // Development aid (off unless built with -DG2B_ATTN_TIMING): cycles that the roles of CTA 0
 // spend waiting and working, read back with g2b_attn_prefill_tc_timing.
 __device__ unsigned long long g2b_timing[16];
+#define TDECL(slot) long long tacc_##slot = 0
 #define TICK(v) const long long v = clock64()
-#define TOCK(slot, v) if (blockIdx.x == 0) g2b_timing[slot] += (unsigned long long)(clock64() - v)
+#define TOCK(slot, v) tacc_##slot += clock64() - v
+#define TFLUSH(slot) if (blockIdx.x == 0) g2b_timing[slot] = (unsigned long long)tacc_##slot
 #else
+#define TDECL(slot)
 #define TICK(v)
 #define TOCK(slot, v)
+#define TFLUSH(slot)
 #endif
 
 __global__ void __launch_bounds__(THREADS, 2)
@@ -201,6 +205,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       const uint32_t q_lo = (uint32_t)dq, q_hi = (uint32_t)(dq >> 32);
       const uint32_t k_lo = (uint32_t)dk, k_hi = (uint32_t)(dk >> 32);
       const uint32_t v_lo = (uint32_t)dv, v_hi = (uint32_t)(dv >> 32);
+      TDECL(0); TDECL(1); TDECL(2); TDECL(3); TDECL(9); TDECL(10); TDECL(11);
       TICK(t_all);
       bool ok = mbar_wait(q_full, 0);
       if (!ok) atomicExch(status, ST_MMA);
@@ -250,6 +255,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       umma_commit(o_ready);
       TOCK(0, t_all);
+      TFLUSH(0); TFLUSH(1); TFLUSH(2); TFLUSH(3); TFLUSH(9); TFLUSH(10); TFLUSH(11);
     }
   } else {
     // softmax: this warp owns rows row0 .. row0 + 15 (tensor-memory lanes of the same numbers);
@@ -263,9 +269,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const uint32_t lane_base = tmem + ((uint32_t)row0 << 16);
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;      // l: this thread's keys only
     bool ok = true;
-#ifdef G2B_ATTN_TIMING
-    const bool timed = threadIdx.x == 0;
-#endif
+    TDECL(4); TDECL(5); TDECL(6); TDECL(7);
     TICK(t_sm);
     for (int i = 0; i < n_pages && ok; ++i) {
       const uint32_t sbuf = lane_base + 64 * (i & 1);
@@ -275,18 +279,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         ok = false;
         break;
       }
-#ifdef G2B_ATTN_TIMING
-      if (timed) { TOCK(5, t_s); }
-#endif
+      TOCK(5, t_s);
       if (threadIdx.x == 0) mbar_arrive(k_empty0 + 8 * (i % K_STAGES));       // S of page i is done: K is free
       tc_fence_after();
       uint32_t sr[32];                             // [4j + 2s + e]: row (s ? rB : rA), key 8j + 2c + e
       TICK(t_ld);
       tmem_ld_16x256b_x8(sbuf, sr);
       tmem_ld_wait();
-#ifdef G2B_ATTN_TIMING
-      if (timed) { TOCK(6, t_ld); }
-#endif
+      TOCK(6, t_ld);
       const int key0 = (first_page + i) * PAGE;
       // raw scores stay in sr; the scale (> 0) is applied to the maximum and inside the exponent.
       // Only pages that cross the limits of the warp's rows are masked (warp-uniform test).
@@ -372,13 +372,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(p_ready0 + 8 * (i & 1));
-#ifdef G2B_ATTN_TIMING
-      if (timed) { TOCK(7, t_st); }
-#endif
+      TOCK(7, t_st);
     }
-#ifdef G2B_ATTN_TIMING
-    if (timed) { TOCK(4, t_sm); g2b_timing[8] = (unsigned long long)n_pages; }
-#endif
+    TOCK(4, t_sm);
+    if (threadIdx.x == 0) { TFLUSH(4); TFLUSH(5); TFLUSH(6); TFLUSH(7); }
     if (ok) {
       if (!mbar_wait(o_ready, 0)) {
         if (lane == 0) atomicExch(status, ST_SOFTMAX);

@@ -52,6 +52,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
 // true when the phase with the given parity has completed; false after SPIN_LIMIT polls
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
@@ -74,6 +77,27 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// shared -> global tile store (clipped at the tensor's bounds) and the same as an addition
+// of floats; both join the thread's current bulk group
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
+               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];\n"
+               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+// at most N of the thread's bulk groups still read their shared-memory source
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(N) : "memory");
+}
+template <int N> __device__ __forceinline__ void bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;\n" ::"n"(N) : "memory");
+}
+// makes the warp's writes to shared memory visible to the bulk-copy unit
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
                                           uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -133,6 +157,87 @@ template <int BN, int STAGES> struct Smem {
   static constexpr int BARRIER_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int TOTAL = BARRIER_OFFSET + 128 + 1024;   // barriers + tmem slot + alignment slack
 };
+
+// Epilogue of one 128 x BN tile by one of the four epilogue warps: warp w owns accumulator
+// lanes (rows) 32w .. 32w+31 and reads them 32 columns at a time.  `scr` is 32 x 33 floats of
+// shared memory of this warp (used by the float outputs to turn rows into coalesced stores).
+template <int BN, int EPI>
+__device__ __forceinline__ void epilogue_tile(uint32_t tmem, float *scr, void *__restrict__ Cv, int m0, int n0,
+                                              int M, int N, int ldc, int warp, int lane) {
+      const int row = m0 + warp * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        const int n = n0 + c0;
+        if (EPI == EPI_STORE_F32 || EPI == EPI_ACCUM_F32) {
+          // through shared memory, so that a warp touches 128 contiguous bytes of one row of
+          // C at a time (the operand stages are free: every MMA has completed)
+          if (n >= N) continue;                              // uniform over the warp
+#pragma unroll
+          for (int j = 0; j < 32; ++j) scr[lane * 33 + j] = __uint_as_float(r[j]);
+          __syncwarp();
+          const bool col_ok = n + lane < N;
+          float *cbase = (float *)Cv + (size_t)(m0 + warp * 32) * ldc + n + lane;
+#pragma unroll 8
+          for (int rr = 0; rr < 32; ++rr) {
+            if (col_ok && m0 + warp * 32 + rr < M) {
+              float *p = cbase + (size_t)rr * ldc;
+              const float v = scr[rr * 33 + lane];
+              // one thread adds to an element once per launch, so the reduction (no value
+              // comes back, nothing waits for the old one) gives the same sum as load-add-store
+              if (EPI == EPI_ACCUM_F32) atomicAdd(p, v);
+              else *p = v;
+            }
+          }
+          __syncwarp();
+          continue;
+        }
+        if (row >= M || n >= N) continue;
+        if (EPI == EPI_SWIGLU_BF16) {
+          // columns 16b .. 16b+7 are gates, 16b+8 .. 16b+15 the ups of the same outputs
+          bf16 *dst = (bf16 *)Cv + (size_t)row * ldc + (n >> 1);
+          float h[16];
+#pragma unroll
+          for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float gate = __uint_as_float(r[16 * blk + j]);
+              const float up = __uint_as_float(r[16 * blk + 8 + j]);
+              h[8 * blk + j] = __fdividef(gate, 1.f + __expf(-gate)) * up;
+            }
+          if (n + 32 <= N && ((((uintptr_t)dst) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 8) {
+              uint4 v;
+              v.x = pack2f(h[j], h[j + 1]); v.y = pack2f(h[j + 2], h[j + 3]);
+              v.z = pack2f(h[j + 4], h[j + 5]); v.w = pack2f(h[j + 6], h[j + 7]);
+              *reinterpret_cast<uint4 *>(dst + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (n + 16 * blk + 8 + j < N) dst[8 * blk + j] = __float2bfloat16_rn(h[8 * blk + j]);
+          }
+        } else if (EPI == EPI_STORE_BF16) {
+          bf16 *dst = (bf16 *)Cv + (size_t)row * ldc + n;
+          if (n + 32 <= N && ((((uintptr_t)dst) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 v;
+              v.x = pack2(r[j], r[j + 1]); v.y = pack2(r[j + 2], r[j + 3]);
+              v.z = pack2(r[j + 4], r[j + 5]); v.w = pack2(r[j + 6], r[j + 7]);
+              *reinterpret_cast<uint4 *>(dst + j) = v;
+            }
+          } else {
+            for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+          }
+        }
+      }
+}
 
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(THREADS)
@@ -213,80 +318,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (lane == 0) atomicExch(status, ST_EPILOGUE_TIMEOUT);
     } else {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      const int row = m0 + warp * 32 + lane;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
-        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-        const int n = n0 + c0;
-        if (EPI == EPI_STORE_F32 || EPI == EPI_ACCUM_F32) {
-          // through shared memory, so that a warp touches 128 contiguous bytes of one row of
-          // C at a time (the operand stages are free: every MMA has completed)
-          if (n >= N) continue;                              // uniform over the warp
-          float *scr = reinterpret_cast<float *>(smem) + warp * (32 * 33);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) scr[lane * 33 + j] = __uint_as_float(r[j]);
-          __syncwarp();
-          const bool col_ok = n + lane < N;
-          float *cbase = (float *)Cv + (size_t)(m0 + warp * 32) * ldc + n + lane;
-#pragma unroll 8
-          for (int rr = 0; rr < 32; ++rr) {
-            if (col_ok && m0 + warp * 32 + rr < M) {
-              float *p = cbase + (size_t)rr * ldc;
-              const float v = scr[rr * 33 + lane];
-              // one thread adds to an element once per launch, so the reduction (no value
-              // comes back, nothing waits for the old one) gives the same sum as load-add-store
-              if (EPI == EPI_ACCUM_F32) atomicAdd(p, v);
-              else *p = v;
-            }
-          }
-          __syncwarp();
-          continue;
-        }
-        if (row >= M || n >= N) continue;
-        if (EPI == EPI_SWIGLU_BF16) {
-          // columns 16b .. 16b+7 are gates, 16b+8 .. 16b+15 the ups of the same outputs
-          bf16 *dst = (bf16 *)Cv + (size_t)row * ldc + (n >> 1);
-          float h[16];
-#pragma unroll
-          for (int blk = 0; blk < 2; ++blk)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float gate = __uint_as_float(r[16 * blk + j]);
-              const float up = __uint_as_float(r[16 * blk + 8 + j]);
-              h[8 * blk + j] = (gate / (1.f + __expf(-gate))) * up;
-            }
-          if (n + 32 <= N && ((((uintptr_t)dst) & 15) == 0)) {
-#pragma unroll
-            for (int j = 0; j < 16; j += 8) {
-              uint4 v;
-              v.x = pack2f(h[j], h[j + 1]); v.y = pack2f(h[j + 2], h[j + 3]);
-              v.z = pack2f(h[j + 4], h[j + 5]); v.w = pack2f(h[j + 6], h[j + 7]);
-              *reinterpret_cast<uint4 *>(dst + j) = v;
-            }
-          } else {
-#pragma unroll
-            for (int blk = 0; blk < 2; ++blk)
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (n + 16 * blk + 8 + j < N) dst[8 * blk + j] = __float2bfloat16_rn(h[8 * blk + j]);
-          }
-        } else if (EPI == EPI_STORE_BF16) {
-          bf16 *dst = (bf16 *)Cv + (size_t)row * ldc + n;
-          if (n + 32 <= N && ((((uintptr_t)dst) & 15) == 0)) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 v;
-              v.x = pack2(r[j], r[j + 1]); v.y = pack2(r[j + 2], r[j + 3]);
-              v.z = pack2(r[j + 4], r[j + 5]); v.w = pack2(r[j + 6], r[j + 7]);
-              *reinterpret_cast<uint4 *>(dst + j) = v;
-            }
-          } else {
-            for (int j = 0; j < 32 && n + j < N; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-          }
-        }
-      }
+      epilogue_tile<BN, EPI>(tmem, reinterpret_cast<float *>(smem) + warp * (32 * 33), Cv, m0, n0, M, N, ldc, warp, lane);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -294,6 +326,259 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 5) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"((uint32_t)BN));
+  }
+}
+
+// Epilogue of one 128 x BN tile through shared memory and tile stores.  Warp w owns rows
+// 32w .. 32w+31; a thread owns one row.  Per box of 128 bytes per row (64 bfloat16 or 32 float
+// outputs) the thread writes its row into a 32 x 128-byte staging buffer of its warp in the
+// 128-byte swizzle (16-byte chunk c of row r at chunk c ^ (r % 8): conflict-free), and lane 0
+// hands the box to the bulk-copy unit, which writes whole rows of C and clips at M and N; for
+// the accumulating epilogue it adds instead (one contributor per element and launch, so the
+// sum does not depend on any order).  Two staging buffers per warp: the copy of one box runs
+// while the next is filled.  The accumulator loads run one chunk ahead of their use.
+// `box` counts the boxes this warp has issued so far (selects the buffer).
+template <int BN, int EPI>
+__device__ __forceinline__ void epilogue_tile_bulk(uint32_t tmem, unsigned char *stage, const CUtensorMap *map_c,
+                                                   int m0, int n0, int M, int N, int warp, int lane,
+                                                   uint32_t &box) {
+  constexpr int CHUNKS = BN / 32;
+  const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+  const int y = m0 + warp * 32;
+  uint32_t r[2][32];
+  tmem_ld32(lane_addr, r[0]);
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+    if (c + 1 < CHUNKS) tmem_ld32(lane_addr + 32 * (c + 1), r[(c + 1) & 1]);
+    const uint32_t(&v)[32] = r[c & 1];
+    // which 16-byte chunks of the row this accumulator chunk fills, and whether it completes a box
+    constexpr int PER_BOX = EPI == EPI_SWIGLU_BF16 ? 4 : (EPI == EPI_STORE_BF16 ? 2 : 1);
+    const int part = c % PER_BOX;
+    if (part == 0) {
+      // the buffer's previous box (two boxes ago) must have been read
+      if (lane == 0) bulk_wait_read<1>();
+      __syncwarp();
+    }
+    unsigned char *buf = stage + (box & 1) * 4096;
+    const uint32_t row_addr = smem_addr(buf) + lane * 128;
+    auto put = [&](int chunk, uint4 val) {
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(row_addr + ((chunk ^ (lane & 7)) << 4)),
+                   "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w) : "memory");
+    };
+    if (EPI == EPI_STORE_F32 || EPI == EPI_ACCUM_F32) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) put(j, make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+    } else if (EPI == EPI_STORE_BF16) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        put(4 * part + j, make_uint4(pack2(v[8 * j], v[8 * j + 1]), pack2(v[8 * j + 2], v[8 * j + 3]),
+                                     pack2(v[8 * j + 4], v[8 * j + 5]), pack2(v[8 * j + 6], v[8 * j + 7])));
+    } else {
+      // columns 16b .. 16b+7 are gates, 16b+8 .. 16b+15 the ups of the same outputs
+      float h[16];
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float gate = __uint_as_float(v[16 * blk + j]);
+          const float up = __uint_as_float(v[16 * blk + 8 + j]);
+          h[8 * blk + j] = __fdividef(gate, 1.f + __expf(-gate)) * up;
+        }
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        put(2 * part + j, make_uint4(pack2f(h[8 * j], h[8 * j + 1]), pack2f(h[8 * j + 2], h[8 * j + 3]),
+                                     pack2f(h[8 * j + 4], h[8 * j + 5]), pack2f(h[8 * j + 6], h[8 * j + 7])));
+    }
+    if (part == PER_BOX - 1) {
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const int first_col = n0 + 32 * (c - part);            // accumulator column of the box
+        if (first_col < N && y < M) {                          // a box wholly outside C is not issued
+          const int x = EPI == EPI_SWIGLU_BF16 ? first_col >> 1 : first_col;
+          if (EPI == EPI_ACCUM_F32) tma_reduce_add_2d(map_c, smem_addr(buf), x, y);
+          else tma_store_2d(map_c, smem_addr(buf), x, y);
+        }
+        bulk_commit();                                        // an empty group keeps the count in step
+      }
+      ++box;
+    }
+  }
+}
+
+// ---- persistent variant -----------------------------------------------------------------
+// One CTA per SM walks over tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (tile t covers
+// rows 128 * (t % tiles_m), columns BN * (t / tiles_m): the CTAs that run at the same time
+// share a few panels of W and all of A in the L2).  The accumulator is double-buffered in
+// tensor memory (2 x BN columns): while the epilogue warps drain tile j, the MMAs of tile j+1
+// run, and the producer's ring of stages never drains between tiles.  Same roles, same bounded
+// waits and status codes as above.
+#ifdef G2B_GEMM_TIMING
+// Development aid (off unless built with -DG2B_GEMM_TIMING): cycles that the roles of CTA 0
+// spend waiting and working, read back with g2b_gemm_tc_timing.
+__device__ unsigned long long g2b_timing[16];
+#define TDECL(slot) long long tacc_##slot = 0
+#define TICK(v) const long long v = clock64()
+#define TOCK(slot, v) tacc_##slot += clock64() - v
+#define TFLUSH(slot) if (blockIdx.x == 0) g2b_timing[slot] = (unsigned long long)tacc_##slot
+#else
+#define TDECL(slot)
+#define TICK(v)
+#define TOCK(slot, v)
+#define TFLUSH(slot)
+#endif
+
+template <int BN, int STAGES> struct SmemP {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int SCRATCH_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int SCRATCH_BYTES = 4 * 2 * 4096;          // two 32 x 128-byte boxes per epilogue warp
+  static constexpr int BARRIER_OFFSET = SCRATCH_OFFSET + SCRATCH_BYTES;
+  static constexpr int TOTAL = BARRIER_OFFSET + 8 * (2 * STAGES + 4) + 16 + 1024;   // + barriers, slot, alignment slack
+};
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                          const __grid_constant__ CUtensorMap map_c, int M, int N, int K,
+                          int *__restrict__ status) {
+  pdl_launch();
+  extern __shared__ unsigned char smem_raw[];
+  using S = SmemP<BN, STAGES>;
+  unsigned char *smem = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::BARRIER_OFFSET);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+  const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES);
+  const uint32_t acc_full0 = smem_addr(bars + 2 * STAGES), acc_empty0 = smem_addr(bars + 2 * STAGES + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nkb = (K + BK - 1) / BK;
+  const int tiles_m = (M + BM - 1) / BM;
+  const int n_tiles = tiles_m * ((N + BN - 1) / BN);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full0 + 8 * b, 1);
+      mbar_init(acc_empty0 + 8 * b, 4);            // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                     smem_addr(tmem_slot)), "r"((uint32_t)(2 * BN)));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+  pdl_wait();
+
+  if (warp == 4) {
+    if (lane == 0) {
+      uint32_t g = 0;                                // k-blocks loaded so far, over all tiles
+      bool ok = true;
+      TDECL(0); TDECL(1);
+      TICK(t_prod);
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+        for (int kb = 0; kb < nkb; ++kb, ++g) {
+          const uint32_t s = g % STAGES;
+          TICK(t_e);
+          if (g >= STAGES && !mbar_wait(empty0 + 8 * s, ((g / STAGES) - 1) & 1)) {
+            atomicExch(status, ST_PRODUCER_TIMEOUT);
+            ok = false;
+            break;
+          }
+          TOCK(1, t_e);
+          const uint32_t a_dst = smem_addr(smem + s * S::STAGE_BYTES);
+          mbar_expect_tx(full0 + 8 * s, S::STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, kb * BK, m0, full0 + 8 * s);
+          tma_load_2d(a_dst + S::A_BYTES, &map_w, kb * BK, n0, full0 + 8 * s);
+        }
+      }
+      TOCK(0, t_prod);
+      TFLUSH(0); TFLUSH(1);
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BN);
+      uint32_t g = 0, j = 0;                         // k-blocks and tiles so far
+      bool ok = true;
+      TDECL(2); TDECL(3); TDECL(4); TDECL(5);
+      TICK(t_mma);
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++j) {
+        const uint32_t buf = j & 1;
+        // the epilogue must have drained this accumulator (it was used by tile j - 2)
+        TICK(t_ae);
+        if (j >= 2 && !mbar_wait(acc_empty0 + 8 * buf, ((j >> 1) - 1) & 1)) {
+          atomicExch(status, ST_MMA_TIMEOUT);
+          break;
+        }
+        TOCK(3, t_ae);
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        for (int kb = 0; kb < nkb; ++kb, ++g) {
+          const uint32_t s = g % STAGES;
+          TICK(t_f);
+          if (!mbar_wait(full0 + 8 * s, (g / STAGES) & 1)) {
+            atomicExch(status, ST_MMA_TIMEOUT);
+            ok = false;
+            break;
+          }
+          TOCK(4, t_f);
+          asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+          const uint32_t a_addr = smem_addr(smem + s * S::STAGE_BYTES);
+          const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(a_addr + S::A_BYTES);
+          TICK(t_i);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_bf16(tmem + buf * BN, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit(empty0 + 8 * s);
+          TOCK(5, t_i);
+        }
+        if (ok) umma_commit(acc_full0 + 8 * buf);    // this tile's MMAs have completed
+      }
+      TOCK(2, t_mma);
+      TFLUSH(2); TFLUSH(3); TFLUSH(4); TFLUSH(5);
+    }
+  } else {
+    unsigned char *stage = smem + S::SCRATCH_OFFSET + warp * (2 * 4096);
+    uint32_t j = 0, box = 0;
+    TDECL(6); TDECL(7); TDECL(8);
+    TICK(t_epi);
+    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++j) {
+      const uint32_t buf = j & 1;
+      TICK(t_af);
+      if (!mbar_wait(acc_full0 + 8 * buf, (j >> 1) & 1)) {
+        if (lane == 0) atomicExch(status, ST_EPILOGUE_TIMEOUT);
+        break;
+      }
+      TOCK(7, t_af);
+      TOCK(8, t_af - 1 + clock64());               // counts tiles (adds 1)
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+      epilogue_tile_bulk<BN, EPI>(tmem + buf * BN, stage, &map_c, m0, n0, M, N, warp, lane, box);
+      // every load of this warp from the accumulator has completed (each is waited for)
+      asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+    }
+    if (lane == 0) bulk_wait<0>();                 // the staging buffers are read and C is written
+    TOCK(6, t_epi);
+    if (threadIdx.x == 0) { TFLUSH(6); TFLUSH(7); TFLUSH(8); }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"((uint32_t)(2 * BN)));
   }
 }
 
@@ -318,7 +603,7 @@ static EncodeTiledFn encode_fn() {
 // Encoded maps are kept by (address, rows, K, stride, box): weights and the step's scratch
 // buffers come back with the same values every step, and an encode costs microseconds.
 struct MapKey {
-  const void *base; int rows, K, ld, box;
+  const void *base; int rows, K, ld, box;          // box: rows of the box; negative for the maps of C
   bool operator==(const MapKey &o) const {
     return base == o.base && rows == o.rows && K == o.K && ld == o.ld && box == o.box;
   }
@@ -366,6 +651,32 @@ static int encode_map(CUtensorMap *map, const void *base, int rows, int K, int l
   return 0;
 }
 
+// A map of C for the tile stores of the persistent kernel: row-major [rows, cols] of bfloat16
+// or float, boxes of 32 rows x 128 bytes, 128-byte swizzle.
+static int make_map_c(CUtensorMap *map, const void *base, int rows, int cols, int ld, bool is_float) {
+  const MapKey key{base, rows, cols, ld, is_float ? -4 : -2};
+  std::lock_guard<std::mutex> lock(g_maps_mutex);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *map = it->second;
+    return 0;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) G2B_REFUSE("gemm_tc: cuTensorMapEncodeTiled is not available from the driver");
+  const int esize = is_float ? 4 : 2;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * esize};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / esize), 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, is_float ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) G2B_REFUSE("gemm_tc: cuTensorMapEncodeTiled for C failed with code %d", (int)r);
+  if (g_maps.size() > 65536) g_maps.clear();
+  g_maps.emplace(key, *map);
+  return 0;
+}
+
 template <int BN, int STAGES, int EPI>
 static int launch(const CUtensorMap &ma, const CUtensorMap &mw, void *C, int M, int N, int K, int ldc,
                   int *status, cudaStream_t stream) {
@@ -383,15 +694,53 @@ static int launch(const CUtensorMap &ma, const CUtensorMap &mw, void *C, int M, 
   return g2b_check_launch("gemm_tc");
 }
 
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <int BN, int STAGES, int EPI>
+static int launch_persistent(const CUtensorMap &ma, const CUtensorMap &mw, void *C, int M, int N, int K, int ldc,
+                             int *status, cudaStream_t stream) {
+  static bool configured = false;
+  const int smem = SmemP<BN, STAGES>::TOTAL;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES, EPI>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) G2B_REFUSE("gemm_tc: shared memory of %d bytes refused: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  if (tiles > 0x7fffffffLL) G2B_REFUSE("gemm_tc: %lld tiles", tiles);
+  const bool is_float = EPI == EPI_STORE_F32 || EPI == EPI_ACCUM_F32;
+  const int c_cols = EPI == EPI_SWIGLU_BF16 ? N / 2 : N;
+  if (((uintptr_t)C & 15) || (ldc * (is_float ? 4 : 2)) % 16)
+    G2B_REFUSE("gemm_tc: the persistent kernel stores tiles of C: C must be 16-byte aligned with a row stride "
+               "that is a multiple of 16 bytes (ldc = %d)", ldc);
+  CUtensorMap mc;
+  const int rc = make_map_c(&mc, C, M, c_cols, ldc, is_float);
+  if (rc) return rc;
+  const unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
+  g2b_launch(gemm_tc_persistent_kernel<BN, STAGES, EPI>, dim3(grid), dim3(THREADS), smem, stream, ma, mw, mc, M, N,
+             K, status);
+  return g2b_check_launch("gemm_tc (persistent)");
+}
+
 // A [M,K], W [N,K] bfloat16, inner stride 1, row strides multiples of 8 elements, base
 // addresses 16-byte aligned.  epi: 0 store bfloat16, 1 store float, 2 add into float,
 // 3 SiLU gate (C is [M, N/2] bfloat16; N a multiple of 16).  `status` is a device int the
 // kernel sets non-zero if one of its bounded waits gave up.  Tile shapes (bn, stages):
 // (64,4) (64,8) (128,3) (128,6) (256,4); bn = 0 picks one from the sizes: wide tiles when
 // there are plenty of them, narrow tiles with a deeper ring when the grid would not fill
-// the GPU (the ring has to cover the latency of the copies by itself then).
+// the GPU (the ring has to cover the latency of the copies by itself then).  persistent = 1:
+// the variant with one CTA per SM and two accumulators, shapes (128,6) and (256,4).
 extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, int K, int lda,
-                           int ldw, int ldc, int epi, int bn, int stages, int *status,
+                           int ldw, int ldc, int epi, int bn, int stages, int persistent, int *status,
                            cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || lda % 8 || ldw % 8)
@@ -410,6 +759,17 @@ extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, 
   rc = make_map(&mw, W, N, K, ldw, bn);
   if (rc) return rc;
 #define G2B_CASE(BN_, ST_, E) \
+  if (persistent && bn == BN_ && stages == ST_ && epi == E)                                        \
+    return launch_persistent<BN_, ST_, E>(ma, mw, C, M, N, K, ldc, status, stream);
+#define G2B_SHAPE(BN_, ST_) \
+  G2B_CASE(BN_, ST_, EPI_STORE_BF16) G2B_CASE(BN_, ST_, EPI_STORE_F32) \
+  G2B_CASE(BN_, ST_, EPI_ACCUM_F32) G2B_CASE(BN_, ST_, EPI_SWIGLU_BF16)
+  G2B_SHAPE(128, 6) G2B_SHAPE(256, 4)
+#undef G2B_SHAPE
+#undef G2B_CASE
+  if (persistent)
+    G2B_REFUSE("gemm_tc: no persistent kernel for tile width %d with %d stages and epilogue %d", bn, stages, epi);
+#define G2B_CASE(BN_, ST_, E) \
   if (bn == BN_ && stages == ST_ && epi == E) return launch<BN_, ST_, E>(ma, mw, C, M, N, K, ldc, status, stream);
 #define G2B_SHAPE(BN_, ST_) \
   G2B_CASE(BN_, ST_, EPI_STORE_BF16) G2B_CASE(BN_, ST_, EPI_STORE_F32) \
@@ -419,3 +779,14 @@ extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, 
 #undef G2B_CASE
   G2B_REFUSE("gemm_tc: no kernel for tile width %d with %d stages and epilogue %d", bn, stages, epi);
 }
+
+#ifdef G2B_GEMM_TIMING
+// Copies the 16 counters to `out` and clears them.
+extern "C" int g2b_gemm_tc_timing(unsigned long long *out) {
+  static unsigned long long zero[16] = {0};
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, g2b_timing, sizeof(zero));
+  cudaMemcpyToSymbol(g2b_timing, zero, sizeof(zero));
+  return 0;
+}
+#endif

@@ -69,13 +69,15 @@ def _tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
             and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def _gemm_tc(a, w, out, epi, bn: int = 0, stages: int = 0) -> None:
-    """bn = 0 lets the launcher pick the tile shape from the sizes."""
+def _gemm_tc(a, w, out, epi, bn: int = 0, stages: int = 0, persistent: bool = False) -> None:
+    """bn = 0 lets the launcher pick the tile shape from the sizes.  persistent: one CTA per SM
+    walks over the tiles with two accumulators (shapes (128, 6) and (256, 4))."""
     f = _fn("gemm_tc.cu", "g2b_gemm_tc",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_int, c_void_p, c_void_p])
+             c_int, c_int, c_void_p, c_void_p])
     _call(f, _ptr(a), _ptr(w), _ptr(out), a.shape[0], w.shape[0], a.shape[1], a.stride(0),
-          w.stride(0), out.stride(0), epi, bn, stages, _ptr(_status_word(a.device)), _stream())
+          w.stride(0), out.stride(0), epi, bn, stages, 1 if persistent else 0,
+          _ptr(_status_word(a.device)), _stream())
 
 
 def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
@@ -93,7 +95,7 @@ def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate:
         _gemm_small(a, w, out, epi)
         return True
     if choice == "tc":
-        _gemm_tc(a, w, out, epi, *_tc_shape(a.shape[0], w.shape[0]))
+        _gemm_tc(a, w, out, epi, *_tc_shape(a.shape[0], w.shape[0], out))
         return True
     return False
 
@@ -111,11 +113,16 @@ def _pick_product(a: torch.Tensor, w: torch.Tensor):
     return None
 
 
-def _tc_shape(M: int, N: int):
-    """(tile width, stages) of the tcgen05 product; (0, 0) lets the launcher choose."""
+def _tc_shape(M: int, N: int, out: torch.Tensor = None):
+    """(tile width, stages, persistent) of the tcgen05 product; (0, 0, False) lets the launcher
+    choose.  Prompts (more than one row of tiles) take the persistent kernel when C can be
+    written as tiles: wide tiles when there are enough of them to fill the GPU."""
     if M <= 128:                       # one row of tiles: the weights stream, as in decode
-        return (128, 3) if N >= 32768 else (64, 8)
-    return (0, 0)
+        return (128, 3, False) if N >= 32768 else (64, 8, False)
+    if out is not None and out.data_ptr() % 16 == 0 and (out.stride(0) * out.element_size()) % 16 == 0:
+        tiles_m = -(-M // 128)
+        return (256, 4, True) if tiles_m * -(-N // 256) >= 96 else (128, 6, True)
+    return (0, 0, False)
 
 
 def linear_normed_bf16(x32, norm_w, eps, rows, w, out, epi=None) -> bool:
@@ -154,7 +161,7 @@ def gate_up_bf16(h: torch.Tensor, w_gate_up: torch.Tensor, mid: torch.Tensor, bl
         _gemm_small(h, w_gate_up, mid, EPI_SWIGLU_BF16)
         return True
     if choice == "tc":
-        _gemm_tc(h, w_gate_up, mid, EPI_SWIGLU_BF16, *_tc_shape(h.shape[0], w_gate_up.shape[0]))
+        _gemm_tc(h, w_gate_up, mid, EPI_SWIGLU_BF16, *_tc_shape(h.shape[0], w_gate_up.shape[0], mid))
         return True
     return False
 

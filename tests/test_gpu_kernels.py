@@ -346,25 +346,21 @@ def test_attn_prefill(nh, nkv, hd, window, kernel):
         t += ql
 
 
-@pytest.mark.parametrize("bn,stages", [(64, 4), (64, 8), (128, 3), (128, 6), (256, 4), (0, 0)])
-@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (65, 256, 128), (200, 1000, 1032), (333, 96, 96),
-                                   (1024, 512, 2048), (129, 311 * 8, 72)])
-def test_gemm_tc(M, N, K, bn, stages):
-    """tcgen05 product: one and many K blocks, ragged M / N / K tails, every epilogue."""
+def _check_gemm_tc(M, N, K, bn, stages, persistent):
     from gguf2bin_b200 import kernels_bf16
     a, w = rnd(M, K, dtype=torch.bfloat16, seed=80), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=81)
     ref = a.double() @ w.double().T
     tol = 1e-5 * math.sqrt(K) * max(1.0, ref.abs().max().item())
     out = torch.full((M, N), 7.0, device=DEV)
-    kernels_bf16._gemm_tc(a, w, out, kernels_bf16.EPI_STORE_F32, bn, stages)
+    kernels_bf16._gemm_tc(a, w, out, kernels_bf16.EPI_STORE_F32, bn, stages, persistent)
     kernels_bf16.check_status()
     assert (out.double() - ref).abs().max().item() < tol
     base = rnd(M, N, seed=82)
     acc = base.clone()
-    kernels_bf16._gemm_tc(a, w, acc, kernels_bf16.EPI_ACCUM_F32, bn, stages)
+    kernels_bf16._gemm_tc(a, w, acc, kernels_bf16.EPI_ACCUM_F32, bn, stages, persistent)
     assert (acc.double() - base.double() - ref).abs().max().item() < tol
     out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
-    kernels_bf16._gemm_tc(a, w, out16, kernels_bf16.EPI_STORE_BF16, bn, stages)
+    kernels_bf16._gemm_tc(a, w, out16, kernels_bf16.EPI_STORE_BF16, bn, stages, persistent)
     assert (out16.double() - ref).abs().max().item() <= ref.abs().max().item() * 2.0 ** -8 + tol
     if N % 16 == 0:
         I = N // 2
@@ -372,9 +368,26 @@ def test_gemm_tc(M, N, K, bn, stages):
         u = ref.view(M, I // 8, 2, 8)[:, :, 1].reshape(M, I)
         want = (g / (1 + torch.exp(-g))) * u
         mid = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
-        kernels_bf16._gemm_tc(a, w, mid, kernels_bf16.EPI_SWIGLU_BF16, bn, stages)
+        kernels_bf16._gemm_tc(a, w, mid, kernels_bf16.EPI_SWIGLU_BF16, bn, stages, persistent)
         assert (mid.double() - want).abs().max().item() <= want.abs().max().item() * 2.0 ** -8 + tol
     kernels_bf16.check_status()
+
+
+@pytest.mark.parametrize("bn,stages", [(64, 4), (64, 8), (128, 3), (128, 6), (256, 4), (0, 0)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (65, 256, 128), (200, 1000, 1032), (333, 96, 96),
+                                   (1024, 512, 2048), (129, 311 * 8, 72)])
+def test_gemm_tc(M, N, K, bn, stages):
+    """tcgen05 product: one and many K blocks, ragged M / N / K tails, every epilogue."""
+    _check_gemm_tc(M, N, K, bn, stages, False)
+
+
+@pytest.mark.parametrize("bn,stages", [(128, 6), (256, 4)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (200, 1000, 1032), (2048 + 17, 2560 + 8, 320),
+                                   (4096, 2048, 136), (1500, 6144, 1024)])
+def test_gemm_tc_persistent(M, N, K, bn, stages):
+    """The persistent variant: fewer tiles than SMs, and several tiles per CTA (both
+    accumulators in use, the ring running across tile borders), ragged tails, every epilogue."""
+    _check_gemm_tc(M, N, K, bn, stages, True)
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 64, 1024), (8, 4096, 1024), (5, 200, 264), (16, 96, 3072), (40, 512, 520)])
