@@ -504,3 +504,24 @@ extern "C" int g2b_advance_positions(int *tok_pos, int n, cudaStream_t stream) {
   g2b_launch(advance_positions_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tok_pos, n);
   return g2b_check_launch("advance_positions");
 }
+
+// Undoes the bookkeeping of one decode step that was launched ahead and is not wanted after
+// all: positions go back by one and, when that step drew a random number, so do the draw
+// counters of the sequences' sampling records (word 3 of a record).
+__global__ void rewind_step_kernel(int *tok_pos, int n, int *seq_state, int words, const int *slots, int undo_draw) {
+  pdl_launch();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  tok_pos[i] -= 1;
+  if (undo_draw) seq_state[(size_t)slots[i] * words + 3] -= 1;
+}
+
+extern "C" int g2b_rewind_step(int *tok_pos, int n, int *seq_state, int words, const int *slots, int undo_draw,
+                               cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (undo_draw && (!seq_state || !slots || words < 4)) G2B_REFUSE("rewind_step: no sampling records to rewind");
+  g2b_launch(rewind_step_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tok_pos, n, seq_state, words, slots,
+             undo_draw);
+  return g2b_check_launch("rewind_step");
+}

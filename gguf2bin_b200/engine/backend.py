@@ -55,10 +55,16 @@ class EngineBackend:
         self.sampler.seed([seq.slot], [stream_id], self.seed)
         return _Handle(seq)
 
+    def _drop_session(self) -> None:
+        """Ends the decode session (a step it launched ahead is taken back first)."""
+        if self._session is not None:
+            self._session.take_back()
+            self._session = None
+
     def close(self, handle: _Handle) -> None:
         if handle.seq.slot >= 0:
             if self._session is not None and any(s is handle.seq for s in self._session.seqs):
-                self._session = None           # its batch no longer exists
+                self._drop_session()           # its batch no longer exists
             self.engine.close_sequence(handle.seq)
 
     def _sample(self, logits: torch.Tensor, handles: Sequence[_Handle]) -> list:
@@ -76,6 +82,7 @@ class EngineBackend:
         return out
 
     def prefill(self, handles: Sequence[_Handle], prompts: Sequence[Sequence[int]]) -> list:
+        self._drop_session()
         entries = [StepEntry(h.seq, p, (len(p) - 1,)) for h, p in zip(handles, prompts)]
         logits = self.engine.step(entries)
         for h, p in zip(handles, prompts):
@@ -93,14 +100,13 @@ class EngineBackend:
                 raise StepError(f"token id {t} outside the vocabulary 0..{V - 1}")
         key = tuple(id(h) for h in handles)
         if self._session is None or self._session_key != key:
+            self._drop_session()
             self._session = DecodeSession(self.engine, [h.seq for h in handles], self.sampler,
                                           self.params, self.use_graph)
             self._session_key = key
         session = self._session
-        session.set_tokens(tokens)
         recent = [h.recent for h in handles] if self.params.repeat_penalty != 1.0 else None
-        session.run(recent)
-        out = session.read_tokens()
+        out = session.step(tokens, recent)
         for h, t in zip(handles, out):
             h.recent.append(t)
             del h.recent[:-RECENT_USE]

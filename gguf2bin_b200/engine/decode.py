@@ -10,6 +10,14 @@ sampler as ``Engine.step``; only the bookkeeping differs.
 
 The pages of every sequence must be reserved up to the length it can reach before the
 session starts (the page table is uploaded once).
+
+``step`` is the host-facing form (tokens in, sampled tokens out).  It keeps the GPU busy
+across the host's turn: as soon as a step's tokens are on their way back it launches the
+next step ahead, fed by the tokens just sampled, which is what the caller hands in next in
+all but the last step of a sequence.  If the caller then wants something else (other tokens,
+other sequences, or nothing more) the step launched ahead is taken back: it wrote the key
+and value of a token at a position that is written again or never read, and its bookkeeping
+(lengths, positions, draw counters) is rewound.
 """
 from __future__ import annotations
 
@@ -50,7 +58,10 @@ class DecodeSession:
         self.want_rows = torch.arange(B, dtype=torch.int32, device=dev)
         self.logits = torch.empty(B, engine.model.vocab, dtype=torch.float32, device=dev)
         self._pinned_in = torch.empty(B, dtype=torch.int32, pin_memory=True)
-        self._pinned_out = torch.empty(B, dtype=torch.int32, pin_memory=True)
+        self._pinned_out = [torch.empty(B, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._out_ready = [torch.cuda.Event(), torch.cuda.Event()]
+        self._out_turn = 0
+        self._ahead: Optional[list] = None      # tokens fed to the step launched ahead, if any
         self.ctx = StepContext(
             n_tokens=B, n_seqs=B, tok_ids=self.tok_ids, tok_pos=self.tok_pos, tok_seq=self.tok_seq,
             page_table=self.page_table, page_size=engine.cache.page_size,
@@ -116,6 +127,52 @@ class DecodeSession:
 
     def read_tokens(self) -> list:
         """The tokens sampled by the last step (device to host)."""
-        self._pinned_out.copy_(self.tok_ids, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self._pinned_out.tolist()
+        return self._collect(self._send_back())
+
+    def _send_back(self) -> int:
+        """Starts the copy of the last step's tokens to the host; returns its turn."""
+        turn = self._out_turn
+        self._out_turn ^= 1
+        self._pinned_out[turn].copy_(self.tok_ids, non_blocking=True)
+        self._out_ready[turn].record()
+        return turn
+
+    def _collect(self, turn: int) -> list:
+        self._out_ready[turn].synchronize()
+        return self._pinned_out[turn].tolist()
+
+    def _room_for_one_more(self) -> bool:
+        page = self.engine.cache.page_size
+        limit = self.engine.model.spec.max_positions
+        return all(s.length + 1 <= len(s.pages) * page and s.length + 1 <= limit for s in self.seqs)
+
+    def step(self, tokens: Sequence[int], recent=None) -> list:
+        """Feeds one token per sequence and returns the sampled next tokens, through pinned
+        host memory both ways.  Steps that sample on the device are launched one ahead."""
+        tokens = [int(t) for t in tokens]
+        if self._ahead is not None and tokens == self._ahead:
+            turn = self._ahead_turn                  # the step launched ahead is this one
+        else:
+            self.take_back()
+            self.set_tokens(tokens)
+            self.run(recent)
+            turn = self._send_back()
+        self._ahead = None
+        ahead_turn = None
+        if self._sample_in_graph and self._room_for_one_more():
+            self.run(None)                           # the next step, fed by the tokens being sampled now;
+            ahead_turn = self._send_back()           # queued before this step's tokens are waited for
+        out = self._collect(turn)
+        if ahead_turn is not None:
+            self._ahead, self._ahead_turn = out, ahead_turn
+        return out
+
+    def take_back(self) -> None:
+        """Undoes a step launched ahead that nobody asked for."""
+        if self._ahead is None:
+            return
+        self._ahead = None
+        kernels.rewind_step(self.tok_pos, self.batch, self.sampler.seq_state, self.slots,
+                            self.params.temperature > 0.0)
+        for s in self.seqs:
+            s.length -= 1

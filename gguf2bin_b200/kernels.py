@@ -176,6 +176,15 @@ def advance_positions(tok_pos: torch.Tensor, n: int) -> None:
     _call(f, _ptr(tok_pos), n, _stream())
 
 
+def rewind_step(tok_pos: torch.Tensor, n: int, seq_state: Optional[torch.Tensor], slots: Optional[torch.Tensor],
+                undo_draw: bool) -> None:
+    """Takes back the device-side bookkeeping of one decode step (positions, and the draw
+    counters of the sampling records when that step sampled with a random number)."""
+    f = _fn("elementwise.cu", "g2b_rewind_step", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p])
+    words = seq_state.shape[1] if seq_state is not None else 0
+    _call(f, _ptr(tok_pos), n, _ptr(seq_state), words, _ptr(slots), 1 if undo_draw else 0, _stream())
+
+
 # ---------------------------------------------------------------------------
 # matrix products
 # ---------------------------------------------------------------------------

@@ -136,3 +136,42 @@ def test_context_limit_and_errors(llms):
     llm.close_sequence(seq)
     with pytest.raises(StepError, match="not live"):
         llm.step([StepEntry(seq, [1], [0])])
+
+
+def test_step_launched_ahead_is_taken_back(llms):
+    """The decode session launches each next step before the host has seen the last tokens.
+    Here the caller then feeds other tokens than the sampled ones (and later ends one sequence
+    early): the step launched ahead must leave no trace, neither in the cache nor in the draw
+    counters of the seeded sampler.  Temperature 0.7, two sequences, against the plain
+    implementation fed the same tokens."""
+    from gguf2bin_b200.engine.backend import EngineBackend
+    from gguf2bin_b200.sampling import SamplingParams
+    llm = llms("b", "float32")
+    temp, seed = 0.7, 77
+    backend = EngineBackend(llm.engine, SamplingParams.plain(temp), seed, max_context=256)
+    prompts = [random_tokens("b", 6, 31), random_tokens("b", 9, 32)]
+    handles = [backend.open(i, 64) for i in range(2)]
+    cfg, W = plain_model("b", "float32")
+    fed = [list(p) for p in prompts]
+    draws = [0, 0]
+
+    def plain_next(i):
+        logits = P.forward(cfg, W, fed[i], np.float32)[-1]
+        t, _ = P.sample_temperature(logits, temp, philox_plain.uniform(seed, i, draws[i]))
+        draws[i] += 1
+        return t
+
+    got = backend.prefill(handles, prompts)
+    assert got == [plain_next(0), plain_next(1)]
+    live = [0, 1]
+    for step in range(8):
+        if step == 3:                              # the caller overrides the sampled tokens
+            got = [(t + 1) % cfg["vocab_size"] for t in got]
+        if step == 6:                              # sequence 0 ends; the batch changes
+            backend.close(handles[0])
+            live, got = [1], got[1:]
+        for i, t in zip(live, got):
+            fed[i].append(t)
+        got = backend.decode([handles[i] for i in live], got)
+        assert got == [plain_next(i) for i in live], f"step {step}"
+    backend.close(handles[1])
