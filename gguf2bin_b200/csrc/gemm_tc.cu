@@ -24,105 +24,18 @@
 // code in `*status`, all roles fall through to the common exit, the tensor memory is freed
 // and the kernel returns; the host reads `*status` (0 = fine).
 #include "common.cuh"
-
-#include <cuda.h>
-
-#include <functional>
-#include <mutex>
-#include <unordered_map>
+#include "tc_common.cuh"
 
 G2B_DEFINE_LAST_ERROR
+
+using namespace tc;
 
 constexpr int BM = 128;
 constexpr int BK = 64;                      // 64 bf16 = 128 bytes = one swizzle row
 constexpr int THREADS = 192;
-constexpr uint32_t SPIN_LIMIT = 1u << 22;   // polls of a barrier before giving up
 
 enum { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ACCUM_F32 = 2, EPI_SWIGLU_BF16 = 3 };
 enum { ST_OK = 0, ST_PRODUCER_TIMEOUT = 1, ST_MMA_TIMEOUT = 2, ST_EPILOGUE_TIMEOUT = 3 };
-
-// ---- PTX wrappers -----------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_addr(const void *p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-// true when the phase with the given parity has completed; false after SPIN_LIMIT polls
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-// shared -> global tile store (clipped at the tensor's bounds) and the same as an addition
-// of floats; both join the thread's current bulk group
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
-               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
-  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];\n"
-               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
-// at most N of the thread's bulk groups still read their shared-memory source
-template <int N> __device__ __forceinline__ void bulk_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(N) : "memory");
-}
-template <int N> __device__ __forceinline__ void bulk_wait() {
-  asm volatile("cp.async.bulk.wait_group %0;\n" ::"n"(N) : "memory");
-}
-// makes the warp's writes to shared memory visible to the bulk-copy unit
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                          uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
 
 __device__ __forceinline__ uint32_t pack2(uint32_t lo, uint32_t hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(lo), __uint_as_float(hi));
@@ -134,21 +47,8 @@ __device__ __forceinline__ uint32_t pack2f(float lo, float hi) {
   return *reinterpret_cast<uint32_t *>(&v);
 }
 
-// Shared-memory operand descriptor: K-major tile of rows x 64 bf16, rows of 128 bytes,
-// 128-byte swizzle, 8-row groups 1024 bytes apart (the layout the TMA unit writes).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFF) >> 4);          // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                          // leading byte offset (unused with swizzle): 1
-  d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                          // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
-  return d;
-}
-// Instruction descriptor: D float, A and B bfloat16, both K-major, M = 128, N = n.
-__host__ __device__ constexpr uint32_t instr_desc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-}
+// Instruction descriptor of a product with M = 128, N = n, both operands K-major.
+__host__ __device__ constexpr uint32_t idesc_n(int n) { return instr_desc(BM, n, false); }
 
 template <int BN, int STAGES> struct Smem {
   static constexpr int A_BYTES = BM * BK * 2;
@@ -293,7 +193,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else if (warp == 5) {
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(BN);
+      constexpr uint32_t idesc = idesc_n(BN);
       bool ok = true;
       for (int kb = 0; kb < nkb && ok; ++kb) {
         const int s = kb % STAGES;
@@ -304,7 +204,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t a_addr = smem_addr(smem + s * S::STAGE_BYTES);
-        const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(a_addr + S::A_BYTES);
+        const uint64_t adesc = desc_k_major(a_addr), bdesc = desc_k_major(a_addr + S::A_BYTES);
 #pragma unroll
         for (int k = 0; k < BK / 16; ++k)            // 16 bf16 = 32 bytes = 2 descriptor units
           umma_bf16(tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
@@ -391,7 +291,7 @@ __device__ __forceinline__ void epilogue_tile_bulk(uint32_t tmem, unsigned char 
                                      pack2f(h[8 * j + 4], h[8 * j + 5]), pack2f(h[8 * j + 6], h[8 * j + 7])));
     }
     if (part == PER_BOX - 1) {
-      fence_async_smem();
+      fence_async_shared();
       __syncwarp();
       if (lane == 0) {
         const int first_col = n0 + 32 * (c - part);            // accumulator column of the box
@@ -509,7 +409,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     }
   } else if (warp == 5) {
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(BN);
+      constexpr uint32_t idesc = idesc_n(BN);
       uint32_t g = 0, j = 0;                         // k-blocks and tiles so far
       bool ok = true;
       TDECL(2); TDECL(3); TDECL(4); TDECL(5);
@@ -535,7 +435,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
           TOCK(4, t_f);
           asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
           const uint32_t a_addr = smem_addr(smem + s * S::STAGE_BYTES);
-          const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(a_addr + S::A_BYTES);
+          const uint64_t adesc = desc_k_major(a_addr), bdesc = desc_k_major(a_addr + S::A_BYTES);
           TICK(t_i);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
@@ -583,97 +483,17 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 }
 
 // ---- host side ----------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
-                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
-// Encoded maps are kept by (address, rows, K, stride, box): weights and the step's scratch
-// buffers come back with the same values every step, and an encode costs microseconds.
-struct MapKey {
-  const void *base; int rows, K, ld, box;          // box: rows of the box; negative for the maps of C
-  bool operator==(const MapKey &o) const {
-    return base == o.base && rows == o.rows && K == o.K && ld == o.ld && box == o.box;
-  }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey &k) const {
-    size_t h = std::hash<const void *>()(k.base);
-    h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.K;
-    h = h * 1000003u ^ (size_t)k.ld;   h = h * 1000003u ^ (size_t)k.box;
-    return h;
-  }
-};
-static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
-static std::mutex g_maps_mutex;
-
-static int encode_map(CUtensorMap *map, const void *base, int rows, int K, int ld, int box_rows);
-
-// A tiled map of a row-major [rows, K] bfloat16 matrix with boxes of box_rows x 64, 128-byte swizzle.
+// Tensor maps come from tc::get_map (kept by address and sizes).
 static int make_map(CUtensorMap *map, const void *base, int rows, int K, int ld, int box_rows) {
-  const MapKey key{base, rows, K, ld, box_rows};
-  std::lock_guard<std::mutex> lock(g_maps_mutex);
-  auto it = g_maps.find(key);
-  if (it != g_maps.end()) {
-    *map = it->second;
-    return 0;
-  }
-  const int rc = encode_map(map, base, rows, K, ld, box_rows);
-  if (rc) return rc;
-  if (g_maps.size() > 65536) g_maps.clear();         // a bound, not a policy: maps are cheap to rebuild
-  g_maps.emplace(key, *map);
+  const int rc = get_map(map, base, rows, K, ld, box_rows);
+  if (rc) G2B_REFUSE("gemm_tc: cuTensorMapEncodeTiled failed or is not available (code %d)", rc);
   return 0;
 }
 
-static int encode_map(CUtensorMap *map, const void *base, int rows, int K, int ld, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) G2B_REFUSE("gemm_tc: cuTensorMapEncodeTiled is not available from the driver");
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) G2B_REFUSE("gemm_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
-  return 0;
-}
-
-// A map of C for the tile stores of the persistent kernel: row-major [rows, cols] of bfloat16
-// or float, boxes of 32 rows x 128 bytes, 128-byte swizzle.
+// A map of C for the tile stores of the persistent kernel: boxes of 32 rows x 128 bytes.
 static int make_map_c(CUtensorMap *map, const void *base, int rows, int cols, int ld, bool is_float) {
-  const MapKey key{base, rows, cols, ld, is_float ? -4 : -2};
-  std::lock_guard<std::mutex> lock(g_maps_mutex);
-  auto it = g_maps.find(key);
-  if (it != g_maps.end()) {
-    *map = it->second;
-    return 0;
-  }
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) G2B_REFUSE("gemm_tc: cuTensorMapEncodeTiled is not available from the driver");
-  const int esize = is_float ? 4 : 2;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * esize};
-  cuuint32_t box[2] = {(cuuint32_t)(128 / esize), 32};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, is_float ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                  const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) G2B_REFUSE("gemm_tc: cuTensorMapEncodeTiled for C failed with code %d", (int)r);
-  if (g_maps.size() > 65536) g_maps.clear();
-  g_maps.emplace(key, *map);
+  const int rc = get_map(map, base, rows, cols, ld, 32, is_float ? 4 : 2);
+  if (rc) G2B_REFUSE("gemm_tc: cuTensorMapEncodeTiled for C failed or is not available (code %d)", rc);
   return 0;
 }
 

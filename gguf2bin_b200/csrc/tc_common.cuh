@@ -54,6 +54,25 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// shared -> global tile store (clipped at the tensor's bounds) and the same as an addition
+// of floats; both join the thread's current bulk group
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n"
+               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];\n"
+               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+// at most N of the thread's bulk groups still read their shared-memory source
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(N) : "memory");
+}
+// at most N of the thread's bulk groups are not yet complete
+template <int N> __device__ __forceinline__ void bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;\n" ::"n"(N) : "memory");
+}
 // generic-proxy writes to shared memory become visible to the async proxy (MMA, TMA)
 __device__ __forceinline__ void fence_async_shared() {
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -227,29 +246,31 @@ static inline EncodeTiledFn encode_fn() {
 }
 
 struct MapKey {
-  const void *base; long long rows; int cols, ld, box_rows;
+  const void *base; long long rows; int cols, ld, box_rows, elem_bytes;
   bool operator==(const MapKey &o) const {
-    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows &&
+           elem_bytes == o.elem_bytes;
   }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey &k) const {
     size_t h = std::hash<const void *>()(k.base);
     h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.cols;
-    h = h * 1000003u ^ (size_t)k.ld;   h = h * 1000003u ^ (size_t)k.box_rows;
+    h = h * 1000003u ^ (size_t)k.ld;   h = h * 1000003u ^ (size_t)(k.box_rows * 8 + k.elem_bytes);
     return h;
   }
 };
 
-// A tiled map of a row-major [rows, cols] bfloat16 matrix (row stride ld elements) with boxes
-// of box_rows x 64 columns and 128-byte swizzle; out-of-range parts of a box read as zero.
-// Encoded maps are kept by (address, sizes): weights, cache layers and scratch buffers come
-// back with the same values every step.  Returns 0, or a CUresult / -1 on failure.
+// A tiled map of a row-major [rows, cols] matrix of bfloat16 (elem_bytes 2) or float (4), row
+// stride ld elements, with boxes of box_rows rows x 128 bytes and 128-byte swizzle; parts of a
+// box outside the matrix read as zero and are not written.  Encoded maps are kept by (address,
+// sizes): weights, cache layers and scratch buffers come back with the same values every step.
+// Returns 0, or a CUresult / -1 on failure.
 static inline int get_map(CUtensorMap *map, const void *base, long long rows, int cols, int ld,
-                          int box_rows) {
+                          int box_rows, int elem_bytes = 2) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
   static std::mutex mutex;
-  const MapKey key{base, rows, cols, ld, box_rows};
+  const MapKey key{base, rows, cols, ld, box_rows, elem_bytes};
   std::lock_guard<std::mutex> lock(mutex);
   auto it = maps.find(key);
   if (it != maps.end()) {
@@ -259,10 +280,11 @@ static inline int get_map(CUtensorMap *map, const void *base, long long rows, in
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -1;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * (cuuint64_t)elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides,
+  CUresult r = fn(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void *>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return (int)r;
