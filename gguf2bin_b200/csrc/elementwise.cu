@@ -67,7 +67,18 @@ __global__ void rmsnorm_kernel(const float *__restrict__ x, const float *__restr
   for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = from_f32<TO>((w[j] * xr[j]) * inv);
 }
 
-// one warp per row, 16-byte loads, eight of them in flight per lane; H a multiple of 4
+__device__ __forceinline__ void store4(float *p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4 *>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(bf16 *p, float a, float b, float c, float d) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162 *>(&raw.x) = __floats2bfloat162_rn(a, b);
+  *reinterpret_cast<__nv_bfloat162 *>(&raw.y) = __floats2bfloat162_rn(c, d);
+  *reinterpret_cast<uint2 *>(p) = raw;
+}
+
+// one warp per row, 16-byte loads, eight of them in flight per lane, four outputs per store; rows
+// of up to 1,024 elements stay in registers between the two passes; H a multiple of 4
 template <typename TO>
 __global__ void __launch_bounds__(128)
 rmsnorm_rows_kernel(const float *__restrict__ x, const float *__restrict__ w,
@@ -80,6 +91,35 @@ rmsnorm_rows_kernel(const float *__restrict__ x, const float *__restrict__ w,
   if (r >= n_rows) return;
   const float *xr = x + (size_t)(rows ? rows[r] : r) * H;
   float ss = 0.f;
+  if (H <= 1024) {
+    float4 v[8], g[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int k = lane * 4 + 128 * i;
+      v[i] = k < H ? *reinterpret_cast<const float4 *>(xr + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int k = lane * 4 + 128 * i;
+      g[i] = k < H ? *reinterpret_cast<const float4 *>(w + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+      ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / (float)H + eps);
+    TO *o = out + (size_t)r * H;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int k = lane * 4 + 128 * i;
+      if (k < H)
+        store4(o + k, (g[i].x * v[i].x) * inv, (g[i].y * v[i].y) * inv, (g[i].z * v[i].z) * inv,
+               (g[i].w * v[i].w) * inv);
+    }
+    return;
+  }
   for (int k0 = lane * 4; k0 < H; k0 += 128 * 8) {
     float4 v[8];
 #pragma unroll
@@ -109,12 +149,9 @@ rmsnorm_rows_kernel(const float *__restrict__ x, const float *__restrict__ w,
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int k = k0 + 128 * i;
-      if (k < H) {
-        o[k + 0] = from_f32<TO>((g[i].x * v[i].x) * inv);
-        o[k + 1] = from_f32<TO>((g[i].y * v[i].y) * inv);
-        o[k + 2] = from_f32<TO>((g[i].z * v[i].z) * inv);
-        o[k + 3] = from_f32<TO>((g[i].w * v[i].w) * inv);
-      }
+      if (k < H)
+        store4(o + k, (g[i].x * v[i].x) * inv, (g[i].y * v[i].y) * inv, (g[i].z * v[i].z) * inv,
+               (g[i].w * v[i].w) * inv);
     }
   }
 }
@@ -123,7 +160,7 @@ extern "C" int g2b_rmsnorm(const float *x, const float *w, const int *rows, int 
                            float eps, void *out, int out_dtype, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (H <= 0) G2B_REFUSE("rmsnorm: bad width %d", H);
-  if (H % 4 == 0 && H >= 128 && ((((uintptr_t)x) | ((uintptr_t)w)) & 15) == 0 &&
+  if (H % 4 == 0 && H >= 128 && ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)out)) & 15) == 0 &&
       (out_dtype == G2B_F32 || out_dtype == G2B_BF16)) {
     const unsigned blocks = (unsigned)((n_rows + 3) / 4);
     if (out_dtype == G2B_F32)
