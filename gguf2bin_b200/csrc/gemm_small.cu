@@ -15,11 +15,10 @@
 //
 // Two ways of staging the activations.  `gemm_small_kernel` stages one 256-wide block of K
 // at a time (any K, M up to 64).  `gemm_small_whole_kernel` stages all of A once, when
-// M x K fits shared memory: its K loop then has no barrier at all, up to 8 blocks of W are
-// in flight per thread, and it can take the float32 residual stream directly and apply
-// RMSNorm while staging (o_j = (w_j * x_j) / sqrt(mean(x^2) + eps), statistics in float32,
-// src/l3_math.c:34-36,49), optionally on gathered rows, which removes the separate norm
-// kernel and a round trip of the normed activations through memory.
+// M x K fits shared memory: its K loop then has no barrier at all and up to 8 blocks of W are
+// in flight per thread.  (A variant that applied the block's RMSNorm while staging the float
+// stream was measured against the norm as a kernel of its own and lost: every 16-row tile
+// repeats the norm of all rows.)
 //
 // Epilogues: store (bfloat16 or float), add into a float matrix (the residual stream), or
 // the SiLU gate on a fused gate/up matrix whose rows alternate 8 gates / 8 ups:
@@ -168,16 +167,14 @@ gemm_small_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W, void *
 // K blocks of W in flight per thread (whole-A kernel): 4 when a CTA has at most four blocks of
 // K, else 8; the shallower ring frees registers, so that three blocks instead of two fit an SM.
 //
-// NORM: A is the float32 stream x[rows_or_identity[m], :] and is normalised while staged.
 // SPLIT > 1: a thread-block cluster of SPLIT CTAs shares one 16-row tile of W, each taking a
 // contiguous slice of K (its part of the activations and of the weights); the CTAs leave
 // their partial tiles in their own shared memory and the first CTA of the cluster adds them
 // in rank order through distributed shared memory.  Narrow outputs (N = 1024 means only 64
 // tiles) fill the GPU this way, and the order of the sum still depends on K and N only.
-template <int MT, int EPI, bool NORM, int DEPTH_WHOLE, int SPLIT>
+template <int MT, int EPI, int DEPTH_WHOLE, int SPLIT>
 __global__ void __launch_bounds__(WARPS * 32, DEPTH_WHOLE == 4 ? 3 : 2)
-gemm_small_whole_kernel(const void *__restrict__ Av, const float *__restrict__ norm_w, float eps,
-                        const int *__restrict__ rows, const bf16 *__restrict__ W,
+gemm_small_whole_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W,
                         void *__restrict__ Cv, int M, int N, int K, int lda, int ldw, int ldc) {
   pdl_launch();
   constexpr int MROWS = MT * 8;
@@ -215,7 +212,7 @@ gemm_small_whole_kernel(const void *__restrict__ Av, const float *__restrict__ n
     if (d < nkb) load_w(wb[d], d);
   pdl_wait();                            // the activations come from the kernel before
 
-  // stage this CTA's columns of A (normalised if NORM): one warp per row, many loads in flight
+  // stage this CTA's columns of A: one warp per row, many copies in flight
   const int k_hi = min(K, k_lo + nkb * KB);               // one past this CTA's last k
   for (int r = warp; r < MROWS; r += WARPS) {
     bf16 *dst = xs + (size_t)r * xrow;
@@ -223,49 +220,8 @@ gemm_small_whole_kernel(const void *__restrict__ Av, const float *__restrict__ n
       for (int k = lane * 8; k < xrow; k += 256) *reinterpret_cast<uint4 *>(dst + k) = make_uint4(0, 0, 0, 0);
       continue;
     }
-    if (NORM) {                                           // SPLIT == 1: the whole row is here
-      const float *x = (const float *)Av + (size_t)(rows ? rows[r] : r) * lda;
-      float ss = 0.f;
-      for (int k0 = lane * 4; k0 < K; k0 += 128 * 8) {
-        float4 v[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int k = k0 + 128 * i;
-          v[i] = k < K ? *reinterpret_cast<const float4 *>(x + k) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
-          ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
-        }
-      }
-      ss = warp_sum(ss);
-      const float inv = 1.f / sqrtf(ss / (float)K + eps);
-      for (int k0 = lane * 4; k0 < K; k0 += 128 * 4) {
-        float4 v[4], w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int k = k0 + 128 * i;
-          if (k < K) {
-            v[i] = *reinterpret_cast<const float4 *>(x + k);
-            w[i] = *reinterpret_cast<const float4 *>(norm_w + k);
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int k = k0 + 128 * i;
-          if (k < K) {
-            uint2 o;
-            o.x = pack_bf16((w[i].x * v[i].x) * inv, (w[i].y * v[i].y) * inv);
-            o.y = pack_bf16((w[i].z * v[i].z) * inv, (w[i].w * v[i].w) * inv);
-            *reinterpret_cast<uint2 *>(dst + k) = o;
-          }
-        }
-      }
-    } else {
-      const bf16 *x = (const bf16 *)Av + (size_t)r * lda + k_lo;
-      for (int k = lane * 8; k < k_hi - k_lo; k += 256) cp_async_16(smem_u32(dst + k), x + k);
-    }
+    const bf16 *x = A + (size_t)r * lda + k_lo;
+    for (int k = lane * 8; k < k_hi - k_lo; k += 256) cp_async_16(smem_u32(dst + k), x + k);
     for (int k = max(0, k_hi - k_lo) + lane * 4; k < xrow; k += 128) *reinterpret_cast<uint2 *>(dst + k) = make_uint2(0, 0);
   }
   cp_async_commit();
@@ -382,9 +338,8 @@ static int final_split(int N, int K) {
   return 1;
 }
 
-template <int MT, bool NORM, int DEPTH_WHOLE, int SPLIT>
-static int launch_whole_depth(const void *A, const float *norm_w, float eps, const int *rows,
-                              const void *W, void *C, int M, int N, int K, int lda, int ldw,
+template <int MT, int DEPTH_WHOLE, int SPLIT>
+static int launch_whole_depth(const void *A, const void *W, void *C, int M, int N, int K, int lda, int ldw,
                               int ldc, int epi, cudaStream_t stream) {
   const int smem = (int)whole_smem(MT * 8, K, SPLIT);
   const int n_tiles = (N + 15) / 16;
@@ -393,13 +348,13 @@ static int launch_whole_depth(const void *A, const float *norm_w, float eps, con
   do {                                                                                           \
     static int configured = 0;                                                                   \
     if (configured < smem) {                                                                     \
-      cudaError_t e = cudaFuncSetAttribute(gemm_small_whole_kernel<MT, E, NORM, DEPTH_WHOLE, SPLIT>, \
+      cudaError_t e = cudaFuncSetAttribute(gemm_small_whole_kernel<MT, E, DEPTH_WHOLE, SPLIT>,       \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem);   \
       if (e != cudaSuccess) G2B_REFUSE("gemm_small: shared memory: %s", cudaGetErrorString(e));  \
       configured = smem;                                                                         \
     }                                                                                            \
-    g2b_launch_cluster(gemm_small_whole_kernel<MT, E, NORM, DEPTH_WHOLE, SPLIT>, dim3(grid),     \
-                       dim3(WARPS * 32), smem, stream, (unsigned)SPLIT, A, norm_w, eps, rows,    \
+    g2b_launch_cluster(gemm_small_whole_kernel<MT, E, DEPTH_WHOLE, SPLIT>, dim3(grid),           \
+                       dim3(WARPS * 32), smem, stream, (unsigned)SPLIT, (const bf16 *)A,         \
                        (const bf16 *)W, C, M, N, K, lda, ldw, ldc);                              \
   } while (0)
   switch (epi) {
@@ -413,19 +368,15 @@ static int launch_whole_depth(const void *A, const float *norm_w, float eps, con
   return g2b_check_launch("gemm_small_whole");
 }
 
-template <int MT, bool NORM>
-static int launch_whole(const void *A, const float *norm_w, float eps, const int *rows,
-                        const void *W, void *C, int M, int N, int K, int lda, int ldw, int ldc,
+template <int MT>
+static int launch_whole(const void *A, const void *W, void *C, int M, int N, int K, int lda, int ldw, int ldc,
                         int epi, cudaStream_t stream) {
   const int nkb = (K + KB - 1) / KB;
-  const int split = NORM ? 1 : final_split(N, K);
-  if (split == 4)
-    return launch_whole_depth<MT, false, 4, 4>(A, norm_w, eps, rows, W, C, M, N, K, lda, ldw, ldc, epi, stream);
-  if (split == 2)
-    return launch_whole_depth<MT, false, 4, 2>(A, norm_w, eps, rows, W, C, M, N, K, lda, ldw, ldc, epi, stream);
-  if (nkb <= 4)
-    return launch_whole_depth<MT, NORM, 4, 1>(A, norm_w, eps, rows, W, C, M, N, K, lda, ldw, ldc, epi, stream);
-  return launch_whole_depth<MT, NORM, 8, 1>(A, norm_w, eps, rows, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+  const int split = final_split(N, K);
+  if (split == 4) return launch_whole_depth<MT, 4, 4>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+  if (split == 2) return launch_whole_depth<MT, 4, 2>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+  if (nkb <= 4) return launch_whole_depth<MT, 4, 1>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+  return launch_whole_depth<MT, 8, 1>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
 }
 
 template <int MT>
@@ -472,38 +423,13 @@ extern "C" int g2b_gemm_small(const void *A, const void *W, void *C, int M, int 
   if (epi == EPI_SWIGLU_BF16 && N % 16) G2B_REFUSE("gemm_small: gated output needs N %% 16 == 0, N=%d", N);
   const int mrows = M <= 8 ? 8 : (M <= 16 ? 16 : (M <= 32 ? 32 : 64));
   if (whole_smem(mrows, K, final_split(N, K))) {
-    if (M <= 8) return launch_whole<1, false>(A, nullptr, 0.f, nullptr, W, C, M, N, K, lda, ldw, ldc, epi, stream);
-    if (M <= 16) return launch_whole<2, false>(A, nullptr, 0.f, nullptr, W, C, M, N, K, lda, ldw, ldc, epi, stream);
-    if (M <= 32) return launch_whole<4, false>(A, nullptr, 0.f, nullptr, W, C, M, N, K, lda, ldw, ldc, epi, stream);
-    return launch_whole<8, false>(A, nullptr, 0.f, nullptr, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+    if (M <= 8) return launch_whole<1>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+    if (M <= 16) return launch_whole<2>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+    if (M <= 32) return launch_whole<4>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+    return launch_whole<8>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
   }
   if (M <= 8) return launch_mt<1>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
   if (M <= 16) return launch_mt<2>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
   if (M <= 32) return launch_mt<4>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
   return launch_mt<8>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
-}
-
-// The same product on the normalised float32 stream: A = rmsnorm(x[rows[m], :]) with weight
-// norm_w and eps, computed while staging (rows == nullptr: rows 0..M-1).  x float32 with
-// row stride ldx (a multiple of 4), K a multiple of 8.  Returns 3 when the case does not
-// fit the whole-A kernel (the caller then normalises separately).
-extern "C" int g2b_gemm_small_normed(const float *x, const float *norm_w, float eps,
-                                     const int *rows, const void *W, void *C, int M, int N, int K,
-                                     int ldx, int ldw, int ldc, int epi, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (M > 64) G2B_REFUSE("gemm_small_normed: M=%d (at most 64 rows)", M);
-  if (K <= 0 || K % 8 || ldx % 4 || ldw % 8)
-    G2B_REFUSE("gemm_small_normed: K=%d, ldx=%d, ldw=%d: K and ldw multiples of 8, ldx of 4", K, ldx, ldw);
-  if (((uintptr_t)x | (uintptr_t)W | (uintptr_t)norm_w) & 15)
-    G2B_REFUSE("gemm_small_normed: operands must be 16-byte aligned");
-  if (epi == EPI_SWIGLU_BF16 && N % 16) G2B_REFUSE("gemm_small_normed: gated output needs N %% 16 == 0, N=%d", N);
-  const int mrows = M <= 8 ? 8 : (M <= 16 ? 16 : (M <= 32 ? 32 : 64));
-  if (!whole_smem(mrows, K)) {
-    snprintf(g2b_error_text, sizeof(g2b_error_text), "gemm_small_normed: %d x %d activations do not fit shared memory", mrows, K);
-    return 3;
-  }
-  if (M <= 8) return launch_whole<1, true>(x, norm_w, eps, rows, W, C, M, N, K, ldx, ldw, ldc, epi, stream);
-  if (M <= 16) return launch_whole<2, true>(x, norm_w, eps, rows, W, C, M, N, K, ldx, ldw, ldc, epi, stream);
-  if (M <= 32) return launch_whole<4, true>(x, norm_w, eps, rows, W, C, M, N, K, ldx, ldw, ldc, epi, stream);
-  return launch_whole<8, true>(x, norm_w, eps, rows, W, C, M, N, K, ldx, ldw, ldc, epi, stream);
 }

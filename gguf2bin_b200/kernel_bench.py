@@ -89,19 +89,15 @@ def decode(a) -> None:
     res = torch.zeros(B, H, device=DEV)
     hb = torch.empty(B, H, dtype=torch.bfloat16, device=DEV)
     b.run("rmsnorm", lambda: [kernels.rmsnorm(x32, nw, 1e-6, hb) for _ in range(L)], L)
-    if b.want("qkv") or b.want("qkv_normed"):
+    if b.want("qkv"):
         W = [bf(NQ + 2 * NK, H) for _ in range(L)]
         b.run("qkv", lambda: [kernels_bf16.linear_bf16(h, w, qkv, False) for w in W], L, W[0].numel() * 2)
-        b.run("qkv_normed", lambda: [kernels_bf16.linear_normed_bf16(x32, nw, 1e-6, None, w, qkv) for w in W],
-              L, W[0].numel() * 2)
     if b.want("o_proj"):
         W = [bf(H, NQ) for _ in range(L)]
         b.run("o_proj", lambda: [kernels_bf16.linear_bf16(o, w, res, True) for w in W], L, W[0].numel() * 2)
-    if b.want("gate_up") or b.want("gate_up_normed"):
+    if b.want("gate_up"):
         W = [bf(2 * I, H) for _ in range(L)]
         b.run("gate_up", lambda: [kernels_bf16.gate_up_bf16(h, w, mid, 8) for w in W], L, W[0].numel() * 2)
-        b.run("gate_up_normed", lambda: [kernels_bf16.linear_normed_bf16(
-            x32, nw, 1e-6, None, w, mid, kernels_bf16.EPI_SWIGLU_BF16) for w in W], L, W[0].numel() * 2)
     if b.want("down"):
         W = [bf(H, I) for _ in range(L)]
         b.run("down", lambda: [kernels_bf16.linear_bf16(mid, w, res, True) for w in W], L, W[0].numel() * 2)

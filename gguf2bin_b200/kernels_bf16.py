@@ -125,32 +125,6 @@ def _tc_shape(M: int, N: int, out: torch.Tensor = None):
     return (0, 0, False)
 
 
-def linear_normed_bf16(x32, norm_w, eps, rows, w, out, epi=None) -> bool:
-    """out = rmsnorm(x32[rows]) @ w.T with the norm computed while the product stages its
-    activations (few rows only).  ``epi`` defaults to a store in ``out``'s dtype."""
-    M = out.shape[0]
-    K = x32.shape[1]
-    if (M > SMALL_M or w.dtype != torch.bfloat16 or x32.dtype != torch.float32 or K % 8
-            or x32.stride(1) != 1 or x32.stride(0) % 4 or w.stride(1) != 1 or w.stride(0) % 8
-            or out.stride(1) != 1 or norm_w.dtype != torch.float32
-            or x32.data_ptr() % 16 or w.data_ptr() % 16 or norm_w.data_ptr() % 16):
-        return False
-    if epi is None:
-        epi = EPI_STORE_BF16 if out.dtype == torch.bfloat16 else EPI_STORE_F32
-    f = _fn("gemm_small.cu", "g2b_gemm_small_normed",
-            [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_void_p])
-    rc = f(_ptr(x32), _ptr(norm_w), eps, _ptr(rows), _ptr(w), _ptr(out), M, w.shape[0], K,
-           x32.stride(0), w.stride(0), out.stride(0), epi, _stream())
-    if rc == 3:                      # the activations do not fit shared memory
-        return False
-    if rc != 0:
-        raise KernelError(f._lib.g2b_last_error().decode("utf-8", "replace"))
-    from . import kernels
-    kernels._launches += 1
-    return True
-
-
 def gate_up_bf16(h: torch.Tensor, w_gate_up: torch.Tensor, mid: torch.Tensor, block: int) -> bool:
     """mid = silu(gate) * up with the gate computed in the product's epilogue; takes fused
     matrices whose rows alternate 8 gates / 8 ups."""

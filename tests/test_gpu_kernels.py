@@ -390,33 +390,6 @@ def test_gemm_tc_persistent(M, N, K, bn, stages):
     _check_gemm_tc(M, N, K, bn, stages, True)
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 64, 1024), (8, 4096, 1024), (5, 200, 264), (16, 96, 3072), (40, 512, 520)])
-def test_gemm_small_normed(M, N, K):
-    """RMSNorm folded into the decode product, with and without a row gather, against
-    norm-then-product in float64."""
-    from gguf2bin_b200 import kernels_bf16
-    x = rnd(M + 3, K, seed=90)
-    nw = 1 + 0.1 * rnd(K, seed=91)
-    w = rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=92)
-    rows = torch.tensor([(3 * i + 1) % (M + 3) for i in range(M)], dtype=torch.int32, device=DEV)
-    for r in (None, rows):
-        xs = x[:M] if r is None else x[r.long()]
-        h = torch.from_numpy(P.rmsnorm(xs.cpu().numpy(), nw.cpu().numpy(), 1e-6, np.float32)).to(DEV)
-        ref = h.to(torch.bfloat16).double() @ w.double().T
-        out = torch.empty(M, N, device=DEV)
-        assert kernels_bf16.linear_normed_bf16(x, nw, 1e-6, r, w, out)
-        tol = 2.0 ** -8 * max(1.0, ref.abs().max().item())      # the normed row is rounded to bfloat16
-        assert (out.double() - ref).abs().max().item() < tol
-        if N % 16 == 0:
-            I = N // 2
-            g = ref.view(M, I // 8, 2, 8)[:, :, 0].reshape(M, I)
-            u = ref.view(M, I // 8, 2, 8)[:, :, 1].reshape(M, I)
-            want = (g / (1 + torch.exp(-g))) * u
-            mid = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
-            assert kernels_bf16.linear_normed_bf16(x, nw, 1e-6, r, w, mid, kernels_bf16.EPI_SWIGLU_BF16)
-            assert (mid.double() - want).abs().max().item() <= want.abs().max().item() * 2.0 ** -8 + 2 * tol
-
-
 def test_argmax_over_many_blocks():
     """Greedy over a large vocabulary (two-stage): ties across slices go to the lower id."""
     from gguf2bin_b200 import kernels
