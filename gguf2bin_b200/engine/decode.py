@@ -34,7 +34,7 @@ from .step import Engine, StepError
 
 
 class DecodeSession:
-    EAGER_STEPS = 2          # plain steps before the graph is captured (they warm every buffer)
+    EAGER_STEPS = 1          # plain steps before the graph is captured (the first sizes every buffer)
 
     def __init__(self, engine: Engine, seqs: Sequence[CacheSequence], sampler: Sampler,
                  params: SamplingParams, use_graph: bool = True):
