@@ -27,7 +27,7 @@ def test_embed_rows(dtype):
     assert torch.equal(out, table[ids.long()].float())
 
 
-@pytest.mark.parametrize("H", [100, 64, 1030])
+@pytest.mark.parametrize("H", [100, 64, 1030, 128, 1024, 1028, 2560, 5120])
 @pytest.mark.parametrize("odtype", [torch.float32, torch.bfloat16])
 def test_rmsnorm(H, odtype):
     from gguf2bin_b200 import kernels
