@@ -68,7 +68,7 @@ class DecodeSession:
             workspace=engine.workspace, dtype=engine.model.dtype, q_lens=[1] * B,
             past_lens=[s.length for s in self.seqs], slots=[s.slot for s in self.seqs],
             max_kv_len=max(len(s.pages) for s in self.seqs) * engine.cache.page_size)
-        self.use_graph = use_graph
+        self.use_graph = use_graph and engine.model.graph_safe
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._graph_generation = -1
         self._steps = 0

@@ -118,6 +118,14 @@ class Model:
                 f"{s.vocab_size}, {self.n_params / 1e6:.1f} M parameters, "
                 f"{self.weight_bytes() / 2**20:.1f} MiB, compute {self.dtype}")
 
+    @property
+    def graph_safe(self) -> bool:
+        """True when every part of every block declares that its step may be replayed from a
+        CUDA graph; one part that does not (a part registered from outside, say) makes all steps
+        of this model run plainly."""
+        return (all(getattr(b, "graph_safe", False) for b in self.blocks)
+                and getattr(self.final_norm, "graph_safe", False))
+
     # ---- one step ---------------------------------------------------------------
     def forward(self, ctx: StepContext, cache: Cache, want_rows: Optional[torch.Tensor],
                 n_want: int, logits_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:

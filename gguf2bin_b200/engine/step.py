@@ -11,6 +11,7 @@ the cache, positions); a refused step changes nothing.
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Optional, Sequence as Seq
 
@@ -38,9 +39,20 @@ class StepEntry:
 
 
 class Engine:
-    """A model with its cache and scratch memory; ``step`` is the one way tokens run."""
+    """A model with its cache and scratch memory; ``step`` is the one way tokens run.
 
-    def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None):
+    A step's launches depend on the step's shape only (how many tokens each sequence brings,
+    where it stands, how many places are wanted); which tokens, pages and places is data that
+    the kernels read from the step's metadata on the device.  So when a shape comes back, the
+    launches of its forward pass are captured once in a CUDA graph and replayed from then on:
+    a prompt step is a few hundred launches, and the host's share of it (a few microseconds
+    each) otherwise competes with the device's."""
+
+    GRAPH_MIN_TOKENS = 32        # smaller steps are cheap to launch (and decoding has its own session)
+    GRAPHS_KEPT = 8
+
+    def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None,
+                 step_graphs: bool = True):
         self.model = model
         self.cache: Cache = model.new_cache(max_tokens, max_seqs)
         self.workspace = Workspace(model.device)
@@ -48,6 +60,9 @@ class Engine:
         self._meta_cap = 0
         self._meta_dev: Optional[torch.Tensor] = None
         self._meta_host: Optional[torch.Tensor] = None
+        self.step_graphs = step_graphs and model.graph_safe
+        self._graphs: "OrderedDict[tuple, tuple]" = OrderedDict()    # shape -> (graph, generation, logits)
+        self._seen: "OrderedDict[tuple, int]" = OrderedDict()        # shapes run plainly so far
 
     # ---- sequences -----------------------------------------------------------
     def open_sequence(self) -> Sequence:
@@ -160,7 +175,42 @@ class Engine:
         # the pinned staging buffer is reused: the previous step's copy must be over
         torch.cuda.current_stream().synchronize()
         ctx, want_rows, n_want = self.build_context(entries)
-        logits = self.model.forward(ctx, self.cache, want_rows, n_want)
+        logits = self._forward(entries, ctx, want_rows, n_want)
         for e in entries:
             e.seq.length += len(e.tokens)
         return logits
+
+    def _forward(self, entries, ctx: StepContext, want_rows, n_want) -> Optional[torch.Tensor]:
+        """The model's forward pass of this step: replayed from a graph when the step's shape
+        has been seen before, captured at its second appearance, run plainly otherwise."""
+        if not self.step_graphs or ctx.n_tokens < self.GRAPH_MIN_TOKENS:
+            return self.model.forward(ctx, self.cache, want_rows, n_want)
+        # everything a launch argument or a buffer address is derived from
+        key = (tuple(ctx.q_lens), tuple(ctx.past_lens), tuple(len(e.want) for e in entries),
+               ctx.page_table.shape[1], self._meta_dev.data_ptr())
+        hit = self._graphs.get(key)
+        if hit is not None:
+            graph, generation, logits = hit
+            if generation == self.workspace.generation:
+                self._graphs.move_to_end(key)
+                graph.replay()
+                return logits
+            del self._graphs[key]                     # scratch buffers moved since the capture
+        if self._seen.get(key, 0) >= 1:
+            # the shape ran plainly before, so every scratch buffer it needs exists already
+            torch.cuda.current_stream().synchronize()
+            generation = self.workspace.generation
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx, self.cache, want_rows, n_want)
+            if self.workspace.generation == generation:
+                self._graphs[key] = (graph, generation, logits)
+                while len(self._graphs) > self.GRAPHS_KEPT:
+                    self._graphs.popitem(last=False)
+                graph.replay()
+                return logits
+            # a buffer was created during the capture after all: run plainly, try again next time
+        self._seen[key] = self._seen.get(key, 0) + 1
+        while len(self._seen) > 256:
+            self._seen.popitem(last=False)
+        return self.model.forward(ctx, self.cache, want_rows, n_want)

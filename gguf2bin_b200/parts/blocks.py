@@ -39,6 +39,16 @@ class PreNormBlock:
     def cache_need(self):
         return self.mixer.cache_need()
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a step of this block may be captured in a CUDA graph and replayed: every part
+        must say so itself (``graph_safe = True``: its step does nothing but launch kernels on
+        the current stream, takes its scratch memory from the step's workspace, and neither reads
+        results on the host nor keeps host-side state from step to step)."""
+        return all(getattr(part, "graph_safe", False)
+                   for part in (self.mixer_norm, self.ffn_norm, self.mixer, self.feed_forward,
+                                getattr(self.mixer, "position", None)) if part is not None)
+
     def forward(self, x32: torch.Tensor, ctx, cache_view) -> None:
         # a part that offers ``forward_from_stream`` takes the stream and the norm and may
         # fold the norm into its first product; any other part gets normed activations

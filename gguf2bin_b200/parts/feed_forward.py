@@ -18,6 +18,8 @@ from .registry import register_feed_forward
 
 
 class SwiGLU:
+    graph_safe = True          # its step only launches kernels: may be replayed from a CUDA graph
+
     def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device):
         self.inter = int(spec["intermediate_size"])
         self.hidden = int(hidden_size)

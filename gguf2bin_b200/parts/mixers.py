@@ -25,6 +25,8 @@ from .registry import norm_class, position_class, register_mixer
 
 
 class GQAAttention:
+    graph_safe = True          # its step only launches kernels: may be replayed from a CUDA graph
+
     def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device):
         self.nh = int(spec["n_heads"])
         self.nkv = int(spec["n_kv_heads"])

@@ -11,6 +11,8 @@ from .registry import register_norm
 
 
 class RMSNorm:
+    graph_safe = True          # its step only launches kernels: may be replayed from a CUDA graph
+
     def __init__(self, spec: PartSpec, width: int, dtype: torch.dtype, device):
         self.eps = float(spec["eps"])
         self.width = int(width)

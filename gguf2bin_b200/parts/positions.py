@@ -19,6 +19,8 @@ _INV_FREQ: dict = {}
 
 
 class RopeNeox:
+    graph_safe = True          # its step only launches kernels: may be replayed from a CUDA graph
+
     def __init__(self, spec: PartSpec, head_dim: int, device):
         self.theta = float(spec["theta"])
         self.rotary_dim = int(spec.get("rotary_dim") or head_dim)
@@ -41,6 +43,8 @@ class RopeNeox:
 
 
 class NoPosition:
+    graph_safe = True          # its step only launches kernels: may be replayed from a CUDA graph
+
     def __init__(self, spec: PartSpec, head_dim: int, device):
         pass
 

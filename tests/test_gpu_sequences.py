@@ -189,3 +189,36 @@ def test_trace_run_program(dtype, tmp_path):
         got = np.fromfile(f, "<f4").reshape(-1, V)
         ref = np.stack([plain_logits("b", storage, reqs[r])[i] for r, i in expect[s["step"]]])
         assert_close(got, ref, dtype, f"trace step {s['step']}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_shape_that_comes_back_is_replayed_from_a_graph(dtype):
+    """Steps of one shape (two prompts of 70 and 40 tokens, logits wanted at three places):
+    the first runs plainly, the second is captured in a CUDA graph, later ones replay it.
+    Every run has other tokens, other slots and other pages, and each is compared with the
+    plain implementation; the same tokens again give the same bits as the plain run did."""
+    from gguf2bin_b200.engine import StepEntry
+    name = "c"
+    eng = make_engine(name, dtype, max_tokens=2048)
+    assert eng.step_graphs, "the library's own parts declare themselves fit for graphs"
+    storage = "float32" if dtype == "float32" else "bfloat16"
+    hold = [eng.open_sequence() for _ in range(3)]          # so that later runs get other slots and pages
+    first = None
+    for run in range(5):
+        seed = 300 if run == 4 else 300 + run               # the last run repeats the first one's tokens
+        a, b = random_tokens(name, 70, seed), random_tokens(name, 40, seed + 50)
+        sa, sb = eng.open_sequence(), eng.open_sequence()
+        got = eng.step([StepEntry(sa, a, (0, 69)), StepEntry(sb, b, (39,))]).cpu().numpy()
+        want = np.stack([plain_logits(name, storage, a)[0], plain_logits(name, storage, a)[69],
+                         plain_logits(name, storage, b)[39]])
+        assert_close(got, want, dtype, f"run {run}")
+        if run == 0:
+            first = got
+        if run == 4:
+            assert np.array_equal(got, first), "a replayed step differs from the plain run of the same tokens"
+        if run % 2 == 0:                                     # keep some, close some: the free pages change
+            eng.close_sequence(sa)
+            eng.close_sequence(sb)
+        else:
+            eng.close_sequence(hold.pop())
+    assert len(eng._graphs) == 1
