@@ -12,7 +12,8 @@ from .kernels import KernelError, _call, _fn, _ptr, _stream
 FAST_HEAD_SIZES = (64, 128)          # head sizes the tensor-core attention kernels are written for
 DECODE_CHUNK_KEYS = 256              # keys per CTA of the decode kernel (attn_decode.cu)
 
-units.SPECIALISED_SOURCES[:] = [("attn_decode.cu", ()), ("attn_decode_noalloc.cu", ()),
+units.SPECIALISED_SOURCES[:] = [("attn_decode.cu", ()), ("attn_decode.cu", ("ATTN_DECODE_PAGES=2",)),
+                                ("attn_decode_noalloc.cu", ()),
                                 ("attn_prefill.cu", ()), ("attn_prefill_tc.cu", ())]
 units.BF16_UNITS[:] = [("gemm_small.cu", ()), ("gemm_tc.cu", ())]
 
@@ -182,19 +183,31 @@ def attn_prefill(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_s
           window, scale, _stream())
 
 
+DECODE_FINE_BELOW = 300       # CTAs of 256-key chunks below which the chunks are halved
+
+
 def attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-                scale) -> None:
+                scale, fine=None) -> None:
     """One token per sequence: split-key attention with partial results in scratch memory
-    and a combine pass."""
+    and a combine pass.  A CTA takes a chunk of 256 keys of one kv head; when that gives
+    fewer CTAs than the GPU holds at once (one or two sequences), chunks of 128 keys
+    (``fine``; default by that rule) give twice as many."""
     T = q.shape[0]
-    n_chunks = -(-max(int(ctx.max_kv_len), 1) // DECODE_CHUNK_KEYS)
+    defines = (f"HD={head_dim}",)
+    chunk_keys = DECODE_CHUNK_KEYS
+    if fine is None:
+        tiles = n_kv_heads * -(-(n_heads // n_kv_heads) // 16)
+        fine = T * tiles * -(-max(int(ctx.max_kv_len), 1) // DECODE_CHUNK_KEYS) < DECODE_FINE_BELOW
+    if fine:
+        defines, chunk_keys = defines + ("ATTN_DECODE_PAGES=2",), DECODE_CHUNK_KEYS // 2
+    n_chunks = -(-max(int(ctx.max_kv_len), 1) // chunk_keys)
     ws = ctx.workspace
     part_o = ws.buffer("attn.part_o", (T * n_heads * n_chunks * head_dim,), torch.float32)
     part_ml = ws.buffer("attn.part_ml", (T * n_heads * n_chunks * 2,), torch.float32)
     f = _fn("attn_decode.cu", "g2b_attn_decode",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
              c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p],
-            defines=(f"HD={head_dim}",))
+            defines=defines)
     _call(f, _ptr(q), _ptr(out), _ptr(cache_pages), _ptr(ctx.tok_pos), _ptr(ctx.tok_seq),
           _ptr(ctx.page_table), ctx.page_table.shape[1], T, n_heads, n_kv_heads, head_dim,
           page_size, window, scale, int(ctx.max_kv_len), _ptr(part_o), _ptr(part_ml), _stream())

@@ -236,11 +236,12 @@ def test_sampling_filtered(top_k, top_p, penalty):
         assert ids[r].item() == P.sample_advanced(logits[r].cpu().numpy(), 0.0, top_k, top_p, penalty, rec, 0.5)[0]
 
 
+@pytest.mark.parametrize("fine", [False, True])
 @pytest.mark.parametrize("nh,nkv,hd,window", [(16, 8, 128, 0), (5, 1, 128, 0), (20, 1, 64, 0), (6, 2, 64, 300),
                                               (4, 4, 128, 70)])
-def test_attn_decode(nh, nkv, hd, window):
+def test_attn_decode(nh, nkv, hd, window, fine):
     """Split-key decode attention: one token per sequence at positions before, at and
-    after chunk (256) and page (64) edges; groups of 1, 2, 5 and 20 query heads per kv
+    after chunk (256, or 128 with ``fine``) and page (64) edges; groups of 1, 2, 5 and 20 query heads per kv
     head; a window that starts inside a chunk."""
     from types import SimpleNamespace
     from gguf2bin_b200 import kernels_bf16
@@ -259,7 +260,7 @@ def test_attn_decode(nh, nkv, hd, window):
                           tok_seq=torch.arange(T, dtype=torch.int32, device=DEV), page_table=table,
                           max_kv_len=table.shape[1] * ps, workspace=Workspace(DEV), all_single=True)
     scale = 1 / math.sqrt(hd)
-    assert kernels_bf16.attention_bf16(q, out, cache, ctx, nh, nkv, hd, ps, window, scale)
+    kernels_bf16.attn_decode(q, out, cache, ctx, nh, nkv, hd, ps, window, scale, fine=fine)
     got = out.float().cpu().numpy().reshape(T, nh, hd)
     for b, l in enumerate(lens):
         K, V = Ks[b].float().cpu().numpy(), Vs[b].float().cpu().numpy()
