@@ -482,6 +482,166 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   }
 }
 
+// ---- pairs of CTAs -------------------------------------------------------------------------
+// A cluster of two CTAs (on two SMs) computes a 256 x 256 tile of C with tcgen05.mma
+// cta_group::2: each CTA brings its own 128 rows of A and 128 of the 256 rows of W (the even
+// CTA, the leader, the first 128), so a CTA takes in 32 KB for every 64-wide block of K
+// instead of the 48 KB of a 128 x 256 tile by itself, and the ring is six blocks deep.  One
+// thread of the leader issues the products for both; the accumulator of a CTA is its own 128
+// rows x 256 columns of tensor memory (two of them, as above), and each CTA's epilogue warps
+// write its rows.  Barriers: "full" lives in the leader and counts the bytes of both CTAs'
+// copies; "empty" and "accumulator ready" exist in both and are signalled in both by one
+// commit; "accumulator drained" lives in the leader and gets the arrivals of all eight
+// epilogue warps.  Pairs walk over tiles t = pair, pair + pairs, ...  Before it frees its
+// tensor memory and exits, a CTA tells its peer that it is done and waits for the same from
+// it (bounded like every other wait): the peer's products read this CTA's shared memory and
+// write its tensor memory, and its barriers get arrivals from there.
+constexpr int PAIR_BN = 256;
+
+template <int STAGES> struct SmemPair {
+  static constexpr int A_BYTES = BM * BK * 2;                 // this CTA's 128 rows of A
+  static constexpr int B_BYTES = (PAIR_BN / 2) * BK * 2;      // this CTA's 128 rows of W
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int SCRATCH_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int SCRATCH_BYTES = 4 * 2 * 4096;          // two 32 x 128-byte boxes per epilogue warp
+  static constexpr int BARRIER_OFFSET = SCRATCH_OFFSET + SCRATCH_BYTES;
+  static constexpr int N_BARRIERS = 2 * STAGES + 5;           // full, empty, 2 ready, 2 drained, done
+  static constexpr int TOTAL = BARRIER_OFFSET + 8 * N_BARRIERS + 16 + 1024;   // + slot, alignment slack
+};
+
+enum { ST_PAIR_TIMEOUT = 4 };
+
+template <int STAGES, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const __grid_constant__ CUtensorMap map_c, int M, int N, int K,
+                    int *__restrict__ status) {
+  pdl_launch();
+  extern __shared__ unsigned char smem_raw[];
+  using S = SmemPair<STAGES>;
+  constexpr int BN = PAIR_BN;
+  unsigned char *smem = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::BARRIER_OFFSET);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + S::N_BARRIERS);
+  const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES);
+  const uint32_t acc_full0 = smem_addr(bars + 2 * STAGES), acc_empty0 = smem_addr(bars + 2 * STAGES + 2);
+  const uint32_t done_bar = smem_addr(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();               // 0: the leader
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int nkb = (K + BK - 1) / BK;
+  const int tiles_m = (M + 2 * BM - 1) / (2 * BM);
+  const int n_tiles = tiles_m * ((N + BN - 1) / BN);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);                   // the leader's producer, with both CTAs' bytes
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full0 + 8 * b, 1);
+      mbar_init(acc_empty0 + 8 * b, 8);            // one arrival per epilogue warp of both CTAs
+    }
+    mbar_init(done_bar, 1);
+    mbar_init_fence();
+  }
+  if (warp == 5) tmem_alloc_pair(smem_addr(tmem_slot), (uint32_t)(2 * BN));
+  tc_fence_before();
+  cluster_sync_all();                              // both CTAs' barriers and tensor memory exist
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  pdl_wait();
+
+  if (warp == 4) {
+    if (lane == 0) {
+      const uint32_t leader_full0 = map_to_cta(full0, 0);
+      uint32_t g = 0;                                // k-blocks loaded so far, over all tiles
+      bool ok = true;
+      for (int t = pair; t < n_tiles && ok; t += pairs) {
+        const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM;
+        const int n0 = (t / tiles_m) * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < nkb; ++kb, ++g) {
+          const uint32_t s = g % STAGES;
+          if (g >= STAGES && !mbar_wait(empty0 + 8 * s, ((g / STAGES) - 1) & 1)) {
+            atomicExch(status, ST_PRODUCER_TIMEOUT);
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_addr(smem + s * S::STAGE_BYTES);
+          if (leader) mbar_expect_tx(full0 + 8 * s, 2 * S::STAGE_BYTES);
+          tma_load_2d_pair(a_dst, &map_a, kb * BK, m0, leader_full0 + 8 * s);
+          tma_load_2d_pair(a_dst + S::A_BYTES, &map_w, kb * BK, n0, leader_full0 + 8 * s);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = instr_desc(2 * BM, BN, false);
+      uint32_t g = 0, j = 0;                         // k-blocks and tiles so far
+      bool ok = true;
+      for (int t = pair; t < n_tiles && ok; t += pairs, ++j) {
+        const uint32_t buf = j & 1;
+        // both CTAs' epilogues must have drained this accumulator (it was used by tile j - 2)
+        if (j >= 2 && !mbar_wait(acc_empty0 + 8 * buf, ((j >> 1) - 1) & 1)) {
+          atomicExch(status, ST_MMA_TIMEOUT);
+          break;
+        }
+        tc_fence_after();
+        for (int kb = 0; kb < nkb; ++kb, ++g) {
+          const uint32_t s = g % STAGES;
+          if (!mbar_wait(full0 + 8 * s, (g / STAGES) & 1)) {
+            atomicExch(status, ST_MMA_TIMEOUT);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_addr(smem + s * S::STAGE_BYTES);
+          const uint64_t adesc = desc_k_major(a_addr), bdesc = desc_k_major(a_addr + S::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            umma_bf16_pair(tmem + buf * BN, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(empty0 + 8 * s, 3);       // the stage is free in both CTAs
+        }
+        if (ok) umma_commit_pair(acc_full0 + 8 * buf, 3);   // this tile's products have completed
+      }
+    }
+  } else {
+    unsigned char *stage = smem + S::SCRATCH_OFFSET + warp * (2 * 4096);
+    const uint32_t leader_acc_empty0 = map_to_cta(acc_empty0, 0);
+    uint32_t j = 0, box = 0;
+    for (int t = pair; t < n_tiles; t += pairs, ++j) {
+      const uint32_t buf = j & 1;
+      if (!mbar_wait(acc_full0 + 8 * buf, (j >> 1) & 1)) {
+        if (lane == 0) atomicExch(status, ST_EPILOGUE_TIMEOUT);
+        break;
+      }
+      tc_fence_after();
+      const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM, n0 = (t / tiles_m) * BN;
+      epilogue_tile_bulk<BN, EPI>(tmem + buf * BN, stage, &map_c, m0, n0, M, N, warp, lane, box);
+      // every load of this warp from the accumulator has completed (each is waited for)
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_acc_empty0 + 8 * buf);
+    }
+    if (lane == 0) bulk_wait<0>();                 // the staging buffers are read and C is written
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    // this CTA issues and receives nothing more: tell the peer, and wait for the same from it
+    if (lane == 0) {
+      mbar_arrive_cluster(map_to_cta(done_bar, rank ^ 1u));
+      if (!mbar_wait(done_bar, 0)) atomicExch(status, ST_PAIR_TIMEOUT);
+    }
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc_pair(tmem, (uint32_t)(2 * BN));
+  }
+}
+
 // ---- host side ----------------------------------------------------------------------
 // Tensor maps come from tc::get_map (kept by address and sizes).
 static int make_map(CUtensorMap *map, const void *base, int rows, int K, int ld, int box_rows) {
@@ -551,6 +711,35 @@ static int launch_persistent(const CUtensorMap &ma, const CUtensorMap &mw, void 
   return g2b_check_launch("gemm_tc (persistent)");
 }
 
+template <int STAGES, int EPI>
+static int launch_pair(const CUtensorMap &ma, const CUtensorMap &mw, void *C, int M, int N, int K, int ldc,
+                       int *status, cudaStream_t stream) {
+  static bool configured = false;
+  const int smem = SmemPair<STAGES>::TOTAL;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<STAGES, EPI>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) G2B_REFUSE("gemm_tc: shared memory of %d bytes refused: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  const long long tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + PAIR_BN - 1) / PAIR_BN);
+  if (tiles > 0x7fffffffLL) G2B_REFUSE("gemm_tc: %lld tiles", tiles);
+  const bool is_float = EPI == EPI_STORE_F32 || EPI == EPI_ACCUM_F32;
+  const int c_cols = EPI == EPI_SWIGLU_BF16 ? N / 2 : N;
+  if (((uintptr_t)C & 15) || (ldc * (is_float ? 4 : 2)) % 16)
+    G2B_REFUSE("gemm_tc: the paired kernel stores tiles of C: C must be 16-byte aligned with a row stride "
+               "that is a multiple of 16 bytes (ldc = %d)", ldc);
+  CUtensorMap mc;
+  const int rc = make_map_c(&mc, C, M, c_cols, ldc, is_float);
+  if (rc) return rc;
+  const int max_pairs = sm_count() / 2;
+  if (max_pairs < 1) G2B_REFUSE("gemm_tc: the paired kernel needs two SMs");
+  const unsigned pairs = (unsigned)(tiles < max_pairs ? tiles : max_pairs);
+  g2b_launch_cluster(gemm_tc_pair_kernel<STAGES, EPI>, dim3(2 * pairs), dim3(THREADS), smem, stream, 2u, ma, mw,
+                     mc, M, N, K, status);
+  return g2b_check_launch("gemm_tc (pairs)");
+}
+
 // A [M,K], W [N,K] bfloat16, inner stride 1, row strides multiples of 8 elements, base
 // addresses 16-byte aligned.  epi: 0 store bfloat16, 1 store float, 2 add into float,
 // 3 SiLU gate (C is [M, N/2] bfloat16; N a multiple of 16).  `status` is a device int the
@@ -576,6 +765,20 @@ extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, 
   CUtensorMap ma, mw;
   int rc = make_map(&ma, A, M, K, lda, BM);
   if (rc) return rc;
+  if (persistent == 2) {                           // pairs of CTAs: 256 x 256 tiles, 128 rows of W per CTA
+    if (bn != PAIR_BN) G2B_REFUSE("gemm_tc: the paired kernel has tiles %d wide, not %d", PAIR_BN, bn);
+    rc = make_map(&mw, W, N, K, ldw, PAIR_BN / 2);
+    if (rc) return rc;
+#define G2B_CASE(ST_, E) \
+    if (stages == ST_ && epi == E) return launch_pair<ST_, E>(ma, mw, C, M, N, K, ldc, status, stream);
+#define G2B_SHAPE(ST_) \
+    G2B_CASE(ST_, EPI_STORE_BF16) G2B_CASE(ST_, EPI_STORE_F32) G2B_CASE(ST_, EPI_ACCUM_F32) \
+    G2B_CASE(ST_, EPI_SWIGLU_BF16)
+    G2B_SHAPE(6) G2B_SHAPE(4)
+#undef G2B_SHAPE
+#undef G2B_CASE
+    G2B_REFUSE("gemm_tc: no paired kernel with %d stages and epilogue %d", stages, epi);
+  }
   rc = make_map(&mw, W, N, K, ldw, bn);
   if (rc) return rc;
 #define G2B_CASE(BN_, ST_, E) \

@@ -59,6 +59,7 @@ def check_status() -> None:
                                   "1024-byte boundary; nothing was computed")
             kernel = "attn_prefill_tc" if code > 10 else "gemm_tc"
             what = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue",
+                    4: "a CTA of a pair, for its peer at the end of the kernel,",
                     11: "the TMA producer", 12: "the MMA issuer", 13: "a softmax warp"}.get(code, "a role")
             raise KernelError(f"{kernel} on {dev}: {what} gave up waiting on a barrier (code {code}); "
                               "the result of that launch is invalid")
@@ -70,14 +71,15 @@ def _tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
             and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def _gemm_tc(a, w, out, epi, bn: int = 0, stages: int = 0, persistent: bool = False) -> None:
+def _gemm_tc(a, w, out, epi, bn: int = 0, stages: int = 0, persistent=False) -> None:
     """bn = 0 lets the launcher pick the tile shape from the sizes.  persistent: one CTA per SM
-    walks over the tiles with two accumulators (shapes (128, 6) and (256, 4))."""
+    walks over the tiles with two accumulators (shapes (128, 6) and (256, 4)); persistent = 2:
+    pairs of CTAs on 256 x 256 tiles (shapes (256, 6) and (256, 4))."""
     f = _fn("gemm_tc.cu", "g2b_gemm_tc",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
              c_int, c_int, c_void_p, c_void_p])
     _call(f, _ptr(a), _ptr(w), _ptr(out), a.shape[0], w.shape[0], a.shape[1], a.stride(0),
-          w.stride(0), out.stride(0), epi, bn, stages, 1 if persistent else 0,
+          w.stride(0), out.stride(0), epi, bn, stages, int(persistent),
           _ptr(_status_word(a.device)), _stream())
 
 
