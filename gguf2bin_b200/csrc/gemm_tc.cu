@@ -483,12 +483,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 }
 
 // ---- pairs of CTAs -------------------------------------------------------------------------
-// A cluster of two CTAs (on two SMs) computes a 256 x 256 tile of C with tcgen05.mma
-// cta_group::2: each CTA brings its own 128 rows of A and 128 of the 256 rows of W (the even
-// CTA, the leader, the first 128), so a CTA takes in 32 KB for every 64-wide block of K
-// instead of the 48 KB of a 128 x 256 tile by itself, and the ring is six blocks deep.  One
+// A cluster of two CTAs (on two SMs) computes a 256 x BN tile of C with tcgen05.mma
+// cta_group::2: each CTA brings its own 128 rows of A and half of the BN rows of W (the even
+// CTA, the leader, the first half), so for BN = 256 a CTA takes in 32 KB for every 64-wide
+// block of K instead of the 48 KB of a 128 x 256 tile by itself, and the ring is six blocks deep.  One
 // thread of the leader issues the products for both; the accumulator of a CTA is its own 128
-// rows x 256 columns of tensor memory (two of them, as above), and each CTA's epilogue warps
+// rows x BN columns of tensor memory (two of them, as above), and each CTA's epilogue warps
 // write its rows.  Barriers: "full" lives in the leader and counts the bytes of both CTAs'
 // copies; "empty" and "accumulator ready" exist in both and are signalled in both by one
 // commit; "accumulator drained" lives in the leader and gets the arrivals of all eight
@@ -496,11 +496,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 // tensor memory and exits, a CTA tells its peer that it is done and waits for the same from
 // it (bounded like every other wait): the peer's products read this CTA's shared memory and
 // write its tensor memory, and its barriers get arrivals from there.
-constexpr int PAIR_BN = 256;
-
-template <int STAGES> struct SmemPair {
+template <int BN, int STAGES> struct SmemPair {
   static constexpr int A_BYTES = BM * BK * 2;                 // this CTA's 128 rows of A
-  static constexpr int B_BYTES = (PAIR_BN / 2) * BK * 2;      // this CTA's 128 rows of W
+  static constexpr int B_BYTES = (BN / 2) * BK * 2;           // this CTA's half of the tile's rows of W
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int SCRATCH_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int SCRATCH_BYTES = 4 * 2 * 4096;          // two 32 x 128-byte boxes per epilogue warp
@@ -511,15 +509,14 @@ template <int STAGES> struct SmemPair {
 
 enum { ST_PAIR_TIMEOUT = 4 };
 
-template <int STAGES, int EPI>
+template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_c, int M, int N, int K,
                     int *__restrict__ status) {
   pdl_launch();
   extern __shared__ unsigned char smem_raw[];
-  using S = SmemPair<STAGES>;
-  constexpr int BN = PAIR_BN;
+  using S = SmemPair<BN, STAGES>;
   unsigned char *smem = reinterpret_cast<unsigned char *>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::BARRIER_OFFSET);
@@ -711,18 +708,18 @@ static int launch_persistent(const CUtensorMap &ma, const CUtensorMap &mw, void 
   return g2b_check_launch("gemm_tc (persistent)");
 }
 
-template <int STAGES, int EPI>
+template <int BN, int STAGES, int EPI>
 static int launch_pair(const CUtensorMap &ma, const CUtensorMap &mw, void *C, int M, int N, int K, int ldc,
                        int *status, cudaStream_t stream) {
   static bool configured = false;
-  const int smem = SmemPair<STAGES>::TOTAL;
+  const int smem = SmemPair<BN, STAGES>::TOTAL;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<STAGES, EPI>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<BN, STAGES, EPI>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) G2B_REFUSE("gemm_tc: shared memory of %d bytes refused: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  const long long tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + PAIR_BN - 1) / PAIR_BN);
+  const long long tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
   if (tiles > 0x7fffffffLL) G2B_REFUSE("gemm_tc: %lld tiles", tiles);
   const bool is_float = EPI == EPI_STORE_F32 || EPI == EPI_ACCUM_F32;
   const int c_cols = EPI == EPI_SWIGLU_BF16 ? N / 2 : N;
@@ -735,7 +732,7 @@ static int launch_pair(const CUtensorMap &ma, const CUtensorMap &mw, void *C, in
   const int max_pairs = sm_count() / 2;
   if (max_pairs < 1) G2B_REFUSE("gemm_tc: the paired kernel needs two SMs");
   const unsigned pairs = (unsigned)(tiles < max_pairs ? tiles : max_pairs);
-  g2b_launch_cluster(gemm_tc_pair_kernel<STAGES, EPI>, dim3(2 * pairs), dim3(THREADS), smem, stream, 2u, ma, mw,
+  g2b_launch_cluster(gemm_tc_pair_kernel<BN, STAGES, EPI>, dim3(2 * pairs), dim3(THREADS), smem, stream, 2u, ma, mw,
                      mc, M, N, K, status);
   return g2b_check_launch("gemm_tc (pairs)");
 }
@@ -765,19 +762,20 @@ extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, 
   CUtensorMap ma, mw;
   int rc = make_map(&ma, A, M, K, lda, BM);
   if (rc) return rc;
-  if (persistent == 2) {                           // pairs of CTAs: 256 x 256 tiles, 128 rows of W per CTA
-    if (bn != PAIR_BN) G2B_REFUSE("gemm_tc: the paired kernel has tiles %d wide, not %d", PAIR_BN, bn);
-    rc = make_map(&mw, W, N, K, ldw, PAIR_BN / 2);
+  if (persistent == 2) {                           // pairs of CTAs: 256 x bn tiles, bn / 2 rows of W per CTA
+    if (bn != 256 && bn != 128) G2B_REFUSE("gemm_tc: the paired kernel has tiles 128 or 256 wide, not %d", bn);
+    rc = make_map(&mw, W, N, K, ldw, bn / 2);
     if (rc) return rc;
-#define G2B_CASE(ST_, E) \
-    if (stages == ST_ && epi == E) return launch_pair<ST_, E>(ma, mw, C, M, N, K, ldc, status, stream);
-#define G2B_SHAPE(ST_) \
-    G2B_CASE(ST_, EPI_STORE_BF16) G2B_CASE(ST_, EPI_STORE_F32) G2B_CASE(ST_, EPI_ACCUM_F32) \
-    G2B_CASE(ST_, EPI_SWIGLU_BF16)
-    G2B_SHAPE(6) G2B_SHAPE(4)
+#define G2B_CASE(BN_, ST_, E) \
+    if (bn == BN_ && stages == ST_ && epi == E)                                                      \
+      return launch_pair<BN_, ST_, E>(ma, mw, C, M, N, K, ldc, status, stream);
+#define G2B_SHAPE(BN_, ST_) \
+    G2B_CASE(BN_, ST_, EPI_STORE_BF16) G2B_CASE(BN_, ST_, EPI_STORE_F32) G2B_CASE(BN_, ST_, EPI_ACCUM_F32) \
+    G2B_CASE(BN_, ST_, EPI_SWIGLU_BF16)
+    G2B_SHAPE(256, 6) G2B_SHAPE(256, 4) G2B_SHAPE(128, 8)
 #undef G2B_SHAPE
 #undef G2B_CASE
-    G2B_REFUSE("gemm_tc: no paired kernel with %d stages and epilogue %d", stages, epi);
+    G2B_REFUSE("gemm_tc: no paired kernel for tile width %d with %d stages and epilogue %d", bn, stages, epi);
   }
   rc = make_map(&mw, W, N, K, ldw, bn);
   if (rc) return rc;

@@ -391,13 +391,13 @@ def test_gemm_tc_persistent(M, N, K, bn, stages):
     _check_gemm_tc(M, N, K, bn, stages, True)
 
 
-@pytest.mark.parametrize("stages", [6, 4])
+@pytest.mark.parametrize("bn,stages", [(256, 6), (256, 4), (128, 8)])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (200, 1000, 1032), (2048 + 17, 2560 + 8, 320),
                                    (4096, 2048, 136), (1500, 6144, 1024), (129, 130 * 8, 72)])
-def test_gemm_tc_pairs(M, N, K, stages):
-    """The product on pairs of CTAs (cta_group::2, 256 x 256 tiles): one tile and several per
+def test_gemm_tc_pairs(M, N, K, bn, stages):
+    """The product on pairs of CTAs (cta_group::2, tiles of 256 rows): one tile and several per
     pair, a peer CTA whose rows of A or of W lie wholly or partly outside, every epilogue."""
-    _check_gemm_tc(M, N, K, 256, stages, 2)
+    _check_gemm_tc(M, N, K, bn, stages, 2)
 
 
 def test_argmax_over_many_blocks():
