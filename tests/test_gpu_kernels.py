@@ -400,6 +400,19 @@ def test_gemm_tc_pairs(M, N, K, bn, stages):
     _check_gemm_tc(M, N, K, bn, stages, 2)
 
 
+def test_linear_of_a_long_prompt_runs_on_pairs():
+    """From 4,096 rows on the product is given to pairs of CTAs; the same result as the plain one."""
+    from gguf2bin_b200 import kernels_bf16
+    M, N, K = 4096 + 40, 2368, 264
+    a, w = rnd(M, K, dtype=torch.bfloat16, seed=85), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=86)
+    out = torch.zeros(M, N, device=DEV)
+    assert kernels_bf16._tc_shape(M, N, out) == (256, 6, 2)
+    assert kernels_bf16.linear_bf16(a, w, out, True)
+    kernels_bf16.check_status()
+    ref = a.double() @ w.double().T
+    assert (out.double() - ref).abs().max().item() < 1e-5 * math.sqrt(K) * max(1.0, ref.abs().max().item())
+
+
 def test_argmax_over_many_blocks():
     """Greedy over a large vocabulary (two-stage): ties across slices go to the lower id."""
     from gguf2bin_b200 import kernels
