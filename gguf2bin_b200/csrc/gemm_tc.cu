@@ -763,7 +763,7 @@ extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, 
   int rc = make_map(&ma, A, M, K, lda, BM);
   if (rc) return rc;
   if (persistent == 2) {                           // pairs of CTAs: 256 x bn tiles, bn / 2 rows of W per CTA
-    if (bn != 256 && bn != 128) G2B_REFUSE("gemm_tc: the paired kernel has tiles 128 or 256 wide, not %d", bn);
+    if (bn != 256) G2B_REFUSE("gemm_tc: the paired kernel has tiles 256 wide, not %d", bn);
     rc = make_map(&mw, W, N, K, ldw, bn / 2);
     if (rc) return rc;
 #define G2B_CASE(BN_, ST_, E) \
@@ -772,7 +772,7 @@ extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, 
 #define G2B_SHAPE(BN_, ST_) \
     G2B_CASE(BN_, ST_, EPI_STORE_BF16) G2B_CASE(BN_, ST_, EPI_STORE_F32) G2B_CASE(BN_, ST_, EPI_ACCUM_F32) \
     G2B_CASE(BN_, ST_, EPI_SWIGLU_BF16)
-    G2B_SHAPE(256, 6) G2B_SHAPE(256, 4) G2B_SHAPE(128, 8)
+    G2B_SHAPE(256, 6) G2B_SHAPE(256, 4)
 #undef G2B_SHAPE
 #undef G2B_CASE
     G2B_REFUSE("gemm_tc: no paired kernel for tile width %d with %d stages and epilogue %d", bn, stages, epi);

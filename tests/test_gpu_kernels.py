@@ -391,7 +391,7 @@ def test_gemm_tc_persistent(M, N, K, bn, stages):
     _check_gemm_tc(M, N, K, bn, stages, True)
 
 
-@pytest.mark.parametrize("bn,stages", [(256, 6), (256, 4), (128, 8)])
+@pytest.mark.parametrize("bn,stages", [(256, 6), (256, 4)])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (200, 1000, 1032), (2048 + 17, 2560 + 8, 320),
                                    (4096, 2048, 136), (1500, 6144, 1024), (129, 130 * 8, 72)])
 def test_gemm_tc_pairs(M, N, K, bn, stages):
