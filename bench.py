@@ -2,7 +2,7 @@
 """Decode and prefill throughput of gguf2bin_b200 on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--batch B] [--layers L] [--context C] [--no-points]
+                    [--batch B] [--layers L] [--context C] [--no-points] [--sizes 0.6b|8b|14b]
 
 The default run has the layer sizes of Qwen3-0.6B (28 layers, width 1024, 16/8 heads of
 128, feed-forward 3072, vocabulary 151936, tied embeddings) with random bfloat16
@@ -45,6 +45,13 @@ QWEN3_0P6B = dict(architectures=["Qwen3ForCausalLM"], hidden_size=1024, intermed
                   num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8,
                   head_dim=128, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
                   tie_word_embeddings=True, max_position_embeddings=40960)
+# the layer sizes of BASELINE.json's other configurations, for `--sizes` (not the default run)
+OTHER_SIZES = {
+    "8b": dict(hidden_size=4096, intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32,
+               num_key_value_heads=8, head_dim=128, tie_word_embeddings=False),
+    "14b": dict(hidden_size=5120, intermediate_size=17408, num_hidden_layers=40, num_attention_heads=40,
+                num_key_value_heads=8, head_dim=128, tie_word_embeddings=False),
+}
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
 
@@ -174,7 +181,9 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=QWEN3_0P6B["num_hidden_layers"])
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has")
+    ap.add_argument("--sizes", default="0.6b", choices=["0.6b"] + sorted(OTHER_SIZES),
+                    help="layer sizes: Qwen3-0.6B (the default run) or those of Qwen3-8B / 14B")
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
     a = ap.parse_args()
@@ -198,8 +207,12 @@ def main() -> int:
     from gguf2bin_b200.weights import write_random_model
 
     cfg = dict(QWEN3_0P6B)
+    cfg.update(OTHER_SIZES.get(a.sizes, {}))
     full_layers = cfg["num_hidden_layers"]
+    if a.layers is None:
+        a.layers = full_layers
     cfg["num_hidden_layers"] = a.layers
+    name = {"0.6b": "Qwen3-0.6B", "8b": "Qwen3-8B", "14b": "Qwen3-14B"}[a.sizes]
     start_ctx = a.context // 2
     steps = min(a.steps, a.context - start_ctx - 1)
     pk = peaks()
@@ -264,16 +277,17 @@ def main() -> int:
                 points[f"decode_b{b}"] = b * k / s
 
     out = {
-        "metric": "decode tokens/s (Qwen3-0.6B sizes, random weights, batch 8, context 2048->4096)",
+        "metric": f"decode tokens/s ({name} sizes, random weights, batch {a.batch}, "
+                  f"context {start_ctx}->{a.context})",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": a.warmup,
         "ms_per_step": sec / steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": "Qwen3-0.6B sizes, random weights", "global_batch": a.batch,
+        "config": {"model": f"{name} sizes, random weights", "global_batch": a.batch,
                    "seq_len": a.context, "decode_from": start_ctx, "layers": a.layers,
                    "layers_of_config": full_layers, "hidden": cfg["hidden_size"],
                    "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
-                   "vocab": vocab, "tied": True, "parallelism": "none (1 GPU)",
+                   "vocab": vocab, "tied": bool(cfg["tie_word_embeddings"]), "parallelism": "none (1 GPU)",
                    "l2": "inputs larger than L2 (weights + cache read every step)",
                    "sampling": "greedy on device"},
         "e2e": e2e, "gpu_launches": per_step * steps, "launches_per_step": per_step,

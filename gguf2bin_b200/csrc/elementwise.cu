@@ -156,12 +156,60 @@ rmsnorm_rows_kernel(const float *__restrict__ x, const float *__restrict__ w,
   }
 }
 
+// one block of 256 threads per row for rows of 1,025 to 8,192 elements: the whole row and its
+// weights are fetched at once (up to eight 16-byte loads each per thread) and stay in registers
+// between the sum and the output; H a multiple of 4
+template <typename TO>
+__global__ void __launch_bounds__(256)
+rmsnorm_block_kernel(const float *__restrict__ x, const float *__restrict__ w,
+                     const int *__restrict__ rows, TO *__restrict__ out, int H, float eps) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const float *xr = x + (size_t)(rows ? rows[r] : r) * H;
+  float4 v[8], g[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int k = threadIdx.x * 4 + 1024 * i;
+    v[i] = k < H ? *reinterpret_cast<const float4 *>(xr + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int k = threadIdx.x * 4 + 1024 * i;
+    g[i] = k < H ? *reinterpret_cast<const float4 *>(w + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+    ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)H + eps);
+  TO *o = out + (size_t)r * H;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int k = threadIdx.x * 4 + 1024 * i;
+    if (k < H)
+      store4(o + k, (g[i].x * v[i].x) * inv, (g[i].y * v[i].y) * inv, (g[i].z * v[i].z) * inv,
+             (g[i].w * v[i].w) * inv);
+  }
+}
+
 extern "C" int g2b_rmsnorm(const float *x, const float *w, const int *rows, int n_rows, int H,
                            float eps, void *out, int out_dtype, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (H <= 0) G2B_REFUSE("rmsnorm: bad width %d", H);
   if (H % 4 == 0 && H >= 128 && ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)out)) & 15) == 0 &&
       (out_dtype == G2B_F32 || out_dtype == G2B_BF16)) {
+    if (H > 1024 && H <= 8192) {
+      if (out_dtype == G2B_F32)
+        g2b_launch(rmsnorm_block_kernel<float>, dim3((unsigned)n_rows), dim3(256), 0, stream, x, w, rows, (float *)out, H, eps);
+      else
+        g2b_launch(rmsnorm_block_kernel<bf16>, dim3((unsigned)n_rows), dim3(256), 0, stream, x, w, rows, (bf16 *)out, H, eps);
+      return g2b_check_launch("rmsnorm");
+    }
     const unsigned blocks = (unsigned)((n_rows + 3) / 4);
     if (out_dtype == G2B_F32)
       g2b_launch(rmsnorm_rows_kernel<float>, dim3(blocks), dim3(128), 0, stream, x, w, rows, (float *)out, n_rows, H, eps);

@@ -313,6 +313,193 @@ gemm_small_whole_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W,
   }
 }
 
+// ---- many tiles per CTA ----------------------------------------------------------------------
+// For wide outputs with a long K (the layers of larger models) one 16-row tile per CTA is a
+// poor unit: every CTA stages all of A first (half as many bytes as it then streams of W),
+// the CTAs come in ragged rounds, and what a CTA keeps in flight is bounded by its registers.
+// Here one CTA per SM takes a contiguous range of tiles, eight at a time, and walks over K in
+// chunks of at most CB blocks: it stages a chunk of A once for the eight tiles (two buffers;
+// the next chunk is fetched into registers while this one is in use) and streams that chunk's
+// columns of W for each tile (16 rows x up to 4 KB contiguous per row), keeping the eight
+// accumulators in registers.  The weights go through a ring of RING blocks in shared memory
+// (16-byte cp.async; every thread reads back only what it copied itself, so the ring needs no
+// barrier), which runs RING blocks = 128 KB ahead of the arithmetic across tiles, chunks and
+// batches.  A thread sums its slice of K in the order of K and the 8 warps are added in
+// order, exactly as in the kernels above: the result has the same bits.
+template <int MT> struct StreamCfg {
+  static constexpr int CB = 8 / MT;                 // K blocks per chunk: 8 rows x 2048 or 16 x 1024 columns
+  static constexpr int MROWS = MT * 8;
+  static constexpr int XROWS = CB * KB + XPAD;      // staged row length
+  static constexpr int RING = 16;                   // blocks of W in flight: 16 rows x 512 bytes each
+  static constexpr int BLOCK_BYTES = 16 * KB * 2;
+  static constexpr size_t STAGE_BYTES = (size_t)2 * MROWS * XROWS * sizeof(bf16);
+  static constexpr size_t RED_BYTES = (size_t)WARPS * 16 * MROWS * sizeof(float);
+  static constexpr size_t TOTAL = STAGE_BYTES + RED_BYTES + (size_t)RING * BLOCK_BYTES;
+};
+constexpr int STREAM_BATCH = 8;                     // tiles whose accumulators a thread holds at once
+
+template <int MT>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+gemm_small_stream_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W, void *__restrict__ Cv,
+                         int M, int N, int K, int lda, int ldw, int ldc, int epi, int n_chunks, int kbc,
+                         int tiles_per_cta) {
+  pdl_launch();
+  using C = StreamCfg<MT>;
+  constexpr int MROWS = C::MROWS, XROWS = C::XROWS, RING = C::RING, G = STREAM_BATCH;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  bf16 *xs = reinterpret_cast<bf16 *>(smem_raw);                        // [2][MROWS][XROWS]
+  float *red = reinterpret_cast<float *>(smem_raw + C::STAGE_BYTES);    // [WARPS][16][MROWS]
+  const uint32_t ring = smem_u32(smem_raw + C::STAGE_BYTES + C::RED_BYTES) + threadIdx.x * 16;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int kw = 32 * warp + 8 * c;
+  const int n_tiles = (N + 15) / 16;
+  const int t_begin = blockIdx.x * tiles_per_cta, t_end = min(n_tiles, t_begin + tiles_per_cta);
+
+  // ---- the weight stream: blocks in the order (batch of 8 tiles, chunk, tile, block of the chunk)
+  int p_tile0 = t_begin, p_chunk = 0, p_j = 0, p_d = 0;    // the block that is copied next
+  uint32_t p_slot = 0;
+  auto issue = [&]() {                                      // one block (or nothing), one group
+    if (p_tile0 < t_end) {
+      const int k = (p_chunk * kbc + p_d) * KB + kw;
+      if (k < K) {
+        const int n0 = (p_tile0 + p_j) * 16;
+        cp_async_16(ring + p_slot * C::BLOCK_BYTES, W + (size_t)min(n0 + g, N - 1) * ldw + k);
+        cp_async_16(ring + p_slot * C::BLOCK_BYTES + 4096, W + (size_t)min(n0 + g + 8, N - 1) * ldw + k);
+      }
+      if (++p_d == kbc) {
+        p_d = 0;
+        if (++p_j == min(G, t_end - p_tile0)) {          // the tiles of this batch that exist
+          p_j = 0;
+          if (++p_chunk == n_chunks) {
+            p_chunk = 0;
+            p_tile0 += G;
+          }
+        }
+      }
+    }
+    cp_async_commit();
+    p_slot = (p_slot + 1) % RING;
+  };
+  // the weights do not depend on anything computed before: start their stream first
+#pragma unroll 1
+  for (int i = 0; i < RING; ++i) issue();
+  pdl_wait();                            // the activations come from the kernel before
+
+  // rows past M of both buffers stay zero
+  for (int i = threadIdx.x; i < 2 * MROWS * (XROWS / 8); i += WARPS * 32) {
+    const int r = (i / (XROWS / 8)) % MROWS;
+    if (r >= M) *reinterpret_cast<uint4 *>(xs + (size_t)i * 8) = make_uint4(0, 0, 0, 0);
+  }
+  // a chunk of A: one 16-byte piece per thread and row, through registers
+  const bool stager = (int)threadIdx.x < kbc * (KB / 8);
+  uint4 areg[MROWS];
+  auto fetch_a = [&](int chunk) {
+    const int k = chunk * kbc * KB + threadIdx.x * 8;
+#pragma unroll
+    for (int r = 0; r < MROWS; ++r)
+      areg[r] = (stager && r < M && k < K) ? *reinterpret_cast<const uint4 *>(A + (size_t)r * lda + k)
+                                           : make_uint4(0, 0, 0, 0);
+  };
+  auto store_a = [&](int buf) {
+    if (stager) {
+      bf16 *dst = xs + (size_t)buf * MROWS * XROWS + threadIdx.x * 8;
+#pragma unroll
+      for (int r = 0; r < MROWS; ++r)
+        if (r < M) *reinterpret_cast<uint4 *>(dst + (size_t)r * XROWS) = areg[r];
+    }
+  };
+
+  uint32_t c_slot = 0;                                  // the ring slot that is consumed next
+  for (int tile0 = t_begin; tile0 < t_end; tile0 += G) {
+    float acc[G][MT][4];
+#pragma unroll
+    for (int j = 0; j < G; ++j)
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) acc[j][mt][0] = acc[j][mt][1] = acc[j][mt][2] = acc[j][mt][3] = 0.f;
+    fetch_a(0);
+    store_a(0);
+    for (int chunk = 0; chunk < n_chunks; ++chunk) {
+      __syncthreads();                               // this chunk of A is in place; the other buffer is free
+      if (chunk + 1 < n_chunks) fetch_a(chunk + 1);
+      const bf16 *xc = xs + (size_t)(chunk & 1) * MROWS * XROWS + kw;
+#pragma unroll
+      for (int j = 0; j < G; ++j) {
+        if (tile0 + j < t_end) {
+          for (int d = 0; d < kbc; ++d) {
+            cp_async_wait<RING - 1>();               // this thread's copies of the block have landed
+            uint4 a_lo = make_uint4(0, 0, 0, 0), a_hi = a_lo;
+            if ((chunk * kbc + d) * KB + kw < K) {
+              asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n"
+                           : "=r"(a_lo.x), "=r"(a_lo.y), "=r"(a_lo.z), "=r"(a_lo.w)
+                           : "r"(ring + c_slot * C::BLOCK_BYTES));
+              asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n"
+                           : "=r"(a_hi.x), "=r"(a_hi.y), "=r"(a_hi.z), "=r"(a_hi.w)
+                           : "r"(ring + c_slot * C::BLOCK_BYTES + 4096));
+            }
+            c_slot = (c_slot + 1) % RING;
+            const uint32_t a1[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};
+            const uint32_t a2[4] = {a_lo.z, a_hi.z, a_lo.w, a_hi.w};
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              const uint4 xv = *reinterpret_cast<const uint4 *>(xc + d * KB + (size_t)(8 * mt + g) * XROWS);
+              mma_bf16_16816(acc[j][mt], a1, xv.x, xv.y);
+              mma_bf16_16816(acc[j][mt], a2, xv.z, xv.w);
+            }
+            issue();                                 // the slot just read is filled again
+          }
+        }
+      }
+      if (chunk + 1 < n_chunks) store_a((chunk + 1) & 1);
+    }
+
+    // per tile: the 8 warps' partial sums -> shared memory, added in warp order
+#pragma unroll
+    for (int j = 0; j < G; ++j) {
+      if (tile0 + j >= t_end) break;
+      __syncthreads();                               // `red` is free (and, for j = 0, A's buffers are)
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        float *r0 = red + ((size_t)warp * 16 + g) * MROWS + 8 * mt + 2 * c;
+        float *r1 = r0 + 8 * MROWS;
+        r0[0] = acc[j][mt][0]; r0[1] = acc[j][mt][1];
+        r1[0] = acc[j][mt][2]; r1[1] = acc[j][mt][3];
+      }
+      __syncthreads();
+      const int n0 = (tile0 + j) * 16;
+      if (epi == EPI_SWIGLU_BF16) {
+        for (int i = threadIdx.x; i < 8 * MROWS; i += WARPS * 32) {
+          const int m = i / 8, r = i % 8;
+          float gate = 0.f, up = 0.f;
+#pragma unroll
+          for (int w = 0; w < WARPS; ++w) {
+            gate += red[((size_t)w * 16 + r) * MROWS + m];
+            up += red[((size_t)w * 16 + 8 + r) * MROWS + m];
+          }
+          if (m < M && n0 + 8 + r < N)
+            ((bf16 *)Cv)[(size_t)m * ldc + (n0 >> 1) + r] = __float2bfloat16_rn((gate / (1.f + expf(-gate))) * up);
+        }
+      } else {
+        for (int i = threadIdx.x; i < 16 * MROWS; i += WARPS * 32) {
+          const int m = i / 16, r = i % 16;
+          float v = 0.f;
+#pragma unroll
+          for (int w = 0; w < WARPS; ++w) v += red[((size_t)w * 16 + r) * MROWS + m];
+          const int n = n0 + r;
+          if (m < M && n < N) {
+            const size_t o = (size_t)m * ldc + n;
+            if (epi == EPI_STORE_BF16) ((bf16 *)Cv)[o] = __float2bfloat16_rn(v);
+            else if (epi == EPI_STORE_F32) ((float *)Cv)[o] = v;
+            else atomicAdd((float *)Cv + o, v);   // a reduction: one add per element and launch
+          }
+        }
+      }
+    }
+    __syncthreads();                                 // before the next batch stages A
+  }
+  cp_async_wait<0>();
+}
+
 // shared memory the whole-A kernel needs, or 0 if the case does not fit
 static size_t whole_smem(int mrows, int K, int split = 1) {
   const int nkb = (K + KB - 1) / KB, per = (nkb + split - 1) / split;
@@ -410,6 +597,47 @@ static int launch_mt(const void *A, const void *W, void *C, int M, int N, int K,
   return g2b_check_launch("gemm_small");
 }
 
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+// Whether the many-tiles kernel takes the case: up to 16 rows, enough tiles to fill the GPU
+// by themselves, and a K of 2,048 or more (at K = 1,024 a tile is four blocks, and the per-tile
+// sum over the warps weighs more than what the shared staging saves: 70 against 59 us for a
+// vocabulary of 151,936).
+static bool stream_case(int M, int N, int K) {
+  const int n_tiles = (N + 15) / 16, nkb = (K + KB - 1) / KB;
+  return M <= 16 && n_tiles >= sm_count() && nkb >= 8;
+}
+
+template <int MT>
+static int launch_stream(const void *A, const void *W, void *C, int M, int N, int K, int lda, int ldw, int ldc,
+                         int epi, cudaStream_t stream) {
+  if (epi < EPI_STORE_BF16 || epi > EPI_SWIGLU_BF16) G2B_REFUSE("gemm_small: unknown epilogue %d", epi);
+  constexpr int CB = StreamCfg<MT>::CB;
+  const int smem = (int)StreamCfg<MT>::TOTAL;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_small_stream_kernel<MT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) G2B_REFUSE("gemm_small: shared memory: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const int n_tiles = (N + 15) / 16, nkb = (K + KB - 1) / KB;
+  const int n_chunks = (nkb + CB - 1) / CB, kbc = (nkb + n_chunks - 1) / n_chunks;
+  const int per = (n_tiles + sm_count() - 1) / sm_count();          // tiles per CTA: the same for (almost) all
+  const unsigned grid = (unsigned)((n_tiles + per - 1) / per);
+  g2b_launch(gemm_small_stream_kernel<MT>, dim3(grid), dim3(WARPS * 32), smem, stream, (const bf16 *)A,
+             (const bf16 *)W, C, M, N, K, lda, ldw, ldc, epi, n_chunks, kbc, per);
+  return g2b_check_launch("gemm_small_stream");
+}
+
 // A [M,K] and W [N,K] bfloat16 with unit inner stride; rows 16-byte aligned.
 // epi: 0 store bfloat16, 1 store float, 2 add into float, 3 SiLU gate (C is [M, N/2] bfloat16;
 // N must be a multiple of 16).
@@ -421,6 +649,10 @@ extern "C" int g2b_gemm_small(const void *A, const void *W, void *C, int M, int 
     G2B_REFUSE("gemm_small: K=%d and the row strides (%d, %d) must be multiples of 8", K, lda, ldw);
   if (((uintptr_t)A | (uintptr_t)W) & 15) G2B_REFUSE("gemm_small: operands must be 16-byte aligned");
   if (epi == EPI_SWIGLU_BF16 && N % 16) G2B_REFUSE("gemm_small: gated output needs N %% 16 == 0, N=%d", N);
+  if (stream_case(M, N, K)) {
+    if (M <= 8) return launch_stream<1>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+    return launch_stream<2>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+  }
   const int mrows = M <= 8 ? 8 : (M <= 16 ? 16 : (M <= 32 ? 32 : 64));
   if (whole_smem(mrows, K, final_split(N, K))) {
     if (M <= 8) return launch_whole<1>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);

@@ -27,7 +27,7 @@ def test_embed_rows(dtype):
     assert torch.equal(out, table[ids.long()].float())
 
 
-@pytest.mark.parametrize("H", [100, 64, 1030, 128, 1024, 1028, 2560, 5120])
+@pytest.mark.parametrize("H", [100, 64, 1030, 128, 1024, 1028, 2560, 4096, 5120, 8192, 8200])
 @pytest.mark.parametrize("odtype", [torch.float32, torch.bfloat16])
 def test_rmsnorm(H, odtype):
     from gguf2bin_b200 import kernels
@@ -272,7 +272,11 @@ def test_attn_decode(nh, nkv, hd, window, fine):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 48, 64), (8, 1024, 2048), (3, 200, 264), (16, 96, 1032),
-                                   (33, 1000, 520), (64, 311, 96)])
+                                   (33, 1000, 520), (64, 311, 96),
+                                   # many tiles per CTA: groups of 1, 2, 4, 8 tiles, one and several chunks of K,
+                                   # a last chunk and a last group that are not full, 8 and 16 staged rows
+                                   (1, 4096, 4096), (8, 6144, 4096), (5, 2400 + 8, 2056), (16, 5120, 3080),
+                                   (3, 40000, 2048), (11, 24576, 2048), (7, 80000 + 24, 2304)])
 def test_gemm_small(M, N, K):
     """Weight-streaming product for few rows: every epilogue, widths that are no multiple
     of the 16-row tile or of the 256-wide K block."""
