@@ -639,6 +639,169 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 }
 
+// ---- weight streaming for 17 to 128 rows -------------------------------------------------------
+// With so few rows the time goes to reading W once, and a 128 x 64 tile of C per CTA leaves the
+// memory idle: N / 64 CTAs, each with a ring that is two thirds rows of A.  Here the operands are
+// swapped: a CTA owns 128 rows of W (the 128-row operand of the product, 16 KB per block of K) and
+// all rows of A (the narrow operand: BNB = 32, 64 or 128 of them), so that a stage is mostly
+// weights; and a cluster of S CTAs shares a tile, each taking a contiguous part of K.  Their
+// partial tiles are added in rank order: after a cluster barrier (every CTA's products are
+// done, so the leader's ring is free) the others write their accumulators into the leader's
+// shared memory through the cluster's window, after a second barrier the leader adds them to
+// its own in rank order and writes C.  The accumulator holds C transposed (lane = row of W,
+// column = row of A): for every row of A the 32 lanes of a warp write 32 consecutive outputs.
+// Every wait on an mbarrier is bounded as above and no role leaves before the two cluster
+// barriers, whatever it has recorded in `status`.
+template <int BNB, int STAGES> struct SmemWS {
+  static constexpr int W_BYTES = BM * BK * 2;
+  static constexpr int A_BYTES = BNB * BK * 2;
+  static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int BARRIER_OFFSET = RING_BYTES;
+  static constexpr int TOTAL = BARRIER_OFFSET + 8 * (2 * STAGES + 1) + 16 + 1024;   // + slot, alignment slack
+};
+
+template <int BNB, int STAGES, int EPI>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                       void *__restrict__ Cv, int M, int N, int K, int ldc, int splits,
+                       int *__restrict__ status) {
+  pdl_launch();
+  extern __shared__ unsigned char smem_raw[];
+  using S = SmemWS<BNB, STAGES>;
+  unsigned char *smem = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::BARRIER_OFFSET);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 1);
+  const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES);
+  const uint32_t acc_bar = smem_addr(bars + 2 * STAGES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = (int)(blockIdx.x % (unsigned)splits);        // = the CTA's rank in its cluster
+  const int n0 = (int)(blockIdx.x / (unsigned)splits) * BM;
+  const int nkb = (K + BK - 1) / BK;
+  const int per = (nkb + splits - 1) / splits;
+  const int kb_lo = rank * per, kb_hi = min(nkb, kb_lo + per);   // this CTA's blocks of K (never empty)
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(acc_bar, 1);
+    mbar_init_fence();
+  }
+  if (warp == 5) tmem_alloc(smem_addr(tmem_slot), (uint32_t)BNB);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  pdl_wait();                  // barriers and tensor memory are set up; now the inputs are needed
+
+  bool have_acc = true;        // epilogue warps: the accumulator is complete
+  if (warp == 4) {
+    if (lane == 0) {
+      for (int kb = kb_lo; kb < kb_hi; ++kb) {
+        const int i = kb - kb_lo, s = i % STAGES;
+        if (i >= STAGES && !mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1)) {
+          atomicExch(status, ST_PRODUCER_TIMEOUT);
+          break;
+        }
+        const uint32_t w_dst = smem_addr(smem + s * S::STAGE_BYTES);
+        mbar_expect_tx(full0 + 8 * s, S::STAGE_BYTES);
+        tma_load_2d(w_dst, &map_w, kb * BK, n0, full0 + 8 * s);
+        tma_load_2d(w_dst + S::W_BYTES, &map_a, kb * BK, 0, full0 + 8 * s);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BM, BNB, false);
+      for (int kb = kb_lo; kb < kb_hi; ++kb) {
+        const int i = kb - kb_lo, s = i % STAGES;
+        if (!mbar_wait(full0 + 8 * s, (i / STAGES) & 1)) {
+          atomicExch(status, ST_MMA_TIMEOUT);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t w_addr = smem_addr(smem + s * S::STAGE_BYTES);
+        const uint64_t wdesc = desc_k_major(w_addr), adesc = desc_k_major(w_addr + S::W_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)
+          umma_bf16(tmem, wdesc + 2 * k, adesc + 2 * k, idesc, (i | k) != 0 ? 1u : 0u);
+        umma_commit(empty0 + 8 * s);
+      }
+      umma_commit(acc_bar);                          // all products issued so far have completed
+    }
+  } else {
+    if (!mbar_wait(acc_bar, 0)) {
+      if (lane == 0) atomicExch(status, ST_EPILOGUE_TIMEOUT);
+      have_acc = false;
+    }
+    have_acc = __all_sync(0xffffffffu, have_acc);    // the same for the whole warp
+    tc_fence_after();
+  }
+
+  // partial tiles in the leader's ring: [rank - 1][row of A][128 rows of W] floats
+  float *part = reinterpret_cast<float *>(smem);
+  const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
+  const int nl = warp * 32 + lane;                   // this thread's row of W within the tile
+  if (splits > 1) {
+    tc_fence_before();
+    cluster_sync_all();                              // every CTA's products are done: the leader's ring is free
+    tc_fence_after();
+    if (rank > 0 && warp < 4 && have_acc) {
+      const uint32_t dst0 = map_to_cta(smem_addr(part), 0) + (uint32_t)(((rank - 1) * BNB) * BM + nl) * 4;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BNB && c0 < M; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(taddr + (uint32_t)c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (c0 + j < M)
+            asm volatile("st.shared::cluster.b32 [%0], %1;\n" ::"r"(dst0 + (uint32_t)((c0 + j) * BM) * 4), "r"(r[j])
+                         : "memory");
+      }
+    }
+    tc_fence_before();
+    cluster_sync_all();                              // the partial tiles are in the leader's shared memory
+    tc_fence_after();
+  }
+  if (rank == 0 && warp < 4 && have_acc) {
+    const int n = n0 + nl;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BNB && c0 < M; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(taddr + (uint32_t)c0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int m = c0 + j;
+        float v = __uint_as_float(r[j]);
+        for (int p = 1; p < splits; ++p) v += part[((size_t)(p - 1) * BNB + m) * BM + nl];
+        if (EPI == EPI_SWIGLU_BF16) {
+          // rows 16b .. 16b+7 of W are gates, 16b+8 .. 16b+15 the ups of the same outputs
+          const float up = __shfl_down_sync(0xffffffffu, v, 8);
+          if (m < M && (lane & 8) == 0 && n + 8 < N)
+            ((bf16 *)Cv)[(size_t)m * ldc + ((n >> 4) << 3) + (n & 7)] =
+                __float2bfloat16_rn(__fdividef(v, 1.f + __expf(-v)) * up);
+        } else if (m < M && n < N) {
+          const size_t o = (size_t)m * ldc + n;
+          if (EPI == EPI_STORE_BF16) ((bf16 *)Cv)[o] = __float2bfloat16_rn(v);
+          else if (EPI == EPI_STORE_F32) ((float *)Cv)[o] = v;
+          else atomicAdd((float *)Cv + o, v);        // a reduction: one add per element and launch
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, (uint32_t)BNB);
+  }
+}
+
 // ---- host side ----------------------------------------------------------------------
 // Tensor maps come from tc::get_map (kept by address and sizes).
 static int make_map(CUtensorMap *map, const void *base, int rows, int K, int ld, int box_rows) {
@@ -737,6 +900,33 @@ static int launch_pair(const CUtensorMap &ma, const CUtensorMap &mw, void *C, in
   return g2b_check_launch("gemm_tc (pairs)");
 }
 
+template <int BNB, int STAGES, int EPI>
+static int launch_wstream(const void *A, const void *W, void *C, int M, int N, int K, int lda, int ldw, int ldc,
+                          int *status, cudaStream_t stream) {
+  static bool configured = false;
+  using S = SmemWS<BNB, STAGES>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_wstream_kernel<BNB, STAGES, EPI>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) G2B_REFUSE("gemm_tc: shared memory of %d bytes refused: %s", S::TOTAL, cudaGetErrorString(e));
+    configured = true;
+  }
+  CUtensorMap mw, ma;
+  int rc = make_map(&mw, W, N, K, ldw, BM);
+  if (rc) return rc;
+  rc = make_map(&ma, A, M, K, lda, BNB);
+  if (rc) return rc;
+  const int tiles = (N + BM - 1) / BM, nkb = (K + BK - 1) / BK;
+  // parts of K: as many as keep every CTA on the GPU at once and give a part 16 blocks or more
+  int splits = 1;
+  while (splits < 4 && tiles * splits * 2 <= sm_count() && nkb / (splits * 2) >= 16) splits *= 2;
+  while (splits > 1 && (splits - 1) * ((nkb + splits - 1) / splits) >= nkb) splits /= 2;   // no empty part
+  if ((long long)(splits - 1) * BNB * BM * 4 > S::RING_BYTES) splits = 1;
+  g2b_launch_cluster(gemm_tc_wstream_kernel<BNB, STAGES, EPI>, dim3((unsigned)(tiles * splits)), dim3(THREADS),
+                     S::TOTAL, stream, (unsigned)splits, mw, ma, C, M, N, K, ldc, splits, status);
+  return g2b_check_launch("gemm_tc (weight streaming)");
+}
+
 // A [M,K], W [N,K] bfloat16, inner stride 1, row strides multiples of 8 elements, base
 // addresses 16-byte aligned.  epi: 0 store bfloat16, 1 store float, 2 add into float,
 // 3 SiLU gate (C is [M, N/2] bfloat16; N a multiple of 16).  `status` is a device int the
@@ -744,7 +934,9 @@ static int launch_pair(const CUtensorMap &ma, const CUtensorMap &mw, void *C, in
 // (64,4) (64,8) (128,3) (128,6) (256,4); bn = 0 picks one from the sizes: wide tiles when
 // there are plenty of them, narrow tiles with a deeper ring when the grid would not fill
 // the GPU (the ring has to cover the latency of the copies by itself then).  persistent = 1:
-// the variant with one CTA per SM and two accumulators, shapes (128,6) and (256,4).
+// the variant with one CTA per SM and two accumulators, shapes (128,6) and (256,4).  persistent
+// = 2: pairs of CTAs on 256 x 256 tiles, shapes (256,6) and (256,4).  persistent = 3 (at most
+// 128 rows; bn and stages are ignored): the weight-streaming kernel with K split over a cluster.
 extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, int K, int lda,
                            int ldw, int ldc, int epi, int bn, int stages, int persistent, int *status,
                            cudaStream_t stream) {
@@ -758,6 +950,18 @@ extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, 
     const long long tiles128 = (long long)((M + BM - 1) / BM) * ((N + 127) / 128);
     if (tiles128 >= 2 * 148) { bn = 128; stages = 3; }
     else { bn = 64; stages = 4; }
+  }
+  if (persistent == 3) {                           // 17 to 128 rows: the weights stream, K split over a cluster
+    if (M > 128) G2B_REFUSE("gemm_tc: the weight-streaming kernel takes at most 128 rows, got %d", M);
+#define G2B_CASE(E) \
+    if (epi == E) {                                                                                        \
+      if (M <= 32) return launch_wstream<32, 9, E>(A, W, C, M, N, K, lda, ldw, ldc, status, stream);       \
+      if (M <= 64) return launch_wstream<64, 8, E>(A, W, C, M, N, K, lda, ldw, ldc, status, stream);       \
+      return launch_wstream<128, 6, E>(A, W, C, M, N, K, lda, ldw, ldc, status, stream);                   \
+    }
+    G2B_CASE(EPI_STORE_BF16) G2B_CASE(EPI_STORE_F32) G2B_CASE(EPI_ACCUM_F32) G2B_CASE(EPI_SWIGLU_BF16)
+#undef G2B_CASE
+    G2B_REFUSE("gemm_tc: unknown epilogue %d", epi);
   }
   CUtensorMap ma, mw;
   int rc = make_map(&ma, A, M, K, lda, BM);

@@ -74,7 +74,8 @@ def _tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
 def _gemm_tc(a, w, out, epi, bn: int = 0, stages: int = 0, persistent=False) -> None:
     """bn = 0 lets the launcher pick the tile shape from the sizes.  persistent: one CTA per SM
     walks over the tiles with two accumulators (shapes (128, 6) and (256, 4)); persistent = 2:
-    pairs of CTAs on 256 x 256 tiles (shapes (256, 6) and (256, 4))."""
+    pairs of CTAs on 256 x 256 tiles (shapes (256, 6) and (256, 4)); persistent = 3: at most 128
+    rows, 128 rows of W per CTA and K split over a cluster (bn and stages are not used)."""
     f = _fn("gemm_tc.cu", "g2b_gemm_tc",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
              c_int, c_int, c_void_p, c_void_p])
@@ -98,7 +99,7 @@ def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate:
         _gemm_small(a, w, out, epi)
         return True
     if choice == "tc":
-        _gemm_tc(a, w, out, epi, *_tc_shape(a.shape[0], w.shape[0], out))
+        _gemm_tc(a, w, out, epi, *_tc_shape(a.shape[0], w.shape[0], out, a.shape[1]))
         return True
     return False
 
@@ -116,13 +117,15 @@ def _pick_product(a: torch.Tensor, w: torch.Tensor):
     return None
 
 
-def _tc_shape(M: int, N: int, out: torch.Tensor = None):
+def _tc_shape(M: int, N: int, out: torch.Tensor = None, K: int = 0):
     """(tile width, stages, persistent) of the tcgen05 product; (0, 0, False) lets the launcher
     choose.  Prompts (more than one row of tiles) take the persistent kernel when C can be
     written as tiles: wide tiles when there are enough of them to fill the GPU; long prompts
     take pairs of CTAs (persistent = 2; measured 4-9 % faster from 4,096 rows on, the same or
     slower at 2,048)."""
     if M <= 128:                       # one row of tiles: the weights stream, as in decode
+        if M > 16 and N >= 2048 and K >= 2048:
+            return (0, 0, 3)           # big weights: 128 rows of W per CTA, K split over a cluster
         return (128, 3, False) if N >= 32768 else (64, 8, False)
     if out is not None and out.data_ptr() % 16 == 0 and (out.stride(0) * out.element_size()) % 16 == 0:
         tiles_m = -(-M // 128)
@@ -152,7 +155,7 @@ def gate_up_bf16(h: torch.Tensor, w_gate_up: torch.Tensor, mid: torch.Tensor, bl
         _gemm_small(h, w_gate_up, mid, EPI_SWIGLU_BF16)
         return True
     if choice == "tc":
-        _gemm_tc(h, w_gate_up, mid, EPI_SWIGLU_BF16, *_tc_shape(h.shape[0], w_gate_up.shape[0], mid))
+        _gemm_tc(h, w_gate_up, mid, EPI_SWIGLU_BF16, *_tc_shape(h.shape[0], w_gate_up.shape[0], mid, h.shape[1]))
         return True
     return False
 
