@@ -645,11 +645,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // swapped: a CTA owns 128 rows of W (the 128-row operand of the product, 16 KB per block of K) and
 // all rows of A (the narrow operand: BNB = 32, 64 or 128 of them), so that a stage is mostly
 // weights; and a cluster of S CTAs shares a tile, each taking a contiguous part of K.  Their
-// partial tiles are added in rank order: after a cluster barrier (every CTA's products are
-// done, so the leader's ring is free) the others write their accumulators into the leader's
-// shared memory through the cluster's window, after a second barrier the leader adds them to
-// its own in rank order and writes C.  The accumulator holds C transposed (lane = row of W,
-// column = row of A): for every row of A the 32 lanes of a warp write 32 consecutive outputs.
+// partial tiles are added in rank order, by all of them: after a cluster barrier (every CTA's
+// products are done, so the rings are free) each CTA lays its accumulator out in its own shared
+// memory; the rows of A are dealt out to the CTAs in equal ranges, and a CTA sends every other
+// one that one's range of its tile with a bulk copy through the cluster's window; a CTA waits
+// for the bytes it is due, a second cluster barrier tells everybody that all copies have
+// arrived, and each CTA adds the S tiles of its range in rank order and writes those rows of C.
+// The accumulator holds C transposed (lane = row of W, column = row of A); on the way through
+// shared memory it is turned, so that C is written in rows, four outputs per lane.
 // Every wait on an mbarrier is bounded as above and no role leaves before the two cluster
 // barriers, whatever it has recorded in `status`.
 template <int BNB, int STAGES> struct SmemWS {
@@ -658,7 +661,7 @@ template <int BNB, int STAGES> struct SmemWS {
   static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int BARRIER_OFFSET = RING_BYTES;
-  static constexpr int TOTAL = BARRIER_OFFSET + 8 * (2 * STAGES + 1) + 16 + 1024;   // + slot, alignment slack
+  static constexpr int TOTAL = BARRIER_OFFSET + 8 * (2 * STAGES + 3) + 1024;   // + slot, one more barrier, alignment slack
 };
 
 template <int BNB, int STAGES, int EPI>
@@ -682,6 +685,11 @@ gemm_tc_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
   const int nkb = (K + BK - 1) / BK;
   const int per = (nkb + splits - 1) / splits;
   const int kb_lo = rank * per, kb_hi = min(nkb, kb_lo + per);   // this CTA's blocks of K (never empty)
+  // CTAs that run side by side would all read the same columns of rows that lie a power of two
+  // apart, which lands on few memory channels: every tile starts its walk over K somewhere else
+  // (and wraps around), so that the order of its sum depends on the tile only
+  const int n_loc = kb_hi - kb_lo;
+  const int rot = (int)((blockIdx.x / (unsigned)splits) * 5u % (unsigned)n_loc);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -698,11 +706,19 @@ gemm_tc_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
   const uint32_t tmem = *tmem_slot;
   pdl_wait();                  // barriers and tensor memory are set up; now the inputs are needed
 
+#ifdef G2B_GEMM_TIMING
+  // stamps of CTA 0 (a leader) and CTA 1 (its first peer), thread 0: after set-up, accumulator
+  // complete, first cluster barrier passed, tile staged / arrived, second barrier passed, end
+#define TSTAMP(i) if (threadIdx.x == 0 && blockIdx.x < 2) g2b_timing[8 * blockIdx.x + (i)] = (unsigned long long)clock64()
+#else
+#define TSTAMP(i)
+#endif
+  TSTAMP(0);
   bool have_acc = true;        // epilogue warps: the accumulator is complete
   if (warp == 4) {
     if (lane == 0) {
-      for (int kb = kb_lo; kb < kb_hi; ++kb) {
-        const int i = kb - kb_lo, s = i % STAGES;
+      for (int i = 0; i < n_loc; ++i) {
+        const int kb = kb_lo + (i + rot) % n_loc, s = i % STAGES;
         if (i >= STAGES && !mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1)) {
           atomicExch(status, ST_PRODUCER_TIMEOUT);
           break;
@@ -716,8 +732,8 @@ gemm_tc_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
   } else if (warp == 5) {
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BM, BNB, false);
-      for (int kb = kb_lo; kb < kb_hi; ++kb) {
-        const int i = kb - kb_lo, s = i % STAGES;
+      for (int i = 0; i < n_loc; ++i) {
+        const int s = i % STAGES;
         if (!mbar_wait(full0 + 8 * s, (i / STAGES) & 1)) {
           atomicExch(status, ST_MMA_TIMEOUT);
           break;
@@ -740,60 +756,139 @@ gemm_tc_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     have_acc = __all_sync(0xffffffffu, have_acc);    // the same for the whole warp
     tc_fence_after();
   }
+  TSTAMP(1);
 
-  // partial tiles in the leader's ring: [rank - 1][row of A][128 rows of W] floats
-  float *part = reinterpret_cast<float *>(smem);
+  // Every CTA lays its partial tile out in its own ring as [row of A][128 rows of W] floats (the 32
+  // lanes of a warp write 32 consecutive floats).  With K in parts, the rows of A are dealt out to
+  // the CTAs of the cluster in equal ranges: a CTA sends every other CTA that one's range of its
+  // tile with one bulk copy through the cluster's window (the bytes are counted on a barrier of
+  // the receiver), then adds the S tiles of its own range in rank order and writes those rows of C.
+  float *tile = reinterpret_cast<float *>(smem);                                 // [BNB][128]
+  float *recv = tile + (size_t)BNB * BM;                                         // [sender][rows of my range][128]
+  const uint32_t part_bar = smem_addr(bars + 2 * STAGES + 1 + 1);               // after the tensor-memory slot
   const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
   const int nl = warp * 32 + lane;                   // this thread's row of W within the tile
+  const int m_all = min(M, BNB);
+  const int mq = (m_all + splits - 1) / splits;      // rows of A per CTA of the cluster
+  const int m_lo = min(m_all, rank * mq), m_hi = min(m_all, m_lo + mq);          // this CTA's range
   if (splits > 1) {
-    tc_fence_before();
-    cluster_sync_all();                              // every CTA's products are done: the leader's ring is free
-    tc_fence_after();
-    if (rank > 0 && warp < 4 && have_acc) {
-      const uint32_t dst0 = map_to_cta(smem_addr(part), 0) + (uint32_t)(((rank - 1) * BNB) * BM + nl) * 4;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BNB && c0 < M; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(taddr + (uint32_t)c0, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (c0 + j < M)
-            asm volatile("st.shared::cluster.b32 [%0], %1;\n" ::"r"(dst0 + (uint32_t)((c0 + j) * BM) * 4), "r"(r[j])
-                         : "memory");
-      }
+    if (threadIdx.x == 0) {
+      mbar_init(part_bar, 1);
+      mbar_init_fence();
+      mbar_expect_tx(part_bar, (uint32_t)(splits - 1) * (uint32_t)(m_hi - m_lo) * BM * 4);
     }
     tc_fence_before();
-    cluster_sync_all();                              // the partial tiles are in the leader's shared memory
+    cluster_sync_all();                              // every CTA's products are done: the rings are free
     tc_fence_after();
+    TSTAMP(2);
   }
-  if (rank == 0 && warp < 4 && have_acc) {
-    const int n = n0 + nl;
+  if (warp < 4 && have_acc) {
 #pragma unroll 1
-    for (int c0 = 0; c0 < BNB && c0 < M; c0 += 32) {
+    for (int c0 = 0; c0 < m_all; c0 += 32) {
       uint32_t r[32];
       tmem_ld32(taddr + (uint32_t)c0, r);
       tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int m = c0 + j;
-        float v = __uint_as_float(r[j]);
-        for (int p = 1; p < splits; ++p) v += part[((size_t)(p - 1) * BNB + m) * BM + nl];
-        if (EPI == EPI_SWIGLU_BF16) {
-          // rows 16b .. 16b+7 of W are gates, 16b+8 .. 16b+15 the ups of the same outputs
-          const float up = __shfl_down_sync(0xffffffffu, v, 8);
-          if (m < M && (lane & 8) == 0 && n + 8 < N)
-            ((bf16 *)Cv)[(size_t)m * ldc + ((n >> 4) << 3) + (n & 7)] =
-                __float2bfloat16_rn(__fdividef(v, 1.f + __expf(-v)) * up);
-        } else if (m < M && n < N) {
-          const size_t o = (size_t)m * ldc + n;
-          if (EPI == EPI_STORE_BF16) ((bf16 *)Cv)[o] = __float2bfloat16_rn(v);
-          else if (EPI == EPI_STORE_F32) ((float *)Cv)[o] = v;
-          else atomicAdd((float *)Cv + o, v);        // a reduction: one add per element and launch
+      for (int j = 0; j < 32; ++j)
+        if (c0 + j < m_all) tile[(size_t)(c0 + j) * BM + nl] = __uint_as_float(r[j]);
+    }
+  }
+  if (splits > 1) {
+    fence_async_shared();                            // the bulk copies below read what was just written
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int q = 0; q < splits; ++q) {
+        const int q_lo = min(m_all, q * mq), q_hi = min(m_all, q_lo + mq);
+        if (q == rank || q_hi <= q_lo) continue;
+        asm volatile(
+            "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+            ::"r"(map_to_cta(smem_addr(recv) + (uint32_t)rank * (uint32_t)mq * BM * 4, (uint32_t)q)),
+              "r"(smem_addr(tile) + (uint32_t)q_lo * BM * 4), "r"((uint32_t)(q_hi - q_lo) * BM * 4),
+              "r"(map_to_cta(part_bar, (uint32_t)q))
+            : "memory");
+      }
+    }
+    if (warp < 4) {
+      if (m_hi > m_lo && !mbar_wait(part_bar, 0)) {  // the other CTAs' rows of my range have arrived
+        if (lane == 0) atomicExch(status, ST_EPILOGUE_TIMEOUT);
+        have_acc = false;
+      }
+      have_acc = __all_sync(0xffffffffu, have_acc);
+    }
+    TSTAMP(3);
+    tc_fence_before();
+    cluster_sync_all();                              // every copy has arrived: nobody's tile is needed any more
+    tc_fence_after();
+    TSTAMP(4);
+  } else {
+    if (warp < 4) asm volatile("bar.sync 1, 128;\n" ::: "memory");       // the four epilogue warps
+  }
+  if (warp < 4 && have_acc) {
+    // this CTA's rows of C: a warp takes every fourth row of A, a lane four neighbours of the
+    // row's 128 outputs
+    const int n = n0 + 4 * lane;
+    const bool vec_ok = ((((uintptr_t)Cv) | ((size_t)ldc * 4)) & 15) == 0;
+    for (int m = m_lo + warp; m < m_hi; m += 4) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        if (p < splits) {
+          const float *src = p == rank ? tile + (size_t)m * BM : recv + ((size_t)p * mq + (m - m_lo)) * BM;
+          const float4 t = *reinterpret_cast<const float4 *>(src + 4 * lane);
+          v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+        }
+      }
+      if (EPI == EPI_SWIGLU_BF16) {
+        // rows 16b .. 16b+7 of W are gates (lanes 4b, 4b+1), 16b+8 .. 16b+15 the ups (lanes 4b+2, 4b+3)
+        float4 up;
+        up.x = __shfl_down_sync(0xffffffffu, v.x, 2); up.y = __shfl_down_sync(0xffffffffu, v.y, 2);
+        up.z = __shfl_down_sync(0xffffffffu, v.z, 2); up.w = __shfl_down_sync(0xffffffffu, v.w, 2);
+        if ((lane & 2) == 0) {
+          const int col = ((n >> 4) << 3) + (n & 7);          // output column of v.x
+          bf16 *dst = (bf16 *)Cv + (size_t)m * ldc + col;
+          const float h0 = __fdividef(v.x, 1.f + __expf(-v.x)) * up.x, h1 = __fdividef(v.y, 1.f + __expf(-v.y)) * up.y;
+          const float h2 = __fdividef(v.z, 1.f + __expf(-v.z)) * up.z, h3 = __fdividef(v.w, 1.f + __expf(-v.w)) * up.w;
+          if (n + 16 <= N && ((((uintptr_t)dst) & 7) == 0)) {
+            *reinterpret_cast<uint2 *>(dst) = make_uint2(pack2f(h0, h1), pack2f(h2, h3));
+          } else {
+            const float h[4] = {h0, h1, h2, h3};
+            for (int e = 0; e < 4; ++e)
+              if (n + 8 + e < N) dst[e] = __float2bfloat16_rn(h[e]);
+          }
+        }
+      } else {
+        const size_t o = (size_t)m * ldc + n;
+        const float f[4] = {v.x, v.y, v.z, v.w};
+        if (EPI == EPI_STORE_BF16) {
+          bf16 *dst = (bf16 *)Cv + o;
+          if (n + 4 <= N && ((((uintptr_t)dst) & 7) == 0)) {
+            *reinterpret_cast<uint2 *>(dst) = make_uint2(pack2f(v.x, v.y), pack2f(v.z, v.w));
+          } else {
+            for (int e = 0; e < 4; ++e)
+              if (n + e < N) dst[e] = __float2bfloat16_rn(f[e]);
+          }
+        } else if (EPI == EPI_STORE_F32) {
+          float *dst = (float *)Cv + o;
+          if (n + 4 <= N && vec_ok) {
+            *reinterpret_cast<float4 *>(dst) = v;
+          } else {
+            for (int e = 0; e < 4; ++e)
+              if (n + e < N) dst[e] = f[e];
+          }
+        } else {
+          float *dst = (float *)Cv + o;            // a reduction: one add per element and launch
+          if (n + 4 <= N && vec_ok) {
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z),
+                         "f"(v.w) : "memory");
+          } else {
+            for (int e = 0; e < 4; ++e)
+              if (n + e < N) atomicAdd(dst + e, f[e]);
+          }
         }
       }
     }
   }
+  TSTAMP(5);
   tc_fence_before();
   __syncthreads();
   if (warp == 5) {
@@ -801,6 +896,7 @@ gemm_tc_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     tmem_dealloc(tmem, (uint32_t)BNB);
   }
 }
+#undef TSTAMP
 
 // ---- host side ----------------------------------------------------------------------
 // Tensor maps come from tc::get_map (kept by address and sizes).
@@ -902,7 +998,7 @@ static int launch_pair(const CUtensorMap &ma, const CUtensorMap &mw, void *C, in
 
 template <int BNB, int STAGES, int EPI>
 static int launch_wstream(const void *A, const void *W, void *C, int M, int N, int K, int lda, int ldw, int ldc,
-                          int *status, cudaStream_t stream) {
+                          int want_splits, int *status, cudaStream_t stream) {
   static bool configured = false;
   using S = SmemWS<BNB, STAGES>;
   if (!configured) {
@@ -920,8 +1016,9 @@ static int launch_wstream(const void *A, const void *W, void *C, int M, int N, i
   // parts of K: as many as keep every CTA on the GPU at once and give a part 16 blocks or more
   int splits = 1;
   while (splits < 4 && tiles * splits * 2 <= sm_count() && nkb / (splits * 2) >= 16) splits *= 2;
+  if (want_splits == 1 || want_splits == 2 || want_splits == 4) splits = want_splits;       // the caller's choice
   while (splits > 1 && (splits - 1) * ((nkb + splits - 1) / splits) >= nkb) splits /= 2;   // no empty part
-  if ((long long)(splits - 1) * BNB * BM * 4 > S::RING_BYTES) splits = 1;
+  static_assert((2 * BNB + 8) * BM * 4 <= S::RING_BYTES, "the tile and the received ranges must fit the ring");
   g2b_launch_cluster(gemm_tc_wstream_kernel<BNB, STAGES, EPI>, dim3((unsigned)(tiles * splits)), dim3(THREADS),
                      S::TOTAL, stream, (unsigned)splits, mw, ma, C, M, N, K, ldc, splits, status);
   return g2b_check_launch("gemm_tc (weight streaming)");
@@ -936,7 +1033,8 @@ static int launch_wstream(const void *A, const void *W, void *C, int M, int N, i
 // the GPU (the ring has to cover the latency of the copies by itself then).  persistent = 1:
 // the variant with one CTA per SM and two accumulators, shapes (128,6) and (256,4).  persistent
 // = 2: pairs of CTAs on 256 x 256 tiles, shapes (256,6) and (256,4).  persistent = 3 (at most
-// 128 rows; bn and stages are ignored): the weight-streaming kernel with K split over a cluster.
+// 128 rows; stages is ignored, bn = 1, 2 or 4 asks for that many parts of K, anything else lets
+// the launcher choose): the weight-streaming kernel with K split over a cluster.
 extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, int K, int lda,
                            int ldw, int ldc, int epi, int bn, int stages, int persistent, int *status,
                            cudaStream_t stream) {
@@ -955,9 +1053,9 @@ extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, 
     if (M > 128) G2B_REFUSE("gemm_tc: the weight-streaming kernel takes at most 128 rows, got %d", M);
 #define G2B_CASE(E) \
     if (epi == E) {                                                                                        \
-      if (M <= 32) return launch_wstream<32, 9, E>(A, W, C, M, N, K, lda, ldw, ldc, status, stream);       \
-      if (M <= 64) return launch_wstream<64, 8, E>(A, W, C, M, N, K, lda, ldw, ldc, status, stream);       \
-      return launch_wstream<128, 6, E>(A, W, C, M, N, K, lda, ldw, ldc, status, stream);                   \
+      if (M <= 32) return launch_wstream<32, 9, E>(A, W, C, M, N, K, lda, ldw, ldc, bn, status, stream);   \
+      if (M <= 64) return launch_wstream<64, 8, E>(A, W, C, M, N, K, lda, ldw, ldc, bn, status, stream);   \
+      return launch_wstream<128, 6, E>(A, W, C, M, N, K, lda, ldw, ldc, bn, status, stream);               \
     }
     G2B_CASE(EPI_STORE_BF16) G2B_CASE(EPI_STORE_F32) G2B_CASE(EPI_ACCUM_F32) G2B_CASE(EPI_SWIGLU_BF16)
 #undef G2B_CASE
