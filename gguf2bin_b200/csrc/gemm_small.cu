@@ -607,13 +607,14 @@ static int sm_count() {
   return n;
 }
 
-// Whether the many-tiles kernel takes the case: up to 16 rows, enough tiles to fill the GPU
+// Whether the many-tiles kernel takes the case: up to 8 rows (with more, the tcgen05 kernel that
+// splits K over a cluster is faster against weights of this size), enough tiles to fill the GPU
 // by themselves, and a K of 2,048 or more (at K = 1,024 a tile is four blocks, and the per-tile
 // sum over the warps weighs more than what the shared staging saves: 70 against 59 us for a
 // vocabulary of 151,936).
 static bool stream_case(int M, int N, int K) {
   const int n_tiles = (N + 15) / 16, nkb = (K + KB - 1) / KB;
-  return M <= 16 && n_tiles >= sm_count() && nkb >= 8;
+  return M <= 8 && n_tiles >= sm_count() && nkb >= 8;
 }
 
 template <int MT>
@@ -649,10 +650,7 @@ extern "C" int g2b_gemm_small(const void *A, const void *W, void *C, int M, int 
     G2B_REFUSE("gemm_small: K=%d and the row strides (%d, %d) must be multiples of 8", K, lda, ldw);
   if (((uintptr_t)A | (uintptr_t)W) & 15) G2B_REFUSE("gemm_small: operands must be 16-byte aligned");
   if (epi == EPI_SWIGLU_BF16 && N % 16) G2B_REFUSE("gemm_small: gated output needs N %% 16 == 0, N=%d", N);
-  if (stream_case(M, N, K)) {
-    if (M <= 8) return launch_stream<1>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
-    return launch_stream<2>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
-  }
+  if (stream_case(M, N, K)) return launch_stream<1>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
   const int mrows = M <= 8 ? 8 : (M <= 16 ? 16 : (M <= 32 ? 32 : 64));
   if (whole_smem(mrows, K, final_split(N, K))) {
     if (M <= 8) return launch_whole<1>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);

@@ -105,12 +105,14 @@ def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate:
 
 
 def _pick_product(a: torch.Tensor, w: torch.Tensor):
-    """Which kernel multiplies: the weight-streaming one up to 16 rows (every 16-row tile of
-    W re-stages all rows of a, which stops paying beyond that) and for narrow outputs up to
-    64 rows; the tcgen05 one otherwise."""
-    M, N = a.shape[0], w.shape[0]
+    """Which kernel multiplies: the weight-streaming mma.sync one up to 16 rows (8 against big
+    weights, where the tcgen05 kernel that splits K over a cluster is faster from 9 rows on:
+    10.7 against 13.4 us for 4096 x 4096 at 16 rows) and for narrow outputs up to 64 rows; the
+    tcgen05 ones otherwise."""
+    M, N, K = a.shape[0], w.shape[0], a.shape[1]
     small, tc_ = _small_ok(a, w), _tc_ok(a, w)
-    if small and (M <= 16 or (N < 2048 and M <= SMALL_M) or not tc_):
+    big = N >= 2048 and K >= 2048
+    if small and (M <= 8 or (M <= 16 and not big) or (N < 2048 and M <= SMALL_M) or not tc_):
         return "small"
     if tc_:
         return "tc"
@@ -124,7 +126,7 @@ def _tc_shape(M: int, N: int, out: torch.Tensor = None, K: int = 0):
     take pairs of CTAs (persistent = 2; measured 4-9 % faster from 4,096 rows on, the same or
     slower at 2,048)."""
     if M <= 128:                       # one row of tiles: the weights stream, as in decode
-        if M > 16 and N >= 2048 and K >= 2048:
+        if M > 8 and N >= 2048 and K >= 2048:
             return (0, 0, 3)           # big weights: 128 rows of W per CTA, K split over a cluster
         return (128, 3, False) if N >= 32768 else (64, 8, False)
     if out is not None and out.data_ptr() % 16 == 0 and (out.stride(0) * out.element_size()) % 16 == 0:

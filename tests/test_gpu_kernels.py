@@ -294,8 +294,8 @@ def test_gemm_small(M, N, K):
     out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
     assert kernels_bf16.linear_bf16(a, w, out16, False)
     assert (out16.double() - ref).abs().max().item() <= ref.abs().max().item() * 2.0 ** -8 + tol
-    # a row changes nothing in the other rows: bit-equal when run alone
-    if M > 1:
+    # a row changes nothing in the other rows: bit-equal when run alone (by the same family of kernels)
+    if M > 1 and kernels_bf16._pick_product(a, w) == "small":
         alone = torch.empty(1, N, device=DEV)
         kernels_bf16.linear_bf16(a[M - 1:M], w, alone, False)
         assert torch.equal(alone[0], out[M - 1])
@@ -404,7 +404,7 @@ def test_gemm_tc_pairs(M, N, K, bn, stages):
     _check_gemm_tc(M, N, K, bn, stages, 2)
 
 
-@pytest.mark.parametrize("M,N,K", [(17, 4096, 4096), (32, 2048 + 8, 2048), (33, 6144, 4096), (64, 4096, 12288),
+@pytest.mark.parametrize("M,N,K", [(9, 4096, 2048), (17, 4096, 4096), (32, 2048 + 8, 2048), (33, 6144, 4096), (64, 4096, 12288),
                                    (100, 2304, 2056), (128, 4096 + 24, 4096 + 8), (20, 130 * 8, 72)])
 def test_gemm_tc_weight_streaming(M, N, K):
     """17 to 128 rows against big weights: 128 rows of W per CTA with 32, 64 or 128 rows of A,
