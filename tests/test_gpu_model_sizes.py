@@ -50,3 +50,28 @@ def test_layer_sizes(name, dtype):
     if dtype == "bfloat16":
         from gguf2bin_b200 import kernels_bf16
         kernels_bf16.check_status()
+
+
+@pytest.mark.parametrize("name,n_requests", [("8b", 12), ("14b", 40)])
+def test_layer_sizes_in_a_wider_batch(name, n_requests):
+    """The same at 12 and 40 sequences: from 9 rows on the products of these widths run on the
+    kernel that splits K over a cluster (32 and 64 rows of activations per CTA).  Short
+    prompts, so that the plain implementation stays quick."""
+    from gguf2bin_b200.engine import Engine, Model, StepEntry
+    from gguf2bin_b200.weights import write_random_model
+    from gguf2bin_b200 import kernels_bf16
+    cfg = dict(architectures=["Qwen3ForCausalLM"], rope_theta=1e6, rms_norm_eps=1e-6,
+               max_position_embeddings=40960, **SIZES[name])
+    folder = write_random_model(tmp_root() / f"sizes_wide_{name}", cfg, seed=12, dtype="bfloat16")
+    pcfg, W = P.read_model_folder(folder)
+    rng = np.random.default_rng(6)
+    reqs = [rng.integers(0, cfg["vocab_size"], 2 + i % 4).tolist() for i in range(n_requests)]
+    eng = Engine(Model.from_folder(folder, dtype="bfloat16"), max_tokens=64 * n_requests)
+    seqs = [eng.open_sequence() for _ in reqs]
+    heads = [len(t) - 1 for t in reqs]
+    out = eng.step([StepEntry(s, t[:h], [h - 1]) for s, t, h in zip(seqs, reqs, heads)]).cpu().numpy()
+    dec = eng.step([StepEntry(s, [t[h]], [0]) for s, t, h in zip(seqs, reqs, heads)]).cpu().numpy()
+    kernels_bf16.check_status()
+    for j, toks in enumerate(reqs):
+        ref = P.forward(pcfg, W, toks, np.float32)[heads[j] - 1:]
+        assert_close(np.stack([out[j], dec[j]]), ref, "bfloat16", f"{name} request {j} of {n_requests}")
