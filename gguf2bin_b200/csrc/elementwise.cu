@@ -262,33 +262,52 @@ extern "C" int g2b_rope_table(const int *tok_pos, const float *inv_freq, float *
   return g2b_check_launch("rope_table");
 }
 
-__device__ __forceinline__ void ld4(const bf16 *p, float (&v)[4]) {
-  const uint2 raw = *reinterpret_cast<const uint2 *>(p);
-  const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
-  const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
-  v[0] = lo.x; v[1] = lo.y; v[2] = hi.x; v[3] = hi.y;
-}
-__device__ __forceinline__ void ld4(const float *p, float (&v)[4]) {
-  const float4 raw = *reinterpret_cast<const float4 *>(p);
-  v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
-}
-__device__ __forceinline__ void st4(bf16 *p, const float (&v)[4]) {
-  uint2 raw;
-  *reinterpret_cast<__nv_bfloat162 *>(&raw.x) = __floats2bfloat162_rn(v[0], v[1]);
-  *reinterpret_cast<__nv_bfloat162 *>(&raw.y) = __floats2bfloat162_rn(v[2], v[3]);
-  *reinterpret_cast<uint2 *>(p) = raw;
-}
-__device__ __forceinline__ void st4(float *p, const float (&v)[4]) {
-  *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
-}
-
-// Head sizes 8 * LPH (LPH a power of two up to 32) with the rotation over the whole head:
-// LPH lanes share a head, so a warp works on 32 / LPH heads of one token at once.  A lane
-// holds four consecutive elements of the first half and their rotation partners in the
-// second half, loaded and stored as one vector each; everything stays in registers.
+// Head sizes 2 * E * LPH (LPH a power of two up to 32, E = 4 or 8) with the rotation over the
+// whole head: LPH lanes share a head, so a warp works on 32 / LPH heads of one token at once.
+// A lane holds E consecutive elements of the first half and their rotation partners in the
+// second half, loaded and stored as vectors; everything stays in registers.  E = 4 gives a
+// decode step more lanes per head (shorter chains); E = 8 moves 16 bytes per load for prompts.
 #define QKN_FAST_WARPS 8
 
-template <typename T, int LPH>
+template <int E> __device__ __forceinline__ void ldE(const bf16 *p, float (&v)[E]) {
+  if constexpr (E == 8) {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(p);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i]));
+      v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+  } else {
+    const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+    v[0] = lo.x; v[1] = lo.y; v[2] = hi.x; v[3] = hi.y;
+  }
+}
+template <int E> __device__ __forceinline__ void ldE(const float *p, float (&v)[E]) {
+#pragma unroll
+  for (int i = 0; i < E; i += 4) {
+    const float4 raw = *reinterpret_cast<const float4 *>(p + i);
+    v[i] = raw.x; v[i + 1] = raw.y; v[i + 2] = raw.z; v[i + 3] = raw.w;
+  }
+}
+template <int E> __device__ __forceinline__ void stE(bf16 *p, const float (&v)[E]) {
+  uint32_t w[E / 2];
+#pragma unroll
+  for (int i = 0; i < E / 2; ++i) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t *>(&h);
+  }
+  if constexpr (E == 8) *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  else *reinterpret_cast<uint2 *>(p) = make_uint2(w[0], w[1]);
+}
+template <int E> __device__ __forceinline__ void stE(float *p, const float (&v)[E]) {
+#pragma unroll
+  for (int i = 0; i < E; i += 4) *reinterpret_cast<float4 *>(p + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+}
+
+template <typename T, int LPH, int E>
 __global__ void __launch_bounds__(QKN_FAST_WARPS * 32)
 qknorm_rope_fast_kernel(
     const T *__restrict__ qkv, int T_tokens, int nh, int nkv,
@@ -299,7 +318,7 @@ qknorm_rope_fast_kernel(
     T *__restrict__ q_out, T *__restrict__ k_out, T *__restrict__ v_out) {
   pdl_launch();
   pdl_wait();
-  constexpr int HPW = 32 / LPH, HD = 8 * LPH, HH = 4 * LPH;
+  constexpr int HPW = 32 / LPH, HD = 2 * E * LPH, HH = E * LPH;
   const unsigned warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned heads = nh + 2 * nkv;
   const unsigned groups = (heads + HPW - 1) / HPW;
@@ -309,11 +328,11 @@ qknorm_rope_fast_kernel(
   const unsigned h = (item - t * groups) * HPW + lane / LPH;
   const bool valid = h < heads;
   const unsigned hc = valid ? h : heads - 1;
-  const int j = 4 * (lane % LPH);
+  const int j = E * (lane % LPH);
   const T *src = qkv + ((size_t)t * heads + hc) * HD;
-  float a[4], b[4];
-  ld4(src + j, a);
-  ld4(src + HH + j, b);
+  float a[E], b[E];
+  ldE<E>(src + j, a);
+  ldE<E>(src + HH + j, b);
   const int kind = hc < (unsigned)nh ? 0 : (hc < (unsigned)(nh + nkv) ? 1 : 2);     // q, k, v
   const float *w = kind == 0 ? q_w : (kind == 1 ? k_w : nullptr);
   T *dst;
@@ -332,7 +351,7 @@ qknorm_rope_fast_kernel(
   }
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < E; ++i) {
     ss = fmaf(a[i], a[i], ss);
     ss = fmaf(b[i], b[i], ss);
   }
@@ -340,30 +359,30 @@ qknorm_rope_fast_kernel(
   for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
   if (w) {
     const float inv = 1.f / sqrtf(ss / (float)HD + eps);
-    float wa[4], wb[4];
-    ld4(w + j, wa);
-    ld4(w + HH + j, wb);
+    float wa[E], wb[E];
+    ldE<E>(w + j, wa);
+    ldE<E>(w + HH + j, wb);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < E; ++i) {
       a[i] = (wa[i] * a[i]) * inv;
       b[i] = (wb[i] * b[i]) * inv;
     }
   }
   if (rope && kind != 2) {
     const float2 *cs = rope + (size_t)t * HH + j;
-    const float4 r01 = *reinterpret_cast<const float4 *>(cs);          // (cos, sin) of j, j+1
-    const float4 r23 = *reinterpret_cast<const float4 *>(cs + 2);      // and of j+2, j+3
-    const float c[4] = {r01.x, r01.z, r23.x, r23.z}, sn[4] = {r01.y, r01.w, r23.y, r23.w};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float av = a[i], bv = b[i];
-      a[i] = av * c[i] - bv * sn[i];
-      b[i] = av * sn[i] + bv * c[i];
+    for (int i = 0; i < E; i += 2) {
+      const float4 r = *reinterpret_cast<const float4 *>(cs + i);      // (cos, sin) of j+i, j+i+1
+      const float a0 = a[i], b0 = b[i], a1 = a[i + 1], b1 = b[i + 1];
+      a[i] = a0 * r.x - b0 * r.y;
+      b[i] = a0 * r.y + b0 * r.x;
+      a[i + 1] = a1 * r.z - b1 * r.w;
+      b[i + 1] = a1 * r.w + b1 * r.z;
     }
   }
   if (valid) {
-    st4(dst + j, a);
-    st4(dst + HH + j, b);
+    stE<E>(dst + j, a);
+    stE<E>(dst + HH + j, b);
   }
 }
 
@@ -431,14 +450,14 @@ qknorm_rope_cache_kernel(
   for (int j = lane; j < hd; j += 32) dst[j] = from_f32<T>(x[j]);
 }
 
-template <typename T, int LPH>
+template <typename T, int LPH, int E>
 static void launch_qkn_fast(const void *qkv, int T_tokens, int nh, int nkv, const float *q_w, const float *k_w,
                             float eps, const float *rope_table, const int *tok_pos, const int *tok_seq,
                             const int *page_table, int P, void *cache, int page_size, void *q_out, void *k_out,
                             void *v_out, cudaStream_t stream) {
   const long long items = (long long)T_tokens * ((nh + 2 * nkv + 32 / LPH - 1) / (32 / LPH));
   const unsigned blocks = (unsigned)((items + QKN_FAST_WARPS - 1) / QKN_FAST_WARPS);
-  g2b_launch(qknorm_rope_fast_kernel<T, LPH>, dim3(blocks), dim3(QKN_FAST_WARPS * 32), 0, stream,
+  g2b_launch(qknorm_rope_fast_kernel<T, LPH, E>, dim3(blocks), dim3(QKN_FAST_WARPS * 32), 0, stream,
              (const T *)qkv, T_tokens, nh, nkv, q_w, k_w, eps, (const float2 *)rope_table, tok_pos, tok_seq,
              page_table, P, (T *)cache, page_size, (T *)q_out, (T *)k_out, (T *)v_out);
 }
@@ -460,20 +479,29 @@ extern "C" int g2b_qknorm_rope_cache(const void *qkv, int dtype, int T_tokens, i
   if (nkv > 0 && !k_out && (!cache || !page_table || page_size <= 0))
     G2B_REFUSE("qknorm_rope_cache: no cache to write to");
   const int heads = nh + 2 * nkv;
-  const int lph = hd / 8;
+  // eight elements per lane and half for prompts (many rows), four for the few rows of a decode step
+  const bool wide = hd % 16 == 0 && hd >= 32 && (long long)T_tokens * heads >= 4096;
+  const int epl = wide ? 8 : 4;
+  const int lph = hd / (2 * epl);
   const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)k_out |
                          (uintptr_t)v_out | (uintptr_t)rope_table | (uintptr_t)q_w | (uintptr_t)k_w) & 15) == 0;
-  const bool fast = aligned && hd % 8 == 0 && lph >= 2 && lph <= 32 && (lph & (lph - 1)) == 0 &&
+  const bool fast = aligned && hd % (2 * epl) == 0 && lph >= 2 && lph <= 32 && (lph & (lph - 1)) == 0 &&
                     (!rope_table || rot_dim == hd) && (long long)T_tokens * heads < (1ll << 31);
   if (fast) {
 #define G2B_QKN_FAST(L)                                                                                     \
   case L:                                                                                                   \
-    if (dtype == G2B_F32)                                                                                   \
-      launch_qkn_fast<float, L>(qkv, T_tokens, nh, nkv, q_w, k_w, eps, rope_table, tok_pos, tok_seq,        \
-                                page_table, P, cache, page_size, q_out, k_out, v_out, stream);              \
+    if (dtype == G2B_F32 && wide)                                                                           \
+      launch_qkn_fast<float, L, 8>(qkv, T_tokens, nh, nkv, q_w, k_w, eps, rope_table, tok_pos, tok_seq,     \
+                                   page_table, P, cache, page_size, q_out, k_out, v_out, stream);           \
+    else if (dtype == G2B_F32)                                                                              \
+      launch_qkn_fast<float, L, 4>(qkv, T_tokens, nh, nkv, q_w, k_w, eps, rope_table, tok_pos, tok_seq,     \
+                                   page_table, P, cache, page_size, q_out, k_out, v_out, stream);           \
+    else if (wide)                                                                                          \
+      launch_qkn_fast<bf16, L, 8>(qkv, T_tokens, nh, nkv, q_w, k_w, eps, rope_table, tok_pos, tok_seq,      \
+                                  page_table, P, cache, page_size, q_out, k_out, v_out, stream);            \
     else                                                                                                    \
-      launch_qkn_fast<bf16, L>(qkv, T_tokens, nh, nkv, q_w, k_w, eps, rope_table, tok_pos, tok_seq,         \
-                               page_table, P, cache, page_size, q_out, k_out, v_out, stream);               \
+      launch_qkn_fast<bf16, L, 4>(qkv, T_tokens, nh, nkv, q_w, k_w, eps, rope_table, tok_pos, tok_seq,      \
+                                  page_table, P, cache, page_size, q_out, k_out, v_out, stream);            \
     break;
     switch (lph) {
       G2B_QKN_FAST(2) G2B_QKN_FAST(4) G2B_QKN_FAST(8) G2B_QKN_FAST(16) G2B_QKN_FAST(32)

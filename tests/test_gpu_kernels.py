@@ -119,9 +119,10 @@ def test_attn_generic(dtype, nh, nkv, hd, window):
 @pytest.mark.parametrize("nh,nkv,hd,rot,norm", [(4, 2, 16, 16, True), (3, 1, 48, 32, True), (2, 2, 128, 128, False),
                                                 (5, 1, 64, 64, True), (4, 2, 256, 256, True), (2, 1, 96, 96, True),
                                                 (3, 3, 32, 32, True), (7, 1, 128, 128, True)])
-def test_qknorm_rope_cache(dtype, nh, nkv, hd, rot, norm):
+@pytest.mark.parametrize("prompt", [70, 700])         # few rows: 4 elements per lane and half; many: 8
+def test_qknorm_rope_cache(dtype, nh, nkv, hd, rot, norm, prompt):
     from gguf2bin_b200 import kernels
-    ps, lens, q_lens = 64, [70, 130], [70, 2]
+    ps, lens, q_lens = 64, [prompt, 130], [prompt, 2]
     cache, table, _, _ = make_paged(2, lens, nkv, hd, ps, dtype, seed=11)
     tok_pos, tok_seq = [], []
     for b, (l, ql) in enumerate(zip(lens, q_lens)):
