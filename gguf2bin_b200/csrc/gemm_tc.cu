@@ -1013,9 +1013,9 @@ static int launch_wstream(const void *A, const void *W, void *C, int M, int N, i
   rc = make_map(&ma, A, M, K, lda, BNB);
   if (rc) return rc;
   const int tiles = (N + BM - 1) / BM, nkb = (K + BK - 1) / BK;
-  // parts of K: as many as keep every CTA on the GPU at once and give a part 16 blocks or more
+  // parts of K: as many as keep every CTA on the GPU at once and give a part 4 blocks or more
   int splits = 1;
-  while (splits < 4 && tiles * splits * 2 <= sm_count() && nkb / (splits * 2) >= 16) splits *= 2;
+  while (splits < 4 && tiles * splits * 2 <= sm_count() && nkb / (splits * 2) >= 4) splits *= 2;
   if (want_splits == 1 || want_splits == 2 || want_splits == 4) splits = want_splits;       // the caller's choice
   while (splits > 1 && (splits - 1) * ((nkb + splits - 1) / splits) >= nkb) splits /= 2;   // no empty part
   static_assert((2 * BNB + 8) * BM * 4 <= S::RING_BYTES, "the tile and the received ranges must fit the ring");

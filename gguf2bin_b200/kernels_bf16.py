@@ -112,11 +112,24 @@ def _pick_product(a: torch.Tensor, w: torch.Tensor):
     M, N, K = a.shape[0], w.shape[0], a.shape[1]
     small, tc_ = _small_ok(a, w), _tc_ok(a, w)
     big = N >= 2048 and K >= 2048
-    if small and (M <= 8 or (M <= 16 and not big) or (N < 2048 and M <= SMALL_M) or not tc_):
+    if small and (M <= 8 or (M <= 16 and not big) or (M <= SMALL_M and not _wstream_case(M, N, K) and N < 2048)
+                  or not tc_):
         return "small"
     if tc_:
         return "tc"
     return None
+
+
+def _wstream_case(M: int, N: int, K: int) -> bool:
+    """Few rows whose product goes to the kernel with 128 rows of W per CTA and K split over a
+    cluster: from 9 rows against big weights; from 17 rows against the weights of a small
+    model's layers too (at 64 rows, 1024 x 3072: 8.5 us against 17.8 by the mma.sync kernel and
+    18.4 by one 128 x 64 tile per CTA), but not against its vocabulary (many tiles with a short K)."""
+    if M > 128:
+        return False
+    if M > 8 and N >= 2048 and K >= 2048:
+        return True
+    return M > 16 and 1024 <= N <= 16384 and K >= 1024
 
 
 def _tc_shape(M: int, N: int, out: torch.Tensor = None, K: int = 0):
@@ -126,8 +139,8 @@ def _tc_shape(M: int, N: int, out: torch.Tensor = None, K: int = 0):
     take pairs of CTAs (persistent = 2; measured 4-9 % faster from 4,096 rows on, the same or
     slower at 2,048)."""
     if M <= 128:                       # one row of tiles: the weights stream, as in decode
-        if M > 8 and N >= 2048 and K >= 2048:
-            return (0, 0, 3)           # big weights: 128 rows of W per CTA, K split over a cluster
+        if _wstream_case(M, N, K):
+            return (0, 0, 3)           # 128 rows of W per CTA, K split over a cluster
         return (128, 3, False) if N >= 32768 else (64, 8, False)
     if out is not None and out.data_ptr() % 16 == 0 and (out.stride(0) * out.element_size()) % 16 == 0:
         tiles_m = -(-M // 128)
