@@ -80,8 +80,14 @@ _scratch: dict = {}       # small persistent device buffers of the bindings, by 
 
 
 def launch_count() -> int:
-    """How many kernel launchers were called so far in this process."""
+    """How many kernels the launchers called so far in this process have launched."""
     return _launches
+
+
+def count_launches(n: int) -> None:
+    """A launcher that starts more than one kernel per call adds the others here."""
+    global _launches
+    _launches += n
 
 
 def _call(f, *args) -> None:
@@ -281,6 +287,7 @@ def sample_rows(logits, temperature, seq_state, slots, out_ids) -> None:
                 [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
         _call(f, _ptr(logits), R, V, logits.stride(0), _ptr(scratch[0]), _ptr(scratch[1]),
               _ptr(out_ids), _stream())
+        count_launches(1)                          # the slices, then the winner among them
         return
     f = _fn("sampling.cu", "g2b_sample_rows",
             [c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p])

@@ -7,6 +7,7 @@ from ctypes import c_float, c_int, c_void_p
 import torch
 
 from .csrc import units
+from . import kernels
 from .kernels import KernelError, _call, _fn, _ptr, _stream
 
 FAST_HEAD_SIZES = (64, 128)          # head sizes the tensor-core attention kernels are written for
@@ -245,3 +246,4 @@ def attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_si
     _call(f, _ptr(q), _ptr(out), _ptr(cache_pages), _ptr(ctx.tok_pos), _ptr(ctx.tok_seq),
           _ptr(ctx.page_table), ctx.page_table.shape[1], T, n_heads, n_kv_heads, head_dim,
           page_size, window, scale, int(ctx.max_kv_len), _ptr(part_o), _ptr(part_ml), _stream())
+    kernels.count_launches(1)                      # the attention and the merge of its chunks
