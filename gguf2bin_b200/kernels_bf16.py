@@ -130,6 +130,8 @@ def _wstream_case(M: int, N: int, K: int) -> bool:
         return False
     if M > 8 and N >= 2048 and K >= 2048:
         return True
+    if N < 2048 and M <= 32 and K <= 2048:
+        return False                   # 1024 x 2048 at 32 rows: 4.9 us by the mma.sync kernel against 6.6
     return M > 16 and 1024 <= N <= 16384 and K >= 1024
 
 
