@@ -13,7 +13,8 @@
 // probabilities are rounded to bfloat16 for the P.V product.
 //
 // Each CTA writes an unnormalised partial output with its maximum and sum (log2 domain)
-// to scratch; `attn_combine_kernel` merges a token's chunks in increasing order.
+// to scratch; `attn_combine_kernel` merges a token's chunks in an order that depends on its
+// position only.
 //
 // Formula: src/l5_model.c:518, 559-577 of AnonymoDGH/gguf2bin.  Compiled per head size
 // (-DHD=64 or 128); the page size is 64 keys.
@@ -258,28 +259,56 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
   }
 }
 
-// out[t, h, :] = sum_i 2^(m_i - M) o_i / sum_i 2^(m_i - M) l_i over the token's chunks in order
-__global__ void __launch_bounds__(HD)
+// out[t, h, :] = sum_i 2^(m_i - M) o_i / sum_i 2^(m_i - M) l_i over the token's chunks.  One block of
+// four warps per (token, head): warp w adds the chunks c0 + w, c0 + w + 4, ... in that order, a lane
+// four neighbouring elements of the head; the four sums are then added in the order of the warps.
+// The order depends on the token's position only.
+constexpr int COMBINE_WARPS = 4;
+__global__ void __launch_bounds__(COMBINE_WARPS * 32)
 attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__ part_ml,
                     const int *__restrict__ tok_pos, int nh, int window, int n_chunks,
                     bf16 *__restrict__ out) {
   pdl_launch();
   pdl_wait();
+  __shared__ float s_max[COMBINE_WARPS];
+  __shared__ float s_acc[COMBINE_WARPS][HD + 1];
   const size_t th = blockIdx.x;                                // t * nh + h
-  const int t = (int)(th / nh), d = threadIdx.x;
+  const int t = (int)(th / nh);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = tok_pos[t];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   const int c0 = lo / CHUNK_KEYS, c1 = pos / CHUNK_KEYS;
   const float2 *ml = part_ml + th * n_chunks;
   float M = -INFINITY;
-  for (int i = c0; i <= c1; ++i) M = fmaxf(M, ml[i].x);
-  float num = 0.f, den = 0.f;
-  for (int i = c0; i <= c1; ++i) {
-    const float w = fast_exp2(ml[i].x - M);
-    num = fmaf(w, part_o[(th * n_chunks + i) * HD + d], num);
-    den = fmaf(w, ml[i].y, den);
+  for (int i = c0 + (int)threadIdx.x; i <= c1; i += COMBINE_WARPS * 32) M = fmaxf(M, ml[i].x);
+  M = warp_max(M);
+  if (lane == 0) s_max[warp] = M;
+  __syncthreads();
+  M = fmaxf(fmaxf(s_max[0], s_max[1]), fmaxf(s_max[2], s_max[3]));
+  const bool active = 4 * lane < HD;
+  float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+  float den = 0.f;
+  for (int i = c0 + warp; i <= c1; i += COMBINE_WARPS) {
+    const float2 mli = ml[i];
+    const float w = fast_exp2(mli.x - M);
+    if (active) {
+      const float4 o = *reinterpret_cast<const float4 *>(part_o + (th * n_chunks + i) * HD + 4 * lane);
+      num.x = fmaf(w, o.x, num.x); num.y = fmaf(w, o.y, num.y);
+      num.z = fmaf(w, o.z, num.z); num.w = fmaf(w, o.w, num.w);
+    }
+    den = fmaf(w, mli.y, den);
   }
-  out[th * HD + d] = __float2bfloat16_rn(num / den);
+  if (active) {
+    s_acc[warp][4 * lane] = num.x; s_acc[warp][4 * lane + 1] = num.y;
+    s_acc[warp][4 * lane + 2] = num.z; s_acc[warp][4 * lane + 3] = num.w;
+  }
+  if (lane == 0) s_acc[warp][HD] = den;
+  __syncthreads();
+  for (int d = threadIdx.x; d < HD; d += COMBINE_WARPS * 32) {
+    const float n = ((s_acc[0][d] + s_acc[1][d]) + s_acc[2][d]) + s_acc[3][d];
+    const float dn = ((s_acc[0][HD] + s_acc[1][HD]) + s_acc[2][HD]) + s_acc[3][HD];
+    out[th * HD + d] = __float2bfloat16_rn(n / dn);
+  }
 }
 
 // Scratch: part_o float [T*nh*n_chunks*HD], part_ml float2 [T*nh*n_chunks], with
@@ -312,7 +341,7 @@ extern "C" int g2b_attn_decode(const void *q, void *out, const void *cache, cons
       scale * LOG2E, part_o, (float2 *)part_ml, n_chunks);
   int rc = g2b_check_launch("attn_decode");
   if (rc) return rc;
-  g2b_launch(attn_combine_kernel, dim3((unsigned)((size_t)T * nh)), dim3(HD), 0, stream, 
+  g2b_launch(attn_combine_kernel, dim3((unsigned)((size_t)T * nh)), dim3(COMBINE_WARPS * 32), 0, stream, 
       part_o, (const float2 *)part_ml, tok_pos, nh, window, n_chunks, (bf16 *)out);
   return g2b_check_launch("attn_combine");
 }
