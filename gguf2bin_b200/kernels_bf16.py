@@ -124,15 +124,19 @@ def _pick_product(a: torch.Tensor, w: torch.Tensor):
 def _wstream_case(M: int, N: int, K: int) -> bool:
     """Few rows whose product goes to the kernel with 128 rows of W per CTA and K split over a
     cluster: from 9 rows against big weights; from 17 rows against the weights of a small
-    model's layers too (at 64 rows, 1024 x 3072: 8.5 us against 17.8 by the mma.sync kernel and
-    18.4 by one 128 x 64 tile per CTA), but not against its vocabulary (many tiles with a short K)."""
+    model's layers too where it was measured faster (at 64 rows, 1024 x 3072: 8.5 us against
+    17.8 by the mma.sync kernel and 18.4 by one 128 x 64 tile per CTA), but not against its
+    vocabulary (many tiles with a short K), and not wide outputs with K = 1024 beyond 64 rows
+    (6144 x 1024 at 128 rows: 11.7 us against 8.4 by one tile per CTA)."""
     if M > 128:
         return False
     if M > 8 and N >= 2048 and K >= 2048:
         return True
-    if N < 2048 and M <= 32 and K <= 2048:
-        return False                   # 1024 x 2048 at 32 rows: 4.9 us by the mma.sync kernel against 6.6
-    return M > 16 and 1024 <= N <= 16384 and K >= 1024
+    if M <= 16 or N < 1024 or K < 1024 or N > 16384:
+        return False
+    if N < 2048:                       # narrow outputs: 1024 x 2048 at 32 rows is 4.9 us by the mma.sync kernel, 6.6 here
+        return not (M <= 32 and K <= 2048)
+    return M <= 64 and N <= 4096       # wide outputs with a short K
 
 
 def _tc_shape(M: int, N: int, out: torch.Tensor = None, K: int = 0):
