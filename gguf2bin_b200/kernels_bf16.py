@@ -136,7 +136,7 @@ def _wstream_case(M: int, N: int, K: int) -> bool:
         return False
     if N < 2048:                       # narrow outputs: 1024 x 2048 at 32 rows is 4.9 us by the mma.sync kernel, 6.6 here
         return not (M <= 32 and K <= 2048)
-    return M <= 64 and N <= 4096       # wide outputs with a short K
+    return M <= 32 or (M <= 64 and N <= 4096)      # wide outputs with a short K
 
 
 def _tc_shape(M: int, N: int, out: torch.Tensor = None, K: int = 0):
