@@ -47,7 +47,7 @@ QWEN3_0P6B = dict(architectures=["Qwen3ForCausalLM"], hidden_size=1024, intermed
                   num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8,
                   head_dim=128, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
                   tie_word_embeddings=True, max_position_embeddings=40960)
-# the layer sizes of BASELINE.json's other configurations, for `--sizes` (not the default run)
+# the layer sizes of Qwen3-8B and Qwen3-14B, for `--sizes` (not the default run)
 OTHER_SIZES = {
     "8b": dict(hidden_size=4096, intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32,
                num_key_value_heads=8, head_dim=128, tie_word_embeddings=False),

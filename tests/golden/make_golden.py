@@ -11,7 +11,7 @@ What it does (CPU only, no network):
   4. feeds the token ids one by one through ``model_forward`` (src/l5_model.c:461)
      and stores the logits of every position as ``<case>_logits.npy``.
 
-Usage:  python tests/golden/make_golden.py [/path/to/reference]
+Usage:  python tests/golden/make_golden.py <checkout of AnonymoDGH/gguf2bin>
 The test ``tests/test_plain_vs_golden.py`` rebuilds the same weights with
 ``case_weights`` and compares the plain implementation with the stored logits.
 """
@@ -136,7 +136,10 @@ def write_g2bx_f32(path: Path, cfg: dict, W: dict) -> None:
 
 
 def main() -> int:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        print("usage: make_golden.py <checkout of AnonymoDGH/gguf2bin>", file=sys.stderr)
+        return 2
+    ref = Path(sys.argv[1])
     with tempfile.TemporaryDirectory() as tmp:
         tmp = Path(tmp)
         exe = tmp / "dump_logits"
