@@ -1,0 +1,27 @@
+"""Which product kernel a shape goes to (pure host-side decisions, no GPU): the table that the
+measurements in the kernels' doc strings led to."""
+import pytest
+
+from gguf2bin_b200.kernels_bf16 import _tc_shape, _wstream_case
+
+
+@pytest.mark.parametrize("M,N,K,want", [
+    # big weights (N and K of 2,048 and more): from 9 rows on, up to 128
+    (8, 4096, 4096, False), (9, 4096, 4096, True), (64, 6144, 4096, True), (128, 24576, 4096, True),
+    (129, 4096, 4096, False), (64, 151936, 4096, True),
+    # a small model's layers: from 17 rows; narrow outputs except the short one at up to 32 rows
+    (16, 1024, 3072, False), (32, 1024, 2048, False), (32, 1024, 3072, True), (64, 1024, 2048, True),
+    (128, 1024, 3072, True),
+    # wide outputs with a short K: up to 32 rows, or up to 64 rows and 4,096 outputs
+    (32, 6144, 1024, True), (64, 4096, 1024, True), (64, 6144, 1024, False), (96, 4096, 1024, False),
+    # a vocabulary with a short K, and shapes that are too small
+    (64, 151936, 1024, False), (64, 512, 4096, False), (64, 4096, 512, False),
+])
+def test_which_few_row_products_split_k_over_a_cluster(M, N, K, want):
+    assert _wstream_case(M, N, K) is want
+
+
+def test_tile_shape_of_a_few_row_product():
+    assert _tc_shape(64, 4096, None, 4096) == (0, 0, 3)             # the cluster kernel picks its own shape
+    assert _tc_shape(64, 151936, None, 1024) == (128, 3, False)     # a vocabulary: wide tiles, one per CTA
+    assert _tc_shape(100, 4096, None, 1024) == (64, 8, False)
