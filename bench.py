@@ -158,7 +158,8 @@ def decode_device_timed(llm, batch: int, start_ctx: int, steps: int, warmup: int
             eng.cache.reserve(s, start_ctx + steps + 1)
             eng.step([StepEntry(s, random_prompts(1, plen, vocab, 100 + i)[0], ())])
         sampler = Sampler(eng.cache.seq_state, eng.device)
-        session = DecodeSession(eng, seqs, sampler, SamplingParams.plain(0.0), use_graph=True)
+        session = DecodeSession(eng, seqs, sampler, SamplingParams.plain(0.0), use_graph=True,
+                                eager_steps=1)
         session.set_tokens(random_prompts(1, batch, vocab, 7)[0])
         for _ in range(warmup):
             session.run()

@@ -50,6 +50,7 @@ class LLM:
         backend = EngineBackend(self.engine, params, seed, max_context=ctx,
                                 use_graph=self.use_graph)
         out = generate(backend, prompts, n, stop_ids, max_batch)
+        backend.finish()
         self.last_decode = dict(seconds=backend.decode_seconds, steps=backend.decode_steps,
                                 tokens=backend.decode_tokens)
         return out

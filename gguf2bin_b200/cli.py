@@ -2,16 +2,18 @@
 AnonymoDGH/gguf2bin): sub-commands ``run``, ``bench``, ``info`` and ``synth`` with the
 same option names and meanings where it has them.
 
-    run   <model_dir> --tokens a,b,c [--tokens d,e ...] [-n N] [-t TEMP] [--top-k K]
-          [--top-p P] [--repeat-penalty R] [-c N | --ctx N] [--seed S] [--dtype D]
-          [--stop id,id] [--ignore-eos]
+    run   <model_dir> --tokens a,b,c [--tokens d,e ...] [--tokens-file FILE] [-n N] [-t TEMP]
+          [--top-k K] [--top-p P] [--repeat-penalty R] [-c N | --ctx N] [--seed S]
+          [--dtype D] [--stop id,id] [--ignore-eos]
     bench <model_dir> [-n N] [-c N] [--dtype D]
     info  <model_dir>
     synth <out_dir> --config config.json [--seed S] [--dtype D]
 
 What differs, and why: a model is a folder (config.json + safetensors), not a G2BX or
 GGUF file; there is no tokenizer, so prompts are token ids (``--tokens``, which may be
-given several times for a batch) and text prompts are refused; sampling is seeded
+given several times for a batch, and ``--tokens-file``, one request per line, for prompts
+too long to type: the reference caps a command-line prompt at 1,024 ids, src/main.c:291-294)
+and text prompts are refused; sampling is seeded
 (``--seed``) instead of taking the clock; ``synth`` writes random weights, not zeros.
 The reference's CPU memory options (--q8-kv, --f32-kv, --max-ram, --swap, --fast,
 --threads) and --bos have no meaning here and are refused with that explanation.
@@ -29,9 +31,34 @@ _CPU_ONLY = {"--q8-kv", "--f32-kv", "--max-ram", "--swap", "--fast", "--threads"
 
 def _ids(text: str) -> list:
     try:
-        return [int(t) for t in text.split(",") if t.strip() != ""]
+        return [int(t) for t in text.replace(",", " ").split()]
     except ValueError:
         raise argparse.ArgumentTypeError(f"token ids must be integers separated by commas: {text!r}")
+
+
+class CommandLineError(ValueError):
+    """An argument that cannot be used; the message is printed as one line."""
+
+
+def read_tokens_file(path) -> list:
+    """One request per line: ids separated by commas or blanks; empty lines and lines that
+    start with ``#`` are skipped."""
+    try:
+        lines = Path(path).read_text().splitlines()
+    except OSError as e:
+        raise CommandLineError(f"--tokens-file {path}: {e.strerror or e}") from None
+    prompts = []
+    for no, line in enumerate(lines, 1):
+        line = line.strip()
+        if not line or line.startswith("#"):
+            continue
+        try:
+            prompts.append([int(t) for t in line.replace(",", " ").split()])
+        except ValueError:
+            raise CommandLineError(f"--tokens-file {path}, line {no}: token ids must be integers") from None
+    if not prompts:
+        raise CommandLineError(f"--tokens-file {path}: no request in the file")
+    return prompts
 
 
 def _parser() -> argparse.ArgumentParser:
@@ -49,6 +76,8 @@ def _parser() -> argparse.ArgumentParser:
     run.add_argument("--repeat-penalty", type=float, default=1.1, help="(default 1.1)")
     run.add_argument("--tokens", type=_ids, action="append", default=[],
                      help="prompt ids a,b,c; repeat the option for a batch")
+    run.add_argument("--tokens-file", action="append", default=[], metavar="FILE",
+                     help="a file with one request per line (ids separated by commas or blanks)")
     run.add_argument("-c", "--ctx", type=int, default=0, help="context limit (default: the model's)")
     run.add_argument("--seed", type=int, default=0)
     run.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
@@ -78,7 +107,10 @@ def cmd_run(a) -> int:
               "pass token ids with --tokens a,b,c", file=sys.stderr)
         return 1
     from .api import LLM
-    prompts = a.tokens or [[1]]                      # src/main.c:312: default prompt [1]
+    prompts = list(a.tokens)
+    for path in a.tokens_file:
+        prompts += read_tokens_file(path)
+    prompts = prompts or [[1]]                       # src/main.c:312: default prompt [1]
     llm = LLM(a.model, dtype=a.dtype,
               max_tokens=sum(-(-(len(p) + a.n) // 64) * 64 for p in prompts))
     print(llm.model.describe(), file=sys.stderr)
@@ -152,7 +184,27 @@ def main(argv=None) -> int:
                   "and -c for the context", file=sys.stderr)
             return 1
     a = _parser().parse_args(argv)
-    return {"run": cmd_run, "bench": cmd_bench, "info": cmd_info, "synth": cmd_synth}[a.command](a)
+    command = {"run": cmd_run, "bench": cmd_bench, "info": cmd_info, "synth": cmd_synth}[a.command]
+    try:
+        return command(a)
+    except _expected_errors() as e:
+        # what a user can cause (a bad folder, a prompt that does not fit, no GPU): one line, no traceback
+        first, *rest = str(e).splitlines() or [type(e).__name__]
+        print(f"{a.command}: {first}", file=sys.stderr)
+        for line in rest:
+            print(line, file=sys.stderr)
+        return 1
+
+
+def _expected_errors() -> tuple:
+    from .cache.pool import CacheError
+    from .config import ConfigError
+    from .csrc.build import KernelBuildError, KernelError
+    from .engine.generate import GenerationError
+    from .engine.step import StepError
+    from .weights import WeightsError
+    return (CommandLineError, CacheError, ConfigError, KernelBuildError, KernelError, GenerationError,
+            StepError, WeightsError, FileNotFoundError)
 
 
 if __name__ == "__main__":

@@ -2,6 +2,7 @@
 to the reader that turns config.json into a ``ModelSpec``."""
 from __future__ import annotations
 
+import dataclasses
 import json
 from pathlib import Path
 from typing import Any, Callable, Mapping
@@ -45,5 +46,38 @@ def read_config_json(folder) -> dict:
     return d
 
 
+def _id_list(v, where: str) -> tuple:
+    if v is None:
+        return ()
+    items = v if isinstance(v, (list, tuple)) else [v]
+    for e in items:
+        if isinstance(e, bool) or not isinstance(e, int):
+            raise ConfigError(f"{where}: eos_token_id must be an integer or a list of integers, got {v!r}")
+    return tuple(int(e) for e in items)
+
+
+def read_generation_stop_ids(folder) -> tuple:
+    """``eos_token_id`` of the folder's generation_config.json (one id or a list); () when
+    the file is absent.  The reference ends a reply at the tokenizer's eos or at
+    ``<|im_end|>`` (src/main.c:387-389 of AnonymoDGH/gguf2bin); without a tokenizer the ids
+    come from the two configuration files that carry them."""
+    path = Path(folder) / "generation_config.json"
+    if not path.is_file():
+        return ()
+    try:
+        d = json.loads(path.read_text())
+    except json.JSONDecodeError as e:
+        raise ConfigError(f"{path}: not valid JSON ({e})") from None
+    if not isinstance(d, dict):
+        raise ConfigError(f"{path}: top level must be an object")
+    return _id_list(d.get("eos_token_id"), str(path))
+
+
 def model_spec_from_folder(folder) -> ModelSpec:
-    return model_spec_from_dict(read_config_json(folder))
+    """The folder's config.json through the registry; stop ids are those of config.json
+    and of generation_config.json together, in that order."""
+    spec = model_spec_from_dict(read_config_json(folder))
+    extra = [t for t in read_generation_stop_ids(folder) if t not in spec.stop_token_ids]
+    if extra:
+        spec = dataclasses.replace(spec, stop_token_ids=tuple(spec.stop_token_ids) + tuple(extra))
+    return spec

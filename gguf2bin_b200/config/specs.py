@@ -46,12 +46,14 @@ class PartSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """One layer: a block arrangement around a mixer and a feed-forward, the norm
-    used in the block, and the tensor-name prefix of the layer in the checkpoint."""
+    used in the block (``ffn_norm``: another one before the feed-forward, when the two
+    places differ), and the tensor-name prefix of the layer in the checkpoint."""
     block: PartSpec
     mixer: PartSpec
     feed_forward: PartSpec
     norm: PartSpec
     prefix: str
+    ffn_norm: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

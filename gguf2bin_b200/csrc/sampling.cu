@@ -334,7 +334,7 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
   // repeat penalty, each distinct id once (src/main.c:204-223)
   if (penalty != 1.f && recent) {
     const int *rc = recent + (size_t)blockIdx.x * recent_ld;
-    const int n = recent_n[blockIdx.x];
+    const int n = min(max(recent_n[blockIdx.x], 0), recent_ld);   // never past the row
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
       const int id = rc[i];
       if (id < 0 || id >= V) continue;

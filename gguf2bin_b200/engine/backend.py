@@ -61,6 +61,12 @@ class EngineBackend:
             self._session.take_back()
             self._session = None
 
+    def finish(self) -> None:
+        """Called once the caller is about to hand the generated tokens on: ends the decode
+        session and reports a kernel that gave up a wait in any step since the last check."""
+        self._drop_session()
+        self.engine.check()
+
     def close(self, handle: _Handle) -> None:
         if handle.seq.slot >= 0:
             if self._session is not None and any(s is handle.seq for s in self._session.seqs):
@@ -76,6 +82,7 @@ class EngineBackend:
         recent = [h.recent for h in handles] if self.params.repeat_penalty != 1.0 else None
         self.sampler.sample(logits, self.params, self._slots[:R], self._ids[:R], recent)
         out = self._ids[:R].tolist()
+        self.engine.check()                    # never hand on tokens of a launch that gave up a wait
         for h, t in zip(handles, out):
             h.recent.append(t)
             del h.recent[:-RECENT_USE]

@@ -3,10 +3,18 @@
 A ``DecodeSession`` is the step function specialised to "every sequence of this batch
 goes on by one token, and the token is the one just sampled": the batch's index tensors
 stay on the device, the sampler writes each new token where the next step reads it, and
-positions advance on the device.  The launches of one step (the model's forward pass,
-sampling, the advance) are the same every time, so after two plain steps they are
-captured once in a CUDA graph and replayed.  It runs the same model, cache, kernels and
-sampler as ``Engine.step``; only the bookkeeping differs.
+positions advance on the device.  It runs the same model, cache, kernels and sampler as
+``Engine.step``; only the bookkeeping differs.
+
+The launches of one such step (the model's forward pass, sampling, the advance) depend on
+the step's shape only: how many sequences, how wide their page table, how it samples.
+Which sequences, pages, positions and tokens is data on the device.  So the device buffers
+of a shape and the CUDA graph captured over them belong to the engine, as a
+``DecodeRunner`` kept by shape: a new session of a shape that was seen before (another
+call, or the batch that is left when a sequence ends and an earlier batch had that size)
+writes its sequences' data into the runner's buffers and replays the graph that is there.
+A graph is captured only once a shape has run plainly a few times, so a batch whose
+sequences end one after another does not pay a capture for every size it passes through.
 
 The pages of every sequence must be reserved up to the length it can reach before the
 session starts (the page table is uploaded once).
@@ -17,7 +25,9 @@ next step ahead, fed by the tokens just sampled, which is what the caller hands 
 all but the last step of a sequence.  If the caller then wants something else (other tokens,
 other sequences, or nothing more) the step launched ahead is taken back: it wrote the key
 and value of a token at a position that is written again or never read, and its bookkeeping
-(lengths, positions, draw counters) is rewound.
+(lengths, positions, draw counters) is rewound.  That only holds for what is stored by
+position: a layer that keeps a state of fixed size has folded the token into it for good,
+so a model with such a layer never runs ahead.
 """
 from __future__ import annotations
 
@@ -28,71 +38,171 @@ import torch
 
 from .. import kernels
 from ..cache.pool import Sequence as CacheSequence
+from ..cache.storage import KVNeed
 from ..parts.base import StepContext
 from ..sampling import Sampler, SamplingParams
 from .step import Engine, StepError
 
+PAGE_TABLE_STEP = 4          # page-table widths are rounded up to this many pages (one 256-key chunk)
+
+
+class DecodeRunner:
+    """Device buffers and, in time, the captured graph of decode steps of one shape."""
+
+    EAGER_STEPS = 4          # plain steps of a shape before its graph is captured
+
+    def __init__(self, engine: Engine, batch: int, table_width: int, temperature: Optional[float]):
+        self.engine, self.batch, self.table_width = engine, batch, table_width
+        self.temperature = temperature          # None: the sampler runs after the step, outside a graph
+        B, P, dev = batch, table_width, engine.device
+        self.n_meta = 4 * B + B * P
+        self._meta = torch.zeros(self.n_meta, dtype=torch.int32, device=dev)
+        self._meta_host = torch.zeros(self.n_meta, dtype=torch.int32, pin_memory=True)
+        self._uploaded = torch.cuda.Event()
+        self.tok_ids = self._meta[0:B]
+        self.tok_pos = self._meta[B:2 * B]
+        self.tok_seq = self._meta[2 * B:3 * B]
+        self.slots = self._meta[3 * B:4 * B]
+        self.page_table = self._meta[4 * B:].view(B, P)
+        self.want_rows = torch.arange(B, dtype=torch.int32, device=dev)
+        self.ctx = StepContext(
+            n_tokens=B, n_seqs=B, tok_ids=self.tok_ids, tok_pos=self.tok_pos, tok_seq=self.tok_seq,
+            page_table=self.page_table, page_size=engine.cache.page_size,
+            workspace=engine.workspace, dtype=engine.model.dtype, q_lens=[1] * B,
+            past_lens=[0] * B, slots=[0] * B, max_kv_len=P * engine.cache.page_size)
+        self.owner: Optional["DecodeSession"] = None
+        self.logits: Optional[torch.Tensor] = None
+        self._graph: Optional[torch.cuda.CUDAGraph] = None
+        self._graph_generation = -1
+        self.plain_steps = 0
+        self.launches_per_step = 0
+
+    def bind(self, session: "DecodeSession") -> None:
+        """Writes the session's sequences into the buffers: positions, slots, pages."""
+        B, P = self.batch, self.table_width
+        self._uploaded.synchronize()               # the staging buffer's last copy is over
+        host = self._meta_host.numpy()
+        host[:] = 0
+        host[B:2 * B] = [s.length for s in session.seqs]         # positions of the next tokens
+        host[2 * B:3 * B] = np.arange(B)
+        host[3 * B:4 * B] = [s.slot for s in session.seqs]
+        for b, s in enumerate(session.seqs):
+            host[4 * B + b * P:4 * B + b * P + len(s.pages)] = s.pages
+        self._meta.copy_(self._meta_host, non_blocking=True)
+        self._uploaded.record()
+        self.ctx.slots = [s.slot for s in session.seqs]
+        self.owner = session
+
+    def _launch(self) -> None:
+        eng = self.engine
+        self.logits = eng.workspace.buffer("decode.logits", (self.batch, eng.model.vocab), torch.float32)
+        eng.model.forward(self.ctx, eng.cache, self.want_rows, self.batch, logits_out=self.logits)
+        if self.temperature is not None:
+            kernels.sample_rows(self.logits, self.temperature, eng.cache.seq_state, self.slots,
+                                self.tok_ids)
+            kernels.advance_positions(self.tok_pos, self.batch)
+
+    def run(self, use_graph: bool, eager_steps: int) -> None:
+        ws = self.engine.workspace
+        if self._graph is not None and ws.generation != self._graph_generation:
+            self._graph, self.plain_steps = None, 0           # scratch buffers moved: capture again
+        if self._graph is not None and use_graph:
+            self._graph.replay()
+            return
+        before = kernels.launch_count()
+        if use_graph and self.plain_steps >= eager_steps:
+            torch.cuda.current_stream().synchronize()
+            generation = ws.generation
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._launch()
+            self.launches_per_step = kernels.launch_count() - before
+            self.engine.graph_captures += 1
+            if ws.generation == generation:
+                self._graph, self._graph_generation = g, generation
+                g.replay()
+                return
+            before = kernels.launch_count()        # a buffer appeared during the capture: run plainly
+        self._launch()
+        self.launches_per_step = kernels.launch_count() - before
+        self.plain_steps += 1
+
+
+def decode_runner(engine: Engine, batch: int, pages: int, temperature: Optional[float]) -> DecodeRunner:
+    """The engine's runner for this shape, made at its first use; the least recently used
+    ones go when there are more than ``Engine.DECODE_RUNNERS_KEPT``."""
+    width = -(-max(int(pages), 1) // PAGE_TABLE_STEP) * PAGE_TABLE_STEP
+    key = (batch, width, temperature)
+    runners = engine.decode_runners
+    runner = runners.get(key)
+    if runner is None:
+        runner = runners[key] = DecodeRunner(engine, batch, width, temperature)
+        while len(runners) > engine.DECODE_RUNNERS_KEPT:
+            runners.popitem(last=False)
+    else:
+        runners.move_to_end(key)
+    return runner
+
 
 class DecodeSession:
-    EAGER_STEPS = 1          # plain steps before the graph is captured (the first sizes every buffer)
+    CHECK_EVERY = 64         # collections between two reads of the kernels' status word
 
     def __init__(self, engine: Engine, seqs: Sequence[CacheSequence], sampler: Sampler,
-                 params: SamplingParams, use_graph: bool = True):
+                 params: SamplingParams, use_graph: bool = True, eager_steps: Optional[int] = None):
+        """``eager_steps``: plain steps of this shape before its graph is captured (default:
+        ``DecodeRunner.EAGER_STEPS``; at least one, which sizes every scratch buffer)."""
         self.engine, self.seqs, self.sampler, self.params = engine, list(seqs), sampler, params
         B = len(self.seqs)
         if B == 0:
             raise StepError("a decode session needs at least one sequence")
-        dev = engine.device
-        P = max(len(s.pages) for s in self.seqs)
-        host = np.zeros(3 * B + B * P, dtype=np.int32)
-        host[B:2 * B] = [s.length for s in self.seqs]            # positions of the next tokens
-        host[2 * B:3 * B] = np.arange(B)
-        for b, s in enumerate(self.seqs):
-            host[3 * B + b * P:3 * B + b * P + len(s.pages)] = s.pages
-        self._meta = torch.from_numpy(host).to(dev)
-        self.tok_ids = self._meta[0:B]
-        self.tok_pos = self._meta[B:2 * B]
-        self.tok_seq = self._meta[2 * B:3 * B]
-        self.page_table = self._meta[3 * B:].view(B, P)
-        self.slots = torch.tensor([s.slot for s in self.seqs], dtype=torch.int32, device=dev)
-        self.want_rows = torch.arange(B, dtype=torch.int32, device=dev)
-        self.logits = torch.empty(B, engine.model.vocab, dtype=torch.float32, device=dev)
+        if sampler.seq_state is not engine.cache.seq_state:
+            raise StepError("the sampler of a decode session must use the engine's per-slot records")
+        # sampling inside the graph needs no host data; filtered sampling uploads the
+        # recent tokens every step and therefore runs after the graph
+        self._sample_in_graph = not params.filtered
+        self.runner = decode_runner(engine, B, max(len(s.pages) for s in self.seqs),
+                                    params.temperature if self._sample_in_graph else None)
+        self.runner.bind(self)
+        self.use_graph = use_graph and engine.model.graph_safe
+        self.eager_steps = max(1, DecodeRunner.EAGER_STEPS if eager_steps is None else int(eager_steps))
+        # a step launched ahead can be taken back only if all it stored is stored by position
+        self._may_run_ahead = self._sample_in_graph and all(
+            isinstance(g["need"], KVNeed) for g in engine.cache.groups.values())
         self._pinned_in = torch.empty(B, dtype=torch.int32, pin_memory=True)
         self._pinned_out = [torch.empty(B, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._out_ready = [torch.cuda.Event(), torch.cuda.Event()]
         self._out_turn = 0
         self._ahead: Optional[list] = None      # tokens fed to the step launched ahead, if any
-        self.ctx = StepContext(
-            n_tokens=B, n_seqs=B, tok_ids=self.tok_ids, tok_pos=self.tok_pos, tok_seq=self.tok_seq,
-            page_table=self.page_table, page_size=engine.cache.page_size,
-            workspace=engine.workspace, dtype=engine.model.dtype, q_lens=[1] * B,
-            past_lens=[s.length for s in self.seqs], slots=[s.slot for s in self.seqs],
-            max_kv_len=max(len(s.pages) for s in self.seqs) * engine.cache.page_size)
-        self.use_graph = use_graph and engine.model.graph_safe
-        self._graph: Optional[torch.cuda.CUDAGraph] = None
-        self._graph_generation = -1
-        self._steps = 0
-        self.launches_per_step = 0
-        # sampling inside the graph needs no host data; filtered sampling uploads the
-        # recent tokens every step and therefore runs after the graph
-        self._sample_in_graph = not params.filtered
+        self._since_check = 0
 
     @property
     def batch(self) -> int:
         return len(self.seqs)
 
+    @property
+    def tok_ids(self) -> torch.Tensor:
+        return self.runner.tok_ids
+
+    @property
+    def logits(self) -> torch.Tensor:
+        """The last step's logits, float32 [batch, vocab] (scratch: valid until the next step)."""
+        return self.runner.logits
+
+    @property
+    def launches_per_step(self) -> int:
+        return self.runner.launches_per_step
+
+    def _own_runner(self) -> None:
+        """Another session of the same shape may have used the runner since: write this
+        session's data back (positions follow from the sequences' lengths)."""
+        if self.runner.owner is not self:
+            self.runner.bind(self)
+
     def set_tokens(self, tokens: Sequence[int]) -> None:
         """The tokens the next step feeds (host to device, from pinned memory)."""
+        self._own_runner()
         self._pinned_in.copy_(torch.tensor(list(tokens), dtype=torch.int32))
-        self.tok_ids.copy_(self._pinned_in, non_blocking=True)
-
-    def _launch(self) -> None:
-        self.engine.model.forward(self.ctx, self.engine.cache, self.want_rows, self.batch,
-                                  logits_out=self.logits)
-        if self._sample_in_graph:
-            kernels.sample_rows(self.logits, self.params.temperature, self.sampler.seq_state,
-                                self.slots, self.tok_ids)
-            kernels.advance_positions(self.tok_pos, self.batch)
+        self.runner.tok_ids.copy_(self._pinned_in, non_blocking=True)
 
     def run(self, recent=None) -> None:
         """One step: feeds ``tok_ids``, leaves the sampled tokens in ``tok_ids`` and the
@@ -100,30 +210,15 @@ class DecodeSession:
         page = self.engine.cache.page_size
         if any(s.length + 1 > len(s.pages) * page for s in self.seqs):
             raise StepError("a sequence of the decode session has no reserved page left")
-        ws = self.engine.workspace
-        if self._graph is not None and ws.generation != self._graph_generation:
-            self._graph, self._steps = None, 0        # scratch buffers moved: capture again
-        if self._graph is not None:
-            self._graph.replay()
-        elif self.use_graph and self._steps >= self.EAGER_STEPS:
-            torch.cuda.current_stream().synchronize()
-            before = kernels.launch_count()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                self._launch()
-            self.launches_per_step = kernels.launch_count() - before
-            self._graph, self._graph_generation = g, ws.generation
-            g.replay()
-        else:
-            before = kernels.launch_count()
-            self._launch()
-            self.launches_per_step = kernels.launch_count() - before
+        self._own_runner()
+        runner = self.runner
+        runner.ctx.past_lens = [s.length for s in self.seqs]
+        runner.run(self.use_graph, self.eager_steps)
         if not self._sample_in_graph:
-            self.sampler.sample(self.logits, self.params, self.slots, self.tok_ids, recent)
-            kernels.advance_positions(self.tok_pos, self.batch)
+            self.sampler.sample(runner.logits, self.params, runner.slots, runner.tok_ids, recent)
+            kernels.advance_positions(runner.tok_pos, self.batch)
         for s in self.seqs:
             s.length += 1
-        self._steps += 1
 
     def read_tokens(self) -> list:
         """The tokens sampled by the last step (device to host)."""
@@ -133,13 +228,23 @@ class DecodeSession:
         """Starts the copy of the last step's tokens to the host; returns its turn."""
         turn = self._out_turn
         self._out_turn ^= 1
-        self._pinned_out[turn].copy_(self.tok_ids, non_blocking=True)
+        self._pinned_out[turn].copy_(self.runner.tok_ids, non_blocking=True)
         self._out_ready[turn].record()
         return turn
 
     def _collect(self, turn: int) -> list:
         self._out_ready[turn].synchronize()
+        self._since_check += 1
+        if self._since_check >= self.CHECK_EVERY:
+            self.check()
         return self._pinned_out[turn].tolist()
+
+    def check(self) -> None:
+        """Reports a kernel that gave up a bounded wait (see ``Engine.check``).  Reading the
+        word costs a small copy, so steps do it every ``CHECK_EVERY`` collections; the session's
+        owner calls it once more before it hands tokens on for good."""
+        self._since_check = 0
+        self.engine.check()
 
     def _room_for_one_more(self) -> bool:
         page = self.engine.cache.page_size
@@ -159,7 +264,7 @@ class DecodeSession:
             turn = self._send_back()
         self._ahead = None
         ahead_turn = None
-        if self._sample_in_graph and self._room_for_one_more():
+        if self._may_run_ahead and self._room_for_one_more():
             self.run(None)                           # the next step, fed by the tokens being sampled now;
             ahead_turn = self._send_back()           # queued before this step's tokens are waited for
         out = self._collect(turn)
@@ -172,7 +277,8 @@ class DecodeSession:
         if self._ahead is None:
             return
         self._ahead = None
-        kernels.rewind_step(self.tok_pos, self.batch, self.sampler.seq_state, self.slots,
+        self._own_runner()
+        kernels.rewind_step(self.runner.tok_pos, self.batch, self.sampler.seq_state, self.runner.slots,
                             self.params.temperature > 0.0)
         for s in self.seqs:
             s.length -= 1

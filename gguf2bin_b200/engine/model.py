@@ -16,10 +16,10 @@ from .. import kernels
 from ..cache.storage import Cache
 from ..config import ModelSpec, model_spec_from_folder
 from ..config.specs import ConfigError
-from ..parts import block_class, norm_class
+from ..csrc.build import _log
+from ..parts import block_class, embedding_class, head_class, norm_class
 from ..parts.base import StepContext
-from ..parts.fused import normed_linear
-from ..weights.loader import Expected, load_weights
+from ..weights.loader import load_weights
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -34,11 +34,11 @@ def parse_dtype(dtype) -> torch.dtype:
 
 def expected_tensors(spec: ModelSpec) -> dict:
     """Every tensor the model needs, by checkpoint name."""
-    out = {spec.embedding["name"]: Expected((spec.vocab_size, spec.hidden_size))}
+    out = dict(embedding_class(spec.embedding).expected(spec.embedding, spec.vocab_size,
+                                                        spec.hidden_size))
     out.update(norm_class(spec.final_norm).expected(spec.final_norm, spec.hidden_size,
                                                     spec.final_norm["name"]))
-    out[spec.head["name"]] = Expected((spec.vocab_size, spec.hidden_size),
-                                      optional=bool(spec.head["tied"]))
+    out.update(head_class(spec.head).expected(spec.head, spec.vocab_size, spec.hidden_size))
     for layer in spec.layers:
         for name, e in block_class(layer.block).expected(layer, spec.hidden_size).items():
             out[layer.prefix + name] = e
@@ -53,13 +53,18 @@ class Model:
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise kernels.KernelError("the engine runs on a CUDA device only (no CPU path)")
+        if not torch.cuda.is_available():
+            raise kernels.KernelError("no CUDA device is available (no NVIDIA driver or no GPU); "
+                                      "the engine has no CPU path")
         self.hidden, self.vocab = spec.hidden_size, spec.vocab_size
         self.blocks = [block_class(l.block)(l, spec.hidden_size, self.dtype, self.device)
                        for l in spec.layers]
         self.final_norm = norm_class(spec.final_norm)(spec.final_norm, spec.hidden_size,
                                                       self.dtype, self.device)
-        self.embedding = None
-        self.head = None
+        self.embedding = embedding_class(spec.embedding)(spec.embedding, spec.vocab_size,
+                                                         spec.hidden_size, self.dtype, self.device)
+        self.head = head_class(spec.head)(spec.head, spec.vocab_size, spec.hidden_size, self.dtype,
+                                          self.device)
         self.n_params = 0
 
     # ---- construction ---------------------------------------------------------
@@ -75,15 +80,28 @@ class Model:
     def bind(self, tensors: dict) -> None:
         spec = self.spec
         self.n_params = sum(t.numel() for t in tensors.values())
-        self.embedding = tensors[spec.embedding["name"]].contiguous()
-        if spec.head["tied"]:
-            self.head = self.embedding           # src/l5_model.c:602-603: no output matrix
-        else:
-            self.head = tensors[spec.head["name"]].contiguous()
+        self.embedding.bind(tensors)
+        self.head.bind(tensors, self.embedding)      # a tied head takes the embedding's table
         self.final_norm.bind(tensors[spec.final_norm["name"]])
         for layer, block in zip(spec.layers, self.blocks):
             n = len(layer.prefix)
             block.bind({k[n:]: v for k, v in tensors.items() if k.startswith(layer.prefix)})
+        for line in self.notices():
+            _log("note: " + line)
+
+    def notices(self) -> list:
+        """What the parts say about kernels they will not get (a head size without a tensor-core
+        attention kernel, a matrix kept in 32-bit under bfloat16 compute): each distinct line
+        once, with the layers it holds for."""
+        where: dict = {}
+        for i, b in enumerate(self.blocks):
+            for line in getattr(b, "notices", list)():
+                where.setdefault(line, []).append(str(i))
+        out = [f"layers {','.join(ls) if len(ls) <= 4 else ls[0] + '..' + ls[-1]}: {line}"
+               for line, ls in where.items()]
+        for part in (self.embedding, self.head):
+            out += getattr(part, "notices", list)()
+        return out
 
     # ---- cache ----------------------------------------------------------------
     def cache_needs(self) -> list:
@@ -104,13 +122,11 @@ class Model:
         return total
 
     def _all_weights(self):
-        yield self.embedding
-        yield self.head
-        for b in self.blocks:
-            for part in (b.mixer, b.feed_forward):
-                for v in vars(part).values():
-                    if isinstance(v, torch.Tensor) and v.dim() == 2:
-                        yield v
+        """Every tensor a part says it holds (a part without ``weights()`` reports none)."""
+        for part in (self.embedding, self.head, self.final_norm, *self.blocks):
+            for t in getattr(part, "weights", tuple)():
+                if t is not None:
+                    yield t
 
     def describe(self) -> str:
         s = self.spec
@@ -123,8 +139,8 @@ class Model:
         """True when every part of every block declares that its step may be replayed from a
         CUDA graph; one part that does not (a part registered from outside, say) makes all steps
         of this model run plainly."""
-        return (all(getattr(b, "graph_safe", False) for b in self.blocks)
-                and getattr(self.final_norm, "graph_safe", False))
+        return all(getattr(part, "graph_safe", False)
+                   for part in (self.embedding, self.final_norm, self.head, *self.blocks))
 
     # ---- one step ---------------------------------------------------------------
     def forward(self, ctx: StepContext, cache: Cache, want_rows: Optional[torch.Tensor],
@@ -135,12 +151,14 @@ class Model:
         ws = ctx.workspace
         ctx.step_cache.clear()                     # per-step tables are rebuilt from this step's tokens
         x = ws.buffer("stream", (ctx.n_tokens, self.hidden), torch.float32)
-        kernels.embed_rows(self.embedding, ctx.tok_ids[:ctx.n_tokens], x)
+        self.embedding.forward(ctx.tok_ids[:ctx.n_tokens], x, ctx)
         for position, entry in enumerate(self.spec.schedule):
             self.blocks[entry.layer].forward(x, ctx, cache.view(self.spec.cache_owner(position)))
         if n_want == 0:
             return None
         logits = logits_out if logits_out is not None else \
             ws.buffer("head.logits", (n_want, self.vocab), torch.float32)
-        normed_linear(x, self.final_norm, self.head, logits, ctx, rows=want_rows)
+        h = ws.buffer("head.normed", (n_want, self.hidden), self.dtype)
+        self.final_norm.forward(x, h, want_rows)
+        self.head.forward(h, logits, ctx)
         return logits

@@ -50,6 +50,7 @@ class Engine:
 
     GRAPH_MIN_TOKENS = 32        # smaller steps are cheap to launch (and decoding has its own session)
     GRAPHS_KEPT = 8
+    DECODE_RUNNERS_KEPT = 24     # shapes of decode steps whose buffers and graphs are kept (engine/decode.py)
 
     def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None,
                  step_graphs: bool = True):
@@ -63,6 +64,8 @@ class Engine:
         self.step_graphs = step_graphs and model.graph_safe
         self._graphs: "OrderedDict[tuple, tuple]" = OrderedDict()    # shape -> (graph, generation, logits)
         self._seen: "OrderedDict[tuple, int]" = OrderedDict()        # shapes run plainly so far
+        self.decode_runners: "OrderedDict[tuple, object]" = OrderedDict()
+        self.graph_captures = 0      # CUDA graphs captured so far (prompt shapes and decode shapes)
 
     # ---- sequences -----------------------------------------------------------
     def open_sequence(self) -> Sequence:
@@ -70,6 +73,15 @@ class Engine:
 
     def close_sequence(self, seq: Sequence) -> None:
         self.cache.close_sequence(seq)
+
+    def check(self) -> None:
+        """Raises ``KernelError`` if a kernel launched so far reported that one of its bounded
+        waits gave up (its output is then invalid).  Reads a word from the device, so it waits
+        for the stream; callers that are about to read logits or tokens on the host call it
+        where they synchronise anyway."""
+        if self.model.dtype == torch.bfloat16:
+            from .. import kernels_bf16
+            kernels_bf16.check_status()
 
     # ---- step ------------------------------------------------------------------
     def _check(self, entries: Seq[StepEntry]) -> None:
@@ -174,6 +186,7 @@ class Engine:
             self.cache.reserve(e.seq, e.seq.length + len(e.tokens))
         # the pinned staging buffer is reused: the previous step's copy must be over
         torch.cuda.current_stream().synchronize()
+        self.check()                 # a kernel of an earlier step that gave up a wait is reported here
         ctx, want_rows, n_want = self.build_context(entries)
         logits = self._forward(entries, ctx, want_rows, n_want)
         for e in entries:
@@ -203,6 +216,7 @@ class Engine:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx, self.cache, want_rows, n_want)
+            self.graph_captures += 1
             if self.workspace.generation == generation:
                 self._graphs[key] = (graph, generation, logits)
                 while len(self._graphs) > self.GRAPHS_KEPT:

@@ -226,6 +226,32 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
     gemm_simt(a, w, out, accumulate)
 
 
+def product_notices(what: str, w: Optional[torch.Tensor], compute_dtype: torch.dtype) -> list:
+    """Why products with the matrix ``w`` will run on the 32-bit FFMA kernel although the
+    model computes in bfloat16: one line per reason, for the notice printed when a model is
+    built (the result is right either way; the speed is not the same)."""
+    if w is None or compute_dtype != torch.bfloat16:
+        return []
+    if w.dtype != torch.bfloat16:
+        return [f"{what}: the matrix is kept in {str(w.dtype).replace('torch.', '')} as stored, so its "
+                "products run on the 32-bit FFMA kernel, not on the tensor cores"]
+    if w.shape[1] % 8 or w.stride(0) % 8 or w.data_ptr() % 16:
+        return [f"{what}: K = {w.shape[1]} is no multiple of 8, so its products run on the 32-bit "
+                "FFMA kernel, not on the tensor cores"]
+    return []
+
+
+def attention_notices(what: str, head_dim: int, page_size: int, compute_dtype: torch.dtype) -> list:
+    if compute_dtype != torch.bfloat16:
+        return []
+    from . import kernels_bf16
+    if head_dim not in kernels_bf16.FAST_HEAD_SIZES or page_size != 64:
+        sizes = " and ".join(str(h) for h in kernels_bf16.FAST_HEAD_SIZES)
+        return [f"{what}: head size {head_dim} runs on the 32-bit attention kernel (the tensor-core "
+                f"kernels take head sizes {sizes})"]
+    return []
+
+
 # ---------------------------------------------------------------------------
 # attention
 # ---------------------------------------------------------------------------
@@ -302,6 +328,11 @@ def sample_filtered(logits, temperature, top_k, top_p, penalty, recent, recent_n
     _need(logits, torch.float32, "logits")
     _need(out_ids, torch.int32, "out_ids")
     R, V = logits.shape
+    if recent is not None:
+        _need(recent, torch.int32, "recent")
+        _need(recent_n, torch.int32, "recent_n")
+        if recent.shape[0] < R or recent_n.shape[0] < R:
+            raise KernelError("sample_filtered: recent and recent_n need a row per row of logits")
     f = _fn("sampling.cu", "g2b_sample_filtered",
             [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_void_p, c_int,
              c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p])

@@ -12,9 +12,9 @@ class PreNormBlock:
     def __init__(self, layer: LayerSpec, hidden_size: int, dtype: torch.dtype, device):
         self.names = dict(layer.block["names"])
         self.hidden, self.dtype = int(hidden_size), dtype
-        ncls = norm_class(layer.norm)
-        self.mixer_norm = ncls(layer.norm, hidden_size, dtype, device)
-        self.ffn_norm = ncls(layer.norm, hidden_size, dtype, device)
+        ffn_norm = layer.ffn_norm or layer.norm
+        self.mixer_norm = norm_class(layer.norm)(layer.norm, hidden_size, dtype, device)
+        self.ffn_norm = norm_class(ffn_norm)(ffn_norm, hidden_size, dtype, device)
         self.mixer = mixer_class(layer.mixer)(layer.mixer, hidden_size, dtype, device)
         self.feed_forward = feed_forward_class(layer.feed_forward)(layer.feed_forward, hidden_size,
                                                                    dtype, device)
@@ -22,10 +22,10 @@ class PreNormBlock:
     @classmethod
     def expected(cls, layer: LayerSpec, hidden_size: int) -> dict:
         names = dict(layer.block["names"])
-        ncls = norm_class(layer.norm)
+        ffn_norm = layer.ffn_norm or layer.norm
         out = {}
-        out.update(ncls.expected(layer.norm, hidden_size, names["mixer_norm"]))
-        out.update(ncls.expected(layer.norm, hidden_size, names["ffn_norm"]))
+        out.update(norm_class(layer.norm).expected(layer.norm, hidden_size, names["mixer_norm"]))
+        out.update(norm_class(ffn_norm).expected(ffn_norm, hidden_size, names["ffn_norm"]))
         out.update(mixer_class(layer.mixer).expected(layer.mixer, hidden_size))
         out.update(feed_forward_class(layer.feed_forward).expected(layer.feed_forward, hidden_size))
         return out
@@ -39,15 +39,24 @@ class PreNormBlock:
     def cache_need(self):
         return self.mixer.cache_need()
 
+    def parts(self) -> tuple:
+        return (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+
+    def weights(self):
+        """Every tensor the block's parts hold (a part without ``weights()`` reports none)."""
+        for part in self.parts():
+            yield from getattr(part, "weights", tuple)()
+
+    def notices(self) -> list:
+        return [line for part in self.parts() for line in getattr(part, "notices", list)()]
+
     @property
     def graph_safe(self) -> bool:
         """Whether a step of this block may be captured in a CUDA graph and replayed: every part
         must say so itself (``graph_safe = True``: its step does nothing but launch kernels on
         the current stream, takes its scratch memory from the step's workspace, and neither reads
         results on the host nor keeps host-side state from step to step)."""
-        return all(getattr(part, "graph_safe", False)
-                   for part in (self.mixer_norm, self.ffn_norm, self.mixer, self.feed_forward,
-                                getattr(self.mixer, "position", None)) if part is not None)
+        return all(getattr(part, "graph_safe", False) for part in self.parts())
 
     def forward(self, x32: torch.Tensor, ctx, cache_view) -> None:
         # a part that offers ``forward_from_stream`` takes the stream and the norm and may

@@ -44,6 +44,13 @@ class SwiGLU:
         self.w_gate_up = fused.reshape(2 * self.inter, self.hidden).contiguous()
         self.w_down = tensors[self.names["down"]].contiguous()
 
+    def weights(self):
+        return (self.w_gate_up, self.w_down)
+
+    def notices(self) -> list:
+        return (kernels.product_notices("feed-forward gate/up", self.w_gate_up, self.dtype)
+                + kernels.product_notices("feed-forward down", self.w_down, self.dtype))
+
     def forward(self, h: torch.Tensor, ctx, residual32: torch.Tensor) -> None:
         T = h.shape[0]
         ws = ctx.workspace

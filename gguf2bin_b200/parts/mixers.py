@@ -25,8 +25,6 @@ from .registry import norm_class, position_class, register_mixer
 
 
 class GQAAttention:
-    graph_safe = True          # its step only launches kernels: may be replayed from a CUDA graph
-
     def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device):
         self.nh = int(spec["n_heads"])
         self.nkv = int(spec["n_kv_heads"])
@@ -82,6 +80,21 @@ class GQAAttention:
             self.q_norm_w = tensors[n["q_norm"]].to(torch.float32).contiguous()
             if not self.shared_kv:
                 self.k_norm_w = tensors[n["k_norm"]].to(torch.float32).contiguous()
+
+    def weights(self):
+        return [t for t in (self.w_qkv, self.w_o, self.q_norm_w, self.k_norm_w) if t is not None]
+
+    def notices(self) -> list:
+        from ..cache.storage import PAGE_SIZE
+        return (kernels.product_notices("attention q/k/v", self.w_qkv, self.dtype)
+                + kernels.product_notices("attention output", self.w_o, self.dtype)
+                + kernels.attention_notices("attention", self.hd, PAGE_SIZE, self.dtype))
+
+    @property
+    def graph_safe(self) -> bool:
+        """Its own step only launches kernels; whether the whole of it may be replayed from a
+        CUDA graph is then up to its position part."""
+        return bool(getattr(self.position, "graph_safe", False))
 
     # ---- cache ---------------------------------------------------------------
     def cache_need(self):

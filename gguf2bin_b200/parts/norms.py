@@ -25,6 +25,9 @@ class RMSNorm:
     def bind(self, weight: torch.Tensor) -> None:
         self.weight = weight.to(torch.float32).contiguous()      # exact widening
 
+    def weights(self):
+        return (self.weight,)
+
     def forward(self, x32: torch.Tensor, out: torch.Tensor, rows=None) -> None:
         kernels.rmsnorm(x32, self.weight, self.eps, out, rows)
 

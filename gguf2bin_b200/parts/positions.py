@@ -23,6 +23,7 @@ class RopeNeox:
 
     def __init__(self, spec: PartSpec, head_dim: int, device):
         self.theta = float(spec["theta"])
+        self.head_dim = int(head_dim)
         self.rotary_dim = int(spec.get("rotary_dim") or head_dim)
         if self.rotary_dim % 2 or not (0 < self.rotary_dim <= head_dim):
             raise ConfigError(f"rope_neox: rotary_dim {self.rotary_dim} must be even and at most "
@@ -38,8 +39,21 @@ class RopeNeox:
     def fused_rotation(self):
         return self.inv_freq, self.rotary_dim
 
-    def apply(self, q, k, ctx) -> None:          # never needed: the rotation is fused
-        raise NotImplementedError
+    def apply(self, q, k, ctx) -> None:
+        """Rotates q [T, heads*head_dim] and k in place.  The library's own mixer never comes
+        here (it hands ``fused_rotation()`` to its fused kernel); a mixer that runs its
+        position part as a step of its own does.  The rotation is that same kernel's, asked
+        for nothing but the rotation."""
+        from .. import kernels
+        rope = ctx.rope_table(self.inv_freq)
+        for i, a in enumerate((q, k)):
+            if a is None or a.numel() == 0:
+                continue
+            out = ctx.workspace.buffer(f"rope.apply.{i}", tuple(a.shape), a.dtype)
+            kernels.qknorm_rope_cache(a, a.shape[1] // self.head_dim, 0, self.head_dim, None, None,
+                                      0.0, rope, self.rotary_dim, ctx.tok_pos, ctx.tok_seq, None,
+                                      None, ctx.page_size, out)
+            a.copy_(out)
 
 
 class NoPosition:

@@ -9,6 +9,7 @@ from ..config.specs import ConfigError, PartSpec
 
 _FAMILIES: dict[str, dict[str, Callable]] = {
     "norm": {}, "position": {}, "mixer": {}, "feed_forward": {}, "block": {},
+    "embedding": {}, "head": {},
 }
 
 
@@ -29,6 +30,8 @@ def register_position(kind, cls): _register("position", kind, cls)
 def register_mixer(kind, cls): _register("mixer", kind, cls)
 def register_feed_forward(kind, cls): _register("feed_forward", kind, cls)
 def register_block(kind, cls): _register("block", kind, cls)
+def register_embedding(kind, cls): _register("embedding", kind, cls)
+def register_head(kind, cls): _register("head", kind, cls)
 
 
 def norm_class(spec): return _lookup("norm", spec)
@@ -36,6 +39,8 @@ def position_class(spec): return _lookup("position", spec)
 def mixer_class(spec): return _lookup("mixer", spec)
 def feed_forward_class(spec): return _lookup("feed_forward", spec)
 def block_class(spec): return _lookup("block", spec)
+def embedding_class(spec): return _lookup("embedding", spec)
+def head_class(spec): return _lookup("head", spec)
 
 
 def registered(family: str) -> list[str]:

@@ -19,6 +19,7 @@ class Sampler:
         self.device = torch.device(device)
         self._recent_host: Optional[torch.Tensor] = None
         self._recent_dev: Optional[torch.Tensor] = None
+        self._cap = 0
 
     def seed(self, slots: Sequence[int], streams: Sequence[int], seed: int) -> None:
         s = torch.tensor(list(slots), dtype=torch.int32, device=self.device)
@@ -33,19 +34,24 @@ class Sampler:
             kernels.sample_rows(logits, params.temperature, self.seq_state, slots, out_ids)
             return
         R = logits.shape[0]
-        if self._recent_host is None or self._recent_host.shape[0] < R:
-            cap = max(R, 64)
-            self._recent_host = torch.zeros(cap, RECENT_USE + 1, dtype=torch.int32, pin_memory=True)
-            self._recent_dev = torch.zeros(cap, RECENT_USE + 1, dtype=torch.int32, device=self.device)
-        host = self._recent_host
+        if self._recent_host is None or self._cap < R:
+            # ids [cap, RECENT_USE] and counts [cap], each contiguous, in one staging buffer
+            self._cap = cap = max(R, 64)
+            self._recent_host = torch.zeros(cap * (RECENT_USE + 1), dtype=torch.int32, pin_memory=True)
+            self._recent_dev = torch.zeros(cap * (RECENT_USE + 1), dtype=torch.int32, device=self.device)
+        cap = self._cap
+        # the last call's copy out of the staging buffer must be over before it is refilled
+        torch.cuda.current_stream().synchronize()
+        host_ids = self._recent_host[:cap * RECENT_USE].view(cap, RECENT_USE)
+        host_n = self._recent_host[cap * RECENT_USE:]
         for r in range(R):
             ids = list(recent[r])[-RECENT_USE:] if recent is not None else []
-            host[r, 0] = len(ids)
+            host_n[r] = len(ids)
             if ids:
-                host[r, 1:1 + len(ids)] = torch.tensor(ids, dtype=torch.int32)
-        torch.cuda.current_stream().synchronize()
-        self._recent_dev[:R].copy_(host[:R], non_blocking=True)
-        dev = self._recent_dev
+                host_ids[r, :len(ids)] = torch.tensor(ids, dtype=torch.int32)
+        self._recent_dev.copy_(self._recent_host, non_blocking=True)
+        dev_ids = self._recent_dev[:cap * RECENT_USE].view(cap, RECENT_USE)
+        dev_n = self._recent_dev[cap * RECENT_USE:]
         kernels.sample_filtered(logits, params.temperature, params.top_k, params.top_p,
-                                params.repeat_penalty, dev[:, 1:], dev[:, 0], self.seq_state,
+                                params.repeat_penalty, dev_ids, dev_n, self.seq_state,
                                 slots, out_ids)

@@ -72,3 +72,15 @@ def test_registry_takes_new_architectures(tmp_path):
     (tmp_path / "config.json").write_text("{not json")
     with pytest.raises(ConfigError, match="JSON"):
         model_spec_from_folder(tmp_path)
+
+
+def test_stop_ids_come_from_both_configuration_files(tmp_path):
+    (tmp_path / "config.json").write_text(json.dumps({**TINY["a"], "eos_token_id": 7}))
+    assert model_spec_from_folder(tmp_path).stop_token_ids == (7,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [9, 7, 3], "top_k": 20}))
+    assert model_spec_from_folder(tmp_path).stop_token_ids == (7, 9, 3)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": "nine"}))
+    with pytest.raises(ConfigError, match="generation_config.json.*eos_token_id"):
+        model_spec_from_folder(tmp_path)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"temperature": 0.6}))
+    assert model_spec_from_folder(tmp_path).stop_token_ids == (7,)

@@ -115,6 +115,41 @@ def test_filtered_sampling_is_reproducible_and_batch_independent(llms):
     assert e.tokens == plain_generate("b", "float32", prompts[0], 6)[0]
 
 
+def plain_generate_filtered(name, storage, prompt, n, temp, top_k, top_p, penalty, seed, stream):
+    """The reference's sampler chain (src/main.c:197-268) over the last 64 tokens of the
+    prompt and what was generated so far (src/main.c:18, 327-333), by the plain implementation."""
+    cfg, W = plain_model(name, storage)
+    toks, out = list(prompt), []
+    for draw in range(n):
+        logits = P.forward(cfg, W, toks, np.float32)[-1]
+        r = philox_plain.uniform(seed, stream, draw) if temp > 0 else 0.0
+        t, _, _ = P.sample_advanced(logits, temp, top_k, top_p, penalty, toks[-64:], r)
+        out.append(int(t))
+        toks.append(int(t))
+    return out
+
+
+@pytest.mark.parametrize("temp,top_k", [(0.0, 0), (0.9, 1), (0.8, 5)])
+def test_repeat_penalty_in_a_batch_against_plain(llms, temp, top_k):
+    """A strong repeat penalty on a batch of four unequal prompts: every row must be
+    penalised with its OWN recent tokens and count (a row that read another row's would
+    choose other ids), and a request's tokens must not depend on its row in the batch."""
+    llm = llms("b", "float32")
+    prompts = [random_tokens("b", n, 90 + i) for i, n in enumerate([7, 70, 3, 21])]
+    kw = dict(n=12, temperature=temp, top_k=top_k, top_p=1.0 if top_k <= 1 else 0.95,
+              repeat_penalty=1.6, seed=31, ignore_eos=True)
+    outs = llm.generate(prompts, **kw)
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        want = plain_generate_filtered("b", "float32", p, 12, temp, top_k, kw["top_p"], 1.6, 31, i)
+        assert o.tokens == want, f"request {i}"
+    # the penalty must have mattered: unpenalised greedy output differs somewhere
+    if temp == 0.0:
+        assert any(o.tokens != plain_generate("b", "float32", p, 12)[0] for p, o in zip(prompts, outs))
+    # each request in a batch of its own (row 0 every time) draws the same tokens
+    one_by_one = llm.generate(prompts, max_batch=1, **kw)
+    assert [o.tokens for o in one_by_one] == [o.tokens for o in outs]
+
+
 def test_context_limit_and_errors(llms):
     from gguf2bin_b200.engine import GenerationError, StepEntry, StepError
     llm = llms("a", "float32")
@@ -175,3 +210,43 @@ def test_step_launched_ahead_is_taken_back(llms):
         got = backend.decode([handles[i] for i in live], got)
         assert got == [plain_next(i) for i in live], f"step {step}"
     backend.close(handles[1])
+
+
+def test_decode_graphs_are_kept_by_shape_not_by_call(llms):
+    """A decode graph belongs to the engine and to a shape (sequences, page-table width,
+    sampling): a second call with the same shape captures nothing, and a batch of 64 whose
+    sequences end one per step (63 shapes, each seen once or twice) captures no graph at all
+    instead of one per shape.  Tokens are compared with an engine that never uses graphs."""
+    from gguf2bin_b200.engine.backend import EngineBackend
+    from gguf2bin_b200.sampling import SamplingParams
+    llm = llms("c", "bfloat16", max_tokens=64 * 128)
+    eng = llm.engine
+    prompts = [random_tokens("c", 5 + (i % 7), 500 + i) for i in range(8)]
+    kw = dict(n=14, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0, ignore_eos=True)
+    first = llm.generate(prompts, **kw)
+    after_first = eng.graph_captures
+    assert after_first >= 1, "fourteen steps of one shape are worth a graph"
+    again = llm.generate(prompts, **kw)
+    assert eng.graph_captures == after_first, "the same shape in a later call captured a graph again"
+    assert [o.tokens for o in again] == [o.tokens for o in first]
+    llm.use_graph = False
+    try:
+        plain = llm.generate(prompts, **kw)
+    finally:
+        llm.use_graph = True
+    assert [o.tokens for o in plain] == [o.tokens for o in first]
+
+    backend = EngineBackend(eng, SamplingParams.plain(0.0), seed=0, max_context=128)
+    many = [random_tokens("c", 3 + (i % 5), 600 + i) for i in range(64)]
+    handles = [backend.open(i, 100) for i in range(64)]
+    got = backend.prefill(handles, many)
+    before = eng.graph_captures
+    live = list(range(64))
+    while len(live) > 1:
+        backend.close(handles[live[0]])
+        live, got = live[1:], got[1:]
+        got = backend.decode([handles[i] for i in live], got)
+    backend.close(handles[live[0]])
+    backend.finish()
+    assert eng.graph_captures - before <= 4, f"{eng.graph_captures - before} graphs for a shrinking batch"
+    assert eng.cache.table.slots.n_held == 0 and eng.cache.table.pages.n_held == 0

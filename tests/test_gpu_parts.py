@@ -43,7 +43,7 @@ def swiglu_spec(inter):
                                 ("down", "ffn.down.weight")))
 
 
-def make_spec(hidden, vocab, mixers, ffns, eps, schedule=None, tied=True):
+def make_spec(hidden, vocab, mixers, ffns, eps, schedule=None, tied=True, embedding=None, head=None):
     from gguf2bin_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
     norm = PartSpec.make("rmsnorm", eps=eps)
     block = PartSpec.make("prenorm", names=(("mixer_norm", "n1.weight"), ("ffn_norm", "n2.weight")))
@@ -52,9 +52,9 @@ def make_spec(hidden, vocab, mixers, ffns, eps, schedule=None, tied=True):
     schedule = schedule or [(i, None) for i in range(len(layers))]
     return ModelSpec(architecture="TestModel", hidden_size=hidden, vocab_size=vocab, max_positions=512,
                      layers=layers, schedule=tuple(ScheduleEntry(a, b) for a, b in schedule),
-                     embedding=PartSpec.make("token_embedding", name="emb.weight"),
+                     embedding=embedding or PartSpec.make("token_embedding", name="emb.weight"),
                      final_norm=PartSpec.make("rmsnorm", eps=eps, name="norm.weight"),
-                     head=PartSpec.make("lm_head", tied=tied, name="head.weight"))
+                     head=head or PartSpec.make("lm_head", tied=tied, name="head.weight"))
 
 
 def build(spec, dtype, seed=0):
@@ -96,7 +96,7 @@ def plain_attention(x, W, pfx, m, positions, kv_store, layer, cache_layer, eps):
 
 
 def plain_forward(spec, W, tokens, eps, toy_mixers=None):
-    x = P.embedding(W["emb.weight"], tokens, np.float32)
+    x = P.embedding(W["emb.weight"], tokens, np.float32) * np.float32(spec.embedding.get("multiplier", 1.0))
     positions = np.arange(len(tokens))
     kv_store = {}
     for position, e in enumerate(spec.schedule):
@@ -115,7 +115,10 @@ def plain_forward(spec, W, tokens, eps, toy_mixers=None):
         else:
             x = x + toy_mixers[layer.feed_forward.kind](h, W, pfx)
     x = P.rmsnorm(x, W["norm.weight"], eps, np.float32)
-    return x @ (W["emb.weight"] if spec.head["tied"] else W["head.weight"]).T
+    logits = x @ (W["emb.weight"] if spec.head["tied"] else W["head.weight"]).T
+    if spec.head.get("cap"):                       # the toy head: scaled, then capped smoothly
+        logits = np.float32(spec.head["cap"]) * np.tanh(logits * np.float32(spec.head["scale"] / spec.head["cap"]))
+    return logits
 
 
 def run_cuttings(eng, requests):
@@ -240,6 +243,18 @@ def test_position_part(dtype):
     ref = np.concatenate([P.rope_neox(x[..., :rot], positions, 777.0, np.float32), x[..., rot:]], -1)
     tol = 3e-6 if dtype == "float32" else 2.0 ** -8
     np.testing.assert_allclose(out.float().cpu().numpy().reshape(4, nh, hd), ref, rtol=tol, atol=tol)
+    # the part run as a step of its own (what a mixer that does not fuse it calls): q and k in place
+    from gguf2bin_b200.engine.workspace import Workspace
+    from gguf2bin_b200.parts.base import StepContext
+    k = gpu(rng.standard_normal((4, 2 * hd)).astype(np.float32), tdt)
+    kx = k.float().cpu().numpy().reshape(4, 2, hd)
+    q2 = q.clone()
+    ctx = StepContext(4, 1, None, pos_t, torch.zeros(4, dtype=torch.int32, device=DEV), None, 64,
+                      Workspace(DEV), tdt)
+    pos.apply(q2, k, ctx)
+    kref = np.concatenate([P.rope_neox(kx[..., :rot], positions, 777.0, np.float32), kx[..., rot:]], -1)
+    np.testing.assert_allclose(q2.float().cpu().numpy().reshape(4, nh, hd), ref, rtol=tol, atol=tol)
+    np.testing.assert_allclose(k.float().cpu().numpy().reshape(4, 2, hd), kref, rtol=tol, atol=tol)
 
 
 # ---------------------------------------------------------------------------
@@ -421,3 +436,104 @@ def test_toy_parts_register_build_and_step(dtype):
     check(eng, spec, W, some_requests(83, [40, 3, 90, 17]), dtype, eps, toy)
     # a reused slot starts from a cleared state: run the same requests again
     check(eng, spec, W, some_requests(83, [40, 3, 90, 17]), dtype, eps, toy)
+
+
+def test_generation_with_a_state_mixer():
+    """The decay mixer's state cannot be rewound, so the decode session must not run a step
+    ahead of the caller for this model: three sequences decode together, the caller overrides
+    the sampled tokens once, and the sequences end at different steps (each end starts a new
+    session for those that are left).  Every token equals the plain implementation's greedy
+    choice over the tokens fed so far; a state that had taken a token twice would not."""
+    from gguf2bin_b200.config import PartSpec
+    from gguf2bin_b200.engine.backend import EngineBackend
+    from gguf2bin_b200.parts import register_mixer
+    from gguf2bin_b200.sampling import SamplingParams
+    register_mixer("toy_decay", DecayMixer)
+    eps = 1e-5
+    mixers = [attention_spec(4, 2, 16, eps, theta=1e4), PartSpec.make("toy_decay", width=24)]
+    spec = make_spec(32, 83, mixers, [swiglu_spec(40), swiglu_spec(24)], eps)
+    eng, W = build(spec, "float32", seed=11)
+    toy = {"toy_decay": decay_mixer_plain}
+    backend = EngineBackend(eng, SamplingParams.plain(0.0), seed=0, max_context=256)
+    prompts = some_requests(83, [9, 4, 17], seed=5)
+    handles = [backend.open(i, 64) for i in range(3)]
+    fed = [list(p) for p in prompts]
+
+    def plain_next(i):
+        return int(np.argmax(plain_forward(spec, W, fed[i], eps, toy)[-1]))
+
+    got = backend.prefill(handles, prompts)
+    assert got == [plain_next(i) for i in range(3)]
+    live = [0, 1, 2]
+    for step in range(10):
+        if step == 3:                              # the caller feeds other tokens than the sampled ones
+            got = [(t + 7) % 83 for t in got]
+        if step in (5, 7):                         # a sequence ends; the others go on as a new batch
+            gone = live[0]
+            backend.close(handles[gone])
+            live, got = live[1:], got[1:]
+        for i, t in zip(live, got):
+            fed[i].append(t)
+        got = backend.decode([handles[i] for i in live], got)
+        assert got == [plain_next(i) for i in live], f"step {step}"
+    backend.close(handles[live[0]])
+    backend.finish()
+    assert eng.cache.table.slots.n_held == 0
+
+
+class ScaledEmbedding:
+    """Toy end: the table's row times a constant."""
+
+    def __init__(self, spec, vocab_size, hidden_size, dtype, device):
+        self.name, self.multiplier = spec["name"], float(spec["multiplier"])
+
+    @classmethod
+    def expected(cls, spec, vocab_size, hidden_size):
+        from gguf2bin_b200.weights import Expected
+        return {spec["name"]: Expected((vocab_size, hidden_size))}
+
+    def bind(self, tensors):
+        self.table = tensors[self.name].contiguous()
+
+    def forward(self, tok_ids, out32, ctx):
+        from gguf2bin_b200 import kernels
+        kernels.embed_rows(self.table, tok_ids, out32)
+        out32.mul_(self.multiplier)
+
+
+class CappedHead:
+    """Toy end: logits = cap * tanh(scale * (h . E^T) / cap) over the embedding's table."""
+
+    def __init__(self, spec, vocab_size, hidden_size, dtype, device):
+        self.scale, self.cap = float(spec["scale"]), float(spec["cap"])
+
+    @classmethod
+    def expected(cls, spec, vocab_size, hidden_size):
+        return {}
+
+    def bind(self, tensors, embedding):
+        self.matrix = embedding.table
+
+    def forward(self, h, logits32, ctx):
+        from gguf2bin_b200 import kernels
+        kernels.linear(h, self.matrix, logits32)
+        logits32.copy_(self.cap * torch.tanh(logits32 * (self.scale / self.cap)))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_ends_register_build_and_step(dtype):
+    """Another architecture's embedding (scaled) and head (a scale and a smooth cap on the
+    logits, tied to the embedding) are parts like the others: registered from here, chosen by
+    the spec, and the model only walks them."""
+    from gguf2bin_b200.config import PartSpec
+    from gguf2bin_b200.parts import register_embedding, register_head
+    register_embedding("toy_scaled_embedding", ScaledEmbedding)
+    register_head("toy_capped_head", CappedHead)
+    eps = 1e-6
+    spec = make_spec(48, 97, [attention_spec(3, 1, 16, eps, theta=1e4)] * 2, [swiglu_spec(40)] * 2, eps,
+                     embedding=PartSpec.make("toy_scaled_embedding", name="emb.weight", multiplier=6.5),
+                     head=PartSpec.make("toy_capped_head", tied=True, name="unused", scale=9.0, cap=1.5))
+    eng, W = build(spec, dtype, seed=13)
+    assert not eng.model.graph_safe          # the toy ends do not say they are fit for graphs
+    assert "unused" not in W
+    check(eng, spec, W, some_requests(97, [33, 2, 70]), dtype, eps)
