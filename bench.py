@@ -2,7 +2,8 @@
 """Decode and prefill throughput of gguf2bin_b200 on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--batch B] [--layers L] [--context C] [--no-points] [--sizes 0.6b|8b|14b]
+                    [--workload decode|ragged8|b64] [--batch B] [--layers L] [--context C]
+                    [--no-points] [--sizes 0.6b|8b|14b]
 
 The default run has the layer sizes of Qwen3-0.6B (28 layers, width 1024, 16/8 heads of
 128, feed-forward 3072, vocabulary 151936, tied embeddings) with random bfloat16
@@ -17,11 +18,19 @@ whole batch.  It prints ONE JSON line:
              from pinned host memory and come back to the host every step; the median of
              three calls (each with its own prompts' prefill before and the set-up of its
              decode session inside the timed steps), all three listed under "runs"
-  prefill    one step over a 2,048-token prompt: tokens per second, milliseconds, and the
-             fraction of the tensor-core peak its flops reach
+  prefill    one step over a 2,048-token prompt: tokens per second, milliseconds (the median of
+             three runs that replay the shape's graph; ``first_ms`` is the first run of the
+             shape, which runs plainly), and the fraction of the tensor-core peak its flops reach
   roofline   bytes a decode step must read (every weight once, the cache of the live
              requests) divided by its time, against the measured copy bandwidth
-  points     decode tokens per second at batch 1 and 64 (fewer steps)
+  points     decode tokens per second at batch 1 and 64 (fewer steps), each with its step time
+             and its own roofline figures
+
+``--workload ragged8`` runs the workload of the Qwen3-8B configuration (all 36 layers): eight
+prompts with lengths drawn uniformly from [128, 2048] (seeded) in ONE ragged prompt step, whose
+tokens per second go under ``prefill``, then 256 decode steps.  ``--workload b64`` runs that of
+the Qwen3-14B configuration (all 40 layers): 64 prompts of 512 tokens in one prompt step, then
+decoding to a context of 2,048.  The weights are made in device memory (no folder is written).
 
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from the
 fallback figures 6.65 TB/s and 1.59 PFLOP/s.  Inputs are synthetic.  Between timed steps
@@ -131,11 +140,13 @@ def model_bytes_and_flops(cfg: dict, n_layers: int):
                 nq=nq)
 
 
-def prefill_flops(cfg: dict, n_layers: int, T: int) -> float:
+def prefill_flops(cfg: dict, n_layers: int, lengths) -> float:
+    """Flops of one prompt step over sequences of these lengths, logits at each one's last place."""
     m = model_bytes_and_flops(cfg, n_layers)
-    linear = 2.0 * T * n_layers * m["layer_params"]
-    attention = n_layers * 4.0 * m["nq"] * T * (T + 1) / 2
-    head = 2.0 * cfg["vocab_size"] * cfg["hidden_size"]
+    total = float(sum(lengths))
+    linear = 2.0 * total * n_layers * m["layer_params"]
+    attention = sum(n_layers * 4.0 * m["nq"] * T * (T + 1) / 2 for T in lengths)
+    head = 2.0 * cfg["vocab_size"] * cfg["hidden_size"] * len(lengths)
     return linear + attention + head
 
 
@@ -145,18 +156,47 @@ def random_prompts(n: int, length: int, vocab: int, seed: int):
     return [rng.integers(0, vocab, length).tolist() for _ in range(n)]
 
 
-def decode_device_timed(llm, batch: int, start_ctx: int, steps: int, warmup: int, vocab: int):
-    """(seconds for exactly `steps` steps, launches per step, mean context) on the device."""
+def timed_prompt_step(llm, prompts, repeats: int):
+    """Milliseconds of ONE step over all the prompts (logits at each last place), device-timed:
+    (the first run of this shape, which runs plainly; the median of the last ``repeats`` runs,
+    which replay the shape's graph)."""
+    import torch
+    from gguf2bin_b200.engine import StepEntry
+    times = []
+    for _ in range(3 + repeats):
+        seqs = [llm.open_sequence() for _ in prompts]
+        for s, p in zip(seqs, prompts):
+            llm.engine.cache.reserve(s, len(p))
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        llm.step([StepEntry(s, p, (len(p) - 1,)) for s, p in zip(seqs, prompts)])
+        e1.record()
+        torch.cuda.synchronize()
+        for s in seqs:
+            llm.close_sequence(s)
+        times.append(e0.elapsed_time(e1))
+    return times[0], statistics.median(times[3:])
+
+
+def decode_device_timed(llm, prompts, steps: int, warmup: int, vocab: int, whole_batch_prefill: bool):
+    """Decodes ``steps`` steps after the prompts and ``warmup`` untimed steps: (seconds for
+    exactly ``steps`` steps, launches per step, mean context over the timed steps), timed on
+    the device.  The prompts are prefilled one sequence per step, or all in one ragged step."""
     import torch
     from gguf2bin_b200.engine import DecodeSession, StepEntry
     from gguf2bin_b200.sampling import Sampler, SamplingParams
     eng = llm.engine
+    batch = len(prompts)
     seqs = [eng.open_sequence() for _ in range(batch)]
     try:
-        plen = start_ctx - warmup
-        for i, s in enumerate(seqs):
-            eng.cache.reserve(s, start_ctx + steps + 1)
-            eng.step([StepEntry(s, random_prompts(1, plen, vocab, 100 + i)[0], ())])
+        for s, p in zip(seqs, prompts):
+            eng.cache.reserve(s, len(p) + warmup + steps + 1)
+        if whole_batch_prefill:
+            eng.step([StepEntry(s, p, ()) for s, p in zip(seqs, prompts)])
+        else:
+            for s, p in zip(seqs, prompts):
+                eng.step([StepEntry(s, p, ())])
         sampler = Sampler(eng.cache.seq_state, eng.device)
         session = DecodeSession(eng, seqs, sampler, SamplingParams.plain(0.0), use_graph=True,
                                 eager_steps=1)
@@ -164,29 +204,49 @@ def decode_device_timed(llm, batch: int, start_ctx: int, steps: int, warmup: int
         for _ in range(warmup):
             session.run()
         torch.cuda.synchronize()
-        assert seqs[0].length == start_ctx
+        start = sum(s.length for s in seqs) / batch
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
         for _ in range(steps):
             session.run()
         t1.record()
         torch.cuda.synchronize()
-        return t0.elapsed_time(t1) / 1e3, session.launches_per_step, start_ctx + steps / 2.0
+        eng.check()
+        return t0.elapsed_time(t1) / 1e3, session.launches_per_step, start + steps / 2.0
     finally:
         for s in seqs:
             eng.close_sequence(s)
 
 
+def hbm_roofline(sizes: dict, batch: int, mean_ctx: float, sec_per_step: float, pk: dict) -> dict:
+    """Bytes a decode step has to read (every weight once, the cache of the live requests)
+    over its time, against the copy bandwidth."""
+    step_bytes = sizes["weight_bytes"] + batch * mean_ctx * sizes["kv_bytes_per_token"]
+    achieved = step_bytes / sec_per_step / 1e9
+    return dict(bound="hbm", achieved=achieved, peak=pk["hbm_gbs"], unit="GB/s",
+                frac=achieved / pk["hbm_gbs"], peaks=pk["source"])
+
+
+WORKLOADS = {
+    # name: (sizes, batch, what it is)
+    "decode": ("0.6b", 8, "every sequence prefilled to half the context, then decoded"),
+    "ragged8": ("8b", 8, "8 prompts with lengths uniform in [128, 2048] in ONE prompt step, then 256 decode steps"),
+    "b64": ("14b", 64, "64 prompts of 512 tokens in one prompt step, decoded to a context of 2048"),
+}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=512)
+    ap.add_argument("--steps", type=int, default=None, help="decode steps timed (default: 512; the workload's own for ragged8 and b64)")
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--workload", default="decode", choices=sorted(WORKLOADS),
+                    help="decode: the default run; ragged8 / b64: the two larger configurations' own workloads")
+    ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has")
-    ap.add_argument("--sizes", default="0.6b", choices=["0.6b"] + sorted(OTHER_SIZES),
-                    help="layer sizes: Qwen3-0.6B (the default run) or those of Qwen3-8B / 14B")
+    ap.add_argument("--sizes", default=None, choices=["0.6b"] + sorted(OTHER_SIZES),
+                    help="layer sizes: Qwen3-0.6B, or those of Qwen3-8B / 14B (default: the workload's)")
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
     a = ap.parse_args()
@@ -203,12 +263,14 @@ def main() -> int:
     if a.warmup < 3:
         a.warmup = 3
 
+    import numpy as np
     import torch
     from gguf2bin_b200 import kernels
     from gguf2bin_b200.api import LLM
-    from gguf2bin_b200.engine import StepEntry
-    from gguf2bin_b200.weights import write_random_model
 
+    w_sizes, w_batch, w_what = WORKLOADS[a.workload]
+    a.sizes = a.sizes or w_sizes
+    a.batch = a.batch or w_batch
     cfg = dict(QWEN3_0P6B)
     cfg.update(OTHER_SIZES.get(a.sizes, {}))
     full_layers = cfg["num_hidden_layers"]
@@ -216,87 +278,106 @@ def main() -> int:
         a.layers = full_layers
     cfg["num_hidden_layers"] = a.layers
     name = {"0.6b": "Qwen3-0.6B", "8b": "Qwen3-8B", "14b": "Qwen3-14B"}[a.sizes]
-    start_ctx = a.context // 2
-    steps = min(a.steps, a.context - start_ctx - 1)
     pk = peaks()
     sizes = model_bytes_and_flops(cfg, a.layers)
     vocab = cfg["vocab_size"]
 
-    with tempfile.TemporaryDirectory(prefix="g2b_bench_") as tmp:
-        folder = write_random_model(Path(tmp) / "model", cfg, seed=0, dtype="bfloat16")
-        max_batch = 64 if not a.no_points else a.batch
-        max_batch = max(max_batch, a.batch)
-        llm = LLM(folder, dtype="bfloat16", max_tokens=max_batch * (a.context + 64), max_seqs=max_batch + 1)
+    # ---- the workload's prompts and steps ----------------------------------------------------
+    if a.workload == "decode":
+        start_ctx = a.context // 2
+        steps = min(a.steps or 512, a.context - start_ctx - 1)
+        decode_prompts = random_prompts(a.batch, start_ctx - a.warmup, vocab, 100)
+        prefill_prompts = random_prompts(1, PREFILL_TOKENS, vocab, 1)
+        seq_len = a.context
+        points_wanted = not a.no_points
+        max_batch = max(64 if points_wanted else a.batch, a.batch)
+        max_tokens = max_batch * (a.context + 64)
+    elif a.workload == "ragged8":
+        lengths = np.random.default_rng(2024).integers(128, 2049, a.batch).tolist()
+        steps = a.steps or 256
+        decode_prompts = [random_prompts(1, n, vocab, 300 + i)[0] for i, n in enumerate(lengths)]
+        prefill_prompts = decode_prompts
+        seq_len = max(lengths) + a.warmup + steps
+        points_wanted, max_batch = False, a.batch
+        max_tokens = sum(-(-(n + a.warmup + steps + 2) // 64) * 64 for n in lengths) + 64
+    else:
+        a.context = 2048
+        steps = min(a.steps or 10 ** 9, a.context - 512 - a.warmup)
+        decode_prompts = random_prompts(a.batch, 512, vocab, 500)
+        prefill_prompts = decode_prompts
+        seq_len = a.context
+        points_wanted, max_batch = False, a.batch
+        max_tokens = a.batch * (a.context + 64)
 
-        # ---- prefill: one step over a 2,048-token prompt, logits at the last place --------
-        prompt = random_prompts(1, PREFILL_TOKENS, vocab, 1)[0]
-        pre_ms = []
-        for i in range(3 + 3):
-            seq = llm.open_sequence()
-            llm.engine.cache.reserve(seq, PREFILL_TOKENS)
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            llm.step([StepEntry(seq, prompt, (PREFILL_TOKENS - 1,))])
-            e1.record()
-            torch.cuda.synchronize()
-            llm.close_sequence(seq)
-            if i >= 3:
-                pre_ms.append(e0.elapsed_time(e1))
-        pre = statistics.median(pre_ms)
-        pre_flops = prefill_flops(cfg, a.layers, PREFILL_TOKENS)
-        prefill = dict(value=PREFILL_TOKENS / (pre / 1e3), tokens=PREFILL_TOKENS, ms=pre,
-                       frac=pre_flops / (pre / 1e3) / (pk["bf16_tflops"] * 1e12))
+    free0, total_mem = torch.cuda.mem_get_info()
+    llm = LLM.random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, max_seqs=max_batch + 1)
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
 
-        # ---- decode, device-timed -----------------------------------------------------------
-        clocks = ClockSampler()
-        clocks.start()
-        launches0 = kernels.launch_count()
-        sec, per_step, mean_ctx = decode_device_timed(llm, a.batch, start_ctx, steps, a.warmup, vocab)
-        clock_info = clocks.stop()
-        value = a.batch * steps / sec
-        step_bytes = sizes["weight_bytes"] + a.batch * mean_ctx * sizes["kv_bytes_per_token"]
-        achieved = step_bytes / (sec / steps) / 1e9
-        roofline = dict(bound="hbm", achieved=achieved, peak=pk["hbm_gbs"], unit="GB/s",
-                        frac=achieved / pk["hbm_gbs"], peaks=pk["source"])
+    # ---- prefill: one step over the prompts, logits at each last place ------------------------
+    pre_first, pre = timed_prompt_step(llm, prefill_prompts, repeats=3)
+    pre_lengths = [len(p) for p in prefill_prompts]
+    pre_tokens = sum(pre_lengths)
+    pre_flops = prefill_flops(cfg, a.layers, pre_lengths)
+    prefill = dict(value=pre_tokens / (pre / 1e3), tokens=pre_tokens, ms=pre,
+                   frac=pre_flops / (pre / 1e3) / (pk["bf16_tflops"] * 1e12),
+                   first_ms=pre_first, sequences=len(pre_lengths))
 
-        # ---- decode through the Python entry point, host tokens in and out ----------------
-        e2e_steps = min(steps, 256)
-        prompts = random_prompts(a.batch, start_ctx, vocab, 11)
-        llm.generate(prompts[:1], n=4, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0,
-                     ignore_eos=True)
-        e2e_runs = []                      # three whole calls; the median is reported, all are listed
-        for _ in range(3):
-            llm.generate(prompts, n=e2e_steps + 1, temperature=0.0, top_k=0, top_p=1.0,
-                         repeat_penalty=1.0, ignore_eos=True, max_batch=a.batch)
-            acct = llm.last_decode
-            e2e_runs.append((acct["tokens"] / acct["seconds"], acct["steps"]))
-        e2e_value, e2e_count = sorted(e2e_runs)[1]
-        e2e = dict(value=e2e_value, unit="tokens/s", h2d_bytes_per_step=4 * a.batch,
-                   d2h_bytes_per_step=4 * a.batch, steps=e2e_count,
-                   runs=[round(v, 1) for v, _ in e2e_runs])
+    # ---- decode, device-timed -----------------------------------------------------------------
+    clocks = ClockSampler()
+    clocks.start()
+    sec, per_step, mean_ctx = decode_device_timed(llm, decode_prompts, steps, a.warmup, vocab,
+                                                  whole_batch_prefill=a.workload != "decode")
+    clock_info = clocks.stop()
+    value = a.batch * steps / sec
+    roofline = hbm_roofline(sizes, a.batch, mean_ctx, sec / steps, pk)
 
-        # ---- other batch sizes ------------------------------------------------------------------
-        points = {}
-        if not a.no_points:
-            for b, k in ((1, min(steps, 256)), (64, min(steps, 128))):
-                s, _, _ = decode_device_timed(llm, b, start_ctx, k, a.warmup, vocab)
-                points[f"decode_b{b}"] = b * k / s
+    # ---- decode through the Python entry point, host tokens in and out -------------------------
+    e2e_steps = min(steps, 256)
+    e2e_prompts = [p + [1] * a.warmup for p in decode_prompts]     # the same lengths as the timed steps start from
+    llm.generate(e2e_prompts[:1], n=4, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0,
+                 ignore_eos=True)
+    e2e_runs = []                      # three whole calls; the median is reported, all are listed
+    for _ in range(3):
+        llm.generate(e2e_prompts, n=e2e_steps + 1, temperature=0.0, top_k=0, top_p=1.0,
+                     repeat_penalty=1.0, ignore_eos=True, max_batch=a.batch)
+        acct = llm.last_decode
+        e2e_runs.append((acct["tokens"] / acct["seconds"], acct["steps"]))
+    e2e_value, e2e_count = sorted(e2e_runs)[1]
+    e2e = dict(value=e2e_value, unit="tokens/s", h2d_bytes_per_step=4 * a.batch,
+               d2h_bytes_per_step=4 * a.batch, steps=e2e_count,
+               runs=[round(v, 1) for v, _ in e2e_runs], graphs_captured=llm.engine.graph_captures)
 
+    # ---- other batch sizes ------------------------------------------------------------------------
+    points = {}
+    if points_wanted:
+        for b, k in ((1, min(steps, 256)), (64, min(steps, 128))):
+            s, _, ctx_b = decode_device_timed(llm, random_prompts(b, start_ctx - a.warmup, vocab, 100), k,
+                                              a.warmup, vocab, whole_batch_prefill=False)
+            r = hbm_roofline(sizes, b, ctx_b, s / k, pk)
+            points[f"decode_b{b}"] = b * k / s
+            points[f"decode_b{b}_ms_per_step"] = s / k * 1e3
+            points[f"decode_b{b}_gbs"] = r["achieved"]
+            points[f"decode_b{b}_frac"] = r["frac"]
+
+    first_ctx = mean_ctx - steps / 2.0
     out = {
         "metric": f"decode tokens/s ({name} sizes, random weights, batch {a.batch}, "
-                  f"context {start_ctx}->{a.context})",
+                  f"context {first_ctx:.0f}->{first_ctx + steps:.0f})",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": a.warmup,
         "ms_per_step": sec / steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": f"{name} sizes, random weights", "global_batch": a.batch,
-                   "seq_len": a.context, "decode_from": start_ctx, "layers": a.layers,
+        "config": {"model": f"{name} sizes, random weights", "workload": f"{a.workload}: {w_what}",
+                   "global_batch": a.batch,
+                   "seq_len": seq_len, "decode_from": round(first_ctx, 1), "layers": a.layers,
                    "layers_of_config": full_layers, "hidden": cfg["hidden_size"],
                    "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
                    "vocab": vocab, "tied": bool(cfg["tie_word_embeddings"]), "parallelism": "none (1 GPU)",
                    "l2": "inputs larger than L2 (weights + cache read every step)",
-                   "sampling": "greedy on device"},
+                   "sampling": "greedy on device",
+                   "weights": "made on the device (Philox normal), never on disk",
+                   "device_gb_free_before_after": f"{free0 / 1e9:.1f} -> {free1 / 1e9:.1f} of {total_mem / 1e9:.1f}"},
         "e2e": e2e, "gpu_launches": per_step * steps, "launches_per_step": per_step,
         "prefill": prefill, "roofline": roofline, "points": points, "clocks": clock_info,
     }

@@ -25,14 +25,27 @@ __all__ = ["LLM", "Generation", "SamplingParams", "StepEntry"]
 
 
 class LLM:
-    def __init__(self, model_dir, dtype: str = "bfloat16", max_tokens: int = 65536,
-                 max_seqs: Optional[int] = None, device: str = "cuda:0"):
+    def __init__(self, model_dir=None, dtype: str = "bfloat16", max_tokens: int = 65536,
+                 max_seqs: Optional[int] = None, device: str = "cuda:0", model: Optional[Model] = None):
         """``max_tokens``: the most tokens all live sequences hold together (each rounded
-        up to a page of 64); it sizes the cache."""
-        self.model = Model.from_folder(model_dir, dtype=dtype, device=device)
+        up to a page of 64); it sizes the cache.  ``model``: a model that exists already
+        (then ``model_dir``, ``dtype`` and ``device`` are not used)."""
+        if (model is None) == (model_dir is None):
+            raise ValueError("LLM needs a model folder or a model, not both")
+        self.model = model if model is not None else Model.from_folder(model_dir, dtype=dtype,
+                                                                       device=device)
         self.engine = Engine(self.model, max_tokens=max_tokens, max_seqs=max_seqs)
         self.use_graph = True          # replay decode steps from a CUDA graph
         self.last_decode: dict = {}    # wall-clock account of the last call's decode steps
+
+    @classmethod
+    def random(cls, config, seed: int = 0, dtype: str = "bfloat16", max_tokens: int = 65536,
+               max_seqs: Optional[int] = None, device: str = "cuda:0", storage=None) -> "LLM":
+        """Random weights for ``config`` (a config.json dictionary) made in device memory:
+        the model that ``synth`` would write for the same configuration and seed, without
+        the folder (see ``Model.random``)."""
+        return cls(model=Model.random(config, seed, dtype, device, storage), max_tokens=max_tokens,
+                   max_seqs=max_seqs)
 
     @property
     def stop_token_ids(self) -> tuple:

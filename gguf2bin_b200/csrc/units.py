@@ -4,7 +4,7 @@ every size at run time; units specialised on a head size exist once per size in
 from __future__ import annotations
 
 GENERIC_UNITS = [("elementwise.cu", ()), ("gemm_simt.cu", ()), ("attn_generic.cu", ()),
-                 ("sampling.cu", ())]
+                 ("sampling.cu", ()), ("random_init.cu", ())]
 
 # head sizes built ahead of time (what the tests and the benchmark use)
 HEAD_SIZES = (64, 128)

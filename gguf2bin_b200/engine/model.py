@@ -77,6 +77,25 @@ class Model:
         model.bind(tensors)
         return model
 
+    @classmethod
+    def random(cls, config, seed: int, dtype="bfloat16", device="cuda:0", storage=None,
+               std: float = 0.02, scale_std: float = 0.1) -> "Model":
+        """A model with random weights made in device memory, never touching the disk:
+        ``config`` is a config.json dictionary (read through the registry) or a ``ModelSpec``.
+        The weights are those of ``write_random_model(folder, config, seed, storage)`` loaded
+        with ``dtype``, bit for bit (``storage`` defaults to the compute dtype).  The
+        reference makes its synthetic model in-process as well (src/l5_model.c:634-680)."""
+        from ..config import model_spec_from_dict
+        from ..weights.random_init import random_tensors_on_device
+        spec = config if isinstance(config, ModelSpec) else model_spec_from_dict(config)
+        model = cls(spec, dtype, device)
+        stored = parse_dtype(storage) if storage is not None else model.dtype
+        with torch.cuda.device(model.device):
+            tensors = random_tensors_on_device(expected_tensors(spec), seed, stored, model.dtype,
+                                               model.device, std, scale_std)
+            model.bind(tensors)
+        return model
+
     def bind(self, tensors: dict) -> None:
         spec = self.spec
         self.n_params = sum(t.numel() for t in tensors.values())

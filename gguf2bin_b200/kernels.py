@@ -192,6 +192,21 @@ def rewind_step(tok_pos: torch.Tensor, n: int, seq_state: Optional[torch.Tensor]
 
 
 # ---------------------------------------------------------------------------
+# random_init.cu
+# ---------------------------------------------------------------------------
+def philox_normal(out: torch.Tensor, seed: int, tensor_index: int, scale_vector: bool, std: float) -> None:
+    """Fills ``out`` (float32 or bfloat16, contiguous) in place with N(0, std), or with
+    1 + N(0, std) for a scale vector; element i gets the value of (seed, tensor_index, i)."""
+    if not out.is_contiguous():
+        raise KernelError("philox_normal: the tensor must be contiguous")
+    from ctypes import c_longlong, c_uint
+    f = _fn("random_init.cu", "g2b_philox_normal",
+            [c_void_p, c_int, c_longlong, c_ulonglong, c_uint, c_int, c_float, c_void_p])
+    _call(f, _ptr(out), _code(out.dtype), out.numel(), int(seed) & 0xFFFFFFFFFFFFFFFF,
+          int(tensor_index) & 0xFFFFFFFF, 1 if scale_vector else 0, float(std), _stream())
+
+
+# ---------------------------------------------------------------------------
 # matrix products
 # ---------------------------------------------------------------------------
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:

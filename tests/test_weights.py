@@ -125,3 +125,28 @@ def test_shards_and_duplicates(tmp_path):
                                                     ("a", (4,), torch.float32, lambda: a)])
     with pytest.raises(WeightsError, match="more than one shard"):
         load_weights(tmp_path, {"a": Expected((4,)), "b": Expected((2, 3))}, torch.float32, "cpu")
+
+
+def test_random_values_follow_the_plain_definition(monkeypatch):
+    """The package's numpy generator against the element-at-a-time copy of its definition,
+    bit for bit; a tensor made in several chunks equals the one made at once; the stream of
+    a tensor does not depend on the other tensors."""
+    import torch
+    from plain import philox_normal_plain as Q
+    from gguf2bin_b200.weights import normal_values, random_tensor, random_init
+    for seed, tensor, n in ((0, 0, 9), (77, 5, 1003), (2 ** 40 + 3, 290, 64)):
+        z = normal_values(n, seed, tensor)
+        ref = np.array([Q.standard_normal(seed, tensor, i) for i in range(n)], np.float32)
+        assert np.array_equal(z.view(np.uint32), ref.view(np.uint32))
+    assert np.array_equal(normal_values(40, 3, 1, first=8), normal_values(48, 3, 1)[8:])
+    e_m, e_s = Expected((7, 13)), Expected((19,), init="scale")
+    m = random_tensor(e_m, 5, 2, torch.bfloat16, 0.02, 0.1)
+    s = random_tensor(e_s, 5, 3, torch.float32, 0.02, 0.1)
+    bits = m.view(torch.int16).numpy().astype(np.uint16).reshape(-1)
+    assert [int(b) for b in bits] == [Q.to_bfloat16_bits(Q.value(5, 2, i, "matrix", 0.02)) for i in range(91)]
+    assert [float(v) for v in s] == [float(Q.value(5, 3, i, "scale", 0.1)) for i in range(19)]
+    monkeypatch.setattr(random_init, "_CHUNK", 16)
+    assert torch.equal(random_tensor(e_m, 5, 2, torch.bfloat16, 0.02, 0.1), m)
+    big = normal_values(400_000, 1, 0)
+    assert abs(big.mean()) < 0.01 and abs(big.std() - 1) < 0.01
+    assert abs((big ** 4).mean() / big.var() ** 2 - 3) < 0.05 and np.abs(big).max() > 4
