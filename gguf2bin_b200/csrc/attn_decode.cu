@@ -328,12 +328,13 @@ extern "C" int g2b_attn_decode(const void *q, void *out, const void *cache, cons
   const int n_chunks = (max_kv_len + CHUNK_KEYS - 1) / CHUNK_KEYS;
   if (n_chunks <= 0) G2B_REFUSE("attn_decode: max_kv_len %d", max_kv_len);
   const int smem = WARPS * 2 * PANEL_BYTES;
-  static bool configured = false;
-  if (!configured) {
+  static G2bPerDevice configured;
+  const int cfg_dev = g2b_current_device();
+  if (cfg_dev < 0 || !configured.value[cfg_dev]) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) G2B_REFUSE("attn_decode: shared memory of %d bytes refused: %s", smem, cudaGetErrorString(e));
-    configured = true;
+    if (cfg_dev >= 0) configured.value[cfg_dev] = 1;
   }
   dim3 grid(n_chunks, nkv * head_tiles, T);
   g2b_launch(attn_decode_kernel, dim3(grid), dim3(WARPS * 32), smem, stream, 

@@ -19,15 +19,21 @@
  * moment its code is loaded there until the process exits.  The call allocates nothing:
  * no cudaMalloc, cudaFree or allocating library routine, torch's included.
  *
- * Limits.  T * n_heads * ceil(max_kv_len / 256) * (head_dim + 2) * 4 bytes must not exceed
- * G2B_NOALLOC_SCRATCH_BYTES (for 16 heads of 128 that is 8 tokens at up to 64k keys, or
- * 64 tokens at up to 3,840 keys); larger requests are refused with a message naming the
- * limit, and nothing is launched.
+ * Limits.  With C = g2b_attn_decode_chunk_keys() (the keys one thread block takes: 256 in
+ * the object as shipped, 128 in a build with -DATTN_DECODE_PAGES=2),
+ * T * n_heads * ceil(max_kv_len / C) * (head_dim + 2) * 4 bytes must not exceed
+ * G2B_NOALLOC_SCRATCH_BYTES.  For 16 heads of 128 and C = 256 that is 8 tokens at up to
+ * 64,512 keys, or 64 tokens at up to 7,936 keys.  Larger requests are refused with a
+ * message naming the limit, and nothing is launched.
  *
- * First call.  The first call on a device looks up the array's device address
+ * What the caller guarantees (neither entry point can check it, the positions being on
+ * the device): every tok_pos[t] < max_kv_len <= P * 64.  A position at or beyond
+ * max_kv_len would make the merge pass read partial results of a neighbouring head.
+ *
+ * First call.  The first call on each device looks up the array's device address
  * (cudaGetSymbolAddress, with that device current) and sets the kernel's shared-memory
- * attribute; make that first call during set-up, before any stream capture begins on that
- * device.  Later calls only launch.
+ * attribute for that device; make that first call during set-up, before any stream
+ * capture begins on that device.  Later calls on that device only launch.
  *
  * Sharing.  All calls in the process share the one array per device, and it keeps the
  * last call's contents.  Nothing in it has to start at zero: every partial that the

@@ -210,12 +210,13 @@ extern "C" int g2b_attn_prefill(const void *q, void *out, const void *cache, con
   if (nkv <= 0 || nh % nkv) G2B_REFUSE("attn_prefill: %d heads are not a multiple of %d kv heads", nh, nkv);
   if (nh > 65535) G2B_REFUSE("attn_prefill: %d heads", nh);
   const int smem = 2 * 2 * PANEL_BYTES;
-  static bool configured = false;
-  if (!configured) {
+  static G2bPerDevice configured;
+  const int cfg_dev = g2b_current_device();
+  if (cfg_dev < 0 || !configured.value[cfg_dev]) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) G2B_REFUSE("attn_prefill: shared memory of %d bytes refused: %s", smem, cudaGetErrorString(e));
-    configured = true;
+    if (cfg_dev >= 0) configured.value[cfg_dev] = 1;
   }
   dim3 grid(n_tiles, nh);
   g2b_launch(attn_prefill_kernel, dim3(grid), dim3(WARPS * 32), smem, stream, 

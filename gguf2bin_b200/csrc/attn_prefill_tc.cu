@@ -159,7 +159,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int n_pages = last_page - first_page + 1;
 
   if (warp == SOFTMAX_WARPS) {
-    if (lane == 0) {
+    if (lane == 0 && PRODUCER_RUNS) {
       mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
       for (int sub = 0; sub < SUBS; ++sub)
@@ -435,9 +435,10 @@ extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, 
   if (rc) G2B_REFUSE("attn_prefill_tc: tensor map of q failed (%d)", rc);
   rc = get_map(&mkv, cache, n_cache_pages * 2 * nkv * PAGE, HD, HD, PAGE);
   if (rc) G2B_REFUSE("attn_prefill_tc: tensor map of the cache failed (%d)", rc);
-  static bool configured = false;
-  static int n_sms = 0;
-  if (!configured) {
+  static G2bPerDevice configured;                      // holds the device's SM count once it is set up
+  const int cfg_dev = g2b_current_device();
+  int n_sms = cfg_dev >= 0 ? configured.value[cfg_dev] : 0;
+  if (n_sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
@@ -445,7 +446,7 @@ extern "C" int g2b_attn_prefill_tc(const void *q, void *out, const void *cache, 
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
     if (e != cudaSuccess) G2B_REFUSE("attn_prefill_tc: shared memory: %s", cudaGetErrorString(e));
     cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    configured = true;
+    if (cfg_dev >= 0) configured.value[cfg_dev] = n_sms;
   }
   g2b_launch(attn_prefill_tc_kernel, dim3((unsigned)n_tiles * nh), dim3(THREADS), SMEM_TOTAL, stream, mq, mkv,
              (bf16 *)out, (const int4 *)tiles, page_table, P, nh, nkv, window, scale * LOG2E, n_sms, status);

@@ -80,6 +80,18 @@ static inline void g2b_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   g2b_launch_cluster(kernel, grid, block, smem, stream, 1u, args...);
 }
 
+// What a launcher has to do once per DEVICE (cudaFuncSetAttribute holds for the device that
+// is current when it is called, not for the process): `static G2bPerDevice done;` and
+//   const int dev = g2b_current_device();
+//   if (dev < 0 || !done.value[dev]) { ...set attributes...; if (dev >= 0) done.value[dev] = 1; }
+// Two threads that meet in a device's first call both set the attributes; that is harmless.
+constexpr int G2B_MAX_DEVICES = 64;
+struct G2bPerDevice { int value[G2B_MAX_DEVICES] = {}; };
+static inline int g2b_current_device() {
+  int d = -1;
+  return (cudaGetDevice(&d) == cudaSuccess && d >= 0 && d < G2B_MAX_DEVICES) ? d : -1;
+}
+
 // element type codes used by the launchers
 enum { G2B_F32 = 0, G2B_BF16 = 1 };
 

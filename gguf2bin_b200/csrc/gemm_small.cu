@@ -533,12 +533,13 @@ static int launch_whole_depth(const void *A, const void *W, void *C, int M, int 
   const unsigned grid = (unsigned)(n_tiles * SPLIT);
 #define G2B_LAUNCH(E)                                                                            \
   do {                                                                                           \
-    static int configured = 0;                                                                   \
-    if (configured < smem) {                                                                     \
+    static G2bPerDevice configured;                                                              \
+    const int cfg_dev = g2b_current_device();                                                    \
+    if (cfg_dev < 0 || configured.value[cfg_dev] < smem) {                                       \
       cudaError_t e = cudaFuncSetAttribute(gemm_small_whole_kernel<MT, E, DEPTH_WHOLE, SPLIT>,       \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem);   \
       if (e != cudaSuccess) G2B_REFUSE("gemm_small: shared memory: %s", cudaGetErrorString(e));  \
-      configured = smem;                                                                         \
+      if (cfg_dev >= 0) configured.value[cfg_dev] = smem;                                        \
     }                                                                                            \
     g2b_launch_cluster(gemm_small_whole_kernel<MT, E, DEPTH_WHOLE, SPLIT>, dim3(grid),           \
                        dim3(WARPS * 32), smem, stream, (unsigned)SPLIT, (const bf16 *)A,         \
@@ -576,12 +577,13 @@ static int launch_mt(const void *A, const void *W, void *C, int M, int N, int K,
   const unsigned grid = (unsigned)((N + 15) / 16);
 #define G2B_LAUNCH(E)                                                                            \
   do {                                                                                           \
-    static bool configured = false;                                                              \
-    if (!configured) {                                                                           \
+    static G2bPerDevice configured;                                                              \
+    const int cfg_dev = g2b_current_device();                                                    \
+    if (cfg_dev < 0 || !configured.value[cfg_dev]) {                                             \
       cudaError_t e = cudaFuncSetAttribute(gemm_small_kernel<MT, E>,                             \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem);   \
       if (e != cudaSuccess) G2B_REFUSE("gemm_small: shared memory: %s", cudaGetErrorString(e));  \
-      configured = true;                                                                         \
+      if (cfg_dev >= 0) configured.value[cfg_dev] = 1;                                           \
     }                                                                                            \
     g2b_launch(gemm_small_kernel<MT, E>, dim3(grid), dim3(WARPS * 32), smem, stream,                                 \
         (const bf16 *)A, (const bf16 *)W, C, M, N, K, lda, ldw, ldc);                            \
@@ -623,12 +625,13 @@ static int launch_stream(const void *A, const void *W, void *C, int M, int N, in
   if (epi < EPI_STORE_BF16 || epi > EPI_SWIGLU_BF16) G2B_REFUSE("gemm_small: unknown epilogue %d", epi);
   constexpr int CB = StreamCfg<MT>::CB;
   const int smem = (int)StreamCfg<MT>::TOTAL;
-  static bool configured = false;
-  if (!configured) {
+  static G2bPerDevice configured;
+  const int cfg_dev = g2b_current_device();
+  if (cfg_dev < 0 || !configured.value[cfg_dev]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_small_stream_kernel<MT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) G2B_REFUSE("gemm_small: shared memory: %s", cudaGetErrorString(e));
-    configured = true;
+    if (cfg_dev >= 0) configured.value[cfg_dev] = 1;
   }
   const int n_tiles = (N + 15) / 16, nkb = (K + KB - 1) / KB;
   const int n_chunks = (nkb + CB - 1) / CB, kbc = (nkb + n_chunks - 1) / n_chunks;

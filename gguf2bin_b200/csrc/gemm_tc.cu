@@ -178,7 +178,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   pdl_wait();                  // barriers and tensor memory are set up; now the inputs are needed
 
   if (warp == 4) {
-    if (lane == 0) {
+    if (lane == 0 && PRODUCER_RUNS) {
       for (int kb = 0; kb < nkb; ++kb) {
         const int s = kb % STAGES;
         if (kb >= STAGES && !mbar_wait(empty0 + 8 * s, ((kb / STAGES) - 1) & 1)) {
@@ -382,7 +382,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   pdl_wait();
 
   if (warp == 4) {
-    if (lane == 0) {
+    if (lane == 0 && PRODUCER_RUNS) {
       uint32_t g = 0;                                // k-blocks loaded so far, over all tiles
       bool ok = true;
       TDECL(0); TDECL(1);
@@ -553,7 +553,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   pdl_wait();
 
   if (warp == 4) {
-    if (lane == 0) {
+    if (lane == 0 && PRODUCER_RUNS) {
       const uint32_t leader_full0 = map_to_cta(full0, 0);
       uint32_t g = 0;                                // k-blocks loaded so far, over all tiles
       bool ok = true;
@@ -716,7 +716,7 @@ gemm_tc_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
   TSTAMP(0);
   bool have_acc = true;        // epilogue warps: the accumulator is complete
   if (warp == 4) {
-    if (lane == 0) {
+    if (lane == 0 && PRODUCER_RUNS) {
       for (int i = 0; i < n_loc; ++i) {
         const int kb = kb_lo + (i + rot) % n_loc, s = i % STAGES;
         if (i >= STAGES && !mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1)) {
@@ -916,13 +916,14 @@ static int make_map_c(CUtensorMap *map, const void *base, int rows, int cols, in
 template <int BN, int STAGES, int EPI>
 static int launch(const CUtensorMap &ma, const CUtensorMap &mw, void *C, int M, int N, int K, int ldc,
                   int *status, cudaStream_t stream) {
-  static bool configured = false;
+  static G2bPerDevice configured;
   const int smem = Smem<BN, STAGES>::TOTAL;
-  if (!configured) {
+  const int cfg_dev = g2b_current_device();
+  if (cfg_dev < 0 || !configured.value[cfg_dev]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, EPI>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) G2B_REFUSE("gemm_tc: shared memory of %d bytes refused: %s", smem, cudaGetErrorString(e));
-    configured = true;
+    if (cfg_dev >= 0) configured.value[cfg_dev] = 1;
   }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) G2B_REFUSE("gemm_tc: M=%d is too large for one launch", M);
@@ -943,13 +944,14 @@ static int sm_count() {
 template <int BN, int STAGES, int EPI>
 static int launch_persistent(const CUtensorMap &ma, const CUtensorMap &mw, void *C, int M, int N, int K, int ldc,
                              int *status, cudaStream_t stream) {
-  static bool configured = false;
+  static G2bPerDevice configured;
   const int smem = SmemP<BN, STAGES>::TOTAL;
-  if (!configured) {
+  const int cfg_dev = g2b_current_device();
+  if (cfg_dev < 0 || !configured.value[cfg_dev]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES, EPI>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) G2B_REFUSE("gemm_tc: shared memory of %d bytes refused: %s", smem, cudaGetErrorString(e));
-    configured = true;
+    if (cfg_dev >= 0) configured.value[cfg_dev] = 1;
   }
   const long long tiles = (long long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   if (tiles > 0x7fffffffLL) G2B_REFUSE("gemm_tc: %lld tiles", tiles);
@@ -970,13 +972,14 @@ static int launch_persistent(const CUtensorMap &ma, const CUtensorMap &mw, void 
 template <int BN, int STAGES, int EPI>
 static int launch_pair(const CUtensorMap &ma, const CUtensorMap &mw, void *C, int M, int N, int K, int ldc,
                        int *status, cudaStream_t stream) {
-  static bool configured = false;
+  static G2bPerDevice configured;
   const int smem = SmemPair<BN, STAGES>::TOTAL;
-  if (!configured) {
+  const int cfg_dev = g2b_current_device();
+  if (cfg_dev < 0 || !configured.value[cfg_dev]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<BN, STAGES, EPI>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) G2B_REFUSE("gemm_tc: shared memory of %d bytes refused: %s", smem, cudaGetErrorString(e));
-    configured = true;
+    if (cfg_dev >= 0) configured.value[cfg_dev] = 1;
   }
   const long long tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
   if (tiles > 0x7fffffffLL) G2B_REFUSE("gemm_tc: %lld tiles", tiles);
@@ -999,13 +1002,14 @@ static int launch_pair(const CUtensorMap &ma, const CUtensorMap &mw, void *C, in
 template <int BNB, int STAGES, int EPI>
 static int launch_wstream(const void *A, const void *W, void *C, int M, int N, int K, int lda, int ldw, int ldc,
                           int want_splits, int *status, cudaStream_t stream) {
-  static bool configured = false;
+  static G2bPerDevice configured;
   using S = SmemWS<BNB, STAGES>;
-  if (!configured) {
+  const int cfg_dev = g2b_current_device();
+  if (cfg_dev < 0 || !configured.value[cfg_dev]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_wstream_kernel<BNB, STAGES, EPI>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (e != cudaSuccess) G2B_REFUSE("gemm_tc: shared memory of %d bytes refused: %s", S::TOTAL, cudaGetErrorString(e));
-    configured = true;
+    if (cfg_dev >= 0) configured.value[cfg_dev] = 1;
   }
   CUtensorMap mw, ma;
   int rc = make_map(&mw, W, N, K, ldw, BM);

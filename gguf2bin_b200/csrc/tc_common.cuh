@@ -13,7 +13,22 @@
 
 namespace tc {
 
-constexpr uint32_t SPIN_LIMIT = 1u << 22;   // polls of a barrier before a wait gives up
+// Polls of a barrier before a wait gives up.  Two switches exist for one purpose, a test of
+// the give-up path that harms nothing: -DG2B_SPIN_LIMIT=n shortens the limit, and
+// -DG2B_TEST_NO_PRODUCER makes the copy-issuing role of every kernel issue nothing, so that
+// no copy is ever in flight and every other role's first wait runs out, records its code in
+// the status word, frees the tensor memory and returns.  Neither is set in the objects that
+// the library uses.
+#ifdef G2B_SPIN_LIMIT
+constexpr uint32_t SPIN_LIMIT = G2B_SPIN_LIMIT;
+#else
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+#endif
+#ifdef G2B_TEST_NO_PRODUCER
+constexpr bool PRODUCER_RUNS = false;
+#else
+constexpr bool PRODUCER_RUNS = true;
+#endif
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) {
   return (uint32_t)__cvta_generic_to_shared(p);

@@ -117,7 +117,7 @@ class DecodeRunner:
             with torch.cuda.graph(g):
                 self._launch()
             self.launches_per_step = kernels.launch_count() - before
-            self.engine.graph_captures += 1
+            self.engine.decode_graph_captures += 1
             if ws.generation == generation:
                 self._graph, self._graph_generation = g, generation
                 g.replay()

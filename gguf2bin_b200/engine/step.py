@@ -65,7 +65,8 @@ class Engine:
         self._graphs: "OrderedDict[tuple, tuple]" = OrderedDict()    # shape -> (graph, generation, logits)
         self._seen: "OrderedDict[tuple, int]" = OrderedDict()        # shapes run plainly so far
         self.decode_runners: "OrderedDict[tuple, object]" = OrderedDict()
-        self.graph_captures = 0      # CUDA graphs captured so far (prompt shapes and decode shapes)
+        self.step_graph_captures = 0       # CUDA graphs captured so far: of prompt-step shapes,
+        self.decode_graph_captures = 0     # and of decode shapes (engine/decode.py)
 
     # ---- sequences -----------------------------------------------------------
     def open_sequence(self) -> Sequence:
@@ -73,6 +74,10 @@ class Engine:
 
     def close_sequence(self, seq: Sequence) -> None:
         self.cache.close_sequence(seq)
+
+    @property
+    def graph_captures(self) -> int:
+        return self.step_graph_captures + self.decode_graph_captures
 
     def check(self) -> None:
         """Raises ``KernelError`` if a kernel launched so far reported that one of its bounded
@@ -216,7 +221,7 @@ class Engine:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx, self.cache, want_rows, n_want)
-            self.graph_captures += 1
+            self.step_graph_captures += 1
             if self.workspace.generation == generation:
                 self._graphs[key] = (graph, generation, logits)
                 while len(self._graphs) > self.GRAPHS_KEPT:

@@ -72,14 +72,15 @@ def _tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
             and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def _gemm_tc(a, w, out, epi, bn: int = 0, stages: int = 0, persistent=False) -> None:
+def _gemm_tc(a, w, out, epi, bn: int = 0, stages: int = 0, persistent=False, defines=()) -> None:
     """bn = 0 lets the launcher pick the tile shape from the sizes.  persistent: one CTA per SM
     walks over the tiles with two accumulators (shapes (128, 6) and (256, 4)); persistent = 2:
     pairs of CTAs on 256 x 256 tiles (shapes (256, 6) and (256, 4)); persistent = 3: at most 128
-    rows, 128 rows of W per CTA and K split over a cluster (bn and stages are not used)."""
+    rows, 128 rows of W per CTA and K split over a cluster (bn and stages are not used).
+    ``defines``: another build of the source (the tests' build whose waits run out)."""
     f = _fn("gemm_tc.cu", "g2b_gemm_tc",
             [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_int, c_int, c_void_p, c_void_p])
+             c_int, c_int, c_void_p, c_void_p], defines=tuple(defines))
     _call(f, _ptr(a), _ptr(w), _ptr(out), a.shape[0], w.shape[0], a.shape[1], a.stride(0),
           w.stride(0), out.stride(0), epi, bn, stages, int(persistent),
           _ptr(_status_word(a.device)), _stream())
@@ -202,12 +203,14 @@ USE_TC_ATTENTION = True      # prompt attention on tcgen05 (else the mma.sync ke
 
 
 def attn_prefill_tc(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-                    scale) -> None:
-    """Prompt attention on the tcgen05 tensor cores over the step's 128-row query tiles."""
+                    scale, defines=()) -> None:
+    """Prompt attention on the tcgen05 tensor cores over the step's 128-row query tiles.
+    ``defines``: another build of the source (the tests' build whose waits run out)."""
     from ctypes import c_longlong
     f = _fn("attn_prefill_tc.cu", "g2b_attn_prefill_tc",
             [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p], defines=(f"HD={head_dim}",))
+             c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+            defines=(f"HD={head_dim}",) + tuple(defines))
     _call(f, _ptr(q), _ptr(out), _ptr(cache_pages), cache_pages.shape[0], _ptr(ctx.attn_tiles_wide),
           ctx.n_attn_tiles_wide, _ptr(ctx.page_table), ctx.page_table.shape[1], q.shape[0], n_heads,
           n_kv_heads, head_dim, page_size, window, scale, _ptr(_status_word(q.device)), _stream())

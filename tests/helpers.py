@@ -3,6 +3,7 @@ plain implementation's logits, and the comparison rules."""
 from __future__ import annotations
 
 import functools
+import os
 import tempfile
 from pathlib import Path
 
@@ -72,17 +73,45 @@ def plain_logits(name: str, storage: str, tokens) -> np.ndarray:
     return _plain_cache[key]
 
 
+# bfloat16 bounds, set from what was measured over every comparison of the GPU suite
+# (G2B_ERROR_REPORT): the worst max |diff| was 0.0093 of max |logit| in the models of the
+# architecture (0.0139 in a toy model whose head scales the logits by nine) and the worst rms
+# diff 0.0082 of the logits' rms, medians 0.0052 and 0.0049.  The bounds are two to three
+# times the worst seen, relative to the logits themselves (no floor): a systematic error of
+# one bfloat16 rounding of the logit scale shows in the rms bound before it shows in the max.
+BF16_MAX_REL = 0.028
+BF16_RMS_REL = 0.016
+F32_REL = 1e-5
+
+
 def tolerance(dtype: str, ref: np.ndarray) -> float:
-    """float32: 1e-5 of the logit scale (the plain implementation itself is within 5e-7
-    of the reference's C).  bfloat16: activations between kernels carry 8 bits, 2^-8
-    relative per rounding; eight roundings' worth of the logit scale."""
-    scale = max(1.0, float(np.abs(ref).max()))
-    return (1e-5 if dtype == "float32" else 8 * 2.0 ** -8) * scale
+    """The bound on max |diff|.  float32: 1e-5 of the logit scale (the plain implementation
+    itself is within 5e-7 of the reference's C; the worst seen here is 3e-6).  bfloat16:
+    ``BF16_MAX_REL`` of the largest logit."""
+    top = float(np.abs(ref).max())
+    return F32_REL * max(1.0, top) if dtype == "float32" else BF16_MAX_REL * max(top, 1e-3)
+
+
+def _report(what: str, dtype: str, got: np.ndarray, ref: np.ndarray) -> None:
+    """With G2B_ERROR_REPORT=<file> every comparison appends a line: what, dtype, max |diff|,
+    rms diff, max |ref|, rms ref, rows, rows whose argmax agrees (as the reference's
+    tools/kvtest.c:26-47 reports max abs delta, rmse and argmax agreement)."""
+    path = os.environ.get("G2B_ERROR_REPORT")
+    if not path:
+        return
+    d = (got - ref).astype(np.float64)
+    rows = got.reshape(-1, got.shape[-1])
+    agree = int((rows.argmax(-1) == ref.reshape(rows.shape).argmax(-1)).sum())
+    with open(path, "a") as f:
+        f.write(f"{what}\t{dtype}\t{np.abs(d).max():.4e}\t{np.sqrt((d ** 2).mean()):.4e}\t"
+                f"{np.abs(ref).max():.4e}\t{np.sqrt((ref.astype(np.float64) ** 2).mean()):.4e}\t"
+                f"{rows.shape[0]}\t{agree}\n")
 
 
 def assert_close(got: np.ndarray, ref: np.ndarray, dtype: str, what: str) -> None:
     assert got.shape == ref.shape, f"{what}: shape {got.shape} vs {ref.shape}"
     assert np.isfinite(got).all(), f"{what}: non-finite logits"
+    _report(what, dtype, got, ref)
     err = np.abs(got - ref)
     tol = tolerance(dtype, ref)
     if err.max() > tol:
@@ -90,3 +119,14 @@ def assert_close(got: np.ndarray, ref: np.ndarray, dtype: str, what: str) -> Non
         first_bad = int(np.nonzero(err.max(axis=-1) > tol)[0][0]) if err.ndim == 2 else -1
         raise AssertionError(f"{what}: max |diff| {err.max():.3e} > {tol:.3e} at {pos}; first "
                              f"row over tolerance: {first_bad}")
+    # the three figures the reference's own comparison tool reports (tools/kvtest.c:26-47):
+    # max abs difference (above), rms difference, and agreement of the argmax
+    rms_err = float(np.sqrt((err.astype(np.float64) ** 2).mean()))
+    rms_ref = float(np.sqrt((ref.astype(np.float64) ** 2).mean()))
+    rms_tol = (F32_REL if dtype == "float32" else BF16_RMS_REL) * max(rms_ref, 1e-3)
+    assert rms_err <= rms_tol, f"{what}: rms diff {rms_err:.3e} > {rms_tol:.3e} (rms of the logits {rms_ref:.3e})"
+    if got.ndim == 2:
+        top2 = np.sort(ref, axis=-1)[:, -2:]
+        clear = (top2[:, 1] - top2[:, 0]) > 2 * err.max(axis=-1)        # the row's own error cannot flip these
+        wrong = np.nonzero(clear & (got.argmax(-1) != ref.argmax(-1)))[0]
+        assert len(wrong) == 0, f"{what}: argmax differs in rows {wrong[:5].tolist()}"

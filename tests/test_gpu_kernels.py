@@ -272,6 +272,52 @@ def test_attn_decode(nh, nkv, hd, window, fine):
                                    err_msg=f"sequence of {l} keys")
 
 
+def last_row_attention(q_row, K, V, nh, window):
+    """The last token's row of ``P.causal_attention`` (same formula: src/l5_model.c:518, 559-577,
+    softmax src/l3_math.c:52-56), computed alone so that thousands of keys stay quick."""
+    l, nkv, hd = K.shape
+    group, lo = nh // nkv, (0 if window <= 0 else max(0, l - window))
+    out = np.zeros((nh, hd), np.float32)
+    for h in range(nh):
+        s = (K[lo:, h // group] @ q_row[h]) * (np.float32(1) / np.sqrt(np.float32(hd)))
+        e = np.exp(s - s.max())
+        out[h] = (e / e.sum(dtype=np.float32)) @ V[lo:, h // group]
+    return out
+
+
+@pytest.mark.parametrize("fine", [False, True])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(16, 8, 128, 0), (8, 2, 64, 0), (16, 8, 128, 3000)])
+def test_attn_decode_long_and_wide(nh, nkv, hd, window, fine):
+    """Twenty sequences of up to 4,100 keys (17 chunks of 256, 33 of 128): the merge of many
+    chunks by four warps, chunk counts that are and are not multiples of four, a window that
+    drops whole chunks.  A planted key far back takes most of one sequence's attention."""
+    from types import SimpleNamespace
+    from gguf2bin_b200 import kernels_bf16
+    from gguf2bin_b200.engine.workspace import Workspace
+    ps = 64
+    lens = [4100, 4096, 4095, 3073, 2049, 2048, 1500, 1281, 1024, 1023, 777, 513, 512, 300, 129, 64, 17, 1, 3584, 2817]
+    cache, table, Ks, Vs = make_paged(len(lens), lens, nkv, hd, ps, torch.bfloat16, seed=140)
+    T = len(lens)
+    q = rnd(T, nh * hd, dtype=torch.bfloat16, seed=141)
+    Ks[0][1300] = (q[0].view(nh, hd)[0] * 0.5)[None, :].expand(nkv, hd)       # in chunk 5 of 17
+    cache[int(table[0, 1300 // ps]), 0, :, 1300 % ps] = Ks[0][1300]
+    out = torch.empty_like(q)
+    ctx = SimpleNamespace(tok_pos=torch.tensor([l - 1 for l in lens], dtype=torch.int32, device=DEV),
+                          tok_seq=torch.arange(T, dtype=torch.int32, device=DEV), page_table=table,
+                          max_kv_len=table.shape[1] * ps, workspace=Workspace(DEV), all_single=True)
+    kernels_bf16.attn_decode(q, out, cache, ctx, nh, nkv, hd, ps, window, 1 / math.sqrt(hd), fine=fine)
+    got = out.float().cpu().numpy().reshape(T, nh, hd)
+    for b, l in enumerate(lens):
+        ref = last_row_attention(q[b].float().cpu().numpy().reshape(nh, hd), Ks[b].float().cpu().numpy(),
+                                 Vs[b].float().cpu().numpy(), nh, window)
+        np.testing.assert_allclose(got[b], ref, atol=2.0 ** -7 * max(1, np.abs(ref).max()), rtol=0,
+                                   err_msg=f"sequence of {l} keys")
+    small = last_row_attention(q[0].float().cpu().numpy().reshape(nh, hd), Ks[0].float().cpu().numpy()[:300],
+                               Vs[0].float().cpu().numpy()[:300], nh, 0)
+    assert window or np.abs(got[0][0] - Vs[0][1300, 0].float().cpu().numpy()).max() < \
+        np.abs(small[0] - Vs[0][1300, 0].float().cpu().numpy()).max(), "the planted key does not stand out"
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 48, 64), (8, 1024, 2048), (3, 200, 264), (16, 96, 1032),
                                    (33, 1000, 520), (64, 311, 96),
                                    # many tiles per CTA: groups of 1, 2, 4, 8 tiles, one and several chunks of K,

@@ -52,11 +52,18 @@ def test_layer_sizes(name, dtype):
         kernels_bf16.check_status()
 
 
-@pytest.mark.parametrize("name,n_requests", [("8b", 12), ("14b", 40)])
+SIZES["0.6b-small-vocab"] = dict(SIZES["0.6b"], vocab_size=1000)
+
+
+@pytest.mark.parametrize("name,n_requests", [("8b", 12), ("14b", 40), ("0.6b-small-vocab", 12),
+                                             ("0.6b-small-vocab", 24), ("0.6b-small-vocab", 40),
+                                             ("0.6b-small-vocab", 64)])
 def test_layer_sizes_in_a_wider_batch(name, n_requests):
-    """The same at 12 and 40 sequences: from 9 rows on the products of these widths run on the
-    kernel that splits K over a cluster (32 and 64 rows of activations per CTA).  Short
-    prompts, so that the plain implementation stays quick."""
+    """The same at 12 to 64 sequences: from 9 rows on the products of the larger widths run on
+    the kernel that splits K over a cluster (32 and 64 rows of activations per CTA), and from
+    17 rows on so do most products of the small model's layers (K = 1,024 and 3,072), which
+    is the route the benchmark's batch of 64 takes.  Short prompts, so that the plain
+    implementation stays quick."""
     from gguf2bin_b200.engine import Engine, Model, StepEntry
     from gguf2bin_b200.weights import write_random_model
     from gguf2bin_b200 import kernels_bf16

@@ -11,7 +11,7 @@ from helpers import TINY, assert_close, model_folder, plain_logits, random_token
 pytestmark = pytest.mark.gpu
 
 CASES = [("a", "float32"), ("b", "float32"), ("a", "bfloat16"), ("b", "bfloat16"),
-         ("c", "float32"), ("c", "bfloat16"), ("d", "bfloat16")]
+         ("c", "float32"), ("c", "bfloat16"), ("d", "bfloat16"), ("d", "float32")]
 LENGTHS = {"a": [60, 7, 33, 64, 1, 41], "b": [100, 5, 11, 2, 77, 128, 64],
            "c": [130, 40, 257, 64, 3], "d": [200, 65, 31, 129]}
 

@@ -98,7 +98,8 @@ def test_a_far_key_stands_out(dtype):
     toks[-1] = A                                         # the query that looks for it
     ref = P.forward(cfg2, W2, toks, np.float32)
     base = P.forward(cfg2, W2, toks[:37] + [10] + toks[38:], np.float32)
-    tol = (1e-5 if dtype == "float32" else 8 * 2.0 ** -8) * max(1.0, np.abs(ref).max())
+    from helpers import tolerance
+    tol = tolerance(dtype, ref)
     assert np.abs(ref[-1] - base[-1]).max() > 3 * tol, \
         "the construction does not make the far key matter"
     eng = Engine(Model.from_folder(folder, dtype=dtype), max_tokens=1024)
@@ -126,6 +127,39 @@ def test_page_edges_and_slot_reuse(dtype):
         eng.close_sequence(seq)
         ref = plain_logits("c", storage, toks)[plen - 1:]
         assert_close(np.concatenate(got), ref, dtype, f"prompt of {plen}")
+
+
+@pytest.mark.parametrize("name,dtype", [("b", "float32"), ("b", "bfloat16"), ("d", "float32"), ("d", "bfloat16")])
+def test_mixed_steps(name, dtype):
+    """Steps whose sequences are at different stages: while X decodes one token, Y brings a
+    whole prompt of 70 tokens and Z continues a prompt that was cut at a page edge (64 tokens
+    in, 30 more now); then X and Y decode while Z brings its last piece.  Logits of every
+    place against the plain implementation of each sequence whole."""
+    from gguf2bin_b200.engine import StepEntry
+    storage = "float32" if dtype == "float32" else "bfloat16"
+    X, Y, Z = random_tokens(name, 24, 61), random_tokens(name, 73, 62), random_tokens(name, 99, 63)
+    eng = make_engine(name, dtype)
+    sx, sy, sz = (eng.open_sequence() for _ in range(3))
+    got = {"x": [], "y": [], "z": []}
+
+    def run(parts):
+        """parts: (key, sequence, tokens); every place is wanted."""
+        out = eng.step([StepEntry(s, t, range(len(t))) for _, s, t in parts]).cpu().numpy()
+        o = 0
+        for key, _, t in parts:
+            got[key].append(out[o:o + len(t)])
+            o += len(t)
+
+    run([("x", sx, X[:20]), ("z", sz, Z[:64])])                         # two prompts, Z's cut at the page edge
+    run([("x", sx, X[20:21]), ("y", sy, Y[:70]), ("z", sz, Z[64:94])])  # decode + fresh prompt + continuation
+    run([("z", sz, Z[94:99]), ("x", sx, X[21:22]), ("y", sy, Y[70:71])])
+    run([("y", sy, Y[71:72]), ("x", sx, X[22:23])])
+    run([("x", sx, X[23:24]), ("y", sy, Y[72:73])])
+    for key, toks in (("x", X), ("y", Y), ("z", Z)):
+        assert_close(np.concatenate(got[key]), plain_logits(name, storage, toks), dtype,
+                     f"{name}/{dtype} sequence {key}")
+    for s in (sx, sy, sz):
+        eng.close_sequence(s)
 
 
 def test_padding_rows_change_nothing():
