@@ -45,7 +45,8 @@ extern "C" int g2b_embed_rows(const void *table, int table_dtype, const int *ids
 }
 
 // ---------------------------------------------------------------------------
-// rmsnorm over rows of the 32-bit stream; rows == nullptr means rows 0..n_rows-1
+// rmsnorm over rows of the 32-bit stream; rows == nullptr means rows 0..n_rows-1;
+// w == nullptr means no per-channel weight (it was multiplied into the next matrix)
 // ---------------------------------------------------------------------------
 template <typename TO>
 __global__ void rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ w,
@@ -64,7 +65,7 @@ __global__ void rmsnorm_kernel(const float *__restrict__ x, const float *__restr
   ss = block_sum(ss, scratch);
   const float inv = 1.f / sqrtf(ss / (float)H + eps);
   TO *o = out + (size_t)r * H;
-  for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = from_f32<TO>((w[j] * xr[j]) * inv);
+  for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = from_f32<TO>(((w ? w[j] : 1.f) * xr[j]) * inv);
 }
 
 __device__ __forceinline__ void store4(float *p, float a, float b, float c, float d) {
@@ -101,7 +102,8 @@ rmsnorm_rows_kernel(const float *__restrict__ x, const float *__restrict__ w,
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int k = lane * 4 + 128 * i;
-      g[i] = k < H ? *reinterpret_cast<const float4 *>(w + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+      g[i] = !w ? make_float4(1.f, 1.f, 1.f, 1.f)
+                : (k < H ? *reinterpret_cast<const float4 *>(w + k) : make_float4(0.f, 0.f, 0.f, 0.f));
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -143,7 +145,7 @@ rmsnorm_rows_kernel(const float *__restrict__ x, const float *__restrict__ w,
       const int k = k0 + 128 * i;
       if (k < H) {
         v[i] = *reinterpret_cast<const float4 *>(xr + k);
-        g[i] = *reinterpret_cast<const float4 *>(w + k);
+        g[i] = w ? *reinterpret_cast<const float4 *>(w + k) : make_float4(1.f, 1.f, 1.f, 1.f);
       }
     }
 #pragma unroll
@@ -177,7 +179,8 @@ rmsnorm_block_kernel(const float *__restrict__ x, const float *__restrict__ w,
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int k = threadIdx.x * 4 + 1024 * i;
-    g[i] = k < H ? *reinterpret_cast<const float4 *>(w + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+    g[i] = !w ? make_float4(1.f, 1.f, 1.f, 1.f)
+              : (k < H ? *reinterpret_cast<const float4 *>(w + k) : make_float4(0.f, 0.f, 0.f, 0.f));
   }
   float ss = 0.f;
 #pragma unroll

@@ -172,11 +172,22 @@ gemm_small_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W, void *
 // their partial tiles in their own shared memory and the first CTA of the cluster adds them
 // in rank order through distributed shared memory.  Narrow outputs (N = 1024 means only 64
 // tiles) fill the GPU this way, and the order of the sum still depends on K and N only.
-template <int MT, int EPI, int DEPTH_WHOLE, int SPLIT>
+//
+// NORMED: A is not bfloat16 activations but the float residual stream, and the product is that
+// of its RMS-normalised rows, norm(x) . W^T with norm(x) = x / sqrt(mean(x^2) + eps) (the norm's
+// per-channel weight was multiplied into W's columns when the weights were bound).  The row's
+// factor is a scalar, so it is applied to the accumulators: while a warp stages a row (rounded
+// to bfloat16 for the tensor cores) it sums the squares of the float values; the epilogue
+// multiplies each output by its row's 1 / sqrt(sum / K + eps).  Against a norm kernel of its own
+// this repeats the sum in every CTA (a few thousand additions, from the L2) but neither
+// normalises nor stores anything twice, and the step has one dependent launch less.
+template <int MT, int EPI, int DEPTH_WHOLE, int SPLIT, bool NORMED = false>
 __global__ void __launch_bounds__(WARPS * 32, DEPTH_WHOLE == 4 ? 3 : 2)
-gemm_small_whole_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W,
-                        void *__restrict__ Cv, int M, int N, int K, int lda, int ldw, int ldc) {
+gemm_small_whole_kernel(const void *__restrict__ Av, const bf16 *__restrict__ W,
+                        void *__restrict__ Cv, int M, int N, int K, int lda, int ldw, int ldc, float eps) {
+  static_assert(!NORMED || SPLIT == 1, "the normalised product is not split over a cluster");
   pdl_launch();
+  const bf16 *A = reinterpret_cast<const bf16 *>(Av);
   constexpr int MROWS = MT * 8;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -191,6 +202,7 @@ gemm_small_whole_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W,
   bf16 *xs = reinterpret_cast<bf16 *>(smem_raw);          // [MROWS][xrow]
   float *red = reinterpret_cast<float *>(smem_raw + (((size_t)MROWS * xrow * sizeof(bf16)) + 127) / 128 * 128);
   float *part = red + WARPS * 16 * MROWS;                 // [16][MROWS]: this CTA's partial tile
+  float *row_scale = part + 16 * MROWS;                   // [MROWS]: NORMED only
 
   const int n0 = (int)(blockIdx.x / SPLIT) * 16;
   const bf16 *w0 = W + (size_t)min(n0 + g, N - 1) * ldw;
@@ -218,6 +230,24 @@ gemm_small_whole_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W,
     bf16 *dst = xs + (size_t)r * xrow;
     if (r >= M) {
       for (int k = lane * 8; k < xrow; k += 256) *reinterpret_cast<uint4 *>(dst + k) = make_uint4(0, 0, 0, 0);
+      if (NORMED && lane == 0) row_scale[r] = 0.f;
+      continue;
+    }
+    if (NORMED) {
+      // the row of the float stream: K a multiple of 8, so a lane takes 8 values at a time
+      const float *x32 = reinterpret_cast<const float *>(Av) + (size_t)r * lda;
+      float ss = 0.f;
+      for (int k = lane * 8; k < K; k += 256) {
+        const float4 a = *reinterpret_cast<const float4 *>(x32 + k);
+        const float4 b = *reinterpret_cast<const float4 *>(x32 + k + 4);
+        ss = fmaf(a.x, a.x, ss); ss = fmaf(a.y, a.y, ss); ss = fmaf(a.z, a.z, ss); ss = fmaf(a.w, a.w, ss);
+        ss = fmaf(b.x, b.x, ss); ss = fmaf(b.y, b.y, ss); ss = fmaf(b.z, b.z, ss); ss = fmaf(b.w, b.w, ss);
+        *reinterpret_cast<uint4 *>(dst + k) = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w),
+                                                         pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+      }
+      for (int k = K + lane * 4; k < xrow; k += 128) *reinterpret_cast<uint2 *>(dst + k) = make_uint2(0, 0);
+      ss = warp_sum(ss);
+      if (lane == 0) row_scale[r] = 1.f / sqrtf(ss / (float)K + eps);
       continue;
     }
     const bf16 *x = A + (size_t)r * lda + k_lo;
@@ -292,6 +322,7 @@ gemm_small_whole_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W,
         gate += red[((size_t)w * 16 + r) * MROWS + m];
         up += red[((size_t)w * 16 + 8 + r) * MROWS + m];
       }
+      if (NORMED) { gate *= row_scale[m]; up *= row_scale[m]; }
       const int col = (n0 >> 1) + r;
       if (m < M && n0 + 8 + r < N)
         ((bf16 *)Cv)[(size_t)m * ldc + col] = __float2bfloat16_rn((gate / (1.f + expf(-gate))) * up);
@@ -302,6 +333,7 @@ gemm_small_whole_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W,
       float v = 0.f;
 #pragma unroll
       for (int w = 0; w < WARPS; ++w) v += red[((size_t)w * 16 + r) * MROWS + m];
+      if (NORMED) v *= row_scale[m];
       const int n = n0 + r;
       if (m < M && n < N) {
         const size_t o = (size_t)m * ldc + n;
@@ -504,7 +536,7 @@ gemm_small_stream_kernel(const bf16 *__restrict__ A, const bf16 *__restrict__ W,
 static size_t whole_smem(int mrows, int K, int split = 1) {
   const int nkb = (K + KB - 1) / KB, per = (nkb + split - 1) / split;
   const size_t stage = ((size_t)mrows * (per * KB + XPAD) * sizeof(bf16) + 127) / 128 * 128;
-  const size_t red = (size_t)(WARPS + 1) * 16 * mrows * sizeof(float);
+  const size_t red = ((size_t)(WARPS + 1) * 16 * mrows + mrows) * sizeof(float);    // + a factor per row
   const size_t need = stage + red;
   return need <= 200 * 1024 ? need : 0;
 }
@@ -542,8 +574,8 @@ static int launch_whole_depth(const void *A, const void *W, void *C, int M, int 
       if (cfg_dev >= 0) configured.value[cfg_dev] = smem;                                        \
     }                                                                                            \
     g2b_launch_cluster(gemm_small_whole_kernel<MT, E, DEPTH_WHOLE, SPLIT>, dim3(grid),           \
-                       dim3(WARPS * 32), smem, stream, (unsigned)SPLIT, (const bf16 *)A,         \
-                       (const bf16 *)W, C, M, N, K, lda, ldw, ldc);                              \
+                       dim3(WARPS * 32), smem, stream, (unsigned)SPLIT, (const void *)A,         \
+                       (const bf16 *)W, C, M, N, K, lda, ldw, ldc, 0.f);                         \
   } while (0)
   switch (epi) {
     case EPI_STORE_BF16: G2B_LAUNCH(EPI_STORE_BF16); break;
@@ -597,6 +629,36 @@ static int launch_mt(const void *A, const void *W, void *C, int M, int N, int K,
   }
 #undef G2B_LAUNCH
   return g2b_check_launch("gemm_small");
+}
+
+// The product of RMS-normalised rows of the float stream (see NORMED above): whole-A kernel,
+// one CTA per tile.
+template <int MT, int DEPTH_WHOLE>
+static int launch_normed(const float *X, const void *W, void *C, int M, int N, int K, int ldx, int ldw,
+                         int ldc, int epi, float eps, cudaStream_t stream) {
+  const int smem = (int)whole_smem(MT * 8, K, 1);
+  const unsigned grid = (unsigned)((N + 15) / 16);
+#define G2B_LAUNCH(E)                                                                            \
+  do {                                                                                           \
+    static G2bPerDevice configured;                                                              \
+    const int cfg_dev = g2b_current_device();                                                    \
+    if (cfg_dev < 0 || configured.value[cfg_dev] < smem) {                                       \
+      cudaError_t e = cudaFuncSetAttribute(gemm_small_whole_kernel<MT, E, DEPTH_WHOLE, 1, true>, \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem);   \
+      if (e != cudaSuccess) G2B_REFUSE("gemm_small: shared memory: %s", cudaGetErrorString(e));  \
+      if (cfg_dev >= 0) configured.value[cfg_dev] = smem;                                        \
+    }                                                                                            \
+    g2b_launch(gemm_small_whole_kernel<MT, E, DEPTH_WHOLE, 1, true>, dim3(grid), dim3(WARPS * 32), smem, \
+               stream, (const void *)X, (const bf16 *)W, C, M, N, K, ldx, ldw, ldc, eps);        \
+  } while (0)
+  switch (epi) {
+    case EPI_STORE_BF16: G2B_LAUNCH(EPI_STORE_BF16); break;
+    case EPI_STORE_F32: G2B_LAUNCH(EPI_STORE_F32); break;
+    case EPI_SWIGLU_BF16: G2B_LAUNCH(EPI_SWIGLU_BF16); break;
+    default: G2B_REFUSE("gemm_small_normed: epilogue %d (store or SiLU gate only)", epi);
+  }
+#undef G2B_LAUNCH
+  return g2b_check_launch("gemm_small_normed");
 }
 
 static int sm_count() {
@@ -665,4 +727,30 @@ extern "C" int g2b_gemm_small(const void *A, const void *W, void *C, int M, int 
   if (M <= 16) return launch_mt<2>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
   if (M <= 32) return launch_mt<4>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
   return launch_mt<8>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+}
+
+// Whether g2b_gemm_small_normed takes the case: up to 16 rows, the whole of A in shared memory,
+// an output wide enough that K is not split over a cluster, and not the shapes that the
+// many-tiles kernel is faster for.
+extern "C" int g2b_gemm_small_normed_takes(int M, int N, int K) {
+  if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K % 8) return 0;
+  if (stream_case(M, N, K)) return 0;
+  return whole_smem(M <= 8 ? 8 : 16, K, 1) != 0 && final_split(N, K) == 1;
+}
+
+// C = norm(X) . W^T for X [M, K] float (the residual stream), norm(x) = x / sqrt(mean(x^2) + eps)
+// without a per-channel weight; W [N, K] bfloat16.  epi as g2b_gemm_small's, without 2.
+extern "C" int g2b_gemm_small_normed(const float *X, const void *W, void *C, int M, int N, int K, int ldx,
+                                     int ldw, int ldc, int epi, float eps, cudaStream_t stream) {
+  if (!g2b_gemm_small_normed_takes(M, N, K)) G2B_REFUSE("gemm_small_normed: M=%d N=%d K=%d is not taken", M, N, K);
+  if (ldx % 4 || ldw % 8) G2B_REFUSE("gemm_small_normed: row strides (%d, %d)", ldx, ldw);
+  if (((uintptr_t)X | (uintptr_t)W) & 15) G2B_REFUSE("gemm_small_normed: operands must be 16-byte aligned");
+  if (epi == EPI_SWIGLU_BF16 && N % 16) G2B_REFUSE("gemm_small_normed: gated output needs N %% 16 == 0, N=%d", N);
+  const int nkb = (K + KB - 1) / KB;
+  if (M <= 8) {
+    if (nkb <= 4) return launch_normed<1, 4>(X, W, C, M, N, K, ldx, ldw, ldc, epi, eps, stream);
+    return launch_normed<1, 8>(X, W, C, M, N, K, ldx, ldw, ldc, epi, eps, stream);
+  }
+  if (nkb <= 4) return launch_normed<2, 4>(X, W, C, M, N, K, ldx, ldw, ldc, epi, eps, stream);
+  return launch_normed<2, 8>(X, W, C, M, N, K, ldx, ldw, ldc, epi, eps, stream);
 }

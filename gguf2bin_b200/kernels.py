@@ -113,10 +113,11 @@ def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> Non
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
             rows: Optional[torch.Tensor] = None) -> None:
-    """out[r] = (w * x[row_r]) / sqrt(mean(x[row_r]^2) + eps); x, w float32; statistics in
-    float32.  ``rows`` (int32) gathers rows of x; out has one row per gathered row."""
+    """out[r] = (w * x[row_r]) / sqrt(mean(x[row_r]^2) + eps); x, w float32 (w None: all
+    ones); statistics in float32.  ``rows`` (int32) gathers rows of x; out has one row per gathered row."""
     _need(x, torch.float32, "x")
-    _need(w, torch.float32, "norm weight")
+    if w is not None:                      # None: no per-channel weight
+        _need(w, torch.float32, "norm weight")
     if rows is not None:
         _need(rows, torch.int32, "rows")
     n_rows, H = out.shape
@@ -295,6 +296,15 @@ def attention(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size
             return
     attn_generic(q, out, cache_pages, ctx.tok_pos, ctx.tok_seq, ctx.page_table, n_heads,
                  n_kv_heads, head_dim, page_size, window, scale)
+
+
+def normed_product(x32, eps, w, out, gate_block=None) -> bool:
+    """out = rmsnorm_without_weight(x32) @ w.T (or its SiLU gate) in one kernel; False when no
+    kernel takes the case (the caller then runs the norm and the product one after the other)."""
+    if w.dtype == torch.bfloat16 and (gate_block is None or gate_block == 8):
+        from . import kernels_bf16
+        return kernels_bf16.normed_product(x32, eps, w, out, gate_block is not None)
+    return False
 
 
 def gate_up_fused(h, w_gate_up, mid, block) -> bool:

@@ -37,6 +37,38 @@ def _gemm_small(a, w, out, epi) -> None:
           w.stride(0), out.stride(0), epi, _stream())
 
 
+def normed_product(x32: torch.Tensor, eps: float, w: torch.Tensor, out: torch.Tensor, gated: bool) -> bool:
+    """out = rmsnorm(x32) @ w.T for the float stream x32 [M, K] with a weightless RMS norm
+    (x / sqrt(mean(x^2) + eps)) computed inside the few-row product: the row's factor scales
+    the accumulators.  ``gated``: w is a fused gate/up matrix (rows alternating 8 / 8) and out
+    gets silu(gate) * up.  False when the case is not taken (more than 16 rows, a K that is
+    split over a cluster or streamed in chunks)."""
+    M, K = x32.shape
+    N = w.shape[0]
+    if (x32.dtype != torch.float32 or w.dtype != torch.bfloat16 or x32.stride(1) != 1 or w.stride(1) != 1
+            or out.stride(1) != 1 or x32.stride(0) % 4 or w.stride(0) % 8
+            or x32.data_ptr() % 16 or w.data_ptr() % 16):
+        return False
+    if gated:
+        if out.dtype != torch.bfloat16 or N % 16:
+            return False
+        epi = EPI_SWIGLU_BF16
+    elif out.dtype == torch.bfloat16:
+        epi = EPI_STORE_BF16
+    elif out.dtype == torch.float32:
+        epi = EPI_STORE_F32
+    else:
+        return False
+    takes = _fn("gemm_small.cu", "g2b_gemm_small_normed_takes", [c_int, c_int, c_int])
+    if not takes(M, N, K):
+        return False
+    f = _fn("gemm_small.cu", "g2b_gemm_small_normed",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _call(f, _ptr(x32), _ptr(w), _ptr(out), M, N, K, x32.stride(0), w.stride(0), out.stride(0), epi,
+          float(eps), _stream())
+    return True
+
+
 _status: dict = {}
 
 

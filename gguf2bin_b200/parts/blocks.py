@@ -35,6 +35,11 @@ class PreNormBlock:
         self.ffn_norm.bind(tensors[self.names["ffn_norm"]])
         self.mixer.bind(tensors)
         self.feed_forward.bind(tensors)
+        # a part that starts from the stream (``forward_from_stream``) may take the weight of
+        # the norm in front of it into its first matrix; the norm is then a plain division
+        for part, norm in ((self.mixer, self.mixer_norm), (self.feed_forward, self.ffn_norm)):
+            if hasattr(part, "forward_from_stream") and hasattr(part, "absorb_norm_weight"):
+                part.absorb_norm_weight(norm)
 
     def cache_need(self):
         return self.mixer.cache_need()

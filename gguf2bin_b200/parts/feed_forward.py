@@ -47,6 +47,15 @@ class SwiGLU:
     def weights(self):
         return (self.w_gate_up, self.w_down)
 
+    def absorb_norm_weight(self, norm) -> bool:
+        """As ``GQAAttention.absorb_norm_weight``, into the columns of the gate/up matrix."""
+        if self.dtype != torch.bfloat16 or self.w_gate_up.dtype != torch.bfloat16 or self.block != 8 \
+                or not hasattr(norm, "give_up_weight"):
+            return False
+        w = norm.give_up_weight()
+        self.w_gate_up = (self.w_gate_up.float() * w.to(self.w_gate_up.device)[None, :]).to(torch.bfloat16).contiguous()
+        return True
+
     def notices(self) -> list:
         return (kernels.product_notices("feed-forward gate/up", self.w_gate_up, self.dtype)
                 + kernels.product_notices("feed-forward down", self.w_down, self.dtype))

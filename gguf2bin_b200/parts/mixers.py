@@ -84,6 +84,17 @@ class GQAAttention:
     def weights(self):
         return [t for t in (self.w_qkv, self.w_o, self.q_norm_w, self.k_norm_w) if t is not None]
 
+    def absorb_norm_weight(self, norm) -> bool:
+        """Takes the weight of the norm in front of this mixer into the columns of the q/k/v
+        matrix, when that is what makes the decode step shorter: bfloat16 compute and a
+        bfloat16 matrix (the product then normalises its own rows, see ``parts/fused.py``).
+        The matrix is rounded to bfloat16 once more; the 32-bit path keeps the formula's order."""
+        if self.dtype != torch.bfloat16 or self.w_qkv.dtype != torch.bfloat16 or not hasattr(norm, "give_up_weight"):
+            return False
+        w = norm.give_up_weight()
+        self.w_qkv = (self.w_qkv.float() * w.to(self.w_qkv.device)[None, :]).to(torch.bfloat16).contiguous()
+        return True
+
     def notices(self) -> list:
         from ..cache.storage import PAGE_SIZE
         return (kernels.product_notices("attention q/k/v", self.w_qkv, self.dtype)

@@ -26,7 +26,20 @@ class RMSNorm:
         self.weight = weight.to(torch.float32).contiguous()      # exact widening
 
     def weights(self):
-        return (self.weight,)
+        return (self.weight,) if self.weight is not None else ()
+
+    # ---- the weight moved into the matrix that follows ----------------------------------
+    def give_up_weight(self) -> torch.Tensor:
+        """Hands the per-channel weight to a part that multiplies it into the columns of its
+        first matrix (W' = W . diag(w), so that W' . x/rms(x) = W . (w * x/rms(x))); from
+        then on this norm only divides by the root mean square."""
+        w, self.weight = self.weight, None
+        return w
+
+    def plain_rms_eps(self):
+        """eps when this norm is x / sqrt(mean(x^2) + eps) and nothing else (its weight was
+        given up), which is what the products that normalise their own input take; else None."""
+        return self.eps if self.weight is None else None
 
     def forward(self, x32: torch.Tensor, out: torch.Tensor, rows=None) -> None:
         kernels.rmsnorm(x32, self.weight, self.eps, out, rows)

@@ -272,6 +272,44 @@ def test_attn_decode(nh, nkv, hd, window, fine):
                                    err_msg=f"sequence of {l} keys")
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 1024), (8, 6144, 1024), (13, 1008, 520), (16, 2048 + 16, 1280),
+                                   (5, 311 * 16, 72), (3, 48, 2056)])
+def test_normed_product(M, N, K):
+    """The few-row product that normalises its own rows: norm(x) . W^T with the row's
+    1 / sqrt(mean(x^2) + eps) applied to the accumulators, plain and with the SiLU gate,
+    against float64; rows of very different size (the factor is per row)."""
+    from gguf2bin_b200 import kernels, kernels_bf16
+    x = rnd(M, K, seed=70) * torch.logspace(-2, 2, M, device=DEV)[:, None]
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=71)
+    eps = 1e-5
+    xb = x.to(torch.bfloat16).double()                                  # what the tensor cores are fed
+    inv = 1 / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + eps)
+    ref = (xb @ w.double().T) * inv
+    tol = 1e-5 * math.sqrt(K) * max(1.0, ref.abs().max().item())
+    out = torch.full((M, N), 7.0, device=DEV)
+    assert kernels.normed_product(x, eps, w, out)
+    assert (out.double() - ref).abs().max().item() < tol
+    out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    assert kernels.normed_product(x, eps, w, out16)
+    assert (out16.double() - ref).abs().max().item() <= ref.abs().max().item() * 2.0 ** -8 + tol
+    I = N // 2
+    g = ref.view(M, I // 8, 2, 8)[:, :, 0].reshape(M, I)
+    u = ref.view(M, I // 8, 2, 8)[:, :, 1].reshape(M, I)
+    want = (g / (1 + torch.exp(-g))) * u
+    mid = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    assert kernels.normed_product(x, eps, w, mid, gate_block=8)
+    assert (mid.double() - want).abs().max().item() <= want.abs().max().item() * 2.0 ** -8 + tol
+    # and it is the norm kernel without a weight followed by the product, up to the rounding of the normed rows
+    h = torch.empty(M, K, dtype=torch.bfloat16, device=DEV)
+    kernels.rmsnorm(x, None, eps, h)
+    two = torch.empty(M, N, device=DEV)
+    kernels.linear(h, w, two)
+    assert (two.double() - ref).abs().max().item() <= 2.0 ** -7 * ref.abs().max().item() + tol
+    # cases that are left to the two kernels
+    assert not kernels.normed_product(rnd(17, K, seed=1), eps, w, torch.empty(17, N, device=DEV))
+    assert not kernels.normed_product(rnd(4, 4096, seed=1), eps, rnd(1024, 4096, dtype=torch.bfloat16), torch.empty(4, 1024, device=DEV))
+
+
 def last_row_attention(q_row, K, V, nh, window):
     """The last token's row of ``P.causal_attention`` (same formula: src/l5_model.c:518, 559-577,
     softmax src/l3_math.c:52-56), computed alone so that thousands of keys stay quick."""
