@@ -50,6 +50,13 @@ __device__ __forceinline__ uint32_t swz(int row, int piece) {
   return (uint32_t)(row * ROW_BYTES + ((piece ^ (row & 7)) << 4));
 }
 
+// a load that is neither cached in registers across the dependency line nor merged with another
+__device__ __forceinline__ int ld_volatile(const int *p) {
+  int v;
+  asm volatile("ld.volatile.global.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ void load_panel(uint32_t smem_panel, const bf16 *gpanel, int lane) {
   // PAGE * ROW_CHUNKS pieces, 32 lanes
 #pragma unroll
@@ -60,59 +67,20 @@ __device__ __forceinline__ void load_panel(uint32_t smem_panel, const bf16 *gpan
   }
 }
 
-__global__ void __launch_bounds__(WARPS * 32)
-attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
-                   const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
-                   const int *__restrict__ page_table, int P, int nh, int nkv, int window,
-                   float scale_log2, float *__restrict__ part_o, float2 *__restrict__ part_ml,
-                   int n_chunks) {
-  pdl_launch();
-  pdl_wait();
-  extern __shared__ __align__(128) unsigned char smem[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, c = lane & 3;
-  const int group = nh / nkv;
-  const int head_tiles = (group + 15) / 16;
-  const int chunk = blockIdx.x;
-  const int kvh = blockIdx.y / head_tiles, ht = blockIdx.y % head_tiles;
-  const int t = blockIdx.z;
-  const int pos = tok_pos[t], b = tok_seq[t];
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const int key_begin = chunk * CHUNK_KEYS;
-  if (key_begin > pos || key_begin + CHUNK_KEYS <= lo) return;     // no key of this chunk is seen
+// What a warp accumulates over its pages: the unnormalised output of the tile's 16 query rows
+// (lane (g, c) holds rows g and g + 8, columns 8n + 2c, 8n + 2c + 1), their running maxima
+// (log2 domain) and sums.
+struct Partial {
+  float o[DTILES][4];
+  float m[2], l[2];
+};
 
-  unsigned char *my = smem + warp * 2 * PANEL_BYTES;
-  const uint32_t k_smem = smem_u32(my), v_smem = smem_u32(my + PANEL_BYTES);
-
-  // the pages of this warp: key_begin/PAGE + warp, + WARPS, ... that hold a visible key
-  const int first_page = key_begin / PAGE;
-  int pages[PAGES_PER_CTA / WARPS];
-  int n_pages = 0;
-#pragma unroll
-  for (int i = 0; i < PAGES_PER_CTA / WARPS; ++i) {
-    const int pg = first_page + warp + i * WARPS;
-    if (pg * PAGE <= pos && (pg + 1) * PAGE > lo) pages[n_pages++] = pg;
-  }
-  const size_t panel_elems = (size_t)PAGE * HD;
-  auto k_panel = [&](int pg) {
-    const int phys = page_table[(size_t)b * P + pg];
-    return cache + (((size_t)phys * 2 + 0) * nkv + kvh) * panel_elems;
-  };
-  auto v_panel = [&](int pg) {
-    const int phys = page_table[(size_t)b * P + pg];
-    return cache + (((size_t)phys * 2 + 1) * nkv + kvh) * panel_elems;
-  };
-
-  if (n_pages > 0) load_panel(k_smem, k_panel(pages[0]), lane);
-  cp_async_commit();
-  if (n_pages > 0) load_panel(v_smem, v_panel(pages[0]), lane);
-  cp_async_commit();
-
-  // query rows of this tile: head = kvh*group + ht*16 + row, as A fragments
+// The query rows of a tile as A fragments: head = kvh * group + ht * 16 + row.
+__device__ __forceinline__ void load_q_tile(uint32_t (&qa)[KSTEPS][4], const bf16 *__restrict__ q, int t,
+                                            int nh, int kvh, int group, int ht, int g, int c) {
   const int row0 = ht * 16 + g, row1 = row0 + 8;
   const bf16 *q0 = q + ((size_t)t * nh + (size_t)kvh * group + row0) * HD;
   const bf16 *q1 = q0 + 8 * HD;
-  uint32_t qa[KSTEPS][4];
 #pragma unroll
   for (int ks = 0; ks < KSTEPS; ++ks) {
     const int d = ks * 16 + 2 * c;
@@ -121,14 +89,22 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
     qa[ks][2] = row0 < group ? *reinterpret_cast<const uint32_t *>(q0 + d + 8) : 0u;
     qa[ks][3] = row1 < group ? *reinterpret_cast<const uint32_t *>(q1 + d + 8) : 0u;
   }
+}
 
-  float o[DTILES][4];
-#pragma unroll
-  for (int n = 0; n < DTILES; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-
+// One warp over the pages pg0, pg0 + stride, ... (n_pages of them, each holding a visible key):
+// K and V panels through the warp's two buffers; while it computes on K the V of the same page
+// is in flight, while it computes P.V the next K is.  The first K and V must have been issued
+// (one commit group each) before the call.
+template <typename PanelOf>
+__device__ __forceinline__ void attend_pages(Partial &acc, const uint32_t (&qa)[KSTEPS][4], uint32_t k_smem,
+                                             uint32_t v_smem, int pg0, int stride, int n_pages, int pos, int lo,
+                                             float scale_log2, int lane, PanelOf panel_of) {
+  const int g = lane >> 2, c = lane & 3;
+  (void)g;
+  float (&o)[DTILES][4] = acc.o;
+  float (&m)[2] = acc.m, (&l)[2] = acc.l;
   for (int i = 0; i < n_pages; ++i) {
-    const int key0 = pages[i] * PAGE;
+    const int key0 = (pg0 + i * stride) * PAGE;
     cp_async_wait<1>();                    // this page's K has landed (its V may be in flight)
     __syncwarp();
     float s[PAGE / 8][4];
@@ -144,7 +120,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
       }
     }
     __syncwarp();                          // every lane is done reading K
-    if (i + 1 < n_pages) load_panel(k_smem, k_panel(pages[i + 1]), lane);
+    if (i + 1 < n_pages) load_panel(k_smem, panel_of(pg0 + (i + 1) * stride, 0), lane);
     cp_async_commit();
 
     // scale (log2 domain), mask, running maximum and sum
@@ -199,7 +175,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
       }
     }
     __syncwarp();
-    if (i + 1 < n_pages) load_panel(v_smem, v_panel(pages[i + 1]), lane);
+    if (i + 1 < n_pages) load_panel(v_smem, panel_of(pg0 + (i + 1) * stride, 1), lane);
     cp_async_commit();
   }
   cp_async_wait<0>();
@@ -208,11 +184,16 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
   }
+}
 
-  // merge the warps in order through shared memory (the panels are no longer needed)
-  __syncthreads();
-  float *xo = reinterpret_cast<float *>(smem);                 // [WARPS][32 lanes][DTILES*4 + 4]
+// The warps of a CTA merged into warp 0, in warp order, through shared memory `xo`
+// ([n_warps][32 lanes][DTILES * 4 + 4] floats; the panels are no longer needed).  Every thread
+// of the CTA calls it.
+__device__ __forceinline__ void merge_warps(Partial &acc, float *xo, int n_warps, int warp, int lane) {
+  float (&o)[DTILES][4] = acc.o;
+  float (&m)[2] = acc.m, (&l)[2] = acc.l;
   constexpr int PER_LANE = DTILES * 4 + 4;
+  __syncthreads();
   if (warp > 0) {
     float *dst = xo + ((size_t)warp * 32 + lane) * PER_LANE;
 #pragma unroll
@@ -224,8 +205,7 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
   }
   __syncthreads();
   if (warp == 0) {
-#pragma unroll
-    for (int w = 1; w < WARPS; ++w) {
+    for (int w = 1; w < n_warps; ++w) {
       const float *src = xo + ((size_t)w * 32 + lane) * PER_LANE;
       float a[2], bb[2];
 #pragma unroll
@@ -245,6 +225,93 @@ attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
         o[n][3] = o[n][3] * a[1] + src[n * 4 + 3] * bb[1];
       }
     }
+  }
+}
+
+__device__ __forceinline__ void clear_partial(Partial &acc) {
+#pragma unroll
+  for (int n = 0; n < DTILES; ++n) acc.o[n][0] = acc.o[n][1] = acc.o[n][2] = acc.o[n][3] = 0.f;
+  acc.m[0] = acc.m[1] = -INFINITY;
+  acc.l[0] = acc.l[1] = 0.f;
+}
+
+__global__ void __launch_bounds__(WARPS * 32)
+attn_decode_kernel(const bf16 *__restrict__ q, const bf16 *__restrict__ cache,
+                   const int *__restrict__ tok_pos, const int *__restrict__ tok_seq,
+                   const int *__restrict__ page_table, int P, int nh, int nkv, int window,
+                   float scale_log2, float *__restrict__ part_o, float2 *__restrict__ part_ml,
+                   int n_chunks) {
+  pdl_launch();
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int group = nh / nkv;
+  const int head_tiles = (group + 15) / 16;
+  const int chunk = blockIdx.x;
+  const int kvh = blockIdx.y / head_tiles, ht = blockIdx.y % head_tiles;
+  const int t = blockIdx.z;
+  const int key_begin = chunk * CHUNK_KEYS;
+  const int first_page = key_begin / PAGE;
+  unsigned char *my = smem + warp * 2 * PANEL_BYTES;
+  const uint32_t k_smem = smem_u32(my), v_smem = smem_u32(my + PANEL_BYTES);
+  const size_t panel_elems = (size_t)PAGE * HD;
+  // the batch's layout (which sequence, which pages) was copied to the device before the step's
+  // first kernel was launched, so it may be read above the dependency line
+  const int b = tok_seq[t];
+  auto panel_of = [&](int pg, int kv) {
+    const int phys = page_table[(size_t)b * P + pg];
+    return cache + (((size_t)phys * 2 + kv) * nkv + kvh) * panel_elems;
+  };
+
+  // Before the kernels in front of this one are done (they compute this token's query and
+  // write its key and value), the warp's first page can already be on its way if it is an OLD
+  // page: one that lies wholly below the token's position and was therefore completed by an
+  // earlier step.  The position itself is moved on the device by earlier kernels (one forward
+  // at the end of every step; one back when a step that was launched ahead is taken back), so
+  // what is read here is a hint: it may lag behind by any number of steps, which is harmless
+  // (whichever value is seen was written after every key below it), and it may be one too
+  // large while a take-back is still on its way, which the "- 1" allows for.  Not with a
+  // window, whose lower edge moves with the position.
+  const int hint = ld_volatile(tok_pos + t);
+  const bool early = window <= 0 && (first_page + warp + 1) * PAGE <= hint - 1;
+  if (early) {
+    load_panel(k_smem, panel_of(first_page + warp, 0), lane);
+    cp_async_commit();
+    load_panel(v_smem, panel_of(first_page + warp, 1), lane);
+    cp_async_commit();
+  }
+  pdl_wait();
+  const int pos = ld_volatile(tok_pos + t);
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  if (key_begin > pos || key_begin + CHUNK_KEYS <= lo) return;     // no key of this chunk is seen (then nothing was fetched early)
+
+  // the pages of this warp: key_begin/PAGE + warp, + WARPS, ... that hold a visible key (the
+  // visible pages of a chunk are a contiguous range)
+  int pg0 = 0, n_pages = 0;
+#pragma unroll
+  for (int i = 0; i < PAGES_PER_CTA / WARPS; ++i) {
+    const int pg = first_page + warp + i * WARPS;
+    if (pg * PAGE <= pos && (pg + 1) * PAGE > lo) {
+      if (n_pages == 0) pg0 = pg;
+      ++n_pages;
+    }
+  }
+  if (!early) {
+    if (n_pages > 0) load_panel(k_smem, panel_of(pg0, 0), lane);
+    cp_async_commit();
+    if (n_pages > 0) load_panel(v_smem, panel_of(pg0, 1), lane);
+    cp_async_commit();
+  }
+
+  uint32_t qa[KSTEPS][4];
+  load_q_tile(qa, q, t, nh, kvh, group, ht, g, c);
+  Partial acc;
+  clear_partial(acc);
+  attend_pages(acc, qa, k_smem, v_smem, pg0, WARPS, n_pages, pos, lo, scale_log2, lane, panel_of);
+  merge_warps(acc, reinterpret_cast<float *>(smem), WARPS, warp, lane);
+  if (warp == 0) {
+    float (&o)[DTILES][4] = acc.o;
+    float (&m)[2] = acc.m, (&l)[2] = acc.l;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int row = ht * 16 + g + 8 * r;
