@@ -259,7 +259,7 @@ def attn_prefill(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_s
           window, scale, _stream())
 
 
-DECODE_FINE_BELOW = 300       # CTAs of 256-key chunks below which the chunks are halved
+DECODE_FINE_BELOW = 200       # CTAs of 256-key chunks below which the chunks are halved (measured: two sequences)
 
 
 def attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
