@@ -379,6 +379,16 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const uint32_t tmem = *tmem_slot;
+  // the weights of the first ring (this CTA's first tile) are requested above the dependency
+  // line: they do not depend on the kernels in front; the rows of A follow below it
+  const int n_early = (int)blockIdx.x < n_tiles ? min(nkb, STAGES) : 0;
+  if (warp == 4 && lane == 0 && PRODUCER_RUNS) {
+    const int n0 = ((int)blockIdx.x / tiles_m) * BN;
+    for (int kb = 0; kb < n_early; ++kb) {
+      mbar_expect_tx(full0 + 8 * kb, S::STAGE_BYTES);
+      tma_load_2d(smem_addr(smem + kb * S::STAGE_BYTES) + S::A_BYTES, &map_w, kb * BK, n0, full0 + 8 * kb);
+    }
+  }
   pdl_wait();
 
   if (warp == 4) {
@@ -399,9 +409,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
           }
           TOCK(1, t_e);
           const uint32_t a_dst = smem_addr(smem + s * S::STAGE_BYTES);
-          mbar_expect_tx(full0 + 8 * s, S::STAGE_BYTES);
+          if ((int)g >= n_early) {                           // the first ring's weights are on their way
+            mbar_expect_tx(full0 + 8 * s, S::STAGE_BYTES);
+            tma_load_2d(a_dst + S::A_BYTES, &map_w, kb * BK, n0, full0 + 8 * s);
+          }
           tma_load_2d(a_dst, &map_a, kb * BK, m0, full0 + 8 * s);
-          tma_load_2d(a_dst + S::A_BYTES, &map_w, kb * BK, n0, full0 + 8 * s);
         }
       }
       TOCK(0, t_prod);
@@ -704,6 +716,17 @@ gemm_tc_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  // The weights do not depend on the kernels in front: the first ring of them is requested
+  // above the dependency line (a stage's barrier expects the stage's whole byte count; the
+  // rows of A follow below the line).
+  const int n_early = min(n_loc, STAGES);
+  if (warp == 4 && lane == 0 && PRODUCER_RUNS) {
+    for (int i = 0; i < n_early; ++i) {
+      const int kb = kb_lo + (i + rot) % n_loc;
+      mbar_expect_tx(full0 + 8 * i, S::STAGE_BYTES);
+      tma_load_2d(smem_addr(smem + i * S::STAGE_BYTES), &map_w, kb * BK, n0, full0 + 8 * i);
+    }
+  }
   pdl_wait();                  // barriers and tensor memory are set up; now the inputs are needed
 
 #ifdef G2B_GEMM_TIMING
@@ -724,8 +747,10 @@ gemm_tc_wstream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
           break;
         }
         const uint32_t w_dst = smem_addr(smem + s * S::STAGE_BYTES);
-        mbar_expect_tx(full0 + 8 * s, S::STAGE_BYTES);
-        tma_load_2d(w_dst, &map_w, kb * BK, n0, full0 + 8 * s);
+        if (i >= n_early) {                                  // the first ring's weights are on their way
+          mbar_expect_tx(full0 + 8 * s, S::STAGE_BYTES);
+          tma_load_2d(w_dst, &map_w, kb * BK, n0, full0 + 8 * s);
+        }
         tma_load_2d(w_dst + S::W_BYTES, &map_a, kb * BK, 0, full0 + 8 * s);
       }
     }
@@ -1017,11 +1042,36 @@ static int launch_wstream(const void *A, const void *W, void *C, int M, int N, i
   rc = make_map(&ma, A, M, K, lda, BNB);
   if (rc) return rc;
   const int tiles = (N + BM - 1) / BM, nkb = (K + BK - 1) / BK;
-  // parts of K: as many as keep every CTA on the GPU at once and give a part 4 blocks or more
+  // parts of K: as many (up to 4) as keep every CTA on the GPU at once and give a part 4 blocks
+  // or more; three where four would not fit (40 tiles: 120 CTAs instead of 80).  How many
+  // clusters of a size the GPU holds at once is asked of the runtime: clusters do not straddle
+  // the GPU's processing clusters, so it can be fewer than SMs / size.
+  static G2bPerDevice fit[5];                     // fit[s].value[device] = clusters of s CTAs at once (+1; 0 = not asked yet)
+  auto clusters_at_once = [&](int s) -> int {
+    if (cfg_dev >= 0 && fit[s].value[cfg_dev]) return fit[s].value[cfg_dev] - 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(s * sm_count()));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = S::TOTAL;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)s;
+    attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_wstream_kernel<BNB, STAGES, EPI>, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = sm_count() / s / 2;                      // a cautious guess
+    }
+    if (cfg_dev >= 0) fit[s].value[cfg_dev] = n + 1;
+    return n;
+  };
   int splits = 1;
-  while (splits < 4 && tiles * splits * 2 <= sm_count() && nkb / (splits * 2) >= 4) splits *= 2;
-  if (want_splits == 1 || want_splits == 2 || want_splits == 4) splits = want_splits;       // the caller's choice
-  while (splits > 1 && (splits - 1) * ((nkb + splits - 1) / splits) >= nkb) splits /= 2;   // no empty part
+  for (int s = 2; s <= 4; ++s)
+    if (nkb / s >= 4 && tiles <= clusters_at_once(s)) splits = s;
+  if (want_splits >= 1 && want_splits <= 4) splits = want_splits;                           // the caller's choice
+  while (splits > 1 && (splits - 1) * ((nkb + splits - 1) / splits) >= nkb) --splits;      // no empty part
   static_assert((2 * BNB + 8) * BM * 4 <= S::RING_BYTES, "the tile and the received ranges must fit the ring");
   g2b_launch_cluster(gemm_tc_wstream_kernel<BNB, STAGES, EPI>, dim3((unsigned)(tiles * splits)), dim3(THREADS),
                      S::TOTAL, stream, (unsigned)splits, mw, ma, C, M, N, K, ldc, splits, status);
@@ -1037,7 +1087,7 @@ static int launch_wstream(const void *A, const void *W, void *C, int M, int N, i
 // the GPU (the ring has to cover the latency of the copies by itself then).  persistent = 1:
 // the variant with one CTA per SM and two accumulators, shapes (128,6) and (256,4).  persistent
 // = 2: pairs of CTAs on 256 x 256 tiles, shapes (256,6) and (256,4).  persistent = 3 (at most
-// 128 rows; stages is ignored, bn = 1, 2 or 4 asks for that many parts of K, anything else lets
+// 128 rows; stages is ignored, bn = 1 to 4 asks for that many parts of K, anything else lets
 // the launcher choose): the weight-streaming kernel with K split over a cluster.
 extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, int K, int lda,
                            int ldw, int ldc, int epi, int bn, int stages, int persistent, int *status,
@@ -1055,9 +1105,14 @@ extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, 
   }
   if (persistent == 3) {                           // 17 to 128 rows: the weights stream, K split over a cluster
     if (M > 128) G2B_REFUSE("gemm_tc: the weight-streaming kernel takes at most 128 rows, got %d", M);
+    const bool crowded = (N + BM - 1) / BM > sm_count() && (bn < 1 || bn > 4);
 #define G2B_CASE(E) \
     if (epi == E) {                                                                                        \
+      /* more tiles than SMs (K is not split then): half the ring, so that two CTAs share an SM and */ \
+      /* the tiles of the second round stream beside those of the first instead of after them       */ \
+      if (M <= 32 && crowded) return launch_wstream<32, 4, E>(A, W, C, M, N, K, lda, ldw, ldc, bn, status, stream); \
       if (M <= 32) return launch_wstream<32, 9, E>(A, W, C, M, N, K, lda, ldw, ldc, bn, status, stream);   \
+      if (M <= 64 && crowded) return launch_wstream<64, 4, E>(A, W, C, M, N, K, lda, ldw, ldc, bn, status, stream); \
       if (M <= 64) return launch_wstream<64, 8, E>(A, W, C, M, N, K, lda, ldw, ldc, bn, status, stream);   \
       return launch_wstream<128, 6, E>(A, W, C, M, N, K, lda, ldw, ldc, bn, status, stream);               \
     }

@@ -490,11 +490,13 @@ def test_gemm_tc_pairs(M, N, K, bn, stages):
 
 
 @pytest.mark.parametrize("M,N,K", [(9, 4096, 2048), (17, 4096, 4096), (32, 2048 + 8, 2048), (33, 6144, 4096), (64, 4096, 12288),
-                                   (100, 2304, 2056), (128, 4096 + 24, 4096 + 8), (20, 130 * 8, 72)])
+                                   (100, 2304, 2056), (128, 4096 + 24, 4096 + 8), (20, 130 * 8, 72),
+                                   (64, 5120, 5120), (23, 5120 + 8, 1096)])
 def test_gemm_tc_weight_streaming(M, N, K):
     """17 to 128 rows against big weights: 128 rows of W per CTA with 32, 64 or 128 rows of A,
-    K in 1, 2 and 4 parts added in rank order through the cluster's shared memory, ragged
-    N and K, every epilogue; the same bits on every run."""
+    K in 1, 2, 3 and 4 parts added in rank order through the cluster's shared memory (three
+    where four would not fit the GPU at once: 40 and 48 tiles), ragged N and K, every epilogue;
+    the same bits on every run; and every number of parts asked for by hand."""
     from gguf2bin_b200 import kernels_bf16
     _check_gemm_tc(M, N, K, 0, 0, 3)
     a, w = rnd(M, K, dtype=torch.bfloat16, seed=80), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=81)
@@ -504,6 +506,11 @@ def test_gemm_tc_weight_streaming(M, N, K):
         kernels_bf16._gemm_tc(a, w, out, kernels_bf16.EPI_ACCUM_F32, 0, 0, 3)
         outs.append(out)
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    ref = a.double() @ w.double().T
+    for parts in (1, 2, 3, 4):
+        out = torch.zeros(M, N, device=DEV)
+        kernels_bf16._gemm_tc(a, w, out, kernels_bf16.EPI_STORE_F32, parts, 0, 3)
+        assert (out.double() - ref).abs().max().item() < 1e-5 * math.sqrt(K) * max(1.0, ref.abs().max().item()), parts
     kernels_bf16.check_status()
 
 
