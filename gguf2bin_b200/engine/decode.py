@@ -70,6 +70,13 @@ class DecodeRunner:
             page_table=self.page_table, page_size=engine.cache.page_size,
             workspace=engine.workspace, dtype=engine.model.dtype, q_lens=[1] * B,
             past_lens=[0] * B, slots=[0] * B, max_kv_len=P * engine.cache.page_size)
+        # what a session needs to talk to the host, kept here so that a new session of a known
+        # shape allocates nothing (pinned memory is slow to get)
+        self.pinned_in = torch.empty(B, dtype=torch.int32, pin_memory=True)
+        self.pinned_out = [torch.empty(B, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.out_ready = [torch.cuda.Event(), torch.cuda.Event()]
+        self.out_turn = 0
+        self.tokens_uploaded = torch.cuda.Event()
         self.owner: Optional["DecodeSession"] = None
         self.logits: Optional[torch.Tensor] = None
         self._graph: Optional[torch.cuda.CUDAGraph] = None
@@ -168,10 +175,6 @@ class DecodeSession:
         # a step launched ahead can be taken back only if all it stored is stored by position
         self._may_run_ahead = self._sample_in_graph and all(
             isinstance(g["need"], KVNeed) for g in engine.cache.groups.values())
-        self._pinned_in = torch.empty(B, dtype=torch.int32, pin_memory=True)
-        self._pinned_out = [torch.empty(B, dtype=torch.int32, pin_memory=True) for _ in range(2)]
-        self._out_ready = [torch.cuda.Event(), torch.cuda.Event()]
-        self._out_turn = 0
         self._ahead: Optional[list] = None      # tokens fed to the step launched ahead, if any
         self._since_check = 0
 
@@ -201,8 +204,11 @@ class DecodeSession:
     def set_tokens(self, tokens: Sequence[int]) -> None:
         """The tokens the next step feeds (host to device, from pinned memory)."""
         self._own_runner()
-        self._pinned_in.copy_(torch.tensor(list(tokens), dtype=torch.int32))
-        self.runner.tok_ids.copy_(self._pinned_in, non_blocking=True)
+        runner = self.runner
+        runner.tokens_uploaded.synchronize()       # the staging buffer's last copy is over
+        runner.pinned_in.numpy()[:] = tokens
+        runner.tok_ids.copy_(runner.pinned_in, non_blocking=True)
+        runner.tokens_uploaded.record()
 
     def run(self, recent=None) -> None:
         """One step: feeds ``tok_ids``, leaves the sampled tokens in ``tok_ids`` and the
@@ -226,18 +232,19 @@ class DecodeSession:
 
     def _send_back(self) -> int:
         """Starts the copy of the last step's tokens to the host; returns its turn."""
-        turn = self._out_turn
-        self._out_turn ^= 1
-        self._pinned_out[turn].copy_(self.runner.tok_ids, non_blocking=True)
-        self._out_ready[turn].record()
+        runner = self.runner
+        turn = runner.out_turn
+        runner.out_turn ^= 1
+        runner.pinned_out[turn].copy_(runner.tok_ids, non_blocking=True)
+        runner.out_ready[turn].record()
         return turn
 
     def _collect(self, turn: int) -> list:
-        self._out_ready[turn].synchronize()
+        self.runner.out_ready[turn].synchronize()
         self._since_check += 1
         if self._since_check >= self.CHECK_EVERY:
             self.check()
-        return self._pinned_out[turn].tolist()
+        return self.runner.pinned_out[turn].tolist()
 
     def check(self) -> None:
         """Reports a kernel that gave up a bounded wait (see ``Engine.check``).  Reading the
