@@ -3,7 +3,9 @@ to the reader that turns config.json into a ``ModelSpec``."""
 from __future__ import annotations
 
 import dataclasses
+import importlib
 import json
+import os
 from pathlib import Path
 from typing import Any, Callable, Mapping
 
@@ -21,7 +23,31 @@ def registered_architectures() -> list[str]:
     return sorted(_ARCHITECTURES)
 
 
+_plugins_loaded = False
+
+
+def load_plugins() -> None:
+    """Imports the modules named in ``GGUF2BIN_B200_PLUGINS`` (comma-separated, importable from
+    ``sys.path``), once.  A module adds an architecture, or kinds of parts, by calling the
+    ``register_*`` functions when it is imported; that is how a model that this package does not
+    know reaches every entry point (the Python API, the command line, ``bin/trace_run``) without a
+    change to the package's files."""
+    global _plugins_loaded
+    if _plugins_loaded:
+        return
+    _plugins_loaded = True
+    for name in os.environ.get("GGUF2BIN_B200_PLUGINS", "").split(","):
+        name = name.strip()
+        if not name:
+            continue
+        try:
+            importlib.import_module(name)
+        except ImportError as e:
+            raise ConfigError(f"GGUF2BIN_B200_PLUGINS: cannot import {name!r}: {e}") from None
+
+
 def model_spec_from_dict(d: Mapping[str, Any]) -> ModelSpec:
+    load_plugins()
     archs = d.get("architectures")
     if not archs or not isinstance(archs, (list, tuple)):
         raise ConfigError("config.json: 'architectures' is missing or empty; registered: "
