@@ -249,6 +249,8 @@ def main() -> int:
                     help="layer sizes: Qwen3-0.6B, or those of Qwen3-8B / 14B (default: the workload's)")
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                    help="length of the prompt of the prefill figure (decode workload; default 2048)")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -287,11 +289,11 @@ def main() -> int:
         start_ctx = a.context // 2
         steps = min(a.steps or 512, a.context - start_ctx - 1)
         decode_prompts = random_prompts(a.batch, start_ctx - a.warmup, vocab, 100)
-        prefill_prompts = random_prompts(1, PREFILL_TOKENS, vocab, 1)
+        prefill_prompts = random_prompts(1, a.prefill_tokens, vocab, 1)
         seq_len = a.context
         points_wanted = not a.no_points
         max_batch = max(64 if points_wanted else a.batch, a.batch)
-        max_tokens = max_batch * (a.context + 64)
+        max_tokens = max(max_batch * (a.context + 64), a.prefill_tokens + 64)
     elif a.workload == "ragged8":
         lengths = np.random.default_rng(2024).integers(128, 2049, a.batch).tolist()
         steps = a.steps or 256
