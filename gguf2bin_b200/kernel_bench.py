@@ -92,6 +92,15 @@ def decode(a) -> None:
     if b.want("qkv"):
         W = [bf(NQ + 2 * NK, H) for _ in range(L)]
         b.run("qkv", lambda: [kernels_bf16.linear_bf16(h, w, qkv, False) for w in W], L, W[0].numel() * 2)
+    if b.want("qkv_normed"):              # what a decode step of up to 16 rows runs: the norm inside the product
+        W = [bf(NQ + 2 * NK, H) for _ in range(L)]
+        if kernels.normed_product(x32, 1e-6, W[0], qkv):
+            b.run("qkv_normed", lambda: [kernels.normed_product(x32, 1e-6, w, qkv) for w in W], L, W[0].numel() * 2)
+    if b.want("gate_up_normed"):
+        W = [bf(2 * I, H) for _ in range(L)]
+        if kernels.normed_product(x32, 1e-6, W[0], mid, 8):
+            b.run("gate_up_normed", lambda: [kernels.normed_product(x32, 1e-6, w, mid, 8) for w in W], L,
+                  W[0].numel() * 2)
     if b.want("o_proj"):
         W = [bf(H, NQ) for _ in range(L)]
         b.run("o_proj", lambda: [kernels_bf16.linear_bf16(o, w, res, True) for w in W], L, W[0].numel() * 2)
