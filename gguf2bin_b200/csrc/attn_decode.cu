@@ -380,6 +380,11 @@ attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__
 
 // Scratch: part_o float [T*nh*n_chunks*HD], part_ml float2 [T*nh*n_chunks], with
 // n_chunks = ceil(max_kv_len / 256).  q, out [T, nh*HD] bfloat16.
+// With programmatic dependent launch on (g2b_set_pdl(1)) the kernel reads tok_pos once above
+// the dependency line, as a hint for which old pages it may fetch early.  A caller whose own
+// kernels move tok_pos while this one may already have started must keep to what the library
+// does: positions grow, and shrink by at most one (a step taken back) between two launches.
+// With ordinary launches (the default of a freshly loaded object) there is no such rule.
 extern "C" int g2b_attn_decode(const void *q, void *out, const void *cache, const int *tok_pos,
                                const int *tok_seq, const int *page_table, int P, int T, int nh,
                                int nkv, int hd, int page_size, int window, float scale,

@@ -29,6 +29,9 @@
  * What the caller guarantees (neither entry point can check it, the positions being on
  * the device): every tok_pos[t] < max_kv_len <= P * 64.  A position at or beyond
  * max_kv_len would make the merge pass read partial results of a neighbouring head.
+ * And only if the caller has switched programmatic dependent launch on (g2b_set_pdl(1);
+ * it is off in a freshly loaded object): kernels of the caller that change tok_pos while
+ * this one may already have started let a position grow, or shrink by at most one.
  *
  * First call.  The first call on each device looks up the array's device address
  * (cudaGetSymbolAddress, with that device current) and sets the kernel's shared-memory
