@@ -1,8 +1,9 @@
 """Generation through the Python entry point against the plain implementation."""
 import numpy as np
 import pytest
+import torch
 
-from helpers import TINY, model_folder, plain_model, random_tokens, tolerance
+from helpers import TINY, assert_close, model_folder, plain_logits as plain_logits_of, plain_model, random_tokens, tolerance
 from plain import philox_plain, qwen3_plain as P
 
 pytestmark = pytest.mark.gpu
@@ -251,3 +252,47 @@ def test_decode_graphs_are_kept_by_shape_not_by_call(llms):
     captured = eng.decode_graph_captures - before
     assert captured <= 4, f"{captured} graphs for a shrinking batch"
     assert eng.cache.table.slots.n_held == 0 and eng.cache.table.pages.n_held == 0
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_steps_taken_back_at_page_edges_leave_the_same_bits(llms, use_graph):
+    """Every step is followed by a step launched ahead that is then taken back, with sequences
+    whose positions cross a page edge meanwhile (the decode attention fetches old pages early,
+    on a hint of the position that a take-back moves down by one): the logits of every real
+    step equal, bit for bit, those of a session that never ran ahead."""
+    from gguf2bin_b200.engine import DecodeSession, StepEntry
+    from gguf2bin_b200.sampling import Sampler, SamplingParams
+    llm = llms("d", "bfloat16", max_tokens=1024)
+    eng = llm.engine
+    prompts = [random_tokens("d", n, 700 + n) for n in (61, 126, 190)]
+    fed = [random_tokens("d", 8, 900 + i) for i in range(3)]
+
+    def run(ahead: bool):
+        seqs = [eng.open_sequence() for _ in prompts]
+        for s, p in zip(seqs, prompts):
+            eng.cache.reserve(s, len(p) + 12)
+        eng.step([StepEntry(s, p, ()) for s, p in zip(seqs, prompts)])
+        session = DecodeSession(eng, seqs, Sampler(eng.cache.seq_state, eng.device), SamplingParams.plain(0.0),
+                                use_graph=use_graph, eager_steps=1)
+        out = []
+        for i in range(8):
+            session.set_tokens([f[i] for f in fed])
+            session.run()
+            out.append(session.logits.clone())
+            if ahead:                                  # a step nobody asked for, and its undoing
+                session.run()
+                session._ahead = session.read_tokens()
+                session.take_back()
+        lengths = [s.length for s in seqs]
+        for s in seqs:
+            eng.close_sequence(s)
+        return out, lengths
+
+    plain, n0 = run(False)
+    with_ahead, n1 = run(True)
+    assert n0 == n1 == [len(p) + 8 for p in prompts]
+    for i, (a, b) in enumerate(zip(plain, with_ahead)):
+        assert torch.equal(a, b), f"step {i}"
+    # and they are the plain implementation's logits
+    ref = plain_logits_of("d", "bfloat16", prompts[1] + fed[1])
+    assert_close(np.stack([x[1].cpu().numpy() for x in plain]), ref[len(prompts[1]):], "bfloat16", "sequence 1")
