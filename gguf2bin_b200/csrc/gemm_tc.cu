@@ -307,6 +307,21 @@ __device__ __forceinline__ void epilogue_tile_bulk(uint32_t tmem, unsigned char 
   }
 }
 
+// The order in which a persistent grid walks over the tiles of C.  Plainly down the rows of a
+// column of tiles and then on to the next column, every column of tiles reads all of A again;
+// that is free while A stays in the L2, and the kernel's whole traffic once A is larger than
+// the L2 (32,768 rows of width 5,120 are 335 MB: 136 columns of tiles would read 45 GB).  So
+// the rows of tiles are taken in groups of `group_m` whose slice of A fits the L2: within a
+// group down the rows, then the next column, and only then the next group.  Every tile is
+// still computed once, by one CTA (or pair), over the whole of K: the result is the same.
+__device__ __forceinline__ void tile_of(int t, int tiles_m, int tiles_n, int group_m, int &tm, int &tn) {
+  const int per_group = group_m * tiles_n;
+  const int grp = t / per_group, within = t - grp * per_group;
+  const int rows = min(group_m, tiles_m - grp * group_m);       // the last group may be shorter
+  tn = within / rows;
+  tm = grp * group_m + (within - tn * rows);
+}
+
 // ---- persistent variant -----------------------------------------------------------------
 // One CTA per SM walks over tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (tile t covers
 // rows 128 * (t % tiles_m), columns BN * (t / tiles_m): the CTAs that run at the same time
@@ -342,7 +357,7 @@ template <int BN, int STAGES> struct SmemP {
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                          const __grid_constant__ CUtensorMap map_c, int M, int N, int K,
+                          const __grid_constant__ CUtensorMap map_c, int M, int N, int K, int group_m,
                           int *__restrict__ status) {
   pdl_launch();
   extern __shared__ unsigned char smem_raw[];
@@ -356,8 +371,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nkb = (K + BK - 1) / BK;
-  const int tiles_m = (M + BM - 1) / BM;
-  const int n_tiles = tiles_m * ((N + BN - 1) / BN);
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -383,7 +398,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   // line: they do not depend on the kernels in front; the rows of A follow below it
   const int n_early = (int)blockIdx.x < n_tiles ? min(nkb, STAGES) : 0;
   if (warp == 4 && lane == 0 && PRODUCER_RUNS) {
-    const int n0 = ((int)blockIdx.x / tiles_m) * BN;
+    int tm, tn;
+    tile_of((int)blockIdx.x, tiles_m, tiles_n, group_m, tm, tn);
+    const int n0 = tn * BN;
     for (int kb = 0; kb < n_early; ++kb) {
       mbar_expect_tx(full0 + 8 * kb, S::STAGE_BYTES);
       tma_load_2d(smem_addr(smem + kb * S::STAGE_BYTES) + S::A_BYTES, &map_w, kb * BK, n0, full0 + 8 * kb);
@@ -398,7 +415,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       TDECL(0); TDECL(1);
       TICK(t_prod);
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-        const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+        int tm, tn;
+        tile_of(t, tiles_m, tiles_n, group_m, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
         for (int kb = 0; kb < nkb; ++kb, ++g) {
           const uint32_t s = g % STAGES;
           TICK(t_e);
@@ -475,7 +494,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       TOCK(7, t_af);
       TOCK(8, t_af - 1 + clock64());               // counts tiles (adds 1)
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+      int tm, tn;
+      tile_of(t, tiles_m, tiles_n, group_m, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
       epilogue_tile_bulk<BN, EPI>(tmem + buf * BN, stage, &map_c, m0, n0, M, N, warp, lane, box);
       // every load of this warp from the accumulator has completed (each is waited for)
       asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
@@ -524,7 +545,7 @@ enum { ST_PAIR_TIMEOUT = 4 };
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    const __grid_constant__ CUtensorMap map_c, int M, int N, int K,
+                    const __grid_constant__ CUtensorMap map_c, int M, int N, int K, int group_m,
                     int *__restrict__ status) {
   pdl_launch();
   extern __shared__ unsigned char smem_raw[];
@@ -542,8 +563,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
   const int nkb = (K + BK - 1) / BK;
-  const int tiles_m = (M + 2 * BM - 1) / (2 * BM);
-  const int n_tiles = tiles_m * ((N + BN - 1) / BN);
+  const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -570,8 +591,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t g = 0;                                // k-blocks loaded so far, over all tiles
       bool ok = true;
       for (int t = pair; t < n_tiles && ok; t += pairs) {
-        const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM;
-        const int n0 = (t / tiles_m) * BN + (int)rank * (BN / 2);
+        int tm, tn;
+        tile_of(t, tiles_m, tiles_n, group_m, tm, tn);
+        const int m0 = tm * (2 * BM) + (int)rank * BM;
+        const int n0 = tn * BN + (int)rank * (BN / 2);
         for (int kb = 0; kb < nkb; ++kb, ++g) {
           const uint32_t s = g % STAGES;
           if (g >= STAGES && !mbar_wait(empty0 + 8 * s, ((g / STAGES) - 1) & 1)) {
@@ -628,7 +651,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         break;
       }
       tc_fence_after();
-      const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM, n0 = (t / tiles_m) * BN;
+      int tm, tn;
+      tile_of(t, tiles_m, tiles_n, group_m, tm, tn);
+      const int m0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * BN;
       epilogue_tile_bulk<BN, EPI>(tmem + buf * BN, stage, &map_c, m0, n0, M, N, warp, lane, box);
       // every load of this warp from the accumulator has completed (each is waited for)
       tc_fence_before();
@@ -966,6 +991,15 @@ static int sm_count() {
   return n;
 }
 
+// Rows of tiles per group (see tile_of): all of them while A fits the L2 with room for the
+// panels of W (up to 48 MB); else as many as keep a group's slice of A near 32 MB.
+static int rows_of_tiles_per_group(int tiles_m, int tile_rows, int K) {
+  const long long tile_bytes = (long long)tile_rows * K * 2;
+  if (tile_bytes * tiles_m <= (48ll << 20)) return tiles_m;
+  const long long g = (32ll << 20) / tile_bytes;       // measured at 16 to 96 MB: 32 to 48 are the fastest
+  return (int)(g < 1 ? 1 : (g > tiles_m ? tiles_m : g));
+}
+
 template <int BN, int STAGES, int EPI>
 static int launch_persistent(const CUtensorMap &ma, const CUtensorMap &mw, void *C, int M, int N, int K, int ldc,
                              int *status, cudaStream_t stream) {
@@ -990,7 +1024,7 @@ static int launch_persistent(const CUtensorMap &ma, const CUtensorMap &mw, void 
   if (rc) return rc;
   const unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
   g2b_launch(gemm_tc_persistent_kernel<BN, STAGES, EPI>, dim3(grid), dim3(THREADS), smem, stream, ma, mw, mc, M, N,
-             K, status);
+             K, rows_of_tiles_per_group((M + BM - 1) / BM, BM, K), status);
   return g2b_check_launch("gemm_tc (persistent)");
 }
 
@@ -1020,7 +1054,7 @@ static int launch_pair(const CUtensorMap &ma, const CUtensorMap &mw, void *C, in
   if (max_pairs < 1) G2B_REFUSE("gemm_tc: the paired kernel needs two SMs");
   const unsigned pairs = (unsigned)(tiles < max_pairs ? tiles : max_pairs);
   g2b_launch_cluster(gemm_tc_pair_kernel<BN, STAGES, EPI>, dim3(2 * pairs), dim3(THREADS), smem, stream, 2u, ma, mw,
-                     mc, M, N, K, status);
+                     mc, M, N, K, rows_of_tiles_per_group((M + 2 * BM - 1) / (2 * BM), 2 * BM, K), status);
   return g2b_check_launch("gemm_tc (pairs)");
 }
 

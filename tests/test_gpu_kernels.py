@@ -514,6 +514,13 @@ def test_gemm_tc_weight_streaming(M, N, K):
     kernels_bf16.check_status()
 
 
+@pytest.mark.parametrize("mode,bn,stages", [(True, 256, 4), (2, 256, 6)])
+def test_gemm_tc_rows_in_groups(mode, bn, stages):
+    """An A operand larger than the L2 makes the persistent kernels walk the rows of tiles in
+    groups (here two groups, the second shorter, three columns of tiles): every tile still once."""
+    _check_gemm_tc(8192 + 40, 520, 4104, bn, stages, mode)
+
+
 def test_linear_of_a_long_prompt_runs_on_pairs():
     """From 4,096 rows on the product is given to pairs of CTAs; the same result as the plain one."""
     from gguf2bin_b200 import kernels_bf16
