@@ -256,3 +256,57 @@ def test_a_shape_that_comes_back_is_replayed_from_a_graph(dtype):
         else:
             eng.close_sequence(hold.pop())
     assert len(eng._graphs) == 1
+
+
+@pytest.mark.parametrize("name,dtype,seed", [("b", "float32", 1), ("c", "bfloat16", 2), ("d", "bfloat16", 3), ("d", "float32", 4)])
+def test_random_schedules(name, dtype, seed):
+    """A seeded random walk over what a caller may do: sequences open at any time, bring their
+    next one to forty tokens in steps shared with whoever else is ready (prompts, continuations
+    and single tokens mixed), want logits at random places, and close when done, in a cache with
+    room for about half of them, so that pages and slots are reused all the time.  Every logit
+    that was asked for equals the plain implementation's at that position of that sequence."""
+    from gguf2bin_b200.engine import StepEntry
+    storage = "float32" if dtype == "float32" else "bfloat16"
+    rng = np.random.default_rng(seed)
+    limit = min(TINY[name]["max_position_embeddings"], 200)
+    eng = make_engine(name, dtype, max_tokens=64 * 10)
+    pending = [random_tokens(name, int(rng.integers(1, limit)), 4000 + 10 * seed + i) for i in range(14)]
+    live = []                                     # [sequence, tokens, fed so far, wanted: list of (position, row of logits)]
+    checked = 0
+    while pending or live:
+        # open what fits
+        while pending and len(live) < 5:
+            need = -(-len(pending[0]) // 64)
+            if need > eng.cache.table.pages.n_free - sum(-(-len(t) // 64) - len(s.pages) for s, t, _, _ in live):
+                break
+            live.append([eng.open_sequence(), pending.pop(0), 0, []])
+        assert live, "the cache is too small for the longest request"
+        # a step over a random non-empty subset of the live sequences
+        chosen = [x for x in live if rng.random() < 0.7] or [live[int(rng.integers(len(live)))]]
+        entries, asked = [], []
+        for x in chosen:
+            seq, toks, fed, _ = x
+            n = int(min(len(toks) - fed, rng.choice([1, 1, 2, 7, 40])))
+            want = sorted(set(int(w) for w in rng.integers(0, n, int(rng.integers(0, 3)))))
+            entries.append(StepEntry(seq, toks[fed:fed + n], want))
+            asked.append((x, fed, n, want))
+        out = eng.step(entries)
+        rows = out.cpu().numpy() if out is not None else np.zeros((0, 0))
+        r = 0
+        for x, fed, n, want in asked:
+            for w in want:
+                x[3].append((fed + w, rows[r]))
+                r += 1
+            x[2] = fed + n
+        assert r == len(rows)
+        for x in [x for x in live if x[2] == len(x[1])]:
+            seq, toks, _, wanted = x
+            if wanted:
+                ref = plain_logits(name, storage, toks)
+                assert_close(np.stack([row for _, row in wanted]), ref[[p for p, _ in wanted]], dtype,
+                             f"{name}/{dtype} sequence of {len(toks)} tokens")
+                checked += len(wanted)
+            eng.close_sequence(seq)
+            live.remove(x)
+    assert checked > 20
+    assert eng.cache.table.pages.n_held == 0 and eng.cache.table.slots.n_held == 0
