@@ -436,6 +436,58 @@ def test_attn_prefill(nh, nkv, hd, window, kernel):
         t += ql
 
 
+def row_attention(q_row, K, V, nh, pos, window=0):
+    """Row ``pos`` of the plain causal attention (keys 0..pos, or the last ``window`` of them)."""
+    lo = 0 if window <= 0 else max(0, pos - window + 1)
+    return last_row_attention(q_row, K[:pos + 1], V[:pos + 1], nh, pos + 1 - lo if window > 0 else 0)
+
+
+@pytest.mark.parametrize("window", [0, 5000])
+def test_attention_over_tens_of_thousands_of_keys(window):
+    """A prompt of 20,000 tokens (157 query tiles, up to 313 pages per tile) through the tcgen05
+    prompt attention, then one token at position 39,999 of a sequence of 40,000 through the
+    decode attention: rows at the start, at tile and page edges, in the middle and at the end
+    against the plain attention of that row; a planted key 19,000 positions back stands out."""
+    from types import SimpleNamespace
+    from gguf2bin_b200 import kernels_bf16
+    from gguf2bin_b200.engine.workspace import Workspace
+    nh, nkv, hd, ps = 4, 2, 128, 64
+    lens = [20000, 40000]
+    cache, table, Ks, Vs = make_paged(2, lens, nkv, hd, ps, torch.bfloat16, seed=170)
+    scale = 1 / math.sqrt(hd)
+    # sequence 0: the whole prompt
+    T = lens[0]
+    q = rnd(T, nh * hd, dtype=torch.bfloat16, seed=171)
+    Ks[0][700] = (q[19700].view(nh, hd)[0] * 0.5)[None, :].expand(nkv, hd)      # row 19,700 looks 19,000 back
+    cache[int(table[0, 700 // ps]), 0, :, 700 % ps] = Ks[0][700]
+    tiles = sorted([(0, r, min(128, T - r), r) for r in range(0, T, 128)], key=lambda t: -t[3])
+    ctx = SimpleNamespace(page_table=table, all_single=False, n_attn_tiles_wide=len(tiles),
+                          attn_tiles_wide=torch.tensor(tiles, dtype=torch.int32, device=DEV))
+    out = torch.zeros_like(q)
+    kernels_bf16.attn_prefill_tc(q, out, cache, ctx, nh, nkv, hd, ps, window, scale)
+    kernels_bf16.check_status()
+    K, V = Ks[0].float().cpu().numpy(), Vs[0].float().cpu().numpy()
+    for pos in (0, 63, 64, 127, 128, 9999, 16383, 16384, 19700, 19999):
+        ref = row_attention(q[pos].float().cpu().numpy().reshape(nh, hd), K, V, nh, pos, window)
+        got = out[pos].float().cpu().numpy().reshape(nh, hd)
+        np.testing.assert_allclose(got, ref, atol=2.0 ** -7 * max(1, np.abs(ref).max()), rtol=0, err_msg=f"row {pos}")
+    if not window:
+        far = np.abs(out[19700].float().cpu().numpy().reshape(nh, hd)[0] - Vs[0][700, 0].float().cpu().numpy()).max()
+        near = np.abs(out[19699].float().cpu().numpy().reshape(nh, hd)[0] - Vs[0][700, 0].float().cpu().numpy()).max()
+        assert far < near, "the planted key does not stand out"
+    # sequence 1: one token at the end of 40,000 keys
+    q1 = rnd(1, nh * hd, dtype=torch.bfloat16, seed=172)
+    out1 = torch.zeros_like(q1)
+    dctx = SimpleNamespace(tok_pos=torch.tensor([lens[1] - 1], dtype=torch.int32, device=DEV),
+                           tok_seq=torch.tensor([1], dtype=torch.int32, device=DEV), page_table=table,
+                           max_kv_len=table.shape[1] * ps, workspace=Workspace(DEV), all_single=True)
+    kernels_bf16.attn_decode(q1, out1, cache, dctx, nh, nkv, hd, ps, window, scale)
+    ref = row_attention(q1[0].float().cpu().numpy().reshape(nh, hd), Ks[1].float().cpu().numpy(),
+                        Vs[1].float().cpu().numpy(), nh, lens[1] - 1, window)
+    np.testing.assert_allclose(out1.float().cpu().numpy().reshape(nh, hd), ref,
+                               atol=2.0 ** -7 * max(1, np.abs(ref).max()), rtol=0, err_msg="decode at 40,000 keys")
+
+
 def _check_gemm_tc(M, N, K, bn, stages, persistent):
     from gguf2bin_b200 import kernels_bf16
     a, w = rnd(M, K, dtype=torch.bfloat16, seed=80), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=81)

@@ -310,3 +310,47 @@ def test_random_schedules(name, dtype, seed):
             live.remove(x)
     assert checked > 20
     assert eng.cache.table.pages.n_held == 0 and eng.cache.table.slots.n_held == 0
+
+
+def test_a_context_of_33000_tokens_cut_three_ways():
+    """Far beyond what the plain implementation can follow in the tests' time, so the engine is
+    compared with itself (the kernels' own long-context tests compare with the plain attention):
+    a prompt of 33,000 tokens whole in one step; in pieces of 8,192; and with its last three
+    tokens decoded one by one.  The logits at the last four places and at two places in the
+    middle agree within the bfloat16 bound."""
+    from gguf2bin_b200.engine import Engine, Model, StepEntry
+    from helpers import tmp_root
+    from gguf2bin_b200.weights import write_random_model
+    cfg = dict(TINY["d"], max_position_embeddings=40960)
+    folder = write_random_model(tmp_root() / "tiny_d_long", cfg, 5, "bfloat16")
+    eng = Engine(Model.from_folder(folder, dtype="bfloat16"), max_tokens=33024 + 64)
+    n = 33000
+    toks = np.random.default_rng(11).integers(0, cfg["vocab_size"], n).tolist()
+    places = [8191, 16400, n - 4, n - 3, n - 2, n - 1]
+
+    s = eng.open_sequence()
+    whole = eng.step([StepEntry(s, toks, places)]).cpu().numpy()
+    eng.close_sequence(s)
+
+    s = eng.open_sequence()
+    got = []
+    for a in range(0, n, 8192):
+        b = min(n, a + 8192)
+        want = [p - a for p in places if a <= p < b]
+        out = eng.step([StepEntry(s, toks[a:b], want)])
+        if want:
+            got.append(out.cpu().numpy())
+    eng.close_sequence(s)
+    pieces = np.concatenate(got)
+
+    s = eng.open_sequence()
+    got = [eng.step([StepEntry(s, toks[:n - 3], [8191, 16400, n - 4])]).cpu().numpy()]
+    for t in toks[n - 3:]:
+        got.append(eng.step([StepEntry(s, [t], [0])]).cpu().numpy())
+    eng.close_sequence(s)
+    decoded = np.concatenate(got)
+
+    assert np.isfinite(whole).all() and np.abs(whole).max() > 0.1
+    assert_close(pieces, whole, "bfloat16", "pieces of 8,192 against the whole prompt")
+    assert_close(decoded, whole, "bfloat16", "last three tokens decoded against the whole prompt")
+    assert eng.cache.table.pages.n_held == 0
