@@ -19,8 +19,10 @@ whole batch.  It prints ONE JSON line:
              three calls (each with its own prompts' prefill before and the set-up of its
              decode session inside the timed steps), all three listed under "runs"
   prefill    one step over a 2,048-token prompt: tokens per second, milliseconds (the median of
-             three runs that replay the shape's graph; ``first_ms`` is the first run of the
-             shape, which runs plainly), and the fraction of the tensor-core peak its flops reach
+             three runs that replay the shape's graph; ``plain_ms`` is a run of the warm engine
+             without the graph, what a shape costs when it is first seen; ``first_ms`` the very
+             first run, which also builds scratch buffers and loads kernels), and the fraction of
+             the tensor-core peak its flops reach
   roofline   bytes a decode step must read (every weight once, the cache of the live
              requests) divided by its time, against the measured copy bandwidth
   points     decode tokens per second at batch 1 and 64 (fewer steps), each with its step time
@@ -158,12 +160,15 @@ def random_prompts(n: int, length: int, vocab: int, seed: int):
 
 def timed_prompt_step(llm, prompts, repeats: int):
     """Milliseconds of ONE step over all the prompts (logits at each last place), device-timed:
-    (the first run of this shape, which runs plainly; the median of the last ``repeats`` runs,
-    which replay the shape's graph)."""
+    (the very first run, which also builds scratch buffers and loads kernels; the median of the
+    last ``repeats`` runs, which replay the shape's graph; a run of the warm engine without the
+    graph, which is what a shape costs the first time it is seen)."""
     import torch
     from gguf2bin_b200.engine import StepEntry
     times = []
-    for _ in range(3 + repeats):
+    for i in range(3 + repeats + 1):
+        if i == 3 + repeats:                       # once more without the graph: a warm engine's plain run,
+            graphs, llm.engine.step_graphs = llm.engine.step_graphs, False     # what a shape seen for the first time costs
         seqs = [llm.open_sequence() for _ in prompts]
         for s, p in zip(seqs, prompts):
             llm.engine.cache.reserve(s, len(p))
@@ -176,7 +181,8 @@ def timed_prompt_step(llm, prompts, repeats: int):
         for s in seqs:
             llm.close_sequence(s)
         times.append(e0.elapsed_time(e1))
-    return times[0], statistics.median(times[3:])
+    llm.engine.step_graphs = graphs
+    return times[0], statistics.median(times[3:-1]), times[-1]
 
 
 def decode_device_timed(llm, prompts, steps: int, warmup: int, vocab: int, whole_batch_prefill: bool):
@@ -317,13 +323,13 @@ def main() -> int:
     free1, _ = torch.cuda.mem_get_info()
 
     # ---- prefill: one step over the prompts, logits at each last place ------------------------
-    pre_first, pre = timed_prompt_step(llm, prefill_prompts, repeats=3)
+    pre_first, pre, pre_plain = timed_prompt_step(llm, prefill_prompts, repeats=3)
     pre_lengths = [len(p) for p in prefill_prompts]
     pre_tokens = sum(pre_lengths)
     pre_flops = prefill_flops(cfg, a.layers, pre_lengths)
     prefill = dict(value=pre_tokens / (pre / 1e3), tokens=pre_tokens, ms=pre,
                    frac=pre_flops / (pre / 1e3) / (pk["bf16_tflops"] * 1e12),
-                   first_ms=pre_first, sequences=len(pre_lengths))
+                   first_ms=pre_first, plain_ms=pre_plain, sequences=len(pre_lengths))
 
     # ---- decode, device-timed -----------------------------------------------------------------
     clocks = ClockSampler()
