@@ -359,9 +359,11 @@ def main() -> int:
     # ---- other batch sizes ------------------------------------------------------------------------
     points = {}
     if points_wanted:
-        for b, k in ((1, min(steps, 256)), (64, min(steps, 128))):
-            s, _, ctx_b = decode_device_timed(llm, random_prompts(b, start_ctx - a.warmup, vocab, 100), k,
-                                              a.warmup, vocab, whole_batch_prefill=False)
+        room = a.context - start_ctx - 1
+        for b, k in ((1, min(room, 256)), (64, min(room, 128))):    # their own step counts, whatever --steps says:
+            warm = max(a.warmup, 16)                                # twenty steps of 0.7 ms mostly measure the clocks settling
+            s, _, ctx_b = decode_device_timed(llm, random_prompts(b, start_ctx - warm, vocab, 100), k,
+                                              warm, vocab, whole_batch_prefill=False)
             r = hbm_roofline(sizes, b, ctx_b, s / k, pk)
             points[f"decode_b{b}"] = b * k / s
             points[f"decode_b{b}_ms_per_step"] = s / k * 1e3
