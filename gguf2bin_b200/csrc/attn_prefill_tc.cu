@@ -269,7 +269,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
     const uint32_t lane_base = tmem + ((uint32_t)row0 << 16);
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;      // l: this thread's keys only
     bool ok = true;
-    TDECL(4); TDECL(5); TDECL(6); TDECL(7);
+    TDECL(4); TDECL(5); TDECL(6); TDECL(7); TDECL(12); TDECL(13);
     TICK(t_sm);
     for (int i = 0; i < n_pages && ok; ++i) {
       const uint32_t sbuf = lane_base + 64 * (i & 1);
@@ -288,6 +288,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       tmem_ld_wait();
       TOCK(6, t_ld);
       const int key0 = (first_page + i) * PAGE;
+      TICK(t_mx);
       // raw scores stay in sr; the scale (> 0) is applied to the maximum and inside the exponent.
       // Only pages that cross the limits of the warp's rows are masked (warp-uniform test).
       const int warp_pos_min = pos0 + row0, warp_pos_max = warp_pos_min + 15;
@@ -316,6 +317,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
       mx_a *= scale_log2;                          // -inf stays -inf
       mx_b *= scale_log2;
+      TOCK(12, t_mx);
       const bool grow_a = mx_a > m_a + RESCALE_STEP || (m_a == -INFINITY && mx_a > -INFINITY);
       const bool grow_b = mx_b > m_b + RESCALE_STEP || (m_b == -INFINITY && mx_b > -INFINITY);
       if (i > 0 && __any_sync(0xffffffffu, grow_a || grow_b)) {
@@ -352,6 +354,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       if (grow_b) m_b = mx_b;
       const float neg_a = m_a == -INFINITY ? 0.f : -m_a;
       const float neg_b = m_b == -INFINITY ? 0.f : -m_b;
+      TICK(t_ex);
       uint32_t pk[16];                             // [2j + s]: row (s ? rB : rA), packed column 4j + c
       float la2[2] = {0.f, 0.f}, lb2[2] = {0.f, 0.f};
 #pragma unroll
@@ -367,6 +370,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       l_a += la2[0] + la2[1];
       l_b += lb2[0] + lb2[1];
+      TOCK(13, t_ex);
       TICK(t_st);
       tmem_st_16x128b_x8(sbuf, pk);                // P over the first 32 columns of this S buffer
       tmem_st_wait();
@@ -375,7 +379,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       TOCK(7, t_st);
     }
     TOCK(4, t_sm);
-    if (threadIdx.x == 0) { TFLUSH(4); TFLUSH(5); TFLUSH(6); TFLUSH(7); }
+    if (threadIdx.x == 0) { TFLUSH(4); TFLUSH(5); TFLUSH(6); TFLUSH(7); TFLUSH(12); TFLUSH(13); }
     if (ok) {
       if (!mbar_wait(o_ready, 0)) {
         if (lane == 0) atomicExch(status, ST_SOFTMAX);

@@ -238,6 +238,65 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // sum does not depend on any order).  Two staging buffers per warp: the copy of one box runs
 // while the next is filled.  The accumulator loads run one chunk ahead of their use.
 // `box` counts the boxes this warp has issued so far (selects the buffer).
+// One chunk of 32 accumulator columns (`v`, chunk `c` of the tile) on its way to C: see below.
+template <int EPI>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&v)[32], int c, unsigned char *stage,
+                                               const CUtensorMap *map_c, int y, int n0, int M, int N, int lane,
+                                               uint32_t &box) {
+  // which 16-byte chunks of the row this accumulator chunk fills, and whether it completes a box
+  constexpr int PER_BOX = EPI == EPI_SWIGLU_BF16 ? 4 : (EPI == EPI_STORE_BF16 ? 2 : 1);
+  const int part = c % PER_BOX;
+  if (part == 0) {
+    // the buffer's previous box (two boxes ago) must have been read
+    if (lane == 0) bulk_wait_read<1>();
+    __syncwarp();
+  }
+  unsigned char *buf = stage + (box & 1) * 4096;
+  const uint32_t row_addr = smem_addr(buf) + lane * 128;
+  auto put = [&](int chunk, uint4 val) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(row_addr + ((chunk ^ (lane & 7)) << 4)),
+                 "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w) : "memory");
+  };
+  if (EPI == EPI_STORE_F32 || EPI == EPI_ACCUM_F32) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) put(j, make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+  } else if (EPI == EPI_STORE_BF16) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      put(4 * part + j, make_uint4(pack2(v[8 * j], v[8 * j + 1]), pack2(v[8 * j + 2], v[8 * j + 3]),
+                                   pack2(v[8 * j + 4], v[8 * j + 5]), pack2(v[8 * j + 6], v[8 * j + 7])));
+  } else {
+    // columns 16b .. 16b+7 are gates, 16b+8 .. 16b+15 the ups of the same outputs
+    float h[16];
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float gate = __uint_as_float(v[16 * blk + j]);
+        const float up = __uint_as_float(v[16 * blk + 8 + j]);
+        h[8 * blk + j] = __fdividef(gate, 1.f + __expf(-gate)) * up;
+      }
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+      put(2 * part + j, make_uint4(pack2f(h[8 * j], h[8 * j + 1]), pack2f(h[8 * j + 2], h[8 * j + 3]),
+                                   pack2f(h[8 * j + 4], h[8 * j + 5]), pack2f(h[8 * j + 6], h[8 * j + 7])));
+  }
+  if (part == PER_BOX - 1) {
+    fence_async_shared();
+    __syncwarp();
+    if (lane == 0) {
+      const int first_col = n0 + 32 * (c - part);            // accumulator column of the box
+      if (first_col < N && y < M) {                          // a box wholly outside C is not issued
+        const int x = EPI == EPI_SWIGLU_BF16 ? first_col >> 1 : first_col;
+        if (EPI == EPI_ACCUM_F32) tma_reduce_add_2d(map_c, smem_addr(buf), x, y);
+        else tma_store_2d(map_c, smem_addr(buf), x, y);
+      }
+      bulk_commit();                                        // an empty group keeps the count in step
+    }
+    ++box;
+  }
+}
+
 template <int BN, int EPI>
 __device__ __forceinline__ void epilogue_tile_bulk(uint32_t tmem, unsigned char *stage, const CUtensorMap *map_c,
                                                    int m0, int n0, int M, int N, int warp, int lane,
@@ -251,59 +310,113 @@ __device__ __forceinline__ void epilogue_tile_bulk(uint32_t tmem, unsigned char 
   for (int c = 0; c < CHUNKS; ++c) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
     if (c + 1 < CHUNKS) tmem_ld32(lane_addr + 32 * (c + 1), r[(c + 1) & 1]);
-    const uint32_t(&v)[32] = r[c & 1];
-    // which 16-byte chunks of the row this accumulator chunk fills, and whether it completes a box
-    constexpr int PER_BOX = EPI == EPI_SWIGLU_BF16 ? 4 : (EPI == EPI_STORE_BF16 ? 2 : 1);
-    const int part = c % PER_BOX;
-    if (part == 0) {
-      // the buffer's previous box (two boxes ago) must have been read
-      if (lane == 0) bulk_wait_read<1>();
-      __syncwarp();
-    }
-    unsigned char *buf = stage + (box & 1) * 4096;
-    const uint32_t row_addr = smem_addr(buf) + lane * 128;
-    auto put = [&](int chunk, uint4 val) {
-      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(row_addr + ((chunk ^ (lane & 7)) << 4)),
-                   "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w) : "memory");
-    };
-    if (EPI == EPI_STORE_F32 || EPI == EPI_ACCUM_F32) {
+    epilogue_chunk<EPI>(r[c & 1], c, stage, map_c, y, n0, M, N, lane, box);
+  }
+}
+
+// ---- K in parts over a cluster ---------------------------------------------------------------
+// With fewer tiles than half the SMs, the CTAs of a cluster take the same tile and one part of
+// K each.  The tile's chunks of 32 columns are dealt out to the ranks in contiguous ranges
+// (whole boxes of the output): a rank keeps its own chunks in tensor memory, lays the others
+// out in its ring of stages (free once its products are done) as [chunk][128 rows][32 floats],
+// and after a cluster barrier sends every other rank that one's chunks with one bulk copy
+// through the cluster's window, counted on a barrier of the receiver.  Then it adds the parts
+// of its own chunks in rank order (the sum does not depend on timing) and sends them through
+// the ordinary epilogue.  The first chunk of rank q of S: PER_BOX * ((CHUNKS / PER_BOX) * q / S).
+constexpr int PART_CHUNK_BYTES = BM * 128;          // one chunk of a tile: 128 rows of 32 floats
+__host__ __device__ constexpr int chunks_per_box(int epi) {
+  return epi == EPI_SWIGLU_BF16 ? 4 : (epi == EPI_STORE_BF16 ? 2 : 1);
+}
+template <int BN, int EPI> __host__ __device__ constexpr int part_chunk_lo(int q, int S) {
+  return chunks_per_box(EPI) * (((BN / 32) / chunks_per_box(EPI)) * q / S);
+}
+// whether S parts fit tiles bn wide: every rank owns a box, and the chunks of the others plus
+// what a rank receives fit the ring
+static bool parts_fit(int bn, int epi, int S, int nkb, int ring_bytes) {
+  const int per_box = chunks_per_box(epi), chunks = bn / 32;
+  if (S < 1 || S > 4 || chunks / per_box < S || nkb < S) return false;
+  for (int q = 0; q < S; ++q) {
+    const int own = per_box * ((chunks / per_box) * (q + 1) / S) - per_box * ((chunks / per_box) * q / S);
+    if ((chunks - own + (S - 1) * own) * PART_CHUNK_BYTES > ring_bytes) return false;
+  }
+  return true;
+}
+
+// the chunks of the other ranks into the ring (epilogue warps, after the tile's products)
+template <int BN, int EPI>
+__device__ __forceinline__ void parts_lay_out(uint32_t tmem, unsigned char *ring, int warp, int lane, int rank, int S) {
+  constexpr int CHUNKS = BN / 32;
+  const int own_lo = part_chunk_lo<BN, EPI>(rank, S), own_hi = part_chunk_lo<BN, EPI>(rank + 1, S);
+  const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+#pragma unroll 1
+  for (int c = 0; c < CHUNKS; ++c) {
+    if (c >= own_lo && c < own_hi) continue;
+    uint32_t r[32];
+    tmem_ld32(lane_addr + 32 * c, r);
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+    const int slot = c < own_lo ? c : c - (own_hi - own_lo);
+    const uint32_t row_addr = smem_addr(ring) + slot * PART_CHUNK_BYTES + (warp * 32 + lane) * 128;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) put(j, make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
-    } else if (EPI == EPI_STORE_BF16) {
+    for (int j = 0; j < 8; ++j)
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(row_addr + ((j ^ (lane & 7)) << 4)),
+                   "r"(r[4 * j]), "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3]) : "memory");
+  }
+}
+// one thread: this rank's copies to the others (after the cluster barrier)
+template <int BN, int EPI>
+__device__ __forceinline__ void parts_send(unsigned char *ring, uint32_t part_bar, int rank, int S) {
+  constexpr int CHUNKS = BN / 32;
+  const int own_lo = part_chunk_lo<BN, EPI>(rank, S), own_n = part_chunk_lo<BN, EPI>(rank + 1, S) - own_lo;
+  for (int q = 0; q < S; ++q) {
+    if (q == rank) continue;
+    const int q_lo = part_chunk_lo<BN, EPI>(q, S), q_n = part_chunk_lo<BN, EPI>(q + 1, S) - q_lo;
+    if (q_n <= 0) continue;
+    const int slot = q_lo < own_lo ? q_lo : q_lo - own_n;              // where q's chunks lie in my ring
+    // in q's ring: after the chunks it laid out itself, one range per sender in rank order
+    const uint32_t dst = smem_addr(ring) + (uint32_t)((CHUNKS - q_n) + (rank < q ? rank : rank - 1) * q_n) * PART_CHUNK_BYTES;
+    asm volatile(
+        "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+        ::"r"(map_to_cta(dst, (uint32_t)q)), "r"(smem_addr(ring) + (uint32_t)slot * PART_CHUNK_BYTES),
+          "r"((uint32_t)q_n * PART_CHUNK_BYTES), "r"(map_to_cta(part_bar, (uint32_t)q))
+        : "memory");
+  }
+}
+// this rank's chunks: own part from tensor memory, the others' from the ring, added in rank order
+template <int BN, int EPI>
+__device__ __forceinline__ void parts_finish(uint32_t tmem, const unsigned char *ring, unsigned char *stage,
+                                             const CUtensorMap *map_c, int m0, int n0, int M, int N, int warp,
+                                             int lane, uint32_t &box, int rank, int S) {
+  constexpr int CHUNKS = BN / 32;
+  const int own_lo = part_chunk_lo<BN, EPI>(rank, S), own_n = part_chunk_lo<BN, EPI>(rank + 1, S) - own_lo;
+  const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t recv0 = smem_addr(ring) + (uint32_t)(CHUNKS - own_n) * PART_CHUNK_BYTES + (warp * 32 + lane) * 128;
+  const int y = m0 + warp * 32;
+#pragma unroll 1
+  for (int i = 0; i < own_n; ++i) {
+    uint32_t mine[32], v[32];
+    tmem_ld32(lane_addr + 32 * (own_lo + i), mine);
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll 1
+    for (int p = 0; p < S; ++p) {
+      if (p == rank) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        put(4 * part + j, make_uint4(pack2(v[8 * j], v[8 * j + 1]), pack2(v[8 * j + 2], v[8 * j + 3]),
-                                     pack2(v[8 * j + 4], v[8 * j + 5]), pack2(v[8 * j + 6], v[8 * j + 7])));
-    } else {
-      // columns 16b .. 16b+7 are gates, 16b+8 .. 16b+15 the ups of the same outputs
-      float h[16];
-#pragma unroll
-      for (int blk = 0; blk < 2; ++blk)
+        for (int j = 0; j < 32; ++j)
+          v[j] = p == 0 ? mine[j] : __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(mine[j]));
+      } else {
+        const uint32_t src = recv0 + (uint32_t)((p < rank ? p : p - 1) * own_n + i) * PART_CHUNK_BYTES;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const float gate = __uint_as_float(v[16 * blk + j]);
-          const float up = __uint_as_float(v[16 * blk + 8 + j]);
-          h[8 * blk + j] = __fdividef(gate, 1.f + __expf(-gate)) * up;
-        }
+          uint4 t;
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n" : "=r"(t.x), "=r"(t.y), "=r"(t.z), "=r"(t.w)
+                       : "r"(src + ((j ^ (lane & 7)) << 4)) : "memory");
+          const uint32_t tt[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
-        put(2 * part + j, make_uint4(pack2f(h[8 * j], h[8 * j + 1]), pack2f(h[8 * j + 2], h[8 * j + 3]),
-                                     pack2f(h[8 * j + 4], h[8 * j + 5]), pack2f(h[8 * j + 6], h[8 * j + 7])));
-    }
-    if (part == PER_BOX - 1) {
-      fence_async_shared();
-      __syncwarp();
-      if (lane == 0) {
-        const int first_col = n0 + 32 * (c - part);            // accumulator column of the box
-        if (first_col < N && y < M) {                          // a box wholly outside C is not issued
-          const int x = EPI == EPI_SWIGLU_BF16 ? first_col >> 1 : first_col;
-          if (EPI == EPI_ACCUM_F32) tma_reduce_add_2d(map_c, smem_addr(buf), x, y);
-          else tma_store_2d(map_c, smem_addr(buf), x, y);
+          for (int e = 0; e < 4; ++e)
+            v[4 * j + e] = p == 0 ? tt[e] : __float_as_uint(__uint_as_float(v[4 * j + e]) + __uint_as_float(tt[e]));
         }
-        bulk_commit();                                        // an empty group keeps the count in step
       }
-      ++box;
     }
+    epilogue_chunk<EPI>(v, own_lo + i, stage, map_c, y, n0, M, N, lane, box);
   }
 }
 
@@ -351,28 +464,36 @@ template <int BN, int STAGES> struct SmemP {
   static constexpr int SCRATCH_OFFSET = STAGES * STAGE_BYTES;
   static constexpr int SCRATCH_BYTES = 4 * 2 * 4096;          // two 32 x 128-byte boxes per epilogue warp
   static constexpr int BARRIER_OFFSET = SCRATCH_OFFSET + SCRATCH_BYTES;
-  static constexpr int TOTAL = BARRIER_OFFSET + 8 * (2 * STAGES + 4) + 16 + 1024;   // + barriers, slot, alignment slack
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = BARRIER_OFFSET + 8 * (2 * STAGES + 5) + 16 + 1024;   // + barriers, slot, alignment slack
 };
 
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                           const __grid_constant__ CUtensorMap map_c, int M, int N, int K, int group_m,
-                          int *__restrict__ status) {
+                          int k_parts, int *__restrict__ status) {
   pdl_launch();
   extern __shared__ unsigned char smem_raw[];
   using S = SmemP<BN, STAGES>;
   unsigned char *smem = reinterpret_cast<unsigned char *>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::BARRIER_OFFSET);
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 5);
   const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + STAGES);
   const uint32_t acc_full0 = smem_addr(bars + 2 * STAGES), acc_empty0 = smem_addr(bars + 2 * STAGES + 2);
+  const uint32_t part_bar = smem_addr(bars + 2 * STAGES + 4);     // the other ranks' parts of my chunks
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nkb = (K + BK - 1) / BK;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  const int n_tiles = tiles_m * tiles_n;
+  // K in parts (k_parts > 1): a cluster per tile, one tile per cluster (the host sees to it),
+  // rank r takes the blocks [r nkb / k_parts, (r + 1) nkb / k_parts) of K
+  const int rank = k_parts > 1 ? (int)cluster_ctarank() : 0;
+  const int walker = (int)blockIdx.x / k_parts, walkers = (int)gridDim.x / k_parts;
+  const int n_tiles = k_parts > 1 ? min(tiles_m * tiles_n, walkers) : tiles_m * tiles_n;
+  const int kb_lo = (int)((long long)nkb * rank / k_parts), kb_hi = (int)((long long)nkb * (rank + 1) / k_parts);
+  const int n_kb = kb_hi - kb_lo;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -383,7 +504,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       mbar_init(acc_full0 + 8 * b, 1);
       mbar_init(acc_empty0 + 8 * b, 4);            // one arrival per epilogue warp
     }
+    mbar_init(part_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    if (k_parts > 1) {
+      const int own = part_chunk_lo<BN, EPI>(rank + 1, k_parts) - part_chunk_lo<BN, EPI>(rank, k_parts);
+      if (walker < n_tiles && own > 0) mbar_expect_tx(part_bar, (uint32_t)((k_parts - 1) * own) * PART_CHUNK_BYTES);
+    }
   }
   if (warp == 5) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
@@ -396,14 +522,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   const uint32_t tmem = *tmem_slot;
   // the weights of the first ring (this CTA's first tile) are requested above the dependency
   // line: they do not depend on the kernels in front; the rows of A follow below it
-  const int n_early = (int)blockIdx.x < n_tiles ? min(nkb, STAGES) : 0;
+  const int n_early = walker < n_tiles ? min(n_kb, STAGES) : 0;
   if (warp == 4 && lane == 0 && PRODUCER_RUNS) {
     int tm, tn;
-    tile_of((int)blockIdx.x, tiles_m, tiles_n, group_m, tm, tn);
+    tile_of(walker, tiles_m, tiles_n, group_m, tm, tn);
     const int n0 = tn * BN;
     for (int kb = 0; kb < n_early; ++kb) {
       mbar_expect_tx(full0 + 8 * kb, S::STAGE_BYTES);
-      tma_load_2d(smem_addr(smem + kb * S::STAGE_BYTES) + S::A_BYTES, &map_w, kb * BK, n0, full0 + 8 * kb);
+      tma_load_2d(smem_addr(smem + kb * S::STAGE_BYTES) + S::A_BYTES, &map_w, (kb_lo + kb) * BK, n0, full0 + 8 * kb);
     }
   }
   pdl_wait();
@@ -414,11 +540,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       bool ok = true;
       TDECL(0); TDECL(1);
       TICK(t_prod);
-      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      for (int t = walker; t < n_tiles && ok; t += walkers) {
         int tm, tn;
         tile_of(t, tiles_m, tiles_n, group_m, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int kb = 0; kb < nkb; ++kb, ++g) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++g) {
           const uint32_t s = g % STAGES;
           TICK(t_e);
           if (g >= STAGES && !mbar_wait(empty0 + 8 * s, ((g / STAGES) - 1) & 1)) {
@@ -445,7 +571,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       bool ok = true;
       TDECL(2); TDECL(3); TDECL(4); TDECL(5);
       TICK(t_mma);
-      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++j) {
+      for (int t = walker; t < n_tiles && ok; t += walkers, ++j) {
         const uint32_t buf = j & 1;
         // the epilogue must have drained this accumulator (it was used by tile j - 2)
         TICK(t_ae);
@@ -455,7 +581,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         }
         TOCK(3, t_ae);
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-        for (int kb = 0; kb < nkb; ++kb, ++g) {
+        for (int kb = 0; kb < n_kb; ++kb, ++g) {
           const uint32_t s = g % STAGES;
           TICK(t_f);
           if (!mbar_wait(full0 + 8 * s, (g / STAGES) & 1)) {
@@ -479,12 +605,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       TOCK(2, t_mma);
       TFLUSH(2); TFLUSH(3); TFLUSH(4); TFLUSH(5);
     }
-  } else {
+  } else if (k_parts == 1) {
     unsigned char *stage = smem + S::SCRATCH_OFFSET + warp * (2 * 4096);
     uint32_t j = 0, box = 0;
     TDECL(6); TDECL(7); TDECL(8);
     TICK(t_epi);
-    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++j) {
+    for (int t = walker; t < n_tiles; t += walkers, ++j) {
       const uint32_t buf = j & 1;
       TICK(t_af);
       if (!mbar_wait(acc_full0 + 8 * buf, (j >> 1) & 1)) {
@@ -507,12 +633,46 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     TOCK(6, t_epi);
     if (threadIdx.x == 0) { TFLUSH(6); TFLUSH(7); TFLUSH(8); }
   }
+  if (k_parts > 1) {
+    // every thread of every CTA of the cluster comes through here, whatever its waits did
+    const bool have_tile = walker < n_tiles;
+    bool have_acc = false;
+    if (warp < 4 && have_tile) {
+      have_acc = mbar_wait(acc_full0, 0);            // this rank's products are complete: its ring is free
+      if (!have_acc && lane == 0) atomicExch(status, ST_EPILOGUE_TIMEOUT);
+      have_acc = __all_sync(0xffffffffu, have_acc);
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      if (have_acc) parts_lay_out<BN, EPI>(tmem, smem, warp, lane, rank, k_parts);
+      fence_async_shared();                          // the bulk copies below read what was just written
+    }
+    cluster_sync_all();                              // every rank's ring is free and its chunks for the others lie ready
+    if (warp < 4 && have_tile) {
+      if (threadIdx.x == 0 && have_acc) parts_send<BN, EPI>(smem, part_bar, rank, k_parts);
+      const int own = part_chunk_lo<BN, EPI>(rank + 1, k_parts) - part_chunk_lo<BN, EPI>(rank, k_parts);
+      if (have_acc && own > 0) {
+        have_acc = mbar_wait(part_bar, 0);           // the other ranks' parts of my chunks have arrived
+        if (!have_acc && lane == 0) atomicExch(status, ST_EPILOGUE_TIMEOUT);
+        have_acc = __all_sync(0xffffffffu, have_acc);
+      }
+      if (have_acc && own > 0) {
+        unsigned char *stage = smem + S::SCRATCH_OFFSET + warp * (2 * 4096);
+        uint32_t box = 0;
+        int tm, tn;
+        tile_of(walker, tiles_m, tiles_n, group_m, tm, tn);
+        parts_finish<BN, EPI>(tmem, smem, stage, &map_c, tm * BM, tn * BN, M, N, warp, lane, box, rank, k_parts);
+      }
+      if (lane == 0) bulk_wait<0>();
+    }
+  }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
   if (warp == 5) {
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"((uint32_t)(2 * BN)));
   }
+  // the copies that read this CTA's ring and the arrivals on its barrier are over when every
+  // rank has its parts: nobody leaves before
+  if (k_parts > 1) cluster_sync_all();
 }
 
 // ---- pairs of CTAs -------------------------------------------------------------------------
@@ -1000,9 +1160,79 @@ static int rows_of_tiles_per_group(int tiles_m, int tile_rows, int K) {
   return (int)(g < 1 ? 1 : (g > tiles_m ? tiles_m : g));
 }
 
+// Clusters of `sz` CTAs of the persistent kernel that the GPU holds at once (clusters do not
+// straddle its processing clusters, so it can be fewer than SMs / sz): asked of the runtime once
+// per device, tile width and size, for the kernel with the adding epilogue (the others use the
+// same shared memory).
+static int clusters_at_once(int bn, int sz) {
+  static G2bPerDevice fit[2][5];                  // value[device] = answer + 1; 0 = not asked yet
+  const int dev = g2b_current_device(), w = bn == 256 ? 1 : 0;
+  if (sz < 2 || sz > 4) return 0;
+  if (dev >= 0 && fit[w][sz].value[dev]) return fit[w][sz].value[dev] - 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(sz * sm_count()));
+  cfg.blockDim = dim3(THREADS);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)sz;
+  attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  cudaError_t e;
+  if (w) {
+    cfg.dynamicSmemBytes = SmemP<256, 4>::TOTAL;
+    cudaFuncSetAttribute(gemm_tc_persistent_kernel<256, 4, EPI_ACCUM_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         SmemP<256, 4>::TOTAL);
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_persistent_kernel<256, 4, EPI_ACCUM_F32>, &cfg);
+  } else {
+    cfg.dynamicSmemBytes = SmemP<128, 6>::TOTAL;
+    cudaFuncSetAttribute(gemm_tc_persistent_kernel<128, 6, EPI_ACCUM_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         SmemP<128, 6>::TOTAL);
+    e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_persistent_kernel<128, 6, EPI_ACCUM_F32>, &cfg);
+  }
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    n = sm_count() / sz / 2;                       // a cautious guess
+  }
+  if (dev >= 0) fit[w][sz].value[dev] = n + 1;
+  return n;
+}
+
+// The persistent kernel's tile width (128 with six stages or 256 with four) and parts of K for
+// a product, from a small model of its time in microseconds, fitted to measurements on a B200
+// at 192 to 2,048 rows against the matrices of three model sizes: rounds of tiles per CTA x
+// blocks of K per part x 0.295 (0.34 for the wide tile), plus what the exchange of the parts
+// costs (2.3 for the narrow tile, 1.4 + 1.5 per part for the wide one).  K goes in parts only
+// when all clusters run at once, a part has at least 8 blocks and the parts save at least 12.
+static void choose_persistent(int M, int N, int K, int epi, int *bn_out, int *parts_out, int only_bn) {
+  const int nkb = (K + BK - 1) / BK, tiles_m = (M + BM - 1) / BM, sms = sm_count();
+  double best = 1e30;
+  for (int w = 0; w < 2; ++w) {
+    const int bn = w ? 256 : 128;
+    if (only_bn && bn != only_bn) continue;
+    const long long tiles = (long long)tiles_m * ((N + bn - 1) / bn);
+    const double t_kb = w ? 0.34 : 0.295;
+    for (int p = 1; p <= 4; ++p) {
+      if (p > 1 && (nkb / p < 8 || (long long)nkb * (p - 1) / p < 12 || !parts_fit(bn, epi, p, nkb, 196608) ||
+                    2 * tiles > sms || tiles > clusters_at_once(bn, p)))
+        continue;
+      const long long rounds = (tiles * p + sms - 1) / sms;
+      const double cost = (double)rounds * ((nkb + p - 1) / p) * t_kb + (p > 1 ? (w ? 1.4 + 1.5 * p : 2.3) : 0.0);
+      if (cost < best - 1e-9) {
+        best = cost;
+        *bn_out = bn;
+        *parts_out = p;
+      }
+    }
+  }
+}
+static_assert(SmemP<128, 6>::RING_BYTES == 196608 && SmemP<256, 4>::RING_BYTES == 196608, "choose_persistent's ring");
+
+// want_parts: 1 to 4 parts of K
 template <int BN, int STAGES, int EPI>
 static int launch_persistent(const CUtensorMap &ma, const CUtensorMap &mw, void *C, int M, int N, int K, int ldc,
-                             int *status, cudaStream_t stream) {
+                             int want_parts, int *status, cudaStream_t stream) {
   static G2bPerDevice configured;
   const int smem = SmemP<BN, STAGES>::TOTAL;
   const int cfg_dev = g2b_current_device();
@@ -1022,9 +1252,20 @@ static int launch_persistent(const CUtensorMap &ma, const CUtensorMap &mw, void 
   CUtensorMap mc;
   const int rc = make_map_c(&mc, C, M, c_cols, ldc, is_float);
   if (rc) return rc;
-  const unsigned grid = (unsigned)(tiles < sm_count() ? tiles : sm_count());
-  g2b_launch(gemm_tc_persistent_kernel<BN, STAGES, EPI>, dim3(grid), dim3(THREADS), smem, stream, ma, mw, mc, M, N,
-             K, rows_of_tiles_per_group((M + BM - 1) / BM, BM, K), status);
+  const int nkb = (K + BK - 1) / BK;
+  const int parts = want_parts < 1 ? 1 : want_parts;
+  if (parts > 1) {
+    if (!parts_fit(BN, EPI, parts, nkb, SmemP<BN, STAGES>::RING_BYTES))
+      G2B_REFUSE("gemm_tc: %d parts of K do not fit tiles %d wide with this epilogue (K = %d)", parts, BN, K);
+    const int room = clusters_at_once(BN, parts);
+    if (tiles > room)
+      G2B_REFUSE("gemm_tc: %lld tiles in %d parts of K are more clusters than the GPU holds at once (%d)", tiles,
+                 parts, room);
+  }
+  const unsigned grid = parts > 1 ? (unsigned)(tiles * parts) : (unsigned)(tiles < sm_count() ? tiles : sm_count());
+  g2b_launch_cluster(gemm_tc_persistent_kernel<BN, STAGES, EPI>, dim3(grid), dim3(THREADS), smem, stream,
+                     (unsigned)parts, ma, mw, mc, M, N, K, rows_of_tiles_per_group((M + BM - 1) / BM, BM, K), parts,
+                     status);
   return g2b_check_launch("gemm_tc (persistent)");
 }
 
@@ -1119,7 +1360,9 @@ static int launch_wstream(const void *A, const void *W, void *C, int M, int N, i
 // (64,4) (64,8) (128,3) (128,6) (256,4); bn = 0 picks one from the sizes: wide tiles when
 // there are plenty of them, narrow tiles with a deeper ring when the grid would not fill
 // the GPU (the ring has to cover the latency of the copies by itself then).  persistent = 1:
-// the variant with one CTA per SM and two accumulators, shapes (128,6) and (256,4).  persistent
+// the variant with one CTA per SM and two accumulators, shapes (128,6) and (256,4), bn = 0 lets
+// the launcher choose between them; with fewer tiles than half the SMs it takes K in parts over
+// a cluster (persistent = 11 to 14 asks for 1 to 4 parts).  persistent
 // = 2: pairs of CTAs on 256 x 256 tiles, shapes (256,6) and (256,4).  persistent = 3 (at most
 // 128 rows; stages is ignored, bn = 1 to 4 asks for that many parts of K, anything else lets
 // the launcher choose): the weight-streaming kernel with K split over a cluster.
@@ -1132,7 +1375,7 @@ extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, 
   if (((uintptr_t)A | (uintptr_t)W) & 15) G2B_REFUSE("gemm_tc: operands must be 16-byte aligned");
   if (epi == EPI_SWIGLU_BF16 && N % 16) G2B_REFUSE("gemm_tc: gated output needs N %% 16 == 0, N=%d", N);
   if (!status) G2B_REFUSE("gemm_tc: no status word");
-  if (bn == 0) {
+  if (bn == 0 && persistent != 1 && persistent < 11) {
     const long long tiles128 = (long long)((M + BM - 1) / BM) * ((N + 127) / 128);
     if (tiles128 >= 2 * 148) { bn = 128; stages = 3; }
     else { bn = 64; stages = 4; }
@@ -1153,6 +1396,17 @@ extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, 
     G2B_CASE(EPI_STORE_BF16) G2B_CASE(EPI_STORE_F32) G2B_CASE(EPI_ACCUM_F32) G2B_CASE(EPI_SWIGLU_BF16)
 #undef G2B_CASE
     G2B_REFUSE("gemm_tc: unknown epilogue %d", epi);
+  }
+  int parts = 1;
+  if (persistent == 1 || persistent >= 11) {
+    // tile width 0: the launcher chooses width and parts of K; a given width: the parts only
+    // (persistent = 11 to 14: the caller's 1 to 4 parts)
+    int w = bn, p = 1;
+    if (bn != 0 && bn != 128 && bn != 256) G2B_REFUSE("gemm_tc: no persistent kernel for tile width %d", bn);
+    if (persistent == 1 || bn == 0) choose_persistent(M, N, K, epi, &w, &p, bn);
+    if (persistent >= 11) p = persistent - 10;
+    if (bn == 0) { bn = w; stages = w == 256 ? 4 : 6; }
+    parts = p;
   }
   CUtensorMap ma, mw;
   int rc = make_map(&ma, A, M, K, lda, BM);
@@ -1176,7 +1430,7 @@ extern "C" int g2b_gemm_tc(const void *A, const void *W, void *C, int M, int N, 
   if (rc) return rc;
 #define G2B_CASE(BN_, ST_, E) \
   if (persistent && bn == BN_ && stages == ST_ && epi == E)                                        \
-    return launch_persistent<BN_, ST_, E>(ma, mw, C, M, N, K, ldc, status, stream);
+    return launch_persistent<BN_, ST_, E>(ma, mw, C, M, N, K, ldc, parts, status, stream);
 #define G2B_SHAPE(BN_, ST_) \
   G2B_CASE(BN_, ST_, EPI_STORE_BF16) G2B_CASE(BN_, ST_, EPI_STORE_F32) \
   G2B_CASE(BN_, ST_, EPI_ACCUM_F32) G2B_CASE(BN_, ST_, EPI_SWIGLU_BF16)

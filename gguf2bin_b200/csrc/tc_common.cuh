@@ -47,7 +47,25 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
 }
 // true when the phase with the given parity has completed; false after SPIN_LIMIT polls
+// One probe first (test_wait: about 45 cycles on a B200), then try_wait, which may put the
+// thread to sleep but costs about 170 cycles even when the phase completed long ago.  More
+// probes take issue slots from the warps that work (measured in the prompt attention).
+#ifndef G2B_WAIT_PROBES
+#define G2B_WAIT_PROBES 1
+#endif
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+#pragma unroll 1
+  for (int i = 0; i < G2B_WAIT_PROBES; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
   for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
     uint32_t done;
     asm volatile(
@@ -174,6 +192,21 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
 // every thread of both CTAs: all of them have arrived, and what they wrote before is visible
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// mbar_wait for a barrier of this CTA on which another CTA of the cluster arrives
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
 }
 // one arrival on a barrier given by its address in the cluster's window (this CTA's or the peer's)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {

@@ -175,7 +175,7 @@ def _wstream_case(M: int, N: int, K: int) -> bool:
 def _tc_shape(M: int, N: int, out: torch.Tensor = None, K: int = 0):
     """(tile width, stages, persistent) of the tcgen05 product; (0, 0, False) lets the launcher
     choose.  Prompts (more than one row of tiles) take the persistent kernel when C can be
-    written as tiles: wide tiles when there are enough of them to fill the GPU; long prompts
+    written as tiles (the launcher picks the tile width, and with few tiles K in parts); long prompts
     take pairs of CTAs (persistent = 2; measured 4-9 % faster from 4,096 rows on, the same or
     slower at 2,048)."""
     if M <= 128:                       # one row of tiles: the weights stream, as in decode
@@ -183,10 +183,9 @@ def _tc_shape(M: int, N: int, out: torch.Tensor = None, K: int = 0):
             return (0, 0, 3)           # 128 rows of W per CTA, K split over a cluster
         return (128, 3, False) if N >= 32768 else (64, 8, False)
     if out is not None and out.data_ptr() % 16 == 0 and (out.stride(0) * out.element_size()) % 16 == 0:
-        tiles_m = -(-M // 128)
         if M >= 4096 and -(-M // 256) * -(-N // 256) >= _sm_count(out.device) // 2:
             return (256, 6, 2)               # long prompts: pairs of CTAs on 256 x 256 tiles
-        return (256, 4, True) if tiles_m * -(-N // 256) >= 96 else (128, 6, True)
+        return (0, 0, True)                  # the launcher picks the width and, with few tiles, parts of K
     return (0, 0, False)
 
 

@@ -488,31 +488,43 @@ def test_attention_over_tens_of_thousands_of_keys(window):
                                atol=2.0 ** -7 * max(1, np.abs(ref).max()), rtol=0, err_msg="decode at 40,000 keys")
 
 
-def _check_gemm_tc(M, N, K, bn, stages, persistent):
+def _check_gemm_tc_epilogue(M, N, K, bn, stages, persistent, epi):
+    """One epilogue of the tcgen05 product against float64."""
     from gguf2bin_b200 import kernels_bf16
     a, w = rnd(M, K, dtype=torch.bfloat16, seed=80), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=81)
     ref = a.double() @ w.double().T
     tol = 1e-5 * math.sqrt(K) * max(1.0, ref.abs().max().item())
-    out = torch.full((M, N), 7.0, device=DEV)
-    kernels_bf16._gemm_tc(a, w, out, kernels_bf16.EPI_STORE_F32, bn, stages, persistent)
-    kernels_bf16.check_status()
-    assert (out.double() - ref).abs().max().item() < tol
-    base = rnd(M, N, seed=82)
-    acc = base.clone()
-    kernels_bf16._gemm_tc(a, w, acc, kernels_bf16.EPI_ACCUM_F32, bn, stages, persistent)
-    assert (acc.double() - base.double() - ref).abs().max().item() < tol
-    out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
-    kernels_bf16._gemm_tc(a, w, out16, kernels_bf16.EPI_STORE_BF16, bn, stages, persistent)
-    assert (out16.double() - ref).abs().max().item() <= ref.abs().max().item() * 2.0 ** -8 + tol
-    if N % 16 == 0:
+    if epi == kernels_bf16.EPI_STORE_F32:
+        out = torch.full((M, N), 7.0, device=DEV)
+        kernels_bf16._gemm_tc(a, w, out, epi, bn, stages, persistent)
+        kernels_bf16.check_status()
+        assert (out.double() - ref).abs().max().item() < tol
+    elif epi == kernels_bf16.EPI_ACCUM_F32:
+        base = rnd(M, N, seed=82)
+        acc = base.clone()
+        kernels_bf16._gemm_tc(a, w, acc, epi, bn, stages, persistent)
+        assert (acc.double() - base.double() - ref).abs().max().item() < tol
+    elif epi == kernels_bf16.EPI_STORE_BF16:
+        out16 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        kernels_bf16._gemm_tc(a, w, out16, epi, bn, stages, persistent)
+        assert (out16.double() - ref).abs().max().item() <= ref.abs().max().item() * 2.0 ** -8 + tol
+    else:
         I = N // 2
         g = ref.view(M, I // 8, 2, 8)[:, :, 0].reshape(M, I)
         u = ref.view(M, I // 8, 2, 8)[:, :, 1].reshape(M, I)
         want = (g / (1 + torch.exp(-g))) * u
         mid = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
-        kernels_bf16._gemm_tc(a, w, mid, kernels_bf16.EPI_SWIGLU_BF16, bn, stages, persistent)
+        kernels_bf16._gemm_tc(a, w, mid, epi, bn, stages, persistent)
         assert (mid.double() - want).abs().max().item() <= want.abs().max().item() * 2.0 ** -8 + tol
     kernels_bf16.check_status()
+
+
+def _check_gemm_tc(M, N, K, bn, stages, persistent):
+    from gguf2bin_b200 import kernels_bf16
+    for epi in (kernels_bf16.EPI_STORE_F32, kernels_bf16.EPI_ACCUM_F32, kernels_bf16.EPI_STORE_BF16):
+        _check_gemm_tc_epilogue(M, N, K, bn, stages, persistent, epi)
+    if N % 16 == 0:
+        _check_gemm_tc_epilogue(M, N, K, bn, stages, persistent, kernels_bf16.EPI_SWIGLU_BF16)
 
 
 @pytest.mark.parametrize("bn,stages", [(64, 4), (64, 8), (128, 3), (128, 6), (256, 4), (0, 0)])
@@ -530,6 +542,42 @@ def test_gemm_tc_persistent(M, N, K, bn, stages):
     """The persistent variant: fewer tiles than SMs, and several tiles per CTA (both
     accumulators in use, the ring running across tile borders), ragged tails, every epilogue."""
     _check_gemm_tc(M, N, K, bn, stages, True)
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 528, 1096), (129, 256, 2048), (1000, 1008, 4096), (640, 2048, 1024),
+                                   (2048, 1024, 3072), (256, 1024, 3072 + 8)])
+def test_gemm_tc_persistent_k_in_parts(M, N, K):
+    """Few tiles: the persistent kernel takes K in 2, 3 or 4 parts over a cluster, whose ranks
+    exchange their partial tiles through the cluster's shared memory and add them in rank order.
+    Every epilogue and both tile widths, by hand and as the launcher chooses (width 0); a number
+    of parts that the tile, the epilogue or the GPU cannot take is refused, never computed wrongly;
+    the same bits on every run."""
+    from gguf2bin_b200 import kernels_bf16
+    from gguf2bin_b200.kernels import KernelError
+    ran = {}
+    for bn, stages in ((128, 6), (256, 4)):
+        for parts in (2, 3, 4):
+            for epi in (kernels_bf16.EPI_ACCUM_F32, kernels_bf16.EPI_STORE_F32, kernels_bf16.EPI_STORE_BF16,
+                        kernels_bf16.EPI_SWIGLU_BF16):
+                try:
+                    _check_gemm_tc_epilogue(M, N, K, bn, stages, 10 + parts, epi)
+                    ran[epi] = ran.get(epi, 0) + 1
+                except KernelError as e:
+                    assert "parts of K" in str(e), str(e)
+            a, w = rnd(M, K, dtype=torch.bfloat16, seed=80), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=81)
+            outs = []
+            try:
+                for _ in range(3):
+                    out = torch.ones(M, N, device=DEV)
+                    kernels_bf16._gemm_tc(a, w, out, kernels_bf16.EPI_ACCUM_F32, bn, stages, 10 + parts)
+                    outs.append(out)
+            except KernelError:
+                continue
+            assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2]), (bn, parts)
+    assert all(ran.get(epi, 0) >= 1 for epi in (0, 1, 2, 3)), ran
+    _check_gemm_tc(M, N, K, 0, 0, True)
+    _check_gemm_tc(M, N, K, 128, 6, True)
+    _check_gemm_tc(M, N, K, 256, 4, True)
 
 
 @pytest.mark.parametrize("bn,stages", [(256, 6), (256, 4)])
