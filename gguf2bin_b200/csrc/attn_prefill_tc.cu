@@ -74,6 +74,26 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// two floats at a time (one instruction of the packed kind each)
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}\n"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}\n"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t *>(&v);
@@ -94,7 +114,10 @@ __device__ unsigned long long g2b_timing[16];
 #define TFLUSH(slot)
 #endif
 
-__global__ void __launch_bounds__(THREADS, 2)
+#ifndef G2B_ATTN_MINBLOCKS
+#define G2B_ATTN_MINBLOCKS 2
+#endif
+__global__ void __launch_bounds__(THREADS, G2B_ATTN_MINBLOCKS)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_kv, bf16 *__restrict__ out,
                        const int4 *__restrict__ tiles, const int *__restrict__ page_table, int P,
@@ -307,8 +330,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       float mxa[2] = {-INFINITY, -INFINITY}, mxb[2] = {-INFINITY, -INFINITY};       // short chains
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        mxa[j & 1] = fmaxf(mxa[j & 1], fmaxf(__uint_as_float(sr[4 * j]), __uint_as_float(sr[4 * j + 1])));
-        mxb[j & 1] = fmaxf(mxb[j & 1], fmaxf(__uint_as_float(sr[4 * j + 2]), __uint_as_float(sr[4 * j + 3])));
+        mxa[j & 1] = max3(mxa[j & 1], __uint_as_float(sr[4 * j]), __uint_as_float(sr[4 * j + 1]));
+        mxb[j & 1] = max3(mxb[j & 1], __uint_as_float(sr[4 * j + 2]), __uint_as_float(sr[4 * j + 3]));
       }
       float mx_a = fmaxf(mxa[0], mxa[1]), mx_b = fmaxf(mxb[0], mxb[1]);
       mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
@@ -356,20 +379,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       const float neg_b = m_b == -INFINITY ? 0.f : -m_b;
       TICK(t_ex);
       uint32_t pk[16];                             // [2j + s]: row (s ? rB : rA), packed column 4j + c
-      float la2[2] = {0.f, 0.f}, lb2[2] = {0.f, 0.f};
+      // two scores at a time: one packed multiply-add into the exponent, one packed addition into the sums
+      float2 la2 = make_float2(0.f, 0.f), lb2 = make_float2(0.f, 0.f);
+      const float2 sc2 = make_float2(scale_log2, scale_log2);
+      const float2 na2 = make_float2(neg_a, neg_a), nb2 = make_float2(neg_b, neg_b);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float a0 = ex2(fmaf(__uint_as_float(sr[4 * j]), scale_log2, neg_a));
-        const float a1 = ex2(fmaf(__uint_as_float(sr[4 * j + 1]), scale_log2, neg_a));
-        const float b0 = ex2(fmaf(__uint_as_float(sr[4 * j + 2]), scale_log2, neg_b));
-        const float b1 = ex2(fmaf(__uint_as_float(sr[4 * j + 3]), scale_log2, neg_b));
-        la2[j & 1] += a0 + a1;
-        lb2[j & 1] += b0 + b1;
-        pk[2 * j] = pack2(a0, a1);
-        pk[2 * j + 1] = pack2(b0, b1);
+        const float2 xa = fma2(make_float2(__uint_as_float(sr[4 * j]), __uint_as_float(sr[4 * j + 1])), sc2, na2);
+        const float2 xb = fma2(make_float2(__uint_as_float(sr[4 * j + 2]), __uint_as_float(sr[4 * j + 3])), sc2, nb2);
+        const float2 pa = make_float2(ex2(xa.x), ex2(xa.y)), pb = make_float2(ex2(xb.x), ex2(xb.y));
+        la2 = add2(la2, pa);
+        lb2 = add2(lb2, pb);
+        pk[2 * j] = pack2(pa.x, pa.y);
+        pk[2 * j + 1] = pack2(pb.x, pb.y);
       }
-      l_a += la2[0] + la2[1];
-      l_b += lb2[0] + lb2[1];
+      l_a += la2.x + la2.y;
+      l_b += lb2.x + lb2.y;
       TOCK(13, t_ex);
       TICK(t_st);
       tmem_st_16x128b_x8(sbuf, pk);                // P over the first 32 columns of this S buffer

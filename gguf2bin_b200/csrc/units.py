@@ -25,4 +25,5 @@ def all_units() -> list:
 # Builds that only the tests load: the tcgen05 kernels with a short wait limit and a copy role
 # that issues nothing, so that a test can see every other role give up and the kernel return.
 WAITS_RUN_OUT = ("G2B_SPIN_LIMIT=4096", "G2B_TEST_NO_PRODUCER")
-TEST_UNITS = [("gemm_tc.cu", WAITS_RUN_OUT), ("attn_prefill_tc.cu", ("HD=128",) + WAITS_RUN_OUT)]
+TEST_UNITS = [("gemm_tc.cu", WAITS_RUN_OUT), ("attn_prefill_tc.cu", ("HD=128",) + WAITS_RUN_OUT),
+              ("attn_prefill_tc_split.cu", ("HD=128",) + WAITS_RUN_OUT)]

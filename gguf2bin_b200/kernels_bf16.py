@@ -15,7 +15,8 @@ DECODE_CHUNK_KEYS = 256              # keys per CTA of the decode kernel (attn_d
 
 units.SPECIALISED_SOURCES[:] = [("attn_decode.cu", ()), ("attn_decode.cu", ("ATTN_DECODE_PAGES=2",)),
                                 ("attn_decode_noalloc.cu", ()),
-                                ("attn_prefill.cu", ()), ("attn_prefill_tc.cu", ())]
+                                ("attn_prefill.cu", ()), ("attn_prefill_tc.cu", ()),
+                                ("attn_prefill_tc_split.cu", ())]
 units.BF16_UNITS[:] = [("gemm_small.cu", ()), ("gemm_tc.cu", ())]
 
 
@@ -234,11 +235,16 @@ USE_TC_ATTENTION = True      # prompt attention on tcgen05 (else the mma.sync ke
 
 
 def attn_prefill_tc(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-                    scale, defines=()) -> None:
-    """Prompt attention on the tcgen05 tensor cores over the step's 128-row query tiles.
+                    scale, defines=(), split=None) -> None:
+    """Prompt attention on the tcgen05 tensor cores over the step's 128-row query tiles.  Two
+    kernels with the same interface: two CTAs per SM, a tile each (``attn_prefill_tc.cu``), and,
+    for work lists of at most two tiles per SM (``split``; default by that rule), one CTA per
+    SM whose two softmax groups share a tile's pages (``attn_prefill_tc_split.cu``).
     ``defines``: another build of the source (the tests' build whose waits run out)."""
     from ctypes import c_longlong
-    f = _fn("attn_prefill_tc.cu", "g2b_attn_prefill_tc",
+    if split is None:
+        split = ctx.n_attn_tiles_wide * n_heads <= 2 * _sm_count(q.device)
+    f = _fn("attn_prefill_tc_split.cu" if split else "attn_prefill_tc.cu", "g2b_attn_prefill_tc",
             [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
              c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
             defines=(f"HD={head_dim}",) + tuple(defines))

@@ -394,7 +394,7 @@ def test_gemm_small(M, N, K):
         assert (mid.double() - want).abs().max().item() <= want.abs().max().item() * 2.0 ** -8 + tol
 
 
-@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05", "tcgen05 split"])
 @pytest.mark.parametrize("nh,nkv,hd,window", [(16, 8, 128, 0), (5, 1, 128, 0), (6, 2, 64, 0), (4, 2, 64, 100),
                                               (2, 2, 128, 33)])
 def test_attn_prefill(nh, nkv, hd, window, kernel):
@@ -422,7 +422,8 @@ def test_attn_prefill(nh, nkv, hd, window, kernel):
         kernels_bf16.attn_prefill(q, out, cache, ctx, nh, nkv, hd, ps, window, 1 / math.sqrt(hd))
     else:
         ctx = SimpleNamespace(page_table=table, all_single=False, n_attn_tiles_wide=len(tiles), attn_tiles_wide=tt)
-        kernels_bf16.attn_prefill_tc(q, out, cache, ctx, nh, nkv, hd, ps, window, 1 / math.sqrt(hd))
+        kernels_bf16.attn_prefill_tc(q, out, cache, ctx, nh, nkv, hd, ps, window, 1 / math.sqrt(hd),
+                                     split=kernel.endswith("split"))
         kernels_bf16.check_status()
     got = out.float().cpu().numpy().reshape(T, nh, hd)
     t = 0
@@ -442,10 +443,11 @@ def row_attention(q_row, K, V, nh, pos, window=0):
     return last_row_attention(q_row, K[:pos + 1], V[:pos + 1], nh, pos + 1 - lo if window > 0 else 0)
 
 
+@pytest.mark.parametrize("split", [False, True])
 @pytest.mark.parametrize("window", [0, 5000])
-def test_attention_over_tens_of_thousands_of_keys(window):
+def test_attention_over_tens_of_thousands_of_keys(window, split):
     """A prompt of 20,000 tokens (157 query tiles, up to 313 pages per tile) through the tcgen05
-    prompt attention, then one token at position 39,999 of a sequence of 40,000 through the
+    prompt attention (both kernels), then one token at position 39,999 of a sequence of 40,000 through the
     decode attention: rows at the start, at tile and page edges, in the middle and at the end
     against the plain attention of that row; a planted key 19,000 positions back stands out."""
     from types import SimpleNamespace
@@ -464,7 +466,7 @@ def test_attention_over_tens_of_thousands_of_keys(window):
     ctx = SimpleNamespace(page_table=table, all_single=False, n_attn_tiles_wide=len(tiles),
                           attn_tiles_wide=torch.tensor(tiles, dtype=torch.int32, device=DEV))
     out = torch.zeros_like(q)
-    kernels_bf16.attn_prefill_tc(q, out, cache, ctx, nh, nkv, hd, ps, window, scale)
+    kernels_bf16.attn_prefill_tc(q, out, cache, ctx, nh, nkv, hd, ps, window, scale, split=split)
     kernels_bf16.check_status()
     K, V = Ks[0].float().cpu().numpy(), Vs[0].float().cpu().numpy()
     for pos in (0, 63, 64, 127, 128, 9999, 16383, 16384, 19700, 19999):

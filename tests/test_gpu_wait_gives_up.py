@@ -47,7 +47,8 @@ def test_product_whose_copies_never_come(what, M, N, K, bn, stages, mode):
     assert (out.double() - ref).abs().max().item() < 1e-5 * math.sqrt(K) * max(1.0, ref.abs().max().item())
 
 
-def test_prompt_attention_whose_copies_never_come():
+@pytest.mark.parametrize("split", [False, True])
+def test_prompt_attention_whose_copies_never_come(split):
     from types import SimpleNamespace
     from gguf2bin_b200 import kernels_bf16
     from gguf2bin_b200.csrc.units import WAITS_RUN_OUT
@@ -68,11 +69,12 @@ def test_prompt_attention_whose_copies_never_come():
     tiles = torch.tensor([[0, 128, T - 128, 128], [0, 0, 128, 0]], dtype=torch.int32, device=DEV)
     ctx = SimpleNamespace(attn_tiles_wide=tiles, n_attn_tiles_wide=2, page_table=table)
     out = torch.zeros_like(q)
-    kernels_bf16.attn_prefill_tc(q, out, cache, ctx, nh, nkv, hd, ps, 0, 1 / math.sqrt(hd), defines=WAITS_RUN_OUT)
+    kernels_bf16.attn_prefill_tc(q, out, cache, ctx, nh, nkv, hd, ps, 0, 1 / math.sqrt(hd), defines=WAITS_RUN_OUT,
+                                 split=split)
     torch.cuda.synchronize()
     with pytest.raises(KernelError, match=r"attn_prefill_tc.*gave up waiting"):
         kernels_bf16.check_status()
-    kernels_bf16.attn_prefill_tc(q, out, cache, ctx, nh, nkv, hd, ps, 0, 1 / math.sqrt(hd))
+    kernels_bf16.attn_prefill_tc(q, out, cache, ctx, nh, nkv, hd, ps, 0, 1 / math.sqrt(hd), split=split)
     kernels_bf16.check_status()
     ref = P.causal_attention(q.float().cpu().numpy().reshape(T, nh, hd), K.float().numpy(), V.float().numpy(),
                              np.float32)
