@@ -1166,37 +1166,43 @@ static int rows_of_tiles_per_group(int tiles_m, int tile_rows, int K) {
 // same shared memory).
 static int clusters_at_once(int bn, int sz) {
   static G2bPerDevice fit[2][5];                  // value[device] = answer + 1; 0 = not asked yet
-  const int dev = g2b_current_device(), w = bn == 256 ? 1 : 0;
+  const int dev = g2b_current_device();
   if (sz < 2 || sz > 4) return 0;
-  if (dev >= 0 && fit[w][sz].value[dev]) return fit[w][sz].value[dev] - 1;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(sz * sm_count()));
-  cfg.blockDim = dim3(THREADS);
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)sz;
-  attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  int n = 0;
-  cudaError_t e;
-  if (w) {
-    cfg.dynamicSmemBytes = SmemP<256, 4>::TOTAL;
-    cudaFuncSetAttribute(gemm_tc_persistent_kernel<256, 4, EPI_ACCUM_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         SmemP<256, 4>::TOTAL);
-    e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_persistent_kernel<256, 4, EPI_ACCUM_F32>, &cfg);
-  } else {
-    cfg.dynamicSmemBytes = SmemP<128, 6>::TOTAL;
-    cudaFuncSetAttribute(gemm_tc_persistent_kernel<128, 6, EPI_ACCUM_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         SmemP<128, 6>::TOTAL);
-    e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_persistent_kernel<128, 6, EPI_ACCUM_F32>, &cfg);
+  if (dev < 0 || !fit[bn == 256][sz].value[dev]) {
+    // all six answers at the first question on a device (not one by one in the middle of a step)
+    for (int w = 0; w < 2; ++w)
+      for (int s = 2; s <= 4; ++s) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(s * sm_count()));
+        cfg.blockDim = dim3(THREADS);
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)s;
+        attr[0].val.clusterDim.y = attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        cudaError_t e;
+        if (w) {
+          cfg.dynamicSmemBytes = SmemP<256, 4>::TOTAL;
+          cudaFuncSetAttribute(gemm_tc_persistent_kernel<256, 4, EPI_ACCUM_F32>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, SmemP<256, 4>::TOTAL);
+          e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_persistent_kernel<256, 4, EPI_ACCUM_F32>, &cfg);
+        } else {
+          cfg.dynamicSmemBytes = SmemP<128, 6>::TOTAL;
+          cudaFuncSetAttribute(gemm_tc_persistent_kernel<128, 6, EPI_ACCUM_F32>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, SmemP<128, 6>::TOTAL);
+          e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_persistent_kernel<128, 6, EPI_ACCUM_F32>, &cfg);
+        }
+        if (e != cudaSuccess) {
+          cudaGetLastError();
+          n = sm_count() / s / 2;                  // a cautious guess
+        }
+        if (dev >= 0) fit[w][s].value[dev] = n + 1;
+        else if (w == (bn == 256) && s == sz) return n;
+      }
   }
-  if (e != cudaSuccess) {
-    cudaGetLastError();
-    n = sm_count() / sz / 2;                       // a cautious guess
-  }
-  if (dev >= 0) fit[w][sz].value[dev] = n + 1;
-  return n;
+  return fit[bn == 256][sz].value[dev] - 1;
 }
 
 // The persistent kernel's tile width (128 with six stages or 256 with four) and parts of K for
