@@ -99,6 +99,7 @@ class Cache:
                                            device=self.device)
         self.seq_state = torch.zeros((n_slots, SEQ_STATE_WORDS), dtype=torch.int32,
                                      device=self.device)
+        self._views: dict = {}
 
     # ---- sequences ---------------------------------------------------------
     def open_sequence(self) -> Sequence:
@@ -117,13 +118,18 @@ class Cache:
 
     # ---- views -------------------------------------------------------------
     def view(self, layer: int):
-        if layer not in self._layer_group:
-            return None
-        key, idx = self._layer_group[layer]
-        g = self.groups[key]
-        if isinstance(g["need"], KVNeed):
-            return KVView(g["storage"][idx], self.page_size)
-        return StateView(g["storage"][idx])
+        """The layer's part of its group's storage (made once: the storage never moves)."""
+        v = self._views.get(layer, self)
+        if v is self:
+            if layer not in self._layer_group:
+                v = None
+            else:
+                key, idx = self._layer_group[layer]
+                g = self.groups[key]
+                v = (KVView(g["storage"][idx], self.page_size) if isinstance(g["need"], KVNeed)
+                     else StateView(g["storage"][idx]))
+            self._views[layer] = v
+        return v
 
     def bytes(self) -> int:
         return sum(g["storage"].numel() * g["storage"].element_size()

@@ -60,6 +60,15 @@ def _need(t: torch.Tensor, dtype: torch.dtype, what: str) -> None:
 
 
 _fn_cache: dict = {}
+_bf16 = None              # the bfloat16 bindings (they import this module, so they are bound at first use)
+
+
+def _bf16_mod():
+    global _bf16
+    if _bf16 is None:
+        from . import kernels_bf16 as m
+        _bf16 = m
+    return _bf16
 
 
 def _fn(unit: str, name: str, argtypes, defines=()):
@@ -236,8 +245,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
     """The product a layer asks for; picks the kernel from the dtypes and sizes.  Anything
     that is not all-bfloat16 runs on the float32 kernel (true 32-bit arithmetic)."""
     if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
-        from . import kernels_bf16
-        if kernels_bf16.linear_bf16(a, w, out, accumulate):
+        if (_bf16 or _bf16_mod()).linear_bf16(a, w, out, accumulate):
             return
     gemm_simt(a, w, out, accumulate)
 
@@ -290,8 +298,7 @@ def attention(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size
     """Attention of a step: the tensor-core kernels when they take the case, else the
     32-bit kernel."""
     if q.dtype == torch.bfloat16:
-        from . import kernels_bf16
-        if kernels_bf16.attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim,
+        if (_bf16 or _bf16_mod()).attention_bf16(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim,
                                        page_size, window, scale):
             return
     attn_generic(q, out, cache_pages, ctx.tok_pos, ctx.tok_seq, ctx.page_table, n_heads,
@@ -302,8 +309,7 @@ def normed_product(x32, eps, w, out, gate_block=None) -> bool:
     """out = rmsnorm_without_weight(x32) @ w.T (or its SiLU gate) in one kernel; False when no
     kernel takes the case (the caller then runs the norm and the product one after the other)."""
     if w.dtype == torch.bfloat16 and (gate_block is None or gate_block == 8):
-        from . import kernels_bf16
-        return kernels_bf16.normed_product(x32, eps, w, out, gate_block is not None)
+        return (_bf16 or _bf16_mod()).normed_product(x32, eps, w, out, gate_block is not None)
     return False
 
 
@@ -311,8 +317,7 @@ def gate_up_fused(h, w_gate_up, mid, block) -> bool:
     """silu(gate) * up computed inside the product's epilogue; False when no kernel takes
     the case (the caller then runs the product and ``swiglu`` separately)."""
     if h.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16:
-        from . import kernels_bf16
-        return kernels_bf16.gate_up_bf16(h, w_gate_up, mid, block)
+        return (_bf16 or _bf16_mod()).gate_up_bf16(h, w_gate_up, mid, block)
     return False
 
 

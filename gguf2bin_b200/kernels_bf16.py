@@ -2,7 +2,7 @@
 False when it does not take the case (the caller then uses the 32-bit kernel)."""
 from __future__ import annotations
 
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_longlong, c_float, c_int, c_void_p
 
 import torch
 
@@ -75,10 +75,13 @@ _status: dict = {}
 
 def _status_word(device) -> torch.Tensor:
     """The device word in which the tcgen05 kernels report a wait that gave up."""
-    key = torch.device(device)
-    if key not in _status:
-        _status[key] = torch.zeros(1, dtype=torch.int32, device=key)
-    return _status[key]
+    word = _status.get(device)
+    if word is None:
+        key = torch.device(device)
+        if key not in _status:
+            _status[key] = torch.zeros(1, dtype=torch.int32, device=key)
+        word = _status[key]
+    return word
 
 
 def check_status() -> None:
@@ -119,8 +122,28 @@ def _gemm_tc(a, w, out, epi, bn: int = 0, stages: int = 0, persistent=False, def
           _ptr(_status_word(a.device)), _stream())
 
 
+_routes: dict = {}        # (sizes, strides, alignment, output) -> (kernel, tile width, stages, persistent)
+
+
+def _route(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
+    """Which kernel multiplies a by w.T into out, and with which tile shape: decided once per
+    combination of sizes, strides and alignments (a step asks the same few questions a hundred
+    times, and on a prompt's first run the host is what the GPU waits for)."""
+    key = (a.shape, w.shape, a.stride(), w.stride(), out.stride(), out.dtype,
+           (a.data_ptr() | w.data_ptr()) & 15, out.data_ptr() & 15, out.device.index)
+    r = _routes.get(key)
+    if r is None:
+        choice = _pick_product(a, w)
+        shape = _tc_shape(a.shape[0], w.shape[0], out, a.shape[1]) if choice == "tc" else (0, 0, False)
+        if len(_routes) > 4096:
+            _routes.clear()
+        r = _routes[key] = (choice,) + tuple(shape)
+    return r
+
+
 def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool) -> bool:
     """out (=|+=) a @ w.T for bfloat16 a and w on the tensor cores."""
+    choice, bn, stages, persistent = _route(a, w, out)
     if out.stride(1) != 1:
         return False
     if accumulate:
@@ -129,12 +152,11 @@ def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate:
         epi = EPI_ACCUM_F32
     else:
         epi = EPI_STORE_BF16 if out.dtype == torch.bfloat16 else EPI_STORE_F32
-    choice = _pick_product(a, w)
     if choice == "small":
         _gemm_small(a, w, out, epi)
         return True
     if choice == "tc":
-        _gemm_tc(a, w, out, epi, *_tc_shape(a.shape[0], w.shape[0], out, a.shape[1]))
+        _gemm_tc(a, w, out, epi, bn, stages, persistent)
         return True
     return False
 
@@ -205,12 +227,12 @@ def gate_up_bf16(h: torch.Tensor, w_gate_up: torch.Tensor, mid: torch.Tensor, bl
     matrices whose rows alternate 8 gates / 8 ups."""
     if block != 8 or mid.dtype != torch.bfloat16 or mid.stride(1) != 1 or w_gate_up.shape[0] % 16:
         return False
-    choice = _pick_product(h, w_gate_up)
+    choice, bn, stages, persistent = _route(h, w_gate_up, mid)
     if choice == "small":
         _gemm_small(h, w_gate_up, mid, EPI_SWIGLU_BF16)
         return True
     if choice == "tc":
-        _gemm_tc(h, w_gate_up, mid, EPI_SWIGLU_BF16, *_tc_shape(h.shape[0], w_gate_up.shape[0], mid, h.shape[1]))
+        _gemm_tc(h, w_gate_up, mid, EPI_SWIGLU_BF16, bn, stages, persistent)
         return True
     return False
 
@@ -241,7 +263,6 @@ def attn_prefill_tc(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, pag
     for work lists of at most two tiles per SM (``split``; default by that rule), one CTA per
     SM whose two softmax groups share a tile's pages (``attn_prefill_tc_split.cu``).
     ``defines``: another build of the source (the tests' build whose waits run out)."""
-    from ctypes import c_longlong
     if split is None:
         split = ctx.n_attn_tiles_wide * n_heads <= 2 * _sm_count(q.device)
     f = _fn("attn_prefill_tc_split.cu" if split else "attn_prefill_tc.cu", "g2b_attn_prefill_tc",
