@@ -43,7 +43,8 @@ def normed_product(x32: torch.Tensor, eps: float, w: torch.Tensor, out: torch.Te
     (x / sqrt(mean(x^2) + eps)) computed inside the few-row product: the row's factor scales
     the accumulators.  ``gated``: w is a fused gate/up matrix (rows alternating 8 / 8) and out
     gets silu(gate) * up.  False when the case is not taken (more than 16 rows, a K that is
-    split over a cluster or streamed in chunks)."""
+    split over a cluster or streamed in chunks, or a case that a norm kernel and the tcgen05 product do
+    faster: ``_normed_loses``)."""
     M, K = x32.shape
     N = w.shape[0]
     if (x32.dtype != torch.float32 or w.dtype != torch.bfloat16 or x32.stride(1) != 1 or w.stride(1) != 1
@@ -59,6 +60,8 @@ def normed_product(x32: torch.Tensor, eps: float, w: torch.Tensor, out: torch.Te
     elif out.dtype == torch.float32:
         epi = EPI_STORE_F32
     else:
+        return False
+    if _normed_loses(M, N, K):
         return False
     takes = _fn("gemm_small.cu", "g2b_gemm_small_normed_takes", [c_int, c_int, c_int])
     if not takes(M, N, K):
@@ -162,15 +165,14 @@ def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate:
 
 
 def _pick_product(a: torch.Tensor, w: torch.Tensor):
-    """Which kernel multiplies: the weight-streaming mma.sync one up to 16 rows (8 against big
-    weights, where the tcgen05 kernel that splits K over a cluster is faster from 9 rows on:
-    10.7 against 13.4 us for 4096 x 4096 at 16 rows) and for narrow outputs up to 64 rows; the
-    tcgen05 ones otherwise."""
+    """Which kernel multiplies: the weight-streaming mma.sync one up to 16 rows (against big
+    weights up to 8 rows, and not against the largest of them: see ``_wstream_case``) and for
+    narrow outputs up to 64 rows; the tcgen05 ones otherwise."""
     M, N, K = a.shape[0], w.shape[0], a.shape[1]
     small, tc_ = _small_ok(a, w), _tc_ok(a, w)
     big = N >= 2048 and K >= 2048
-    if small and (M <= 8 or (M <= 16 and not big) or (M <= SMALL_M and not _wstream_case(M, N, K) and N < 2048)
-                  or not tc_):
+    if small and ((M <= 8 and not (tc_ and _wstream_case(M, N, K))) or (8 < M <= 16 and not big)
+                  or (M <= SMALL_M and not _wstream_case(M, N, K) and N < 2048) or not tc_):
         return "small"
     if tc_:
         return "tc"
@@ -179,20 +181,43 @@ def _pick_product(a: torch.Tensor, w: torch.Tensor):
 
 def _wstream_case(M: int, N: int, K: int) -> bool:
     """Few rows whose product goes to the kernel with 128 rows of W per CTA and K split over a
-    cluster: from 9 rows against big weights; from 17 rows against the weights of a small
-    model's layers too where it was measured faster (at 64 rows, 1024 x 3072: 8.5 us against
-    17.8 by the mma.sync kernel and 18.4 by one 128 x 64 tile per CTA), but not against its
-    vocabulary (many tiles with a short K), and not wide outputs with K = 1024 beyond 64 rows
-    (6144 x 1024 at 128 rows: 11.7 us against 8.4 by one tile per CTA)."""
+    cluster.  Against big weights (N and K of 2,048 and more), measured at the layer sizes of
+    Qwen3-1.7B to 14B: from 9 to 64 rows always (10.7 against 13.4 us by the mma.sync kernel
+    for 4096 x 4096 at 16 rows); up to 8 rows only against the largest matrices or a very long
+    K (5120 x 17408: 31.6 against 43.8 us; 2048 x 6144: 10.7 against 17.0; but 6144 x 4096:
+    13.5 against 12.5, and the mma.sync kernel can take the norm in front along), never
+    against a vocabulary; from 65 rows only narrow outputs up to 96 rows (24576 x 4096 at 65
+    rows: 54.0 against 39.0 us by the persistent kernel; 4096 x 12288: 22.8 against 24.7).
+    Against the weights of a small model's layers from 17 rows where it was measured faster
+    (at 64 rows, 1024 x 3072: 8.5 us against 17.8 by the mma.sync kernel and 18.4 by one
+    128 x 64 tile per CTA), but not against its vocabulary (many tiles with a short K), and not
+    wide outputs with K = 1024 beyond 64 rows (6144 x 1024 at 128 rows: 11.7 us against 8.4
+    by one tile per CTA)."""
     if M > 128:
         return False
-    if M > 8 and N >= 2048 and K >= 2048:
-        return True
+    if N >= 2048 and K >= 2048:
+        if M <= 8:
+            return N <= 65536 and (N * K >= (24 << 20) or K >= 6144)
+        if M <= 64:
+            return True
+        return N < 8192 and M <= 96
     if M <= 16 or N < 1024 or K < 1024 or N > 16384:
         return False
     if N < 2048:                       # narrow outputs: 1024 x 2048 at 32 rows is 4.9 us by the mma.sync kernel, 6.6 here
         return not (M <= 32 and K <= 2048)
     return M <= 32 or (M <= 64 and N <= 4096)      # wide outputs with a short K
+
+
+def _normed_loses(M: int, N: int, K: int) -> bool:
+    """Whether the few-row product that takes the norm along is the slower way: 9 to 16 rows
+    against big weights (a decode step of 16 sequences at Qwen3-8B sizes: 270 us a layer with it,
+    160 with a norm kernel and the tcgen05 product), and up to 8 rows against the largest
+    matrices (34816 x 5120: 62.4 us against 54.6 + 2.1)."""
+    if N < 2048 or K < 2048:
+        return False
+    if M > 8:
+        return True
+    return N <= 65536 and N * K >= (48 << 20)
 
 
 def _tc_shape(M: int, N: int, out: torch.Tensor = None, K: int = 0):
@@ -204,7 +229,8 @@ def _tc_shape(M: int, N: int, out: torch.Tensor = None, K: int = 0):
     if M <= 128:                       # one row of tiles: the weights stream, as in decode
         if _wstream_case(M, N, K):
             return (0, 0, 3)           # 128 rows of W per CTA, K split over a cluster
-        return (128, 3, False) if N >= 32768 else (64, 8, False)
+        if not (M > 64 and N >= 2048 and K >= 2048 and N <= 65536):      # (else the persistent kernel, below)
+            return (128, 3, False) if N >= 32768 else (64, 8, False)
     if out is not None and out.data_ptr() % 16 == 0 and (out.stride(0) * out.element_size()) % 16 == 0:
         if M >= 4096 and -(-M // 256) * -(-N // 256) >= _sm_count(out.device) // 2:
             return (256, 6, 2)               # long prompts: pairs of CTAs on 256 x 256 tiles
