@@ -355,15 +355,31 @@ attn_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__
   const bool active = 4 * lane < HD;
   float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
   float den = 0.f;
-  for (int i = c0 + warp; i <= c1; i += COMBINE_WARPS) {
-    const float2 mli = ml[i];
-    const float w = fast_exp2(mli.x - M);
-    if (active) {
-      const float4 o = *reinterpret_cast<const float4 *>(part_o + (th * n_chunks + i) * HD + 4 * lane);
-      num.x = fmaf(w, o.x, num.x); num.y = fmaf(w, o.y, num.y);
-      num.z = fmaf(w, o.z, num.z); num.w = fmaf(w, o.w, num.w);
+  // eight chunks' loads in flight at a time (a token far into its sequence has hundreds of chunks,
+  // and one load after the other cost 20 us at 65,536 keys); they are added in the same order
+  constexpr int AHEAD = 8;
+  for (int i0 = c0 + warp; i0 <= c1; i0 += AHEAD * COMBINE_WARPS) {
+    float2 mlv[AHEAD];
+    float4 ov[AHEAD];
+#pragma unroll
+    for (int u = 0; u < AHEAD; ++u) {
+      const int i = i0 + u * COMBINE_WARPS;
+      if (i <= c1) {
+        mlv[u] = ml[i];
+        if (active) ov[u] = *reinterpret_cast<const float4 *>(part_o + (th * n_chunks + i) * HD + 4 * lane);
+      }
     }
-    den = fmaf(w, mli.y, den);
+#pragma unroll
+    for (int u = 0; u < AHEAD; ++u) {
+      if (i0 + u * COMBINE_WARPS <= c1) {
+        const float w = fast_exp2(mlv[u].x - M);
+        if (active) {
+          num.x = fmaf(w, ov[u].x, num.x); num.y = fmaf(w, ov[u].y, num.y);
+          num.z = fmaf(w, ov[u].z, num.z); num.w = fmaf(w, ov[u].w, num.w);
+        }
+        den = fmaf(w, mlv[u].y, den);
+      }
+    }
   }
   if (active) {
     s_acc[warp][4 * lane] = num.x; s_acc[warp][4 * lane + 1] = num.y;

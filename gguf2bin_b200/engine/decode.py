@@ -98,6 +98,8 @@ class DecodeRunner:
         self._meta.copy_(self._meta_host, non_blocking=True)
         self._uploaded.record()
         self.ctx.slots = [s.slot for s in session.seqs]
+        # the page table is as wide as what is reserved; kernels that size their work by the keys plan with what is there
+        self.ctx.kv_len_hint = max(s.length for s in session.seqs) + 1
         self.owner = session
 
     def _launch(self) -> None:

@@ -14,6 +14,7 @@ FAST_HEAD_SIZES = (64, 128)          # head sizes the tensor-core attention kern
 DECODE_CHUNK_KEYS = 256              # keys per CTA of the decode kernel (attn_decode.cu)
 
 units.SPECIALISED_SOURCES[:] = [("attn_decode.cu", ()), ("attn_decode.cu", ("ATTN_DECODE_PAGES=2",)),
+                                ("attn_decode.cu", ("ATTN_DECODE_PAGES=6",)), ("attn_decode.cu", ("ATTN_DECODE_PAGES=8",)),
                                 ("attn_decode_noalloc.cu", ()),
                                 ("attn_prefill.cu", ()), ("attn_prefill_tc.cu", ()),
                                 ("attn_prefill_tc_split.cu", ())]
@@ -312,22 +313,47 @@ def attn_prefill(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_s
 
 
 DECODE_FINE_BELOW = 200       # CTAs of 256-key chunks below which the chunks are halved (measured: two sequences)
+DECODE_CTAS_PER_SM = 3        # CTAs of the decode kernel that an SM holds at head size 128 (64 KB of panels each)
+
+
+def decode_chunk_pages(units: int, pages: int, head_dim: int, slots: int) -> int:
+    """Pages of 64 keys per CTA of the decode attention: 4 (chunks of 256 keys) as a rule; 2
+    when that gives fewer CTAs than the GPU holds at once (one or two sequences); 6 or 8 when
+    the CTAs of 4 pages come in one round and a bit (8 sequences at 2,048 to 2,300 keys: 512 to
+    576 CTAs for 444 places took 16.5 to 17.2 us, 384 CTAs at 1,536 keys 11.8) and longer chunks
+    make it fewer rounds' worth of pages.  ``units``: tokens x kv heads x head tiles;
+    ``slots``: CTAs the GPU holds at once."""
+    ctas4 = units * -(-pages // 4)
+    if ctas4 < DECODE_FINE_BELOW:
+        return 2
+    best, cost = 4, -(-ctas4 // slots) * 4
+    if head_dim == 128:
+        for ppc in (6, 8):
+            c = -(-(units * -(-pages // ppc)) // slots) * ppc
+            if c < cost:
+                best, cost = ppc, c
+    return best
 
 
 def attn_decode(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
-                scale, fine=None) -> None:
+                scale, fine=None, pages=None) -> None:
     """One token per sequence: split-key attention with partial results in scratch memory
-    and a combine pass.  A CTA takes a chunk of 256 keys of one kv head; when that gives
-    fewer CTAs than the GPU holds at once (one or two sequences), chunks of 128 keys
-    (``fine``; default by that rule) give twice as many."""
+    and a combine pass.  A CTA takes a chunk of keys of one kv head: 256 as a rule, 128, 384 or
+    512 where ``decode_chunk_pages`` says so (``fine`` = 128; ``pages`` = pages of 64 keys per
+    CTA, 2 to 8; default by that rule)."""
     T = q.shape[0]
     defines = (f"HD={head_dim}",)
-    chunk_keys = DECODE_CHUNK_KEYS
-    if fine is None:
-        tiles = n_kv_heads * -(-(n_heads // n_kv_heads) // 16)
-        fine = T * tiles * -(-max(int(ctx.max_kv_len), 1) // DECODE_CHUNK_KEYS) < DECODE_FINE_BELOW
-    if fine:
-        defines, chunk_keys = defines + ("ATTN_DECODE_PAGES=2",), DECODE_CHUNK_KEYS // 2
+    if pages is None:
+        if fine is None:
+            tiles = n_kv_heads * -(-(n_heads // n_kv_heads) // 16)
+            keys = getattr(ctx, "kv_len_hint", 0) or ctx.max_kv_len       # max_kv_len may be the reserved length
+            pages = decode_chunk_pages(T * tiles, -(-max(int(keys), 1) // 64), head_dim,
+                                       DECODE_CTAS_PER_SM * _sm_count(q.device))
+        else:
+            pages = 2 if fine else 4
+    if pages != 4:
+        defines = defines + (f"ATTN_DECODE_PAGES={pages}",)
+    chunk_keys = 64 * pages
     n_chunks = -(-max(int(ctx.max_kv_len), 1) // chunk_keys)
     ws = ctx.workspace
     part_o = ws.buffer("attn.part_o", (T * n_heads * n_chunks * head_dim,), torch.float32)

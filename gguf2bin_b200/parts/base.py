@@ -51,7 +51,8 @@ class StepContext:
     q_lens: list = field(default_factory=list)       # tokens of each sequence in this step
     past_lens: list = field(default_factory=list)    # tokens each sequence held before it
     slots: list = field(default_factory=list)        # slot of each sequence
-    max_kv_len: int = 0                              # longest sequence after this step
+    max_kv_len: int = 0                              # longest sequence after this step (a replayed decode step: its upper bound)
+    kv_len_hint: int = 0                             # where max_kv_len is an upper bound: the longest sequence as of now (0: unknown)
     seq_meta: Optional[torch.Tensor] = None          # [B,4] int32: q_start, q_len, past, slot
     attn_tiles: Optional[torch.Tensor] = None        # [n,4] int32: sequence, first token, rows, position
     n_attn_tiles: int = 0                            # of row 0; tiles of ATTN_TILE_ROWS query rows
