@@ -12,8 +12,10 @@
 // (v > 0 ? v / R : v * R), then logits / temp in descending order (ties: lower id
 // first), the best top_k kept, softmax over the kept, the shortest prefix whose
 // cumulative sum reaches top_p kept and renormalised, then the first kept entry with
-// r <= cumulative sum.  Implemented as weighted radix descents over the order-preserving
-// integer image of the logits, so no sort of the vocabulary is needed.
+// r <= cumulative sum.  With a top_k of up to 2,048 the kept entries are listed and sorted
+// (two counting passes over the order-preserving integer image of the logits find where the
+// k-th largest lies); without a top_k, weighted radix descents over that image do the same
+// without a sort of the vocabulary.
 #include "common.cuh"
 
 G2B_DEFINE_LAST_ERROR
@@ -76,14 +78,19 @@ __device__ int block_argmax(const float *row, int V, float inv_temp, float *best
 }
 
 // ---- greedy / plain temperature ---------------------------------------------
+// Temperature: warp w owns the contiguous range [w C, (w + 1) C) of the row, C a multiple of
+// 32, and reads it 32 consecutive entries at a time (whole cache lines: a thread per contiguous
+// chunk read 30 times the bytes).  The cumulative sum runs in index order: over the warps'
+// totals to the warp whose range holds the crossing, over that warp's steps of 32 to the step,
+// and by a prefix sum over its lanes to the entry.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float *__restrict__ logits, int V, int ld, float temp, int *seq_state,
                    int state_words, const int *__restrict__ slots, int *__restrict__ out_ids) {
   pdl_launch();
   pdl_wait();
-  __shared__ float scratch[32];
-  __shared__ float s_part[SAMPLE_THREADS];
-  __shared__ int s_choice;
+  __shared__ float s_wtot[SAMPLE_THREADS / 32];
+  __shared__ float s_r, s_total, s_before;
+  __shared__ int s_warp, s_choice;
   const float *row = logits + (size_t)blockIdx.x * ld;
   if (temp <= 0.f) {
     const int id = block_argmax(row, V, 1.f, nullptr);
@@ -93,33 +100,53 @@ sample_rows_kernel(const float *__restrict__ logits, int V, int ld, float temp, 
   float mx;
   block_argmax(row, V, 1.f, &mx);                  // max of the raw logits
   mx = mx / temp;
-  // every thread owns a contiguous chunk so that the cumulative sum runs in index order
-  const int chunk = (V + blockDim.x - 1) / blockDim.x;
-  const int begin = min(V, (int)threadIdx.x * chunk), end = min(V, begin + chunk);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_warps = blockDim.x >> 5;
+  const int C = ((V + n_warps - 1) / n_warps + 31) / 32 * 32;
+  const int begin = min(V, warp * C), end = min(V, begin + C);
   float part = 0.f;
-  for (int i = begin; i < end; ++i) part += expf(row[i] / temp - mx);
-  s_part[threadIdx.x] = part;
-  const float total = block_sum(part, scratch);
+  for (int i = begin + lane; i < end; i += 32) part += expf(row[i] / temp - mx);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if (lane == 0) s_wtot[warp] = part;
   __syncthreads();
   if (threadIdx.x == 0) {
     const float r = next_uniform(seq_state, slots[blockIdx.x], state_words);
+    float total = 0.f;
+    for (int w = 0; w < n_warps; ++w) total += s_wtot[w];
     // first i with r <= c_i where c_i = (e_0 + ... + e_i) / total
     float c = 0.f;
     int owner = -1;
-    for (int t = 0; t < (int)blockDim.x; ++t) {
-      if (r <= (c + s_part[t]) / total && s_part[t] > 0.f) { owner = t; break; }
-      c += s_part[t];
+    for (int w = 0; w < n_warps; ++w) {
+      if (s_wtot[w] > 0.f && r <= (c + s_wtot[w]) / total) { owner = w; break; }
+      c += s_wtot[w];
     }
-    int choice = V - 1;
-    if (owner >= 0) {
-      const int b = min(V, owner * chunk), e = min(V, b + chunk);
-      for (int i = b; i < e; ++i) {
-        c += expf(row[i] / temp - mx);
-        if (r <= c / total) { choice = i; break; }
-        if (i == e - 1) choice = i;                // rounding: stay inside the owner's chunk
+    s_r = r; s_total = total; s_before = c; s_warp = owner;
+    s_choice = V - 1;
+  }
+  __syncthreads();
+  if (warp == s_warp) {
+    const float r = s_r, total = s_total;
+    float c = s_before;
+    int choice = end - 1;                          // rounding: stay inside the owner's range
+    for (int i0 = begin; i0 < end; i0 += 32) {
+      const int i = i0 + lane;
+      const float e = i < end ? expf(row[i] / temp - mx) : 0.f;
+      float incl = e;                              // inclusive prefix sum over the lanes
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
       }
+      const bool hit = i < end && r <= (c + incl) / total;
+      const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+      if (ballot) {
+        choice = i0 + __ffs(ballot) - 1;
+        break;
+      }
+      c += __shfl_sync(0xffffffffu, incl, 31);
     }
-    s_choice = choice;
+    if (lane == 0) s_choice = choice;
   }
   __syncthreads();
   if (threadIdx.x == 0) out_ids[blockIdx.x] = s_choice;
@@ -278,30 +305,54 @@ __device__ Descent radix_descent(const float *row, int V, float inv_temp, float 
 }
 
 // Among entries whose key equals `key`, in index order, the index at which
-// `above + running weight` first reaches target; `*count_out` gets how many equal-key
-// entries are taken (including it).  Sequential over the equal-key entries by thread 0:
-// ties are rare.
+// `above + running weight` first reaches target.  All threads look for the equal-key entries
+// (ties are rare: usually there is one) and list their indices; thread 0 puts the list in
+// index order and walks it.  Only when the list overflows (thousands of equal logits) does
+// thread 0 walk the whole row.
+constexpr int TIE_CAP = 1024;
 template <bool MASS>
 __device__ int tie_walk(const float *row, int V, float inv_temp, float mx, uint32_t key,
-                        float above, float target, int *count_out) {
-  __shared__ int s_idx, s_cnt;
+                        float above, float target, int *tie_list) {
+  __shared__ int s_idx, s_n;
+  if (threadIdx.x == 0) s_n = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    if (order_key(row[i] * inv_temp) == key) {
+      const int j = atomicAdd(&s_n, 1);
+      if (j < TIE_CAP) tie_list[j] = i;
+    }
+  }
+  __syncthreads();
   if (threadIdx.x == 0) {
     float run = above;
-    int idx = -1, cnt = 0;
-    for (int i = 0; i < V; ++i) {
-      const float v = row[i] * inv_temp;
-      if (order_key(v) != key) continue;
-      run += MASS ? expf(v - mx) : 1.f;
-      ++cnt;
-      idx = i;
-      if (run >= target) break;
+    int idx = -1;
+    const int n = s_n;
+    if (n <= TIE_CAP) {
+      for (int a = 1; a < n; ++a) {                 // insertion sort: index order
+        const int v = tie_list[a];
+        int b = a - 1;
+        while (b >= 0 && tie_list[b] > v) { tie_list[b + 1] = tie_list[b]; --b; }
+        tie_list[b + 1] = v;
+      }
+      for (int a = 0; a < n; ++a) {
+        const int i = tie_list[a];
+        run += MASS ? expf(row[i] * inv_temp - mx) : 1.f;
+        idx = i;
+        if (run >= target) break;
+      }
+    } else {
+      for (int i = 0; i < V; ++i) {
+        const float v = row[i] * inv_temp;
+        if (order_key(v) != key) continue;
+        run += MASS ? expf(v - mx) : 1.f;
+        idx = i;
+        if (run >= target) break;
+      }
     }
     s_idx = idx;
-    s_cnt = cnt;
   }
   __syncthreads();
   const int idx = s_idx;
-  if (count_out) *count_out = s_cnt;
   __syncthreads();
   return idx;
 }
@@ -319,6 +370,95 @@ __device__ float admitted_mass(const float *row, int V, float inv_temp, float mx
   return block_sum(part, scratch);
 }
 
+// ---- top-k as a short list --------------------------------------------------------------
+// With a top_k of a few dozen the kept set is tiny: two counting passes over the row (11 bits
+// of the key each) find the 22-bit prefix of the k-th largest key, a third lists every entry
+// at or above that prefix (the k - 1 larger ones and those that share it: usually a handful),
+// the list is sorted (key descending, then index ascending: the reference's order), cut to k,
+// and top-p and the draw are walks over at most k entries.  When the list would overflow
+// (thousands of logits sharing 22 bits) the caller takes the descents over the whole row.
+constexpr int LIST_CAP = 2048;
+struct ShortList {
+  uint32_t key[LIST_CAP];
+  int idx[LIST_CAP];
+  float e[LIST_CAP];
+  int hist[2048];
+};
+
+// Returns the number of listed entries (sorted, at least top_k of them), or -1 on overflow.
+__device__ int list_top_k(const float *row, int V, float inv_temp, int top_k, ShortList &L) {
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_above, s_n;
+  if (threadIdx.x == 0) { s_prefix = 0u; s_above = 0; s_n = 0; }
+  __syncthreads();
+  for (int pass = 0; pass < 2; ++pass) {
+    const int shift = pass == 0 ? 21 : 10;
+    for (int i = threadIdx.x; i < 2048; i += blockDim.x) L.hist[i] = 0;
+    __syncthreads();
+    const uint32_t prefix = s_prefix;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const uint32_t k = order_key(row[i] * inv_temp);
+      if (pass == 1 && (k >> 21) != (prefix >> 21)) continue;
+      // most logits share a few bins: the lanes of a warp that hit the same bin add once
+      const int bin = (int)((k >> shift) & 0x7ffu);
+      const unsigned peers = __match_any_sync(__activemask(), bin);
+      if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&L.hist[bin], __popc(peers));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int run = s_above, chosen = 0;
+      for (int d = 2047; d >= 0; --d) {
+        if (run + L.hist[d] >= top_k) { chosen = d; break; }
+        run += L.hist[d];
+      }
+      s_above = run;
+      s_prefix = prefix | ((uint32_t)chosen << shift);
+      if (pass == 1) s_n = run + L.hist[chosen];        // entries at or above the 22-bit prefix
+    }
+    __syncthreads();
+  }
+  const int total = s_n;
+  if (total > LIST_CAP || total < top_k) return -1;
+  const uint32_t floor22 = s_prefix >> 10;
+  __syncthreads();
+  if (threadIdx.x == 0) s_n = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const uint32_t k = order_key(row[i] * inv_temp);
+    if ((k >> 10) >= floor22) {
+      const int j = atomicAdd(&s_n, 1);
+      if (j < LIST_CAP) { L.key[j] = k; L.idx[j] = i; }
+    }
+  }
+  __syncthreads();
+  const int n = s_n;
+  if (n > LIST_CAP) return -1;
+  int n2 = 1;
+  while (n2 < n) n2 <<= 1;
+  for (int i = n + threadIdx.x; i < n2; i += blockDim.x) { L.key[i] = 0u; L.idx[i] = 0x7fffffff; }
+  __syncthreads();
+  // bitonic sort: key descending, index ascending
+  for (int k = 2; k <= n2; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = threadIdx.x; i < n2; i += blockDim.x) {
+        const int p = i ^ j;
+        if (p > i) {
+          const bool up = (i & k) == 0;             // this pair in "descending" order
+          const uint32_t ka = L.key[i], kb = L.key[p];
+          const int ia = L.idx[i], ib = L.idx[p];
+          const bool a_first = ka > kb || (ka == kb && ia < ib);     // a belongs before b
+          if (a_first != up) {
+            L.key[i] = kb; L.key[p] = ka;
+            L.idx[i] = ib; L.idx[p] = ia;
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  return n;
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, int top_k,
                        float top_p, float penalty, const int *__restrict__ recent, int recent_ld,
@@ -327,8 +467,10 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
   pdl_launch();
   pdl_wait();
   __shared__ float scratch[32];
-  __shared__ float hist[256];
   __shared__ float s_r;
+  __shared__ ShortList L;
+  float *hist = L.e;                                // the descents' 256 bins and the tie list live in the list's arrays
+  int *tie_list = L.idx;
   float *row = logits + (size_t)blockIdx.x * ld;
 
   // repeat penalty, each distinct id once (src/main.c:204-223)
@@ -355,13 +497,48 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
   float mx;
   block_argmax(row, V, inv_temp, &mx);
 
+  if (top_k > 0 && top_k < V && top_k <= LIST_CAP) {
+    const int n = list_top_k(row, V, inv_temp, top_k, L);
+    if (n >= 0) {
+      const int n_keep0 = min(n, top_k);
+      for (int j = threadIdx.x; j < n_keep0; j += blockDim.x) L.e[j] = expf(row[L.idx[j]] * inv_temp - mx);
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int n_keep = n_keep0;
+        float kept = 0.f;
+        for (int j = 0; j < n_keep; ++j) kept += L.e[j];
+        if (top_p < 1.f) {
+          // shortest prefix (descending) whose cumulative probability reaches top_p
+          const float target = top_p * kept;
+          float run = 0.f;
+          for (int j = 0; j < n_keep; ++j) {
+            run += L.e[j];
+            if (run >= target) { n_keep = j + 1; break; }
+          }
+          kept = 0.f;
+          for (int j = 0; j < n_keep; ++j) kept += L.e[j];
+        }
+        const float target = next_uniform(seq_state, slots[blockIdx.x], state_words) * kept;
+        float run = 0.f;
+        int pick = L.idx[n_keep - 1];
+        for (int j = 0; j < n_keep; ++j) {
+          run += L.e[j];
+          if (run >= target) { pick = L.idx[j]; break; }
+        }
+        out_ids[blockIdx.x] = pick;
+      }
+      return;
+    }
+    __syncthreads();
+  }
+
   // kept set: key > bound_key, or key == bound_key with index <= tie_idx
   bool bounded = false;
   uint32_t bound_key = 0u;
   int tie_idx = V;
   if (top_k > 0 && top_k < V) {
     const Descent d = radix_descent<false>(row, V, inv_temp, mx, 0u, false, (float)top_k, hist);
-    tie_idx = tie_walk<false>(row, V, inv_temp, mx, d.key, d.above, (float)top_k, nullptr);
+    tie_idx = tie_walk<false>(row, V, inv_temp, mx, d.key, d.above, (float)top_k, tie_list);
     bound_key = d.key;
     bounded = true;
   }
@@ -370,7 +547,7 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
     // shortest prefix (descending) whose cumulative probability reaches top_p
     const float target = top_p * kept;
     const Descent d = radix_descent<true>(row, V, inv_temp, mx, bound_key, bounded, target, hist);
-    int t2 = tie_walk<true>(row, V, inv_temp, mx, d.key, d.above, target, nullptr);
+    int t2 = tie_walk<true>(row, V, inv_temp, mx, d.key, d.above, target, tie_list);
     if (bounded && d.key == bound_key && t2 > tie_idx) t2 = tie_idx;
     bound_key = d.key;
     tie_idx = t2;
@@ -381,7 +558,7 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
   __syncthreads();
   const float target = s_r * kept;
   const Descent d = radix_descent<true>(row, V, inv_temp, mx, bound_key, bounded, target, hist);
-  int choice = tie_walk<true>(row, V, inv_temp, mx, d.key, d.above, target, nullptr);
+  int choice = tie_walk<true>(row, V, inv_temp, mx, d.key, d.above, target, tie_list);
   if (bounded && d.key == bound_key && choice > tie_idx) choice = tie_idx;
   if (threadIdx.x == 0) out_ids[blockIdx.x] = choice < 0 ? 0 : choice;
 }

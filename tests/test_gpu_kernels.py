@@ -201,12 +201,20 @@ def test_sampling_greedy_and_temperature():
     assert state[slots.long(), 3].tolist() == [3] * R
 
 
-@pytest.mark.parametrize("top_k,top_p,penalty", [(40, 0.9, 1.1), (0, 0.9, 1.0), (5, 1.0, 1.3), (0, 1.0, 1.0), (1, 0.5, 1.0)])
-def test_sampling_filtered(top_k, top_p, penalty):
+@pytest.mark.parametrize("V,ties", [(2011, False), (151936, False), (40000, True)])
+@pytest.mark.parametrize("top_k,top_p,penalty", [(40, 0.9, 1.1), (0, 0.9, 1.0), (5, 1.0, 1.3), (0, 1.0, 1.0), (1, 0.5, 1.0),
+                                                 (2048, 0.95, 1.0), (3000, 0.9, 1.1)])
+def test_sampling_filtered(top_k, top_p, penalty, V, ties):
+    """Repeat penalty, top-k, top-p and the draw against the plain sampler: a small and a real
+    vocabulary; a top_k that is listed and sorted (up to 2,048) and one that is not; and logits
+    rounded to tenths, so that hundreds of entries tie at every cut and the listed path gives
+    way to the descents over the whole row."""
     from gguf2bin_b200 import kernels
     from gguf2bin_b200.cache import SEQ_STATE_WORDS
-    R, V, temp = 5, 2011, 0.7
+    R, temp = 5, 0.7
     logits = rnd(R, V, scale=2.5, seed=31)
+    if ties:
+        logits = (logits * 10).round() / 10
     recent = torch.randint(0, V, (R, 64), generator=torch.Generator().manual_seed(5), dtype=torch.int32)
     recent[:, 10] = recent[:, 3]                       # a repeated id is penalised once
     recent_n = torch.tensor([64, 0, 17, 64, 1], dtype=torch.int32)
