@@ -14,7 +14,9 @@ every group has storage of its own:
 
 Beside the groups there is one fixed-size record per slot, ``seq_state``
 (``[slots, SEQ_STATE_WORDS]`` int32): the sampler's key and draw counter live there, so
-a sequence's random stream does not depend on the batch it is in.
+a sequence's random stream does not depend on the batch it is in, and so do the sequence's
+most recent tokens (a ring of ``SS_RING_WORDS`` ids and the count of tokens written to it),
+which the repeat penalty reads on the device.
 """
 from __future__ import annotations
 
@@ -26,9 +28,10 @@ import torch
 from .pool import CacheError, Sequence, SlotTable
 
 PAGE_SIZE = 64
-SEQ_STATE_WORDS = 8
-# word indices of the per-slot record
-SS_SEED_LO, SS_SEED_HI, SS_STREAM, SS_DRAWS = 0, 1, 2, 3
+# word indices of the per-slot record (the same numbers as in csrc/sampling.cu)
+SS_SEED_LO, SS_SEED_HI, SS_STREAM, SS_DRAWS, SS_RECENT_TOTAL = 0, 1, 2, 3, 4
+SS_RING, SS_RING_WORDS = 8, 72           # ring of recent token ids: the last 64 are used, 8 spare for a step taken back
+SEQ_STATE_WORDS = SS_RING + SS_RING_WORDS
 
 
 @dataclass(frozen=True)

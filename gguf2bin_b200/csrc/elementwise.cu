@@ -623,21 +623,26 @@ extern "C" int g2b_advance_positions(int *tok_pos, int n, cudaStream_t stream) {
 
 // Undoes the bookkeeping of one decode step that was launched ahead and is not wanted after
 // all: positions go back by one and, when that step drew a random number, so do the draw
-// counters of the sequences' sampling records (word 3 of a record).
-__global__ void rewind_step_kernel(int *tok_pos, int n, int *seq_state, int words, const int *slots, int undo_draw) {
+// counters of the sequences' sampling records, and the count of its recent ids when that step added one.
+// (words 3 and 4 of a record: the draw counter and the count of ids in the ring of recent ids;
+// the id that the step wrote stays in the ring, one place past the window)
+__global__ void rewind_step_kernel(int *tok_pos, int n, int *seq_state, int words, const int *slots, int undo_draw,
+                                   int undo_recent) {
   pdl_launch();
   pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   tok_pos[i] -= 1;
   if (undo_draw) seq_state[(size_t)slots[i] * words + 3] -= 1;
+  if (undo_recent) seq_state[(size_t)slots[i] * words + 4] -= 1;
 }
 
 extern "C" int g2b_rewind_step(int *tok_pos, int n, int *seq_state, int words, const int *slots, int undo_draw,
-                               cudaStream_t stream) {
+                               int undo_recent, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (undo_draw && (!seq_state || !slots || words < 4)) G2B_REFUSE("rewind_step: no sampling records to rewind");
+  if ((undo_draw || undo_recent) && (!seq_state || !slots || words < 5))
+    G2B_REFUSE("rewind_step: no sampling records to rewind");
   g2b_launch(rewind_step_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tok_pos, n, seq_state, words, slots,
-             undo_draw);
+             undo_draw, undo_recent);
   return g2b_check_launch("rewind_step");
 }

@@ -22,6 +22,13 @@ G2B_DEFINE_LAST_ERROR
 
 #define SAMPLE_THREADS 1024
 
+// Words of a sequence's record (seq_state[slot]): the sampler's key (seed, stream id), its draw
+// counter, the count of tokens written to the ring of recent ids, and the ring itself.  The
+// repeat penalty looks at the last RECENT_WINDOW ids; the ring is a few longer, so that the one
+// step a decode session may take back leaves the window as it was.
+constexpr int SS_DRAWS = 3, SS_RECENT_TOTAL = 4, SS_RING = 8, SS_RING_WORDS = 72;
+constexpr int RECENT_WINDOW = 64;
+
 __device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
                                               uint32_t k0, uint32_t k1, uint32_t out[4]) {
 #pragma unroll
@@ -39,9 +46,32 @@ __device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t
 __device__ __forceinline__ float next_uniform(int *seq_state, int slot, int words) {
   int *rec = seq_state + (size_t)slot * words;
   uint32_t o[4];
-  philox4x32_10((uint32_t)rec[3], (uint32_t)rec[2], 0u, 0u, (uint32_t)rec[0], (uint32_t)rec[1], o);
-  rec[3] += 1;
+  philox4x32_10((uint32_t)rec[SS_DRAWS], (uint32_t)rec[2], 0u, 0u, (uint32_t)rec[0], (uint32_t)rec[1], o);
+  rec[SS_DRAWS] += 1;
   return (float)(o[0] >> 8) * (1.0f / 16777216.0f);
+}
+
+// Every entry of a row, once, by the threads of a block: f(index, value).  Four 16-byte loads
+// per thread are in flight at a time when the row allows it (one block reading 4 bytes per
+// thread and trip took 90 us for a vocabulary of 150k entries; this takes 6).
+template <typename F>
+__device__ __forceinline__ void scan_row(const float *__restrict__ row, int V, F f) {
+  const int n4 = (((uintptr_t)row & 15) == 0) ? V / 4 : 0;
+  const float4 *r4 = reinterpret_cast<const float4 *>(row);
+  const int nt = blockDim.x;
+  int i4 = threadIdx.x;
+  for (; i4 + 3 * nt < n4; i4 += 4 * nt) {
+    const float4 a = r4[i4], b = r4[i4 + nt], c = r4[i4 + 2 * nt], d = r4[i4 + 3 * nt];
+    f(4 * i4, a.x); f(4 * i4 + 1, a.y); f(4 * i4 + 2, a.z); f(4 * i4 + 3, a.w);
+    f(4 * (i4 + nt), b.x); f(4 * (i4 + nt) + 1, b.y); f(4 * (i4 + nt) + 2, b.z); f(4 * (i4 + nt) + 3, b.w);
+    f(4 * (i4 + 2 * nt), c.x); f(4 * (i4 + 2 * nt) + 1, c.y); f(4 * (i4 + 2 * nt) + 2, c.z); f(4 * (i4 + 2 * nt) + 3, c.w);
+    f(4 * (i4 + 3 * nt), d.x); f(4 * (i4 + 3 * nt) + 1, d.y); f(4 * (i4 + 3 * nt) + 2, d.z); f(4 * (i4 + 3 * nt) + 3, d.w);
+  }
+  for (; i4 < n4; i4 += nt) {
+    const float4 a = r4[i4];
+    f(4 * i4, a.x); f(4 * i4 + 1, a.y); f(4 * i4 + 2, a.z); f(4 * i4 + 3, a.w);
+  }
+  for (int i = 4 * n4 + threadIdx.x; i < V; i += nt) f(i, row[i]);
 }
 
 // ---- block argmax: lowest index among equal maxima ---------------------------
@@ -50,10 +80,10 @@ __device__ int block_argmax(const float *row, int V, float inv_temp, float *best
   __shared__ int s_idx[32];
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i] * inv_temp;
+  scan_row(row, V, [&](int i, float x) {
+    const float v = x * inv_temp;
     if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
-  }
+  });
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -78,78 +108,138 @@ __device__ int block_argmax(const float *row, int V, float inv_temp, float *best
 }
 
 // ---- greedy / plain temperature ---------------------------------------------
-// Temperature: warp w owns the contiguous range [w C, (w + 1) C) of the row, C a multiple of
-// 32, and reads it 32 consecutive entries at a time (whole cache lines: a thread per contiguous
-// chunk read 30 times the bytes).  The cumulative sum runs in index order: over the warps'
-// totals to the warp whose range holds the crossing, over that warp's steps of 32 to the step,
-// and by a prefix sum over its lanes to the entry.
-__global__ void __launch_bounds__(SAMPLE_THREADS)
-sample_rows_kernel(const float *__restrict__ logits, int V, int ld, float temp, int *seq_state,
-                   int state_words, const int *__restrict__ slots, int *__restrict__ out_ids) {
-  pdl_launch();
-  pdl_wait();
-  __shared__ float s_wtot[SAMPLE_THREADS / 32];
-  __shared__ float s_r, s_total, s_before;
-  __shared__ int s_warp, s_choice;
-  const float *row = logits + (size_t)blockIdx.x * ld;
-  if (temp <= 0.f) {
-    const int id = block_argmax(row, V, 1.f, nullptr);
-    if (threadIdx.x == 0) out_ids[blockIdx.x] = id;
-    return;
-  }
+// Temperature: the row is cut into pieces of G consecutive entries (G = 128, or a multiple for
+// rows beyond 262,144 entries), and one pass leaves the sum of e^(x/T - max) of every piece in
+// shared memory: a warp takes a piece at a time, 128 entries per trip (16 bytes per lane).  The
+// cumulative sum then runs in index order: over the pieces (32 lanes, a run of pieces each, and
+// a prefix sum over the lanes) to the piece that holds the crossing, and inside that piece by a
+// prefix sum over its entries.
+constexpr int MAX_PIECES = 2048;
+// Every thread of the block calls it; returns the chosen index to all of them.  s_piece:
+// MAX_PIECES floats of shared memory.
+__device__ int pick_by_temperature(const float *__restrict__ row, int V, float temp, float *s_piece,
+                                   int *seq_state, int slot, int state_words) {
+  __shared__ float s_before, s_target;
+  __shared__ int s_owner, s_choice;
   float mx;
   block_argmax(row, V, 1.f, &mx);                  // max of the raw logits
   mx = mx / temp;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_warps = blockDim.x >> 5;
-  const int C = ((V + n_warps - 1) / n_warps + 31) / 32 * 32;
-  const int begin = min(V, warp * C), end = min(V, begin + C);
-  float part = 0.f;
-  for (int i = begin + lane; i < end; i += 32) part += expf(row[i] / temp - mx);
+  const int trips = (V + 128 * MAX_PIECES - 1) / (128 * MAX_PIECES);     // trips of 128 entries per piece
+  const int G = 128 * trips, n_pieces = (V + G - 1) / G;
+  const bool vec = ((uintptr_t)row & 15) == 0;
+  // the four entries of this lane in the trip that starts at entry i0 (0 beyond the row)
+  auto four = [&](int i0, float (&e)[4]) {
+    const int i = i0 + 4 * lane;
+    if (vec && i + 3 < V) {
+      const float4 x = *reinterpret_cast<const float4 *>(row + i);
+      e[0] = expf(x.x / temp - mx); e[1] = expf(x.y / temp - mx);
+      e[2] = expf(x.z / temp - mx); e[3] = expf(x.w / temp - mx);
+    } else {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-  if (lane == 0) s_wtot[warp] = part;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const float r = next_uniform(seq_state, slots[blockIdx.x], state_words);
-    float total = 0.f;
-    for (int w = 0; w < n_warps; ++w) total += s_wtot[w];
-    // first i with r <= c_i where c_i = (e_0 + ... + e_i) / total
-    float c = 0.f;
-    int owner = -1;
-    for (int w = 0; w < n_warps; ++w) {
-      if (s_wtot[w] > 0.f && r <= (c + s_wtot[w]) / total) { owner = w; break; }
-      c += s_wtot[w];
+      for (int q = 0; q < 4; ++q) e[q] = i + q < V ? expf(row[i + q] / temp - mx) : 0.f;
     }
-    s_r = r; s_total = total; s_before = c; s_warp = owner;
-    s_choice = V - 1;
+  };
+  for (int j = warp; j < n_pieces; j += n_warps) {
+    float part = 0.f;
+    for (int t = 0; t < trips; ++t) {
+      float e[4];
+      four(j * G + 128 * t, e);
+      part += (e[0] + e[1]) + (e[2] + e[3]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (lane == 0) s_piece[j] = part;
   }
   __syncthreads();
-  if (warp == s_warp) {
-    const float r = s_r, total = s_total;
-    float c = s_before;
-    int choice = end - 1;                          // rounding: stay inside the owner's range
-    for (int i0 = begin; i0 < end; i0 += 32) {
-      const int i = i0 + lane;
-      const float e = i < end ? expf(row[i] / temp - mx) : 0.f;
-      float incl = e;                              // inclusive prefix sum over the lanes
+  if (warp == 0) {
+    // lane l owns the pieces [l per, (l + 1) per); first the lane, then the piece in it
+    const int per = (n_pieces + 31) / 32;
+    const int p0 = min(n_pieces, lane * per), p1 = min(n_pieces, p0 + per);
+    float mine = 0.f;
+    for (int j = p0; j < p1; ++j) mine += s_piece[j];
+    float incl = mine;
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const float up = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += up;
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    const float total = __shfl_sync(0xffffffffu, incl, 31);
+    float r = 0.f;
+    if (lane == 0) r = next_uniform(seq_state, slot, state_words);
+    r = __shfl_sync(0xffffffffu, r, 0);
+    // first i with r <= c_i / total, taken as c_i >= r total
+    const float target = r * total;
+    const unsigned hit = __ballot_sync(0xffffffffu, mine > 0.f && incl >= target);
+    if (hit) {
+      const int l = __ffs(hit) - 1;
+      const float c_l = __shfl_sync(0xffffffffu, incl - mine, l);
+      if (lane == l) {
+        float c = c_l;
+        int j = p0;
+        for (; j < p1; ++j) {
+          if (s_piece[j] > 0.f && c + s_piece[j] >= target) break;
+          c += s_piece[j];
+        }
+        if (j >= p1) {                               // rounding: the lane's last piece
+          j = p1 - 1;
+          c -= s_piece[j];
+        }
+        s_owner = j; s_before = c;
       }
-      const bool hit = i < end && r <= (c + incl) / total;
-      const unsigned ballot = __ballot_sync(0xffffffffu, hit);
-      if (ballot) {
-        choice = i0 + __ffs(ballot) - 1;
-        break;
+    } else if (lane == 0) {
+      s_owner = -1; s_before = 0.f;
+    }
+    if (lane == 0) s_target = target;
+    __syncwarp();
+    const int owner = s_owner;
+    int choice = V - 1;
+    if (owner >= 0) {
+      float c = s_before;
+      choice = min(V, (owner + 1) * G) - 1;          // rounding: stay inside the piece
+      for (int t = 0; t < trips; ++t) {
+        float e[4];
+        const int i0 = owner * G + 128 * t;
+        four(i0, e);
+        const float mine4 = (e[0] + e[1]) + (e[2] + e[3]);
+        float inc = mine4;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float up = __shfl_up_sync(0xffffffffu, inc, o);
+          if (lane >= o) inc += up;
+        }
+        float run = c + inc - mine4;                 // before this lane's four
+        int found = -1;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          run += e[q];
+          if (found < 0 && i0 + 4 * lane + q < V && run >= s_target) found = i0 + 4 * lane + q;
+        }
+        const unsigned any = __ballot_sync(0xffffffffu, found >= 0);
+        if (any) {
+          choice = __shfl_sync(0xffffffffu, found, __ffs(any) - 1);
+          break;
+        }
+        c += __shfl_sync(0xffffffffu, inc, 31);
       }
-      c += __shfl_sync(0xffffffffu, incl, 31);
     }
     if (lane == 0) s_choice = choice;
   }
   __syncthreads();
-  if (threadIdx.x == 0) out_ids[blockIdx.x] = s_choice;
+  return s_choice;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_rows_kernel(const float *__restrict__ logits, int V, int ld, float temp, int *seq_state,
+                   int state_words, const int *__restrict__ slots, int *__restrict__ out_ids) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float s_piece[MAX_PIECES];
+  const float *row = logits + (size_t)blockIdx.x * ld;
+  const int id = temp <= 0.f ? block_argmax(row, V, 1.f, nullptr)
+                             : pick_by_temperature(row, V, temp, s_piece, seq_state, slots[blockIdx.x], state_words);
+  if (threadIdx.x == 0) out_ids[blockIdx.x] = id;
 }
 
 extern "C" int g2b_sample_rows(const float *logits, int R, int V, int ld, float temp,
@@ -270,14 +360,14 @@ __device__ Descent radix_descent(const float *row, int V, float inv_temp, float 
     __syncthreads();
     const uint32_t prefix = s_prefix;
     const uint32_t mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const float v = row[i] * inv_temp;
+    scan_row(row, V, [&](int, float x) {
+      const float v = x * inv_temp;
       const uint32_t k = order_key(v);
-      if (bounded && k < bound_key) continue;      // below the kept set
-      if ((k & mask) != (prefix & mask)) continue;
+      if (bounded && k < bound_key) return;        // below the kept set
+      if ((k & mask) != (prefix & mask)) return;
       const float w = MASS ? expf(v - mx) : 1.f;
       atomicAdd(&hist[(k >> shift) & 0xffu], w);
-    }
+    });
     __syncthreads();
     if (threadIdx.x == 0) {
       float run = s_above;
@@ -316,12 +406,12 @@ __device__ int tie_walk(const float *row, int V, float inv_temp, float mx, uint3
   __shared__ int s_idx, s_n;
   if (threadIdx.x == 0) s_n = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    if (order_key(row[i] * inv_temp) == key) {
+  scan_row(row, V, [&](int i, float x) {
+    if (order_key(x * inv_temp) == key) {
       const int j = atomicAdd(&s_n, 1);
       if (j < TIE_CAP) tie_list[j] = i;
     }
-  }
+  });
   __syncthreads();
   if (threadIdx.x == 0) {
     float run = above;
@@ -361,22 +451,23 @@ __device__ int tie_walk(const float *row, int V, float inv_temp, float mx, uint3
 __device__ float admitted_mass(const float *row, int V, float inv_temp, float mx,
                                uint32_t bound_key, int tie_idx, bool bounded, float *scratch) {
   float part = 0.f;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = row[i] * inv_temp;
+  scan_row(row, V, [&](int i, float x) {
+    const float v = x * inv_temp;
     const uint32_t k = order_key(v);
-    if (bounded && (k < bound_key || (k == bound_key && i > tie_idx))) continue;
+    if (bounded && (k < bound_key || (k == bound_key && i > tie_idx))) return;
     part += expf(v - mx);
-  }
+  });
   return block_sum(part, scratch);
 }
 
-// ---- top-k as a short list --------------------------------------------------------------
-// With a top_k of a few dozen the kept set is tiny: two counting passes over the row (11 bits
-// of the key each) find the 22-bit prefix of the k-th largest key, a third lists every entry
-// at or above that prefix (the k - 1 larger ones and those that share it: usually a handful),
-// the list is sorted (key descending, then index ascending: the reference's order), cut to k,
-// and top-p and the draw are walks over at most k entries.  When the list would overflow
-// (thousands of logits sharing 22 bits) the caller takes the descents over the whole row.
+// ---- the kept entries as a short list ---------------------------------------------------
+// With a top_k of a few dozen, or a top_p that a few hundred entries reach, the kept set is
+// tiny: every entry at or above a 22-bit prefix of the key is listed (a complete head of the
+// row's descending order), the list is sorted (key descending, then index ascending: the
+// reference's order), and the cuts and the draw are walks over it.  The prefix comes from a
+// look at 4,096 entries of the row, or, when that guess fails, from two counting passes over
+// the whole row.  When neither gives a list that fits (thousands of logits sharing 22 bits, a
+// top_p that needs more than the list holds) the caller takes the descents over the whole row.
 constexpr int LIST_CAP = 2048;
 struct ShortList {
   uint32_t key[LIST_CAP];
@@ -385,65 +476,44 @@ struct ShortList {
   int hist[2048];
 };
 
-// Returns the number of listed entries (sorted, at least top_k of them), or -1 on overflow.
-__device__ int list_top_k(const float *row, int V, float inv_temp, int top_k, ShortList &L) {
-  __shared__ uint32_t s_prefix;
-  __shared__ int s_above, s_n;
-  if (threadIdx.x == 0) { s_prefix = 0u; s_above = 0; s_n = 0; }
-  __syncthreads();
-  for (int pass = 0; pass < 2; ++pass) {
-    const int shift = pass == 0 ? 21 : 10;
-    for (int i = threadIdx.x; i < 2048; i += blockDim.x) L.hist[i] = 0;
-    __syncthreads();
-    const uint32_t prefix = s_prefix;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const uint32_t k = order_key(row[i] * inv_temp);
-      if (pass == 1 && (k >> 21) != (prefix >> 21)) continue;
-      // most logits share a few bins: the lanes of a warp that hit the same bin add once
-      const int bin = (int)((k >> shift) & 0x7ffu);
-      const unsigned peers = __match_any_sync(__activemask(), bin);
-      if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&L.hist[bin], __popc(peers));
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int run = s_above, chosen = 0;
-      for (int d = 2047; d >= 0; --d) {
-        if (run + L.hist[d] >= top_k) { chosen = d; break; }
-        run += L.hist[d];
-      }
-      s_above = run;
-      s_prefix = prefix | ((uint32_t)chosen << shift);
-      if (pass == 1) s_n = run + L.hist[chosen];        // entries at or above the 22-bit prefix
-    }
-    __syncthreads();
+// From the top bin down to the one where the running count reaches `want`: lane l of warp 0 owns
+// the 64 bins below 2048 - 64 l; a prefix sum over the lanes finds the lane, which walks its
+// own bins.  *chosen: that bin (the lowest one if the count is never reached); *above: the
+// count in the bins above it.  Warp 0 calls it; the others skip it.
+__device__ __forceinline__ void walk_bins(const int *hist, int above0, int want, int *chosen_out, int *above_out) {
+  const int lane = threadIdx.x & 31, hi = 2047 - 64 * lane;
+  int mine = 0;
+  for (int d = hi; d > hi - 64; --d) mine += hist[d];
+  int incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += up;
   }
-  const int total = s_n;
-  if (total > LIST_CAP || total < top_k) return -1;
-  const uint32_t floor22 = s_prefix >> 10;
-  __syncthreads();
-  if (threadIdx.x == 0) s_n = 0;
-  __syncthreads();
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const uint32_t k = order_key(row[i] * inv_temp);
-    if ((k >> 10) >= floor22) {
-      const int j = atomicAdd(&s_n, 1);
-      if (j < LIST_CAP) { L.key[j] = k; L.idx[j] = i; }
-    }
+  const unsigned hit = __ballot_sync(0xffffffffu, above0 + incl >= want);
+  const int owner = hit ? __ffs(hit) - 1 : 31;
+  int run = above0 + incl - mine, chosen = hi - 63;
+  for (int d = hi; d > hi - 64; --d) {
+    if (run + hist[d] >= want) { chosen = d; break; }
+    run += hist[d];
   }
-  __syncthreads();
-  const int n = s_n;
-  if (n > LIST_CAP) return -1;
+  if (!hit) run -= hist[chosen];
+  *chosen_out = __shfl_sync(0xffffffffu, chosen, owner);
+  *above_out = __shfl_sync(0xffffffffu, run, owner);
+}
+
+// Sorts the first n entries of the list: key descending, then index ascending.
+__device__ void sort_list(ShortList &L, int n) {
   int n2 = 1;
   while (n2 < n) n2 <<= 1;
   for (int i = n + threadIdx.x; i < n2; i += blockDim.x) { L.key[i] = 0u; L.idx[i] = 0x7fffffff; }
   __syncthreads();
-  // bitonic sort: key descending, index ascending
   for (int k = 2; k <= n2; k <<= 1) {
     for (int j = k >> 1; j > 0; j >>= 1) {
       for (int i = threadIdx.x; i < n2; i += blockDim.x) {
         const int p = i ^ j;
         if (p > i) {
-          const bool up = (i & k) == 0;             // this pair in "descending" order
+          const bool up = (i & k) == 0;             // this pair in list order
           const uint32_t ka = L.key[i], kb = L.key[p];
           const int ia = L.idx[i], ib = L.idx[p];
           const bool a_first = ka > kb || (ka == kb && ia < ib);     // a belongs before b
@@ -456,6 +526,114 @@ __device__ int list_top_k(const float *row, int V, float inv_temp, int top_k, Sh
       __syncthreads();
     }
   }
+}
+
+// Every entry whose key has at least the 22-bit prefix `floor22` into the list; returns their
+// number (which may exceed LIST_CAP: then the list is not complete).
+__device__ int list_from_floor(const float *row, int V, float inv_temp, uint32_t floor22, ShortList &L) {
+  __shared__ int s_n;
+  __syncthreads();
+  if (threadIdx.x == 0) s_n = 0;
+  __syncthreads();
+  scan_row(row, V, [&](int i, float x) {
+    const uint32_t k = order_key(x * inv_temp);
+    if ((k >> 10) >= floor22) {
+      const int j = atomicAdd(&s_n, 1);
+      if (j < LIST_CAP) { L.key[j] = k; L.idx[j] = i; }
+    }
+  });
+  __syncthreads();
+  return s_n;
+}
+
+// The `want` largest entries (and a few hundred more) in ONE pass over the row: 4,096 evenly
+// spaced entries are looked at first, and the 22-bit prefix of the m-th largest of them, m a
+// little more than want's share of the sample, is the floor of the list.  Returns the number of
+// listed entries (sorted; a complete head of the row's descending order), or -1 when the floor
+// turned out too high or too low (fewer than want entries, or more than the list holds): the
+// caller then counts over the whole row.
+__device__ int list_by_sampled_floor(const float *row, int V, float inv_temp, int want, ShortList &L) {
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_above;
+  constexpr int SAMPLES = 4096;
+  static_assert(2 * LIST_CAP == SAMPLES, "the sample lives in the list's key and index arrays");
+  uint32_t *samp = L.key;                           // key[] and idx[] are adjacent: 4,096 words
+  const int S = min(V, SAMPLES);
+  // three times want's share of the sample for a small want, one and a half for a large one, and 8
+  const long long m64 = (long long)want * S * (want <= 128 ? 6 : 3) / (2LL * V) + 8;
+  if (m64 > S / 2) return -1;                       // want is a large share of the row: count instead
+  const int m = (int)m64;
+  for (int t = threadIdx.x; t < S; t += blockDim.x)
+    samp[t] = order_key(row[(long long)t * V / S] * inv_temp);
+  if (threadIdx.x == 0) { s_prefix = 0u; s_above = 0; }
+  __syncthreads();
+  for (int pass = 0; pass < 2; ++pass) {
+    const int shift = pass == 0 ? 21 : 10;
+    for (int i = threadIdx.x; i < 2048; i += blockDim.x) L.hist[i] = 0;
+    __syncthreads();
+    const uint32_t prefix = s_prefix;
+    for (int t = threadIdx.x; t < S; t += blockDim.x) {
+      const uint32_t k = samp[t];
+      if (pass == 1 && (k >> 21) != (prefix >> 21)) continue;
+      atomicAdd(&L.hist[(k >> shift) & 0x7ffu], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      int chosen, above;
+      walk_bins(L.hist, s_above, m, &chosen, &above);
+      if (threadIdx.x == 0) {
+        s_above = above;
+        s_prefix = prefix | ((uint32_t)chosen << shift);
+      }
+    }
+    __syncthreads();
+  }
+  const uint32_t floor22 = s_prefix >> 10;
+  const int n = list_from_floor(row, V, inv_temp, floor22, L);
+  if (n < want || n > LIST_CAP) return -1;
+  sort_list(L, n);
+  return n;
+}
+
+// The same by counting: two passes over the row (11 bits of the key each) find the 22-bit prefix
+// of the want-th largest key exactly, a third lists the entries at or above it.  -1 when more
+// than the list holds share that prefix.
+__device__ int list_top_k(const float *row, int V, float inv_temp, int top_k, ShortList &L) {
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_above, s_total;
+  __syncthreads();
+  if (threadIdx.x == 0) { s_prefix = 0u; s_above = 0; s_total = 0; }
+  __syncthreads();
+  for (int pass = 0; pass < 2; ++pass) {
+    const int shift = pass == 0 ? 21 : 10;
+    for (int i = threadIdx.x; i < 2048; i += blockDim.x) L.hist[i] = 0;
+    __syncthreads();
+    const uint32_t prefix = s_prefix;
+    scan_row(row, V, [&](int, float x) {
+      const uint32_t k = order_key(x * inv_temp);
+      if (pass == 1 && (k >> 21) != (prefix >> 21)) return;
+      // most logits share a few bins: the lanes of a warp that hit the same bin add once
+      const int bin = (int)((k >> shift) & 0x7ffu);
+      const unsigned peers = __match_any_sync(__activemask(), bin);
+      if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&L.hist[bin], __popc(peers));
+    });
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      int chosen, above;
+      walk_bins(L.hist, s_above, top_k, &chosen, &above);
+      if (threadIdx.x == 0) {
+        s_above = above;
+        s_prefix = prefix | ((uint32_t)chosen << shift);
+        if (pass == 1) s_total = above + L.hist[chosen];    // entries at or above the 22-bit prefix
+      }
+    }
+    __syncthreads();
+  }
+  const int total = s_total;
+  if (total > LIST_CAP || total < top_k) return -1;
+  const int n = list_from_floor(row, V, inv_temp, s_prefix >> 10, L);
+  if (n > LIST_CAP) return -1;
+  sort_list(L, n);
   return n;
 }
 
@@ -463,74 +641,107 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, int top_k,
                        float top_p, float penalty, const int *__restrict__ recent, int recent_ld,
                        const int *__restrict__ recent_n, int *seq_state, int state_words,
-                       const int *__restrict__ slots, int *__restrict__ out_ids) {
+                       const int *__restrict__ slots, int *__restrict__ out_ids, int append) {
   pdl_launch();
   pdl_wait();
   __shared__ float scratch[32];
   __shared__ float s_r;
+  __shared__ int s_done;
   __shared__ ShortList L;
   float *hist = L.e;                                // the descents' 256 bins and the tie list live in the list's arrays
   int *tie_list = L.idx;
   float *row = logits + (size_t)blockIdx.x * ld;
 
-  // repeat penalty, each distinct id once (src/main.c:204-223)
-  if (penalty != 1.f && recent) {
-    const int *rc = recent + (size_t)blockIdx.x * recent_ld;
-    const int n = min(max(recent_n[blockIdx.x], 0), recent_ld);   // never past the row
+  // repeat penalty, each distinct id once (src/main.c:204-223): over the ids the caller gives,
+  // or (recent == nullptr) over the last RECENT_WINDOW ids in the sequence's own ring
+  int *rec = (seq_state && slots && state_words >= SS_RING + SS_RING_WORDS)
+                 ? seq_state + (size_t)slots[blockIdx.x] * state_words : nullptr;
+  const bool ring = recent == nullptr && rec != nullptr;
+  if (penalty != 1.f && (recent || ring)) {
+    const int *rc = recent ? recent + (size_t)blockIdx.x * recent_ld : rec + SS_RING;
+    const int total = ring ? max(rec[SS_RECENT_TOTAL], 0) : 0;
+    const int n = ring ? min(total, RECENT_WINDOW) : min(max(recent_n[blockIdx.x], 0), recent_ld);   // never past the row
+    // entry i of the window (any order will do: every distinct id counts once)
+    auto entry = [&](int i) { return ring ? rc[(total - 1 - i) % SS_RING_WORDS] : rc[i]; };
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-      const int id = rc[i];
+      const int id = entry(i);
       if (id < 0 || id >= V) continue;
       bool first = true;
-      for (int j = 0; j < i; ++j) if (rc[j] == id) { first = false; break; }
+      for (int j = 0; j < i; ++j) if (entry(j) == id) { first = false; break; }
       if (!first) continue;
       const float v = row[id];
       row[id] = v > 0.f ? v / penalty : v * penalty;
     }
     __syncthreads();
   }
+  // the chosen id goes into the ring (a caller that keeps the recent ids itself passes them in)
+  auto keep = [&](int id) {
+    out_ids[blockIdx.x] = id;
+    if (ring && append) {
+      const int total = max(rec[SS_RECENT_TOTAL], 0);
+      rec[SS_RING + total % SS_RING_WORDS] = id;
+      rec[SS_RECENT_TOTAL] = total + 1;
+    }
+  };
   if (temp <= 0.f) {
     const int id = block_argmax(row, V, 1.f, nullptr);
-    if (threadIdx.x == 0) out_ids[blockIdx.x] = id;
+    if (threadIdx.x == 0) keep(id);
     return;
   }
   const float inv_temp = 1.f / temp;
   float mx;
-  block_argmax(row, V, inv_temp, &mx);
-
-  if (top_k > 0 && top_k < V && top_k <= LIST_CAP) {
-    const int n = list_top_k(row, V, inv_temp, top_k, L);
+  const bool cut_k = top_k > 0 && top_k < V;
+  // (When nothing is cut, the draw still walks the entries in descending order, as the
+  // reference's filtered sampler does: the descents below.)
+  // The kept entries as a sorted list: the best top_k, or without a top_k the best 512 or more, among
+  // which the shortest head that reaches top_p of the WHOLE row's mass usually lies.
+  const int want = cut_k ? top_k : min(V, 512);
+  if (want <= LIST_CAP && (cut_k || top_p < 1.f)) {
+    int n = list_by_sampled_floor(row, V, inv_temp, want, L);
+    if (n < 0 && cut_k) n = list_top_k(row, V, inv_temp, top_k, L);
     if (n >= 0) {
-      const int n_keep0 = min(n, top_k);
-      for (int j = threadIdx.x; j < n_keep0; j += blockDim.x) L.e[j] = expf(row[L.idx[j]] * inv_temp - mx);
+      const int n_list = cut_k ? min(n, top_k) : n;
+      mx = row[L.idx[0]] * inv_temp;               // the list's head is the row's maximum
+      float whole = 0.f;                            // without a top_k: the mass of the whole row
+      if (!cut_k) whole = admitted_mass(row, V, inv_temp, mx, 0u, V, false, scratch);
+      for (int j = threadIdx.x; j < n_list; j += blockDim.x) L.e[j] = expf(row[L.idx[j]] * inv_temp - mx);
       __syncthreads();
       if (threadIdx.x == 0) {
-        int n_keep = n_keep0;
+        int n_keep = n_list;
+        bool done = true;
         float kept = 0.f;
-        for (int j = 0; j < n_keep; ++j) kept += L.e[j];
+        if (cut_k) for (int j = 0; j < n_keep; ++j) kept += L.e[j];
+        else kept = whole;
         if (top_p < 1.f) {
-          // shortest prefix (descending) whose cumulative probability reaches top_p
+          // shortest head (descending) whose cumulative probability reaches top_p
           const float target = top_p * kept;
           float run = 0.f;
+          done = cut_k;                             // a top_k's list always holds the head; the best 512 may not
           for (int j = 0; j < n_keep; ++j) {
             run += L.e[j];
-            if (run >= target) { n_keep = j + 1; break; }
+            if (run >= target) { n_keep = j + 1; done = true; break; }
           }
           kept = 0.f;
           for (int j = 0; j < n_keep; ++j) kept += L.e[j];
         }
-        const float target = next_uniform(seq_state, slots[blockIdx.x], state_words) * kept;
-        float run = 0.f;
-        int pick = L.idx[n_keep - 1];
-        for (int j = 0; j < n_keep; ++j) {
-          run += L.e[j];
-          if (run >= target) { pick = L.idx[j]; break; }
+        s_done = done ? 1 : 0;
+        if (done) {
+          const float target = next_uniform(seq_state, slots[blockIdx.x], state_words) * kept;
+          float run = 0.f;
+          int pick = L.idx[n_keep - 1];
+          for (int j = 0; j < n_keep; ++j) {
+            run += L.e[j];
+            if (run >= target) { pick = L.idx[j]; break; }
+          }
+          keep(pick);
         }
-        out_ids[blockIdx.x] = pick;
       }
-      return;
+      __syncthreads();
+      if (s_done) return;
     }
     __syncthreads();
   }
+  block_argmax(row, V, inv_temp, &mx);
 
   // kept set: key > bound_key, or key == bound_key with index <= tie_idx
   bool bounded = false;
@@ -560,28 +771,52 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
   const Descent d = radix_descent<true>(row, V, inv_temp, mx, bound_key, bounded, target, hist);
   int choice = tie_walk<true>(row, V, inv_temp, mx, d.key, d.above, target, tie_list);
   if (bounded && d.key == bound_key && choice > tie_idx) choice = tie_idx;
-  if (threadIdx.x == 0) out_ids[blockIdx.x] = choice < 0 ? 0 : choice;
+  if (threadIdx.x == 0) keep(choice < 0 ? 0 : choice);
 }
 
-// recent: [R, recent_ld] ids, recent_n[R] how many are valid; logits are modified in
-// place by the penalty.
+// recent: [R, recent_ld] ids, recent_n[R] how many are valid; or recent == nullptr: the last
+// ids of every row's sequence are in its record (seq_state[slots[row]]), and with `append` the
+// chosen id is added to them.  logits are modified in place by the penalty.
 extern "C" int g2b_sample_filtered(float *logits, int R, int V, int ld, float temp, int top_k,
                                    float top_p, float penalty, const int *recent, int recent_ld,
                                    const int *recent_n, int *seq_state, int state_words,
-                                   const int *slots, int *out_ids, cudaStream_t stream) {
+                                   const int *slots, int *out_ids, int append, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V <= 0 || ld < V) G2B_REFUSE("sample_filtered: bad sizes V=%d ld=%d", V, ld);
   if (!(top_p > 0.f)) G2B_REFUSE("sample_filtered: top_p must be in (0, 1], got %g", top_p);
   if (!(penalty > 0.f)) G2B_REFUSE("sample_filtered: repeat penalty must be positive, got %g", penalty);
   if (temp > 0.f && (!seq_state || !slots || state_words < 4))
     G2B_REFUSE("sample_filtered: temperature sampling needs the per-slot state");
+  if (!recent && penalty != 1.f && (!seq_state || !slots || state_words < SS_RING + SS_RING_WORDS))
+    G2B_REFUSE("sample_filtered: a repeat penalty without the recent ids needs the per-slot records with their rings");
   g2b_launch(sample_filtered_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, 
       logits, V, ld, temp, top_k, top_p, penalty, recent, recent_ld, recent_n, seq_state,
-      state_words, slots, out_ids);
+      state_words, slots, out_ids, append);
   return g2b_check_launch("sample_filtered");
 }
 
-// Seeds the per-slot records of the given slots: {seed_lo, seed_hi, stream, draws = 0}.
+// Starts the rings of recent ids of the given slots: src [n, 1 + RECENT_WINDOW] = count, ids
+// (oldest first).
+__global__ void recent_set_kernel(int *seq_state, int words, const int *slots, const int *src, int n) {
+  pdl_launch();
+  pdl_wait();
+  const int r = blockIdx.x;
+  if (r >= n) return;
+  int *rec = seq_state + (size_t)slots[r] * words;
+  const int *row = src + (size_t)r * (1 + RECENT_WINDOW);
+  const int count = min(max(row[0], 0), RECENT_WINDOW);
+  for (int i = threadIdx.x; i < count; i += blockDim.x) rec[SS_RING + i] = row[1 + i];
+  if (threadIdx.x == 0) rec[SS_RECENT_TOTAL] = count;
+}
+
+extern "C" int g2b_recent_set(int *seq_state, int words, const int *slots, const int *src, int n,
+                              cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (words < SS_RING + SS_RING_WORDS) G2B_REFUSE("recent_set: records of %d words have no ring", words);
+  g2b_launch(recent_set_kernel, dim3(n), dim3(64), 0, stream, seq_state, words, slots, src, n);
+  return g2b_check_launch("recent_set");
+}
+
 __global__ void seed_slots_kernel(int *seq_state, int words, const int *slots, const int *streams,
                                   int n, uint32_t seed_lo, uint32_t seed_hi) {
   pdl_launch();

@@ -14,11 +14,10 @@ from .step import Engine, StepEntry, StepError
 
 
 class _Handle:
-    __slots__ = ("seq", "recent")
+    __slots__ = ("seq",)
 
     def __init__(self, seq: CacheSequence):
         self.seq = seq
-        self.recent: list = []
 
 
 class EngineBackend:
@@ -79,21 +78,17 @@ class EngineBackend:
             self._ids = torch.empty(2 * R, dtype=torch.int32, device=self.engine.device)
             self._slots = torch.empty(2 * R, dtype=torch.int32, device=self.engine.device)
         self._slots[:R].copy_(torch.tensor([h.seq.slot for h in handles], dtype=torch.int32))
-        recent = [h.recent for h in handles] if self.params.repeat_penalty != 1.0 else None
-        self.sampler.sample(logits, self.params, self._slots[:R], self._ids[:R], recent)
+        self.sampler.sample(logits, self.params, self._slots[:R], self._ids[:R])
         out = self._ids[:R].tolist()
         self.engine.check()                    # never hand on tokens of a launch that gave up a wait
-        for h, t in zip(handles, out):
-            h.recent.append(t)
-            del h.recent[:-RECENT_USE]
         return out
 
     def prefill(self, handles: Sequence[_Handle], prompts: Sequence[Sequence[int]]) -> list:
         self._drop_session()
         entries = [StepEntry(h.seq, p, (len(p) - 1,)) for h, p in zip(handles, prompts)]
         logits = self.engine.step(entries)
-        for h, p in zip(handles, prompts):
-            h.recent = list(p[-RECENT_USE:])
+        if self.params.repeat_penalty != 1.0:  # the tails of the prompts: what the penalty looks back over first
+            self.sampler.set_recent([h.seq.slot for h in handles], [p[-RECENT_USE:] for p in prompts])
         return self._sample(logits, handles)
 
     def decode(self, handles: Sequence[_Handle], tokens: Sequence[int]) -> list:
@@ -112,11 +107,7 @@ class EngineBackend:
                                           self.params, self.use_graph)
             self._session_key = key
         session = self._session
-        recent = [h.recent for h in handles] if self.params.repeat_penalty != 1.0 else None
-        out = session.step(tokens, recent)
-        for h, t in zip(handles, out):
-            h.recent.append(t)
-            del h.recent[:-RECENT_USE]
+        out = session.step(tokens)
         self.decode_seconds += time.perf_counter() - t0
         self.decode_steps += 1
         self.decode_tokens += len(handles)

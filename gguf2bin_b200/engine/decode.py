@@ -51,9 +51,9 @@ class DecodeRunner:
 
     EAGER_STEPS = 4          # plain steps of a shape before its graph is captured
 
-    def __init__(self, engine: Engine, batch: int, table_width: int, temperature: Optional[float]):
+    def __init__(self, engine: Engine, batch: int, table_width: int, params: Optional[SamplingParams]):
         self.engine, self.batch, self.table_width = engine, batch, table_width
-        self.temperature = temperature          # None: the sampler runs after the step, outside a graph
+        self.params = params                    # None: the caller samples after the step, outside a graph
         B, P, dev = batch, table_width, engine.device
         self.n_meta = 4 * B + B * P
         self._meta = torch.zeros(self.n_meta, dtype=torch.int32, device=dev)
@@ -106,9 +106,14 @@ class DecodeRunner:
         eng = self.engine
         self.logits = eng.workspace.buffer("decode.logits", (self.batch, eng.model.vocab), torch.float32)
         eng.model.forward(self.ctx, eng.cache, self.want_rows, self.batch, logits_out=self.logits)
-        if self.temperature is not None:
-            kernels.sample_rows(self.logits, self.temperature, eng.cache.seq_state, self.slots,
-                                self.tok_ids)
+        p = self.params
+        if p is not None:
+            if p.filtered:        # the repeat penalty reads and extends the sequences' rings of recent ids
+                kernels.sample_filtered(self.logits, p.temperature, p.top_k, p.top_p, p.repeat_penalty,
+                                        None, None, eng.cache.seq_state, self.slots, self.tok_ids, append=True)
+            else:
+                kernels.sample_rows(self.logits, p.temperature, eng.cache.seq_state, self.slots,
+                                    self.tok_ids)
             kernels.advance_positions(self.tok_pos, self.batch)
 
     def run(self, use_graph: bool, eager_steps: int) -> None:
@@ -137,15 +142,15 @@ class DecodeRunner:
         self.plain_steps += 1
 
 
-def decode_runner(engine: Engine, batch: int, pages: int, temperature: Optional[float]) -> DecodeRunner:
-    """The engine's runner for this shape, made at its first use; the least recently used
-    ones go when there are more than ``Engine.DECODE_RUNNERS_KEPT``."""
+def decode_runner(engine: Engine, batch: int, pages: int, params: Optional[SamplingParams]) -> DecodeRunner:
+    """The engine's runner for this shape and way of sampling, made at its first use; the least
+    recently used ones go when there are more than ``Engine.DECODE_RUNNERS_KEPT``."""
     width = -(-max(int(pages), 1) // PAGE_TABLE_STEP) * PAGE_TABLE_STEP
-    key = (batch, width, temperature)
+    key = (batch, width, params)
     runners = engine.decode_runners
     runner = runners.get(key)
     if runner is None:
-        runner = runners[key] = DecodeRunner(engine, batch, width, temperature)
+        runner = runners[key] = DecodeRunner(engine, batch, width, params)
         while len(runners) > engine.DECODE_RUNNERS_KEPT:
             runners.popitem(last=False)
     else:
@@ -166,11 +171,10 @@ class DecodeSession:
             raise StepError("a decode session needs at least one sequence")
         if sampler.seq_state is not engine.cache.seq_state:
             raise StepError("the sampler of a decode session must use the engine's per-slot records")
-        # sampling inside the graph needs no host data; filtered sampling uploads the
-        # recent tokens every step and therefore runs after the graph
-        self._sample_in_graph = not params.filtered
-        self.runner = decode_runner(engine, B, max(len(s.pages) for s in self.seqs),
-                                    params.temperature if self._sample_in_graph else None)
+        # sampling runs inside the step (and its graph): it needs no host data, the recent ids
+        # that a repeat penalty looks at are in the sequences' records on the device
+        self._sample_in_graph = True
+        self.runner = decode_runner(engine, B, max(len(s.pages) for s in self.seqs), params)
         self.runner.bind(self)
         self.use_graph = use_graph and engine.model.graph_safe
         self.eager_steps = max(1, DecodeRunner.EAGER_STEPS if eager_steps is None else int(eager_steps))
@@ -212,7 +216,7 @@ class DecodeSession:
         runner.tok_ids.copy_(runner.pinned_in, non_blocking=True)
         runner.tokens_uploaded.record()
 
-    def run(self, recent=None) -> None:
+    def run(self) -> None:
         """One step: feeds ``tok_ids``, leaves the sampled tokens in ``tok_ids`` and the
         logits in ``logits``."""
         page = self.engine.cache.page_size
@@ -223,7 +227,7 @@ class DecodeSession:
         runner.ctx.past_lens = [s.length for s in self.seqs]
         runner.run(self.use_graph, self.eager_steps)
         if not self._sample_in_graph:
-            self.sampler.sample(runner.logits, self.params, runner.slots, runner.tok_ids, recent)
+            self.sampler.sample(runner.logits, self.params, runner.slots, runner.tok_ids)
             kernels.advance_positions(runner.tok_pos, self.batch)
         for s in self.seqs:
             s.length += 1
@@ -260,7 +264,7 @@ class DecodeSession:
         limit = self.engine.model.spec.max_positions
         return all(s.length + 1 <= len(s.pages) * page and s.length + 1 <= limit for s in self.seqs)
 
-    def step(self, tokens: Sequence[int], recent=None) -> list:
+    def step(self, tokens: Sequence[int]) -> list:
         """Feeds one token per sequence and returns the sampled next tokens, through pinned
         host memory both ways.  Steps that sample on the device are launched one ahead."""
         tokens = [int(t) for t in tokens]
@@ -269,12 +273,12 @@ class DecodeSession:
         else:
             self.take_back()
             self.set_tokens(tokens)
-            self.run(recent)
+            self.run()
             turn = self._send_back()
         self._ahead = None
         ahead_turn = None
         if self._may_run_ahead and self._room_for_one_more():
-            self.run(None)                           # the next step, fed by the tokens being sampled now;
+            self.run()                               # the next step, fed by the tokens being sampled now;
             ahead_turn = self._send_back()           # queued before this step's tokens are waited for
         out = self._collect(turn)
         if ahead_turn is not None:
@@ -288,6 +292,6 @@ class DecodeSession:
         self._ahead = None
         self._own_runner()
         kernels.rewind_step(self.runner.tok_pos, self.batch, self.sampler.seq_state, self.runner.slots,
-                            self.params.temperature > 0.0)
+                            self.params.temperature > 0.0, self.params.filtered)
         for s in self.seqs:
             s.length -= 1

@@ -17,7 +17,7 @@ from .csrc.build import KernelBuildError, KernelError, load_unit
 
 __all__ = ["KernelError", "KernelBuildError", "embed_rows", "rmsnorm", "qknorm_rope_cache",
            "rope_table", "cache_write", "swiglu", "advance_positions", "gemm_simt", "linear", "attn_generic",
-           "attention", "sample_rows", "sample_filtered", "seed_slots"]
+           "attention", "sample_rows", "sample_filtered", "recent_set", "seed_slots"]
 
 F32, BF16 = 0, 1
 EPI_STORE_F32, EPI_STORE_BF16, EPI_ACCUM_F32 = 0, 1, 2
@@ -193,12 +193,15 @@ def advance_positions(tok_pos: torch.Tensor, n: int) -> None:
 
 
 def rewind_step(tok_pos: torch.Tensor, n: int, seq_state: Optional[torch.Tensor], slots: Optional[torch.Tensor],
-                undo_draw: bool) -> None:
-    """Takes back the device-side bookkeeping of one decode step (positions, and the draw
-    counters of the sampling records when that step sampled with a random number)."""
-    f = _fn("elementwise.cu", "g2b_rewind_step", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p])
+                undo_draw: bool, undo_recent: bool = False) -> None:
+    """Takes back the device-side bookkeeping of one decode step (positions; the draw
+    counters of the sampling records when that step sampled with a random number; the count
+    of recent ids when it added one to the sequences' rings)."""
+    f = _fn("elementwise.cu", "g2b_rewind_step",
+            [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
     words = seq_state.shape[1] if seq_state is not None else 0
-    _call(f, _ptr(tok_pos), n, _ptr(seq_state), words, _ptr(slots), 1 if undo_draw else 0, _stream())
+    _call(f, _ptr(tok_pos), n, _ptr(seq_state), words, _ptr(slots), 1 if undo_draw else 0,
+          1 if undo_recent else 0, _stream())
 
 
 # ---------------------------------------------------------------------------
@@ -352,9 +355,11 @@ def sample_rows(logits, temperature, seq_state, slots, out_ids) -> None:
 
 
 def sample_filtered(logits, temperature, top_k, top_p, penalty, recent, recent_n, seq_state, slots,
-                    out_ids) -> None:
+                    out_ids, append: bool = False) -> None:
     """Repeat penalty, top-k, top-p, then temperature sampling; logits are changed in
-    place by the penalty.  recent int32 [R, n], recent_n int32 [R]."""
+    place by the penalty.  recent int32 [R, n], recent_n int32 [R]; or ``recent=None``: every
+    row's recent ids are those in its sequence's record (``seq_state[slots[row]]``), to which
+    the chosen id is added when ``append`` is set."""
     _need(logits, torch.float32, "logits")
     _need(out_ids, torch.int32, "out_ids")
     R, V = logits.shape
@@ -365,11 +370,22 @@ def sample_filtered(logits, temperature, top_k, top_p, penalty, recent, recent_n
             raise KernelError("sample_filtered: recent and recent_n need a row per row of logits")
     f = _fn("sampling.cu", "g2b_sample_filtered",
             [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_void_p, c_int,
-             c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
+             c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p])
     _call(f, _ptr(logits), R, V, logits.stride(0), temperature, top_k, top_p, penalty,
           _ptr(recent), recent.shape[1] if recent is not None else 0, _ptr(recent_n),
           _ptr(seq_state), seq_state.shape[1] if seq_state is not None else 0, _ptr(slots),
-          _ptr(out_ids), _stream())
+          _ptr(out_ids), 1 if append else 0, _stream())
+
+
+def recent_set(seq_state, slots, rows) -> None:
+    """Starts the recent-id rings of the given slots: rows int32 [n, 65] = count, ids (oldest
+    first); the repeat penalty of later ``sample_filtered`` calls without ``recent`` reads them."""
+    _need(slots, torch.int32, "slots")
+    _need(rows, torch.int32, "rows")
+    if rows.dim() != 2 or rows.shape[1] != 65 or rows.shape[0] < slots.shape[0]:
+        raise KernelError("recent_set: rows must be [n, 65]")
+    f = _fn("sampling.cu", "g2b_recent_set", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p])
+    _call(f, _ptr(seq_state), seq_state.shape[1], _ptr(slots), _ptr(rows), slots.shape[0], _stream())
 
 
 def seed_slots(seq_state, slots, streams, seed: int) -> None:

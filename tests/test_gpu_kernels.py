@@ -245,6 +245,49 @@ def test_sampling_filtered(top_k, top_p, penalty, V, ties):
         assert ids[r].item() == P.sample_advanced(logits[r].cpu().numpy(), 0.0, top_k, top_p, penalty, rec, 0.5)[0]
 
 
+def test_sampling_with_the_recent_ids_on_the_device():
+    """The repeat penalty over the ids in the sequences' own records: started with a prompt's
+    tail (three, sixty-four and no ids), extended by every sampled id, across the ring's wrap,
+    and with one step taken back; every draw against the plain sampler given the same window."""
+    from gguf2bin_b200 import kernels
+    from gguf2bin_b200.cache import SEQ_STATE_WORDS, SS_RECENT_TOTAL
+    R, V, temp, top_k, top_p, penalty = 3, 1009, 0.7, 20, 0.9, 1.5
+    seed = 99
+    state = torch.zeros(5, SEQ_STATE_WORDS, dtype=torch.int32, device=DEV)
+    slots = torch.tensor([4, 0, 2], dtype=torch.int32, device=DEV)
+    kernels.seed_slots(state, slots, torch.arange(R, dtype=torch.int32, device=DEV), seed)
+    g = torch.Generator().manual_seed(3)
+    windows = [torch.randint(0, V, (n,), generator=g).tolist() for n in (3, 64, 0)]
+    rows = torch.zeros(R, 65, dtype=torch.int32)
+    for r, w in enumerate(windows):
+        rows[r, 0] = len(w)
+        rows[r, 1:1 + len(w)] = torch.tensor(w, dtype=torch.int32)
+    kernels.recent_set(state, slots, rows.to(DEV))
+    ids = torch.empty(R, dtype=torch.int32, device=DEV)
+    draws = [0] * R
+    for step in range(90):                               # past the ring's 72 places
+        logits = rnd(R, V, scale=2.5, seed=400 + step)
+        work = logits.clone()
+        kernels.sample_filtered(work, temp, top_k, top_p, penalty, None, None, state, slots, ids, append=True)
+        got = ids.tolist()
+        for r in range(R):
+            u = philox_plain.uniform(seed, r, draws[r])
+            _, kept, cdf = P.sample_advanced(logits[r].cpu().numpy(), temp, top_k, top_p, penalty, windows[r][-64:], u)
+            where = np.nonzero(kept == got[r])[0]
+            assert len(where) == 1, (step, r, got[r], "not in the kept set")
+            i = int(where[0])
+            assert (cdf[i - 1] if i > 0 else 0.0) - 1e-4 <= u <= cdf[i] + 1e-4, (step, r)
+            draws[r] += 1
+            windows[r].append(got[r])
+        if step % 7 == 3:                                # this step is taken back: its id and its draw do not count
+            pos = torch.zeros(R, dtype=torch.int32, device=DEV)
+            kernels.rewind_step(pos, R, state, slots, True, True)
+            for r in range(R):
+                windows[r].pop()
+                draws[r] -= 1
+    assert state[slots.long(), SS_RECENT_TOTAL].tolist() == [len(w) for w in windows]
+
+
 @pytest.mark.parametrize("fine", [False, True])
 @pytest.mark.parametrize("nh,nkv,hd,window", [(16, 8, 128, 0), (5, 1, 128, 0), (20, 1, 64, 0), (6, 2, 64, 300),
                                               (4, 4, 128, 70)])
