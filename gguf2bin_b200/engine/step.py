@@ -24,6 +24,8 @@ from ..parts.base import ATTN_TILE_ROWS, ATTN_WIDE_TILE_ROWS, StepContext
 from .model import Model
 from .workspace import Workspace
 
+SINGLE_TABLE_STEP = 4        # page-table widths of one-token steps are rounded up to this many pages
+
 
 class StepError(ValueError):
     """A step that cannot run; nothing was changed."""
@@ -48,7 +50,7 @@ class Engine:
     a prompt step is a few hundred launches, and the host's share of it (a few microseconds
     each) otherwise competes with the device's."""
 
-    GRAPH_MIN_TOKENS = 32        # smaller steps are cheap to launch (and decoding has its own session)
+    GRAPH_MIN_TOKENS = 32        # smaller prompt steps are cheap to launch
     GRAPHS_KEPT = 8
     DECODE_RUNNERS_KEPT = 24     # shapes of decode steps whose buffers and graphs are kept (engine/decode.py)
 
@@ -125,6 +127,8 @@ class Engine:
         past = [e.seq.length for e in entries]
         T = sum(q_lens)
         P = max(len(e.seq.pages) for e in entries)
+        if T == B:                   # one token each: the table's width in steps, so that the shape's graph lasts
+            P = -(-P // SINGLE_TABLE_STEP) * SINGLE_TABLE_STEP
         n_want = sum(len(e.want) for e in entries)
         # prompt-attention work list: tiles of 64 query rows, the longest key ranges first
         tiles, wide = [], []
@@ -201,11 +205,22 @@ class Engine:
     def _forward(self, entries, ctx: StepContext, want_rows, n_want) -> Optional[torch.Tensor]:
         """The model's forward pass of this step: replayed from a graph when the step's shape
         has been seen before, captured at its second appearance, run plainly otherwise."""
-        if not self.step_graphs or ctx.n_tokens < self.GRAPH_MIN_TOKENS:
+        single = ctx.all_single
+        if single:
+            # One token per sequence: the kernels take every position from device memory, so one
+            # graph serves the shape for as long as the page table keeps its width; the attention
+            # is laid out for all the keys the table covers and plans with those there are.
+            ctx.kv_len_hint = ctx.max_kv_len
+            ctx.max_kv_len = ctx.page_table.shape[1] * self.cache.page_size
+        if not self.step_graphs or (ctx.n_tokens < self.GRAPH_MIN_TOKENS and not single):
             return self.model.forward(ctx, self.cache, want_rows, n_want)
         # everything a launch argument or a buffer address is derived from
-        key = (tuple(ctx.q_lens), tuple(ctx.past_lens), tuple(len(e.want) for e in entries),
-               ctx.page_table.shape[1], self._meta_dev.data_ptr())
+        if single:
+            key = ("single", ctx.n_seqs, tuple(len(e.want) for e in entries), ctx.page_table.shape[1],
+                   self._meta_dev.data_ptr())
+        else:
+            key = (tuple(ctx.q_lens), tuple(ctx.past_lens), tuple(len(e.want) for e in entries),
+                   ctx.page_table.shape[1], self._meta_dev.data_ptr())
         hit = self._graphs.get(key)
         if hit is not None:
             graph, generation, logits = hit
