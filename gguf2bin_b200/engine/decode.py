@@ -31,6 +31,7 @@ so a model with such a layer never runs ahead.
 """
 from __future__ import annotations
 
+import weakref
 from typing import Optional, Sequence
 
 import numpy as np
@@ -41,7 +42,7 @@ from ..cache.pool import Sequence as CacheSequence
 from ..cache.storage import KVNeed
 from ..parts.base import StepContext
 from ..sampling import Sampler, SamplingParams
-from .step import Engine, StepError
+from .step import Engine, StepError, capture_graph
 
 PAGE_TABLE_STEP = 4          # page-table widths are rounded up to this many pages (one 256-key chunk)
 
@@ -77,7 +78,7 @@ class DecodeRunner:
         self.out_ready = [torch.cuda.Event(), torch.cuda.Event()]
         self.out_turn = 0
         self.tokens_uploaded = torch.cuda.Event()
-        self.owner: Optional["DecodeSession"] = None
+        self._owner = None                      # weak: the session holds the runner, not the other way round
         self.logits: Optional[torch.Tensor] = None
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._graph_generation = -1
@@ -100,7 +101,10 @@ class DecodeRunner:
         self.ctx.slots = [s.slot for s in session.seqs]
         # the page table is as wide as what is reserved; kernels that size their work by the keys plan with what is there
         self.ctx.kv_len_hint = max(s.length for s in session.seqs) + 1
-        self.owner = session
+        self._owner = weakref.ref(session)
+
+    def owned_by(self, session: "DecodeSession") -> bool:
+        return self._owner is not None and self._owner() is session
 
     def _launch(self) -> None:
         eng = self.engine
@@ -127,9 +131,7 @@ class DecodeRunner:
         if use_graph and self.plain_steps >= eager_steps:
             torch.cuda.current_stream().synchronize()
             generation = ws.generation
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                self._launch()
+            g, _ = capture_graph(self._launch)
             self.launches_per_step = kernels.launch_count() - before
             self.engine.decode_graph_captures += 1
             if ws.generation == generation:
@@ -204,7 +206,7 @@ class DecodeSession:
     def _own_runner(self) -> None:
         """Another session of the same shape may have used the runner since: write this
         session's data back (positions follow from the sequences' lengths)."""
-        if self.runner.owner is not self:
+        if not self.runner.owned_by(self):
             self.runner.bind(self)
 
     def set_tokens(self, tokens: Sequence[int]) -> None:

@@ -11,6 +11,7 @@ the cache, positions); a refused step changes nothing.
 """
 from __future__ import annotations
 
+import gc
 from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Optional, Sequence as Seq
@@ -29,6 +30,23 @@ SINGLE_TABLE_STEP = 4        # page-table widths of one-token steps are rounded 
 
 class StepError(ValueError):
     """A step that cannot run; nothing was changed."""
+
+
+def capture_graph(launch):
+    """Captures what ``launch()`` puts on the current stream in a new CUDA graph; returns the
+    graph and ``launch``'s result.  The collector of reference cycles is held off meanwhile: it
+    could free an older graph in the middle of the capture, and releasing a graph is an
+    operation that a capturing stream forbids (the capture would be lost)."""
+    graph = torch.cuda.CUDAGraph()
+    collecting = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph):
+            result = launch()
+    finally:
+        if collecting:
+            gc.enable()
+    return graph, result
 
 
 @dataclass
@@ -233,9 +251,7 @@ class Engine:
             # the shape ran plainly before, so every scratch buffer it needs exists already
             torch.cuda.current_stream().synchronize()
             generation = self.workspace.generation
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                logits = self.model.forward(ctx, self.cache, want_rows, n_want)
+            graph, logits = capture_graph(lambda: self.model.forward(ctx, self.cache, want_rows, n_want))
             self.step_graph_captures += 1
             if self.workspace.generation == generation:
                 self._graphs[key] = (graph, generation, logits)

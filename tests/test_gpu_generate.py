@@ -254,6 +254,60 @@ def test_decode_graphs_are_kept_by_shape_not_by_call(llms):
     assert eng.cache.table.slots.n_held == 0 and eng.cache.table.pages.n_held == 0
 
 
+def test_graphs_that_are_let_go_do_not_spoil_a_capture(llms):
+    """Shapes come and go (sequences that end at different steps, more shapes than the engine
+    keeps runners for), and Python's collector of cycles is set to run at every few allocations:
+    a graph that is released while another is being captured would end that capture with an
+    error.  Tokens equal those of an engine that uses no graphs."""
+    import gc
+    llm = llms("c", "bfloat16", max_tokens=16 * 128)
+    eng = llm.engine
+    prompts = [random_tokens("c", 3 + (i % 6), 800 + i) for i in range(12)]
+    kw = dict(temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0, ignore_eos=True)
+    kept, eng.DECODE_RUNNERS_KEPT = eng.DECODE_RUNNERS_KEPT, 2
+    thresholds = gc.get_threshold()
+    before = eng.decode_graph_captures
+    try:
+        gc.set_threshold(5, 1, 1)
+        with_graphs = [llm.generate(prompts[:b], n=8, max_batch=b, **kw) for b in (12, 7, 3, 9, 12, 5, 7)]
+    finally:
+        gc.set_threshold(*thresholds)
+        eng.DECODE_RUNNERS_KEPT = kept
+    assert eng.decode_graph_captures - before >= 6
+    llm.use_graph = False
+    try:
+        plain = [llm.generate(prompts[:b], n=8, max_batch=b, **kw) for b in (12, 7, 3, 9, 12, 5, 7)]
+    finally:
+        llm.use_graph = True
+    assert [[o.tokens for o in call] for call in with_graphs] == [[o.tokens for o in call] for call in plain]
+
+
+def test_the_cycle_collector_rests_while_a_graph_is_captured():
+    """Releasing a CUDA graph is forbidden while a stream captures, and Python's collector of
+    cycles may release one at any allocation: ``capture_graph`` holds it off and puts it back."""
+    import gc
+    from gguf2bin_b200.engine.step import capture_graph
+    x = torch.zeros(4, device="cuda")
+    seen = []
+
+    def launch():
+        seen.append(gc.isenabled())
+        x.add_(1.0)
+        return "result"
+    assert gc.isenabled()
+    graph, result = capture_graph(launch)
+    assert seen == [False] and gc.isenabled() and result == "result"
+    graph.replay()
+    graph.replay()
+    assert x.tolist() == [2.0] * 4
+    gc.disable()
+    try:
+        capture_graph(launch)
+        assert not gc.isenabled(), "a collector that was off stays off"
+    finally:
+        gc.enable()
+
+
 @pytest.mark.parametrize("use_graph", [False, True])
 def test_steps_taken_back_at_page_edges_leave_the_same_bits(llms, use_graph):
     """Every step is followed by a step launched ahead that is then taken back, with sequences
