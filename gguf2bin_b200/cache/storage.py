@@ -17,6 +17,10 @@ Beside the groups there is one fixed-size record per slot, ``seq_state``
 a sequence's random stream does not depend on the batch it is in, and so do the sequence's
 most recent tokens (a ring of ``SS_RING_WORDS`` ids and the count of tokens written to it),
 which the repeat penalty reads on the device.
+
+Every storage has one page and one slot more than the table hands out (``spare_page``,
+``spare_slot``): a step that runs more rows than it has sequences, to keep a shape it has
+launches for, points the extra rows there; what they write is never read by a sequence.
 """
 from __future__ import annotations
 
@@ -83,6 +87,7 @@ class Cache:
         self.table = SlotTable(n_slots, n_pages, self.page_size)
         self.dtype, self.device = dtype, torch.device(device)
         self.n_pages, self.n_slots = n_pages, n_slots
+        self.spare_page, self.spare_slot = n_pages, n_slots          # beyond what the table hands out
         self.groups: dict[tuple, dict] = {}
         self._layer_group: dict[int, tuple] = {}
         for layer, need in enumerate(needs):
@@ -95,12 +100,12 @@ class Cache:
             need, nl = g["need"], len(g["layers"])
             if isinstance(need, KVNeed):
                 g["storage"] = torch.zeros(
-                    (nl, n_pages, 2, need.n_kv_heads, self.page_size, need.head_dim),
+                    (nl, n_pages + 1, 2, need.n_kv_heads, self.page_size, need.head_dim),
                     dtype=dtype, device=self.device)
             else:
-                g["storage"] = torch.zeros((nl, n_slots) + tuple(need.shape), dtype=need.dtype,
+                g["storage"] = torch.zeros((nl, n_slots + 1) + tuple(need.shape), dtype=need.dtype,
                                            device=self.device)
-        self.seq_state = torch.zeros((n_slots, SEQ_STATE_WORDS), dtype=torch.int32,
+        self.seq_state = torch.zeros((n_slots + 1, SEQ_STATE_WORDS), dtype=torch.int32,
                                      device=self.device)
         self._views: dict = {}
 

@@ -632,7 +632,7 @@ __global__ void rewind_step_kernel(int *tok_pos, int n, int *seq_state, int word
   pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  tok_pos[i] -= 1;
+  tok_pos[i] = max(tok_pos[i] - 1, 0);          // a row of padding may have been set back to 0 since the step
   if (undo_draw) seq_state[(size_t)slots[i] * words + 3] -= 1;
   if (undo_recent) seq_state[(size_t)slots[i] * words + 4] -= 1;
 }

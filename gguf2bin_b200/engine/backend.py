@@ -34,7 +34,6 @@ class EngineBackend:
         self._slots = torch.empty(1024, dtype=torch.int32, device=engine.device)
         self.use_graph = use_graph
         self._session: Optional[DecodeSession] = None
-        self._session_key: tuple = ()
         # wall-clock account of the decode calls, for measurements through this API
         self.decode_seconds = 0.0
         self.decode_steps = 0
@@ -68,8 +67,8 @@ class EngineBackend:
 
     def close(self, handle: _Handle) -> None:
         if handle.seq.slot >= 0:
-            if self._session is not None and any(s is handle.seq for s in self._session.seqs):
-                self._drop_session()           # its batch no longer exists
+            if self._session is not None and not self._session.retire(handle.seq):
+                self._drop_session()           # the others are better off as a batch of their own
             self.engine.close_sequence(handle.seq)
 
     def _sample(self, logits: torch.Tensor, handles: Sequence[_Handle]) -> list:
@@ -94,19 +93,20 @@ class EngineBackend:
     def decode(self, handles: Sequence[_Handle], tokens: Sequence[int]) -> list:
         """Feeds one token per sequence (host to device), returns the sampled next tokens
         (device to host).  While the same sequences keep decoding, the step runs as a
-        ``DecodeSession`` (index tensors resident, launches replayed from a graph)."""
+        ``DecodeSession`` (index tensors resident, launches replayed from a graph).  With a repeat
+        penalty the tokens fed are expected to be the ones sampled: the recent ids that the penalty
+        reads are kept on the device as they are sampled."""
         t0 = time.perf_counter()
         V = self.engine.model.vocab
         for t in tokens:
             if not (0 <= int(t) < V):
                 raise StepError(f"token id {t} outside the vocabulary 0..{V - 1}")
-        key = tuple(id(h) for h in handles)
-        if self._session is None or self._session_key != key:
-            self._drop_session()
-            self._session = DecodeSession(self.engine, [h.seq for h in handles], self.sampler,
-                                          self.params, self.use_graph)
-            self._session_key = key
         session = self._session
+        if session is None or len(session.seqs) != len(handles) or any(
+                s is not h.seq for s, h in zip(session.seqs, handles)):
+            self._drop_session()
+            session = self._session = DecodeSession(self.engine, [h.seq for h in handles], self.sampler,
+                                                    self.params, self.use_graph)
         out = session.step(tokens)
         self.decode_seconds += time.perf_counter() - t0
         self.decode_steps += 1

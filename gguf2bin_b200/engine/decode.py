@@ -13,8 +13,13 @@ of a shape and the CUDA graph captured over them belong to the engine, as a
 ``DecodeRunner`` kept by shape: a new session of a shape that was seen before (another
 call, or the batch that is left when a sequence ends and an earlier batch had that size)
 writes its sequences' data into the runner's buffers and replays the graph that is there.
-A graph is captured only once a shape has run plainly a few times, so a batch whose
-sequences end one after another does not pay a capture for every size it passes through.
+A graph is captured only once a shape has run plainly a few times, and a batch of more than
+a few sequences runs with its rows rounded up to a multiple of eight: the rows beyond its
+sequences feed the cache's spare page and slot, and nobody reads what they produce.  When a
+sequence of the batch ends, its row becomes one more of these and the others stay where they
+are (``retire``); only when eight rows fewer will do is the batch put together anew.  So a
+batch whose sequences end one after another passes through few shapes, keeps replaying the
+graph it has, and loses no step that was launched ahead.
 
 The pages of every sequence must be reserved up to the length it can reach before the
 session starts (the page table is uploaded once).
@@ -45,6 +50,13 @@ from ..sampling import Sampler, SamplingParams
 from .step import Engine, StepError, capture_graph
 
 PAGE_TABLE_STEP = 4          # page-table widths are rounded up to this many pages (one 256-key chunk)
+ROW_STEP = 8                 # batches of more than EXACT_ROWS sequences run this many rows at a time
+EXACT_ROWS = 4
+
+
+def padded_rows(n_seqs: int) -> int:
+    """Rows that a decode step of ``n_seqs`` sequences runs."""
+    return n_seqs if n_seqs <= EXACT_ROWS else -(-n_seqs // ROW_STEP) * ROW_STEP
 
 
 class DecodeRunner:
@@ -85,20 +97,29 @@ class DecodeRunner:
         self.plain_steps = 0
         self.launches_per_step = 0
 
-    def bind(self, session: "DecodeSession") -> None:
-        """Writes the session's sequences into the buffers: positions, slots, pages."""
+    def bind(self, session: "DecodeSession", keep_tokens: bool = False) -> None:
+        """Writes the session's sequences into the buffers, each in its row: positions, slots,
+        pages.  The other rows start at position 0 of the cache's spare page with the spare slot's
+        record; they advance with the others, so they stay below the positions the table covers.
+        ``keep_tokens``: the token ids that the last step left on the device stay (the rows have
+        steps behind them)."""
         B, P = self.batch, self.table_width
+        cache = self.engine.cache
         self._uploaded.synchronize()               # the staging buffer's last copy is over
         host = self._meta_host.numpy()
-        host[:] = 0
-        host[B:2 * B] = [s.length for s in session.seqs]         # positions of the next tokens
+        host[:2 * B] = 0
         host[2 * B:3 * B] = np.arange(B)
-        host[3 * B:4 * B] = [s.slot for s in session.seqs]
-        for b, s in enumerate(session.seqs):
-            host[4 * B + b * P:4 * B + b * P + len(s.pages)] = s.pages
-        self._meta.copy_(self._meta_host, non_blocking=True)
+        host[3 * B:4 * B] = cache.spare_slot
+        host[4 * B:] = cache.spare_page
+        slots = [cache.spare_slot] * B
+        for r, s in zip(session.rows, session.seqs):
+            host[B + r] = s.length                 # position of the next token
+            host[3 * B + r] = slots[r] = s.slot
+            host[4 * B + r * P:4 * B + r * P + len(s.pages)] = s.pages
+        first = B if keep_tokens else 0
+        self._meta[first:].copy_(self._meta_host[first:], non_blocking=True)
         self._uploaded.record()
-        self.ctx.slots = [s.slot for s in session.seqs]
+        self.ctx.slots = slots
         # the page table is as wide as what is reserved; kernels that size their work by the keys plan with what is there
         self.ctx.kv_len_hint = max(s.length for s in session.seqs) + 1
         self._owner = weakref.ref(session)
@@ -145,8 +166,8 @@ class DecodeRunner:
 
 
 def decode_runner(engine: Engine, batch: int, pages: int, params: Optional[SamplingParams]) -> DecodeRunner:
-    """The engine's runner for this shape and way of sampling, made at its first use; the least
-    recently used ones go when there are more than ``Engine.DECODE_RUNNERS_KEPT``."""
+    """The engine's runner for steps of ``batch`` rows and this way of sampling, made at its first
+    use; the least recently used ones go when there are more than ``Engine.DECODE_RUNNERS_KEPT``."""
     width = -(-max(int(pages), 1) // PAGE_TABLE_STEP) * PAGE_TABLE_STEP
     key = (batch, width, params)
     runners = engine.decode_runners
@@ -169,6 +190,7 @@ class DecodeSession:
         ``DecodeRunner.EAGER_STEPS``; at least one, which sizes every scratch buffer)."""
         self.engine, self.seqs, self.sampler, self.params = engine, list(seqs), sampler, params
         B = len(self.seqs)
+        self.rows = list(range(B))          # the row of each sequence: they stay where they are when others end
         if B == 0:
             raise StepError("a decode session needs at least one sequence")
         if sampler.seq_state is not engine.cache.seq_state:
@@ -176,28 +198,41 @@ class DecodeSession:
         # sampling runs inside the step (and its graph): it needs no host data, the recent ids
         # that a repeat penalty looks at are in the sequences' records on the device
         self._sample_in_graph = True
-        self.runner = decode_runner(engine, B, max(len(s.pages) for s in self.seqs), params)
+        self.runner = decode_runner(engine, padded_rows(B), max(len(s.pages) for s in self.seqs), params)
         self.runner.bind(self)
         self.use_graph = use_graph and engine.model.graph_safe
         self.eager_steps = max(1, DecodeRunner.EAGER_STEPS if eager_steps is None else int(eager_steps))
         # a step launched ahead can be taken back only if all it stored is stored by position
         self._may_run_ahead = self._sample_in_graph and all(
             isinstance(g["need"], KVNeed) for g in engine.cache.groups.values())
-        self._ahead: Optional[list] = None      # tokens fed to the step launched ahead, if any
+        self._ahead: Optional[list] = None      # tokens, row by row, fed to the step launched ahead, if any
         self._since_check = 0
+
+    def retire(self, seq: CacheSequence) -> bool:
+        """A sequence of the batch has ended.  Its row goes on as one more row of padding (spare
+        page, spare slot) and the others stay in their rows, so the shape, its graph and a step
+        launched ahead (whose other rows are what they would have been) all live on.  False: the
+        batch is better rebuilt without the sequence, because fewer rows will do, and the session
+        must not be used further."""
+        k = next((k for k, s in enumerate(self.seqs) if s is seq), None)
+        if k is None:
+            return True
+        if padded_rows(len(self.seqs) - 1) < self.runner.batch or not self.runner.owned_by(self):
+            return False
+        del self.seqs[k], self.rows[k]
+        self.runner.bind(self, keep_tokens=True)
+        return True
 
     @property
     def batch(self) -> int:
         return len(self.seqs)
 
     @property
-    def tok_ids(self) -> torch.Tensor:
-        return self.runner.tok_ids
-
-    @property
     def logits(self) -> torch.Tensor:
         """The last step's logits, float32 [batch, vocab] (scratch: valid until the next step)."""
-        return self.runner.logits
+        if self.rows == list(range(self.batch)):
+            return self.runner.logits[:self.batch]
+        return self.runner.logits[self.rows]
 
     @property
     def launches_per_step(self) -> int:
@@ -214,7 +249,9 @@ class DecodeSession:
         self._own_runner()
         runner = self.runner
         runner.tokens_uploaded.synchronize()       # the staging buffer's last copy is over
-        runner.pinned_in.numpy()[:] = tokens
+        staged = runner.pinned_in.numpy()
+        staged[:] = 0
+        staged[self.rows] = tokens
         runner.tok_ids.copy_(runner.pinned_in, non_blocking=True)
         runner.tokens_uploaded.record()
 
@@ -226,17 +263,21 @@ class DecodeSession:
             raise StepError("a sequence of the decode session has no reserved page left")
         self._own_runner()
         runner = self.runner
-        runner.ctx.past_lens = [s.length for s in self.seqs]
+        past = [0] * runner.batch
+        for r, s in zip(self.rows, self.seqs):
+            past[r] = s.length
+        runner.ctx.past_lens = past
         runner.run(self.use_graph, self.eager_steps)
         if not self._sample_in_graph:
             self.sampler.sample(runner.logits, self.params, runner.slots, runner.tok_ids)
-            kernels.advance_positions(runner.tok_pos, self.batch)
+            kernels.advance_positions(runner.tok_pos, runner.batch)
         for s in self.seqs:
             s.length += 1
 
     def read_tokens(self) -> list:
         """The tokens sampled by the last step (device to host)."""
-        return self._collect(self._send_back())
+        by_row = self._collect(self._send_back())
+        return [by_row[r] for r in self.rows]
 
     def _send_back(self) -> int:
         """Starts the copy of the last step's tokens to the host; returns its turn."""
@@ -248,6 +289,7 @@ class DecodeSession:
         return turn
 
     def _collect(self, turn: int) -> list:
+        """The tokens of that copy, row by row."""
         self.runner.out_ready[turn].synchronize()
         self._since_check += 1
         if self._since_check >= self.CHECK_EVERY:
@@ -270,7 +312,7 @@ class DecodeSession:
         """Feeds one token per sequence and returns the sampled next tokens, through pinned
         host memory both ways.  Steps that sample on the device are launched one ahead."""
         tokens = [int(t) for t in tokens]
-        if self._ahead is not None and tokens == self._ahead:
+        if self._ahead is not None and tokens == [self._ahead[r] for r in self.rows]:
             turn = self._ahead_turn                  # the step launched ahead is this one
         else:
             self.take_back()
@@ -282,10 +324,10 @@ class DecodeSession:
         if self._may_run_ahead and self._room_for_one_more():
             self.run()                               # the next step, fed by the tokens being sampled now;
             ahead_turn = self._send_back()           # queued before this step's tokens are waited for
-        out = self._collect(turn)
+        by_row = self._collect(turn)
         if ahead_turn is not None:
-            self._ahead, self._ahead_turn = out, ahead_turn
-        return out
+            self._ahead, self._ahead_turn = by_row, ahead_turn
+        return [by_row[r] for r in self.rows]
 
     def take_back(self) -> None:
         """Undoes a step launched ahead that nobody asked for."""
@@ -293,7 +335,7 @@ class DecodeSession:
             return
         self._ahead = None
         self._own_runner()
-        kernels.rewind_step(self.runner.tok_pos, self.batch, self.sampler.seq_state, self.runner.slots,
+        kernels.rewind_step(self.runner.tok_pos, self.runner.batch, self.sampler.seq_state, self.runner.slots,
                             self.params.temperature > 0.0, self.params.filtered)
         for s in self.seqs:
             s.length -= 1

@@ -166,14 +166,12 @@ def linear_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate:
 
 
 def _pick_product(a: torch.Tensor, w: torch.Tensor):
-    """Which kernel multiplies: the weight-streaming mma.sync one up to 16 rows (against big
-    weights up to 8 rows, and not against the largest of them: see ``_wstream_case``) and for
-    narrow outputs up to 64 rows; the tcgen05 ones otherwise."""
+    """Which kernel multiplies: the weight-streaming mma.sync one up to 16 rows, and up to 64
+    for narrow outputs, wherever the tcgen05 kernel with K split over a cluster was not measured
+    faster (``_wstream_case``); the tcgen05 ones otherwise."""
     M, N, K = a.shape[0], w.shape[0], a.shape[1]
     small, tc_ = _small_ok(a, w), _tc_ok(a, w)
-    big = N >= 2048 and K >= 2048
-    if small and ((M <= 8 and not (tc_ and _wstream_case(M, N, K))) or (8 < M <= 16 and not big)
-                  or (M <= SMALL_M and not _wstream_case(M, N, K) and N < 2048) or not tc_):
+    if small and (not tc_ or (not _wstream_case(M, N, K) and (M <= 16 or (M <= SMALL_M and N <= 2048)))):
         return "small"
     if tc_:
         return "tc"
@@ -183,42 +181,55 @@ def _pick_product(a: torch.Tensor, w: torch.Tensor):
 def _wstream_case(M: int, N: int, K: int) -> bool:
     """Few rows whose product goes to the kernel with 128 rows of W per CTA and K split over a
     cluster.  Against big weights (N and K of 2,048 and more), measured at the layer sizes of
-    Qwen3-1.7B to 14B: from 9 to 64 rows always (10.7 against 13.4 us by the mma.sync kernel
-    for 4096 x 4096 at 16 rows); up to 8 rows only against the largest matrices or a very long
-    K (5120 x 17408: 31.6 against 43.8 us; 2048 x 6144: 10.7 against 17.0; but 6144 x 4096:
-    13.5 against 12.5, and the mma.sync kernel can take the norm in front along), never
-    against a vocabulary; from 65 rows only narrow outputs up to 96 rows (24576 x 4096 at 65
-    rows: 54.0 against 39.0 us by the persistent kernel; 4096 x 12288: 22.8 against 24.7).
+    Qwen3-1.7B to 14B: from 9 to 64 rows (10.7 against 13.4 us by the mma.sync kernel for
+    4096 x 4096 at 16 rows) unless the matrix is small (4096 x 2048 at 16 rows: 7.2 against 5.5 us;
+    2048 x 2048 at 32 rows: 6.0 against 5.3); up to 8 rows only against the largest matrices or a
+    very long K (5120 x 17408: 31.6 against 43.8 us; 2048 x 6144: 10.7 against 17.0; but
+    6144 x 4096: 13.5 against 12.5, and the mma.sync kernel can take the norm in front along);
+    from 65 rows only narrow outputs up to 96 rows (24576 x 4096 at 65 rows: 54.0 against 39.0 us
+    by the persistent kernel; 4096 x 12288: 22.8 against 24.7).
+    A vocabulary (151,936 rows) at every number of rows up to 64: at K = 2,048 to 5,120 it reads
+    W at 6.2-6.4 TB/s with 1 to 8 rows where the mma.sync kernel reaches 5.5-6.3 (K = 2,048, one row:
+    97.8 against 108.5 us), and at 16 rows and more the other kernels are far behind (K = 4,096,
+    16 rows: 200 against 584 us).  At K = 1,024 from 9 rows (16 rows: 56.2 against 81.8 us; 64 rows:
+    64.4 against 81.2 by 128 x 128 tiles, one per CTA); up to 8 rows the two are within 4 us and the
+    mma.sync kernel takes the final norm along.
     Against the weights of a small model's layers from 17 rows where it was measured faster
     (at 64 rows, 1024 x 3072: 8.5 us against 17.8 by the mma.sync kernel and 18.4 by one
-    128 x 64 tile per CTA), but not against its vocabulary (many tiles with a short K), and not
-    wide outputs with K = 1024 beyond 64 rows (6144 x 1024 at 128 rows: 11.7 us against 8.4
-    by one tile per CTA)."""
+    128 x 64 tile per CTA); wide outputs with K = 1024 up to 48 rows, or 64 with 4,096 outputs
+    (6144 x 1024 at 48 rows: 7.8 against 9.0 us by 128 x 64 tiles, at 64 rows 8.4 against 8.0; at
+    128 rows: 11.7 us against 8.4)."""
     if M > 128:
         return False
     if N >= 2048 and K >= 2048:
         if M <= 8:
-            return N <= 65536 and (N * K >= (24 << 20) or K >= 6144)
+            return N * K >= (24 << 20) or K >= 6144
+        if M <= 16:
+            return N * K > (8 << 20)
+        if M <= 32:
+            return N * K > (4 << 20)
         if M <= 64:
             return True
         return N < 8192 and M <= 96
+    if N > 65536:                      # a vocabulary with a short K
+        return 8 < M <= 64 and K >= 1024
     if M <= 16 or N < 1024 or K < 1024 or N > 16384:
         return False
     if N < 2048:                       # narrow outputs: 1024 x 2048 at 32 rows is 4.9 us by the mma.sync kernel, 6.6 here
         return not (M <= 32 and K <= 2048)
-    return M <= 32 or (M <= 64 and N <= 4096)      # wide outputs with a short K
+    return M <= 48 or (M <= 64 and N <= 4096)      # wide outputs with a short K
 
 
 def _normed_loses(M: int, N: int, K: int) -> bool:
     """Whether the few-row product that takes the norm along is the slower way: 9 to 16 rows
     against big weights (a decode step of 16 sequences at Qwen3-8B sizes: 270 us a layer with it,
     160 with a norm kernel and the tcgen05 product), and up to 8 rows against the largest
-    matrices (34816 x 5120: 62.4 us against 54.6 + 2.1)."""
+    matrices, a vocabulary among them (34816 x 5120: 62.4 us against 54.6 + 2.1)."""
     if N < 2048 or K < 2048:
         return False
     if M > 8:
         return True
-    return N <= 65536 and N * K >= (48 << 20)
+    return N * K >= (48 << 20)
 
 
 def _tc_shape(M: int, N: int, out: torch.Tensor = None, K: int = 0):

@@ -83,8 +83,9 @@ def test_groups_have_storage_of_their_own():
     assert len(cache.groups) == 4
     full, win, st, other = cache.view(0), cache.view(1), cache.view(4), cache.view(5)
     assert cache.view(2) is None
-    assert tuple(full.pages.shape) == (4, 2, 2, 64, 16) and tuple(other.pages.shape) == (4, 2, 1, 64, 32)
-    assert tuple(st.states.shape) == (3, 5, 3)
+    assert tuple(full.pages.shape) == (5, 2, 2, 64, 16) and tuple(other.pages.shape) == (5, 2, 1, 64, 32)   # one spare page
+    assert tuple(st.states.shape) == (4, 5, 3)                    # and one spare slot
+    assert cache.spare_page == 4 and cache.spare_slot == 3
     ptrs = {v.pages.data_ptr() for v in (full, win, cache.view(3), other)}
     assert len(ptrs) == 4                                  # layers 0 and 3 share a group, not storage
     assert full.pages.untyped_storage().data_ptr() == cache.view(3).pages.untyped_storage().data_ptr()

@@ -151,6 +151,33 @@ def test_repeat_penalty_in_a_batch_against_plain(llms, temp, top_k):
     assert [o.tokens for o in one_by_one] == [o.tokens for o in outs]
 
 
+def test_rows_beyond_the_sequences_change_nothing(llms):
+    """Six and eleven sequences decode as steps of eight and sixteen rows (the rows beyond them
+    use the cache's spare page and slot), and keep that shape while sequences end: every
+    request's tokens equal the plain implementation's, with a penalty that reads each row's own
+    recent ids and a random stream per request; nothing stays held in the cache."""
+    from gguf2bin_b200.engine.decode import padded_rows
+    assert [padded_rows(n) for n in (1, 4, 5, 8, 9, 64, 65)] == [1, 4, 8, 8, 16, 64, 72]
+    llm = llms("b", "float32", max_tokens=2048)
+    eng = llm.engine
+    lens = [7, 70, 3, 21, 64, 1, 33, 12, 5, 90, 2]
+    prompts = [random_tokens("b", n, 300 + i) for i, n in enumerate(lens)]
+    kw = dict(temperature=0.8, top_k=5, top_p=0.95, repeat_penalty=1.6, seed=77)
+    want = [plain_generate_filtered("b", "float32", p, 12, 0.8, 5, 0.95, 1.6, 77, i) for i, p in enumerate(prompts)]
+    # stop ids that end some requests early, at different steps
+    stops = {want[1][4], want[4][8], want[9][2]}
+    for n_req in (6, 11):
+        shapes_before = set(eng.decode_runners)
+        outs = llm.generate(prompts[:n_req], n=12, stop_ids=stops, **kw)
+        for i, o in enumerate(outs):
+            cut = next((j for j, t in enumerate(want[i]) if t in stops), 12)
+            assert o.tokens == want[i][:cut], f"{n_req} requests, request {i}"
+        assert any(len(o.tokens) < 12 for o in outs)
+        new_shapes = set(eng.decode_runners) - shapes_before
+        assert all(k[0] in (1, 2, 3, 4, 8, 16) for k in new_shapes) and any(k[0] == padded_rows(n_req) for k in new_shapes)
+        assert eng.cache.table.pages.n_held == 0 and eng.cache.table.slots.n_held == 0
+
+
 def test_context_limit_and_errors(llms):
     from gguf2bin_b200.engine import GenerationError, StepEntry, StepError
     llm = llms("a", "float32")
@@ -213,11 +240,68 @@ def test_step_launched_ahead_is_taken_back(llms):
     backend.close(handles[1])
 
 
+@pytest.mark.parametrize("filtered", [False, True])
+def test_rows_of_sequences_that_end_go_on_as_padding(llms, filtered):
+    """Eight sequences, then seven, six and five, in steps of eight rows.  Sequences end in the middle of the batch while a
+    step is launched ahead; the others keep their rows and that step.  Right after one of them
+    ended the caller feeds other tokens than the sampled ones, so the step launched ahead is
+    taken back from rows of which one has just become padding (not with the repeat penalty,
+    whose recent ids on the device are the sampled ones).  Every token against the plain
+    implementation fed the same tokens, with each request's own random stream and recent ids."""
+    from gguf2bin_b200.engine.backend import EngineBackend
+    from gguf2bin_b200.sampling import SamplingParams
+    llm = llms("b", "float32", max_tokens=2048)
+    eng = llm.engine
+    temp, seed = 0.7, 123
+    params = SamplingParams(temperature=temp, top_k=6, top_p=0.9, repeat_penalty=1.5) if filtered \
+        else SamplingParams.plain(temp)
+    backend = EngineBackend(eng, params, seed, max_context=256)
+    prompts = [random_tokens("b", n, 400 + n) for n in (6, 9, 63, 2, 30, 64, 11, 17)]
+    handles = [backend.open(i, 100) for i in range(8)]
+    cfg, W = plain_model("b", "float32")
+    fed = [list(p) for p in prompts]
+    draws = [0] * 8
+
+    def plain_next(i):
+        logits = P.forward(cfg, W, fed[i], np.float32)[-1]
+        r = philox_plain.uniform(seed, i, draws[i])
+        draws[i] += 1
+        if filtered:
+            return int(P.sample_advanced(logits, temp, 6, 0.9, 1.5, fed[i][-64:], r)[0])
+        return P.sample_temperature(logits, temp, r)[0]
+
+    got = backend.prefill(handles, prompts)
+    assert got == [plain_next(i) for i in range(8)]
+    live = list(range(8))
+    ends = {2: 3, 4: 0, 5: 6}                          # step -> the sequence that ends before it
+    session = None
+    for step in range(9):
+        if step in ends:
+            k = live.index(ends[step])
+            backend.close(handles[ends[step]])
+            live, got = live[:k] + live[k + 1:], got[:k] + got[k + 1:]
+            if step > 2:
+                assert backend._session is session, "the batch was put together anew"
+        if step in (4, 7) and not filtered:            # the caller overrides the sampled tokens (the recent
+            got = [(t + 1 + i) % cfg["vocab_size"] for i, t in enumerate(got)]     # ids on the device are the sampled ones)
+        for i, t in zip(live, got):
+            fed[i].append(t)
+        got = backend.decode([handles[i] for i in live], got)
+        session = backend._session
+        assert session.runner.batch == 8
+        assert got == [plain_next(i) for i in live], f"step {step}"
+    assert session.rows == [1, 2, 4, 5, 7]
+    for i in live:
+        backend.close(handles[i])
+    backend.finish()
+    assert eng.cache.table.pages.n_held == 0 and eng.cache.table.slots.n_held == 0
+
+
 def test_decode_graphs_are_kept_by_shape_not_by_call(llms):
     """A decode graph belongs to the engine and to a shape (sequences, page-table width,
     sampling): a second call with the same shape captures nothing, and a batch of 64 whose
-    sequences end one per step (63 shapes, each seen once or twice) captures no graph at all
-    instead of one per shape.  Tokens are compared with an engine that never uses graphs."""
+    sequences end one per step passes through eight shapes of rows, not 63, and captures a graph
+    for each at most.  Tokens are compared with an engine that never uses graphs."""
     from gguf2bin_b200.engine.backend import EngineBackend
     from gguf2bin_b200.sampling import SamplingParams
     llm = llms("c", "bfloat16", max_tokens=64 * 128)
@@ -250,7 +334,7 @@ def test_decode_graphs_are_kept_by_shape_not_by_call(llms):
     backend.close(handles[live[0]])
     backend.finish()
     captured = eng.decode_graph_captures - before
-    assert captured <= 4, f"{captured} graphs for a shrinking batch"
+    assert captured <= 8, f"{captured} graphs for a shrinking batch"
     assert eng.cache.table.slots.n_held == 0 and eng.cache.table.pages.n_held == 0
 
 
@@ -260,23 +344,24 @@ def test_graphs_that_are_let_go_do_not_spoil_a_capture(llms):
     a graph that is released while another is being captured would end that capture with an
     error.  Tokens equal those of an engine that uses no graphs."""
     import gc
-    llm = llms("c", "bfloat16", max_tokens=16 * 128)
+    llm = llms("c", "bfloat16", max_tokens=32 * 128)
     eng = llm.engine
-    prompts = [random_tokens("c", 3 + (i % 6), 800 + i) for i in range(12)]
+    prompts = [random_tokens("c", 3 + (i % 6), 800 + i) for i in range(28)]
     kw = dict(temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0, ignore_eos=True)
+    sizes = (12, 20, 3, 9, 28, 5, 20)                 # steps of 16, 24, 3, 16, 32, 8 and 24 rows
     kept, eng.DECODE_RUNNERS_KEPT = eng.DECODE_RUNNERS_KEPT, 2
     thresholds = gc.get_threshold()
     before = eng.decode_graph_captures
     try:
         gc.set_threshold(5, 1, 1)
-        with_graphs = [llm.generate(prompts[:b], n=8, max_batch=b, **kw) for b in (12, 7, 3, 9, 12, 5, 7)]
+        with_graphs = [llm.generate(prompts[:b], n=8, max_batch=b, **kw) for b in sizes]
     finally:
         gc.set_threshold(*thresholds)
         eng.DECODE_RUNNERS_KEPT = kept
     assert eng.decode_graph_captures - before >= 6
     llm.use_graph = False
     try:
-        plain = [llm.generate(prompts[:b], n=8, max_batch=b, **kw) for b in (12, 7, 3, 9, 12, 5, 7)]
+        plain = [llm.generate(prompts[:b], n=8, max_batch=b, **kw) for b in sizes]
     finally:
         llm.use_graph = True
     assert [[o.tokens for o in call] for call in with_graphs] == [[o.tokens for o in call] for call in plain]

@@ -85,6 +85,15 @@ def test_it_steps_and_generates(tmp_path, dtype):
             for t in o.tokens:
                 assert t == int(np.argmax(toy_hybrid.plain_forward(cfg, W, seq)[-1]))
                 seq.append(t)
+        # six sequences run as steps of eight rows: the rows beyond them fold their tokens into
+        # the spare slot's state, not into a sequence's
+        more = reqs + [r[:k] for r, k in zip(reqs, (9, 3, 20))]
+        for toks, o in zip(more, llm.generate(more, n=5, temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0,
+                                              ignore_eos=True)):
+            seq = list(toks)
+            for t in o.tokens:
+                assert t == int(np.argmax(toy_hybrid.plain_forward(cfg, W, seq)[-1]))
+                seq.append(t)
 
 
 @pytest.mark.gpu
