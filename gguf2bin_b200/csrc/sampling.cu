@@ -18,9 +18,27 @@
 // without a sort of the vocabulary.
 #include "common.cuh"
 
+#include <climits>
+
 G2B_DEFINE_LAST_ERROR
 
 #define SAMPLE_THREADS 1024
+
+#ifdef G2B_SAMPLE_TIMING
+// Development aid (off unless built with -DG2B_SAMPLE_TIMING): the clock of block (0, 0) at the ends
+// of the phases of the filtered sampler's two kernels; g2b_sample_stamps copies them out.
+__device__ long long g2b_stamps[32];
+#define G2B_STAMP(i)                                                                      \
+  do {                                                                                    \
+    __syncthreads();                                                                      \
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) g2b_stamps[i] = clock64(); \
+  } while (0)
+extern "C" int g2b_sample_stamps(long long *out) {
+  return cudaMemcpyFromSymbol(out, g2b_stamps, sizeof(g2b_stamps)) == cudaSuccess ? 0 : 1;
+}
+#else
+#define G2B_STAMP(i) do { } while (0)
+#endif
 
 // Words of a sequence's record (seq_state[slot]): the sampler's key (seed, stream id), its draw
 // counter, the count of tokens written to the ring of recent ids, and the ring itself.  The
@@ -118,16 +136,31 @@ constexpr int MAX_PIECES = 2048;
 // Every thread of the block calls it; returns the chosen index to all of them.  s_piece:
 // MAX_PIECES floats of shared memory.
 __device__ int pick_by_temperature(const float *__restrict__ row, int V, float temp, float *s_piece,
-                                   int *seq_state, int slot, int state_words) {
+                                   int *seq_state, int slot, int state_words,
+                                   const float2 *__restrict__ pieces = nullptr) {
   __shared__ float s_before, s_target;
   __shared__ int s_owner, s_choice;
-  float mx;
-  block_argmax(row, V, 1.f, &mx);                  // max of the raw logits
-  mx = mx / temp;
+  __shared__ float s_wmax[32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_warps = blockDim.x >> 5;
   const int trips = (V + 128 * MAX_PIECES - 1) / (128 * MAX_PIECES);     // trips of 128 entries per piece
   const int G = 128 * trips, n_pieces = (V + G - 1) / G;
+  float mx;
+  if (pieces) {                                    // max of x / temp over the pieces' maxima
+    float m = -INFINITY;
+    for (int j = threadIdx.x; j < n_pieces; j += blockDim.x) m = fmaxf(m, pieces[j].x);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) s_wmax[warp] = m;
+    __syncthreads();
+    m = lane < n_warps ? s_wmax[lane] : -INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    mx = m;
+  } else {
+    block_argmax(row, V, 1.f, &mx);                // max of the raw logits
+    mx = mx / temp;
+  }
   const bool vec = ((uintptr_t)row & 15) == 0;
   // the four entries of this lane in the trip that starts at entry i0 (0 beyond the row)
   auto four = [&](int i0, float (&e)[4]) {
@@ -141,16 +174,23 @@ __device__ int pick_by_temperature(const float *__restrict__ row, int V, float t
       for (int q = 0; q < 4; ++q) e[q] = i + q < V ? expf(row[i + q] / temp - mx) : 0.f;
     }
   };
-  for (int j = warp; j < n_pieces; j += n_warps) {
-    float part = 0.f;
-    for (int t = 0; t < trips; ++t) {
-      float e[4];
-      four(j * G + 128 * t, e);
-      part += (e[0] + e[1]) + (e[2] + e[3]);
+  if (pieces) {                                    // a piece's sum was taken against its own maximum
+    for (int j = threadIdx.x; j < n_pieces; j += blockDim.x) {
+      const float2 p = pieces[j];
+      s_piece[j] = p.y > 0.f ? p.y * expf(p.x - mx) : 0.f;
     }
+  } else {
+    for (int j = warp; j < n_pieces; j += n_warps) {
+      float part = 0.f;
+      for (int t = 0; t < trips; ++t) {
+        float e[4];
+        four(j * G + 128 * t, e);
+        part += (e[0] + e[1]) + (e[2] + e[3]);
+      }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-    if (lane == 0) s_piece[j] = part;
+      for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+      if (lane == 0) s_piece[j] = part;
+    }
   }
   __syncthreads();
   if (warp == 0) {
@@ -230,27 +270,83 @@ __device__ int pick_by_temperature(const float *__restrict__ row, int V, float t
   return s_choice;
 }
 
+// The pieces' sums by many blocks per row: a warp per piece, which leaves the piece's maximum of
+// x / temp and its sum of e^(x/temp - that maximum) in pieces[row][piece]; the row's block then
+// scales each sum to the row's maximum instead of reading the row (twice) itself: 38 us by one
+// block for 150k entries.
+constexpr int PIECE_BLOCKS = 64, PIECE_THREADS = 256;
+
+__global__ void __launch_bounds__(PIECE_THREADS)
+temperature_pieces_kernel(const float *__restrict__ logits, int V, int ld, float temp, float2 *__restrict__ pieces) {
+  pdl_launch();
+  pdl_wait();
+  const float *row = logits + (size_t)blockIdx.y * ld;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int trips = (V + 128 * MAX_PIECES - 1) / (128 * MAX_PIECES);
+  const int G = 128 * trips, n_pieces = (V + G - 1) / G;
+  const bool vec = ((uintptr_t)row & 15) == 0;
+  float2 *out = pieces + (size_t)blockIdx.y * MAX_PIECES;
+  for (int j = blockIdx.x * (PIECE_THREADS / 32) + warp; j < n_pieces; j += PIECE_BLOCKS * (PIECE_THREADS / 32)) {
+    float m = -INFINITY, sum = 0.f;                // running maximum and sum against it, trip by trip
+    for (int t = 0; t < trips; ++t) {
+      const int i = j * G + 128 * t + 4 * lane;
+      float x[4];
+      if (vec && i + 3 < V) {
+        const float4 v = *reinterpret_cast<const float4 *>(row + i);
+        x[0] = v.x / temp; x[1] = v.y / temp; x[2] = v.z / temp; x[3] = v.w / temp;
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) x[q] = i + q < V ? row[i + q] / temp : -INFINITY;
+      }
+      float tm = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, o));
+      if (tm == -INFINITY) continue;               // nothing of the row in this trip
+      const float m_new = fmaxf(m, tm);
+      float part = 0.f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) part += x[q] == -INFINITY ? 0.f : expf(x[q] - m_new);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+      sum = (m == -INFINITY ? 0.f : sum * expf(m - m_new)) + part;
+      m = m_new;
+    }
+    if (lane == 0) out[j] = make_float2(m, sum);
+  }
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float *__restrict__ logits, int V, int ld, float temp, int *seq_state,
-                   int state_words, const int *__restrict__ slots, int *__restrict__ out_ids) {
+                   int state_words, const int *__restrict__ slots, int *__restrict__ out_ids,
+                   const float2 *__restrict__ pieces) {
   pdl_launch();
   pdl_wait();
   __shared__ float s_piece[MAX_PIECES];
   const float *row = logits + (size_t)blockIdx.x * ld;
   const int id = temp <= 0.f ? block_argmax(row, V, 1.f, nullptr)
-                             : pick_by_temperature(row, V, temp, s_piece, seq_state, slots[blockIdx.x], state_words);
+                             : pick_by_temperature(row, V, temp, s_piece, seq_state, slots[blockIdx.x], state_words,
+                                                   pieces ? pieces + (size_t)blockIdx.x * MAX_PIECES : nullptr);
   if (threadIdx.x == 0) out_ids[blockIdx.x] = id;
 }
 
+// pieces: scratch of R x 2,048 x 2 floats, or null; with it, the pieces' sums of a large
+// vocabulary are taken by many blocks per row first (temperature_pieces_kernel).
 extern "C" int g2b_sample_rows(const float *logits, int R, int V, int ld, float temp,
                                int *seq_state, int state_words, const int *slots, int *out_ids,
-                               cudaStream_t stream) {
+                               float *pieces, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V <= 0 || ld < V) G2B_REFUSE("sample_rows: bad sizes V=%d ld=%d", V, ld);
   if (temp > 0.f && (!seq_state || !slots || state_words < 4))
     G2B_REFUSE("sample_rows: temperature sampling needs the per-slot state");
+  const bool split = pieces && temp > 0.f && V >= 8192 && R <= 65535 && (((uintptr_t)pieces) & 7) == 0;
+  if (split) {
+    g2b_launch(temperature_pieces_kernel, dim3(PIECE_BLOCKS, R), dim3(PIECE_THREADS), 0, stream, logits, V, ld,
+               temp, (float2 *)pieces);
+    int rc = g2b_check_launch("sample_rows (pieces)");
+    if (rc) return rc;
+  }
   g2b_launch(sample_rows_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, logits, V, ld, temp, seq_state,
-                                                       state_words, slots, out_ids);
+             state_words, slots, out_ids, (const float2 *)(split ? pieces : nullptr));
   return g2b_check_launch("sample_rows");
 }
 
@@ -483,7 +579,8 @@ struct ShortList {
 __device__ __forceinline__ void walk_bins(const int *hist, int above0, int want, int *chosen_out, int *above_out) {
   const int lane = threadIdx.x & 31, hi = 2047 - 64 * lane;
   int mine = 0;
-  for (int d = hi; d > hi - 64; --d) mine += hist[d];
+  // (the lanes' ranges lie 64 words apart, all in one bank: each lane starts at another place of its range)
+  for (int d = 0; d < 64; ++d) mine += hist[hi - ((d + lane) & 63)];
   int incl = mine;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -493,11 +590,13 @@ __device__ __forceinline__ void walk_bins(const int *hist, int above0, int want,
   const unsigned hit = __ballot_sync(0xffffffffu, above0 + incl >= want);
   const int owner = hit ? __ffs(hit) - 1 : 31;
   int run = above0 + incl - mine, chosen = hi - 63;
-  for (int d = hi; d > hi - 64; --d) {
-    if (run + hist[d] >= want) { chosen = d; break; }
-    run += hist[d];
+  if (lane == owner) {
+    for (int d = hi; d > hi - 64; --d) {
+      if (run + hist[d] >= want) { chosen = d; break; }
+      run += hist[d];
+    }
+    if (!hit) run -= hist[chosen];
   }
-  if (!hit) run -= hist[chosen];
   *chosen_out = __shfl_sync(0xffffffffu, chosen, owner);
   *above_out = __shfl_sync(0xffffffffu, run, owner);
 }
@@ -526,6 +625,31 @@ __device__ void sort_list(ShortList &L, int n) {
       __syncthreads();
     }
   }
+}
+
+// Sorts a list of up to RANK_SORT_MAX entries by counting, for every entry, the entries that belong
+// before it: no barriers but two, where the bitonic network has one per step (21 steps for 64
+// entries cost 2.8 us).  The sorted list passes through the list's other two arrays.
+constexpr int RANK_SORT_MAX = 256;
+__device__ void rank_sort(ShortList &L, int n) {
+  uint32_t *tkey = reinterpret_cast<uint32_t *>(L.e);
+  int *tidx = L.hist;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const uint32_t k = L.key[i];
+    const int id = L.idx[i];
+    int before = 0;
+#pragma unroll 4
+    for (int j = 0; j < n; ++j) {
+      const uint32_t kj = L.key[j];
+      before += (kj > k || (kj == k && L.idx[j] < id)) ? 1 : 0;
+    }
+    tkey[before] = k;
+    tidx[before] = id;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) { L.key[i] = tkey[i]; L.idx[i] = tidx[i]; }
+  __syncthreads();
 }
 
 // Every entry whose key has at least the 22-bit prefix `floor22` into the list; returns their
@@ -591,13 +715,17 @@ __device__ int list_by_sampled_floor(const float *row, int V, float inv_temp, in
   const uint32_t floor22 = s_prefix >> 10;
   const int n = list_from_floor(row, V, inv_temp, floor22, L);
   if (n < want || n > LIST_CAP) return -1;
-  sort_list(L, n);
+  if (n <= RANK_SORT_MAX) rank_sort(L, n);
+  else sort_list(L, n);
   return n;
 }
 
-// The same by counting: two passes over the row (11 bits of the key each) find the 22-bit prefix
-// of the want-th largest key exactly, a third lists the entries at or above it.  -1 when more
-// than the list holds share that prefix.
+// The same by counting: a pass over the row counts the keys by their upper 11 bits and finds the
+// bin in which the want-th largest lies; if that bin and those above hold few entries they are the
+// list, otherwise a second pass over the next 11 bits narrows the bin down.  (The counts are plain
+// shared-memory additions: gathering a warp's equal bins first with match.any cost 1,300 cycles per
+// entry where the bins differ.)  The last pass lists the entries at or above the floor.  -1 when
+// more than the list holds share the 22-bit prefix.
 __device__ int list_top_k(const float *row, int V, float inv_temp, int top_k, ShortList &L) {
   __shared__ uint32_t s_prefix;
   __shared__ int s_above, s_total;
@@ -612,10 +740,7 @@ __device__ int list_top_k(const float *row, int V, float inv_temp, int top_k, Sh
     scan_row(row, V, [&](int, float x) {
       const uint32_t k = order_key(x * inv_temp);
       if (pass == 1 && (k >> 21) != (prefix >> 21)) return;
-      // most logits share a few bins: the lanes of a warp that hit the same bin add once
-      const int bin = (int)((k >> shift) & 0x7ffu);
-      const unsigned peers = __match_any_sync(__activemask(), bin);
-      if ((int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&L.hist[bin], __popc(peers));
+      atomicAdd(&L.hist[(k >> shift) & 0x7ffu], 1);
     });
     __syncthreads();
     if (threadIdx.x < 32) {
@@ -624,16 +749,156 @@ __device__ int list_top_k(const float *row, int V, float inv_temp, int top_k, Sh
       if (threadIdx.x == 0) {
         s_above = above;
         s_prefix = prefix | ((uint32_t)chosen << shift);
-        if (pass == 1) s_total = above + L.hist[chosen];    // entries at or above the 22-bit prefix
+        s_total = above + L.hist[chosen];           // entries at or above the prefix so far
       }
     }
     __syncthreads();
+    if (pass == 0 && s_total <= RANK_SORT_MAX) break;       // few enough: the bin's lower edge is the floor
   }
   const int total = s_total;
+  G2B_STAMP(2);
   if (total > LIST_CAP || total < top_k) return -1;
   const int n = list_from_floor(row, V, inv_temp, s_prefix >> 10, L);
+  G2B_STAMP(3);
   if (n > LIST_CAP) return -1;
-  sort_list(L, n);
+  if (n <= RANK_SORT_MAX) rank_sort(L, n);
+  else sort_list(L, n);
+  G2B_STAMP(4);
+  return n;
+}
+
+// Repeat penalty, each distinct id once (src/main.c:204-223), on the entries [begin, end) of the
+// row: over the n ids the caller gives, or (ids == nullptr) over the last RECENT_WINDOW ids in the
+// sequence's own ring `rec`.  Every thread of the block calls it.
+__device__ void apply_penalty(float *row, int V, int begin, int end, float penalty, const int *ids, int n_ids,
+                              const int *rec) {
+  if (penalty == 1.f || (!ids && !rec)) return;
+  const bool ring = ids == nullptr;
+  const int *rc = ring ? rec + SS_RING : ids;
+  const int total = ring ? max(rec[SS_RECENT_TOTAL], 0) : 0;
+  const int n = ring ? min(total, RECENT_WINDOW) : n_ids;
+  // entry i of the window (any order will do: every distinct id counts once)
+  auto entry = [&](int i) { return ring ? rc[(total - 1 - i) % SS_RING_WORDS] : rc[i]; };
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int id = entry(i);
+    if (id < begin || id >= end || id >= V) continue;
+    bool first = true;
+    for (int j = 0; j < i; ++j) if (entry(j) == id) { first = false; break; }
+    if (!first) continue;
+    const float v = row[id];
+    row[id] = v > 0.f ? v / penalty : v * penalty;
+  }
+}
+
+// ---- the best top_k of a row by many blocks ------------------------------------------------
+// A row is one block's work above, and a block pulls a vocabulary of 150k entries through one SM
+// at a few dozen GB/s: 50 us for the reference's default parameters.  With a top_k of up to
+// LOCAL_CAP the row is cut into FILTER_SPLITS slices first; a block per slice applies the repeat
+// penalty to its entries and lists its own best top_k (sorted; every entry of the row's best
+// top_k is among some slice's).  The row's block then sorts the slices' lists together instead
+// of reading the row.  cand: int [rows x FILTER_SPLITS x (1 + 2 LOCAL_CAP)]: per slice the
+// number listed (-1: the slice's list did not fit, the row's block reads the row itself), the
+// keys, the indices.
+constexpr int FILTER_SPLITS = 32, LOCAL_CAP = 64, FILTER_THREADS = 256;
+constexpr int CAND_WORDS = 1 + 2 * LOCAL_CAP;
+
+__global__ void __launch_bounds__(FILTER_THREADS)
+filter_slices_kernel(float *__restrict__ logits, int V, int ld, float temp, int top_k, float penalty,
+                     const int *__restrict__ recent, int recent_ld, const int *__restrict__ recent_n,
+                     const int *seq_state, int state_words, const int *__restrict__ slots, int *__restrict__ cand) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ ShortList L;
+  const int r = blockIdx.y;
+  float *row = logits + (size_t)r * ld;
+  // gridDim.x slices (32 with few rows, fewer with many: enough blocks to fill the GPU once); the
+  // places of the others are marked empty
+  const int per = ((V + (int)gridDim.x - 1) / (int)gridDim.x + 3) & ~3;     // slices start at multiples of 16 bytes
+  const int begin = min(V, (int)blockIdx.x * per), end = min(V, begin + per);
+  if (blockIdx.x == 0)
+    for (int sl = gridDim.x + threadIdx.x; sl < FILTER_SPLITS; sl += blockDim.x)
+      cand[((size_t)r * FILTER_SPLITS + sl) * CAND_WORDS] = 0;
+  const int *rec = (seq_state && slots && state_words >= SS_RING + SS_RING_WORDS)
+                       ? seq_state + (size_t)slots[r] * state_words : nullptr;
+  G2B_STAMP(0);
+  apply_penalty(row, V, begin, end, penalty, recent ? recent + (size_t)r * recent_ld : nullptr,
+                recent ? min(max(recent_n[r], 0), recent_ld) : 0, rec);
+  __syncthreads();
+  G2B_STAMP(1);
+  int *out = cand + ((size_t)r * FILTER_SPLITS + blockIdx.x) * CAND_WORDS;
+  const int want = min(top_k, end - begin);
+  int n = 0;
+  if (want > 0) n = list_top_k(row + begin, end - begin, 1.f / temp, want, L);
+  const int m = n < 0 ? -1 : min(n, want);
+  for (int j = threadIdx.x; j < m; j += blockDim.x) {
+    out[1 + j] = (int)L.key[j];
+    out[1 + LOCAL_CAP + j] = begin + L.idx[j];
+  }
+  if (threadIdx.x == 0) out[0] = m;
+  G2B_STAMP(5);
+}
+
+// How many entries of the sorted list (zk, zi)[0, n) belong before the entry (k, id).
+__device__ __forceinline__ int count_before(const uint32_t *zk, const int *zi, int n, uint32_t k, int id) {
+  int lo = 0, hi = n;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    const uint32_t mk = zk[mid];
+    if (mk > k || (mk == k && zi[mid] < id)) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+// The best `want` entries of a row from its slices' sorted lists: the lists are merged in pairs,
+// five times, each result cut to `want`; an entry's place in a merged list is its place in its own
+// list plus the number of entries of the other list that belong before it (a binary search), so a
+// level is one step for all entries at once.  -1 when a slice gave no list.
+__device__ int list_from_slices(const int *__restrict__ cand, int want, ShortList &L) {
+  static_assert(FILTER_SPLITS == 32 && FILTER_SPLITS * LOCAL_CAP <= LIST_CAP, "the lists side by side, LOCAL_CAP apart");
+  __shared__ int s_len[2][FILTER_SPLITS];
+  uint32_t *key[2] = {L.key, reinterpret_cast<uint32_t *>(L.e)};
+  int *idx[2] = {L.idx, L.hist};
+  __syncthreads();
+  if (threadIdx.x < FILTER_SPLITS) s_len[0][threadIdx.x] = cand[(size_t)threadIdx.x * CAND_WORDS];
+  __syncthreads();
+  const int my_len = s_len[0][threadIdx.x & 31];      // every warp looks at all 32 lengths
+  if (__any_sync(0xffffffffu, my_len < 0 || my_len > LOCAL_CAP)) return -1;
+  for (int t = threadIdx.x; t < FILTER_SPLITS * LOCAL_CAP; t += blockDim.x) {
+    const int sl = t / LOCAL_CAP, j = t % LOCAL_CAP;
+    if (j < s_len[0][sl]) {
+      const int *src = cand + (size_t)sl * CAND_WORDS;
+      L.key[t] = (uint32_t)src[1 + j];
+      L.idx[t] = src[1 + LOCAL_CAP + j];
+    }
+  }
+  __syncthreads();
+  int from = 0;
+  for (int lists = FILTER_SPLITS; lists > 1; lists >>= 1, from ^= 1) {
+    const uint32_t *ik = key[from];
+    const int *ii = idx[from];
+    uint32_t *ok = key[from ^ 1];
+    int *oi = idx[from ^ 1];
+    for (int t = threadIdx.x; t < lists * LOCAL_CAP; t += blockDim.x) {
+      const int mine = t / LOCAL_CAP, j = t % LOCAL_CAP, other = mine ^ 1;
+      if (j < s_len[from][mine]) {
+        const uint32_t k = ik[mine * LOCAL_CAP + j];
+        const int id = ii[mine * LOCAL_CAP + j];
+        const int place = j + count_before(ik + other * LOCAL_CAP, ii + other * LOCAL_CAP, s_len[from][other], k, id);
+        if (place < want) {
+          ok[(mine >> 1) * LOCAL_CAP + place] = k;
+          oi[(mine >> 1) * LOCAL_CAP + place] = id;
+        }
+      }
+    }
+    if (threadIdx.x < lists / 2)
+      s_len[from ^ 1][threadIdx.x] = min(want, s_len[from][2 * threadIdx.x] + s_len[from][2 * threadIdx.x + 1]);
+    __syncthreads();
+  }
+  const int n = s_len[from][0];
+  if (from == 1) {                                   // (five levels: the result is in the second pair of arrays)
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { L.key[i] = key[1][i]; L.idx[i] = idx[1][i]; }
+    __syncthreads();
+  }
   return n;
 }
 
@@ -641,9 +906,12 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, int top_k,
                        float top_p, float penalty, const int *__restrict__ recent, int recent_ld,
                        const int *__restrict__ recent_n, int *seq_state, int state_words,
-                       const int *__restrict__ slots, int *__restrict__ out_ids, int append) {
+                       const int *__restrict__ slots, int *__restrict__ out_ids, int append,
+                       const int *__restrict__ cand_all) {
   pdl_launch();
   pdl_wait();
+  const int *cand = cand_all ? cand_all + (size_t)blockIdx.x * FILTER_SPLITS * CAND_WORDS : nullptr;
+  G2B_STAMP(8);
   __shared__ float scratch[32];
   __shared__ float s_r;
   __shared__ int s_done;
@@ -652,26 +920,12 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
   int *tie_list = L.idx;
   float *row = logits + (size_t)blockIdx.x * ld;
 
-  // repeat penalty, each distinct id once (src/main.c:204-223): over the ids the caller gives,
-  // or (recent == nullptr) over the last RECENT_WINDOW ids in the sequence's own ring
   int *rec = (seq_state && slots && state_words >= SS_RING + SS_RING_WORDS)
                  ? seq_state + (size_t)slots[blockIdx.x] * state_words : nullptr;
   const bool ring = recent == nullptr && rec != nullptr;
-  if (penalty != 1.f && (recent || ring)) {
-    const int *rc = recent ? recent + (size_t)blockIdx.x * recent_ld : rec + SS_RING;
-    const int total = ring ? max(rec[SS_RECENT_TOTAL], 0) : 0;
-    const int n = ring ? min(total, RECENT_WINDOW) : min(max(recent_n[blockIdx.x], 0), recent_ld);   // never past the row
-    // entry i of the window (any order will do: every distinct id counts once)
-    auto entry = [&](int i) { return ring ? rc[(total - 1 - i) % SS_RING_WORDS] : rc[i]; };
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-      const int id = entry(i);
-      if (id < 0 || id >= V) continue;
-      bool first = true;
-      for (int j = 0; j < i; ++j) if (entry(j) == id) { first = false; break; }
-      if (!first) continue;
-      const float v = row[id];
-      row[id] = v > 0.f ? v / penalty : v * penalty;
-    }
+  if (!cand) {                                      // (with candidates, the kernel that listed them has done it)
+    apply_penalty(row, V, 0, V, penalty, recent ? recent + (size_t)blockIdx.x * recent_ld : nullptr,
+                  recent ? min(max(recent_n[blockIdx.x], 0), recent_ld) : 0, rec);
     __syncthreads();
   }
   // the chosen id goes into the ring (a caller that keeps the recent ids itself passes them in)
@@ -697,7 +951,8 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
   // which the shortest head that reaches top_p of the WHOLE row's mass usually lies.
   const int want = cut_k ? top_k : min(V, 512);
   if (want <= LIST_CAP && (cut_k || top_p < 1.f)) {
-    int n = list_by_sampled_floor(row, V, inv_temp, want, L);
+    int n = cand ? list_from_slices(cand, want, L) : list_by_sampled_floor(row, V, inv_temp, want, L);
+    G2B_STAMP(9);
     if (n < 0 && cut_k) n = list_top_k(row, V, inv_temp, top_k, L);
     if (n >= 0) {
       const int n_list = cut_k ? min(n, top_k) : n;
@@ -706,7 +961,49 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
       if (!cut_k) whole = admitted_mass(row, V, inv_temp, mx, 0u, V, false, scratch);
       for (int j = threadIdx.x; j < n_list; j += blockDim.x) L.e[j] = expf(row[L.idx[j]] * inv_temp - mx);
       __syncthreads();
-      if (threadIdx.x == 0) {
+      G2B_STAMP(10);
+      if (cut_k && n_list >= 1 && n_list <= 64) {
+        // a short list: the cumulative sums by one warp, two entries a lane (the cuts and the draw are
+        // then three ballots, where one thread walking the list took 3 us)
+        if (threadIdx.x < 32) {
+          const int lane = threadIdx.x;
+          const float e0 = 2 * lane < n_list ? L.e[2 * lane] : 0.f;
+          const float e1 = 2 * lane + 1 < n_list ? L.e[2 * lane + 1] : 0.f;
+          float u = 0.f;
+          if (lane == 0) u = next_uniform(seq_state, slots[blockIdx.x], state_words);
+          u = __shfl_sync(0xffffffffu, u, 0);
+          const float pair = e0 + e1;
+          float incl = pair;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const float up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+          }
+          const float c0 = incl - pair + e0, c1 = c0 + e1;      // cumulative sums at 2 lane, 2 lane + 1
+          // first list place whose cumulative sum reaches `target`, among the first n (n if there is none)
+          auto first_reaching = [&](float target, int n) {
+            const unsigned h0 = __ballot_sync(0xffffffffu, 2 * lane < n && c0 >= target);
+            const unsigned h1 = __ballot_sync(0xffffffffu, 2 * lane + 1 < n && c1 >= target);
+            const int j0 = h0 ? 2 * (__ffs(h0) - 1) : n, j1 = h1 ? 2 * (__ffs(h1) - 1) + 1 : n;
+            return min(j0, j1);
+          };
+          auto cumulative_at = [&](int j) {
+            return __shfl_sync(0xffffffffu, (j & 1) ? c1 : c0, j >> 1);
+          };
+          int n_keep = n_list;
+          if (top_p < 1.f) {
+            // shortest head (descending) whose cumulative probability reaches top_p
+            const int j = first_reaching(top_p * cumulative_at(n_list - 1), n_list);
+            if (j < n_list) n_keep = j + 1;
+          }
+          const float kept = cumulative_at(n_keep - 1);
+          const int j = first_reaching(u * kept, n_keep);
+          if (lane == 0) {
+            keep(L.idx[j < n_keep ? j : n_keep - 1]);
+            s_done = 1;
+          }
+        }
+      } else if (threadIdx.x == 0) {
         int n_keep = n_list;
         bool done = true;
         float kept = 0.f;
@@ -737,6 +1034,7 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
         }
       }
       __syncthreads();
+      G2B_STAMP(11);
       if (s_done) return;
     }
     __syncthreads();
@@ -776,11 +1074,28 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
 
 // recent: [R, recent_ld] ids, recent_n[R] how many are valid; or recent == nullptr: the last
 // ids of every row's sequence are in its record (seq_state[slots[row]]), and with `append` the
-// chosen id is added to them.  logits are modified in place by the penalty.
+// chosen id is added to them.  logits are modified in place by the penalty.  cand: scratch of
+// g2b_sample_filtered_scratch_words(R) ints, or null; with it, a small top_k over a large
+// vocabulary is listed by many blocks per row first (filter_slices_kernel).
+static int g2b_sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+extern "C" int g2b_sample_filtered_scratch_words(int R) {
+  return (int)min((long long)R * FILTER_SPLITS * CAND_WORDS, (long long)INT_MAX);
+}
+
 extern "C" int g2b_sample_filtered(float *logits, int R, int V, int ld, float temp, int top_k,
                                    float top_p, float penalty, const int *recent, int recent_ld,
                                    const int *recent_n, int *seq_state, int state_words,
-                                   const int *slots, int *out_ids, int append, cudaStream_t stream) {
+                                   const int *slots, int *out_ids, int append, int *cand,
+                                   cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V <= 0 || ld < V) G2B_REFUSE("sample_filtered: bad sizes V=%d ld=%d", V, ld);
   if (!(top_p > 0.f)) G2B_REFUSE("sample_filtered: top_p must be in (0, 1], got %g", top_p);
@@ -789,9 +1104,21 @@ extern "C" int g2b_sample_filtered(float *logits, int R, int V, int ld, float te
     G2B_REFUSE("sample_filtered: temperature sampling needs the per-slot state");
   if (!recent && penalty != 1.f && (!seq_state || !slots || state_words < SS_RING + SS_RING_WORDS))
     G2B_REFUSE("sample_filtered: a repeat penalty without the recent ids needs the per-slot records with their rings");
-  g2b_launch(sample_filtered_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, 
+  // slices per row: 32 while that is at most about one round of blocks (three of them fit an SM), else 16, 8, 4
+  int n_slices = FILTER_SPLITS;
+  while (n_slices > 4 && (long long)n_slices * R > 3LL * g2b_sm_count()) n_slices >>= 1;
+  const bool slices = cand && temp > 0.f && top_k > 0 && top_k <= LOCAL_CAP && V >= 8192 &&
+                      (long long)n_slices * R <= 3LL * g2b_sm_count();
+  if (slices) {
+    g2b_launch(filter_slices_kernel, dim3(n_slices, R), dim3(FILTER_THREADS), 0, stream,
+        logits, V, ld, temp, top_k, penalty, recent, recent_ld, recent_n, (const int *)seq_state, state_words,
+        slots, cand);
+    int rc = g2b_check_launch("sample_filtered (slices)");
+    if (rc) return rc;
+  }
+  g2b_launch(sample_filtered_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream,
       logits, V, ld, temp, top_k, top_p, penalty, recent, recent_ld, recent_n, seq_state,
-      state_words, slots, out_ids, append);
+      state_words, slots, out_ids, append, (const int *)(slices ? cand : nullptr));
   return g2b_check_launch("sample_filtered");
 }
 

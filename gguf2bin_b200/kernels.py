@@ -86,6 +86,18 @@ def _fn(unit: str, name: str, argtypes, defines=()):
 
 _launches = 0
 _scratch: dict = {}       # small persistent device buffers of the bindings, by (device, use)
+_scratch_outgrown: list = []     # buffers that were replaced by larger ones: a captured graph may still use them
+
+
+def _scratch_buffer(key, n: int, dtype) -> torch.Tensor:
+    """The persistent buffer of that use with at least ``n`` elements.  A buffer that is
+    outgrown is kept, not freed: launches captured in a CUDA graph go on writing to it."""
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < n or buf.dtype != dtype:
+        if buf is not None:
+            _scratch_outgrown.append(buf)
+        buf = _scratch[key] = torch.empty(n, dtype=dtype, device=key[0])
+    return buf
 
 
 def launch_count() -> int:
@@ -335,13 +347,9 @@ def sample_rows(logits, temperature, seq_state, slots, out_ids) -> None:
     R, V = logits.shape
     if temperature <= 0.0 and V >= 4096:
         # greedy over a large vocabulary: many blocks per row, then one
-        key = (logits.device, "argmax")
-        scratch = _scratch.get(key)
-        if scratch is None or scratch[0].shape[0] < R * 64:
-            n = max(R, 64) * 64
-            scratch = (torch.empty(n, dtype=torch.float32, device=logits.device),
-                       torch.empty(n, dtype=torch.int32, device=logits.device))
-            _scratch[key] = scratch
+        n = max(R, 64) * 64
+        scratch = (_scratch_buffer((logits.device, "argmax values"), n, torch.float32),
+                   _scratch_buffer((logits.device, "argmax indices"), n, torch.int32))
         f = _fn("sampling.cu", "g2b_argmax_rows",
                 [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
         _call(f, _ptr(logits), R, V, logits.stride(0), _ptr(scratch[0]), _ptr(scratch[1]),
@@ -349,9 +357,15 @@ def sample_rows(logits, temperature, seq_state, slots, out_ids) -> None:
         count_launches(1)                          # the slices, then the winner among them
         return
     f = _fn("sampling.cu", "g2b_sample_rows",
-            [c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
+            [c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    pieces = None
+    if temperature > 0.0 and V >= 8192:
+        # a large vocabulary: many blocks per row sum its pieces first
+        pieces = _scratch_buffer((logits.device, "pieces"), max(R, 64) * 2048 * 2, torch.float32)
+        count_launches(1)
     _call(f, _ptr(logits), R, V, logits.stride(0), temperature, _ptr(seq_state),
-          seq_state.shape[1] if seq_state is not None else 0, _ptr(slots), _ptr(out_ids), _stream())
+          seq_state.shape[1] if seq_state is not None else 0, _ptr(slots), _ptr(out_ids), _ptr(pieces),
+          _stream())
 
 
 def sample_filtered(logits, temperature, top_k, top_p, penalty, recent, recent_n, seq_state, slots,
@@ -370,11 +384,17 @@ def sample_filtered(logits, temperature, top_k, top_p, penalty, recent, recent_n
             raise KernelError("sample_filtered: recent and recent_n need a row per row of logits")
     f = _fn("sampling.cu", "g2b_sample_filtered",
             [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_void_p, c_int,
-             c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p])
+             c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+    cand = None
+    if temperature > 0.0 and 0 < top_k <= 64 and V >= 8192:
+        # a small top_k over a large vocabulary: many blocks per row list the candidates first
+        words = _fn("sampling.cu", "g2b_sample_filtered_scratch_words", [c_int])
+        cand = _scratch_buffer((logits.device, "filter"), int(words(max(R, 64))), torch.int32)
+        count_launches(1)
     _call(f, _ptr(logits), R, V, logits.stride(0), temperature, top_k, top_p, penalty,
           _ptr(recent), recent.shape[1] if recent is not None else 0, _ptr(recent_n),
           _ptr(seq_state), seq_state.shape[1] if seq_state is not None else 0, _ptr(slots),
-          _ptr(out_ids), 1 if append else 0, _stream())
+          _ptr(out_ids), 1 if append else 0, _ptr(cand), _stream())
 
 
 def recent_set(seq_state, slots, rows) -> None:

@@ -201,6 +201,43 @@ def test_sampling_greedy_and_temperature():
     assert state[slots.long(), 3].tolist() == [3] * R
 
 
+@pytest.mark.parametrize("V,scale", [(151936, 3.0), (8192, 0.5), (300001, 6.0), (40003, 30.0)])
+def test_temperature_sampling_of_a_large_vocabulary(V, scale):
+    """From 8,192 entries on, many blocks per row sum the row's pieces (each against its own
+    maximum) before the row's block draws: a vocabulary of the real size, the smallest that takes
+    this way, one whose pieces are 256 entries, one that is no multiple of four (unaligned rows);
+    flat and peaked rows; a row whose maximum is in its last, partial piece."""
+    from gguf2bin_b200 import kernels
+    from gguf2bin_b200.cache import SEQ_STATE_WORDS
+    R = 5
+    logits = rnd(R, V, scale=scale, seed=33)
+    logits[1, V - 1] = logits[1].max() + 4.0
+    logits[2, 7] = logits[2].max() + 9.0              # most of the mass in one entry
+    state = torch.zeros(R, SEQ_STATE_WORDS, dtype=torch.int32, device=DEV)
+    slots = torch.tensor([2, 0, 4, 1, 3], dtype=torch.int32, device=DEV)
+    seed = 4321
+    kernels.seed_slots(state, slots, torch.arange(R, dtype=torch.int32, device=DEV), seed)
+    ids = torch.empty(R, dtype=torch.int32, device=DEV)
+    # The cumulative distribution of src/l5_model.c:615-619 with the sums taken in float64: the plain
+    # sampler adds 150k float32 terms one after the other, as the reference does, and its total is
+    # off by 2.5e-4 at this size, which is no property to reproduce.
+    cdfs = []
+    for row in logits.cpu().numpy():
+        x = (row / np.float32(0.9)).astype(np.float64)
+        e = np.exp(x - x.max())
+        cdfs.append(np.cumsum(e) / e.sum())
+    chosen = set()
+    for draw in range(6):
+        kernels.sample_rows(logits, 0.9, state, slots, ids)
+        for r in range(R):
+            u = philox_plain.uniform(seed, r, draw)
+            got = ids[r].item()
+            lo = cdfs[r][got - 1] if got > 0 else 0.0
+            assert lo - 1e-5 <= u <= cdfs[r][got] + 1e-5, (r, draw, got, u)
+            chosen.add(got)
+    assert scale > 10 or len(chosen) > R
+
+
 @pytest.mark.parametrize("V,ties", [(2011, False), (151936, False), (40000, True)])
 @pytest.mark.parametrize("top_k,top_p,penalty", [(40, 0.9, 1.1), (0, 0.9, 1.0), (5, 1.0, 1.3), (0, 1.0, 1.0), (1, 0.5, 1.0),
                                                  (2048, 0.95, 1.0), (3000, 0.9, 1.1)])
