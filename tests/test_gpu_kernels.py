@@ -282,6 +282,38 @@ def test_sampling_filtered(top_k, top_p, penalty, V, ties):
         assert ids[r].item() == P.sample_advanced(logits[r].cpu().numpy(), 0.0, top_k, top_p, penalty, rec, 0.5)[0]
 
 
+@pytest.mark.parametrize("R", [40, 100, 160])
+def test_sampling_filtered_many_rows(R):
+    """With many rows the rows are cut into fewer slices (16, 8, 4; none beyond what fills the GPU
+    once): every row against the plain sampler, with ids of the penalty in every slice."""
+    from gguf2bin_b200 import kernels
+    from gguf2bin_b200.cache import SEQ_STATE_WORDS
+    V, temp, top_k, top_p, penalty = 151936, 0.7, 40, 0.9, 1.3
+    logits = rnd(R, V, scale=2.5, seed=35)
+    g = torch.Generator().manual_seed(6)
+    recent = torch.randint(0, V, (R, 64), generator=g, dtype=torch.int32)
+    top = logits.topk(8, dim=1).indices.cpu().to(torch.int32)
+    recent[:, :8] = top                                # the penalty reorders the head of every row
+    recent_n = torch.full((R,), 64, dtype=torch.int32)
+    state = torch.zeros(R, SEQ_STATE_WORDS, dtype=torch.int32, device=DEV)
+    slots = torch.arange(R, dtype=torch.int32, device=DEV)
+    seed = 78
+    kernels.seed_slots(state, slots, slots.clone(), seed)
+    ids = torch.empty(R, dtype=torch.int32, device=DEV)
+    work = logits.clone()
+    kernels.sample_filtered(work, temp, top_k, top_p, penalty, recent.to(DEV), recent_n.to(DEV), state, slots, ids)
+    host = logits.cpu().numpy()
+    for r in range(R):
+        u = philox_plain.uniform(seed, r, 0)
+        want, kept, cdf = P.sample_advanced(host[r], temp, top_k, top_p, penalty, recent[r].tolist(), u)
+        got = ids[r].item()
+        where = np.nonzero(kept == got)[0]
+        assert len(where) == 1, (r, got, "not in the kept set", len(kept))
+        i = int(where[0])
+        lo = cdf[i - 1] if i > 0 else 0.0
+        assert lo - 1e-4 <= u <= cdf[i] + 1e-4, (r, got, want, u, lo, cdf[i])
+
+
 def test_sampling_with_the_recent_ids_on_the_device():
     """The repeat penalty over the ids in the sequences' own records: started with a prompt's
     tail (three, sixty-four and no ids), extended by every sampled id, across the ring's wrap,
