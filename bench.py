@@ -164,9 +164,14 @@ def timed_prompt_step(llm, prompts, repeats: int):
     (the very first run, which also builds scratch buffers and loads kernels; the median of the
     last ``repeats`` runs, which replay the shape's graph; a run of the warm engine without the
     graph, which is what a shape costs the first time it is seen)."""
+    import gc
     import torch
     from gguf2bin_b200.engine import StepEntry
     times = []
+    # the plain run's time is the host's; a collection of Python's cycle collector in the middle of it
+    # (this program holds hundreds of thousands of token ids in lists) adds a millisecond or two
+    gc.collect()
+    gc.disable()
     for i in range(3 + repeats + 1):
         if i == 3 + repeats:                       # once more without the graph: a warm engine's plain run,
             graphs, llm.engine.step_graphs = llm.engine.step_graphs, False     # what a shape seen for the first time costs
@@ -183,6 +188,7 @@ def timed_prompt_step(llm, prompts, repeats: int):
             llm.close_sequence(s)
         times.append(e0.elapsed_time(e1))
     llm.engine.step_graphs = graphs
+    gc.enable()
     return times[0], statistics.median(times[3:-1]), times[-1]
 
 
