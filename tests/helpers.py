@@ -30,8 +30,14 @@ TINY = {
               num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=1, head_dim=128,
               vocab_size=1000, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=True,
               max_position_embeddings=512),
+    # a vocabulary large enough for the samplers that cut a row into slices (8,192 entries and more),
+    # and no multiple of four: every second row of logits starts off a 16-byte boundary
+    "e": dict(architectures=["Qwen3ForCausalLM"], hidden_size=64, intermediate_size=96,
+              num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1, head_dim=32,
+              vocab_size=8209, rope_theta=1e4, rms_norm_eps=1e-6, tie_word_embeddings=True,
+              max_position_embeddings=96),
 }
-SEEDS = {"a": 0, "b": 1, "c": 2, "d": 3}
+SEEDS = {"a": 0, "b": 1, "c": 2, "d": 3, "e": 4}
 
 _tmp_root = None
 

@@ -151,6 +151,27 @@ def test_repeat_penalty_in_a_batch_against_plain(llms, temp, top_k):
     assert [o.tokens for o in one_by_one] == [o.tokens for o in outs]
 
 
+@pytest.mark.parametrize("filtered", [True, False])
+def test_sampling_over_a_large_vocabulary_inside_the_step(llms, filtered):
+    """A vocabulary of 8,209 entries: the samplers that give a row to many blocks run inside the
+    decode step and its graph (five requests in steps of eight rows, rows that start off a 16-byte
+    boundary, the repeat penalty's ring).  Every token against the plain implementation."""
+    llm = llms("e", "float32", max_tokens=1024)
+    prompts = [random_tokens("e", n, 950 + i) for i, n in enumerate([5, 30, 2, 64, 17])]
+    n_new = 12
+    if filtered:
+        kw = dict(temperature=0.7, top_k=40, top_p=0.9, repeat_penalty=1.3, seed=5)
+        want = [plain_generate_filtered("e", "float32", p, n_new, 0.7, 40, 0.9, 1.3, 5, i) for i, p in enumerate(prompts)]
+    else:
+        kw = dict(temperature=0.9, top_k=0, top_p=1.0, repeat_penalty=1.0, seed=5)
+        want = [plain_generate("e", "float32", p, n_new, 0.9, seed=5, stream=i)[0] for i, p in enumerate(prompts)]
+    before = llm.engine.decode_graph_captures
+    outs = llm.generate(prompts, n=n_new, ignore_eos=True, **kw)
+    assert llm.engine.decode_graph_captures > before, "twelve steps of one shape are worth a graph"
+    for i, o in enumerate(outs):
+        assert o.tokens == want[i], f"request {i}"
+
+
 def test_rows_beyond_the_sequences_change_nothing(llms):
     """Six and eleven sequences decode as steps of eight and sixteen rows (the rows beyond them
     use the cache's spare page and slot), and keep that shape while sequences end: every
