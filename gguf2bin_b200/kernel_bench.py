@@ -110,12 +110,21 @@ def decode(a) -> None:
     if b.want("down"):
         W = [bf(H, I) for _ in range(L)]
         b.run("down", lambda: [kernels_bf16.linear_bf16(mid, w, res, True) for w in W], L, W[0].numel() * 2)
-    if b.want("lm_head") or b.want("greedy"):
+    if b.want("lm_head") or b.want("greedy") or b.want("temperature") or b.want("default_sampling"):
+        from .cache import SEQ_STATE_WORDS
         Wh = bf(V, H)
         logits = torch.empty(B, V, device=DEV)
         ids = torch.empty(B, dtype=torch.int32, device=DEV)
+        state = torch.zeros(B, SEQ_STATE_WORDS, dtype=torch.int32, device=DEV)
+        slots = torch.arange(B, dtype=torch.int32, device=DEV)
+        kernels.seed_slots(state, slots, slots.clone(), 1)
         b.run("lm_head", lambda: kernels_bf16.linear_bf16(h, Wh, logits, False), 1, Wh.numel() * 2)
         b.run("greedy", lambda: kernels.sample_rows(logits, 0.0, None, None, ids), 1, logits.numel() * 4)
+        logits.copy_(torch.randn(B, V, device=DEV) * 2.5)
+        b.run("temperature", lambda: kernels.sample_rows(logits, 0.7, state, slots, ids), 1, logits.numel() * 4)
+        # temperature 0.7, top-k 40, top-p 0.9, repeat penalty 1.1 over the ids in the sequences' records
+        b.run("default_sampling", lambda: kernels.sample_filtered(logits, 0.7, 40, 0.9, 1.1, None, None, state, slots,
+                                                                  ids, append=True), 1, logits.numel() * 4)
     ps, ctx_len = 64, a.ctx
     pages_per = -(-(ctx_len + 1) // ps)
     if b.want("attn_decode") or b.want("qknorm_rope_cache"):
