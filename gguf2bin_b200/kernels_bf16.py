@@ -185,7 +185,7 @@ def _wstream_case(M: int, N: int, K: int) -> bool:
     4096 x 4096 at 16 rows) unless the matrix is small (4096 x 2048 at 16 rows: 7.2 against 5.5 us;
     2048 x 2048 at 32 rows: 6.0 against 5.3); up to 8 rows only against the largest matrices or a
     very long K (5120 x 17408: 31.6 against 43.8 us; 2048 x 6144: 10.7 against 17.0; but
-    6144 x 4096: 13.5 against 12.5, and the mma.sync kernel can take the norm in front along);
+    6144 x 4096: 13.4 against 12.3, and the mma.sync kernel can take the norm in front along);
     from 65 rows only narrow outputs up to 96 rows (24576 x 4096 at 65 rows: 54.0 against 39.0 us
     by the persistent kernel; 4096 x 12288: 22.8 against 24.7).
     A vocabulary (151,936 rows) at every number of rows up to 64: at K = 2,048 to 5,120 it reads
@@ -203,7 +203,7 @@ def _wstream_case(M: int, N: int, K: int) -> bool:
         return False
     if N >= 2048 and K >= 2048:
         if M <= 8:
-            return N * K >= (24 << 20) or K >= 6144
+            return N * K > (24 << 20) or K >= 6144
         if M <= 16:
             return N * K > (8 << 20)
         if M <= 32:

@@ -15,7 +15,7 @@ from gguf2bin_b200.kernels_bf16 import _normed_loses, _tc_shape, _wstream_case
     (16, 12288, 2048, True),
     # up to 8 rows: only the largest matrices (a vocabulary is one) or a very long K
     (8, 5120, 17408, True), (1, 2048, 6144, True), (4, 19456, 2560, True), (8, 4096, 12288, True),
-    (8, 2560, 4096, False), (1, 4096, 2048, False), (8, 151936, 4096, True), (1, 151936, 2048, True),
+    (8, 2560, 4096, False), (8, 6144, 4096, False), (1, 4096, 2048, False), (8, 151936, 4096, True), (1, 151936, 2048, True),
     # a small model's layers: from 17 rows; narrow outputs except the short one at up to 32 rows
     (16, 1024, 3072, False), (32, 1024, 2048, False), (32, 1024, 3072, True), (64, 1024, 2048, True),
     (128, 1024, 3072, True),
