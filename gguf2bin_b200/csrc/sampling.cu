@@ -13,9 +13,11 @@
 // first), the best top_k kept, softmax over the kept, the shortest prefix whose
 // cumulative sum reaches top_p kept and renormalised, then the first kept entry with
 // r <= cumulative sum.  With a top_k of up to 2,048 the kept entries are listed and sorted
-// (two counting passes over the order-preserving integer image of the logits find where the
-// k-th largest lies); without a top_k, weighted radix descents over that image do the same
-// without a sort of the vocabulary.
+// (counting passes over the order-preserving integer image of the logits find where the
+// k-th largest lies; a top_k of up to 64 over a large vocabulary is listed slice by slice by
+// many blocks first); without a top_k the row is summed by buckets of its values, and only the
+// buckets in which the cut and the draw fall are listed; weighted radix descents over the
+// integer image do the same without any list when none fits (thousands of equal logits).
 #include "common.cuh"
 
 #include <climits>
@@ -902,6 +904,153 @@ __device__ int list_from_slices(const int *__restrict__ cand, int want, ShortLis
   return n;
 }
 
+// ---- without a top_k: the row by buckets of its values ------------------------------------------
+// A top_p alone (or nothing but the repeat penalty) keeps whatever share of the vocabulary holds the
+// mass: a few entries of a peaked distribution, tens of thousands of a flat one, which no short
+// list holds; finding the cut by radix descents over the keys took 1.5 ms for 150k entries (every
+// pass adds 150k weights into a handful of bins).  Here one pass adds every entry's e^(v - max)
+// and a count into the bucket floor(64 (max - v)) of its value v = x / temp (2,048 buckets: 32
+// units below the maximum, what lies further down shares the last one).  Buckets are in descending
+// order of value, so the cumulative sums over them say in which bucket the top_p cut falls and in
+// which the draw; only those one or two buckets are listed, sorted (key descending, index
+// ascending: the reference's order) and walked.  Returns the chosen index to every thread, or -1
+// when a bucket that has to be listed holds more than the list does (the caller's descents then).
+// Warp 0 calls it: the first j < n with base + e[0] + ... + e[j] >= target (n if there is none) and
+// that sum (the whole sum if there is none).
+__device__ int first_reaching(const float *e, int n, float base, float target, float *sum_out) {
+  const int lane = threadIdx.x & 31;
+  float run = base;
+  for (int i0 = 0; i0 < n; i0 += 32) {
+    const float x = i0 + lane < n ? e[i0 + lane] : 0.f;
+    float incl = x;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    const unsigned hit = __ballot_sync(0xffffffffu, i0 + lane < n && run + incl >= target);
+    if (hit) {
+      const int l = __ffs(hit) - 1;
+      *sum_out = run + __shfl_sync(0xffffffffu, incl, l);
+      return i0 + l;
+    }
+    run += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  *sum_out = run;
+  return n;
+}
+
+constexpr int N_BUCKETS = 2048;
+constexpr float BUCKETS_PER_UNIT = 64.f;
+__device__ __forceinline__ int bucket_of(float v, float mx) {
+  return max(0, min(N_BUCKETS - 1, (int)((mx - v) * BUCKETS_PER_UNIT)));     // falls as v rises; the maximum is in bucket 0
+}
+
+// The entries of bucket b into the list, sorted, with their weights in le; their number.
+__device__ int list_bucket(const float *row, int V, float inv_temp, float mx, int b, ShortList &L, float *le) {
+  __shared__ int s_n;
+  __syncthreads();
+  if (threadIdx.x == 0) s_n = 0;
+  __syncthreads();
+  scan_row(row, V, [&](int i, float x) {
+    const float v = x * inv_temp;
+    if (bucket_of(v, mx) == b) {
+      const int j = atomicAdd(&s_n, 1);
+      if (j < LIST_CAP) { L.key[j] = order_key(v); L.idx[j] = i; }
+    }
+  });
+  __syncthreads();
+  const int n = s_n;
+  if (n > LIST_CAP) return n;
+  sort_list(L, n);                                   // in place: the list's other arrays hold the buckets
+  for (int j = threadIdx.x; j < n; j += blockDim.x) le[j] = expf(row[L.idx[j]] * inv_temp - mx);
+  __syncthreads();
+  return n;
+}
+
+__device__ int pick_by_buckets(const float *row, int V, float inv_temp, float top_p, float u, ShortList &L, float *le) {
+  static_assert(N_BUCKETS == 2048 && LIST_CAP == 2048, "the buckets live in the list's arrays");
+  __shared__ int s_keep, s_choice;
+  __shared__ float s_kept, s_base;
+  float *mass = L.e;                                 // per bucket, then cumulative from the top
+  int *cnt = L.hist;
+  float mx;
+  block_argmax(row, V, inv_temp, &mx);
+  for (int i = threadIdx.x; i < N_BUCKETS; i += blockDim.x) { mass[i] = 0.f; cnt[i] = 0; }
+  __syncthreads();
+  scan_row(row, V, [&](int, float x) {
+    const float v = x * inv_temp;
+    const int b = bucket_of(v, mx);
+    atomicAdd(&mass[b], expf(v - mx));
+    atomicAdd(&cnt[b], 1);
+  });
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    // cumulative sums in bucket order: lane l owns the 64 buckets from 64 l
+    const int lane = threadIdx.x, b0 = 64 * lane;
+    float mine = 0.f;
+    for (int d = 0; d < 64; ++d) mine += mass[b0 + d];
+    float incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    float run = incl - mine;
+    for (int d = 0; d < 64; ++d) { run += mass[b0 + d]; mass[b0 + d] = run; }
+  }
+  __syncthreads();
+  // first bucket, up to b_max, whose cumulative sum reaches target (b_max if none does)
+  auto bucket_reaching = [&](float target, int b_max) {
+    int lo = 0, hi = b_max;
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (mass[mid] >= target) hi = mid; else lo = mid + 1;
+    }
+    while (lo > 0 && cnt[lo] == 0) --lo;             // (rounding left the target above the total: the last entries)
+    return lo;
+  };
+  const float total = mass[N_BUCKETS - 1];
+  int bp = N_BUCKETS - 1, n_p = 0;                   // the cut's bucket and the entries listed from it
+  if (top_p < 1.f) {
+    const float target = top_p * total;
+    bp = bucket_reaching(target, N_BUCKETS - 1);
+    if (cnt[bp] > LIST_CAP) return -1;
+    const float base = bp > 0 ? mass[bp - 1] : 0.f;
+    n_p = list_bucket(row, V, inv_temp, mx, bp, L, le);
+    if (threadIdx.x < 32) {
+      float kept;
+      const int j = first_reaching(le, n_p, base, target, &kept);       // the shortest head that reaches top_p
+      if (threadIdx.x == 0) { s_keep = j < n_p ? j + 1 : n_p; s_kept = kept; s_base = base; }
+    }
+    __syncthreads();
+  } else if (threadIdx.x == 0) {
+    s_kept = total; s_keep = 0; s_base = 0.f;
+  }
+  __syncthreads();
+  const float kept = s_kept, target = u * kept;
+  const int keep_p = s_keep;
+  int bu = bucket_reaching(target, bp);
+  // (with a cut, the draw falls in the cut's bucket when it lies beyond the buckets above it)
+  if (top_p < 1.f && target > s_base) bu = bp;
+  int n_u = n_p, limit = keep_p;
+  float base = s_base;
+  if (!(top_p < 1.f && bu == bp)) {
+    if (cnt[bu] > LIST_CAP) return -1;
+    base = bu > 0 ? mass[bu - 1] : 0.f;
+    n_u = list_bucket(row, V, inv_temp, mx, bu, L, le);
+    limit = n_u;
+  }
+  if (threadIdx.x < 32) {
+    float sum;
+    const int j = first_reaching(le, limit, base, target, &sum);
+    if (threadIdx.x == 0) s_choice = L.idx[limit > 0 ? min(j, limit - 1) : 0];
+  }
+  __syncthreads();
+  (void)n_u;
+  return s_choice;
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, int top_k,
                        float top_p, float penalty, const int *__restrict__ recent, int recent_ld,
@@ -916,6 +1065,7 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
   __shared__ float s_r;
   __shared__ int s_done;
   __shared__ ShortList L;
+  __shared__ float s_le[LIST_CAP];
   float *hist = L.e;                                // the descents' 256 bins and the tie list live in the list's arrays
   int *tie_list = L.idx;
   float *row = logits + (size_t)blockIdx.x * ld;
@@ -945,6 +1095,18 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
   const float inv_temp = 1.f / temp;
   float mx;
   const bool cut_k = top_k > 0 && top_k < V;
+  // the token's one random number, whichever way the kept set is found below
+  if (threadIdx.x == 0) s_r = next_uniform(seq_state, slots[blockIdx.x], state_words);
+  __syncthreads();
+  const float u = s_r;
+  if (!cut_k) {
+    // no top_k: the row by buckets of its values (a flat distribution keeps tens of thousands of entries)
+    const int id = pick_by_buckets(row, V, inv_temp, top_p, u, L, s_le);
+    if (id >= 0) {
+      if (threadIdx.x == 0) keep(id);
+      return;
+    }
+  }
   // (When nothing is cut, the draw still walks the entries in descending order, as the
   // reference's filtered sampler does: the descents below.)
   // The kept entries as a sorted list: the best top_k, or without a top_k the best 512 or more, among
@@ -969,9 +1131,6 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
           const int lane = threadIdx.x;
           const float e0 = 2 * lane < n_list ? L.e[2 * lane] : 0.f;
           const float e1 = 2 * lane + 1 < n_list ? L.e[2 * lane + 1] : 0.f;
-          float u = 0.f;
-          if (lane == 0) u = next_uniform(seq_state, slots[blockIdx.x], state_words);
-          u = __shfl_sync(0xffffffffu, u, 0);
           const float pair = e0 + e1;
           float incl = pair;
 #pragma unroll
@@ -1023,7 +1182,7 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
         }
         s_done = done ? 1 : 0;
         if (done) {
-          const float target = next_uniform(seq_state, slots[blockIdx.x], state_words) * kept;
+          const float target = u * kept;
           float run = 0.f;
           int pick = L.idx[n_keep - 1];
           for (int j = 0; j < n_keep; ++j) {
@@ -1063,9 +1222,7 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
     bounded = true;
     kept = admitted_mass(row, V, inv_temp, mx, bound_key, tie_idx, bounded, scratch);
   }
-  if (threadIdx.x == 0) s_r = next_uniform(seq_state, slots[blockIdx.x], state_words);
-  __syncthreads();
-  const float target = s_r * kept;
+  const float target = u * kept;
   const Descent d = radix_descent<true>(row, V, inv_temp, mx, bound_key, bounded, target, hist);
   int choice = tie_walk<true>(row, V, inv_temp, mx, d.key, d.above, target, tie_list);
   if (bounded && d.key == bound_key && choice > tie_idx) choice = tie_idx;

@@ -282,6 +282,43 @@ def test_sampling_filtered(top_k, top_p, penalty, V, ties):
         assert ids[r].item() == P.sample_advanced(logits[r].cpu().numpy(), 0.0, top_k, top_p, penalty, rec, 0.5)[0]
 
 
+@pytest.mark.parametrize("V,scale,top_p,penalty", [(151936, 2.5, 0.9, 1.0), (151936, 2.5, 1.0, 1.2), (151936, 12.0, 0.95, 1.1),
+                                                   (50021, 0.3, 0.5, 1.0), (9001, 40.0, 0.9, 1.0), (300, 2.0, 0.8, 1.3)])
+def test_sampling_without_a_top_k(V, scale, top_p, penalty):
+    """No top_k: a top_p alone, or only the repeat penalty.  Flat rows, of which the top_p keeps tens
+    of thousands of entries, and peaked ones, of which it keeps one or two; a row whose values all lie
+    within a few buckets; every draw against the plain sampler's kept set and cumulative sums."""
+    from gguf2bin_b200 import kernels
+    from gguf2bin_b200.cache import SEQ_STATE_WORDS
+    R, temp = 4, 0.7
+    logits = rnd(R, V, scale=scale, seed=36)
+    recent = torch.randint(0, V, (R, 64), generator=torch.Generator().manual_seed(7), dtype=torch.int32)
+    recent[:, :4] = logits.topk(4, dim=1).indices.cpu().to(torch.int32)
+    recent_n = torch.tensor([64, 0, 30, 64], dtype=torch.int32)
+    state = torch.zeros(R, SEQ_STATE_WORDS, dtype=torch.int32, device=DEV)
+    slots = torch.arange(R, dtype=torch.int32, device=DEV)
+    seed = 79
+    kernels.seed_slots(state, slots, slots.clone(), seed)
+    ids = torch.empty(R, dtype=torch.int32, device=DEV)
+    host = logits.cpu().numpy()
+    sizes = set()
+    for draw in range(5):
+        work = logits.clone()
+        kernels.sample_filtered(work, temp, 0, top_p, penalty, recent.to(DEV), recent_n.to(DEV), state, slots, ids)
+        for r in range(R):
+            u = philox_plain.uniform(seed, r, draw)
+            want, kept, cdf = P.sample_advanced(host[r], temp, 0, top_p, penalty, recent[r, :recent_n[r]].tolist(), u)
+            got = ids[r].item()
+            where = np.nonzero(kept == got)[0]
+            assert len(where) == 1, (r, draw, got, "not in the kept set", len(kept))
+            i = int(where[0])
+            lo = cdf[i - 1] if i > 0 else 0.0
+            assert lo - 1e-4 <= u <= cdf[i] + 1e-4, (r, draw, got, want, u, lo, cdf[i])
+            sizes.add(len(kept))
+    assert state[:, 3].tolist() == [5] * R, "one random number per token"
+    assert scale > 10 or V < 1000 or max(sizes) > 100
+
+
 @pytest.mark.parametrize("R", [40, 100, 160])
 def test_sampling_filtered_many_rows(R):
     """With many rows the rows are cut into fewer slices (16, 8, 4; none beyond what fills the GPU
