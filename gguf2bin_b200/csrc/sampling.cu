@@ -795,14 +795,18 @@ __device__ void apply_penalty(float *row, int V, int begin, int end, float penal
 // ---- the best top_k of a row by many blocks ------------------------------------------------
 // A row is one block's work above, and a block pulls a vocabulary of 150k entries through one SM
 // at a few dozen GB/s: 50 us for the reference's default parameters.  With a top_k of up to
-// LOCAL_CAP the row is cut into FILTER_SPLITS slices first; a block per slice applies the repeat
+// MAX_SLICE_CAP the row is cut into slices first (32 for a top_k up to 64, 16 up to 128, 8 up to
+// 256: their lists side by side are 2,048 places); a block per slice applies the repeat
 // penalty to its entries and lists its own best top_k (sorted; every entry of the row's best
-// top_k is among some slice's).  The row's block then sorts the slices' lists together instead
-// of reading the row.  cand: int [rows x FILTER_SPLITS x (1 + 2 LOCAL_CAP)]: per slice the
-// number listed (-1: the slice's list did not fit, the row's block reads the row itself), the
+// top_k is among some slice's).  The row's block then merges the slices' lists instead
+// of reading the row.  cand: int [rows x ROW_CAND_WORDS]: per row the slices' numbers of listed
+// entries (-1: the slice's list did not fit, the row's block reads the row itself), the
 // keys, the indices.
-constexpr int FILTER_SPLITS = 32, LOCAL_CAP = 64, FILTER_THREADS = 256;
-constexpr int CAND_WORDS = 1 + 2 * LOCAL_CAP;
+constexpr int MAX_SLICES = 32, FILTER_THREADS = 256;
+constexpr int MAX_SLICE_CAP = 256;       // places per slice: 64 for a top_k up to 64 (32 slices), 128 (16), 256 (8)
+constexpr int ROW_CAND_WORDS = MAX_SLICES + 2 * 2048;       // per row: the slices' counts, their keys, their indices
+
+__host__ __device__ inline int slice_cap(int top_k) { return top_k <= 64 ? 64 : (top_k <= 128 ? 128 : 256); }
 
 __global__ void __launch_bounds__(FILTER_THREADS)
 filter_slices_kernel(float *__restrict__ logits, int V, int ld, float temp, int top_k, float penalty,
@@ -813,13 +817,14 @@ filter_slices_kernel(float *__restrict__ logits, int V, int ld, float temp, int 
   __shared__ ShortList L;
   const int r = blockIdx.y;
   float *row = logits + (size_t)r * ld;
-  // gridDim.x slices (32 with few rows, fewer with many: enough blocks to fill the GPU once); the
-  // places of the others are marked empty
+  const int cap = slice_cap(top_k), lists = 2048 / cap;
+  // gridDim.x slices (as many as there are lists with few rows, fewer with many: enough blocks to
+  // fill the GPU once); the places of the others are marked empty
   const int per = ((V + (int)gridDim.x - 1) / (int)gridDim.x + 3) & ~3;     // slices start at multiples of 16 bytes
   const int begin = min(V, (int)blockIdx.x * per), end = min(V, begin + per);
+  int *mine = cand + (size_t)r * ROW_CAND_WORDS;
   if (blockIdx.x == 0)
-    for (int sl = gridDim.x + threadIdx.x; sl < FILTER_SPLITS; sl += blockDim.x)
-      cand[((size_t)r * FILTER_SPLITS + sl) * CAND_WORDS] = 0;
+    for (int sl = gridDim.x + threadIdx.x; sl < lists; sl += blockDim.x) mine[sl] = 0;
   const int *rec = (seq_state && slots && state_words >= SS_RING + SS_RING_WORDS)
                        ? seq_state + (size_t)slots[r] * state_words : nullptr;
   G2B_STAMP(0);
@@ -827,16 +832,16 @@ filter_slices_kernel(float *__restrict__ logits, int V, int ld, float temp, int 
                 recent ? min(max(recent_n[r], 0), recent_ld) : 0, rec);
   __syncthreads();
   G2B_STAMP(1);
-  int *out = cand + ((size_t)r * FILTER_SPLITS + blockIdx.x) * CAND_WORDS;
   const int want = min(top_k, end - begin);
   int n = 0;
   if (want > 0) n = list_top_k(row + begin, end - begin, 1.f / temp, want, L);
   const int m = n < 0 ? -1 : min(n, want);
+  int *keys = mine + MAX_SLICES + blockIdx.x * cap, *idxs = keys + 2048;
   for (int j = threadIdx.x; j < m; j += blockDim.x) {
-    out[1 + j] = (int)L.key[j];
-    out[1 + LOCAL_CAP + j] = begin + L.idx[j];
+    keys[j] = (int)L.key[j];
+    idxs[j] = begin + L.idx[j];
   }
-  if (threadIdx.x == 0) out[0] = m;
+  if (threadIdx.x == 0) mine[blockIdx.x] = m;
   G2B_STAMP(5);
 }
 
@@ -852,43 +857,44 @@ __device__ __forceinline__ int count_before(const uint32_t *zk, const int *zi, i
 }
 
 // The best `want` entries of a row from its slices' sorted lists: the lists are merged in pairs,
-// five times, each result cut to `want`; an entry's place in a merged list is its place in its own
+// level by level, each result cut to `want`; an entry's place in a merged list is its place in its own
 // list plus the number of entries of the other list that belong before it (a binary search), so a
-// level is one step for all entries at once.  -1 when a slice gave no list.
-__device__ int list_from_slices(const int *__restrict__ cand, int want, ShortList &L) {
-  static_assert(FILTER_SPLITS == 32 && FILTER_SPLITS * LOCAL_CAP <= LIST_CAP, "the lists side by side, LOCAL_CAP apart");
-  __shared__ int s_len[2][FILTER_SPLITS];
+// level is one step for all entries at once.  cand: the row's part of the scratch; cap: places per
+// list (2,048 / cap lists).  -1 when a slice gave no list.
+__device__ int list_from_slices(const int *__restrict__ cand, int cap, int want, ShortList &L) {
+  static_assert(LIST_CAP == 2048, "the lists side by side fill the list's arrays");
+  __shared__ int s_len[2][MAX_SLICES];
   uint32_t *key[2] = {L.key, reinterpret_cast<uint32_t *>(L.e)};
   int *idx[2] = {L.idx, L.hist};
+  const int shift = cap == 64 ? 6 : (cap == 128 ? 7 : 8);     // cap is 64, 128 or 256
+  const int lists0 = LIST_CAP >> shift;
   __syncthreads();
-  if (threadIdx.x < FILTER_SPLITS) s_len[0][threadIdx.x] = cand[(size_t)threadIdx.x * CAND_WORDS];
+  if (threadIdx.x < MAX_SLICES) s_len[0][threadIdx.x] = threadIdx.x < lists0 ? cand[threadIdx.x] : 0;
   __syncthreads();
-  const int my_len = s_len[0][threadIdx.x & 31];      // every warp looks at all 32 lengths
-  if (__any_sync(0xffffffffu, my_len < 0 || my_len > LOCAL_CAP)) return -1;
-  for (int t = threadIdx.x; t < FILTER_SPLITS * LOCAL_CAP; t += blockDim.x) {
-    const int sl = t / LOCAL_CAP, j = t % LOCAL_CAP;
-    if (j < s_len[0][sl]) {
-      const int *src = cand + (size_t)sl * CAND_WORDS;
-      L.key[t] = (uint32_t)src[1 + j];
-      L.idx[t] = src[1 + LOCAL_CAP + j];
+  const int my_len = s_len[0][threadIdx.x & 31];      // every warp looks at all the lengths
+  if (__any_sync(0xffffffffu, my_len < 0 || my_len > cap)) return -1;
+  for (int t = threadIdx.x; t < LIST_CAP; t += blockDim.x) {
+    if ((t & (cap - 1)) < s_len[0][t >> shift]) {
+      L.key[t] = (uint32_t)cand[MAX_SLICES + t];
+      L.idx[t] = cand[MAX_SLICES + LIST_CAP + t];
     }
   }
   __syncthreads();
   int from = 0;
-  for (int lists = FILTER_SPLITS; lists > 1; lists >>= 1, from ^= 1) {
+  for (int lists = lists0; lists > 1; lists >>= 1, from ^= 1) {
     const uint32_t *ik = key[from];
     const int *ii = idx[from];
     uint32_t *ok = key[from ^ 1];
     int *oi = idx[from ^ 1];
-    for (int t = threadIdx.x; t < lists * LOCAL_CAP; t += blockDim.x) {
-      const int mine = t / LOCAL_CAP, j = t % LOCAL_CAP, other = mine ^ 1;
+    for (int t = threadIdx.x; t < (lists << shift); t += blockDim.x) {
+      const int mine = t >> shift, j = t & (cap - 1), other = mine ^ 1;
       if (j < s_len[from][mine]) {
-        const uint32_t k = ik[mine * LOCAL_CAP + j];
-        const int id = ii[mine * LOCAL_CAP + j];
-        const int place = j + count_before(ik + other * LOCAL_CAP, ii + other * LOCAL_CAP, s_len[from][other], k, id);
+        const uint32_t k = ik[t];
+        const int id = ii[t];
+        const int place = j + count_before(ik + (other << shift), ii + (other << shift), s_len[from][other], k, id);
         if (place < want) {
-          ok[(mine >> 1) * LOCAL_CAP + place] = k;
-          oi[(mine >> 1) * LOCAL_CAP + place] = id;
+          ok[((mine >> 1) << shift) + place] = k;
+          oi[((mine >> 1) << shift) + place] = id;
         }
       }
     }
@@ -897,7 +903,7 @@ __device__ int list_from_slices(const int *__restrict__ cand, int want, ShortLis
     __syncthreads();
   }
   const int n = s_len[from][0];
-  if (from == 1) {                                   // (five levels: the result is in the second pair of arrays)
+  if (from == 1) {                                   // (an odd number of levels: the result is in the second pair of arrays)
     for (int i = threadIdx.x; i < n; i += blockDim.x) { L.key[i] = key[1][i]; L.idx[i] = idx[1][i]; }
     __syncthreads();
   }
@@ -1059,7 +1065,7 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
                        const int *__restrict__ cand_all) {
   pdl_launch();
   pdl_wait();
-  const int *cand = cand_all ? cand_all + (size_t)blockIdx.x * FILTER_SPLITS * CAND_WORDS : nullptr;
+  const int *cand = cand_all ? cand_all + (size_t)blockIdx.x * ROW_CAND_WORDS : nullptr;
   G2B_STAMP(8);
   __shared__ float scratch[32];
   __shared__ float s_r;
@@ -1095,11 +1101,33 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
   const float inv_temp = 1.f / temp;
   float mx;
   const bool cut_k = top_k > 0 && top_k < V;
-  // the token's one random number, whichever way the kept set is found below
-  if (threadIdx.x == 0) s_r = next_uniform(seq_state, slots[blockIdx.x], state_words);
-  __syncthreads();
-  const float u = s_r;
+  // The token's one random number, whichever way the kept set is found below.  Thread 0 asks for the
+  // record's words here and computes the number where it is first needed: two dependent trips to
+  // memory that would otherwise stand before the block's first barrier.
+  uint32_t draw_words[4] = {0u, 0u, 0u, 0u};
+  int *draw_rec = nullptr;
+  if (threadIdx.x == 0) {
+    draw_rec = seq_state + (size_t)slots[blockIdx.x] * state_words;
+    draw_words[0] = (uint32_t)draw_rec[SS_DRAWS]; draw_words[1] = (uint32_t)draw_rec[2];
+    draw_words[2] = (uint32_t)draw_rec[0]; draw_words[3] = (uint32_t)draw_rec[1];
+  }
+  bool drawn = false;
+  float u = 0.f;
+  // every thread calls it, once is enough: the number to all threads (a barrier inside)
+  auto draw = [&]() {
+    if (drawn) return;
+    if (threadIdx.x == 0) {
+      uint32_t o[4];
+      philox4x32_10(draw_words[0], draw_words[1], 0u, 0u, draw_words[2], draw_words[3], o);
+      draw_rec[SS_DRAWS] = (int)draw_words[0] + 1;
+      s_r = (float)(o[0] >> 8) * (1.0f / 16777216.0f);
+    }
+    __syncthreads();
+    u = s_r;
+    drawn = true;
+  };
   if (!cut_k) {
+    draw();
     // no top_k: the row by buckets of its values (a flat distribution keeps tens of thousands of entries)
     const int id = pick_by_buckets(row, V, inv_temp, top_p, u, L, s_le);
     if (id >= 0) {
@@ -1113,7 +1141,7 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
   // which the shortest head that reaches top_p of the WHOLE row's mass usually lies.
   const int want = cut_k ? top_k : min(V, 512);
   if (want <= LIST_CAP && (cut_k || top_p < 1.f)) {
-    int n = cand ? list_from_slices(cand, want, L) : list_by_sampled_floor(row, V, inv_temp, want, L);
+    int n = cand ? list_from_slices(cand, slice_cap(top_k), want, L) : list_by_sampled_floor(row, V, inv_temp, want, L);
     G2B_STAMP(9);
     if (n < 0 && cut_k) n = list_top_k(row, V, inv_temp, top_k, L);
     if (n >= 0) {
@@ -1123,40 +1151,41 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
       if (!cut_k) whole = admitted_mass(row, V, inv_temp, mx, 0u, V, false, scratch);
       for (int j = threadIdx.x; j < n_list; j += blockDim.x) L.e[j] = expf(row[L.idx[j]] * inv_temp - mx);
       __syncthreads();
+      draw();
       G2B_STAMP(10);
-      if (cut_k && n_list >= 1 && n_list <= 64) {
-        // a short list: the cumulative sums by one warp, two entries a lane (the cuts and the draw are
-        // then three ballots, where one thread walking the list took 3 us)
+      if (cut_k && n_list >= 1) {
+        // a top_k's list: the cumulative sums by one warp, 32 entries a trip (the cuts and the draw by
+        // one thread walking the list took 3 us for 40 entries)
         if (threadIdx.x < 32) {
           const int lane = threadIdx.x;
-          const float e0 = 2 * lane < n_list ? L.e[2 * lane] : 0.f;
-          const float e1 = 2 * lane + 1 < n_list ? L.e[2 * lane + 1] : 0.f;
-          const float pair = e0 + e1;
-          float incl = pair;
+          float run = 0.f;                           // the weights become their cumulative sums, in place
+          for (int i0 = 0; i0 < n_list; i0 += 32) {
+            float incl = i0 + lane < n_list ? L.e[i0 + lane] : 0.f;
 #pragma unroll
-          for (int o = 1; o < 32; o <<= 1) {
-            const float up = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += up;
+            for (int o = 1; o < 32; o <<= 1) {
+              const float up = __shfl_up_sync(0xffffffffu, incl, o);
+              if (lane >= o) incl += up;
+            }
+            if (i0 + lane < n_list) L.e[i0 + lane] = run + incl;
+            run += __shfl_sync(0xffffffffu, incl, 31);
           }
-          const float c0 = incl - pair + e0, c1 = c0 + e1;      // cumulative sums at 2 lane, 2 lane + 1
-          // first list place whose cumulative sum reaches `target`, among the first n (n if there is none)
-          auto first_reaching = [&](float target, int n) {
-            const unsigned h0 = __ballot_sync(0xffffffffu, 2 * lane < n && c0 >= target);
-            const unsigned h1 = __ballot_sync(0xffffffffu, 2 * lane + 1 < n && c1 >= target);
-            const int j0 = h0 ? 2 * (__ffs(h0) - 1) : n, j1 = h1 ? 2 * (__ffs(h1) - 1) + 1 : n;
-            return min(j0, j1);
-          };
-          auto cumulative_at = [&](int j) {
-            return __shfl_sync(0xffffffffu, (j & 1) ? c1 : c0, j >> 1);
+          __syncwarp();
+          // first place among the first m whose cumulative sum reaches target (m if none does)
+          auto reaching = [&](float target, int m) {
+            int lo = 0, hi = m;
+            while (lo < hi) {
+              const int mid = (lo + hi) >> 1;
+              if (L.e[mid] >= target) hi = mid; else lo = mid + 1;
+            }
+            return lo;
           };
           int n_keep = n_list;
           if (top_p < 1.f) {
             // shortest head (descending) whose cumulative probability reaches top_p
-            const int j = first_reaching(top_p * cumulative_at(n_list - 1), n_list);
+            const int j = reaching(top_p * L.e[n_list - 1], n_list);
             if (j < n_list) n_keep = j + 1;
           }
-          const float kept = cumulative_at(n_keep - 1);
-          const int j = first_reaching(u * kept, n_keep);
+          const int j = reaching(u * L.e[n_keep - 1], n_keep);
           if (lane == 0) {
             keep(L.idx[j < n_keep ? j : n_keep - 1]);
             s_done = 1;
@@ -1222,6 +1251,7 @@ sample_filtered_kernel(float *__restrict__ logits, int V, int ld, float temp, in
     bounded = true;
     kept = admitted_mass(row, V, inv_temp, mx, bound_key, tie_idx, bounded, scratch);
   }
+  draw();
   const float target = u * kept;
   const Descent d = radix_descent<true>(row, V, inv_temp, mx, bound_key, bounded, target, hist);
   int choice = tie_walk<true>(row, V, inv_temp, mx, d.key, d.above, target, tie_list);
@@ -1245,7 +1275,7 @@ static int g2b_sm_count() {
 }
 
 extern "C" int g2b_sample_filtered_scratch_words(int R) {
-  return (int)min((long long)R * FILTER_SPLITS * CAND_WORDS, (long long)INT_MAX);
+  return (int)min((long long)R * ROW_CAND_WORDS, (long long)INT_MAX);
 }
 
 extern "C" int g2b_sample_filtered(float *logits, int R, int V, int ld, float temp, int top_k,
@@ -1261,10 +1291,11 @@ extern "C" int g2b_sample_filtered(float *logits, int R, int V, int ld, float te
     G2B_REFUSE("sample_filtered: temperature sampling needs the per-slot state");
   if (!recent && penalty != 1.f && (!seq_state || !slots || state_words < SS_RING + SS_RING_WORDS))
     G2B_REFUSE("sample_filtered: a repeat penalty without the recent ids needs the per-slot records with their rings");
-  // slices per row: 32 while that is at most about one round of blocks (three of them fit an SM), else 16, 8, 4
-  int n_slices = FILTER_SPLITS;
+  // slices per row: as many as there are lists while that is at most about one round of blocks (three of
+  // them fit an SM), else half as many, down to 4
+  int n_slices = 2048 / slice_cap(top_k);
   while (n_slices > 4 && (long long)n_slices * R > 3LL * g2b_sm_count()) n_slices >>= 1;
-  const bool slices = cand && temp > 0.f && top_k > 0 && top_k <= LOCAL_CAP && V >= 8192 &&
+  const bool slices = cand && temp > 0.f && top_k > 0 && top_k <= MAX_SLICE_CAP && V >= 8192 &&
                       (long long)n_slices * R <= 3LL * g2b_sm_count();
   if (slices) {
     g2b_launch(filter_slices_kernel, dim3(n_slices, R), dim3(FILTER_THREADS), 0, stream,

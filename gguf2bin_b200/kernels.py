@@ -386,7 +386,7 @@ def sample_filtered(logits, temperature, top_k, top_p, penalty, recent, recent_n
             [c_void_p, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_void_p, c_int,
              c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
     cand = None
-    if temperature > 0.0 and 0 < top_k <= 64 and V >= 8192:
+    if temperature > 0.0 and 0 < top_k <= 256 and V >= 8192:
         # a small top_k over a large vocabulary: many blocks per row list the candidates first
         words = _fn("sampling.cu", "g2b_sample_filtered_scratch_words", [c_int])
         cand = _scratch_buffer((logits.device, "filter"), int(words(max(R, 64))), torch.int32)

@@ -240,7 +240,8 @@ def test_temperature_sampling_of_a_large_vocabulary(V, scale):
 
 @pytest.mark.parametrize("V,ties", [(2011, False), (151936, False), (40000, True)])
 @pytest.mark.parametrize("top_k,top_p,penalty", [(40, 0.9, 1.1), (0, 0.9, 1.0), (5, 1.0, 1.3), (0, 1.0, 1.0), (1, 0.5, 1.0),
-                                                 (2048, 0.95, 1.0), (3000, 0.9, 1.1)])
+                                                 (2048, 0.95, 1.0), (3000, 0.9, 1.1), (64, 0.99, 1.1), (100, 0.9, 1.1),
+                                                 (256, 1.0, 1.0), (257, 0.97, 1.2)])
 def test_sampling_filtered(top_k, top_p, penalty, V, ties):
     """Repeat penalty, top-k, top-p and the draw against the plain sampler: a small and a real
     vocabulary; a top_k that is listed and sorted (up to 2,048) and one that is not; and logits
