@@ -591,16 +591,31 @@ __device__ __forceinline__ void walk_bins(const int *hist, int above0, int want,
   }
   const unsigned hit = __ballot_sync(0xffffffffu, above0 + incl >= want);
   const int owner = hit ? __ffs(hit) - 1 : 31;
-  int run = above0 + incl - mine, chosen = hi - 63;
-  if (lane == owner) {
-    for (int d = hi; d > hi - 64; --d) {
-      if (run + hist[d] >= want) { chosen = d; break; }
-      run += hist[d];
-    }
-    if (!hit) run -= hist[chosen];
+  // the owner's 64 bins by all lanes, two each, from the top down
+  const int top = 2047 - 64 * owner;
+  const int before = __shfl_sync(0xffffffffu, above0 + incl - mine, owner);      // count above the owner's bins
+  const int h0 = hist[top - 2 * lane], h1 = hist[top - 2 * lane - 1];
+  int pair = h0 + h1;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, pair, o);
+    if (lane >= o) pair += up;
   }
-  *chosen_out = __shfl_sync(0xffffffffu, chosen, owner);
-  *above_out = __shfl_sync(0xffffffffu, run, owner);
+  const int c0 = before + pair - h1, c1 = before + pair;       // counts down to and including bin top - 2 lane, top - 2 lane - 1
+  const unsigned r0 = __ballot_sync(0xffffffffu, c0 >= want), r1 = __ballot_sync(0xffffffffu, c1 >= want);
+  int chosen, above;
+  if (r0 | r1) {
+    const int l0 = r0 ? __ffs(r0) - 1 : 32, l1 = r1 ? __ffs(r1) - 1 : 32;
+    const bool first = l0 <= l1;                     // the upper bin of lane l0 comes before the lower bin of lane l1 >= l0
+    const int l = first ? l0 : l1;
+    chosen = top - 2 * l - (first ? 0 : 1);
+    above = __shfl_sync(0xffffffffu, first ? c0 - h0 : c1 - h1, l);
+  } else {                                           // the count is never reached: the lowest bin
+    chosen = top - 63;
+    above = __shfl_sync(0xffffffffu, c1 - h1, 31);
+  }
+  *chosen_out = chosen;
+  *above_out = above;
 }
 
 // Sorts the first n entries of the list: key descending, then index ascending.
@@ -637,17 +652,27 @@ __device__ void rank_sort(ShortList &L, int n) {
   uint32_t *tkey = reinterpret_cast<uint32_t *>(L.e);
   int *tidx = L.hist;
   __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const uint32_t k = L.key[i];
-    const int id = L.idx[i];
+  // four threads share an entry: each counts over a quarter of the list
+  const int per_trip = blockDim.x >> 2, q = threadIdx.x & 3;
+  for (int base = 0; base < n; base += per_trip) {
+    const int i = base + (threadIdx.x >> 2);
+    const bool live = i < n;
+    const uint32_t k = live ? L.key[i] : 0u;
+    const int id = live ? L.idx[i] : 0;
     int before = 0;
+    if (live) {
 #pragma unroll 4
-    for (int j = 0; j < n; ++j) {
-      const uint32_t kj = L.key[j];
-      before += (kj > k || (kj == k && L.idx[j] < id)) ? 1 : 0;
+      for (int j = q; j < n; j += 4) {
+        const uint32_t kj = L.key[j];
+        before += (kj > k || (kj == k && L.idx[j] < id)) ? 1 : 0;
+      }
     }
-    tkey[before] = k;
-    tidx[before] = id;
+    before += __shfl_xor_sync(0xffffffffu, before, 1);
+    before += __shfl_xor_sync(0xffffffffu, before, 2);
+    if (live && q == 0) {
+      tkey[before] = k;
+      tidx[before] = id;
+    }
   }
   __syncthreads();
   for (int i = threadIdx.x; i < n; i += blockDim.x) { L.key[i] = tkey[i]; L.idx[i] = tidx[i]; }
