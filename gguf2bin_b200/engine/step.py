@@ -58,6 +58,14 @@ class StepEntry:
     want: Seq[int] = field(default_factory=tuple)
 
 
+class _PaddingSequence:
+    """What stands in for a sequence in the rows that fill a prompt step up to a multiple of
+    ``PROMPT_ROW_STEP``: the cache's spare slot and spare page, nothing before it."""
+
+    def __init__(self, cache: Cache):
+        self.slot, self.pages, self.length = cache.spare_slot, [cache.spare_page], 0
+
+
 class Engine:
     """A model with its cache and scratch memory; ``step`` is the one way tokens run.
 
@@ -66,7 +74,13 @@ class Engine:
     the kernels read from the step's metadata on the device.  So when a shape comes back, the
     launches of its forward pass are captured once in a CUDA graph and replayed from then on:
     a prompt step is a few hundred launches, and the host's share of it (a few microseconds
-    each) otherwise competes with the device's."""
+    each) otherwise competes with the device's.  So that prompts of other lengths find a graph
+    too, a prompt step's rows are filled up to a multiple of ``PROMPT_ROW_STEP`` with the tokens of
+    a padding sequence on the cache's spare page: what the launches depend on is then the number
+    of rows, of sequences, of attention tiles and of wanted places and the width of the page
+    table, and prompts of 449 to 512 tokens, say, share one graph."""
+
+    PROMPT_ROW_STEP = 64         # at most one page of padding tokens (the cache has one spare page)
 
     GRAPH_MIN_TOKENS = 32        # smaller prompt steps are cheap to launch
     GRAPHS_KEPT = 8
@@ -85,6 +99,7 @@ class Engine:
         self._graphs: "OrderedDict[tuple, tuple]" = OrderedDict()    # shape -> (graph, generation, logits)
         self._seen: "OrderedDict[tuple, int]" = OrderedDict()        # shapes run plainly so far
         self.decode_runners: "OrderedDict[tuple, object]" = OrderedDict()
+        self._padding = _PaddingSequence(self.cache)
         self.step_graph_captures = 0       # CUDA graphs captured so far: of prompt-step shapes,
         self.decode_graph_captures = 0     # and of decode shapes (engine/decode.py)
 
@@ -214,11 +229,25 @@ class Engine:
         # the pinned staging buffer is reused: the previous step's copy must be over
         torch.cuda.current_stream().synchronize()
         self.check()                 # a kernel of an earlier step that gave up a wait is reported here
-        ctx, want_rows, n_want = self.build_context(entries)
-        logits = self._forward(entries, ctx, want_rows, n_want)
+        run = self._filled_up(entries)
+        ctx, want_rows, n_want = self.build_context(run)
+        logits = self._forward(run, ctx, want_rows, n_want)
         for e in entries:
             e.seq.length += len(e.tokens)
         return logits
+
+    def _filled_up(self, entries: Seq[StepEntry]) -> Seq[StepEntry]:
+        """The step's entries, with a last one of padding tokens when the step is one that graphs are
+        kept for (a prompt step of ``GRAPH_MIN_TOKENS`` rows and more) and its rows are no multiple
+        of ``PROMPT_ROW_STEP``.  The padding's rows are rows of a sequence of their own (nothing of
+        the others' results depends on them); its keys and values land on the spare page."""
+        T = sum(len(e.tokens) for e in entries)
+        if not self.step_graphs or T == len(entries) or T < self.GRAPH_MIN_TOKENS:
+            return entries
+        fill = -T % self.PROMPT_ROW_STEP
+        if fill == 0:
+            return entries
+        return list(entries) + [StepEntry(self._padding, [0] * fill, ())]
 
     def _forward(self, entries, ctx: StepContext, want_rows, n_want) -> Optional[torch.Tensor]:
         """The model's forward pass of this step: replayed from a graph when the step's shape
@@ -237,7 +266,9 @@ class Engine:
             key = ("single", ctx.n_seqs, tuple(len(e.want) for e in entries), ctx.page_table.shape[1],
                    self._meta_dev.data_ptr())
         else:
-            key = (tuple(ctx.q_lens), tuple(ctx.past_lens), tuple(len(e.want) for e in entries),
+            # which tokens, positions, pages, tiles and places is data on the device; the launches see
+            # only how many there are (the same numbers fix where each table lies in the step's metadata)
+            key = ("prompt", ctx.n_tokens, ctx.n_seqs, ctx.n_attn_tiles, ctx.n_attn_tiles_wide, n_want,
                    ctx.page_table.shape[1], self._meta_dev.data_ptr())
         hit = self._graphs.get(key)
         if hit is not None:

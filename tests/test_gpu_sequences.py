@@ -164,7 +164,8 @@ def test_mixed_steps(name, dtype):
 
 def test_padding_rows_change_nothing():
     """A batch with a one-token neighbour gives bit-equal logits to the same request
-    alone: there is no padding, and no reduction spans sequences."""
+    alone: rows of padding (the step is filled up to 64 rows: 14 of them alone, 13 with
+    the neighbour) and rows of other sequences change no bit, no reduction spans rows."""
     from gguf2bin_b200.engine import StepEntry
     for dtype in ("float32", "bfloat16"):
         eng = make_engine("b", dtype)
@@ -256,6 +257,51 @@ def test_a_shape_that_comes_back_is_replayed_from_a_graph(dtype):
         else:
             eng.close_sequence(hold.pop())
     assert len(eng._graphs) == 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompts_of_other_lengths_find_a_graph(dtype):
+    """Prompt steps are filled up to a multiple of 64 rows with a padding sequence on the cache's
+    spare page, so prompts of 129 to 192 tokens are one shape: the first runs plainly, the second
+    is captured, the others replay that graph, each with its own length, tokens, slot and pages and
+    each against the plain implementation at every place.  The same for two prompts in one step
+    whose lengths change while their sum's bucket and their tiles do not.  A length of exactly 192
+    needs no padding and is a shape of its own.  Nothing is held by the padding."""
+    from gguf2bin_b200.engine import StepEntry
+    name = "c"
+    eng = make_engine(name, dtype, max_tokens=4096)
+    storage = "float32" if dtype == "float32" else "bfloat16"
+    def prompt_graphs():
+        return sum(1 for key in eng._graphs if key[0] == "prompt")
+    for i, n in enumerate((150, 129, 191, 170, 135)):
+        toks = random_tokens(name, n, 400 + i)
+        s = eng.open_sequence()
+        places = (0, n // 2, n - 1)
+        got = eng.step([StepEntry(s, toks, places)]).cpu().numpy()
+        assert_close(got, plain_logits(name, storage, toks)[list(places)], dtype, f"prompt of {n}")
+        # and it decodes on from there: the padding left nothing in its pages
+        nxt = random_tokens(name, 1, 450 + i)
+        got = eng.step([StepEntry(s, nxt, [0])]).cpu().numpy()
+        assert_close(got, plain_logits(name, storage, toks + nxt)[-1:], dtype, f"token after a prompt of {n}")
+        if i % 2:
+            eng.close_sequence(s)
+    assert prompt_graphs() == 1, "five lengths of one bucket: one graph"
+    for i, (na, nb) in enumerate(((100, 60), (110, 50), (127, 40), (90, 64))):     # 154 to 167 rows, three tiles of 64 rows and two of 128
+        a, b = random_tokens(name, na, 500 + i), random_tokens(name, nb, 550 + i)
+        sa, sb = eng.open_sequence(), eng.open_sequence()
+        got = eng.step([StepEntry(sa, a, (na - 1,)), StepEntry(sb, b, (0, nb - 1))]).cpu().numpy()
+        want = np.stack([plain_logits(name, storage, a)[-1], plain_logits(name, storage, b)[0],
+                         plain_logits(name, storage, b)[-1]])
+        assert_close(got, want, dtype, f"prompts of {na} and {nb}")
+        eng.close_sequence(sa)
+        eng.close_sequence(sb)
+    assert prompt_graphs() == 2
+    toks = random_tokens(name, 192, 600)
+    s = eng.open_sequence()
+    assert_close(eng.step([StepEntry(s, toks, range(192))]).cpu().numpy(), plain_logits(name, storage, toks), dtype,
+                 "prompt of 192")
+    eng.close_sequence(s)
+    assert prompt_graphs() == 2, "a shape seen once is not captured"
 
 
 @pytest.mark.parametrize("name,dtype,seed", [("b", "float32", 1), ("c", "bfloat16", 2), ("d", "bfloat16", 3), ("d", "float32", 4)])
