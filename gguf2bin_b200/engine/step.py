@@ -83,7 +83,7 @@ class Engine:
     PROMPT_ROW_STEP = 64         # at most one page of padding tokens (the cache has one spare page)
 
     GRAPH_MIN_TOKENS = 32        # smaller prompt steps are cheap to launch
-    GRAPHS_KEPT = 8
+    GRAPHS_KEPT = 64             # one per 64-token bucket of prompt lengths up to 4,096; a graph holds launches, no buffers
     DECODE_RUNNERS_KEPT = 24     # shapes of decode steps whose buffers and graphs are kept (engine/decode.py)
 
     def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None,
@@ -251,7 +251,8 @@ class Engine:
 
     def _forward(self, entries, ctx: StepContext, want_rows, n_want) -> Optional[torch.Tensor]:
         """The model's forward pass of this step: replayed from a graph when the step's shape
-        has been seen before, captured at its second appearance, run plainly otherwise."""
+        has been captured, captured at its second appearance (one token per sequence) or its third
+        (prompts), run plainly otherwise."""
         single = ctx.all_single
         if single:
             # One token per sequence: the kernels take every position from device memory, so one
@@ -278,8 +279,10 @@ class Engine:
                 graph.replay()
                 return logits
             del self._graphs[key]                     # scratch buffers moved since the capture
-        if self._seen.get(key, 0) >= 1:
-            # the shape ran plainly before, so every scratch buffer it needs exists already
+        if self._seen.get(key, 0) >= (1 if single else 2):
+            # The shape ran plainly before, so every scratch buffer it needs exists already.  A prompt
+            # shape is captured when it comes for the third time: a capture costs as much as two or three
+            # plain steps, and of the shapes of ragged batches most never come back.
             torch.cuda.current_stream().synchronize()
             generation = self.workspace.generation
             graph, logits = capture_graph(lambda: self.model.forward(ctx, self.cache, want_rows, n_want))

@@ -229,7 +229,7 @@ def test_trace_run_program(dtype, tmp_path):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_a_shape_that_comes_back_is_replayed_from_a_graph(dtype):
     """Steps of one shape (two prompts of 70 and 40 tokens, logits wanted at three places):
-    the first runs plainly, the second is captured in a CUDA graph, later ones replay it.
+    the first two run plainly, the third is captured in a CUDA graph, later ones replay it.
     Every run has other tokens, other slots and other pages, and each is compared with the
     plain implementation; the same tokens again give the same bits as the plain run did."""
     from gguf2bin_b200.engine import StepEntry
@@ -262,9 +262,9 @@ def test_a_shape_that_comes_back_is_replayed_from_a_graph(dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_prompts_of_other_lengths_find_a_graph(dtype):
     """Prompt steps are filled up to a multiple of 64 rows with a padding sequence on the cache's
-    spare page, so prompts of 129 to 192 tokens are one shape: the first runs plainly, the second
+    spare page, so prompts of 129 to 192 tokens are one shape: the first two run plainly, the third
     is captured, the others replay that graph, each with its own length, tokens, slot and pages and
-    each against the plain implementation at every place.  The same for two prompts in one step
+    each against the plain implementation at three places.  The same for two prompts in one step
     whose lengths change while their sum's bucket and their tiles do not.  A length of exactly 192
     needs no padding and is a shape of its own.  Nothing is held by the padding."""
     from gguf2bin_b200.engine import StepEntry
