@@ -896,6 +896,7 @@ __device__ int list_from_slices(const int *__restrict__ cand, int cap, int want,
   __syncthreads();
   if (threadIdx.x < MAX_SLICES) s_len[0][threadIdx.x] = threadIdx.x < lists0 ? cand[threadIdx.x] : 0;
   __syncthreads();
+  G2B_STAMP(12);
   const int my_len = s_len[0][threadIdx.x & 31];      // every warp looks at all the lengths
   if (__any_sync(0xffffffffu, my_len < 0 || my_len > cap)) return -1;
   for (int t = threadIdx.x; t < LIST_CAP; t += blockDim.x) {
@@ -905,6 +906,7 @@ __device__ int list_from_slices(const int *__restrict__ cand, int cap, int want,
     }
   }
   __syncthreads();
+  G2B_STAMP(13);
   int from = 0;
   for (int lists = lists0; lists > 1; lists >>= 1, from ^= 1) {
     const uint32_t *ik = key[from];
@@ -927,6 +929,7 @@ __device__ int list_from_slices(const int *__restrict__ cand, int cap, int want,
       s_len[from ^ 1][threadIdx.x] = min(want, s_len[from][2 * threadIdx.x] + s_len[from][2 * threadIdx.x + 1]);
     __syncthreads();
   }
+  G2B_STAMP(14);
   const int n = s_len[from][0];
   if (from == 1) {                                   // (an odd number of levels: the result is in the second pair of arrays)
     for (int i = threadIdx.x; i < n; i += blockDim.x) { L.key[i] = key[1][i]; L.idx[i] = idx[1][i]; }
