@@ -82,7 +82,7 @@ class Engine:
 
     PROMPT_ROW_STEP = 64         # at most one page of padding tokens (the cache has one spare page)
 
-    GRAPH_MIN_TOKENS = 32        # smaller prompt steps are cheap to launch
+    GRAPH_MIN_TOKENS = 2         # every step that is not one token per sequence (those have their own graphs)
     GRAPHS_KEPT = 64             # one per 64-token bucket of prompt lengths up to 4,096; a graph holds launches, no buffers
     DECODE_RUNNERS_KEPT = 24     # shapes of decode steps whose buffers and graphs are kept (engine/decode.py)
 
@@ -238,7 +238,7 @@ class Engine:
 
     def _filled_up(self, entries: Seq[StepEntry]) -> Seq[StepEntry]:
         """The step's entries, with a last one of padding tokens when the step is one that graphs are
-        kept for (a prompt step of ``GRAPH_MIN_TOKENS`` rows and more) and its rows are no multiple
+        kept for (any step that is not one token per sequence) and its rows are no multiple
         of ``PROMPT_ROW_STEP``.  The padding's rows are rows of a sequence of their own (nothing of
         the others' results depends on them); its keys and values land on the spare page."""
         T = sum(len(e.tokens) for e in entries)
