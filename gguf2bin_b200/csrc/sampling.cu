@@ -24,7 +24,9 @@
 
 G2B_DEFINE_LAST_ERROR
 
+#ifndef SAMPLE_THREADS
 #define SAMPLE_THREADS 1024
+#endif
 
 #ifdef G2B_SAMPLE_TIMING
 // Development aid (off unless built with -DG2B_SAMPLE_TIMING): the clock of block (0, 0) at the ends
@@ -870,15 +872,19 @@ filter_slices_kernel(float *__restrict__ logits, int V, int ld, float temp, int 
   G2B_STAMP(5);
 }
 
-// How many entries of the sorted list (zk, zi)[0, n) belong before the entry (k, id).
-__device__ __forceinline__ int count_before(const uint32_t *zk, const int *zi, int n, uint32_t k, int id) {
-  int lo = 0, hi = n;
-  while (lo < hi) {
-    const int mid = (lo + hi) >> 1;
-    const uint32_t mk = zk[mid];
-    if (mk > k || (mk == k && zi[mid] < id)) lo = mid + 1; else hi = mid;
+// How many entries of the sorted list (zk, zi)[0, n), n <= cap (a power of two), belong before the
+// entry (k, id): a search without branches, the same steps for every lane.
+__device__ __forceinline__ int count_before(const uint32_t *zk, const int *zi, int n, int cap, uint32_t k, int id) {
+  int pos = 0;
+  for (int step = cap; step > 0; step >>= 1) {
+    const int m = pos + step;                        // are the first m entries all before (k, id)?
+    const int at = min(m, n) - 1;
+    const uint32_t mk = zk[max(at, 0)];
+    const int mi = zi[max(at, 0)];
+    const bool before = m <= n && (mk > k || (mk == k && mi < id));
+    pos = before ? m : pos;
   }
-  return lo;
+  return pos;
 }
 
 // The best `want` entries of a row from its slices' sorted lists: the lists are merged in pairs,
@@ -889,8 +895,8 @@ __device__ __forceinline__ int count_before(const uint32_t *zk, const int *zi, i
 __device__ int list_from_slices(const int *__restrict__ cand, int cap, int want, ShortList &L) {
   static_assert(LIST_CAP == 2048, "the lists side by side fill the list's arrays");
   __shared__ int s_len[2][MAX_SLICES];
-  uint32_t *key[2] = {L.key, reinterpret_cast<uint32_t *>(L.e)};
-  int *idx[2] = {L.idx, L.hist};
+  uint32_t *ik = L.key, *ok = reinterpret_cast<uint32_t *>(L.e);      // this level's lists, the next level's
+  int *ii = L.idx, *oi = L.hist;
   const int shift = cap == 64 ? 6 : (cap == 128 ? 7 : 8);     // cap is 64, 128 or 256
   const int lists0 = LIST_CAP >> shift;
   __syncthreads();
@@ -909,16 +915,12 @@ __device__ int list_from_slices(const int *__restrict__ cand, int cap, int want,
   G2B_STAMP(13);
   int from = 0;
   for (int lists = lists0; lists > 1; lists >>= 1, from ^= 1) {
-    const uint32_t *ik = key[from];
-    const int *ii = idx[from];
-    uint32_t *ok = key[from ^ 1];
-    int *oi = idx[from ^ 1];
     for (int t = threadIdx.x; t < (lists << shift); t += blockDim.x) {
       const int mine = t >> shift, j = t & (cap - 1), other = mine ^ 1;
       if (j < s_len[from][mine]) {
         const uint32_t k = ik[t];
         const int id = ii[t];
-        const int place = j + count_before(ik + (other << shift), ii + (other << shift), s_len[from][other], k, id);
+        const int place = j + count_before(ik + (other << shift), ii + (other << shift), s_len[from][other], cap, k, id);
         if (place < want) {
           ok[((mine >> 1) << shift) + place] = k;
           oi[((mine >> 1) << shift) + place] = id;
@@ -928,11 +930,13 @@ __device__ int list_from_slices(const int *__restrict__ cand, int cap, int want,
     if (threadIdx.x < lists / 2)
       s_len[from ^ 1][threadIdx.x] = min(want, s_len[from][2 * threadIdx.x] + s_len[from][2 * threadIdx.x + 1]);
     __syncthreads();
+    uint32_t *tk = ik; ik = ok; ok = tk;
+    int *ti = ii; ii = oi; oi = ti;
   }
   G2B_STAMP(14);
   const int n = s_len[from][0];
   if (from == 1) {                                   // (an odd number of levels: the result is in the second pair of arrays)
-    for (int i = threadIdx.x; i < n; i += blockDim.x) { L.key[i] = key[1][i]; L.idx[i] = idx[1][i]; }
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { L.key[i] = ik[i]; L.idx[i] = ii[i]; }
     __syncthreads();
   }
   return n;
