@@ -2,9 +2,12 @@
 the wanted places.
 
 A step runs only the tokens it is given, as one ragged batch: the tokens of all
-sequences one after another, each token with its own absolute position, no padding
-anywhere (so padding cannot change a result).  Sequences of a step may be at any
-position: all prompts at once, then one token each, or a prompt cut into pieces.
+sequences one after another, each token with its own absolute position; no sequence is
+padded to another's length.  Rows that fill a step up to a round number of rows (so that
+steps of other lengths find the same launches) are the tokens of a sequence of their own
+on the cache's spare page: no result of the others depends on them.  Sequences of a step
+may be at any position: all prompts at once, then one token each, or a prompt cut into
+pieces.
 
 Before anything is launched the whole step is checked on the host (token ids, room in
 the cache, positions); a refused step changes nothing.
