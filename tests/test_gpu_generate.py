@@ -172,6 +172,39 @@ def test_sampling_over_a_large_vocabulary_inside_the_step(llms, filtered):
         assert o.tokens == want[i], f"request {i}"
 
 
+@pytest.mark.parametrize("name", ["b", "e"])
+def test_graphs_and_rows_of_padding_change_no_token_in_float32(name):
+    """Sixty generation calls drawn at random (1 to 20 requests of 1 to 80 prompt tokens, 1 to 30
+    new tokens, batches of 1 to 16, stop ids that end requests at any step, four ways of sampling)
+    through an engine that replays graphs, fills its steps up and keeps rows of padding, and
+    through one that launches every step plainly with exactly its own rows: in 32-bit arithmetic
+    no row's result depends on the rows beside it, so every token and every reason to stop agrees.
+    Nothing stays held in either cache."""
+    from gguf2bin_b200.api import LLM
+    rng = np.random.default_rng(11)
+    vocab = TINY[name]["vocab_size"]
+    room = TINY[name]["max_position_embeddings"] - 35
+    a = LLM(model_folder(name, "float32"), dtype="float32", max_tokens=40 * 128)
+    b = LLM(model_folder(name, "float32"), dtype="float32", max_tokens=40 * 128)
+    b.use_graph = False
+    b.engine.step_graphs = False
+    ways = [dict(temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0),
+            dict(temperature=0.8, top_k=0, top_p=1.0, repeat_penalty=1.0),
+            dict(temperature=0.7, top_k=40, top_p=0.9, repeat_penalty=1.1),
+            dict(temperature=0.9, top_k=0, top_p=0.8, repeat_penalty=1.3)]
+    for it in range(60):
+        prompts = [rng.integers(0, vocab, int(rng.integers(1, min(81, room)))).tolist()
+                   for _ in range(int(rng.integers(1, 21)))]
+        kw = dict(n=int(rng.integers(1, 31)), stop_ids=rng.integers(0, vocab, int(rng.integers(0, vocab // 12))).tolist(),
+                  seed=it, max_batch=int(rng.integers(1, 17)), **ways[it % 4])
+        got, want = a.generate(prompts, **kw), b.generate(prompts, **kw)
+        for i, (x, y) in enumerate(zip(got, want)):
+            assert x.tokens == y.tokens and x.finish_reason == y.finish_reason, f"call {it}, request {i}"
+        for llm in (a, b):
+            assert llm.engine.cache.table.pages.n_held == 0 and llm.engine.cache.table.slots.n_held == 0
+    assert a.engine.graph_captures > 10 and b.engine.graph_captures == 0
+
+
 def test_rows_beyond_the_sequences_change_nothing(llms):
     """Six and eleven sequences decode as steps of eight and sixteen rows (the rows beyond them
     use the cache's spare page and slot), and keep that shape while sequences end: every
