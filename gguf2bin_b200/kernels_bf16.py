@@ -237,15 +237,22 @@ def _tc_shape(M: int, N: int, out: torch.Tensor = None, K: int = 0):
     choose.  Prompts (more than one row of tiles) take the persistent kernel when C can be
     written as tiles (the launcher picks the tile width, and with few tiles K in parts); long prompts
     take pairs of CTAs (persistent = 2; measured 4-9 % faster from 4,096 rows on, the same or
-    slower at 2,048)."""
+    slower at 2,048 with the short K of a small model; with a K of 4,096 and more from 1,024 rows on)."""
     if M <= 128:                       # one row of tiles: the weights stream, as in decode
         if _wstream_case(M, N, K):
             return (0, 0, 3)           # 128 rows of W per CTA, K split over a cluster
         if not (M > 64 and N >= 2048 and K >= 2048 and N <= 65536):      # (else the persistent kernel, below)
             return (128, 3, False) if N >= 32768 else (64, 8, False)
     if out is not None and out.data_ptr() % 16 == 0 and (out.stride(0) * out.element_size()) % 16 == 0:
-        if M >= 4096 and -(-M // 256) * -(-N // 256) >= _sm_count(out.device) // 2:
+        tiles = -(-M // 256) * -(-N // 256)
+        if M >= 4096 and tiles >= _sm_count(out.device) // 2:
             return (256, 6, 2)               # long prompts: pairs of CTAs on 256 x 256 tiles
+        if M >= 1024 and K >= 4096 and tiles >= 48:
+            # A long K (the layer sizes of Qwen3-8B and 14B) from 1,024 rows on: 3 to 9 % faster than the
+            # persistent kernel at 1,024 to 3,072 rows (6144 x 4096 at 2,048 rows: 70.4 against 74.9 us;
+            # 4096 x 12288: 143.9 against 154.3), 5120 x 17408 at 2,048 rows 279 against 392 us; only
+            # 24576 x 4096 at 3,072 rows lost 2 %.  With K up to 3,072 (a small model) it was the same or slower.
+            return (256, 6, 2)
         return (0, 0, True)                  # the launcher picks the width and, with few tiles, parts of K
     return (0, 0, False)
 

@@ -742,7 +742,9 @@ def test_gemm_tc_persistent_k_in_parts(M, N, K):
 
 @pytest.mark.parametrize("bn,stages", [(256, 6), (256, 4)])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (200, 1000, 1032), (2048 + 17, 2560 + 8, 320),
-                                   (4096, 2048, 136), (1500, 6144, 1024), (129, 130 * 8, 72)])
+                                   (4096, 2048, 136), (1500, 6144, 1024), (129, 130 * 8, 72),
+                                   # a long K at a thousand rows: where prompts against big weights take this kernel
+                                   (1100, 4096, 4096), (1024, 2048 + 16, 12288 + 8)])
 def test_gemm_tc_pairs(M, N, K, bn, stages):
     """The product on pairs of CTAs (cta_group::2, tiles of 256 rows): one tile and several per
     pair, a peer CTA whose rows of A or of W lie wholly or partly outside, every epilogue."""

@@ -52,3 +52,17 @@ def test_wide_products_of_65_to_128_rows_go_to_the_persistent_kernel():
         assert _tc_shape(100, 24576, out, 4096) == (0, 0, True)
     assert _tc_shape(100, 4096, out, 12288) == (0, 0, True)        # narrow output beyond 96 rows
     assert _tc_shape(90, 4096, out, 12288) == (0, 0, 3)
+
+
+def test_prompts_of_a_thousand_rows_and_a_long_k_go_to_pairs_of_ctas():
+    import torch
+    out = torch.empty(8, 8, dtype=torch.bfloat16)                   # stands for an aligned output
+    if out.data_ptr() % 16:
+        return
+    out = out.as_strided((1, 8), (8, 1))
+    assert _tc_shape(2048, 6144, out, 4096) == (256, 6, 2)
+    assert _tc_shape(1024, 5120, out, 17408) == (256, 6, 2)
+    assert _tc_shape(1024, 4096, out, 12288) == (256, 6, 2)          # 64 tiles of 256 x 256
+    assert _tc_shape(1000, 6144, out, 4096) == (0, 0, True)
+    assert _tc_shape(2048, 6144, out, 1024) == (0, 0, True)          # the short K of a small model
+    assert _tc_shape(2048, 1024, out, 4096) == (0, 0, True)          # few tiles: the persistent kernel may split K
