@@ -304,12 +304,17 @@ USE_TC_ATTENTION = True      # prompt attention on tcgen05 (else the mma.sync ke
 def attn_prefill_tc(q, out, cache_pages, ctx, n_heads, n_kv_heads, head_dim, page_size, window,
                     scale, defines=(), split=None) -> None:
     """Prompt attention on the tcgen05 tensor cores over the step's 128-row query tiles.  Two
-    kernels with the same interface: two CTAs per SM, a tile each (``attn_prefill_tc.cu``), and,
-    for work lists of at most two tiles per SM (``split``; default by that rule), one CTA per
-    SM whose two softmax groups share a tile's pages (``attn_prefill_tc_split.cu``).
+    kernels with the same interface: two CTAs per SM, a tile each (``attn_prefill_tc.cu``), and
+    one CTA per SM whose two softmax groups share a tile's pages (``attn_prefill_tc_split.cu``;
+    ``split``).  The second by default when the work list is at most one item (tile x head) per SM,
+    or at most two per SM with tiles of a thousand keys and more: 16 heads at 2,048 tokens 26.8
+    against 32.6 us, 1,536 tokens 18.6 against 24.2, 32 heads at 512 tokens 10.0 against 11.5; but
+    eight prompts of 256 tokens (256 items of two and four pages) 14.0 against 10.5 by two CTAs per
+    SM, and 160 items of up to eight pages 14.1 against 12.5.
     ``defines``: another build of the source (the tests' build whose waits run out)."""
     if split is None:
-        split = ctx.n_attn_tiles_wide * n_heads <= 2 * _sm_count(q.device)
+        items, sms = ctx.n_attn_tiles_wide * n_heads, _sm_count(q.device)
+        split = items <= sms or (items <= 2 * sms and getattr(ctx, "max_kv_len", 0) >= 1024)
     f = _fn("attn_prefill_tc_split.cu" if split else "attn_prefill_tc.cu", "g2b_attn_prefill_tc",
             [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
              c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
